@@ -1,0 +1,165 @@
+// Token loader core + prefetching batch pipe.
+//
+// File format (llm.c ".bin"): 64 x int32 header, header[0] == 20240520, header[2] == token count,
+// then uint16 tokens.  A batch is a window of B*T+1 tokens at `pos`: ids[i] = w[i], tgt[i] = w[i+1];
+// pos advances by B*T and wraps to 0 when the next window would overrun the file
+// (semantics of train/gpt.cu:925-945).  Unlike the reference (fseek+fread on the training thread) the
+// file is mmap'ed and windows are expanded to int32 by a worker thread directly into caller-provided
+// (pinned) slots, so the training thread never touches the disk.
+#include <atomic>
+#include <condition_variable>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <fcntl.h>
+#include <mutex>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <thread>
+#include <unistd.h>
+#include <vector>
+
+namespace {
+
+struct Loader {
+  int fd = -1;
+  const uint8_t* map = nullptr;
+  size_t map_bytes = 0;
+  const uint16_t* tok = nullptr;
+  int64_t ntok = 0, pos = 0;
+  int B = 0, T = 0;
+};
+
+struct Job { int slot; int32_t* ids; int32_t* tgt; };
+
+struct Pipe {
+  Loader* ld;
+  std::thread th;
+  std::mutex mu;
+  std::condition_variable cv_job, cv_done;
+  std::deque<Job> jobs;
+  std::vector<int> done;  // per-slot completion counters
+  std::vector<int> want;
+  std::vector<int64_t> slot_pos;
+  bool stop = false;
+};
+
+void fill(Loader* ld, int32_t* ids, int32_t* tgt) {
+  const int64_t n = (int64_t)ld->B * ld->T;
+  if (ld->pos + n + 1 > ld->ntok) ld->pos = 0;
+  const uint16_t* w = ld->tok + ld->pos;
+  for (int64_t i = 0; i < n; i++) { ids[i] = w[i]; tgt[i] = w[i + 1]; }
+  ld->pos += n;
+}
+
+void worker(Pipe* p) {
+  for (;;) {
+    Job j;
+    {
+      std::unique_lock<std::mutex> lk(p->mu);
+      p->cv_job.wait(lk, [&] { return p->stop || !p->jobs.empty(); });
+      if (p->stop && p->jobs.empty()) return;
+      j = p->jobs.front();
+      p->jobs.pop_front();
+    }
+    int64_t before = p->ld->pos;
+    fill(p->ld, j.ids, j.tgt);
+    {
+      std::lock_guard<std::mutex> lk(p->mu);
+      p->slot_pos[j.slot] = before;
+      p->done[j.slot]++;
+    }
+    p->cv_done.notify_all();
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// Returns a handle or nullptr; *err: 1 = cannot open, 2 = bad magic / short header, 3 = too few tokens.
+void* mlb_loader_open(const char* path, int B, int T, int* err) {
+  *err = 0;
+  int fd = open(path, O_RDONLY);
+  if (fd < 0) { *err = 1; return nullptr; }
+  struct stat st;
+  if (fstat(fd, &st) != 0 || (size_t)st.st_size < 256) { close(fd); *err = 2; return nullptr; }
+  void* m = mmap(nullptr, st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
+  if (m == MAP_FAILED) { close(fd); *err = 1; return nullptr; }
+  const int32_t* h = (const int32_t*)m;
+  if (h[0] != 20240520) { munmap(m, st.st_size); close(fd); *err = 2; return nullptr; }
+  int64_t ntok = h[2];
+  int64_t have = ((int64_t)st.st_size - 256) / 2;
+  if (ntok > have) ntok = have;  // truncated file: serve what is there
+  if (ntok < (int64_t)B * T + 1) { munmap(m, st.st_size); close(fd); *err = 3; return nullptr; }
+  madvise(m, st.st_size, MADV_SEQUENTIAL);
+  Loader* ld = new Loader;
+  ld->fd = fd; ld->map = (const uint8_t*)m; ld->map_bytes = st.st_size;
+  ld->tok = (const uint16_t*)((const uint8_t*)m + 256);
+  ld->ntok = ntok; ld->B = B; ld->T = T;
+  return ld;
+}
+int64_t mlb_loader_ntok(void* h) { return ((Loader*)h)->ntok; }
+int64_t mlb_loader_pos(void* h) { return ((Loader*)h)->pos; }
+void mlb_loader_set_pos(void* h, int64_t pos) { ((Loader*)h)->pos = pos; }
+void mlb_loader_next(void* h, int32_t* ids, int32_t* tgt) { fill((Loader*)h, ids, tgt); }
+void mlb_loader_close(void* h) {
+  Loader* ld = (Loader*)h;
+  if (!ld) return;
+  munmap((void*)ld->map, ld->map_bytes);
+  close(ld->fd);
+  delete ld;
+}
+
+void* mlb_pipe_create(void* loader, int nslots) {
+  Pipe* p = new Pipe;
+  p->ld = (Loader*)loader;
+  p->done.assign(nslots, 0);
+  p->want.assign(nslots, 0);
+  p->slot_pos.assign(nslots, 0);
+  p->th = std::thread(worker, p);
+  return p;
+}
+// Queue an asynchronous refill of `slot` (windows are served in submission order).
+void mlb_pipe_submit(void* h, int slot, int32_t* ids, int32_t* tgt) {
+  Pipe* p = (Pipe*)h;
+  {
+    std::lock_guard<std::mutex> lk(p->mu);
+    p->want[slot]++;
+    p->jobs.push_back({slot, ids, tgt});
+  }
+  p->cv_job.notify_one();
+}
+// Block until every refill submitted for `slot` has finished; returns the file position it was cut from.
+int64_t mlb_pipe_wait(void* h, int slot) {
+  Pipe* p = (Pipe*)h;
+  std::unique_lock<std::mutex> lk(p->mu);
+  p->cv_done.wait(lk, [&] { return p->done[slot] >= p->want[slot]; });
+  return p->slot_pos[slot];
+}
+void mlb_pipe_destroy(void* h) {
+  Pipe* p = (Pipe*)h;
+  if (!p) return;
+  {
+    std::lock_guard<std::mutex> lk(p->mu);
+    p->stop = true;
+  }
+  p->cv_job.notify_all();
+  p->th.join();
+  delete p;
+}
+
+// Writes a .bin file in the same format (used by tests and synthetic-shard generation).
+int mlb_write_token_bin(const char* path, const uint16_t* tok, int64_t n) {
+  FILE* f = fopen(path, "wb");
+  if (!f) return 1;
+  int32_t h[64];
+  memset(h, 0, sizeof h);
+  h[0] = 20240520; h[1] = 1; h[2] = (int32_t)n;
+  int bad = fwrite(h, 4, 64, f) != 64 || fwrite(tok, 2, n, f) != (size_t)n;
+  fclose(f);
+  return bad ? 2 : 0;
+}
+
+}  // extern "C"

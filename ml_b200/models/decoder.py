@@ -1,0 +1,220 @@
+"""Llama-style decoder as an explicit forward / backward engine over flat buffers.
+
+Architecture (train/gpt.cu:1-4, forward :450-571, backward :574-747): bias-free linears, pre-norm RMSNorm,
+rotate-half RoPE applied in place to Q and K before qkv is saved, causal MHA, SwiGLU on a fused
+[gate|up] projection, untied LM head; the residual add is fused with the *next* RMSNorm.  Compute dtype
+bf16 on GPU (fp32 on CPU), fp32 master weights / grads / AdamW moments.
+
+Backward is written out by hand rather than recorded by autograd: gradients are accumulated into
+one flat fp32 buffer (dW GEMMs add into it), and at each bucket boundary (LM head, final norm, every
+layer, embedding) a hook fires so a data-parallel engine can start reducing / updating that bucket
+while the rest of backward runs.
+"""
+from __future__ import annotations
+
+import math
+from typing import Callable, Optional
+
+import torch
+
+from .. import ops
+from ..config import Config
+from ..layout import DecoderLayout, flops_per_step
+from ..utils import rng as _rng
+
+
+class GPT:
+    def __init__(self, cfg: Config, B: int, device="cpu", dtype: Optional[torch.dtype] = None,
+                 opt_state: bool = True, alloc_grads: bool = True):
+        cfg.validate()
+        self.cfg = cfg
+        self.B = B
+        self.device = torch.device(device)
+        if dtype is None:
+            dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.dtype = dtype
+        self.layout = L = DecoderLayout(cfg)
+        self.np = L.num_params
+        dev = self.device
+        self.master = torch.zeros(self.np, dtype=torch.float32, device=dev)
+        self.params = self.master if dtype == torch.float32 else torch.zeros(self.np, dtype=dtype, device=dev)
+        self.grads = torch.zeros(self.np, dtype=torch.float32, device=dev) if alloc_grads else None
+        self.m = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
+        self.v = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
+        self.cos, self.sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, dev)
+        self._alloc_acts(B)
+        # hooks: called as hook(name, offset, numel) when a gradient bucket is final
+        self.bucket_hook: Optional[Callable[[str, int, int], None]] = None
+        self.prof = None
+        self.skip = set()
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc_acts(self, B):
+        c = self.cfg
+        BT, C, I, V, Lh = B * c.T, c.C, c.I, c.V, c.L
+        e = lambda *s: torch.empty(*s, dtype=self.dtype, device=self.device)
+        f = lambda *s: torch.empty(*s, dtype=torch.float32, device=self.device)
+        self.x0 = e(BT, C)
+        self.ln1 = [e(BT, C) for _ in range(Lh)]
+        self.qkv = [e(BT, 3 * C) for _ in range(Lh)]
+        self.atty = [e(BT, C) for _ in range(Lh)]
+        self.resid1 = [e(BT, C) for _ in range(Lh)]
+        self.ln2 = [e(BT, C) for _ in range(Lh)]
+        self.gu = [e(BT, 2 * I) for _ in range(Lh)]
+        self.sw = [e(BT, I) for _ in range(Lh)]
+        self.resid2 = [e(BT, C) for _ in range(Lh)]
+        self.rstd1 = [f(BT) for _ in range(Lh)]
+        self.rstd2 = [f(BT) for _ in range(Lh)]
+        self.lse = [f(B, c.H, c.T) for _ in range(Lh)]
+        self.lnf_out = e(BT, C)
+        self.rstdf = f(BT)
+        self.logits = e(BT, V)
+        self.losses = f(BT)
+        # scratch
+        self.proj = e(BT, C)
+        self.dresid = e(BT, C)
+        self.dresid1 = e(BT, C)
+        self.dln = e(BT, C)
+        self.dsw = e(BT, I)
+        self.dgu = e(BT, 2 * I)
+        self.dqkv = e(BT, 3 * C)
+        self.datty = e(BT, C)
+
+    def P(self, off, *shape):
+        n = math.prod(shape)
+        return self.params[off:off + n].view(*shape)
+
+    def G(self, off, *shape):
+        n = math.prod(shape)
+        return self.grads[off:off + n].view(*shape)
+
+    # ------------------------------------------------------------------ init
+    def init_weights(self, seed: int = 1234):
+        """Host xorshift64 / Box-Muller stream consumed in buffer order; std 0.02; o- and down-projections
+        scaled by 1/sqrt(2L); norm weights 1 without consuming the stream (train/gpt.cu:775-806)."""
+        h = _rng.init_decoder(self.layout, seed)
+        self.master.copy_(h.to(self.device))
+        self.sync_params()
+
+    def sync_params(self):
+        if self.params.data_ptr() != self.master.data_ptr():
+            ops.cast(self.params, self.master)
+
+    # ------------------------------------------------------------------ forward
+    def _mark(self, name):
+        if self.prof is not None:
+            self.prof.mark(name)
+
+    def forward(self, ids, B=None, prefix=None, n_pre=0):
+        c, Lo = self.cfg, self.layout
+        B = self.B if B is None else B
+        T, C, I, H, hd = c.T, c.C, c.I, c.H, c.hd
+        BT = B * T
+        assert B <= self.B
+        sl = lambda t: t[:BT]
+        x0 = sl(self.x0)
+        ops.embed_fwd(x0, self.P(Lo.off_wte, c.V, C), ids)
+        if prefix is not None and n_pre > 0:
+            ops.set_prefix(x0, prefix, B, T, n_pre)
+        ops.rmsnorm_fwd(sl(self.ln1[0]), sl(self.rstd1[0]), x0, self.P(Lo.layer(0).ln1, C), c.eps)
+        resid_in = x0
+        for l in range(c.L):
+            o = Lo.layer(l)
+            qkv = sl(self.qkv[l])
+            ops.linear_fwd(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C))
+            if "rope" not in self.skip:
+                ops.rope_fwd(qkv, self.cos, self.sin, B, T, H, hd)
+            self._mark("F_qkv+rope")
+            ops.attn_fwd(sl(self.atty[l]), self.lse[l][:B], qkv, B, T, H, hd)
+            self._mark("F_attn")
+            proj = sl(self.proj)
+            ops.linear_fwd(proj, sl(self.atty[l]), self.P(o.o, C, C))
+            ops.add_rmsnorm_fwd(sl(self.resid1[l]), sl(self.ln2[l]), sl(self.rstd2[l]), resid_in, proj,
+                                self.P(o.ln2, C), c.eps)
+            ops.linear_fwd(sl(self.gu[l]), sl(self.ln2[l]), self.P(o.gate, 2 * I, C))
+            ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
+            ops.linear_fwd(proj, sl(self.sw[l]), self.P(o.down, C, I))
+            if l + 1 < c.L:
+                nw, nout, nrstd = self.P(Lo.layer(l + 1).ln1, C), sl(self.ln1[l + 1]), sl(self.rstd1[l + 1])
+            else:
+                nw, nout, nrstd = self.P(Lo.off_lnf, C), sl(self.lnf_out), sl(self.rstdf)
+            ops.add_rmsnorm_fwd(sl(self.resid2[l]), nout, nrstd, sl(self.resid1[l]), proj, nw, c.eps)
+            resid_in = sl(self.resid2[l])
+            self._mark("F_mlp+norm")
+        ops.linear_fwd(self.logits[:BT], sl(self.lnf_out), self.P(Lo.off_lm, c.V, C))
+        self._mark("F_lmhead")
+        return self.logits[:BT]
+
+    # ------------------------------------------------------------------ backward
+    def _hook(self, name, off, n):
+        if self.bucket_hook is not None:
+            self.bucket_hook(name, off, n)
+
+    def backward(self, ids, tgt, B=None, zero=True, n_pre=0, valid_tokens=None):
+        """Consumes the logits of the last forward (they are overwritten by dlogits)."""
+        c, Lo = self.cfg, self.layout
+        B = self.B if B is None else B
+        T, C, I, H, hd, V = c.T, c.C, c.I, c.H, c.hd, c.V
+        BT = B * T
+        sl = lambda t: t[:BT]
+        if zero:
+            self.grads.zero_()
+        valid = valid_tokens if valid_tokens is not None else BT - B * n_pre
+        logits = self.logits[:BT]
+        ops.ce_fwd_bwd(sl(self.losses), logits, tgt, 1.0 / float(valid))
+        self._mark("B_ce")
+        dln, dresid, dresid1 = sl(self.dln), sl(self.dresid), sl(self.dresid1)
+        ops.linear_dw(self.G(Lo.off_lm, V, C), logits, sl(self.lnf_out))
+        ops.linear_dx(dln, logits, self.P(Lo.off_lm, V, C))
+        self._mark("B_lmhead")
+        last = sl(self.resid2[c.L - 1]) if c.L > 0 else sl(self.x0)
+        ops.rmsnorm_bwd(dresid, self.G(Lo.off_lnf, C), dln, last, self.P(Lo.off_lnf, C), sl(self.rstdf), None)
+        self._mark("B_norm")
+        self._hook("lm", Lo.off_lm, V * C)
+        self._hook("lnf", Lo.off_lnf, C)
+        for l in range(c.L - 1, -1, -1):
+            o = Lo.layer(l)
+            dsw, dgu, dqkv, datty = sl(self.dsw), sl(self.dgu), sl(self.dqkv), sl(self.datty)
+            ops.linear_dw(self.G(o.down, C, I), dresid, sl(self.sw[l]))
+            ops.linear_dx(dsw, dresid, self.P(o.down, C, I))
+            ops.swiglu_bwd(dgu, dsw, sl(self.gu[l]))
+            ops.linear_dw(self.G(o.gate, 2 * I, C), dgu, sl(self.ln2[l]))
+            ops.linear_dx(dln, dgu, self.P(o.gate, 2 * I, C))
+            self._mark("B_mlp_gemm")
+            ops.rmsnorm_bwd(dresid1, self.G(o.ln2, C), dln, sl(self.resid1[l]), self.P(o.ln2, C),
+                            sl(self.rstd2[l]), dresid)
+            self._mark("B_norm")
+            ops.linear_dw(self.G(o.o, C, C), dresid1, sl(self.atty[l]))
+            ops.linear_dx(datty, dresid1, self.P(o.o, C, C))
+            ops.attn_bwd(dqkv, datty, sl(self.qkv[l]), sl(self.atty[l]), self.lse[l][:B], B, T, H, hd)
+            if "rope" not in self.skip:
+                ops.rope_bwd(dqkv, self.cos, self.sin, B, T, H, hd)
+            self._mark("B_attn")
+            ops.linear_dw(self.G(o.qkv, 3 * C, C), dqkv, sl(self.ln1[l]))
+            ops.linear_dx(dln, dqkv, self.P(o.qkv, 3 * C, C))
+            self._mark("B_qkv_gemm")
+            x_in = sl(self.resid2[l - 1]) if l > 0 else sl(self.x0)
+            ops.rmsnorm_bwd(dresid, self.G(o.ln1, C), dln, x_in, self.P(o.ln1, C), sl(self.rstd1[l]), dresid1)
+            self._mark("B_norm")
+            self._hook(f"layer{l}", Lo.layer_base(l), Lo.layer_stride)
+        ops.embed_bwd(self.G(Lo.off_wte, V, C), dresid, ids, T, n_pre)
+        self._hook("wte", Lo.off_wte, V * C)
+
+    # ------------------------------------------------------------------ optimizer / loss
+    def adamw(self, lr, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, t=1, grad_scale=1.0, off=0, n=None):
+        n = self.np - off if n is None else n
+        bc1 = 1.0 - b1 ** t
+        bc2 = 1.0 - b2 ** t
+        s = slice(off, off + n)
+        ops.adamw(self.master[s], self.params[s], self.grads[s], self.m[s], self.v[s],
+                  lr, b1, b2, eps, wd, bc1, bc2, grad_scale)
+
+    def mean_loss(self, B=None, n_pre=0, valid_tokens=None) -> float:
+        """Sum of per-row losses in double over the host / valid (train/gpt.cu:763-772)."""
+        B = self.B if B is None else B
+        BT = B * self.cfg.T
+        valid = valid_tokens if valid_tokens is not None else BT - B * n_pre
+        return float(self.losses[:BT].double().sum().item() / valid)
+
+    def flops_per_step(self, B=None) -> float:
+        return flops_per_step(self.cfg, self.B if B is None else B)
