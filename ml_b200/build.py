@@ -116,7 +116,7 @@ def build_cuda(verbose=False, force=False):
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
         objs = list(ex.map(compile_one, cuda_sources()))
-    cmd = [nvcc, "-shared", "-o", str(CUDA_LIB), *map(str, objs), "-lcudart"]
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(CUDA_LIB), *map(str, objs), "-lcudart"]
     subprocess.run(cmd, check=True)
     _stamp(CUDA_LIB).write_text(h)
     if verbose:

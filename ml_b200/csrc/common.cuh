@@ -1,0 +1,78 @@
+// Shared device/host helpers for the sm_100a kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+typedef __nv_bfloat16 bf16;
+typedef __nv_bfloat162 bf162;
+
+#define MLB_API extern "C" __attribute__((visibility("default")))
+
+// Error word shared by every kernel that can give up on a bounded wait (mbarrier, peer flag).
+// 0 = ok.  Layout of a non-zero value: (code << 24) | detail.  Host reads it with mlb_get_error().
+enum : int {
+  MLB_ERR_NONE = 0,
+  MLB_ERR_MBAR_TIMEOUT = 1,   // an mbarrier wait in a TMA/tcgen05 pipeline ran out
+  MLB_ERR_FLAG_TIMEOUT = 2,   // a wait on a peer/host flag ran out
+  MLB_ERR_BOUNDS = 3,         // a self-check found an index out of range
+};
+// Each translation unit owns one copy (no relocatable device code is used); MLB_DEFINE_ERROR_WORD(tag) also
+// exports mlb_get_error_<tag>() / mlb_clear_error_<tag>() for the host.
+#define MLB_DEFINE_ERROR_WORD(tag)                                             \
+  MLB_API int mlb_get_error_##tag() {                                          \
+    int v = 0;                                                                 \
+    cudaMemcpyFromSymbol(&v, g_mlb_error, sizeof(int));                        \
+    return v;                                                                  \
+  }                                                                            \
+  MLB_API void mlb_clear_error_##tag() {                                       \
+    int v = 0;                                                                 \
+    cudaMemcpyToSymbol(g_mlb_error, &v, sizeof(int));                          \
+  }
+static __device__ int g_mlb_error = 0;
+
+__device__ __forceinline__ void mlb_set_error(int code, int detail) {
+  atomicCAS(&g_mlb_error, 0, (code << 24) | (detail & 0xFFFFFF));
+}
+
+static inline int ceil_div_i(long a, long b) { return (int)((a + b - 1) / b); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum for blockDim.x <= 1024 (multiple of 32). `red` needs 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+struct __align__(16) bf16x8 { bf162 v[4]; };
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  bf162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}

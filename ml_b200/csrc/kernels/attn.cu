@@ -1,0 +1,759 @@
+// Causal flash attention, forward and backward, on tcgen05 tensor cores with TMEM accumulators.
+//
+// Replaces the reference's cuDNN-frontend SDPA graphs (train/attn_cudnn.cuh:31-128).  Like them it reads Q, K and V
+// strided straight out of qkv[B,T,3C] (one TMA tensor map over the [B*T, 3C] matrix; a head is a 64- or 128-column
+// window), writes O into atty[B,T,C], saves the per-row log-sum-exp, and in backward writes dQ, dK, dV strided into
+// dqkv[B,T,3C].  Scale 1/sqrt(hd), causal over the whole sequence, no dropout.
+//
+// Forward, one CTA (128 threads) per 128-query tile: S = Q K^T by tcgen05.mma into TMEM, each thread owns one query
+// row (TMEM lane) for the online softmax, P is written bf16 into 128B-swizzled shared memory and fed back as the A
+// operand of O_blk = P V (V consumed MN-major, i.e. untransposed), O is rescaled in registers.
+// Backward, two kernels that each own their accumulators in TMEM (no atomics, deterministic):
+//   dK/dV kernel per 128-key tile:  S^T = K Q^T, dP^T = V dO^T, P^T and dS^T to shared memory, dV += P^T dO, dK += dS^T Q.
+//   dQ kernel per 128-query tile:   S = Q K^T, dP = dO V^T, dS to shared memory, dQ += dS K.
+// RoPE's backward rotation of dQ/dK can be applied in the epilogue (each thread holds a full head row).
+// Head sizes other than 64/128 (or unaligned strides) use a plain SIMT implementation further down.
+#include "../tc.cuh"
+
+MLB_DEFINE_ERROR_WORD(attn)
+
+namespace {
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr int TILE_BYTES = 128 * 64 * 2;  // one [128 rows x 64 bf16] swizzled chunk = 16 KB
+
+// K-major view of a [128 x (64*chunks)] tile: k-step ks covers 16 elements of the contraction dimension.
+__device__ __forceinline__ uint64_t desc_k(uint32_t base, int ks) {
+  return tc::smem_desc_sw128(base + (ks >> 2) * TILE_BYTES + (ks & 3) * 32, 16, 1024);
+}
+// MN-major view of a [128 contraction rows x (64*chunks)] tile: k-step ks covers 16 rows.
+__device__ __forceinline__ uint64_t desc_mn(uint32_t base, int ks) {
+  return tc::smem_desc_sw128(base + ks * 2048, TILE_BYTES, 1024);
+}
+// Byte offset of element (row r, column c) in a K-major swizzled [128 x 128] bf16 tile made of two 64-column chunks;
+// c must be a multiple of 8 (16-byte unit).
+__device__ __forceinline__ uint32_t sw_off(int r, int c) {
+  return (uint32_t)((c >> 6) * TILE_BYTES + r * 128 + ((((c & 63) >> 3) ^ (r & 7)) << 4));
+}
+
+struct AttnArgs {
+  int B, T, H, hd;
+  float scale;
+  bf16* out;          // fwd: atty ; bwd: dqkv
+  float* lse;         // [B,H,T]
+  const float* delta; // [B,H,T] (bwd)
+  const float* cosT;  // optional fused RoPE-backward tables [T, hd/2]
+  const float* sinT;
+};
+
+// ================================================================== forward
+template <int HD>
+struct FwdSmem {
+  static constexpr int CH = HD / 64;
+  static constexpr int Q = 0;
+  static constexpr int K0 = Q + CH * TILE_BYTES;
+  static constexpr int K1 = K0 + CH * TILE_BYTES;
+  static constexpr int V = K1 + CH * TILE_BYTES;
+  static constexpr int P = V + CH * TILE_BYTES;
+  static constexpr int BAR = P + 2 * TILE_BYTES;
+  static constexpr int TOTAL = BAR + 128 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
+  using S = FwdSmem<HD>;
+  constexpr int CH = HD / 64;
+  constexpr uint32_t TMEM_COLS = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + S::BAR);
+  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 4, *bar_o = bars + 5;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 6);
+
+  const int nq = (a.T + 127) / 128;
+  const int qt = nq - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * 128;
+  const int C = a.H * HD;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int row0 = b * a.T;  // first row of this sample in the [B*T, 3C] matrix
+
+  if (tid == 0) {
+    tc::mbar_init(bar_q, 1); tc::mbar_init(&bar_k[0], 1); tc::mbar_init(&bar_k[1], 1);
+    tc::mbar_init(bar_v, 1); tc::mbar_init(bar_s, 1); tc::mbar_init(bar_o, 1);
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tm);
+  }
+  if (warp == 0) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s = tmem, t_o = tmem + 128;
+  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+
+  const int nkb = qt + 1;
+  if (tid == 0) {
+    tc::mbar_expect_tx(bar_q, CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::Q + c * TILE_BYTES, &tm, bar_q, h * HD + c * 64, row0 + q0);
+    tc::mbar_expect_tx(&bar_k[0], CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::K0 + c * TILE_BYTES, &tm, &bar_k[0], C + h * HD + c * 64, row0);
+    tc::mbar_expect_tx(bar_v, CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm, bar_v, 2 * C + h * HD + c * 64, row0);
+  }
+
+  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);
+  const float sl2 = a.scale * LOG2E;
+  const uint32_t sQ = tc::smem_u32(smem + S::Q), sV = tc::smem_u32(smem + S::V), sP = tc::smem_u32(smem + S::P);
+  float m = -INFINITY, l = 0.f;
+  float o[HD];
+#pragma unroll
+  for (int i = 0; i < HD; i++) o[i] = 0.f;
+  const int qrow = q0 + tid;
+  bool ok = true;
+
+  for (int j = 0; j < nkb && ok; j++) {
+    const int buf = j & 1, k0 = j * 128;
+    if (tid == 0) {
+      if (j + 1 < nkb) {
+        uint8_t* dst = smem + (buf ? S::K0 : S::K1);
+        tc::mbar_expect_tx(&bar_k[buf ^ 1], CH * TILE_BYTES);
+        for (int c = 0; c < CH; c++) tc::tma_load_2d(dst + c * TILE_BYTES, &tm, &bar_k[buf ^ 1], C + h * HD + c * 64, row0 + k0 + 128);
+      }
+      if (j == 0) ok = tc::mbar_wait(bar_q, 0, 10);
+      ok = ok && tc::mbar_wait(&bar_k[buf], (j >> 1) & 1, 11);
+      if (ok) {
+        tc::tc_fence_after();
+        const uint32_t sK = tc::smem_u32(smem + (buf ? S::K1 : S::K0));
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_s, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
+      }
+      tc::mma_commit(bar_s);  // always commit so the other threads' wait is released by the hardware, not by a timeout
+    }
+    if (!tc::mbar_wait(bar_s, j & 1, 12)) { ok = false; break; }
+    tc::tc_fence_after();
+    // ---- pass 1: row maximum (log2 domain)
+    const bool diag = (j == qt);
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < 4; c++) {
+      uint32_t r[32];
+      tc::tmem_ld32(t_s + lane_addr + c * 32, r);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i++) {
+        const int kcol = k0 + c * 32 + i;
+        const float v = __uint_as_float(r[i]);
+        if (!diag || kcol <= qrow) mx = fmaxf(mx, v);
+      }
+    }
+    const float m_new = fmaxf(m, mx * sl2);
+    const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+    // ---- pass 2: P = exp2(s - m), row sum, bf16 P into swizzled shared memory
+    float rs = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < 4; c++) {
+      uint32_t r[32];
+      tc::tmem_ld32(t_s + lane_addr + c * 32, r);
+      tc::tmem_ld_wait();
+      float p[32];
+#pragma unroll
+      for (int i = 0; i < 32; i++) {
+        const int kcol = k0 + c * 32 + i;
+        const float v = exp2f(__uint_as_float(r[i]) * sl2 - m_new);
+        p[i] = (!diag || kcol <= qrow) ? v : 0.f;
+        rs += p[i];
+      }
+#pragma unroll
+      for (int v8 = 0; v8 < 4; v8++) {
+        uint4 pk;
+        pk.x = pack_bf16(p[v8 * 8 + 0], p[v8 * 8 + 1]); pk.y = pack_bf16(p[v8 * 8 + 2], p[v8 * 8 + 3]);
+        pk.z = pack_bf16(p[v8 * 8 + 4], p[v8 * 8 + 5]); pk.w = pack_bf16(p[v8 * 8 + 6], p[v8 * 8 + 7]);
+        *reinterpret_cast<uint4*>(smem + S::P + sw_off(tid, c * 32 + v8 * 8)) = pk;
+      }
+    }
+    l = l * alpha + rs;
+    m = m_new;
+    tc::fence_async_smem();
+    tc::tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc::tc_fence_after();
+      bool okv = tc::mbar_wait(bar_v, j & 1, 13);
+      if (okv) {
+        tc::tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_o, desc_k(sP, ks), desc_mn(sV, ks), idesc_o, ks > 0);
+      }
+      tc::mma_commit(bar_o);
+    }
+    if (!tc::mbar_wait(bar_o, j & 1, 14)) { ok = false; break; }
+    tc::tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < HD / 32; c++) {
+      uint32_t r[32];
+      tc::tmem_ld32(t_o + lane_addr + c * 32, r);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && j + 1 < nkb) {
+      tc::mbar_expect_tx(bar_v, CH * TILE_BYTES);
+      for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm, bar_v, 2 * C + h * HD + c * 64, row0 + k0 + 128);
+    }
+  }
+  if (ok && qrow < a.T) {
+    const float inv = 1.f / l;
+    bf16* dst = a.out + ((size_t)(row0 + qrow)) * C + h * HD;
+#pragma unroll
+    for (int v8 = 0; v8 < HD / 8; v8++) {
+      uint4 pk;
+      pk.x = pack_bf16(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv); pk.y = pack_bf16(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
+      pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
+      *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
+    }
+    a.lse[((size_t)b * a.H + h) * a.T + qrow] = (m + log2f(l)) * LN2;
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ================================================================== backward: delta = rowsum(dO * O)
+__global__ void attn_delta_k(float* __restrict__ delta, const bf16* __restrict__ dout, const bf16* __restrict__ out, int B, int T,
+                             int H, int hd) {
+  const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= (long)B * T * H) return;
+  const int h = w % H;
+  const long bt = w / H;
+  const bf16* po = out + bt * (long)H * hd + h * hd;
+  const bf16* pd = dout + bt * (long)H * hd + h * hd;
+  float s = 0.f;
+  for (int i = lane; i < hd; i += 32) s += __bfloat162float(po[i]) * __bfloat162float(pd[i]);
+  s = warp_sum(s);
+  const int b = bt / T, t = bt % T;
+  if (lane == 0) delta[((long)b * H + h) * T + t] = s;
+}
+
+// Writes one thread's fp32 row (HD values) as bf16 to dst, optionally applying RoPE's backward rotation
+// (d0' = d0 c + d1 s, d1' = d1 c - d0 s on pairs (i, i + HD/2)).
+template <int HD>
+__device__ __forceinline__ void store_row_rope(bf16* dst, float (&v)[HD], const float* cosT, const float* sinT, int t) {
+  if (cosT) {
+    const float* c = cosT + (size_t)t * (HD / 2);
+    const float* s = sinT + (size_t)t * (HD / 2);
+#pragma unroll
+    for (int i = 0; i < HD / 2; i++) {
+      const float d0 = v[i], d1 = v[i + HD / 2], cc = c[i], ss = s[i];
+      v[i] = d0 * cc + d1 * ss;
+      v[i + HD / 2] = d1 * cc - d0 * ss;
+    }
+  }
+#pragma unroll
+  for (int v8 = 0; v8 < HD / 8; v8++) {
+    uint4 pk;
+    pk.x = pack_bf16(v[v8 * 8 + 0], v[v8 * 8 + 1]); pk.y = pack_bf16(v[v8 * 8 + 2], v[v8 * 8 + 3]);
+    pk.z = pack_bf16(v[v8 * 8 + 4], v[v8 * 8 + 5]); pk.w = pack_bf16(v[v8 * 8 + 6], v[v8 * 8 + 7]);
+    *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
+  }
+}
+
+// ================================================================== backward: dK, dV (one CTA per 128-key tile)
+template <int HD>
+struct BwdKVSmem {
+  static constexpr int CH = HD / 64;
+  static constexpr int NBUF = (HD == 64) ? 2 : 1;
+  static constexpr int K = 0;
+  static constexpr int V = K + CH * TILE_BYTES;
+  static constexpr int Q = V + CH * TILE_BYTES;                 // NBUF buffers
+  static constexpr int DO = Q + NBUF * CH * TILE_BYTES;         // NBUF buffers
+  static constexpr int PT = DO + NBUF * CH * TILE_BYTES;
+  static constexpr int DST = PT + 2 * TILE_BYTES;
+  static constexpr int STAT = DST + 2 * TILE_BYTES;             // lse[128], delta[128] floats
+  static constexpr int BAR = STAT + 1024;
+  static constexpr int TOTAL = BAR + 128 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+                                                             const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
+  using S = BwdKVSmem<HD>;
+  constexpr int CH = HD / 64, NBUF = S::NBUF;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + S::BAR);
+  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[2]*/, *bar_s = bars + 3, *bar_d = bars + 4;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 5);
+  float* s_lse = (float*)(smem + S::STAT);
+  float* s_delta = s_lse + 128;
+
+  const int nq = (a.T + 127) / 128;
+  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int k0 = kt * 128;
+  const int C = a.H * HD;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int row0 = b * a.T;
+
+  if (tid == 0) {
+    tc::mbar_init(bar_kv, 1); tc::mbar_init(&bar_q[0], 1); tc::mbar_init(&bar_q[1], 1);
+    tc::mbar_init(bar_s, 1); tc::mbar_init(bar_d, 1);
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tm_qkv);
+    tc::tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 0) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_st = tmem, t_dpt = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 256 + HD;
+  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+
+  auto load_q_do = [&](int i, int buf) {
+    tc::mbar_expect_tx(&bar_q[buf], 2 * CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) {
+      tc::tma_load_2d(smem + S::Q + (buf * CH + c) * TILE_BYTES, &tm_qkv, &bar_q[buf], h * HD + c * 64, row0 + i * 128);
+      tc::tma_load_2d(smem + S::DO + (buf * CH + c) * TILE_BYTES, &tm_do, &bar_q[buf], h * HD + c * 64, row0 + i * 128);
+    }
+  };
+  if (tid == 0) {
+    tc::mbar_expect_tx(bar_kv, 2 * CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) {
+      tc::tma_load_2d(smem + S::K + c * TILE_BYTES, &tm_qkv, bar_kv, C + h * HD + c * 64, row0 + k0);
+      tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm_qkv, bar_kv, 2 * C + h * HD + c * 64, row0 + k0);
+    }
+    load_q_do(kt, 0);
+  }
+  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);
+  const float sl2 = a.scale * LOG2E;
+  const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V);
+  const uint32_t sPT = tc::smem_u32(smem + S::PT), sDST = tc::smem_u32(smem + S::DST);
+  const int krow = k0 + tid;
+  bool ok = true;
+  int it = 0;
+  for (int i = kt; i < nq && ok; i++, it++) {
+    const int buf = (NBUF == 2) ? (it & 1) : 0;
+    const int qphase = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
+    const int q0 = i * 128;
+    if (tid == 0) {
+      if (NBUF == 2 && i + 1 < nq) load_q_do(i + 1, buf ^ 1);
+      if (it == 0) ok = tc::mbar_wait(bar_kv, 0, 20);
+      ok = ok && tc::mbar_wait(&bar_q[buf], qphase, 21);
+      if (ok) {
+        tc::tc_fence_after();
+        const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * CH * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * CH * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
+      }
+      tc::mma_commit(bar_s);
+    }
+    {  // per-query statistics of this block (queries past the sequence end contribute nothing)
+      const int q = q0 + tid;
+      const size_t si = ((size_t)b * a.H + h) * a.T + q;
+      s_lse[tid] = (q < a.T) ? a.lse[si] * LOG2E : INFINITY;
+      s_delta[tid] = (q < a.T) ? a.delta[si] : 0.f;
+    }
+    __syncthreads();
+    if (!tc::mbar_wait(bar_s, it & 1, 22)) { ok = false; break; }
+    tc::tc_fence_after();
+    const bool diag = (i == kt);
+#pragma unroll 1
+    for (int c = 0; c < 4; c++) {
+      uint32_t rs[32], rd[32];
+      tc::tmem_ld32(t_st + lane_addr + c * 32, rs);
+      tc::tmem_ld32(t_dpt + lane_addr + c * 32, rd);
+      tc::tmem_ld_wait();
+      float p[32], ds[32];
+#pragma unroll
+      for (int x = 0; x < 32; x++) {
+        const int qc = c * 32 + x;
+        float pv = exp2f(__uint_as_float(rs[x]) * sl2 - s_lse[qc]);
+        if (diag && (q0 + qc) < krow) pv = 0.f;
+        p[x] = pv;
+        ds[x] = pv * (__uint_as_float(rd[x]) - s_delta[qc]) * a.scale;
+      }
+#pragma unroll
+      for (int v8 = 0; v8 < 4; v8++) {
+        uint4 pk, dk;
+        pk.x = pack_bf16(p[v8 * 8 + 0], p[v8 * 8 + 1]); pk.y = pack_bf16(p[v8 * 8 + 2], p[v8 * 8 + 3]);
+        pk.z = pack_bf16(p[v8 * 8 + 4], p[v8 * 8 + 5]); pk.w = pack_bf16(p[v8 * 8 + 6], p[v8 * 8 + 7]);
+        dk.x = pack_bf16(ds[v8 * 8 + 0], ds[v8 * 8 + 1]); dk.y = pack_bf16(ds[v8 * 8 + 2], ds[v8 * 8 + 3]);
+        dk.z = pack_bf16(ds[v8 * 8 + 4], ds[v8 * 8 + 5]); dk.w = pack_bf16(ds[v8 * 8 + 6], ds[v8 * 8 + 7]);
+        const uint32_t off = sw_off(tid, c * 32 + v8 * 8);
+        *reinterpret_cast<uint4*>(smem + S::PT + off) = pk;
+        *reinterpret_cast<uint4*>(smem + S::DST + off) = dk;
+      }
+    }
+    tc::fence_async_smem();
+    tc::tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc::tc_fence_after();
+      const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * CH * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * CH * TILE_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dv, desc_k(sPT, ks), desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, desc_k(sDST, ks), desc_mn(sQ, ks), idesc_d, (it > 0 || ks > 0));
+      tc::mma_commit(bar_d);
+    }
+    if (!tc::mbar_wait(bar_d, it & 1, 23)) { ok = false; break; }
+    tc::tc_fence_after();
+    if (NBUF == 1 && tid == 0 && i + 1 < nq) load_q_do(i + 1, 0);
+    __syncthreads();  // s_lse / s_delta are rewritten at the top of the next iteration
+  }
+  if (ok) {
+    // The TMEM loads are warp-collective: every thread takes part, only rows inside the sequence are stored.
+    float v[HD];
+    bf16* base = a.out + ((size_t)(row0 + krow)) * 3 * C + h * HD;
+#pragma unroll
+    for (int c = 0; c < HD / 32; c++) {
+      uint32_t r[32];
+      tc::tmem_ld32(t_dk + lane_addr + c * 32, r);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 32; x++) v[c * 32 + x] = __uint_as_float(r[x]);
+    }
+    if (krow < a.T) store_row_rope<HD>(base + C, v, a.cosT, a.sinT, krow);
+#pragma unroll
+    for (int c = 0; c < HD / 32; c++) {
+      uint32_t r[32];
+      tc::tmem_ld32(t_dv + lane_addr + c * 32, r);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 32; x++) v[c * 32 + x] = __uint_as_float(r[x]);
+    }
+    if (krow < a.T) store_row_rope<HD>(base + 2 * C, v, nullptr, nullptr, krow);
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ================================================================== backward: dQ (one CTA per 128-query tile)
+template <int HD>
+struct BwdQSmem {
+  static constexpr int CH = HD / 64;
+  static constexpr int NBUF = (HD == 64) ? 2 : 1;
+  static constexpr int Q = 0;
+  static constexpr int DO = Q + CH * TILE_BYTES;
+  static constexpr int K = DO + CH * TILE_BYTES;               // NBUF
+  static constexpr int V = K + NBUF * CH * TILE_BYTES;         // NBUF
+  static constexpr int DS = V + NBUF * CH * TILE_BYTES;
+  static constexpr int BAR = DS + 2 * TILE_BYTES;
+  static constexpr int TOTAL = BAR + 128 + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+                                                            const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
+  using S = BwdQSmem<HD>;
+  constexpr int CH = HD / 64, NBUF = S::NBUF;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + S::BAR);
+  uint64_t *bar_q = bars, *bar_kv = bars + 1 /*[2]*/, *bar_s = bars + 3, *bar_d = bars + 4;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 5);
+
+  const int nq = (a.T + 127) / 128;
+  const int qt = nq - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * 128;
+  const int C = a.H * HD;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int row0 = b * a.T;
+
+  if (tid == 0) {
+    tc::mbar_init(bar_q, 1); tc::mbar_init(&bar_kv[0], 1); tc::mbar_init(&bar_kv[1], 1);
+    tc::mbar_init(bar_s, 1); tc::mbar_init(bar_d, 1);
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tm_qkv);
+    tc::tma_prefetch_desc(&tm_do);
+  }
+  if (warp == 0) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s = tmem, t_dp = tmem + 128, t_dq = tmem + 256;
+  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+
+  auto load_kv = [&](int j, int buf) {
+    tc::mbar_expect_tx(&bar_kv[buf], 2 * CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) {
+      tc::tma_load_2d(smem + S::K + (buf * CH + c) * TILE_BYTES, &tm_qkv, &bar_kv[buf], C + h * HD + c * 64, row0 + j * 128);
+      tc::tma_load_2d(smem + S::V + (buf * CH + c) * TILE_BYTES, &tm_qkv, &bar_kv[buf], 2 * C + h * HD + c * 64, row0 + j * 128);
+    }
+  };
+  if (tid == 0) {
+    tc::mbar_expect_tx(bar_q, 2 * CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) {
+      tc::tma_load_2d(smem + S::Q + c * TILE_BYTES, &tm_qkv, bar_q, h * HD + c * 64, row0 + q0);
+      tc::tma_load_2d(smem + S::DO + c * TILE_BYTES, &tm_do, bar_q, h * HD + c * 64, row0 + q0);
+    }
+    load_kv(0, 0);
+  }
+  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);
+  const float sl2 = a.scale * LOG2E;
+  const uint32_t sQ = tc::smem_u32(smem + S::Q), sDO = tc::smem_u32(smem + S::DO), sDS = tc::smem_u32(smem + S::DS);
+  const int qrow = q0 + tid;
+  const size_t si = ((size_t)b * a.H + h) * a.T + qrow;
+  const float lse2 = (qrow < a.T) ? a.lse[si] * LOG2E : INFINITY;
+  const float delta = (qrow < a.T) ? a.delta[si] : 0.f;
+  const int nkb = qt + 1;
+  bool ok = true;
+  for (int j = 0; j < nkb && ok; j++) {
+    const int buf = (NBUF == 2) ? (j & 1) : 0;
+    const int kphase = (NBUF == 2) ? ((j >> 1) & 1) : (j & 1);
+    const int k0 = j * 128;
+    const uint32_t sK = tc::smem_u32(smem + S::K + buf * CH * TILE_BYTES), sV = tc::smem_u32(smem + S::V + buf * CH * TILE_BYTES);
+    if (tid == 0) {
+      if (NBUF == 2 && j + 1 < nkb) load_kv(j + 1, buf ^ 1);
+      if (j == 0) ok = tc::mbar_wait(bar_q, 0, 30);
+      ok = ok && tc::mbar_wait(&bar_kv[buf], kphase, 31);
+      if (ok) {
+        tc::tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_s, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dp, desc_k(sDO, ks), desc_k(sV, ks), idesc_s, ks > 0);
+      }
+      tc::mma_commit(bar_s);
+    }
+    if (!tc::mbar_wait(bar_s, j & 1, 32)) { ok = false; break; }
+    tc::tc_fence_after();
+    const bool diag = (j == qt);
+#pragma unroll 1
+    for (int c = 0; c < 4; c++) {
+      uint32_t rs[32], rd[32];
+      tc::tmem_ld32(t_s + lane_addr + c * 32, rs);
+      tc::tmem_ld32(t_dp + lane_addr + c * 32, rd);
+      tc::tmem_ld_wait();
+      float ds[32];
+#pragma unroll
+      for (int x = 0; x < 32; x++) {
+        const int kcol = k0 + c * 32 + x;
+        float pv = exp2f(__uint_as_float(rs[x]) * sl2 - lse2);
+        if (diag && kcol > qrow) pv = 0.f;
+        ds[x] = pv * (__uint_as_float(rd[x]) - delta) * a.scale;
+      }
+#pragma unroll
+      for (int v8 = 0; v8 < 4; v8++) {
+        uint4 dk;
+        dk.x = pack_bf16(ds[v8 * 8 + 0], ds[v8 * 8 + 1]); dk.y = pack_bf16(ds[v8 * 8 + 2], ds[v8 * 8 + 3]);
+        dk.z = pack_bf16(ds[v8 * 8 + 4], ds[v8 * 8 + 5]); dk.w = pack_bf16(ds[v8 * 8 + 6], ds[v8 * 8 + 7]);
+        *reinterpret_cast<uint4*>(smem + S::DS + sw_off(tid, c * 32 + v8 * 8)) = dk;
+      }
+    }
+    tc::fence_async_smem();
+    tc::tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc::tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, desc_k(sDS, ks), desc_mn(sK, ks), idesc_d, (j > 0 || ks > 0));
+      tc::mma_commit(bar_d);
+    }
+    if (!tc::mbar_wait(bar_d, j & 1, 33)) { ok = false; break; }
+    tc::tc_fence_after();
+    if (NBUF == 1 && tid == 0 && j + 1 < nkb) load_kv(j + 1, 0);
+  }
+  if (ok) {
+    float v[HD];
+#pragma unroll
+    for (int c = 0; c < HD / 32; c++) {
+      uint32_t r[32];
+      tc::tmem_ld32(t_dq + lane_addr + c * 32, r);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 32; x++) v[c * 32 + x] = __uint_as_float(r[x]);
+    }
+    if (qrow < a.T) store_row_rope<HD>(a.out + ((size_t)(row0 + qrow)) * 3 * C + h * HD, v, a.cosT, a.sinT, qrow);
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ================================================================== SIMT fallback (any head size <= 256, any T)
+// One block per (query row, head, sample); scores kept in shared memory.
+__global__ void attn_fwd_simt_k(bf16* __restrict__ out, float* __restrict__ lse, const bf16* __restrict__ qkv, int B, int T, int H,
+                                int hd, float scale) {
+  extern __shared__ float sc[];  // T scores + 32 reduce
+  float* red = sc + T;
+  const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z, C = H * hd;
+  const bf16* q = qkv + ((size_t)(b * T + i)) * 3 * C + h * hd;
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) {
+    const bf16* k = qkv + ((size_t)(b * T + j)) * 3 * C + C + h * hd;
+    float s = 0.f;
+    for (int d = 0; d < hd; d++) s += __bfloat162float(q[d]) * __bfloat162float(k[d]);
+    s *= scale;
+    sc[j] = s;
+    mx = fmaxf(mx, s);
+  }
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) { float p = __expf(sc[j] - mx); sc[j] = p; sum += p; }
+  sum = block_sum(sum, red);
+  __syncthreads();
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j <= i; j++) acc += sc[j] * __bfloat162float(qkv[((size_t)(b * T + j)) * 3 * C + 2 * C + h * hd + d]);
+    out[((size_t)(b * T + i)) * C + h * hd + d] = __float2bfloat16(acc / sum);
+  }
+  if (threadIdx.x == 0) lse[((size_t)b * H + h) * T + i] = mx + __logf(sum);
+}
+// dQ for query i.
+__global__ void attn_bwd_q_simt_k(bf16* __restrict__ dqkv, const bf16* __restrict__ dout, const bf16* __restrict__ qkv,
+                                  const float* __restrict__ lse, const float* __restrict__ delta, int B, int T, int H, int hd,
+                                  float scale) {
+  extern __shared__ float sc[];
+  const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z, C = H * hd;
+  const bf16* q = qkv + ((size_t)(b * T + i)) * 3 * C + h * hd;
+  const bf16* dO = dout + ((size_t)(b * T + i)) * C + h * hd;
+  const float L = lse[((size_t)b * H + h) * T + i], D = delta[((size_t)b * H + h) * T + i];
+  for (int j = threadIdx.x; j <= i; j += blockDim.x) {
+    const bf16* k = qkv + ((size_t)(b * T + j)) * 3 * C + C + h * hd;
+    const bf16* v = k + C;
+    float s = 0.f, dp = 0.f;
+    for (int d = 0; d < hd; d++) {
+      s += __bfloat162float(q[d]) * __bfloat162float(k[d]);
+      dp += __bfloat162float(dO[d]) * __bfloat162float(v[d]);
+    }
+    sc[j] = __expf(s * scale - L) * (dp - D) * scale;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j <= i; j++) acc += sc[j] * __bfloat162float(qkv[((size_t)(b * T + j)) * 3 * C + C + h * hd + d]);
+    dqkv[((size_t)(b * T + i)) * 3 * C + h * hd + d] = __float2bfloat16(acc);
+  }
+}
+// dK, dV for key j.
+__global__ void attn_bwd_kv_simt_k(bf16* __restrict__ dqkv, const bf16* __restrict__ dout, const bf16* __restrict__ qkv,
+                                   const float* __restrict__ lse, const float* __restrict__ delta, int B, int T, int H, int hd,
+                                   float scale) {
+  extern __shared__ float sc[];  // p[T], ds[T]
+  float* sp = sc;
+  float* sds = sc + T;
+  const int j = blockIdx.x, h = blockIdx.y, b = blockIdx.z, C = H * hd;
+  const bf16* k = qkv + ((size_t)(b * T + j)) * 3 * C + C + h * hd;
+  const bf16* v = k + C;
+  for (int i = j + threadIdx.x; i < T; i += blockDim.x) {
+    const bf16* q = qkv + ((size_t)(b * T + i)) * 3 * C + h * hd;
+    const bf16* dO = dout + ((size_t)(b * T + i)) * C + h * hd;
+    float s = 0.f, dp = 0.f;
+    for (int d = 0; d < hd; d++) {
+      s += __bfloat162float(q[d]) * __bfloat162float(k[d]);
+      dp += __bfloat162float(dO[d]) * __bfloat162float(v[d]);
+    }
+    const size_t si = ((size_t)b * H + h) * T + i;
+    const float p = __expf(s * scale - lse[si]);
+    sp[i] = p;
+    sds[i] = p * (dp - delta[si]) * scale;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float dk = 0.f, dv = 0.f;
+    for (int i = j; i < T; i++) {
+      dk += sds[i] * __bfloat162float(qkv[((size_t)(b * T + i)) * 3 * C + h * hd + d]);
+      dv += sp[i] * __bfloat162float(dout[((size_t)(b * T + i)) * C + h * hd + d]);
+    }
+    dqkv[((size_t)(b * T + j)) * 3 * C + C + h * hd + d] = __float2bfloat16(dk);
+    dqkv[((size_t)(b * T + j)) * 3 * C + 2 * C + h * hd + d] = __float2bfloat16(dv);
+  }
+}
+
+int g_attn_force_simt = 0;
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+bool tc_ok(const void* qkv, const void* other, int H, int hd) {
+  const int C = H * hd;
+  return !g_attn_force_simt && (hd == 64 || hd == 128) && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)other % 16 == 0) && (C % 8 == 0);
+}
+
+}  // namespace
+
+MLB_API void mlb_attn_force_simt(int on) { g_attn_force_simt = on; }
+
+// out[B,T,C], lse[B,H,T] from qkv[B,T,3C].
+MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, int H, int hd, cudaStream_t st) {
+  const int C = H * hd;
+  const float scale = 1.0f / sqrtf((float)hd);
+  if (tc_ok(qkv, out, H, hd)) {
+    const CUtensorMap* tm = mlb_tmap_cached(qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, 64);
+    if (!tm) return -2;
+    AttnArgs a{B, T, H, hd, scale, (bf16*)out, lse, nullptr, nullptr, nullptr};
+    dim3 grid((T + 127) / 128, H, B);
+    if (hd == 64) {
+      static int once = set_smem(attn_fwd_tc_kernel<64>, FwdSmem<64>::TOTAL);
+      (void)once;
+      attn_fwd_tc_kernel<64><<<grid, 128, FwdSmem<64>::TOTAL, st>>>(*tm, a);
+    } else {
+      static int once = set_smem(attn_fwd_tc_kernel<128>, FwdSmem<128>::TOTAL);
+      (void)once;
+      attn_fwd_tc_kernel<128><<<grid, 128, FwdSmem<128>::TOTAL, st>>>(*tm, a);
+    }
+    return (int)cudaGetLastError();
+  }
+  if (hd > 256) return -4;
+  attn_fwd_simt_k<<<dim3(T, H, B), 128, (T + 32) * sizeof(float), st>>>((bf16*)out, lse, (const bf16*)qkv, B, T, H, hd, scale);
+  return (int)cudaGetLastError();
+}
+
+// dqkv[B,T,3C] from dout[B,T,C], qkv, out, lse.  `delta` is scratch of B*H*T floats.  If cosT/sinT are given, RoPE's
+// backward rotation is applied to dQ and dK before they are stored (tensor-core path only; returns 1 if it was applied,
+// 0 if the caller still has to rotate, <0 or a CUDA error code > 1 on failure).
+MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, int B, int T,
+                         int H, int hd, const float* cosT, const float* sinT, cudaStream_t st) {
+  const int C = H * hd;
+  const float scale = 1.0f / sqrtf((float)hd);
+  {
+    long warps = (long)B * T * H;
+    attn_delta_k<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
+  }
+  if (tc_ok(qkv, dout, H, hd) && ((uintptr_t)dqkv % 16 == 0)) {
+    const CUtensorMap* tq = mlb_tmap_cached(qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, 64);
+    const CUtensorMap* td = mlb_tmap_cached(dout, (uint64_t)B * T, C, C, 128, 64);
+    if (!tq || !td) return -2;
+    AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT};
+    dim3 grid((T + 127) / 128, H, B);
+    if (hd == 64) {
+      static int o1 = set_smem(attn_bwd_kv_tc_kernel<64>, BwdKVSmem<64>::TOTAL);
+      static int o2 = set_smem(attn_bwd_q_tc_kernel<64>, BwdQSmem<64>::TOTAL);
+      (void)o1; (void)o2;
+      attn_bwd_kv_tc_kernel<64><<<grid, 128, BwdKVSmem<64>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_q_tc_kernel<64><<<grid, 128, BwdQSmem<64>::TOTAL, st>>>(*tq, *td, a);
+    } else {
+      static int o1 = set_smem(attn_bwd_kv_tc_kernel<128>, BwdKVSmem<128>::TOTAL);
+      static int o2 = set_smem(attn_bwd_q_tc_kernel<128>, BwdQSmem<128>::TOTAL);
+      (void)o1; (void)o2;
+      attn_bwd_kv_tc_kernel<128><<<grid, 128, BwdKVSmem<128>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_q_tc_kernel<128><<<grid, 128, BwdQSmem<128>::TOTAL, st>>>(*tq, *td, a);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e + 1000;
+    return cosT ? 1 : 0;
+  }
+  if (hd > 256) return -4;
+  attn_bwd_q_simt_k<<<dim3(T, H, B), 128, T * sizeof(float), st>>>((bf16*)dqkv, (const bf16*)dout, (const bf16*)qkv, lse, delta, B, T, H,
+                                                                  hd, scale);
+  attn_bwd_kv_simt_k<<<dim3(T, H, B), 128, 2 * T * sizeof(float), st>>>((bf16*)dqkv, (const bf16*)dout, (const bf16*)qkv, lse, delta, B,
+                                                                       T, H, hd, scale);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e + 1000;
+  return 0;
+}

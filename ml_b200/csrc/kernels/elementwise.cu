@@ -1,0 +1,626 @@
+// Bandwidth-bound kernels of the training step: embedding, RMSNorm (fwd, fused residual-add fwd, bwd), RoPE,
+// SwiGLU, fused cross-entropy, AdamW, vision helpers and casts.  All are written for HBM3e streaming:
+// 16-byte vector accesses, one pass over DRAM per tensor (second passes over a row hit L1/L2), fp32 math,
+// one rounding to bf16 on store.  Formulas follow the reference kernels they replace
+// (train/gpt_kernels.cuh: encoder :225-243, rmsnorm :275-458, rope :645-713, swiglu :589-640, CE :1169-1210,
+// adamw :1357-1400) but none of the code is shared with them.
+#include "../common.cuh"
+
+MLB_DEFINE_ERROR_WORD(elementwise)
+
+namespace {
+
+__device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const bf162* h = reinterpret_cast<const bf162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void embed_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ wte, const int* __restrict__ ids, int C) {
+  const long row = blockIdx.x;
+  const bf16* src = wte + (long)ids[row] * C;
+  bf16* dst = out + row * C;
+  if ((C & 7) == 0) {
+    for (int i = threadIdx.x * 8; i < C; i += blockDim.x * 8)
+      *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+  } else {
+    for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = src[i];
+  }
+}
+__global__ void embed_bwd_k(float* __restrict__ dwte, const bf16* __restrict__ dout, const int* __restrict__ ids, int C,
+                            int T, int n_pre) {
+  const long row = blockIdx.x;
+  if ((int)(row % T) < n_pre) return;
+  float* dst = dwte + (long)ids[row] * C;
+  const bf16* src = dout + row * C;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) atomicAdd(dst + i, __bfloat162float(src[i]));
+}
+__global__ void set_prefix_k(bf16* __restrict__ x, const bf16* __restrict__ prefix, int B, int T, int n_pre, int C) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  long n = (long)B * n_pre * C;
+  if (i >= n) return;
+  int c = i % C;
+  long r = i / C;
+  int b = r / n_pre, p = r % n_pre;
+  x[((long)b * T + p) * C + c] = prefix[i];
+}
+__global__ void gather_prefix_k(bf16* __restrict__ dprefix, const bf16* __restrict__ dresid, int B, int T, int n_pre, int C) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  long n = (long)B * n_pre * C;
+  if (i >= n) return;
+  int c = i % C;
+  long r = i / C;
+  int b = r / n_pre, p = r % n_pre;
+  dprefix[i] = dresid[((long)b * T + p) * C + c];
+}
+
+// ------------------------------------------------------------------ RMSNorm forward (one warp per row)
+// ADD: resid = a + b is stored (bf16) and the norm is taken over the un-rounded fp32 sum.
+template <bool ADD>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, float* __restrict__ rstd, bf16* __restrict__ resid,
+                                                     const bf16* __restrict__ a, const bf16* __restrict__ b,
+                                                     const bf16* __restrict__ w, long rows, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const bf16* pa = a + row * C;
+  const bf16* pb = ADD ? b + row * C : nullptr;
+  float ss = 0.f;
+  if ((C & 7) == 0) {
+    for (int i = lane * 8; i < C; i += 256) {
+      float x[8];
+      load8(pa + i, x);
+      if (ADD) {
+        float y[8];
+        load8(pb + i, y);
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] += y[j];
+        store8(resid + row * C + i, x);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)C + eps);
+    if (lane == 0) rstd[row] = r;
+    for (int i = lane * 8; i < C; i += 256) {
+      float x[8], ww[8];
+      load8(pa + i, x);
+      if (ADD) {
+        float y[8];
+        load8(pb + i, y);
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[j] += y[j];
+      }
+      load8(w + i, ww);
+#pragma unroll
+      for (int j = 0; j < 8; j++) x[j] = x[j] * r * ww[j];
+      store8(out + row * C + i, x);
+    }
+  } else {
+    for (int i = lane; i < C; i += 32) {
+      float x = __bfloat162float(pa[i]);
+      if (ADD) { x += __bfloat162float(pb[i]); resid[row * C + i] = __float2bfloat16(x); }
+      ss += x * x;
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)C + eps);
+    if (lane == 0) rstd[row] = r;
+    for (int i = lane; i < C; i += 32) {
+      float x = __bfloat162float(pa[i]);
+      if (ADD) x += __bfloat162float(pb[i]);
+      out[row * C + i] = __float2bfloat16(x * r * __bfloat162float(w[i]));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward, ONE launch, deterministic
+// dx = add + rstd*w*dy - x*rstd^3/C * sum_c(dy*w*x);   dw[c] += sum_rows dy*x*rstd.
+// Each block walks a strided set of rows (warp per row) keeping per-column dw partial sums in registers/shared
+// memory, writes its partial row to `partial[block][C]`, and the last block to finish (atomic ticket) folds the
+// partials into dw in a fixed order.  `partial` is scratch: gridDim.x*C floats; `ticket` one int that is 0 on
+// entry and left 0 on exit.
+template <int VPL>  // VPL = C / 256 (vectors of 8 per lane); 0 = generic C (scalar path)
+__global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, float* __restrict__ dw, const bf16* __restrict__ dy,
+                                                     const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                     const float* __restrict__ rstd, const bf16* __restrict__ add, long rows,
+                                                     int C, float* __restrict__ partial, int* __restrict__ ticket) {
+  extern __shared__ float sh[];  // C floats: block-level dw partial
+  __shared__ int is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < C; i += blockDim.x) sh[i] = 0.f;
+  __syncthreads();
+  const float invC = 1.f / (float)C;
+  if (VPL > 0) {
+    constexpr int NV = VPL > 0 ? VPL : 1;
+    constexpr bool CACHE = NV <= 4;  // wider rows re-read w/x/dy from L1 instead of holding them in registers
+    constexpr int NC = CACHE ? NV : 1;
+    float acc[NV][8];
+    float ww[NC][8];
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      if (CACHE) load8(w + (v * 32 + lane) * 8, ww[v]);
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[v][j] = 0.f;
+    }
+    for (long row = (long)blockIdx.x * nwarp + warp; row < rows; row += (long)gridDim.x * nwarp) {
+      const float r = rstd[row];
+      float xv[NC][8], dv[NC][8];
+      float dot = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        const long off = row * C + (v * 32 + lane) * 8;
+        const int cv = CACHE ? v : 0;
+        load8(x + off, xv[cv]);
+        load8(dy + off, dv[cv]);
+        if (!CACHE) load8(w + (v * 32 + lane) * 8, ww[0]);
+#pragma unroll
+        for (int j = 0; j < 8; j++) dot += dv[cv][j] * ww[cv][j] * xv[cv][j];
+      }
+      dot = warp_sum(dot);
+      const float k = r * r * r * invC * dot;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        const long off = row * C + (v * 32 + lane) * 8;
+        const int cv = CACHE ? v : 0;
+        if (!CACHE) { load8(x + off, xv[0]); load8(dy + off, dv[0]); load8(w + (v * 32 + lane) * 8, ww[0]); }
+        float o[8];
+        if (add) load8(add + off, o);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; j++) o[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          o[j] += dv[cv][j] * ww[cv][j] * r - xv[cv][j] * k;
+          acc[v][j] += dv[cv][j] * xv[cv][j] * r;
+        }
+        store8(dx + off, o);
+      }
+    }
+    // fold the 8 warps' register partials in warp order (deterministic)
+    for (int wv = 0; wv < nwarp; wv++) {
+      if (warp == wv) {
+#pragma unroll
+        for (int v = 0; v < NV; v++)
+#pragma unroll
+          for (int j = 0; j < 8; j++) sh[(v * 32 + lane) * 8 + j] += acc[v][j];
+      }
+      __syncthreads();
+    }
+  } else {
+    for (long row = (long)blockIdx.x * nwarp + warp; row < rows; row += (long)gridDim.x * nwarp) {
+      const float r = rstd[row];
+      float dot = 0.f;
+      for (int i = lane; i < C; i += 32)
+        dot += __bfloat162float(dy[row * C + i]) * __bfloat162float(w[i]) * __bfloat162float(x[row * C + i]);
+      dot = warp_sum(dot);
+      const float k = r * r * r * invC * dot;
+      for (int i = lane; i < C; i += 32) {
+        float d = __bfloat162float(dy[row * C + i]), xx = __bfloat162float(x[row * C + i]);
+        float o = d * __bfloat162float(w[i]) * r - xx * k;
+        if (add) o += __bfloat162float(add[row * C + i]);
+        dx[row * C + i] = __float2bfloat16(o);
+        atomicAdd(&sh[i], d * xx * r);  // shared-memory atomics; this path is for odd C only
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < C; i += blockDim.x) partial[(long)blockIdx.x * C + i] = sh[i];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    for (int i = threadIdx.x; i < C; i += blockDim.x) {
+      float s = 0.f;
+      for (int b = 0; b < (int)gridDim.x; b++) s += __ldcg(&partial[(long)b * C + i]);
+      dw[i] += s;
+    }
+    if (threadIdx.x == 0) *ticket = 0;
+  }
+}
+
+// ------------------------------------------------------------------ RoPE (in place on the Q and K slices of qkv[B*T, 3C])
+// pairs (i, i + hd/2); fwd: x0' = x0 c - x1 s, x1' = x1 c + x0 s; bwd uses -s.
+__global__ void rope_k(bf16* __restrict__ qkv, const float* __restrict__ cosT, const float* __restrict__ sinT, long rows, int T,
+                       int H, int hd, float sign) {
+  const int h2 = hd >> 1;
+  const int per_row = 2 * H * (h2 >> 3);  // vectors of 8 pairs per row (q and k)
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * per_row) return;
+  const long row = idx / per_row;
+  int r = idx % per_row;
+  const int which = r / (H * (h2 >> 3));
+  r %= H * (h2 >> 3);
+  const int h = r / (h2 >> 3), v = r % (h2 >> 3);
+  const int t = row % T;
+  bf16* p0 = qkv + row * (3L * H * hd) + (long)which * H * hd + h * hd + v * 8;
+  bf16* p1 = p0 + h2;
+  float a[8], b[8];
+  load8(p0, a);
+  load8(p1, b);
+  const float4* c4 = reinterpret_cast<const float4*>(cosT + (long)t * h2 + v * 8);
+  const float4* s4 = reinterpret_cast<const float4*>(sinT + (long)t * h2 + v * 8);
+  float c[8], s[8];
+  *reinterpret_cast<float4*>(c) = c4[0]; *reinterpret_cast<float4*>(c + 4) = c4[1];
+  *reinterpret_cast<float4*>(s) = s4[0]; *reinterpret_cast<float4*>(s + 4) = s4[1];
+  float o0[8], o1[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float sj = s[j] * sign;
+    o0[j] = a[j] * c[j] - b[j] * sj;
+    o1[j] = b[j] * c[j] + a[j] * sj;
+  }
+  store8(p0, o0);
+  store8(p1, o1);
+}
+__global__ void rope_scalar_k(bf16* __restrict__ qkv, const float* __restrict__ cosT, const float* __restrict__ sinT, long rows,
+                              int T, int H, int hd, float sign) {
+  const int h2 = hd >> 1;
+  const int per_row = 2 * H * h2;
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * per_row) return;
+  const long row = idx / per_row;
+  int r = idx % per_row;
+  const int which = r / (H * h2);
+  r %= H * h2;
+  const int h = r / h2, i = r % h2;
+  const int t = row % T;
+  bf16* p0 = qkv + row * (3L * H * hd) + (long)which * H * hd + h * hd + i;
+  float a = __bfloat162float(p0[0]), b = __bfloat162float(p0[h2]);
+  float c = cosT[(long)t * h2 + i], s = sinT[(long)t * h2 + i] * sign;
+  p0[0] = __float2bfloat16(a * c - b * s);
+  p0[h2] = __float2bfloat16(b * c + a * s);
+}
+
+// ------------------------------------------------------------------ SwiGLU on gu[rows, 2I] = [gate | up]
+__global__ void swiglu_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ gu, long rows, int I) {
+  const int vpr = I >> 3;
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * vpr) return;
+  const long row = idx / vpr;
+  const int v = idx % vpr;
+  float g[8], u[8], o[8];
+  load8(gu + row * 2L * I + v * 8, g);
+  load8(gu + row * 2L * I + I + v * 8, u);
+#pragma unroll
+  for (int j = 0; j < 8; j++) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+  store8(out + row * (long)I + v * 8, o);
+}
+__global__ void swiglu_bwd_k(bf16* __restrict__ dgu, const bf16* __restrict__ dout, const bf16* __restrict__ gu, long rows, int I) {
+  const int vpr = I >> 3;
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * vpr) return;
+  const long row = idx / vpr;
+  const int v = idx % vpr;
+  float g[8], u[8], d[8], dg[8], du[8];
+  load8(gu + row * 2L * I + v * 8, g);
+  load8(gu + row * 2L * I + I + v * 8, u);
+  load8(dout + row * (long)I + v * 8, d);
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float s = 1.f / (1.f + __expf(-g[j]));
+    dg[j] = d[j] * u[j] * s * (1.f + g[j] * (1.f - s));
+    du[j] = d[j] * g[j] * s;
+  }
+  store8(dgu + row * 2L * I + v * 8, dg);
+  store8(dgu + row * 2L * I + I + v * 8, du);
+}
+__global__ void swiglu_fwd_scalar_k(bf16* out, const bf16* gu, long rows, int I) {
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * I) return;
+  long row = idx / I;
+  int i = idx % I;
+  float g = __bfloat162float(gu[row * 2L * I + i]), u = __bfloat162float(gu[row * 2L * I + I + i]);
+  out[idx] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+}
+__global__ void swiglu_bwd_scalar_k(bf16* dgu, const bf16* dout, const bf16* gu, long rows, int I) {
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * I) return;
+  long row = idx / I;
+  int i = idx % I;
+  float g = __bfloat162float(gu[row * 2L * I + i]), u = __bfloat162float(gu[row * 2L * I + I + i]);
+  float d = __bfloat162float(dout[idx]);
+  float s = 1.f / (1.f + __expf(-g));
+  dgu[row * 2L * I + i] = __float2bfloat16(d * u * s * (1.f + g * (1.f - s)));
+  dgu[row * 2L * I + I + i] = __float2bfloat16(d * g * s);
+}
+
+// ------------------------------------------------------------------ fused cross-entropy (one block per row, in place)
+// pass 1: online max / sum-exp over the row; pass 2 (row is L2-resident): logits <- (softmax - onehot) * dscale.
+// Rows with tgt < 0: loss 0, gradient row zeroed.
+__global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, bf16* __restrict__ logits,
+                                                    const int* __restrict__ tgt, int V, long ld, float dscale) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  bf16* z = logits + row * ld;
+  const int t = tgt[row];
+  const bool vec = ((V & 7) == 0) && ((ld & 7) == 0);
+  if (t < 0) {
+    if (threadIdx.x == 0) losses[row] = 0.f;
+    if (vec) {
+      for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) *reinterpret_cast<uint4*>(z + i) = make_uint4(0, 0, 0, 0);
+    } else {
+      for (int i = threadIdx.x; i < V; i += blockDim.x) z[i] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+  float m = -INFINITY, s = 0.f;
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) {
+      float x[8];
+      load8(z + i, x);
+      float mx = x[0];
+#pragma unroll
+      for (int j = 1; j < 8; j++) mx = fmaxf(mx, x[j]);
+      if (mx > m) { s *= __expf(m - mx); m = mx; }
+#pragma unroll
+      for (int j = 0; j < 8; j++) s += __expf(x[j] - m);
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      float x = __bfloat162float(z[i]);
+      if (x > m) { s *= __expf(m - x); m = x; }
+      s += __expf(x - m);
+    }
+  }
+  const float M = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - M);
+  const float S = block_sum(s, red);
+  const float zt = __bfloat162float(z[t]);
+  __syncthreads();  // everyone has read z[t] before anyone overwrites it
+  if (threadIdx.x == 0) losses[row] = __logf(S) + M - zt;
+  const float inv = dscale / S;
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) {
+      float x[8];
+      load8(z + i, x);
+#pragma unroll
+      for (int j = 0; j < 8; j++) x[j] = __expf(x[j] - M) * inv - ((i + j == t) ? dscale : 0.f);
+      store8(z + i, x);
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      float x = __bfloat162float(z[i]);
+      z[i] = __float2bfloat16(__expf(x - M) * inv - ((i == t) ? dscale : 0.f));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ AdamW (fp32 master/m/v, bf16 copy written in the same pass)
+__global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, const float* __restrict__ grads,
+                        float* __restrict__ m, float* __restrict__ v, long n, float lr, float b1, float b2, float eps, float wd,
+                        float inv_bc1, float inv_bc2, float grad_scale) {
+  long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    float4 g = *reinterpret_cast<const float4*>(grads + i);
+    float4 mm = *reinterpret_cast<const float4*>(m + i);
+    float4 vv = *reinterpret_cast<const float4*>(v + i);
+    float4 p = *reinterpret_cast<const float4*>(master + i);
+    float* gp = &g.x; float* mp = &mm.x; float* vp = &vv.x; float* pp = &p.x;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float gj = gp[j] * grad_scale;
+      mp[j] = b1 * mp[j] + (1.f - b1) * gj;
+      vp[j] = b2 * vp[j] + (1.f - b2) * gj * gj;
+      pp[j] -= lr * (mp[j] * inv_bc1 / (sqrtf(vp[j] * inv_bc2) + eps) + wd * pp[j]);
+    }
+    *reinterpret_cast<float4*>(m + i) = mm;
+    *reinterpret_cast<float4*>(v + i) = vv;
+    *reinterpret_cast<float4*>(master + i) = p;
+    if (params) {
+      uint2 o;
+      o.x = pack_bf16(p.x, p.y);
+      o.y = pack_bf16(p.z, p.w);
+      *reinterpret_cast<uint2*>(params + i) = o;
+    }
+  } else {
+    for (; i < n; i++) {
+      const float gj = grads[i] * grad_scale;
+      float mj = b1 * m[i] + (1.f - b1) * gj, vj = b2 * v[i] + (1.f - b2) * gj * gj, pj = master[i];
+      pj -= lr * (mj * inv_bc1 / (sqrtf(vj * inv_bc2) + eps) + wd * pj);
+      m[i] = mj; v[i] = vj; master[i] = pj;
+      if (params) params[i] = __float2bfloat16(pj);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ casts / utilities
+__global__ void cast_f2b_k(bf16* __restrict__ out, const float* __restrict__ in, long n, float scale) {
+  long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    float4 f = *reinterpret_cast<const float4*>(in + i);
+    uint2 o;
+    o.x = pack_bf16(f.x * scale, f.y * scale);
+    o.y = pack_bf16(f.z * scale, f.w * scale);
+    *reinterpret_cast<uint2*>(out + i) = o;
+  } else {
+    for (; i < n; i++) out[i] = __float2bfloat16(in[i] * scale);
+  }
+}
+__global__ void cast_b2f_k(float* __restrict__ out, const bf16* __restrict__ in, long n, float scale) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __bfloat162float(in[i]) * scale;
+}
+__global__ void scale_f32_k(float* __restrict__ x, long n, float scale) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] *= scale;
+}
+__global__ void residual_add_k(bf16* __restrict__ out, const bf16* __restrict__ a, const bf16* __restrict__ b, long n) {
+  long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i + 7 < n) {
+    float x[8], y[8];
+    load8(a + i, x);
+    load8(b + i, y);
+#pragma unroll
+    for (int j = 0; j < 8; j++) x[j] += y[j];
+    store8(out + i, x);
+  } else {
+    for (; i < n; i++) out[i] = __float2bfloat16(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+  }
+}
+
+// ------------------------------------------------------------------ vision helpers
+// pixels fp32 [B, Cin, Himg, Wimg] -> patches bf16 [B*gh*gw, Cin*P*P] with element order (c, py, px).
+__global__ void patchify_k(bf16* __restrict__ out, const float* __restrict__ px, int B, int Cin, int Himg, int Wimg, int P) {
+  const int gh = Himg / P, gw = Wimg / P, pd = Cin * P * P;
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  long n = (long)B * gh * gw * pd;
+  if (idx >= n) return;
+  int e = idx % pd;
+  long pr = idx / pd;
+  int pxl = e % P, pyl = (e / P) % P, c = e / (P * P);
+  int pw = pr % gw, ph = (pr / gw) % gh, b = pr / (gw * gh);
+  out[idx] = __float2bfloat16(px[(((long)b * Cin + c) * Himg + ph * P + pyl) * Wimg + pw * P + pxl]);
+}
+__global__ void add_posembed_k(bf16* __restrict__ x, const bf16* __restrict__ pos, long NP, int n_patch, int vC) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= NP * vC) return;
+  long r = i / vC;
+  int c = i % vC;
+  x[i] = __float2bfloat16(__bfloat162float(x[i]) + __bfloat162float(pos[(r % n_patch) * vC + c]));
+}
+// dpos[p, c] += sum_b dx[b*n_patch + p, c]  (one thread per (p,c): deterministic, no atomics)
+__global__ void posembed_grad_k(float* __restrict__ dpos, const bf16* __restrict__ dx, long NP, int n_patch, int vC) {
+  long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long)n_patch * vC) return;
+  int nb = NP / n_patch;
+  float s = 0.f;
+  for (int b = 0; b < nb; b++) s += __bfloat162float(dx[(long)b * n_patch * vC + i]);
+  dpos[i] += s;
+}
+
+inline int gs(long n, int per_block) { return (int)((n + per_block - 1) / per_block); }
+
+}  // namespace
+
+#define LAUNCH_RET return (int)cudaGetLastError()
+
+MLB_API int mlb_embed_fwd(void* out, const void* wte, const int* ids, long BT, int C, cudaStream_t st) {
+  embed_fwd_k<<<(unsigned)BT, 96, 0, st>>>((bf16*)out, (const bf16*)wte, ids, C);
+  LAUNCH_RET;
+}
+MLB_API int mlb_embed_bwd(float* dwte, const void* dout, const int* ids, long BT, int C, int T, int n_pre, cudaStream_t st) {
+  embed_bwd_k<<<(unsigned)BT, 256, 0, st>>>(dwte, (const bf16*)dout, ids, C, T, n_pre);
+  LAUNCH_RET;
+}
+MLB_API int mlb_set_prefix(void* x, const void* prefix, int B, int T, int n_pre, int C, cudaStream_t st) {
+  long n = (long)B * n_pre * C;
+  if (n == 0) return 0;
+  set_prefix_k<<<gs(n, 256), 256, 0, st>>>((bf16*)x, (const bf16*)prefix, B, T, n_pre, C);
+  LAUNCH_RET;
+}
+MLB_API int mlb_gather_prefix_grad(void* dprefix, const void* dresid, int B, int T, int n_pre, int C, cudaStream_t st) {
+  long n = (long)B * n_pre * C;
+  if (n == 0) return 0;
+  gather_prefix_k<<<gs(n, 256), 256, 0, st>>>((bf16*)dprefix, (const bf16*)dresid, B, T, n_pre, C);
+  LAUNCH_RET;
+}
+MLB_API int mlb_rmsnorm_fwd(void* out, float* rstd, const void* x, const void* w, long rows, int C, float eps, cudaStream_t st) {
+  rmsnorm_fwd_k<false><<<gs(rows, 8), 256, 0, st>>>((bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w, rows, C, eps);
+  LAUNCH_RET;
+}
+MLB_API int mlb_add_rmsnorm_fwd(void* resid, void* out, float* rstd, const void* a, const void* b, const void* w, long rows, int C,
+                                float eps, cudaStream_t st) {
+  rmsnorm_fwd_k<true><<<gs(rows, 8), 256, 0, st>>>((bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b, (const bf16*)w,
+                                                   rows, C, eps);
+  LAUNCH_RET;
+}
+
+// Number of blocks rmsnorm_bwd uses for `rows`; the caller provides scratch of blocks*C floats + one zeroed int.
+MLB_API int mlb_rmsnorm_bwd_blocks(long rows) {
+  long b = (rows + 7) / 8;
+  return (int)(b < 296 ? b : 296);
+}
+MLB_API int mlb_rmsnorm_bwd(void* dx, float* dw, const void* dy, const void* x, const void* w, const float* rstd, const void* add,
+                            long rows, int C, float* partial, int* ticket, cudaStream_t st) {
+  const int blocks = mlb_rmsnorm_bwd_blocks(rows);
+  const size_t sh = (size_t)C * sizeof(float);
+#define RB(V)                                                                                                         \
+  rmsnorm_bwd_k<V><<<blocks, 256, sh, st>>>((bf16*)dx, dw, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,   \
+                                            (const bf16*)add, rows, C, partial, ticket)
+  if (sh > 48 * 1024) return -3;
+  switch ((C % 256 == 0) ? C / 256 : 0) {
+    case 1: RB(1); break;
+    case 2: RB(2); break;
+    case 3: RB(3); break;
+    case 4: RB(4); break;
+    case 6: RB(6); break;
+    case 8: RB(8); break;
+    default: RB(0); break;
+  }
+#undef RB
+  LAUNCH_RET;
+}
+MLB_API int mlb_rope(void* qkv, const float* cosT, const float* sinT, long rows, int T, int H, int hd, float sign, cudaStream_t st) {
+  const int h2 = hd / 2;
+  if (h2 % 8 == 0 && (H * hd) % 8 == 0) {
+    long n = rows * 2L * H * (h2 / 8);
+    rope_k<<<gs(n, 256), 256, 0, st>>>((bf16*)qkv, cosT, sinT, rows, T, H, hd, sign);
+  } else {
+    long n = rows * 2L * H * h2;
+    rope_scalar_k<<<gs(n, 256), 256, 0, st>>>((bf16*)qkv, cosT, sinT, rows, T, H, hd, sign);
+  }
+  LAUNCH_RET;
+}
+MLB_API int mlb_swiglu_fwd(void* out, const void* gu, long rows, int I, cudaStream_t st) {
+  if (I % 8 == 0) swiglu_fwd_k<<<gs(rows * (I / 8), 256), 256, 0, st>>>((bf16*)out, (const bf16*)gu, rows, I);
+  else swiglu_fwd_scalar_k<<<gs(rows * I, 256), 256, 0, st>>>((bf16*)out, (const bf16*)gu, rows, I);
+  LAUNCH_RET;
+}
+MLB_API int mlb_swiglu_bwd(void* dgu, const void* dout, const void* gu, long rows, int I, cudaStream_t st) {
+  if (I % 8 == 0) swiglu_bwd_k<<<gs(rows * (I / 8), 256), 256, 0, st>>>((bf16*)dgu, (const bf16*)dout, (const bf16*)gu, rows, I);
+  else swiglu_bwd_scalar_k<<<gs(rows * I, 256), 256, 0, st>>>((bf16*)dgu, (const bf16*)dout, (const bf16*)gu, rows, I);
+  LAUNCH_RET;
+}
+MLB_API int mlb_ce_fwd_bwd(float* losses, void* logits, const int* tgt, long rows, int V, long ld, float dscale, int threads,
+                           cudaStream_t st) {
+  if (threads != 128 && threads != 256 && threads != 512) threads = 512;
+  ce_fwd_bwd_k<<<(unsigned)rows, threads, 0, st>>>(losses, (bf16*)logits, tgt, V, ld, dscale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_adamw(float* master, void* params, const float* grads, float* m, float* v, long n, float lr, float b1, float b2,
+                      float eps, float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
+  if (n == 0) return 0;
+  adamw_k<<<gs((n + 3) / 4, 256), 256, 0, st>>>(master, (bf16*)params, grads, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2,
+                                                grad_scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_cast_f2b(void* out, const float* in, long n, float scale, cudaStream_t st) {
+  cast_f2b_k<<<gs((n + 3) / 4, 256), 256, 0, st>>>((bf16*)out, in, n, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_cast_b2f(float* out, const void* in, long n, float scale, cudaStream_t st) {
+  cast_b2f_k<<<gs(n, 256), 256, 0, st>>>(out, (const bf16*)in, n, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_scale_f32(float* x, long n, float scale, cudaStream_t st) {
+  scale_f32_k<<<gs(n, 256), 256, 0, st>>>(x, n, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_residual_add(void* out, const void* a, const void* b, long n, cudaStream_t st) {
+  residual_add_k<<<gs((n + 7) / 8, 256), 256, 0, st>>>((bf16*)out, (const bf16*)a, (const bf16*)b, n);
+  LAUNCH_RET;
+}
+MLB_API int mlb_patchify(void* out, const float* px, int B, int Cin, int Himg, int Wimg, int P, cudaStream_t st) {
+  long n = (long)B * (Himg / P) * (Wimg / P) * Cin * P * P;
+  patchify_k<<<gs(n, 256), 256, 0, st>>>((bf16*)out, px, B, Cin, Himg, Wimg, P);
+  LAUNCH_RET;
+}
+MLB_API int mlb_add_posembed(void* x, const void* pos, long NP, int n_patch, int vC, cudaStream_t st) {
+  add_posembed_k<<<gs(NP * vC, 256), 256, 0, st>>>((bf16*)x, (const bf16*)pos, NP, n_patch, vC);
+  LAUNCH_RET;
+}
+MLB_API int mlb_posembed_grad(float* dpos, const void* dx, long NP, int n_patch, int vC, cudaStream_t st) {
+  posembed_grad_k<<<gs((long)n_patch * vC, 256), 256, 0, st>>>(dpos, (const bf16*)dx, NP, n_patch, vC);
+  LAUNCH_RET;
+}

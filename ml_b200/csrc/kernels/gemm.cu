@@ -1,0 +1,391 @@
+// BF16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands staged by TMA).
+//
+// One kernel template covers the three products a linear layer needs (the reference gets them from
+// cuBLASLt: linear_forward / linear_backward_inp / linear_backward_weight, train/gpt_kernels.cuh:165-194):
+//     fwd  out[M,N]  = x[M,K]    . W[N,K]^T     A K-major,  B K-major,  bf16 store
+//     dX   dx[M,K]   = dout[M,N] . W[N,K]       A K-major,  B MN-major, bf16 store
+//     dW   dW[N,K]  += dout[M,N]^T . x[M,K]     A MN-major, B MN-major, fp32 red.add (split-K over tokens)
+// "D[m,n] = sum_k A(m,k) B(n,k)" with each operand either K-major (k contiguous in memory) or MN-major.
+//
+// Structure: persistent CTAs (one per SM), 192 threads = 1 TMA-producer warp, 1 MMA-issuer warp (a single
+// elected thread issues tcgen05.mma), 4 epilogue warps.  Tile 128 x BN x 64 with a multi-stage shared-memory
+// ring guarded by full/empty mbarriers; two TMEM accumulators (2 x BN columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Every mbarrier wait is bounded: on expiry the kernel records an error
+// word, frees its TMEM and returns.
+#include "../tc.cuh"
+
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+enum { EPI_BF16 = 0, EPI_F32_ADD = 1 };
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+  static constexpr int B_BYTES = BN * BK * 2;   // 16/32 KB
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
+};
+
+struct GemmArgs {
+  void* out;
+  int M, N, K;       // logical problem: D[M,N], reduction K
+  int ldo;           // output row pitch in elements
+  int tiles_m, tiles_n, splits, kb_per_split, kb_total;
+};
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+  using S = GemmSmem<BN>;
+  constexpr int STAGES = S::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = g.tiles_m * g.tiles_n * g.splits;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; i++) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; i++) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 4); }
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tmA);
+    tc::tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) tc::tmem_alloc(tmem_slot, 2 * BN);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (tc::elect_one()) {
+      int stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n, sp = t / (g.tiles_m * g.tiles_n);
+        const int m0 = mt * BM, n0 = nt * BN;
+        const int kb0 = sp * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+        for (int kb = kb0; kb < kb1; kb++) {
+          if (!tc::mbar_wait(&empty[stage], phase ^ 1, 1)) { ok = false; break; }
+          uint8_t* sA = smem + stage * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          tc::mbar_expect_tx(&full[stage], S::STAGE_BYTES);
+          if (!A_MN) {
+            tc::tma_load_2d(sA, &tmA, &full[stage], kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; c++) tc::tma_load_2d(sA + c * 8192, &tmA, &full[stage], m0 + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tc::tma_load_2d(sB, &tmB, &full[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; c++) tc::tma_load_2d(sB + c * 8192, &tmB, &full[stage], n0 + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (tc::elect_one()) {
+      constexpr uint32_t idesc = tc::idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+        const int sp = t / (g.tiles_m * g.tiles_n);
+        const int kb0 = sp * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+        const int acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, 2)) { ok = false; break; }
+        tc::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; kb++) {
+          if (!tc::mbar_wait(&full[stage], phase, 3)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t sA = tc::smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sB = sA + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; k++) {
+            const uint64_t da = A_MN ? tc::smem_desc_sw128(sA + k * 2048, 8192, 1024) : tc::smem_desc_sw128(sA + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? tc::smem_desc_sw128(sB + k * 2048, 8192, 1024) : tc::smem_desc_sw128(sB + k * 32, 16, 1024);
+            tc::mma_bf16_ss(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc::mma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc::mma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int lg = warp & 3;  // TMEM lane group this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+      const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n;
+      const int m0 = mt * BM, n0 = nt * BN;
+      const int acc = it & 1, acc_phase = (it >> 1) & 1;
+      if (!tc::mbar_wait(&acc_full[acc], acc_phase, 4)) { ok = false; break; }
+      tc::tc_fence_after();
+      const int row = m0 + lg * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        tc::tmem_ld32(taddr + c * 32, r);
+        tc::tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < g.M && col0 < g.N) {
+          if (EPI == EPI_BF16) {
+            bf16* o = (bf16*)g.out + (size_t)row * g.ldo + col0;
+            if (col0 + 32 <= g.N) {
+#pragma unroll
+              for (int v = 0; v < 4; v++) {
+                uint4 pk;
+                pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                *reinterpret_cast<uint4*>(o + v * 8) = pk;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < g.N; i++) o[i] = __float2bfloat16(__uint_as_float(r[i]));
+            }
+          } else {
+            float* o = (float*)g.out + (size_t)row * g.ldo + col0;
+            if (col0 + 32 <= g.N) {
+#pragma unroll
+              for (int v = 0; v < 8; v++) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + v * 4),
+                             "f"(__uint_as_float(r[v * 4 + 0])), "f"(__uint_as_float(r[v * 4 + 1])),
+                             "f"(__uint_as_float(r[v * 4 + 2])), "f"(__uint_as_float(r[v * 4 + 3]))
+                             : "memory");
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < g.N; i++) atomicAdd(o + i, __uint_as_float(r[i]));
+            }
+          }
+        }
+      }
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * BN);
+}
+
+// ------------------------------------------------------------------ SIMT fallback (any shape / alignment)
+// D[m,n] = sum_k A[m*sam + k*sak] * B[n*sbn + k*sbk]; 64x64 tile, 16x16 threads, 4x4 per thread.
+template <int EPI>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(void* out, const bf16* __restrict__ A, const bf16* __restrict__ B,
+                                                        int M, int N, int K, long sam, long sak, long sbn, long sbk, int ldo) {
+  __shared__ float sA[16][65], sB[16][65];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      int kk, mm;
+      if (sak == 1) { kk = i & 15; mm = i >> 4; } else { mm = i & 63; kk = i >> 6; }
+      int gm = m0 + mm, gk = k0 + kk;
+      sA[kk][mm] = (gm < M && gk < K) ? __bfloat162float(A[gm * sam + gk * sak]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      int kk, nn;
+      if (sbk == 1) { kk = i & 15; nn = i >> 4; } else { nn = i & 63; kk = i >> 6; }
+      int gn = n0 + nn, gk = k0 + kk;
+      sB[kk][nn] = (gn < N && gk < K) ? __bfloat162float(B[gn * sbn + gk * sbk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; kk++) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) { a[i] = sA[kk][ty * 4 + i]; b[i] = sB[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] += a[i] * b[j];
+    }
+    __syncthreads();
+  }
+  for (int i = 0; i < 4; i++)
+    for (int j = 0; j < 4; j++) {
+      int gm = m0 + ty * 4 + i, gn = n0 + tx * 4 + j;
+      if (gm < M && gn < N) {
+        if (EPI == EPI_BF16) ((bf16*)out)[(size_t)gm * ldo + gn] = __float2bfloat16(acc[i][j]);
+        else ((float*)out)[(size_t)gm * ldo + gn] += acc[i][j];
+      }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+std::mutex g_tmap_mu;
+typedef std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t> TmapKey;
+std::map<TmapKey, CUtensorMap*> g_tmaps;
+
+}  // namespace
+
+bool mlb_make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                        uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  if (((uintptr_t)base & 15) || ((pitch_elems * 2) & 15)) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_elems * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+const CUtensorMap* mlb_tmap_cached(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                                   uint32_t box_rows, uint32_t box_cols) {
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  TmapKey key(base, rows, cols, pitch_elems, box_rows, box_cols);
+  auto it = g_tmaps.find(key);
+  if (it != g_tmaps.end()) return it->second;
+  CUtensorMap* m = new CUtensorMap;
+  if (!mlb_make_tmap_bf16(m, base, rows, cols, pitch_elems, box_rows, box_cols)) { delete m; return nullptr; }
+  g_tmaps[key] = m;
+  return m;
+}
+
+namespace {
+
+int g_num_sms = 0;
+int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+int g_force_simt = 0;        // test hook: route everything through the SIMT kernel
+int g_max_ctas = 0;          // 0 = one CTA per SM; >0 caps the persistent grid (leaves SMs to a concurrent kernel)
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmArgs& g, cudaStream_t st) {
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, EPI>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  int total = g.tiles_m * g.tiles_n * g.splits;
+  int cap = g_max_ctas > 0 ? g_max_ctas : num_sms();
+  int grid = total < cap ? total : cap;
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, st>>>(*tmA, *tmB, g);
+  return (int)cudaGetLastError();
+}
+
+// Generic entry: D[M,N] (+)= sum_k A(m,k) B(n,k).
+// A_MN=false: A is [M,K] row-major with pitch lda.  A_MN=true: A is stored [K,M] row-major with pitch lda.
+// Same for B with N.  EPI_BF16 stores bf16; EPI_F32_ADD accumulates into fp32.
+template <bool A_MN, bool B_MN, int EPI>
+int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st) {
+  bool aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && (lda % 8 == 0) && (ldb % 8 == 0) &&
+                 ((uintptr_t)out % 16 == 0) && (ldo % 8 == 0) && (N % 8 == 0) && M > 0 && N > 0 && K > 0;
+  // MN-major operands are fetched in 64-wide chunks along M/N: the global extent must be a multiple of 8 elements
+  // (16 bytes) for the tensor map; out-of-range chunks are zero-filled by TMA.
+  if (A_MN) aligned = aligned && (M % 8 == 0);
+  if (B_MN) aligned = aligned && (N % 8 == 0);
+  if (!A_MN || !B_MN) aligned = aligned && (K % 8 == 0);
+  if (g_force_simt || !aligned || get_encode() == nullptr) {
+    dim3 grid(ceil_div_i(N, 64), ceil_div_i(M, 64));
+    long sam = A_MN ? 1 : lda, sak = A_MN ? lda : 1, sbn = B_MN ? 1 : ldb, sbk = B_MN ? ldb : 1;
+    gemm_simt_kernel<EPI><<<grid, 256, 0, st>>>(out, A, B, M, N, K, sam, sak, sbn, sbk, ldo);
+    return (int)cudaGetLastError();
+  }
+  const int BN = (N > 128) ? 256 : 128;
+  GemmArgs g;
+  g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
+  g.tiles_m = ceil_div_i(M, BM);
+  g.tiles_n = ceil_div_i(N, BN);
+  g.kb_total = ceil_div_i(K, BK);
+  g.splits = 1;
+  if (EPI == EPI_F32_ADD) {
+    // split the reduction so the persistent grid is filled: choose the split count with the best last-wave fill
+    int tiles = g.tiles_m * g.tiles_n, sms = g_max_ctas > 0 ? g_max_ctas : num_sms();
+    int best = 1;
+    double best_eff = 0;
+    for (int s = 1; s <= 32; s++) {
+      if (g.kb_total / s < 8 && s > 1) break;
+      long w = (long)tiles * s;
+      double eff = (double)w / ((double)((w + sms - 1) / sms) * sms);
+      if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    g.splits = best;
+  }
+  g.kb_per_split = ceil_div_i(g.kb_total, g.splits);
+  g.splits = ceil_div_i(g.kb_total, g.kb_per_split);
+  const CUtensorMap* tmA = A_MN ? mlb_tmap_cached(A, K, M, lda, 64, 64) : mlb_tmap_cached(A, M, K, lda, BM, 64);
+  const CUtensorMap* tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, BN, 64);
+  if (!tmA || !tmB) return -2;
+  if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, g, st);
+  return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, g, st);
+}
+
+}  // namespace
+
+// out[M,N] = x[M,K] . W[N,K]^T
+MLB_API int mlb_linear_fwd(void* out, const void* x, const void* W, int M, int N, int K, int ldo, int ldx, int ldw, cudaStream_t st) {
+  return gemm_dispatch<false, false, EPI_BF16>(out, ldo, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, st);
+}
+// dx[M,K] = dout[M,N] . W[N,K]      (GEMM view: D[M,K], reduction N; B(n=k_in, k=n_out) is MN-major)
+MLB_API int mlb_linear_dx(void* dx, const void* dout, const void* W, int M, int N, int K, int lddx, int lddo, int ldw, cudaStream_t st) {
+  return gemm_dispatch<false, true, EPI_BF16>(dx, lddx, (const bf16*)dout, lddo, (const bf16*)W, ldw, M, K, N, st);
+}
+// dW[N,K] += dout[M,N]^T . x[M,K]   (GEMM view: D[N,K], reduction M; both operands MN-major)
+MLB_API int mlb_linear_dw(void* dW, const void* dout, const void* x, int M, int N, int K, int lddw, int lddo, int ldx, cudaStream_t st) {
+  return gemm_dispatch<true, true, EPI_F32_ADD>(dW, lddw, (const bf16*)dout, lddo, (const bf16*)x, ldx, N, K, M, st);
+}
+
+MLB_API void mlb_gemm_force_simt(int on) { g_force_simt = on; }
+MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
+
+MLB_DEFINE_ERROR_WORD(gemm)

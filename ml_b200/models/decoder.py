@@ -186,8 +186,10 @@ class GPT:
             self._mark("B_norm")
             ops.linear_dw(self.G(o.o, C, C), dresid1, sl(self.atty[l]))
             ops.linear_dx(datty, dresid1, self.P(o.o, C, C))
-            ops.attn_bwd(dqkv, datty, sl(self.qkv[l]), sl(self.atty[l]), self.lse[l][:B], B, T, H, hd)
-            if "rope" not in self.skip:
+            want_rope = "rope" not in self.skip
+            fused = ops.attn_bwd(dqkv, datty, sl(self.qkv[l]), sl(self.atty[l]), self.lse[l][:B], B, T, H, hd,
+                                 rope=(self.cos, self.sin) if want_rope else None)
+            if want_rope and not fused:
                 ops.rope_bwd(dqkv, self.cos, self.sin, B, T, H, hd)
             self._mark("B_attn")
             ops.linear_dw(self.G(o.qkv, 3 * C, C), dqkv, sl(self.ln1[l]))

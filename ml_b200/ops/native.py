@@ -1,0 +1,274 @@
+"""ctypes binding of the sm_100a kernel library (libmlb_cuda.so).
+
+Every function takes torch CUDA tensors (bf16 activations / parameters, fp32 statistics, gradients and
+optimizer state), checks dtype / contiguity, and launches on the current torch stream.  Nothing here falls
+back to PyTorch: if the library cannot be loaded the import fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from functools import lru_cache
+
+import torch
+
+from .. import build as _build
+
+_i32, _i64, _f32, _vp = C.c_int, C.c_long, C.c_float, C.c_void_p
+
+
+@lru_cache(maxsize=1)
+def lib():
+    if not _build.is_fresh(_build.CUDA_LIB, _build.cuda_hash()):
+        if _build.CUDA_LIB.exists() and _build._nvcc() is None:
+            pass  # no compiler on this machine: use the library that travelled with the tree
+        else:
+            _build.build_cuda()
+    L = C.CDLL(str(_build.CUDA_LIB))
+    sig = {
+        "mlb_linear_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
+        "mlb_linear_dx": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
+        "mlb_linear_dw": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
+        "mlb_gemm_force_simt": [_i32],
+        "mlb_gemm_set_max_ctas": [_i32],
+        "mlb_attn_force_simt": [_i32],
+        "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
+        "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
+        "mlb_embed_fwd": [_vp, _vp, _vp, _i64, _i32, _vp],
+        "mlb_embed_bwd": [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp],
+        "mlb_set_prefix": [_vp, _vp, _i32, _i32, _i32, _i32, _vp],
+        "mlb_gather_prefix_grad": [_vp, _vp, _i32, _i32, _i32, _i32, _vp],
+        "mlb_rmsnorm_fwd": [_vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp],
+        "mlb_add_rmsnorm_fwd": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp],
+        "mlb_rmsnorm_bwd_blocks": [_i64],
+        "mlb_rmsnorm_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp, _vp, _vp],
+        "mlb_rope": [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp],
+        "mlb_swiglu_fwd": [_vp, _vp, _i64, _i32, _vp],
+        "mlb_swiglu_bwd": [_vp, _vp, _vp, _i64, _i32, _vp],
+        "mlb_ce_fwd_bwd": [_vp, _vp, _vp, _i64, _i32, _i64, _f32, _i32, _vp],
+        "mlb_adamw": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp],
+        "mlb_cast_f2b": [_vp, _vp, _i64, _f32, _vp],
+        "mlb_cast_b2f": [_vp, _vp, _i64, _f32, _vp],
+        "mlb_scale_f32": [_vp, _i64, _f32, _vp],
+        "mlb_residual_add": [_vp, _vp, _vp, _i64, _vp],
+        "mlb_patchify": [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp],
+        "mlb_add_posembed": [_vp, _vp, _i64, _i32, _i32, _vp],
+        "mlb_posembed_grad": [_vp, _vp, _i64, _i32, _i32, _vp],
+    }
+    for name, args in sig.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = _i32
+    for tag in ("gemm", "attn", "elementwise", "comm"):
+        for pre in ("mlb_get_error_", "mlb_clear_error_"):
+            if hasattr(L, pre + tag):
+                getattr(L, pre + tag).restype = _i32
+                getattr(L, pre + tag).argtypes = []
+    return L
+
+
+LAUNCHES = 0  # number of kernel-launching calls made through this module (bench.py reports it)
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(rc, name):
+    global LAUNCHES
+    LAUNCHES += 1
+    if rc != 0:
+        raise RuntimeError(f"{name} failed: code {rc} ({_cuda_err(rc)})")
+
+
+def _cuda_err(rc):
+    try:
+        return torch.cuda.cudart().cudaGetErrorString(rc) if rc > 0 else "library error"
+    except Exception:
+        return "?"
+
+
+def get_error() -> int:
+    """Non-zero if a kernel gave up on a bounded wait: (code << 24) | detail, see csrc/common.cuh."""
+    L = lib()
+    for tag in ("gemm", "attn", "elementwise", "comm"):
+        if hasattr(L, "mlb_get_error_" + tag):
+            v = getattr(L, "mlb_get_error_" + tag)()
+            if v:
+                return v
+    return 0
+
+
+def clear_error():
+    L = lib()
+    for tag in ("gemm", "attn", "elementwise", "comm"):
+        if hasattr(L, "mlb_clear_error_" + tag):
+            getattr(L, "mlb_clear_error_" + tag)()
+
+
+def _b(t, name="tensor"):
+    assert t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous(), f"{name}: need contiguous CUDA bf16"
+    return t.data_ptr()
+
+
+def _f(t, name="tensor"):
+    assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous(), f"{name}: need contiguous CUDA fp32"
+    return t.data_ptr()
+
+
+def _i(t, name="tensor"):
+    assert t.is_cuda and t.dtype == torch.int32 and t.is_contiguous(), f"{name}: need contiguous CUDA int32"
+    return t.data_ptr()
+
+
+_scratch = {}
+
+
+def scratch(key, numel, dtype, device, zero=False):
+    k = (key, str(device), dtype)
+    t = _scratch.get(k)
+    if t is None or t.numel() < numel:
+        t = (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=device)
+        _scratch[k] = t
+    return t
+
+
+# ------------------------------------------------------------------ linear
+def linear_fwd(out, x, W):
+    M, K = x.shape
+    N = W.shape[0]
+    _chk(lib().mlb_linear_fwd(_b(out), _b(x), _b(W), M, N, K, out.stride(0), x.stride(0), W.stride(0), _st()), "linear_fwd")
+
+
+def linear_dx(dx, dout, W):
+    M, N = dout.shape
+    K = W.shape[1]
+    _chk(lib().mlb_linear_dx(_b(dx), _b(dout), _b(W), M, N, K, dx.stride(0), dout.stride(0), W.stride(0), _st()), "linear_dx")
+
+
+def linear_dw(dW, dout, x):
+    M, N = dout.shape
+    K = x.shape[1]
+    _chk(lib().mlb_linear_dw(_f(dW), _b(dout), _b(x), M, N, K, dW.stride(0), dout.stride(0), x.stride(0), _st()), "linear_dw")
+
+
+# ------------------------------------------------------------------ attention
+def attn_fwd(out, lse, qkv, B, T, H, hd):
+    _chk(lib().mlb_attn_fwd(_b(out), _f(lse), _b(qkv), B, T, H, hd, _st()), "attn_fwd")
+
+
+def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
+    """rope=(cos, sin): ask the kernel to apply RoPE's backward rotation to dQ/dK in its epilogue.
+    Returns True if it did (tensor-core path), False if the caller still has to call rope_bwd."""
+    delta = scratch("attn_delta", B * H * T, torch.float32, qkv.device)
+    cp = _f(rope[0]) if rope is not None else None
+    sp = _f(rope[1]) if rope is not None else None
+    rc = lib().mlb_attn_bwd(_b(dqkv), _b(dout), _b(qkv), _b(out), _f(lse), _f(delta), B, T, H, hd, cp, sp, _st())
+    global LAUNCHES
+    LAUNCHES += 3
+    if rc < 0 or rc > 1:
+        raise RuntimeError(f"attn_bwd failed: code {rc}")
+    return rc == 1
+
+
+# ------------------------------------------------------------------ embedding
+def embed_fwd(out, wte, ids):
+    _chk(lib().mlb_embed_fwd(_b(out), _b(wte), _i(ids), ids.numel(), wte.shape[1], _st()), "embed_fwd")
+
+
+def embed_bwd(dwte, dout, ids, T, n_pre):
+    _chk(lib().mlb_embed_bwd(_f(dwte), _b(dout), _i(ids), ids.numel(), dwte.shape[1], T, n_pre, _st()), "embed_bwd")
+
+
+def set_prefix(x, prefix, B, T, n_pre):
+    _chk(lib().mlb_set_prefix(_b(x), _b(prefix), B, T, n_pre, x.shape[-1], _st()), "set_prefix")
+
+
+def gather_prefix_grad(dprefix, dresid, B, T, n_pre):
+    _chk(lib().mlb_gather_prefix_grad(_b(dprefix), _b(dresid), B, T, n_pre, dresid.shape[-1], _st()), "gather_prefix_grad")
+
+
+# ------------------------------------------------------------------ norms
+def rmsnorm_fwd(out, rstd, x, w, eps):
+    rows, Cc = x.shape
+    _chk(lib().mlb_rmsnorm_fwd(_b(out), _f(rstd), _b(x), _b(w), rows, Cc, eps, _st()), "rmsnorm_fwd")
+
+
+def add_rmsnorm_fwd(resid, out, rstd, a, b, w, eps):
+    rows, Cc = a.shape
+    _chk(lib().mlb_add_rmsnorm_fwd(_b(resid), _b(out), _f(rstd), _b(a), _b(b), _b(w), rows, Cc, eps, _st()), "add_rmsnorm_fwd")
+
+
+def rmsnorm_bwd(dx, dw, dy, x, w, rstd, add=None):
+    rows, Cc = x.shape
+    L = lib()
+    blocks = L.mlb_rmsnorm_bwd_blocks(rows)
+    part = scratch("rms_partial", blocks * Cc, torch.float32, x.device)
+    ticket = scratch("rms_ticket", 1, torch.int32, x.device, zero=True)
+    _chk(L.mlb_rmsnorm_bwd(_b(dx), _f(dw), _b(dy), _b(x), _b(w), _f(rstd), _b(add) if add is not None else None,
+                           rows, Cc, part.data_ptr(), ticket.data_ptr(), _st()), "rmsnorm_bwd")
+
+
+# ------------------------------------------------------------------ rope / swiglu / CE / AdamW
+def rope_fwd(qkv, cos, sin, B, T, H, hd):
+    _chk(lib().mlb_rope(_b(qkv), _f(cos), _f(sin), B * T, T, H, hd, 1.0, _st()), "rope_fwd")
+
+
+def rope_bwd(dqkv, cos, sin, B, T, H, hd):
+    _chk(lib().mlb_rope(_b(dqkv), _f(cos), _f(sin), B * T, T, H, hd, -1.0, _st()), "rope_bwd")
+
+
+def swiglu_fwd(out, gu):
+    rows, I2 = gu.shape
+    _chk(lib().mlb_swiglu_fwd(_b(out), _b(gu), rows, I2 // 2, _st()), "swiglu_fwd")
+
+
+def swiglu_bwd(dgu, dout, gu):
+    rows, I2 = gu.shape
+    _chk(lib().mlb_swiglu_bwd(_b(dgu), _b(dout), _b(gu), rows, I2 // 2, _st()), "swiglu_bwd")
+
+
+def ce_fwd_bwd(losses, logits, tgt, dscale, V_valid=None, threads=512):
+    rows, V = logits.shape
+    _chk(lib().mlb_ce_fwd_bwd(_f(losses), _b(logits), _i(tgt), rows, V if V_valid is None else V_valid, logits.stride(0),
+                              dscale, threads, _st()), "ce_fwd_bwd")
+
+
+def adamw(master, params, grads, m, v, lr, b1, b2, eps, wd, bc1, bc2, grad_scale=1.0):
+    n = master.numel()
+    pp = None if (params is None or params.data_ptr() == master.data_ptr()) else _b(params)
+    _chk(lib().mlb_adamw(_f(master), pp, _f(grads), _f(m), _f(v), n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, _st()), "adamw")
+
+
+# ------------------------------------------------------------------ vision / utilities
+def patchify(out, pixels, patch):
+    B, Cin, Hh, Ww = pixels.shape
+    _chk(lib().mlb_patchify(_b(out), _f(pixels), B, Cin, Hh, Ww, patch, _st()), "patchify")
+
+
+def add_posembed(x, pos, n_patch):
+    NP, vC = x.shape
+    _chk(lib().mlb_add_posembed(_b(x), _b(pos), NP, n_patch, vC, _st()), "add_posembed")
+
+
+def posembed_grad(dpos, dx, n_patch):
+    NP, vC = dx.shape
+    _chk(lib().mlb_posembed_grad(_f(dpos), _b(dx), NP, n_patch, vC, _st()), "posembed_grad")
+
+
+def residual_add(out, a, b):
+    _chk(lib().mlb_residual_add(_b(out), _b(a), _b(b), out.numel(), _st()), "residual_add")
+
+
+def cast(out, x, scale=1.0):
+    n = out.numel()
+    if out.dtype == torch.bfloat16 and x.dtype == torch.float32:
+        _chk(lib().mlb_cast_f2b(_b(out), _f(x), n, scale, _st()), "cast_f2b")
+    elif out.dtype == torch.float32 and x.dtype == torch.bfloat16:
+        _chk(lib().mlb_cast_b2f(_f(out), _b(x), n, scale, _st()), "cast_b2f")
+    else:
+        raise TypeError(f"cast {x.dtype} -> {out.dtype} is not a kernel of this library")
+
+
+def scale_(x, s):
+    _chk(lib().mlb_scale_f32(_f(x), x.numel(), s, _st()), "scale_f32")

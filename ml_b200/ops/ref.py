@@ -148,7 +148,8 @@ def attn_fwd(out, lse, qkv, B, T, H, hd):
     out.view(B, T, H, hd).copy_(o.permute(0, 2, 1, 3))
 
 
-def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd):
+def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
+    """Returns False: RoPE's backward rotation is never fused here (the caller applies rope_bwd)."""
     v5 = qkv.view(B, T, 3, H, hd)
     q, k, v = (_f(v5[:, :, i]).permute(0, 2, 1, 3) for i in range(3))
     do = _f(dout).view(B, T, H, hd).permute(0, 2, 1, 3)
@@ -167,6 +168,7 @@ def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd):
     d5[:, :, 0] = dq.permute(0, 2, 1, 3).to(dqkv.dtype)
     d5[:, :, 1] = dk.permute(0, 2, 1, 3).to(dqkv.dtype)
     d5[:, :, 2] = dv.permute(0, 2, 1, 3).to(dqkv.dtype)
+    return False
 
 
 # ------------------------------------------------------------------ cross entropy

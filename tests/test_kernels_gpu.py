@@ -1,0 +1,313 @@
+"""GPU numerics: every sm_100a kernel against the fp32 PyTorch oracle (ml_b200.ops.ref) on the same inputs,
+including odd shapes that take the scalar / SIMT paths and rows with tgt = -1."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from ml_b200.ops import ref
+
+
+def nat():
+    from ml_b200.ops import native
+    return native
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=dev(), dtype=torch.float32) * scale).to(dtype)
+
+
+def close(a, b, rtol=2e-2, atol=2e-2, name=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref_mag = b.abs().max().item()
+    assert torch.isfinite(a).all(), f"{name}: non-finite output"
+    assert err <= atol + rtol * ref_mag, f"{name}: max err {err} vs ref magnitude {ref_mag}"
+
+
+@pytest.fixture(autouse=True)
+def _no_kernel_error():
+    yield
+    torch.cuda.synchronize()
+    e = nat().get_error()
+    nat().clear_error()
+    assert e == 0, f"kernel error word {e:#x}"
+
+
+# ------------------------------------------------------------------ GEMM
+GEMM_SHAPES = [(256, 256, 128), (384, 768, 768), (1024, 2304, 768), (512, 4096, 768), (300, 520, 264), (128, 128, 64),
+               (2048, 768, 2048), (256, 1000, 512)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_linear_fwd(M, N, K):
+    torch.manual_seed(0)
+    x, W = rnd(M, K), rnd(N, K, scale=0.05)
+    out, exp = torch.empty(M, N, device=dev(), dtype=torch.bfloat16), torch.empty(M, N, device=dev())
+    nat().linear_fwd(out, x, W)
+    ref.linear_fwd(exp, x, W)
+    close(out, exp, name="linear_fwd")
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_linear_dx(M, N, K):
+    torch.manual_seed(1)
+    dout, W = rnd(M, N), rnd(N, K, scale=0.05)
+    dx, exp = torch.empty(M, K, device=dev(), dtype=torch.bfloat16), torch.empty(M, K, device=dev())
+    nat().linear_dx(dx, dout, W)
+    ref.linear_dx(exp, dout, W)
+    close(dx, exp, name="linear_dx")
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES + [(16384, 768, 768)])
+def test_linear_dw_accumulates(M, N, K):
+    torch.manual_seed(2)
+    dout, x = rnd(M, N, scale=0.1), rnd(M, K)
+    dW = torch.randn(N, K, device=dev())
+    exp = dW.clone()
+    nat().linear_dw(dW, dout, x)
+    ref.linear_dw(exp, dout, x)
+    close(dW, exp, rtol=1e-2, atol=1e-2, name="linear_dw")
+
+
+def test_gemm_simt_path_odd_shape():
+    torch.manual_seed(3)
+    M, N, K = 130, 100, 100   # C=100-style odd sizes: no 16-byte pitch, SIMT kernel
+    x, W = rnd(M, K), rnd(N, K, scale=0.1)
+    out, exp = torch.empty(M, N, device=dev(), dtype=torch.bfloat16), torch.empty(M, N, device=dev())
+    nat().linear_fwd(out, x, W)
+    ref.linear_fwd(exp, x, W)
+    close(out, exp, name="simt fwd")
+    dout = rnd(M, N)
+    dx, expx = torch.empty(M, K, device=dev(), dtype=torch.bfloat16), torch.empty(M, K, device=dev())
+    nat().linear_dx(dx, dout, W)
+    ref.linear_dx(expx, dout, W)
+    close(dx, expx, name="simt dx")
+    dW = torch.zeros(N, K, device=dev())
+    expw = torch.zeros(N, K, device=dev())
+    nat().linear_dw(dW, dout, x)
+    ref.linear_dw(expw, dout, x)
+    close(dW, expw, name="simt dw")
+
+
+def test_gemm_tc_matches_simt():
+    """Same inputs through the tcgen05 kernel and the SIMT kernel."""
+    torch.manual_seed(4)
+    M, N, K = 512, 768, 256
+    x, W = rnd(M, K), rnd(N, K, scale=0.05)
+    a = torch.empty(M, N, device=dev(), dtype=torch.bfloat16)
+    b = torch.empty_like(a)
+    nat().linear_fwd(a, x, W)
+    nat().lib().mlb_gemm_force_simt(1)
+    try:
+        nat().linear_fwd(b, x, W)
+    finally:
+        nat().lib().mlb_gemm_force_simt(0)
+    close(a, b, rtol=1e-2, atol=1e-2, name="tc vs simt")
+
+
+# ------------------------------------------------------------------ attention
+ATTN_CASES = [(2, 128, 2, 64), (1, 256, 3, 64), (2, 384, 2, 64), (2, 192, 2, 64), (2, 64, 4, 64), (1, 1024, 2, 64),
+              (1, 256, 2, 128), (2, 320, 1, 128), (2, 64, 4, 32), (1, 100, 2, 16)]
+
+
+@pytest.mark.parametrize("B,T,H,hd", ATTN_CASES)
+def test_attn_fwd_bwd(B, T, H, hd):
+    torch.manual_seed(5)
+    C = H * hd
+    qkv = rnd(B * T, 3 * C, scale=1.0)
+    out = torch.empty(B * T, C, device=dev(), dtype=torch.bfloat16)
+    lse = torch.empty(B, H, T, device=dev())
+    nat().attn_fwd(out, lse, qkv, B, T, H, hd)
+    eo, el = torch.empty(B * T, C, device=dev()), torch.empty(B, H, T, device=dev())
+    ref.attn_fwd(eo, el, qkv, B, T, H, hd)
+    close(out, eo, name="attn out")
+    close(lse, el, rtol=1e-3, atol=2e-2, name="attn lse")
+    dout = rnd(B * T, C)
+    dqkv = torch.empty(B * T, 3 * C, device=dev(), dtype=torch.bfloat16)
+    fused = nat().attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd)
+    assert fused is False
+    ed = torch.empty(B * T, 3 * C, device=dev())
+    ref.attn_bwd(ed, dout, qkv, eo.to(torch.bfloat16), el, B, T, H, hd)
+    d5, e5 = dqkv.view(B, T, 3, C), ed.view(B, T, 3, C)
+    for i, nm in enumerate(("dq", "dk", "dv")):
+        close(d5[:, :, i], e5[:, :, i], rtol=3e-2, atol=3e-2, name=nm)
+
+
+def test_attn_bwd_fused_rope_matches_separate():
+    torch.manual_seed(6)
+    B, T, H, hd = 2, 256, 2, 64
+    C = H * hd
+    qkv, dout = rnd(B * T, 3 * C), rnd(B * T, C)
+    out = torch.empty(B * T, C, device=dev(), dtype=torch.bfloat16)
+    lse = torch.empty(B, H, T, device=dev())
+    nat().attn_fwd(out, lse, qkv, B, T, H, hd)
+    cos, sin = ref.rope_tables(T, hd, 10000.0, dev())
+    a = torch.empty(B * T, 3 * C, device=dev(), dtype=torch.bfloat16)
+    b = torch.empty_like(a)
+    assert nat().attn_bwd(a, dout, qkv, out, lse, B, T, H, hd, rope=(cos, sin)) is True
+    nat().attn_bwd(b, dout, qkv, out, lse, B, T, H, hd)
+    nat().rope_bwd(b, cos, sin, B, T, H, hd)
+    close(a, b, rtol=2e-2, atol=2e-2, name="fused rope bwd")
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("rows,C", [(64, 768), (33, 128), (17, 100), (8, 2048), (5, 1024)])
+def test_rmsnorm_fwd_bwd(rows, C):
+    torch.manual_seed(7)
+    x, b2, w = rnd(rows, C), rnd(rows, C), (1 + 0.1 * torch.randn(C, device=dev())).to(torch.bfloat16)
+    out, rstd = torch.empty_like(x), torch.empty(rows, device=dev())
+    eo, er = torch.empty(rows, C, device=dev()), torch.empty(rows, device=dev())
+    nat().rmsnorm_fwd(out, rstd, x, w, 1e-5)
+    ref.rmsnorm_fwd(eo, er, x, w, 1e-5)
+    close(out, eo, name="rmsnorm out")
+    close(rstd, er, rtol=1e-4, atol=1e-5, name="rstd")
+    resid, out2, rstd2 = torch.empty_like(x), torch.empty_like(x), torch.empty(rows, device=dev())
+    e_res, e_out, e_r = torch.empty(rows, C, device=dev()), torch.empty(rows, C, device=dev()), torch.empty(rows, device=dev())
+    nat().add_rmsnorm_fwd(resid, out2, rstd2, x, b2, w, 1e-5)
+    ref.add_rmsnorm_fwd(e_res, e_out, e_r, x, b2, w, 1e-5)
+    close(resid, e_res, name="resid")
+    close(out2, e_out, name="add_rmsnorm out")
+    for add in (None, b2):
+        dy = rnd(rows, C)
+        dx, dw = torch.empty_like(x), torch.randn(C, device=dev())
+        edx, edw = torch.empty(rows, C, device=dev()), dw.clone()
+        nat().rmsnorm_bwd(dx, dw, dy, x, w, rstd, add)
+        ref.rmsnorm_bwd(edx, edw, dy, x, w, er, add)
+        close(dx, edx, name="rmsnorm dx")
+        close(dw, edw, rtol=1e-3, atol=1e-3, name="rmsnorm dw")
+
+
+def test_rmsnorm_bwd_deterministic_and_many_rows():
+    torch.manual_seed(8)
+    rows, C = 4096, 768
+    x, dy, w = rnd(rows, C), rnd(rows, C), rnd(C)
+    rstd = torch.rand(rows, device=dev()) + 0.5
+    res = []
+    for _ in range(2):
+        dx, dw = torch.empty_like(x), torch.zeros(C, device=dev())
+        nat().rmsnorm_bwd(dx, dw, dy, x, w, rstd, None)
+        res.append((dx.clone(), dw.clone()))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    edx, edw = torch.empty(rows, C, device=dev()), torch.zeros(C, device=dev())
+    ref.rmsnorm_bwd(edx, edw, dy, x, w, rstd, None)
+    close(res[0][1], edw, rtol=2e-3, atol=1e-2, name="dw many rows")
+
+
+@pytest.mark.parametrize("B,T,H,hd", [(2, 64, 4, 32), (1, 128, 12, 64), (2, 32, 2, 128), (1, 16, 3, 6)])
+def test_rope(B, T, H, hd):
+    torch.manual_seed(9)
+    C = H * hd
+    cos, sin = ref.rope_tables(T, hd, 10000.0, dev())
+    qkv = rnd(B * T, 3 * C)
+    a, e = qkv.clone(), qkv.clone()
+    nat().rope_fwd(a, cos, sin, B, T, H, hd)
+    ref.rope_fwd(e, cos, sin, B, T, H, hd)
+    close(a, e, name="rope fwd")
+    nat().rope_bwd(a, cos, sin, B, T, H, hd)
+    close(a, qkv, rtol=2e-2, atol=3e-2, name="rope round trip")
+
+
+@pytest.mark.parametrize("rows,I", [(64, 2048), (10, 192), (7, 100)])
+def test_swiglu(rows, I):
+    torch.manual_seed(10)
+    gu, d = rnd(rows, 2 * I, scale=2.0), rnd(rows, I)
+    out, eo = torch.empty(rows, I, device=dev(), dtype=torch.bfloat16), torch.empty(rows, I, device=dev())
+    nat().swiglu_fwd(out, gu)
+    ref.swiglu_fwd(eo, gu)
+    close(out, eo, name="swiglu fwd")
+    dgu, edgu = torch.empty_like(gu), torch.empty(rows, 2 * I, device=dev())
+    nat().swiglu_bwd(dgu, d, gu)
+    ref.swiglu_bwd(edgu, d, gu)
+    close(dgu, edgu, name="swiglu bwd")
+
+
+@pytest.mark.parametrize("rows,V", [(64, 50304), (16, 512), (9, 1001)])
+def test_cross_entropy(rows, V):
+    torch.manual_seed(11)
+    logits = rnd(rows, V, scale=3.0)
+    tgt = torch.randint(0, V, (rows,), device=dev(), dtype=torch.int32)
+    tgt[::4] = -1
+    dscale = 1.0 / 37
+    a, e = logits.clone(), logits.float().clone()
+    la, le = torch.empty(rows, device=dev()), torch.empty(rows, device=dev())
+    nat().ce_fwd_bwd(la, a, tgt, dscale)
+    ref.ce_fwd_bwd(le, e, tgt, dscale)
+    close(la, le, rtol=1e-3, atol=1e-3, name="ce loss")
+    close(a, e, rtol=2e-2, atol=1e-4, name="dlogits")
+    assert (a[::4] == 0).all() and (la[::4] == 0).all()
+
+
+@pytest.mark.parametrize("n", [4096 * 3, 1001])
+def test_adamw(n):
+    torch.manual_seed(12)
+    master = torch.randn(n, device=dev())
+    g = torch.randn(n, device=dev())
+    m, v = torch.rand(n, device=dev()) * 0.1, torch.rand(n, device=dev()) * 0.01
+    p = torch.empty(n, device=dev(), dtype=torch.bfloat16)
+    em, emm, ev = master.clone(), m.clone(), v.clone()
+    args = (1e-3, 0.9, 0.95, 1e-8, 0.1, 1 - 0.9 ** 3, 1 - 0.95 ** 3, 0.25)
+    nat().adamw(master, p, g, m, v, *args)
+    ref.adamw(em, None, g, emm, ev, *args)
+    close(master, em, rtol=1e-5, atol=1e-6, name="adamw master")
+    close(m, emm, rtol=1e-5, atol=1e-7, name="adamw m")
+    close(v, ev, rtol=1e-5, atol=1e-7, name="adamw v")
+    assert torch.equal(p, master.to(torch.bfloat16))
+
+
+def test_embedding_and_prefix():
+    torch.manual_seed(13)
+    B, T, C, V, n_pre = 2, 16, 96, 50, 4
+    wte = rnd(V, C)
+    ids = torch.randint(0, V, (B * T,), device=dev(), dtype=torch.int32)
+    out = torch.empty(B * T, C, device=dev(), dtype=torch.bfloat16)
+    nat().embed_fwd(out, wte, ids)
+    assert torch.equal(out, wte[ids.long()])
+    prefix = rnd(B * n_pre, C)
+    nat().set_prefix(out, prefix, B, T, n_pre)
+    assert torch.equal(out.view(B, T, C)[:, :n_pre], prefix.view(B, n_pre, C))
+    d = rnd(B * T, C)
+    dw, edw = torch.zeros(V, C, device=dev()), torch.zeros(V, C, device=dev())
+    nat().embed_bwd(dw, d, ids, T, n_pre)
+    ref.embed_bwd(edw, d, ids, T, n_pre)
+    close(dw, edw, rtol=1e-4, atol=1e-4, name="embed bwd")
+    g = torch.empty(B * n_pre, C, device=dev(), dtype=torch.bfloat16)
+    nat().gather_prefix_grad(g, d, B, T, n_pre)
+    assert torch.equal(g.view(B, n_pre, C), d.view(B, T, C)[:, :n_pre])
+
+
+def test_vision_helpers_and_casts():
+    torch.manual_seed(14)
+    B, P, g = 2, 16, 3
+    px = torch.randn(B, 3, g * P, g * P, device=dev())
+    out = torch.empty(B * g * g, 3 * P * P, device=dev(), dtype=torch.bfloat16)
+    e = torch.empty(B * g * g, 3 * P * P, device=dev())
+    nat().patchify(out, px, P)
+    ref.patchify(e, px, P)
+    assert torch.equal(out, e.to(torch.bfloat16))
+    NP, vC, n_patch = B * 9, 96, 9
+    x, pos = rnd(NP, vC), rnd(n_patch, vC)
+    a, ee = x.clone(), x.clone()
+    nat().add_posembed(a, pos, n_patch)
+    ref.add_posembed(ee, pos, n_patch)
+    close(a, ee, name="posembed")
+    dpos, edpos = torch.zeros(n_patch, vC, device=dev()), torch.zeros(n_patch, vC, device=dev())
+    nat().posembed_grad(dpos, x, n_patch)
+    ref.posembed_grad(edpos, x, n_patch)
+    close(dpos, edpos, rtol=1e-4, atol=1e-4, name="posembed grad")
+    r = torch.empty_like(x)
+    nat().residual_add(r, x, a)
+    close(r, x.float() + a.float(), name="residual")
+    f = torch.randn(1003, device=dev())
+    bb = torch.empty(1003, device=dev(), dtype=torch.bfloat16)
+    nat().cast(bb, f)
+    assert torch.equal(bb, f.to(torch.bfloat16))
+    ff = torch.empty(1003, device=dev())
+    nat().cast(ff, bb, 0.5)
+    close(ff, bb.float() * 0.5, rtol=1e-6, atol=1e-6, name="cast back")
