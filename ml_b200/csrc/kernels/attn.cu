@@ -225,6 +225,33 @@ __global__ void __launch_bounds__(128) attn_fwd_tc_kernel(const __grid_constant_
 // ================================================================== backward: delta = rowsum(dO * O)
 __global__ void attn_delta_k(float* __restrict__ delta, const bf16* __restrict__ dout, const bf16* __restrict__ out, int B, int T,
                              int H, int hd) {
+  // one group of hd/8 consecutive lanes per (row, head): 16-byte loads, shuffle reduction inside the group
+  const int gsz = hd >> 3;  // lanes per head (8 for hd=64, 16 for hd=128); a power of two <= 32 on this path
+  const long gidx = ((long)blockIdx.x * blockDim.x + threadIdx.x) / gsz;
+  const int gl = threadIdx.x % gsz;
+  const long total = (long)B * T * H;
+  float s = 0.f;
+  if (gidx < total) {
+    const uint4 a = *reinterpret_cast<const uint4*>(out + gidx * hd + gl * 8);
+    const uint4 d = *reinterpret_cast<const uint4*>(dout + gidx * hd + gl * 8);
+    const bf162* pa = reinterpret_cast<const bf162*>(&a);
+    const bf162* pd = reinterpret_cast<const bf162*>(&d);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pd[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  for (int o = gsz >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (gidx < total && gl == 0) {
+    const int h = gidx % H;
+    const long bt = gidx / H;
+    const int b = bt / T, t = bt % T;
+    delta[((long)b * H + h) * T + t] = s;
+  }
+}
+__global__ void attn_delta_scalar_k(float* __restrict__ delta, const bf16* __restrict__ dout, const bf16* __restrict__ out, int B,
+                                    int T, int H, int hd) {
   const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= (long)B * T * H) return;
@@ -722,8 +749,11 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
   const int C = H * hd;
   const float scale = 1.0f / sqrtf((float)hd);
   {
-    long warps = (long)B * T * H;
-    attn_delta_k<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
+    const long heads = (long)B * T * H;
+    const int gsz = hd / 8;
+    const bool vec = (hd % 8 == 0) && gsz <= 32 && (gsz & (gsz - 1)) == 0 && ((uintptr_t)dout % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    if (vec) attn_delta_k<<<(unsigned)((heads * gsz + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
+    else attn_delta_scalar_k<<<(unsigned)((heads * 32 + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
   }
   if (tc_ok(qkv, dout, H, hd) && ((uintptr_t)dqkv % 16 == 0)) {
     const CUtensorMap* tq = mlb_tmap_cached(qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, 64);

@@ -219,11 +219,54 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, floa
   if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
   __syncthreads();
   if (is_last) {
+    // Fold the per-block partial rows into dw in a fixed order: warp w sums blocks w, w+8, ... for every column, the
+    // eight warp sums are then added in warp order through shared memory.
     __threadfence();
-    for (int i = threadIdx.x; i < C; i += blockDim.x) {
-      float s = 0.f;
-      for (int b = 0; b < (int)gridDim.x; b++) s += __ldcg(&partial[(long)b * C + i]);
-      dw[i] += s;
+    const int nb = (int)gridDim.x;
+    for (int c0 = 0; c0 < C; c0 += 32 * 4) {
+      const int c = c0 + lane * 4;
+      float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c + 3 < C) {
+        for (int b = warp; b < nb; b += nwarp) {
+          const float4 p = __ldcg(reinterpret_cast<const float4*>(&partial[(long)b * C + c]));
+          acc4.x += p.x; acc4.y += p.y; acc4.z += p.z; acc4.w += p.w;
+        }
+      } else {
+        for (int b = warp; b < nb; b += nwarp) {
+          if (c < C) acc4.x += __ldcg(&partial[(long)b * C + c]);
+          if (c + 1 < C) acc4.y += __ldcg(&partial[(long)b * C + c + 1]);
+          if (c + 2 < C) acc4.z += __ldcg(&partial[(long)b * C + c + 2]);
+        }
+      }
+      __syncthreads();
+      float* red = sh;  // reuse: nwarp x 128 floats (C >= 128 floats is not guaranteed, so clamp below)
+      if (C >= nwarp * 128) {
+        red[warp * 128 + lane * 4 + 0] = acc4.x; red[warp * 128 + lane * 4 + 1] = acc4.y;
+        red[warp * 128 + lane * 4 + 2] = acc4.z; red[warp * 128 + lane * 4 + 3] = acc4.w;
+        __syncthreads();
+        if (warp == 0) {
+          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int w2 = 0; w2 < nwarp; w2++) {
+            t.x += red[w2 * 128 + lane * 4 + 0]; t.y += red[w2 * 128 + lane * 4 + 1];
+            t.z += red[w2 * 128 + lane * 4 + 2]; t.w += red[w2 * 128 + lane * 4 + 3];
+          }
+          if (c < C) dw[c] += t.x;
+          if (c + 1 < C) dw[c + 1] += t.y;
+          if (c + 2 < C) dw[c + 2] += t.z;
+          if (c + 3 < C) dw[c + 3] += t.w;
+        }
+      } else {
+        // narrow rows: serialise the warps instead of staging through shared memory
+        for (int w2 = 0; w2 < nwarp; w2++) {
+          if (warp == w2) {
+            if (c < C) dw[c] += acc4.x;
+            if (c + 1 < C) dw[c + 1] += acc4.y;
+            if (c + 2 < C) dw[c + 2] += acc4.z;
+            if (c + 3 < C) dw[c + 3] += acc4.w;
+          }
+          __syncthreads();
+        }
+      }
     }
     if (threadIdx.x == 0) *ticket = 0;
   }
@@ -399,7 +442,10 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, 
 // ------------------------------------------------------------------ AdamW (fp32 master/m/v, bf16 copy written in the same pass)
 __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, const float* __restrict__ grads,
                         float* __restrict__ m, float* __restrict__ v, long n, float lr, float b1, float b2, float eps, float wd,
-                        float inv_bc1, float inv_bc2, float grad_scale) {
+                        float inv_bc1, float inv_bc2, float grad_scale, const float* __restrict__ dev_hyper) {
+  // dev_hyper (optional, device memory): {lr, 1/bc1, 1/bc2, grad_scale} override the launch arguments, so a captured
+  // CUDA graph can be replayed with the step-dependent bias corrections of the current step.
+  if (dev_hyper) { lr = dev_hyper[0]; inv_bc1 = dev_hyper[1]; inv_bc2 = dev_hyper[2]; grad_scale = dev_hyper[3]; }
   long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i + 3 < n) {
     float4 g = *reinterpret_cast<const float4*>(grads + i);
@@ -589,10 +635,10 @@ MLB_API int mlb_ce_fwd_bwd(float* losses, void* logits, const int* tgt, long row
   LAUNCH_RET;
 }
 MLB_API int mlb_adamw(float* master, void* params, const float* grads, float* m, float* v, long n, float lr, float b1, float b2,
-                      float eps, float wd, float bc1, float bc2, float grad_scale, cudaStream_t st) {
+                      float eps, float wd, float bc1, float bc2, float grad_scale, const float* dev_hyper, cudaStream_t st) {
   if (n == 0) return 0;
   adamw_k<<<gs((n + 3) / 4, 256), 256, 0, st>>>(master, (bf16*)params, grads, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2,
-                                                grad_scale);
+                                                grad_scale, dev_hyper);
   LAUNCH_RET;
 }
 MLB_API int mlb_cast_f2b(void* out, const float* in, long n, float scale, cudaStream_t st) {

@@ -34,8 +34,9 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * BK * 2;   // 16/32 KB
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGING_BYTES = 4 * 2 * 4096;  // 4 epilogue warps x 2 buffers x [32 rows x 128 B]
   static constexpr int BAR_BYTES = 256;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
 };
 
 struct GemmArgs {
@@ -47,12 +48,14 @@ struct GemmArgs {
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs g) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full = (uint64_t*)(smem + STAGES * S::STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* full = (uint64_t*)(staging + S::STAGING_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -67,6 +70,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tmA);
     tc::tma_prefetch_desc(&tmB);
+    tc::tma_prefetch_desc(&tmD);
   }
   if (warp == 1) tc::tmem_alloc(tmem_slot, 2 * BN);
   tc::tc_fence_before();
@@ -136,8 +140,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
+    // Each warp owns 32 accumulator rows (its TMEM lane group).  A 128-byte-wide slab of those rows (64 bf16 or
+    // 32 fp32 columns) is converted into a swizzled 4 KB staging buffer and handed to TMA: a tiled store for bf16
+    // outputs, an fp32 add-reduce for split-K weight gradients.  Two buffers per warp keep one transfer in flight;
+    // TMA clips rows / columns beyond the matrix.
     const int lg = warp & 3;  // TMEM lane group this warp may read
-    int it = 0;
+    uint8_t* my_stage = staging + lg * 8192;
+    constexpr int SLAB_COLS = (EPI == EPI_BF16) ? 64 : 32;
+    int it = 0, slab = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
       const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n;
@@ -145,50 +155,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int acc = it & 1, acc_phase = (it >> 1) & 1;
       if (!tc::mbar_wait(&acc_full[acc], acc_phase, 4)) { ok = false; break; }
       tc::tc_fence_after();
-      const int row = m0 + lg * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
+      const bool rows_live = (m0 + lg * 32) < g.M;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        uint32_t r[32];
-        tc::tmem_ld32(taddr + c * 32, r);
+      for (int c = 0; c < BN / SLAB_COLS; c++) {
+        uint8_t* buf = my_stage + (slab & 1) * 4096;
+        uint32_t r[32], r2[32];
+        tc::tmem_ld32(taddr + c * SLAB_COLS, r);
+        if (EPI == EPI_BF16) tc::tmem_ld32(taddr + c * SLAB_COLS + 32, r2);
         tc::tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < g.M && col0 < g.N) {
-          if (EPI == EPI_BF16) {
-            bf16* o = (bf16*)g.out + (size_t)row * g.ldo + col0;
-            if (col0 + 32 <= g.N) {
+        const int col0 = n0 + c * SLAB_COLS;
+        if (!rows_live || col0 >= g.N) continue;   // warp-uniform
+        if (lane == 0) tc::tma_wait_group_read<1>();   // the transfer that last used this buffer has read it
+        __syncwarp();
+        uint8_t* rowp = buf + lane * 128;
+        if (EPI == EPI_BF16) {
 #pragma unroll
-              for (int v = 0; v < 4; v++) {
-                uint4 pk;
-                pk.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                pk.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                pk.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                pk.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                *reinterpret_cast<uint4*>(o + v * 8) = pk;
-              }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < g.N; i++) o[i] = __float2bfloat16(__uint_as_float(r[i]));
-            }
-          } else {
-            float* o = (float*)g.out + (size_t)row * g.ldo + col0;
-            if (col0 + 32 <= g.N) {
+          for (int v = 0; v < 8; v++) {
+            const uint32_t* src = (v < 4) ? &r[v * 8] : &r2[(v - 4) * 8];
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            pk.y = pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            pk.z = pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            pk.w = pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = pk;
+          }
+        } else {
 #pragma unroll
-              for (int v = 0; v < 8; v++) {
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + v * 4),
-                             "f"(__uint_as_float(r[v * 4 + 0])), "f"(__uint_as_float(r[v * 4 + 1])),
-                             "f"(__uint_as_float(r[v * 4 + 2])), "f"(__uint_as_float(r[v * 4 + 3]))
-                             : "memory");
-              }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < g.N; i++) atomicAdd(o + i, __uint_as_float(r[i]));
-            }
+          for (int v = 0; v < 8; v++) {
+            uint4 pk = make_uint4(r[v * 4 + 0], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = pk;
           }
         }
+        tc::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (EPI == EPI_BF16) tc::tma_store_2d(&tmD, buf, col0, m0 + lg * 32);
+          else tc::tma_reduce_add_2d(&tmD, buf, col0, m0 + lg * 32);
+          tc::tma_commit_group();
+        }
+        slab++;   // counts issued transfers only, so the two buffers strictly alternate
       }
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
     }
+    if (lane == 0) tc::tma_wait_group<0>();   // all stores / reductions of this warp have completed
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -259,34 +271,34 @@ EncodeTiledFn get_encode() {
 }
 
 std::mutex g_tmap_mu;
-typedef std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t> TmapKey;
+typedef std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t, int> TmapKey;
 std::map<TmapKey, CUtensorMap*> g_tmaps;
 
 }  // namespace
 
-bool mlb_make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
-                        uint32_t box_rows, uint32_t box_cols) {
+bool mlb_make_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                   uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return false;
-  if (((uintptr_t)base & 15) || ((pitch_elems * 2) & 15)) return false;
+  if (((uintptr_t)base & 15) || ((pitch_elems * elem_bytes) & 15) || box_cols * elem_bytes != 128) return false;
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {pitch_elems * 2};
+  cuuint64_t strides[1] = {pitch_elems * elem_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
 const CUtensorMap* mlb_tmap_cached(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
-                                   uint32_t box_rows, uint32_t box_cols) {
+                                   uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
   std::lock_guard<std::mutex> lk(g_tmap_mu);
-  TmapKey key(base, rows, cols, pitch_elems, box_rows, box_cols);
+  TmapKey key(base, rows, cols, pitch_elems, box_rows, box_cols, elem_bytes);
   auto it = g_tmaps.find(key);
   if (it != g_tmaps.end()) return it->second;
   CUtensorMap* m = new CUtensorMap;
-  if (!mlb_make_tmap_bf16(m, base, rows, cols, pitch_elems, box_rows, box_cols)) { delete m; return nullptr; }
+  if (!mlb_make_tmap(m, base, rows, cols, pitch_elems, box_rows, box_cols, elem_bytes)) { delete m; return nullptr; }
   g_tmaps[key] = m;
   return m;
 }
@@ -308,7 +320,7 @@ int g_force_simt = 0;        // test hook: route everything through the SIMT ker
 int g_max_ctas = 0;          // 0 = one CTA per SM; >0 caps the persistent grid (leaves SMs to a concurrent kernel)
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
-int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmArgs& g, cudaStream_t st) {
+int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, const GemmArgs& g, cudaStream_t st) {
   auto kern = gemm_tc_kernel<BN, A_MN, B_MN, EPI>;
   static bool attr_done = false;
   if (!attr_done) {
@@ -319,7 +331,7 @@ int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const GemmArgs& g,
   int total = g.tiles_m * g.tiles_n * g.splits;
   int cap = g_max_ctas > 0 ? g_max_ctas : num_sms();
   int grid = total < cap ? total : cap;
-  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, st>>>(*tmA, *tmB, g);
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, st>>>(*tmA, *tmB, *tmD, g);
   return (int)cudaGetLastError();
 }
 
@@ -365,9 +377,10 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   g.splits = ceil_div_i(g.kb_total, g.kb_per_split);
   const CUtensorMap* tmA = A_MN ? mlb_tmap_cached(A, K, M, lda, 64, 64) : mlb_tmap_cached(A, M, K, lda, BM, 64);
   const CUtensorMap* tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, BN, 64);
-  if (!tmA || !tmB) return -2;
-  if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, g, st);
-  return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, g, st);
+  const CUtensorMap* tmD = (EPI == EPI_BF16) ? mlb_tmap_cached(out, M, N, ldo, 32, 64, 2) : mlb_tmap_cached(out, M, N, ldo, 32, 32, 4);
+  if (!tmA || !tmB || !tmD) return -2;
+  if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
+  return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
 }
 
 }  // namespace

@@ -73,6 +73,26 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// shared -> global tiled store / fp32 add-reduce (bulk async-group completion); out-of-range parts of the box are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(smem_u32(smem_src)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_wait_group_read() {  // at most N groups still reading their shared-memory source
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -159,8 +179,9 @@ __device__ __forceinline__ bool elect_one() {
 // 2D row-major bf16 tensor [rows, cols] with `pitch_elems` elements between rows; box = [box_rows, 64 cols]
 // (64 bf16 = one 128-byte swizzle row).  Requires 16-byte aligned base and pitch.  Returns false if the
 // driver entry point is unavailable or the encode is rejected.
-bool mlb_make_tmap_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
-                        uint32_t box_rows, uint32_t box_cols = 64);
+// `elem_bytes` = 2 (bf16) or 4 (fp32; box_cols is then 32 so that a box row is still 128 bytes).
+bool mlb_make_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                   uint32_t box_rows, uint32_t box_cols, int elem_bytes);
 // Cached lookup (key = all arguments); the returned pointer stays valid for the life of the process.
 const CUtensorMap* mlb_tmap_cached(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
-                                   uint32_t box_rows, uint32_t box_cols = 64);
+                                   uint32_t box_rows, uint32_t box_cols = 64, int elem_bytes = 2);

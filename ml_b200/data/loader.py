@@ -1,0 +1,132 @@
+"""llm.c `.bin` token loader and the pinned, double-buffered input pipe.
+
+`TokenLoader` wraps the C++ core (csrc/host/loader.cpp): mmap'ed file, window of B*T+1 tokens at `pos`,
+ids = w[:-1], tgt = w[1:], pos += B*T, wrap to 0 when the next window would overrun (train/gpt.cu:925-945).
+
+`BatchPipe` is the counterpart of the reference's BatchPipe (train/gpt.cu:950-992): two slots of pinned host
+memory + device ids/tgt, a dedicated copy stream, and ready/consumed events so that the refill of a slot
+waits until compute has consumed it.  Here the host-side fill runs on a C++ worker thread, so the training
+thread only enqueues copies.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ..utils.hostlib import lib
+
+_ERR = {1: "cannot open file", 2: "bad magic / short header (not an llm.c .bin)", 3: "fewer than B*T+1 tokens"}
+
+
+def write_token_bin(path: str, tokens: torch.Tensor):
+    t = tokens.to(torch.int32).numpy().astype("uint16")
+    rc = lib().mlb_write_token_bin(path.encode(), t.ctypes.data, t.size)
+    if rc:
+        raise OSError(f"write_token_bin({path}) failed: {rc}")
+
+
+class TokenLoader:
+    def __init__(self, path: str, B: int, T: int):
+        err = C.c_int(0)
+        self.h = lib().mlb_loader_open(path.encode(), B, T, C.byref(err))
+        if not self.h:
+            raise OSError(f"{path}: {_ERR.get(err.value, 'error %d' % err.value)}")
+        self.B, self.T, self.path = B, T, path
+        self.ntok = lib().mlb_loader_ntok(self.h)
+
+    @property
+    def pos(self) -> int:
+        return lib().mlb_loader_pos(self.h)
+
+    @pos.setter
+    def pos(self, v: int):
+        lib().mlb_loader_set_pos(self.h, int(v))
+
+    def next_into(self, ids: torch.Tensor, tgt: torch.Tensor):
+        n = self.B * self.T
+        assert ids.dtype == torch.int32 and tgt.dtype == torch.int32 and ids.numel() == n and tgt.numel() == n
+        assert not ids.is_cuda and ids.is_contiguous() and tgt.is_contiguous()
+        lib().mlb_loader_next(self.h, ids.data_ptr(), tgt.data_ptr())
+
+    def next(self):
+        ids = torch.empty(self.B * self.T, dtype=torch.int32)
+        tgt = torch.empty_like(ids)
+        self.next_into(ids, tgt)
+        return ids, tgt
+
+    def close(self):
+        if self.h:
+            lib().mlb_loader_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class BatchPipe:
+    """Two-slot prefetching pipe.  Usage per step: `ids, tgt = pipe.acquire(step)` (device tensors, valid on the
+    current stream) ... compute ... `pipe.release(step)` (queues the refill of that slot with the batch for step+2)."""
+
+    def __init__(self, loader: TokenLoader, device, nslots: int = 2):
+        self.loader, self.device, self.n = loader, torch.device(device), nslots
+        n = loader.B * loader.T
+        cuda = self.device.type == "cuda"
+        self.h_ids = [torch.empty(n, dtype=torch.int32, pin_memory=cuda) for _ in range(nslots)]
+        self.h_tgt = [torch.empty(n, dtype=torch.int32, pin_memory=cuda) for _ in range(nslots)]
+        self.d_ids = [torch.empty(n, dtype=torch.int32, device=self.device) for _ in range(nslots)]
+        self.d_tgt = [torch.empty(n, dtype=torch.int32, device=self.device) for _ in range(nslots)]
+        self.pipe = lib().mlb_pipe_create(loader.h, nslots)
+        self.copy_stream = torch.cuda.Stream(self.device) if cuda else None
+        self.ready = [torch.cuda.Event() for _ in range(nslots)] if cuda else None
+        self.consumed = [torch.cuda.Event() for _ in range(nslots)] if cuda else None
+        self.slot_pos = [0] * nslots
+        for s in range(nslots):
+            self._submit(s)
+        for s in range(nslots):
+            self._upload(s, first=True)
+
+    def _submit(self, s):
+        lib().mlb_pipe_submit(self.pipe, s, self.h_ids[s].data_ptr(), self.h_tgt[s].data_ptr())
+
+    def _upload(self, s, first=False):
+        self.slot_pos[s] = lib().mlb_pipe_wait(self.pipe, s)
+        if self.copy_stream is None:
+            self.d_ids[s].copy_(self.h_ids[s])
+            self.d_tgt[s].copy_(self.h_tgt[s])
+            return
+        with torch.cuda.stream(self.copy_stream):
+            if not first:
+                self.copy_stream.wait_event(self.consumed[s])
+            self.d_ids[s].copy_(self.h_ids[s], non_blocking=True)
+            self.d_tgt[s].copy_(self.h_tgt[s], non_blocking=True)
+            self.ready[s].record(self.copy_stream)
+
+    def acquire(self, step: int):
+        s = step % self.n
+        if self.copy_stream is not None:
+            torch.cuda.current_stream().wait_event(self.ready[s])
+        return self.d_ids[s], self.d_tgt[s]
+
+    def release(self, step: int):
+        s = step % self.n
+        if self.copy_stream is not None:
+            self.consumed[s].record(torch.cuda.current_stream())
+            # the pinned slot may be rewritten only after its H2D copy has run
+            self.ready[s].synchronize()
+        self._submit(s)
+        self._upload(s)
+
+    def close(self):
+        if self.pipe:
+            lib().mlb_pipe_destroy(self.pipe)
+            self.pipe = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,378 @@
+"""Command-line modes: `python -m ml_b200.gpt <mode> [args]` (also `python -m ml_b200 <mode>`).
+
+Modes and their positional arguments follow the reference program (train/gpt.cu:1252-1258, :1614):
+    overfit | mm_overfit | mm_bench [B steps] | bench [B steps] | train <tokens.bin> [steps] |
+    bench_ddp [B steps] | train_ddp <tokens.bin> [steps] | plan (plan_pp, topology) | lmce_check
+plus the ENTROPY_* environment knobs.  The printed line formats are kept because scripts parse them.
+Additions: `train` takes --ckpt-dir/--save-every/--resume/--log-dir (the prototype's checkpoint and metrics
+options, csrc/src/main.cu:30-57), a warm-up + cosine LR schedule (--warmup-ratio), and `train_ddp` really
+trains from a data file on every rank (the reference aliases it to bench_ddp).
+"""
+from __future__ import annotations
+
+import math
+import os
+import signal
+import sys
+import time
+
+MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|plan|lmce_check"
+
+
+def _banner(mode, dev):
+    import torch
+    if dev.type == "cuda":
+        p = torch.cuda.get_device_properties(dev)
+        print(f"== ml_b200 gpt :: {mode} on {p.name} ({p.multi_processor_count} SMs) ==")
+    else:
+        print(f"== ml_b200 gpt :: {mode} on cpu ==")
+
+
+def check_device_arch(dev):
+    """The kernel library is built for sm_100a only: refuse anything else up front (train/gpt.cu:1030-1041)."""
+    import torch
+    if dev.type != "cuda":
+        return
+    major, minor = torch.cuda.get_device_capability(dev)
+    if major != 10:
+        sys.exit(f"this build targets sm_100a (B200); device reports sm_{major}{minor}")
+
+
+def lr_at(step, total, base, warmup_ratio):
+    """Linear warm-up then cosine decay (csrc/src/main.cu:244-254); warmup_ratio <= 0 keeps the constant rate."""
+    if warmup_ratio <= 0 or total <= 0:
+        return base
+    w = max(1, int(total * warmup_ratio))
+    if step < w:
+        return base * (step + 1) / w
+    p = (step - w) / max(1, total - w)
+    return base * 0.5 * (1.0 + math.cos(math.pi * min(1.0, p)))
+
+
+def _device():
+    import torch
+    forced = os.environ.get("ENTROPY_DEVICE", "")
+    if forced:
+        return torch.device(forced)
+    return torch.device("cuda", int(os.environ.get("LOCAL_RANK", os.environ.get("SLURM_LOCALID", 0)))) if torch.cuda.is_available() else torch.device("cpu")
+
+
+def mode_overfit(argv):
+    from . import Config
+    from .trainer import Trainer
+    from .utils.rng import Stream
+    dev = _device()
+    _banner("overfit", dev)
+    cfg = Config(V=256, C=128, L=4, H=4, I=256, T=64)
+    B = 4
+    tr = Trainer(cfg, B, dev, lr=1e-3, wd=0.0)
+    ids, tgt = Stream(99).token_pairs(B * cfg.T, cfg.V)
+    tr.set_batch(ids.to(dev), tgt.to(dev))
+    print(f"overfitting a fixed random batch (BT={B * cfg.T}, {tr.model.np} params)...")
+    last = None
+    for step in range(200):
+        tr.step()
+        if step % 20 == 0 or step == 199:
+            last = tr.model.mean_loss()
+            print(f"step {step:3d}  loss {last:.5f}")
+    print("(expect loss -> near 0 if fwd/bwd/optimizer are correct)")
+    return 0 if last is not None and last < 0.05 else 1
+
+
+def _mm_setup(B, dev, cfg_defaults, lr, wd, env_cfg):
+    import torch
+    from . import Config, VisionConfig
+    from .config import env_int
+    from .trainer import Trainer
+    from .data import mm_batch
+    n_patch = env_int("ENTROPY_MM_PATCHES", 16) if env_cfg else 16
+    T_text = env_int("ENTROPY_MM_TEXT", 48) if env_cfg else 48
+    T = n_patch + T_text
+    if env_cfg:
+        cfg = Config(V=env_int("ENTROPY_V", 256), C=env_int("ENTROPY_C", 128), L=env_int("ENTROPY_L", 4),
+                     H=env_int("ENTROPY_H", 4), I=env_int("ENTROPY_I", 256), T=T)
+        vc = VisionConfig(vC=env_int("ENTROPY_VC", 96), vL=env_int("ENTROPY_VL", 3), vI=env_int("ENTROPY_VI", 192), n_patch=n_patch)
+    else:
+        cfg = Config(V=256, C=128, L=4, H=4, I=256, T=T)
+        vc = VisionConfig(vC=96, vL=3, vI=192, n_patch=n_patch)
+    tr = Trainer(cfg, B, dev, lr=lr, wd=wd, vision=vc, n_text=T_text)
+    patches, ids, tgt = mm_batch(B, n_patch, T_text, cfg.V, vc.patch_dim)
+    tr.vision.patches.copy_(patches.to(tr.vision.dtype).to(dev))
+    tr.set_batch(ids.to(dev), tgt.to(dev))
+    return tr, cfg, vc, n_patch, T_text
+
+
+def mode_mm_overfit(argv):
+    dev = _device()
+    _banner("mm_overfit", dev)
+    tr, cfg, vc, n_patch, T_text = _mm_setup(2, dev, None, 1e-3, 0.0, False)
+    print(f"multimodal overfit: {n_patch} img tokens + {T_text} text, LM {tr.model.np / 1e3:.0f}K params, "
+          f"vision {tr.vision.np / 1e3:.0f}K params")
+    last = None
+    for step in range(200):
+        tr.step()
+        if step % 20 == 0 or step == 199:
+            last = tr.model.mean_loss(n_pre=n_patch, valid_tokens=2 * T_text)
+            print(f"step {step:3d}  loss {last:.5f}")
+    print("(loss -> ~0 means gradients flow LM -> projector -> vision tower correctly)")
+    return 0 if last < 0.05 else 1
+
+
+def _timed(tr, steps, dev, warm=3):
+    import torch
+    for _ in range(warm):
+        tr.step()
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            tr.step()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps / 1e3
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tr.step()
+    return (time.perf_counter() - t0) / steps
+
+
+def mode_mm_bench(argv):
+    dev = _device()
+    _banner("mm_bench", dev)
+    B = int(argv[0]) if argv else 2
+    steps = int(argv[1]) if len(argv) > 1 else 50
+    tr, cfg, vc, n_patch, T_text = _mm_setup(B, dev, None, 1e-4, 0.1, True)
+    tr.use_graph = dev.type == "cuda" and os.environ.get("ENTROPY_GRAPH", "1") != "0"
+    print(f"MM bench: B={B} patches={n_patch} text={T_text} LM {tr.model.np / 1e6:.1f}M params vision "
+          f"{tr.vision.np / 1e6:.1f}M params steps={steps}")
+    dt = _timed(tr, steps, dev)
+    ls = tr.model.mean_loss(n_pre=n_patch, valid_tokens=B * T_text)
+    print(f"mm step: {dt * 1e3:.2f} ms | text tok/s {B * T_text / dt:.0f} | image tok/s {B * n_patch / dt:.0f} | loss {ls:.4f}")
+    return 0
+
+
+def mode_bench(argv):
+    import torch
+    from . import Config, RunConfig
+    from .trainer import Trainer
+    from .data import bench_batch
+    from .layout import flops_per_step
+    from .utils.prof import Prof
+    dev = _device()
+    _banner("bench", dev)
+    check_device_arch(dev)
+    cfg = Config.from_env()
+    B = int(argv[0]) if argv else 8
+    steps = int(argv[1]) if len(argv) > 1 else 20
+    run = RunConfig.from_env()
+    tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, use_graph=bool(run.graph))
+    ids, tgt = bench_batch(B, cfg.T, cfg.V)
+    tr.set_batch(ids.to(dev), tgt.to(dev))
+    print(f"config: V={cfg.V} C={cfg.C} L={cfg.L} H={cfg.H} I={cfg.I} T={cfg.T} B={B}  params={tr.model.np / 1e6:.1f}M")
+    for _ in range(3):
+        tr.step()
+    if run.prof:
+        prof = Prof(dev)
+        tr.model.prof = prof
+        g, tr.use_graph = tr.use_graph, False
+        prof.mark("step_start")
+        tr.step()
+        prof.mark("adamw")
+        print("  -- profile (1 step) --")
+        prof.report()
+        tr.model.prof, tr.use_graph = None, g
+    # forward-only breakdown
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tr.model.forward(tr.ids[0])
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    dtf = (time.perf_counter() - t0) / steps
+    dt = _timed(tr, steps, dev, warm=1)
+    print(f"  [fwd-only {dtf * 1e3:.2f} ms | fwd+bwd+opt {dt * 1e3:.2f} ms{' (graph)' if tr.use_graph else ''}]")
+    fl = flops_per_step(cfg, B)
+    peak = run.peak_tflops * 1e12
+    print(f"step time: {dt * 1e3:.2f} ms   throughput: {B * cfg.T / dt:.0f} tok/s   TFLOP/s: {fl / dt / 1e12:.1f}   "
+          f"MFU: {100 * fl / dt / peak:.1f}%")
+    return 0
+
+
+def _train_loop(argv, ddp):
+    import argparse
+    import torch
+    import torch.distributed as dist
+    from . import Config, RunConfig
+    from .trainer import Trainer
+    from .data import TokenLoader, BatchPipe
+    from .layout import flops_per_step
+    from .parallel.bootstrap import init_distributed, shutdown
+    from .utils import ckpt as ck
+    from .utils.metrics import MetricsLogger
+    ap = argparse.ArgumentParser(prog="gpt train")
+    ap.add_argument("bin")
+    ap.add_argument("steps", nargs="?", type=int, default=100)
+    ap.add_argument("--ckpt-dir", "--checkpoint", default="")
+    ap.add_argument("--save-every", type=int, default=0)
+    ap.add_argument("--resume", type=int, default=-1, help="step to resume from (-2 = latest)")
+    ap.add_argument("--log-dir", default="")
+    ap.add_argument("--wandb", action="store_true")
+    ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--weight-decay", type=float, default=0.1)
+    ap.add_argument("--warmup-ratio", type=float, default=0.0)
+    a = ap.parse_args(argv)
+    if ddp:
+        rank, world, local, dev = init_distributed()
+    else:
+        rank, world, dev = 0, 1, _device()
+    if rank == 0:
+        _banner("train_ddp" if ddp else "train", dev)
+    cfg = Config.from_env()
+    run = RunConfig.from_env()
+    B = run.B if "ENTROPY_B" in os.environ else 16
+    tr = Trainer(cfg, B, dev, run, lr=a.lr, wd=a.weight_decay, world=world, rank=rank,
+                 use_graph=bool(run.train_graph) and a.warmup_ratio <= 0)
+    loader = TokenLoader(a.bin, B * tr.accum, cfg.T)
+    if rank == 0:
+        print(f"loader: {a.bin}  {loader.ntok} tokens")
+    # every rank reads a disjoint stride of the file: rank r starts r windows in, and skips world windows per step
+    win = B * tr.accum * cfg.T
+    loader.pos = (rank * win) % max(1, loader.ntok - win - 1)
+    start_step, tokens_seen = 0, 0
+    if a.ckpt_dir and a.resume != -1:
+        st = ck.latest_step(a.ckpt_dir) if a.resume == -2 else a.resume
+        info = ck.load(a.ckpt_dir, st, tr.model.master, tr.model.m, tr.model.v) if st is not None else None
+        if info is not None:
+            tr.model.sync_params()
+            start_step, tokens_seen, tr.t = info["step"], info["tokens_seen"], info["opt_t"]
+            loader.pos = info["loader_pos"]
+            if rank == 0:
+                print(f"resumed from step {start_step} (loss {info['loss']:.4f}, {tokens_seen} tokens seen)")
+        elif rank == 0:
+            print("no checkpoint to resume from; starting fresh")
+    pipe = BatchPipe(loader, dev)
+    writer = ck.CheckpointWriter() if (a.ckpt_dir and rank == 0) else None
+    logger = MetricsLogger(a.log_dir, rank, wandb=a.wandb) if a.log_dir else None
+    stop = {"flag": False}
+    for sig in (signal.SIGINT, signal.SIGTERM):
+        try:
+            signal.signal(sig, lambda *_: stop.__setitem__("flag", True))
+        except ValueError:
+            pass
+    if rank == 0:
+        print(f"training: B={B} T={cfg.T} accum={tr.accum} world={world} params={tr.model.np / 1e6:.1f}M steps={a.steps}")
+    fl = flops_per_step(cfg, B) * tr.accum * world
+    peak = run.peak_tflops * 1e12 * world
+    t_last, s_last = time.perf_counter(), start_step
+    loss = float("nan")
+    for step in range(start_step, a.steps):
+        if stop["flag"]:
+            if rank == 0:
+                print("signal received: stopping after this step")
+            break
+        ids, tgt = pipe.acquire(step)
+        tr.ids.copy_(ids.view(tr.accum, -1))
+        tr.tgt.copy_(tgt.view(tr.accum, -1))
+        tr.hyper["lr"] = lr_at(step, a.steps, a.lr, a.warmup_ratio)
+        tr.ddp.hyper["lr"] = tr.hyper["lr"]
+        tr.step()
+        pipe.release(step)
+        if world > 1:
+            # the file is striped over ranks: skip the windows the other ranks consume
+            loader.pos = (loader.pos + (world - 1) * win) % max(1, loader.ntok - win - 1)
+        tokens_seen += win * world
+        if (step + 1) % run.log_every == 0 or step + 1 == a.steps:
+            loss = tr.loss()
+            if world > 1:
+                t = torch.tensor([loss], device=dev)
+                dist.all_reduce(t)
+                loss = float(t.item()) / world
+            now = time.perf_counter()
+            dt = (now - t_last) / max(1, step + 1 - s_last)
+            t_last, s_last = now, step + 1
+            if rank == 0:
+                print(f"step {step + 1:5d} | loss {loss:.4f} | {dt * 1e3:.2f} ms | {win * world / dt:.0f} tok/s | "
+                      f"{fl / dt / 1e12:.1f} TFLOP/s | MFU {100 * fl / dt / peak:.1f}%")
+                if logger:
+                    logger.log(step + 1, loss, tr.hyper["lr"], tokens_seen, dt * 1e3, {"mfu": fl / dt / peak, "tflops": fl / dt / 1e12})
+        if writer and a.save_every > 0 and (step + 1) % a.save_every == 0:
+            writer.save(a.ckpt_dir, step + 1, loss if loss == loss else 0.0, tokens_seen, tr.model.master, tr.model.m,
+                        tr.model.v, loader_pos=pipe.slot_pos[(step + 1) % pipe.n], opt_t=tr.t)
+    if writer:
+        writer.close()
+    if logger:
+        logger.close()
+    pipe.close()
+    if ddp:
+        shutdown()
+    return 0
+
+
+def mode_bench_ddp(argv):
+    import torch
+    import torch.distributed as dist
+    from . import Config, RunConfig
+    from .trainer import Trainer
+    from .data import bench_batch
+    from .layout import flops_per_step
+    from .parallel.bootstrap import init_distributed, shutdown
+    rank, world, local, dev = init_distributed()
+    if rank == 0:
+        _banner("bench_ddp", dev)
+    # the reference pins this shape in bench_ddp (train/gpt.cu:1563); ENTROPY_* overrides are honoured here
+    cfg = Config.from_env(V=32768)
+    B = int(argv[0]) if argv else 16
+    steps = int(argv[1]) if len(argv) > 1 else 30
+    run = RunConfig.from_env()
+    tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, world=world, rank=rank, use_graph=bool(run.graph))
+    ids, tgt = [], []
+    for k in range(tr.accum):
+        a, b = bench_batch(B, cfg.T, cfg.V, rank)
+        ids.append(a)
+        tgt.append(b)
+    tr.set_batch(torch.stack(ids).to(dev), torch.stack(tgt).to(dev))
+    if rank == 0:
+        print(f"DDP world={world}  per-GPU B={B}  accum={tr.accum}  global tokens/opt-step={B * cfg.T * world * tr.accum}  "
+              f"params={tr.model.np / 1e6:.1f}M overlap_opt={run.ddp_overlap_opt} comm={tr.ddp.comm}")
+    for _ in range(3):
+        tr.step()
+    if world > 1:
+        dist.barrier()
+    dt = _timed(tr, steps, dev, warm=0)
+    if world > 1:
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    if rank == 0:
+        gtok = B * cfg.T * world * tr.accum
+        fl = flops_per_step(cfg, B) * world * tr.accum
+        peak = run.peak_tflops * 1e12 * world
+        print(f"opt-step {dt * 1e3:.2f} ms | global {gtok / dt:.0f} tok/s | {fl / dt / 1e12:.1f} TFLOP/s agg | "
+              f"MFU {100 * fl / dt / peak:.1f}% | per-GPU {B * cfg.T * tr.accum / dt:.0f} tok/s")
+    shutdown()
+    return 0
+
+
+def main(argv=None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    mode = argv[0] if argv else "overfit"
+    rest = argv[1:]
+    if mode == "lmce_check":   # runs before any CUDA initialisation
+        from .utils import lmce_check
+        return lmce_check.main()
+    if mode in ("plan", "plan_pp", "topology"):
+        from .parallel.plan import plan_from_env
+        print(plan_from_env())
+        return 0
+    table = {"overfit": mode_overfit, "mm_overfit": mode_mm_overfit, "mm_bench": mode_mm_bench, "bench": mode_bench,
+             "bench_ddp": mode_bench_ddp, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
+    if mode not in table:
+        print(f"usage: python -m ml_b200.gpt [{MODES}] [args]", file=sys.stderr)
+        return 2
+    return table[mode](rest)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

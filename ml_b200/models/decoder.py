@@ -203,13 +203,13 @@ class GPT:
         self._hook("wte", Lo.off_wte, V * C)
 
     # ------------------------------------------------------------------ optimizer / loss
-    def adamw(self, lr, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, t=1, grad_scale=1.0, off=0, n=None):
+    def adamw(self, lr, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, t=1, grad_scale=1.0, off=0, n=None, dev_hyper=None):
         n = self.np - off if n is None else n
         bc1 = 1.0 - b1 ** t
         bc2 = 1.0 - b2 ** t
         s = slice(off, off + n)
         ops.adamw(self.master[s], self.params[s], self.grads[s], self.m[s], self.v[s],
-                  lr, b1, b2, eps, wd, bc1, bc2, grad_scale)
+                  lr, b1, b2, eps, wd, bc1, bc2, grad_scale, dev_hyper)
 
     def mean_loss(self, B=None, n_pre=0, valid_tokens=None) -> float:
         """Sum of per-row losses in double over the host / valid (train/gpt.cu:763-772)."""

@@ -110,6 +110,6 @@ class VisionTower:
         ops.posembed_grad(self.G(VL.o_pos, vc.n_patch, vC), self.dx, vc.n_patch)
         ops.linear_dw(self.G(VL.o_pw, vC, vc.patch_dim), self.dx, self.patches)
 
-    def adamw(self, lr, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, t=1, grad_scale=1.0):
+    def adamw(self, lr, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, t=1, grad_scale=1.0, dev_hyper=None):
         ops.adamw(self.master, self.params, self.grads, self.m, self.v, lr, b1, b2, eps, wd,
-                  1.0 - b1 ** t, 1.0 - b2 ** t, grad_scale)
+                  1.0 - b1 ** t, 1.0 - b2 ** t, grad_scale, dev_hyper)

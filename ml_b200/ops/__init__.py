@@ -13,15 +13,15 @@ _NAMES = [
     "ce_fwd_bwd", "adamw", "patchify", "add_posembed", "posembed_grad", "residual_add", "cast",
 ]
 
-_native = None
+_native_mod = None
 
 
-def native():
-    global _native
-    if _native is None:
-        from . import native as _n
-        _native = _n
-    return _native
+def _load_native():
+    global _native_mod
+    if _native_mod is None:
+        import importlib
+        _native_mod = importlib.import_module(".native", __name__)
+    return _native_mod
 
 
 def _make(name):
@@ -30,7 +30,7 @@ def _make(name):
     def op(*args, **kw):
         t = next(a for a in args if hasattr(a, "is_cuda"))
         if t.is_cuda:
-            return getattr(native(), name)(*args, **kw)
+            return getattr(_load_native(), name)(*args, **kw)
         return rf(*args, **kw)
 
     op.__name__ = name

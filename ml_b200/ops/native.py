@@ -46,7 +46,7 @@ def lib():
         "mlb_swiglu_fwd": [_vp, _vp, _i64, _i32, _vp],
         "mlb_swiglu_bwd": [_vp, _vp, _vp, _i64, _i32, _vp],
         "mlb_ce_fwd_bwd": [_vp, _vp, _vp, _i64, _i32, _i64, _f32, _i32, _vp],
-        "mlb_adamw": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp],
+        "mlb_adamw": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp],
         "mlb_cast_f2b": [_vp, _vp, _i64, _f32, _vp],
         "mlb_cast_b2f": [_vp, _vp, _i64, _f32, _vp],
         "mlb_scale_f32": [_vp, _i64, _f32, _vp],
@@ -234,10 +234,13 @@ def ce_fwd_bwd(losses, logits, tgt, dscale, V_valid=None, threads=512):
                               dscale, threads, _st()), "ce_fwd_bwd")
 
 
-def adamw(master, params, grads, m, v, lr, b1, b2, eps, wd, bc1, bc2, grad_scale=1.0):
+def adamw(master, params, grads, m, v, lr, b1, b2, eps, wd, bc1, bc2, grad_scale=1.0, dev_hyper=None):
+    """dev_hyper: optional CUDA fp32[4] = {lr, 1/bc1, 1/bc2, grad_scale} read by the kernel instead of the scalar
+    arguments (lets a captured graph follow the optimizer step count)."""
     n = master.numel()
     pp = None if (params is None or params.data_ptr() == master.data_ptr()) else _b(params)
-    _chk(lib().mlb_adamw(_f(master), pp, _f(grads), _f(m), _f(v), n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, _st()), "adamw")
+    hp = _f(dev_hyper) if dev_hyper is not None else None
+    _chk(lib().mlb_adamw(_f(master), pp, _f(grads), _f(m), _f(v), n, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, hp, _st()), "adamw")
 
 
 # ------------------------------------------------------------------ vision / utilities

@@ -192,9 +192,12 @@ def ce_fwd_bwd(losses, logits, tgt, dscale, V_valid=None):
 
 
 # ------------------------------------------------------------------ AdamW
-def adamw(master, params, grads, m, v, lr, b1, b2, eps, wd, bc1, bc2, grad_scale=1.0):
+def adamw(master, params, grads, m, v, lr, b1, b2, eps, wd, bc1, bc2, grad_scale=1.0, dev_hyper=None):
     """g*=grad_scale; m=b1 m+(1-b1)g; v=b2 v+(1-b2)g^2; p -= lr*(m/bc1/(sqrt(v/bc2)+eps) + wd*p).
     Weight decay applies to every parameter (train/gpt_kernels.cuh:1357-1380)."""
+    if dev_hyper is not None:
+        lr, bc1, bc2, grad_scale = (float(dev_hyper[0]), 1.0 / float(dev_hyper[1]), 1.0 / float(dev_hyper[2]),
+                                    float(dev_hyper[3]))
     g = grads * grad_scale
     m.mul_(b1).add_(g, alpha=1 - b1)
     v.mul_(b2).addcmul_(g, g, value=1 - b2)

@@ -1,0 +1,157 @@
+"""Trainer: the public training-step API (what `bench.py`, the CLI modes and user code call).
+
+One optimizer step = `accum` micro-batches of forward + backward (gradients accumulate in fp32), bucketed
+gradient reduction overlapped with the last backward, AdamW.  On CUDA the whole step can be captured once
+into a CUDA graph and replayed (`use_graph=True`): inputs live in static device buffers, the AdamW step
+counter is applied through bias corrections computed for step `t` at capture time unless `frozen_bc` is
+off, in which case the optimizer runs outside the graph.  `step_host` is the end-to-end call: it copies this
+step's tokens from pinned host memory, runs the step, and reads the mean loss back.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .config import Config, RunConfig, VisionConfig
+from .models import GPT, VisionTower
+from .parallel.ddp import DDP
+from . import ops
+
+
+class Trainer:
+    def __init__(self, cfg: Config, B: int, device="cuda", run: Optional[RunConfig] = None, lr=1e-4, wd=0.1,
+                 b1=0.9, b2=0.95, eps=1e-8, world=1, rank=0, group=None, seed=1234, use_graph=False,
+                 vision: Optional[VisionConfig] = None, n_text: Optional[int] = None):
+        self.cfg, self.B, self.run = cfg, B, run or RunConfig()
+        self.device = torch.device(device)
+        self.world, self.rank = world, rank
+        self.model = GPT(cfg, B, self.device)
+        self.model.init_weights(seed)
+        self.vision = None
+        if vision is not None:
+            self.vision = VisionTower(vision, cfg.C, B, self.device)
+            self.vision.init_weights(777)
+            self.n_pre = vision.n_patch
+            self.n_text = n_text if n_text is not None else cfg.T - vision.n_patch
+        else:
+            self.n_pre = 0
+        self.hyper = dict(lr=lr, b1=b1, b2=b2, eps=eps, wd=wd)
+        comm = self.run.comm if (self.device.type == "cuda" and world > 1) else "nccl"
+        self.ddp = DDP(self.model, world, self.run.accum, bool(self.run.bf16_reduce), comm, group,
+                       overlap_opt=bool(self.run.ddp_overlap_opt), opt_hyper=self.hyper)
+        self.accum = self.ddp.accum
+        self.t = 1
+        n = B * cfg.T
+        cuda = self.device.type == "cuda"
+        self.ids = torch.zeros(self.accum, n, dtype=torch.int32, device=self.device)
+        self.tgt = torch.zeros(self.accum, n, dtype=torch.int32, device=self.device)
+        self.h_ids = torch.zeros(self.accum, n, dtype=torch.int32, pin_memory=cuda)
+        self.h_tgt = torch.zeros(self.accum, n, dtype=torch.int32, pin_memory=cuda)
+        self.h_loss = torch.zeros(1, dtype=torch.float32, pin_memory=cuda)
+        self.d_loss = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.pixels = None
+        self.use_graph = bool(use_graph) and cuda
+        self.graph = None
+        # optimizer scalars of the current step, read by the AdamW kernels from device memory so that a captured
+        # graph follows the step count: {lr, 1/bc1, 1/bc2, grad_scale}
+        self.h_hyper = torch.zeros(4, dtype=torch.float32, pin_memory=cuda)
+        self.d_hyper = torch.zeros(4, dtype=torch.float32, device=self.device) if cuda else None
+        self.ddp.dev_hyper = self.d_hyper
+        self.h_hyper_v = torch.zeros(4, dtype=torch.float32, pin_memory=cuda)
+        self.d_hyper_v = torch.zeros(4, dtype=torch.float32, device=self.device) if cuda else None
+
+    # ------------------------------------------------------------------ one optimizer step (device-resident inputs)
+    def _micro(self, k):
+        m, v = self.model, self.vision
+        zero = self.ddp.set_microbatch(k)
+        if v is None:
+            m.forward(self.ids[k])
+            m.backward(self.ids[k], self.tgt[k], zero=zero)
+        else:
+            img = v.forward(v.patches) if self.pixels is None else v.forward_pixels(self.pixels)
+            m.forward(self.ids[k], prefix=img, n_pre=self.n_pre)
+            m.backward(self.ids[k], self.tgt[k], zero=zero, n_pre=self.n_pre, valid_tokens=self.B * self.n_text)
+            ops.gather_prefix_grad(v.dimg, m.dresid[:self.B * self.cfg.T], self.B, self.cfg.T, self.n_pre)
+            v.backward(zero=zero)
+
+    def _step_body(self):
+        for k in range(self.accum):
+            self._micro(k)
+        done = self.ddp.finish()
+        h = self.hyper
+        if not done:
+            self.ddp.t = self.t
+            self.ddp.step_optimizer()
+        if self.vision is not None:
+            self.vision.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, 1.0 / self.accum, self.d_hyper_v)
+        # mean loss of the last micro-batch, reduced on the device (one float to read back)
+        BT = self.B * self.cfg.T
+        valid = self.B * self.n_text if self.vision is not None else BT
+        torch.sum(self.model.losses[:BT], dim=0, keepdim=True, out=self.d_loss)
+        self.d_loss.mul_(1.0 / valid)
+
+    def step(self):
+        """Runs one optimizer step on the batch currently in self.ids / self.tgt."""
+        self.ddp.t = self.t
+        self._push_hyper()
+        if self.use_graph:
+            if self.graph is None:
+                self._capture()
+            self.graph.replay()
+        else:
+            self._step_body()
+        self.t += 1
+
+    @staticmethod
+    def _launch_count():
+        from .ops import native
+        return native.LAUNCHES
+
+    launches_per_step = 0   # kernels of this library recorded in the captured graph (graph mode)
+
+    def _push_hyper(self):
+        if self.d_hyper is None:
+            return
+        h = self.hyper
+        self.h_hyper[0] = h["lr"]
+        self.h_hyper[1] = 1.0 / (1.0 - h["b1"] ** self.t)
+        self.h_hyper[2] = 1.0 / (1.0 - h["b2"] ** self.t)
+        self.h_hyper[3] = self.ddp.adamw_grad_scale
+        self.d_hyper.copy_(self.h_hyper, non_blocking=True)
+        if self.vision is not None:
+            self.h_hyper_v.copy_(self.h_hyper)
+            self.h_hyper_v[3] = 1.0 / self.accum
+            self.d_hyper_v.copy_(self.h_hyper_v, non_blocking=True)
+
+    def _capture(self):
+        # warm the allocator / tensor-map caches outside capture, then record the step once
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._step_body()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        n0 = self._launch_count()
+        with torch.cuda.graph(self.graph):
+            self._step_body()
+        self.launches_per_step = self._launch_count() - n0
+
+    # ------------------------------------------------------------------ end-to-end step (host tokens in, loss out)
+    def step_host(self, ids_host: torch.Tensor, tgt_host: torch.Tensor) -> float:
+        """ids_host / tgt_host: int32 [accum, B*T] (or [B*T]) in host memory (pinned for async copies)."""
+        self.ids.copy_(ids_host.view(self.accum, -1), non_blocking=True)
+        self.tgt.copy_(tgt_host.view(self.accum, -1), non_blocking=True)
+        self.step()
+        self.h_loss.copy_(self.d_loss, non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        return float(self.h_loss[0])
+
+    def set_batch(self, ids: torch.Tensor, tgt: torch.Tensor):
+        self.ids.copy_(ids.view(self.accum, -1))
+        self.tgt.copy_(tgt.view(self.accum, -1))
+
+    def loss(self) -> float:
+        return float(self.d_loss.item())
