@@ -48,6 +48,11 @@ struct AttnArgs {
 };
 
 // ================================================================== forward
+// 512 threads: warp w reads TMEM lane group (w & 3) and column quarter (w >> 2), i.e. four threads share a query row,
+// each owning 32 of the 128 score columns and HD/4 of the output columns.  S for block j+1 is issued into the second
+// TMEM score buffer before the softmax of block j starts, so the tensor core works under the exponentials.
+constexpr int ATT_THREADS = 512;
+
 template <int HD>
 struct FwdSmem {
   static constexpr int CH = HD / 64;
@@ -56,31 +61,34 @@ struct FwdSmem {
   static constexpr int K1 = K0 + CH * TILE_BYTES;
   static constexpr int V = K1 + CH * TILE_BYTES;
   static constexpr int P = V + CH * TILE_BYTES;
-  static constexpr int BAR = P + 2 * TILE_BYTES;
+  static constexpr int RED = P + 2 * TILE_BYTES;   // 4 x 128 floats: per-quarter row maxima / row sums
+  static constexpr int BAR = RED + 2048;
   static constexpr int TOTAL = BAR + 128 + 1024;
 };
 
 template <int HD>
-__global__ void __launch_bounds__(128) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
+__global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
   using S = FwdSmem<HD>;
-  constexpr int CH = HD / 64;
-  constexpr uint32_t TMEM_COLS = 256;
+  constexpr int CH = HD / 64, OC = HD / 4;
+  constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + S::BAR);
-  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 4, *bar_o = bars + 5;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 6);
+  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 4, *bar_o = bars + 6;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 7);
+  float* s_red = (float*)(smem + S::RED);
 
   const int nq = (a.T + 127) / 128;
   const int qt = nq - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = qt * 128;
   const int C = a.H * HD;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int row0 = b * a.T;  // first row of this sample in the [B*T, 3C] matrix
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
+  const int row0 = b * a.T;
 
   if (tid == 0) {
-    tc::mbar_init(bar_q, 1); tc::mbar_init(&bar_k[0], 1); tc::mbar_init(&bar_k[1], 1);
-    tc::mbar_init(bar_v, 1); tc::mbar_init(bar_s, 1); tc::mbar_init(bar_o, 1);
+    tc::mbar_init(bar_q, 1); tc::mbar_init(&bar_k[0], 1); tc::mbar_init(&bar_k[1], 1); tc::mbar_init(bar_v, 1);
+    tc::mbar_init(&bar_s[0], 1); tc::mbar_init(&bar_s[1], 1); tc::mbar_init(bar_o, 1);
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tm);
   }
@@ -89,89 +97,93 @@ __global__ void __launch_bounds__(128) attn_fwd_tc_kernel(const __grid_constant_
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_s = tmem, t_o = tmem + 128;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-
+  const uint32_t t_o = tmem + 256;
+  const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
   const int nkb = qt + 1;
+  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);
+  const uint32_t sQ = tc::smem_u32(smem + S::Q), sV = tc::smem_u32(smem + S::V), sP = tc::smem_u32(smem + S::P);
+
+  auto load_k = [&](int j, int buf) {
+    tc::mbar_expect_tx(&bar_k[buf], CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++)
+      tc::tma_load_2d(smem + (buf ? S::K1 : S::K0) + c * TILE_BYTES, &tm, &bar_k[buf], C + h * HD + c * 64, row0 + j * 128);
+  };
+  auto load_v = [&](int j) {
+    tc::mbar_expect_tx(bar_v, CH * TILE_BYTES);
+    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm, bar_v, 2 * C + h * HD + c * 64, row0 + j * 128);
+  };
+  auto issue_s = [&](int j) {   // S(j) = Q K_j^T into score buffer j & 1
+    const uint32_t sK = tc::smem_u32(smem + ((j & 1) ? S::K1 : S::K0));
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(tmem + (j & 1) * 128, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
+  };
+
   if (tid == 0) {
     tc::mbar_expect_tx(bar_q, CH * TILE_BYTES);
     for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::Q + c * TILE_BYTES, &tm, bar_q, h * HD + c * 64, row0 + q0);
-    tc::mbar_expect_tx(&bar_k[0], CH * TILE_BYTES);
-    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::K0 + c * TILE_BYTES, &tm, &bar_k[0], C + h * HD + c * 64, row0);
-    tc::mbar_expect_tx(bar_v, CH * TILE_BYTES);
-    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm, bar_v, 2 * C + h * HD + c * 64, row0);
+    load_k(0, 0);
+    if (nkb > 1) load_k(1, 1);
+    load_v(0);
+    if (tc::mbar_wait(bar_q, 0, 10) && tc::mbar_wait(&bar_k[0], 0, 11)) {
+      tc::tc_fence_after();
+      issue_s(0);
+    }
+    tc::mma_commit(&bar_s[0]);
   }
 
-  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);
   const float sl2 = a.scale * LOG2E;
-  const uint32_t sQ = tc::smem_u32(smem + S::Q), sV = tc::smem_u32(smem + S::V), sP = tc::smem_u32(smem + S::P);
   float m = -INFINITY, l = 0.f;
-  float o[HD];
+  float o[OC];
 #pragma unroll
-  for (int i = 0; i < HD; i++) o[i] = 0.f;
-  const int qrow = q0 + tid;
+  for (int i = 0; i < OC; i++) o[i] = 0.f;
+  const int qrow = q0 + row;
   bool ok = true;
 
-  for (int j = 0; j < nkb && ok; j++) {
-    const int buf = j & 1, k0 = j * 128;
+  for (int j = 0; j < nkb; j++) {
+    const int k0 = j * 128;
+    if (!tc::mbar_wait(&bar_s[j & 1], (j >> 1) & 1, 12)) { ok = false; break; }
+    tc::tc_fence_after();
     if (tid == 0) {
       if (j + 1 < nkb) {
-        uint8_t* dst = smem + (buf ? S::K0 : S::K1);
-        tc::mbar_expect_tx(&bar_k[buf ^ 1], CH * TILE_BYTES);
-        for (int c = 0; c < CH; c++) tc::tma_load_2d(dst + c * TILE_BYTES, &tm, &bar_k[buf ^ 1], C + h * HD + c * 64, row0 + k0 + 128);
+        if (tc::mbar_wait(&bar_k[(j + 1) & 1], ((j + 1) >> 1) & 1, 13)) {
+          tc::tc_fence_after();
+          issue_s(j + 1);
+        }
+        tc::mma_commit(&bar_s[(j + 1) & 1]);
       }
-      if (j == 0) ok = tc::mbar_wait(bar_q, 0, 10);
-      ok = ok && tc::mbar_wait(&bar_k[buf], (j >> 1) & 1, 11);
-      if (ok) {
-        tc::tc_fence_after();
-        const uint32_t sK = tc::smem_u32(smem + (buf ? S::K1 : S::K0));
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_s, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
-      }
-      tc::mma_commit(bar_s);  // always commit so the other threads' wait is released by the hardware, not by a timeout
+      if (j + 2 < nkb) load_k(j + 2, j & 1);   // S(j) has completed: its K buffer is free
     }
-    if (!tc::mbar_wait(bar_s, j & 1, 12)) { ok = false; break; }
-    tc::tc_fence_after();
-    // ---- pass 1: row maximum (log2 domain)
+    uint32_t r[32];
+    tc::tmem_ld32(tmem + (j & 1) * 128 + lane_addr + cq * 32, r);
+    tc::tmem_ld_wait();
     const bool diag = (j == qt);
+    const int kc0 = k0 + cq * 32;
     float mx = -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < 4; c++) {
-      uint32_t r[32];
-      tc::tmem_ld32(t_s + lane_addr + c * 32, r);
-      tc::tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
-        const int kcol = k0 + c * 32 + i;
-        const float v = __uint_as_float(r[i]);
-        if (!diag || kcol <= qrow) mx = fmaxf(mx, v);
-      }
+    for (int i = 0; i < 32; i++) {
+      const float v = __uint_as_float(r[i]);
+      if (!diag || kc0 + i <= qrow) mx = fmaxf(mx, v);
     }
+    s_red[cq * 128 + row] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(s_red[row], s_red[128 + row]), fmaxf(s_red[256 + row], s_red[384 + row]));
     const float m_new = fmaxf(m, mx * sl2);
     const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-    // ---- pass 2: P = exp2(s - m), row sum, bf16 P into swizzled shared memory
     float rs = 0.f;
-#pragma unroll 1
-    for (int c = 0; c < 4; c++) {
-      uint32_t r[32];
-      tc::tmem_ld32(t_s + lane_addr + c * 32, r);
-      tc::tmem_ld_wait();
-      float p[32];
+    float pf[32];
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
-        const int kcol = k0 + c * 32 + i;
-        const float v = exp2f(__uint_as_float(r[i]) * sl2 - m_new);
-        p[i] = (!diag || kcol <= qrow) ? v : 0.f;
-        rs += p[i];
-      }
+    for (int i = 0; i < 32; i++) {
+      const float v = exp2f(__uint_as_float(r[i]) * sl2 - m_new);
+      pf[i] = (!diag || kc0 + i <= qrow) ? v : 0.f;
+      rs += pf[i];
+    }
 #pragma unroll
-      for (int v8 = 0; v8 < 4; v8++) {
-        uint4 pk;
-        pk.x = pack_bf16(p[v8 * 8 + 0], p[v8 * 8 + 1]); pk.y = pack_bf16(p[v8 * 8 + 2], p[v8 * 8 + 3]);
-        pk.z = pack_bf16(p[v8 * 8 + 4], p[v8 * 8 + 5]); pk.w = pack_bf16(p[v8 * 8 + 6], p[v8 * 8 + 7]);
-        *reinterpret_cast<uint4*>(smem + S::P + sw_off(tid, c * 32 + v8 * 8)) = pk;
-      }
+    for (int v8 = 0; v8 < 4; v8++) {
+      uint4 pk;
+      pk.x = pack_bf16(pf[v8 * 8 + 0], pf[v8 * 8 + 1]); pk.y = pack_bf16(pf[v8 * 8 + 2], pf[v8 * 8 + 3]);
+      pk.z = pack_bf16(pf[v8 * 8 + 4], pf[v8 * 8 + 5]); pk.w = pack_bf16(pf[v8 * 8 + 6], pf[v8 * 8 + 7]);
+      *reinterpret_cast<uint4*>(smem + S::P + sw_off(row, cq * 32 + v8 * 8)) = pk;
     }
     l = l * alpha + rs;
     m = m_new;
@@ -180,42 +192,47 @@ __global__ void __launch_bounds__(128) attn_fwd_tc_kernel(const __grid_constant_
     __syncthreads();
     if (tid == 0) {
       tc::tc_fence_after();
-      bool okv = tc::mbar_wait(bar_v, j & 1, 13);
-      if (okv) {
+      if (tc::mbar_wait(bar_v, j & 1, 14)) {
         tc::tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_o, desc_k(sP, ks), desc_mn(sV, ks), idesc_o, ks > 0);
       }
       tc::mma_commit(bar_o);
     }
-    if (!tc::mbar_wait(bar_o, j & 1, 14)) { ok = false; break; }
+    if (!tc::mbar_wait(bar_o, j & 1, 15)) { ok = false; break; }
     tc::tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < HD / 32; c++) {
-      uint32_t r[32];
-      tc::tmem_ld32(t_o + lane_addr + c * 32, r);
+    if (tid == 0 && j + 1 < nkb) load_v(j + 1);   // P V_j has completed: the V buffer is free
+    if (OC == 16) {
+      uint32_t ro[16];
+      tc::tmem_ld16(t_o + lane_addr + cq * 16, ro);
       tc::tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; i++) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
+      for (int i = 0; i < 16; i++) o[i] = o[i] * alpha + __uint_as_float(ro[i]);
+    } else {
+      uint32_t ro[32];
+      tc::tmem_ld32(t_o + lane_addr + cq * 32, ro);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i++) o[i % OC] = o[i % OC] * alpha + __uint_as_float(ro[i]);
     }
     tc::tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && j + 1 < nkb) {
-      tc::mbar_expect_tx(bar_v, CH * TILE_BYTES);
-      for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm, bar_v, 2 * C + h * HD + c * 64, row0 + k0 + 128);
-    }
   }
+  // combine the four partial row sums, normalise, store
+  __syncthreads();
+  s_red[cq * 128 + row] = l;
+  __syncthreads();
+  const float L = s_red[row] + s_red[128 + row] + s_red[256 + row] + s_red[384 + row];
   if (ok && qrow < a.T) {
-    const float inv = 1.f / l;
-    bf16* dst = a.out + ((size_t)(row0 + qrow)) * C + h * HD;
+    const float inv = 1.f / L;
+    bf16* dst = a.out + ((size_t)(row0 + qrow)) * C + h * HD + cq * OC;
 #pragma unroll
-    for (int v8 = 0; v8 < HD / 8; v8++) {
+    for (int v8 = 0; v8 < OC / 8; v8++) {
       uint4 pk;
       pk.x = pack_bf16(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv); pk.y = pack_bf16(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
       pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
       *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
     }
-    a.lse[((size_t)b * a.H + h) * a.T + qrow] = (m + log2f(l)) * LN2;
+    if (cq == 0) a.lse[((size_t)b * a.H + h) * a.T + qrow] = (m + log2f(L)) * LN2;
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -266,30 +283,45 @@ __global__ void attn_delta_scalar_k(float* __restrict__ delta, const bf16* __res
   if (lane == 0) delta[((long)b * H + h) * T + t] = s;
 }
 
-// Writes one thread's fp32 row (HD values) as bf16 to dst, optionally applying RoPE's backward rotation
-// (d0' = d0 c + d1 s, d1' = d1 c - d0 s on pairs (i, i + HD/2)).
+// Epilogue helper for the backward kernels: one warp moves 64 accumulator columns of its 32 rows from TMEM to
+// dst as bf16: columns [c0, c0+32) and [c0 + HD/2, c0 + HD/2 + 32), which are exactly RoPE's rotation pairs
+// (i, i + HD/2).  With tables given, RoPE's backward rotation (d0' = d0 c + d1 s, d1' = d1 c - d0 s) is applied.
 template <int HD>
-__device__ __forceinline__ void store_row_rope(bf16* dst, float (&v)[HD], const float* cosT, const float* sinT, int t) {
-  if (cosT) {
-    const float* c = cosT + (size_t)t * (HD / 2);
-    const float* s = sinT + (size_t)t * (HD / 2);
+__device__ __forceinline__ void store_pairs_rope(bf16* dst_row, uint32_t taddr, int c0, bool live, const float* cosT,
+                                                 const float* sinT, int t) {
+  uint32_t ra[32], rb[32];
+  tc::tmem_ld32(taddr + c0, ra);
+  tc::tmem_ld32(taddr + c0 + HD / 2, rb);
+  tc::tmem_ld_wait();
+  if (!live) return;
+  float x0[32], x1[32];
 #pragma unroll
-    for (int i = 0; i < HD / 2; i++) {
-      const float d0 = v[i], d1 = v[i + HD / 2], cc = c[i], ss = s[i];
-      v[i] = d0 * cc + d1 * ss;
-      v[i + HD / 2] = d1 * cc - d0 * ss;
+  for (int i = 0; i < 32; i++) { x0[i] = __uint_as_float(ra[i]); x1[i] = __uint_as_float(rb[i]); }
+  if (cosT) {
+    const float* c = cosT + (size_t)t * (HD / 2) + c0;
+    const float* s = sinT + (size_t)t * (HD / 2) + c0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+      const float d0 = x0[i], d1 = x1[i], cc = c[i], ss = s[i];
+      x0[i] = d0 * cc + d1 * ss;
+      x1[i] = d1 * cc - d0 * ss;
     }
   }
 #pragma unroll
-  for (int v8 = 0; v8 < HD / 8; v8++) {
-    uint4 pk;
-    pk.x = pack_bf16(v[v8 * 8 + 0], v[v8 * 8 + 1]); pk.y = pack_bf16(v[v8 * 8 + 2], v[v8 * 8 + 3]);
-    pk.z = pack_bf16(v[v8 * 8 + 4], v[v8 * 8 + 5]); pk.w = pack_bf16(v[v8 * 8 + 6], v[v8 * 8 + 7]);
-    *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
+  for (int v8 = 0; v8 < 4; v8++) {
+    uint4 pa, pb;
+    pa.x = pack_bf16(x0[v8 * 8 + 0], x0[v8 * 8 + 1]); pa.y = pack_bf16(x0[v8 * 8 + 2], x0[v8 * 8 + 3]);
+    pa.z = pack_bf16(x0[v8 * 8 + 4], x0[v8 * 8 + 5]); pa.w = pack_bf16(x0[v8 * 8 + 6], x0[v8 * 8 + 7]);
+    pb.x = pack_bf16(x1[v8 * 8 + 0], x1[v8 * 8 + 1]); pb.y = pack_bf16(x1[v8 * 8 + 2], x1[v8 * 8 + 3]);
+    pb.z = pack_bf16(x1[v8 * 8 + 4], x1[v8 * 8 + 5]); pb.w = pack_bf16(x1[v8 * 8 + 6], x1[v8 * 8 + 7]);
+    *reinterpret_cast<uint4*>(dst_row + c0 + v8 * 8) = pa;
+    *reinterpret_cast<uint4*>(dst_row + c0 + HD / 2 + v8 * 8) = pb;
   }
 }
 
 // ================================================================== backward: dK, dV (one CTA per 128-key tile)
+// 512 threads; thread (row = key, quarter cq) handles 32 of the 128 query columns of S^T / dP^T.  The MMAs of the next
+// query block are queued right behind the dV/dK MMAs of the current one, so one commit covers both.
 template <int HD>
 struct BwdKVSmem {
   static constexpr int CH = HD / 64;
@@ -306,8 +338,9 @@ struct BwdKVSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(128) attn_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
-                                                             const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
+__global__ void __launch_bounds__(ATT_THREADS, 1) attn_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+                                                                        const __grid_constant__ CUtensorMap tm_do,
+                                                                        const AttnArgs a) {
   using S = BwdKVSmem<HD>;
   constexpr int CH = HD / 64, NBUF = S::NBUF;
   constexpr uint32_t TMEM_COLS = 512;
@@ -323,7 +356,8 @@ __global__ void __launch_bounds__(128) attn_bwd_kv_tc_kernel(const __grid_consta
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int k0 = kt * 128;
   const int C = a.H * HD;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
   const int row0 = b * a.T;
 
   if (tid == 0) {
@@ -339,7 +373,11 @@ __global__ void __launch_bounds__(128) attn_bwd_kv_tc_kernel(const __grid_consta
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t t_st = tmem, t_dpt = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 256 + HD;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);
+  const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V);
+  const uint32_t sPT = tc::smem_u32(smem + S::PT), sDST = tc::smem_u32(smem + S::DST);
 
   auto load_q_do = [&](int i, int buf) {
     tc::mbar_expect_tx(&bar_q[buf], 2 * CH * TILE_BYTES);
@@ -348,6 +386,14 @@ __global__ void __launch_bounds__(128) attn_bwd_kv_tc_kernel(const __grid_consta
       tc::tma_load_2d(smem + S::DO + (buf * CH + c) * TILE_BYTES, &tm_do, &bar_q[buf], h * HD + c * 64, row0 + i * 128);
     }
   };
+  auto issue_scores = [&](int buf) {   // S^T = K Q^T and dP^T = V dO^T for the block in `buf`
+    const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * CH * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * CH * TILE_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
+  };
+  const int n_it = nq - kt;
   if (tid == 0) {
     tc::mbar_expect_tx(bar_kv, 2 * CH * TILE_BYTES);
     for (int c = 0; c < CH; c++) {
@@ -355,66 +401,50 @@ __global__ void __launch_bounds__(128) attn_bwd_kv_tc_kernel(const __grid_consta
       tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm_qkv, bar_kv, 2 * C + h * HD + c * 64, row0 + k0);
     }
     load_q_do(kt, 0);
-  }
-  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);
-  const float sl2 = a.scale * LOG2E;
-  const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V);
-  const uint32_t sPT = tc::smem_u32(smem + S::PT), sDST = tc::smem_u32(smem + S::DST);
-  const int krow = k0 + tid;
-  bool ok = true;
-  int it = 0;
-  for (int i = kt; i < nq && ok; i++, it++) {
-    const int buf = (NBUF == 2) ? (it & 1) : 0;
-    const int qphase = (NBUF == 2) ? ((it >> 1) & 1) : (it & 1);
-    const int q0 = i * 128;
-    if (tid == 0) {
-      if (NBUF == 2 && i + 1 < nq) load_q_do(i + 1, buf ^ 1);
-      if (it == 0) ok = tc::mbar_wait(bar_kv, 0, 20);
-      ok = ok && tc::mbar_wait(&bar_q[buf], qphase, 21);
-      if (ok) {
-        tc::tc_fence_after();
-        const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * CH * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * CH * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
-      }
-      tc::mma_commit(bar_s);
+    if (tc::mbar_wait(bar_kv, 0, 20) && tc::mbar_wait(&bar_q[0], 0, 21)) {
+      tc::tc_fence_after();
+      issue_scores(0);
     }
-    {  // per-query statistics of this block (queries past the sequence end contribute nothing)
-      const int q = q0 + tid;
+    tc::mma_commit(bar_s);
+  }
+  const float sl2 = a.scale * LOG2E;
+  const int krow = k0 + row;
+  bool ok = true;
+  for (int it = 0; it < n_it; it++) {
+    const int i = kt + it, q0 = i * 128;
+    const int buf = (NBUF == 2) ? (it & 1) : 0;
+    if (tid < 256) {   // per-query statistics of this block (queries past the sequence end contribute nothing)
+      const int q = q0 + (tid & 127);
       const size_t si = ((size_t)b * a.H + h) * a.T + q;
-      s_lse[tid] = (q < a.T) ? a.lse[si] * LOG2E : INFINITY;
-      s_delta[tid] = (q < a.T) ? a.delta[si] : 0.f;
+      if (tid < 128) s_lse[tid] = (q < a.T) ? a.lse[si] * LOG2E : INFINITY;
+      else s_delta[tid - 128] = (q < a.T) ? a.delta[si] : 0.f;
     }
     __syncthreads();
     if (!tc::mbar_wait(bar_s, it & 1, 22)) { ok = false; break; }
     tc::tc_fence_after();
-    const bool diag = (i == kt);
-#pragma unroll 1
-    for (int c = 0; c < 4; c++) {
+    // every MMA issued so far has completed: the other Q/dO buffer (read by the previous dV/dK) can be refilled
+    if (NBUF == 2 && tid == 0 && it + 1 < n_it) load_q_do(i + 1, buf ^ 1);
+    const bool diag = (it == 0);
+    {
       uint32_t rs[32], rd[32];
-      tc::tmem_ld32(t_st + lane_addr + c * 32, rs);
-      tc::tmem_ld32(t_dpt + lane_addr + c * 32, rd);
+      tc::tmem_ld32(t_st + lane_addr + cq * 32, rs);
+      tc::tmem_ld32(t_dpt + lane_addr + cq * 32, rd);
       tc::tmem_ld_wait();
-      float p[32], ds[32];
-#pragma unroll
-      for (int x = 0; x < 32; x++) {
-        const int qc = c * 32 + x;
-        float pv = exp2f(__uint_as_float(rs[x]) * sl2 - s_lse[qc]);
-        if (diag && (q0 + qc) < krow) pv = 0.f;
-        p[x] = pv;
-        ds[x] = pv * (__uint_as_float(rd[x]) - s_delta[qc]) * a.scale;
-      }
 #pragma unroll
       for (int v8 = 0; v8 < 4; v8++) {
+        float p[8], ds[8];
+#pragma unroll
+        for (int x = 0; x < 8; x++) {
+          const int qc = cq * 32 + v8 * 8 + x;
+          float pv = exp2f(__uint_as_float(rs[v8 * 8 + x]) * sl2 - s_lse[qc]);
+          if (diag && (q0 + qc) < krow) pv = 0.f;
+          p[x] = pv;
+          ds[x] = pv * (__uint_as_float(rd[v8 * 8 + x]) - s_delta[qc]) * a.scale;
+        }
         uint4 pk, dk;
-        pk.x = pack_bf16(p[v8 * 8 + 0], p[v8 * 8 + 1]); pk.y = pack_bf16(p[v8 * 8 + 2], p[v8 * 8 + 3]);
-        pk.z = pack_bf16(p[v8 * 8 + 4], p[v8 * 8 + 5]); pk.w = pack_bf16(p[v8 * 8 + 6], p[v8 * 8 + 7]);
-        dk.x = pack_bf16(ds[v8 * 8 + 0], ds[v8 * 8 + 1]); dk.y = pack_bf16(ds[v8 * 8 + 2], ds[v8 * 8 + 3]);
-        dk.z = pack_bf16(ds[v8 * 8 + 4], ds[v8 * 8 + 5]); dk.w = pack_bf16(ds[v8 * 8 + 6], ds[v8 * 8 + 7]);
-        const uint32_t off = sw_off(tid, c * 32 + v8 * 8);
+        pk.x = pack_bf16(p[0], p[1]); pk.y = pack_bf16(p[2], p[3]); pk.z = pack_bf16(p[4], p[5]); pk.w = pack_bf16(p[6], p[7]);
+        dk.x = pack_bf16(ds[0], ds[1]); dk.y = pack_bf16(ds[2], ds[3]); dk.z = pack_bf16(ds[4], ds[5]); dk.w = pack_bf16(ds[6], ds[7]);
+        const uint32_t off = sw_off(row, cq * 32 + v8 * 8);
         *reinterpret_cast<uint4*>(smem + S::PT + off) = pk;
         *reinterpret_cast<uint4*>(smem + S::DST + off) = dk;
       }
@@ -429,35 +459,35 @@ __global__ void __launch_bounds__(128) attn_bwd_kv_tc_kernel(const __grid_consta
       for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dv, desc_k(sPT, ks), desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
 #pragma unroll
       for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, desc_k(sDST, ks), desc_mn(sQ, ks), idesc_d, (it > 0 || ks > 0));
-      tc::mma_commit(bar_d);
+      if (it + 1 < n_it) {
+        bool ready = true;
+        if (NBUF == 1) {   // single buffer: dV/dK must finish reading Q/dO before the next block is loaded over them
+          tc::mma_commit(bar_d);
+          ready = tc::mbar_wait(bar_d, it & 1, 23);
+          if (ready) load_q_do(i + 1, 0);
+        }
+        const int nb = (NBUF == 2) ? (buf ^ 1) : 0;
+        const int nphase = (NBUF == 2) ? (((it + 1) >> 1) & 1) : ((it + 1) & 1);
+        if (ready && tc::mbar_wait(&bar_q[nb], nphase, 24)) {
+          tc::tc_fence_after();
+          issue_scores(nb);
+        }
+      }
+      tc::mma_commit(bar_s);
     }
-    if (!tc::mbar_wait(bar_d, it & 1, 23)) { ok = false; break; }
-    tc::tc_fence_after();
-    if (NBUF == 1 && tid == 0 && i + 1 < nq) load_q_do(i + 1, 0);
-    __syncthreads();  // s_lse / s_delta are rewritten at the top of the next iteration
   }
+  if (ok) ok = tc::mbar_wait(bar_s, n_it & 1, 25);   // dV / dK of the last block are complete
+  tc::tc_fence_after();
   if (ok) {
-    // The TMEM loads are warp-collective: every thread takes part, only rows inside the sequence are stored.
-    float v[HD];
-    bf16* base = a.out + ((size_t)(row0 + krow)) * 3 * C + h * HD;
-#pragma unroll
-    for (int c = 0; c < HD / 32; c++) {
-      uint32_t r[32];
-      tc::tmem_ld32(t_dk + lane_addr + c * 32, r);
-      tc::tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < 32; x++) v[c * 32 + x] = __uint_as_float(r[x]);
+    // jobs: HD/64 column-pair slabs for dK (with RoPE) then HD/64 for dV; one job per quarter-group of warps
+    constexpr int JOBS = HD / 64;
+    if (cq < 2 * JOBS) {
+      const bool is_k = cq < JOBS;
+      const int pass = is_k ? cq : cq - JOBS;
+      bf16* dst = a.out + ((size_t)(row0 + krow)) * 3 * C + (is_k ? C : 2 * C) + h * HD;
+      store_pairs_rope<HD>(dst, (is_k ? t_dk : t_dv) + lane_addr, pass * 32, krow < a.T, is_k ? a.cosT : nullptr,
+                           is_k ? a.sinT : nullptr, krow);
     }
-    if (krow < a.T) store_row_rope<HD>(base + C, v, a.cosT, a.sinT, krow);
-#pragma unroll
-    for (int c = 0; c < HD / 32; c++) {
-      uint32_t r[32];
-      tc::tmem_ld32(t_dv + lane_addr + c * 32, r);
-      tc::tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < 32; x++) v[c * 32 + x] = __uint_as_float(r[x]);
-    }
-    if (krow < a.T) store_row_rope<HD>(base + 2 * C, v, nullptr, nullptr, krow);
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -479,8 +509,9 @@ struct BwdQSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(128) attn_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
-                                                            const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
+__global__ void __launch_bounds__(ATT_THREADS, 1) attn_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+                                                                       const __grid_constant__ CUtensorMap tm_do,
+                                                                       const AttnArgs a) {
   using S = BwdQSmem<HD>;
   constexpr int CH = HD / 64, NBUF = S::NBUF;
   constexpr uint32_t TMEM_COLS = 512;
@@ -494,7 +525,8 @@ __global__ void __launch_bounds__(128) attn_bwd_q_tc_kernel(const __grid_constan
   const int qt = nq - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = qt * 128;
   const int C = a.H * HD;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
   const int row0 = b * a.T;
 
   if (tid == 0) {
@@ -510,7 +542,10 @@ __global__ void __launch_bounds__(128) attn_bwd_q_tc_kernel(const __grid_constan
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t t_s = tmem, t_dp = tmem + 128, t_dq = tmem + 256;
-  const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);
+  const uint32_t sQ = tc::smem_u32(smem + S::Q), sDO = tc::smem_u32(smem + S::DO), sDS = tc::smem_u32(smem + S::DS);
 
   auto load_kv = [&](int j, int buf) {
     tc::mbar_expect_tx(&bar_kv[buf], 2 * CH * TILE_BYTES);
@@ -519,6 +554,14 @@ __global__ void __launch_bounds__(128) attn_bwd_q_tc_kernel(const __grid_constan
       tc::tma_load_2d(smem + S::V + (buf * CH + c) * TILE_BYTES, &tm_qkv, &bar_kv[buf], 2 * C + h * HD + c * 64, row0 + j * 128);
     }
   };
+  auto issue_scores = [&](int buf) {   // S = Q K^T and dP = dO V^T for the key block in `buf`
+    const uint32_t sK = tc::smem_u32(smem + S::K + buf * CH * TILE_BYTES), sV = tc::smem_u32(smem + S::V + buf * CH * TILE_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_s, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dp, desc_k(sDO, ks), desc_k(sV, ks), idesc_s, ks > 0);
+  };
+  const int nkb = qt + 1;
   if (tid == 0) {
     tc::mbar_expect_tx(bar_q, 2 * CH * TILE_BYTES);
     for (int c = 0; c < CH; c++) {
@@ -526,58 +569,43 @@ __global__ void __launch_bounds__(128) attn_bwd_q_tc_kernel(const __grid_constan
       tc::tma_load_2d(smem + S::DO + c * TILE_BYTES, &tm_do, bar_q, h * HD + c * 64, row0 + q0);
     }
     load_kv(0, 0);
+    if (tc::mbar_wait(bar_q, 0, 30) && tc::mbar_wait(&bar_kv[0], 0, 31)) {
+      tc::tc_fence_after();
+      issue_scores(0);
+    }
+    tc::mma_commit(bar_s);
   }
-  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);
   const float sl2 = a.scale * LOG2E;
-  const uint32_t sQ = tc::smem_u32(smem + S::Q), sDO = tc::smem_u32(smem + S::DO), sDS = tc::smem_u32(smem + S::DS);
-  const int qrow = q0 + tid;
+  const int qrow = q0 + row;
   const size_t si = ((size_t)b * a.H + h) * a.T + qrow;
   const float lse2 = (qrow < a.T) ? a.lse[si] * LOG2E : INFINITY;
   const float delta = (qrow < a.T) ? a.delta[si] : 0.f;
-  const int nkb = qt + 1;
   bool ok = true;
-  for (int j = 0; j < nkb && ok; j++) {
+  for (int j = 0; j < nkb; j++) {
     const int buf = (NBUF == 2) ? (j & 1) : 0;
-    const int kphase = (NBUF == 2) ? ((j >> 1) & 1) : (j & 1);
     const int k0 = j * 128;
-    const uint32_t sK = tc::smem_u32(smem + S::K + buf * CH * TILE_BYTES), sV = tc::smem_u32(smem + S::V + buf * CH * TILE_BYTES);
-    if (tid == 0) {
-      if (NBUF == 2 && j + 1 < nkb) load_kv(j + 1, buf ^ 1);
-      if (j == 0) ok = tc::mbar_wait(bar_q, 0, 30);
-      ok = ok && tc::mbar_wait(&bar_kv[buf], kphase, 31);
-      if (ok) {
-        tc::tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_s, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dp, desc_k(sDO, ks), desc_k(sV, ks), idesc_s, ks > 0);
-      }
-      tc::mma_commit(bar_s);
-    }
     if (!tc::mbar_wait(bar_s, j & 1, 32)) { ok = false; break; }
     tc::tc_fence_after();
+    if (NBUF == 2 && tid == 0 && j + 1 < nkb) load_kv(j + 1, buf ^ 1);
     const bool diag = (j == qt);
-#pragma unroll 1
-    for (int c = 0; c < 4; c++) {
+    {
       uint32_t rs[32], rd[32];
-      tc::tmem_ld32(t_s + lane_addr + c * 32, rs);
-      tc::tmem_ld32(t_dp + lane_addr + c * 32, rd);
+      tc::tmem_ld32(t_s + lane_addr + cq * 32, rs);
+      tc::tmem_ld32(t_dp + lane_addr + cq * 32, rd);
       tc::tmem_ld_wait();
-      float ds[32];
-#pragma unroll
-      for (int x = 0; x < 32; x++) {
-        const int kcol = k0 + c * 32 + x;
-        float pv = exp2f(__uint_as_float(rs[x]) * sl2 - lse2);
-        if (diag && kcol > qrow) pv = 0.f;
-        ds[x] = pv * (__uint_as_float(rd[x]) - delta) * a.scale;
-      }
 #pragma unroll
       for (int v8 = 0; v8 < 4; v8++) {
+        float ds[8];
+#pragma unroll
+        for (int x = 0; x < 8; x++) {
+          const int kcol = k0 + cq * 32 + v8 * 8 + x;
+          float pv = exp2f(__uint_as_float(rs[v8 * 8 + x]) * sl2 - lse2);
+          if (diag && kcol > qrow) pv = 0.f;
+          ds[x] = pv * (__uint_as_float(rd[v8 * 8 + x]) - delta) * a.scale;
+        }
         uint4 dk;
-        dk.x = pack_bf16(ds[v8 * 8 + 0], ds[v8 * 8 + 1]); dk.y = pack_bf16(ds[v8 * 8 + 2], ds[v8 * 8 + 3]);
-        dk.z = pack_bf16(ds[v8 * 8 + 4], ds[v8 * 8 + 5]); dk.w = pack_bf16(ds[v8 * 8 + 6], ds[v8 * 8 + 7]);
-        *reinterpret_cast<uint4*>(smem + S::DS + sw_off(tid, c * 32 + v8 * 8)) = dk;
+        dk.x = pack_bf16(ds[0], ds[1]); dk.y = pack_bf16(ds[2], ds[3]); dk.z = pack_bf16(ds[4], ds[5]); dk.w = pack_bf16(ds[6], ds[7]);
+        *reinterpret_cast<uint4*>(smem + S::DS + sw_off(row, cq * 32 + v8 * 8)) = dk;
       }
     }
     tc::fence_async_smem();
@@ -585,25 +613,31 @@ __global__ void __launch_bounds__(128) attn_bwd_q_tc_kernel(const __grid_constan
     __syncthreads();
     if (tid == 0) {
       tc::tc_fence_after();
+      const uint32_t sK = tc::smem_u32(smem + S::K + buf * CH * TILE_BYTES);
 #pragma unroll
       for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, desc_k(sDS, ks), desc_mn(sK, ks), idesc_d, (j > 0 || ks > 0));
-      tc::mma_commit(bar_d);
+      if (j + 1 < nkb) {
+        bool ready = true;
+        if (NBUF == 1) {
+          tc::mma_commit(bar_d);
+          ready = tc::mbar_wait(bar_d, j & 1, 33);
+          if (ready) load_kv(j + 1, 0);
+        }
+        const int nb = (NBUF == 2) ? (buf ^ 1) : 0;
+        const int nphase = (NBUF == 2) ? (((j + 1) >> 1) & 1) : ((j + 1) & 1);
+        if (ready && tc::mbar_wait(&bar_kv[nb], nphase, 34)) {
+          tc::tc_fence_after();
+          issue_scores(nb);
+        }
+      }
+      tc::mma_commit(bar_s);
     }
-    if (!tc::mbar_wait(bar_d, j & 1, 33)) { ok = false; break; }
-    tc::tc_fence_after();
-    if (NBUF == 1 && tid == 0 && j + 1 < nkb) load_kv(j + 1, 0);
   }
-  if (ok) {
-    float v[HD];
-#pragma unroll
-    for (int c = 0; c < HD / 32; c++) {
-      uint32_t r[32];
-      tc::tmem_ld32(t_dq + lane_addr + c * 32, r);
-      tc::tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < 32; x++) v[c * 32 + x] = __uint_as_float(r[x]);
-    }
-    if (qrow < a.T) store_row_rope<HD>(a.out + ((size_t)(row0 + qrow)) * 3 * C + h * HD, v, a.cosT, a.sinT, qrow);
+  if (ok) ok = tc::mbar_wait(bar_s, nkb & 1, 35);
+  tc::tc_fence_after();
+  if (ok && cq < HD / 64) {
+    bf16* dst = a.out + ((size_t)(row0 + qrow)) * 3 * C + h * HD;
+    store_pairs_rope<HD>(dst, t_dq + lane_addr, cq * 32, qrow < a.T, a.cosT, a.sinT, qrow);
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -728,11 +762,11 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
     if (hd == 64) {
       static int once = set_smem(attn_fwd_tc_kernel<64>, FwdSmem<64>::TOTAL);
       (void)once;
-      attn_fwd_tc_kernel<64><<<grid, 128, FwdSmem<64>::TOTAL, st>>>(*tm, a);
+      attn_fwd_tc_kernel<64><<<grid, ATT_THREADS, FwdSmem<64>::TOTAL, st>>>(*tm, a);
     } else {
       static int once = set_smem(attn_fwd_tc_kernel<128>, FwdSmem<128>::TOTAL);
       (void)once;
-      attn_fwd_tc_kernel<128><<<grid, 128, FwdSmem<128>::TOTAL, st>>>(*tm, a);
+      attn_fwd_tc_kernel<128><<<grid, ATT_THREADS, FwdSmem<128>::TOTAL, st>>>(*tm, a);
     }
     return (int)cudaGetLastError();
   }
@@ -765,14 +799,14 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
       static int o1 = set_smem(attn_bwd_kv_tc_kernel<64>, BwdKVSmem<64>::TOTAL);
       static int o2 = set_smem(attn_bwd_q_tc_kernel<64>, BwdQSmem<64>::TOTAL);
       (void)o1; (void)o2;
-      attn_bwd_kv_tc_kernel<64><<<grid, 128, BwdKVSmem<64>::TOTAL, st>>>(*tq, *td, a);
-      attn_bwd_q_tc_kernel<64><<<grid, 128, BwdQSmem<64>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_kv_tc_kernel<64><<<grid, ATT_THREADS, BwdKVSmem<64>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_q_tc_kernel<64><<<grid, ATT_THREADS, BwdQSmem<64>::TOTAL, st>>>(*tq, *td, a);
     } else {
       static int o1 = set_smem(attn_bwd_kv_tc_kernel<128>, BwdKVSmem<128>::TOTAL);
       static int o2 = set_smem(attn_bwd_q_tc_kernel<128>, BwdQSmem<128>::TOTAL);
       (void)o1; (void)o2;
-      attn_bwd_kv_tc_kernel<128><<<grid, 128, BwdKVSmem<128>::TOTAL, st>>>(*tq, *td, a);
-      attn_bwd_q_tc_kernel<128><<<grid, 128, BwdQSmem<128>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_kv_tc_kernel<128><<<grid, ATT_THREADS, BwdKVSmem<128>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_q_tc_kernel<128><<<grid, ATT_THREADS, BwdQSmem<128>::TOTAL, st>>>(*tq, *td, a);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e + 1000;

@@ -239,33 +239,20 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, floa
         }
       }
       __syncthreads();
-      float* red = sh;  // reuse: nwarp x 128 floats (C >= 128 floats is not guaranteed, so clamp below)
-      if (C >= nwarp * 128) {
-        red[warp * 128 + lane * 4 + 0] = acc4.x; red[warp * 128 + lane * 4 + 1] = acc4.y;
-        red[warp * 128 + lane * 4 + 2] = acc4.z; red[warp * 128 + lane * 4 + 3] = acc4.w;
-        __syncthreads();
-        if (warp == 0) {
-          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int w2 = 0; w2 < nwarp; w2++) {
-            t.x += red[w2 * 128 + lane * 4 + 0]; t.y += red[w2 * 128 + lane * 4 + 1];
-            t.z += red[w2 * 128 + lane * 4 + 2]; t.w += red[w2 * 128 + lane * 4 + 3];
-          }
-          if (c < C) dw[c] += t.x;
-          if (c + 1 < C) dw[c + 1] += t.y;
-          if (c + 2 < C) dw[c + 2] += t.z;
-          if (c + 3 < C) dw[c + 3] += t.w;
-        }
-      } else {
-        // narrow rows: serialise the warps instead of staging through shared memory
+      float* red = sh;  // the dynamic shared buffer holds at least nwarp x 128 floats (see the launcher)
+      red[warp * 128 + lane * 4 + 0] = acc4.x; red[warp * 128 + lane * 4 + 1] = acc4.y;
+      red[warp * 128 + lane * 4 + 2] = acc4.z; red[warp * 128 + lane * 4 + 3] = acc4.w;
+      __syncthreads();
+      if (warp == 0) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int w2 = 0; w2 < nwarp; w2++) {
-          if (warp == w2) {
-            if (c < C) dw[c] += acc4.x;
-            if (c + 1 < C) dw[c + 1] += acc4.y;
-            if (c + 2 < C) dw[c + 2] += acc4.z;
-            if (c + 3 < C) dw[c + 3] += acc4.w;
-          }
-          __syncthreads();
+          t.x += red[w2 * 128 + lane * 4 + 0]; t.y += red[w2 * 128 + lane * 4 + 1];
+          t.z += red[w2 * 128 + lane * 4 + 2]; t.w += red[w2 * 128 + lane * 4 + 3];
         }
+        if (c < C) dw[c] += t.x;
+        if (c + 1 < C) dw[c + 1] += t.y;
+        if (c + 2 < C) dw[c + 2] += t.z;
+        if (c + 3 < C) dw[c + 3] += t.w;
       }
     }
     if (threadIdx.x == 0) *ticket = 0;
@@ -590,7 +577,7 @@ MLB_API int mlb_rmsnorm_bwd_blocks(long rows) {
 MLB_API int mlb_rmsnorm_bwd(void* dx, float* dw, const void* dy, const void* x, const void* w, const float* rstd, const void* add,
                             long rows, int C, float* partial, int* ticket, cudaStream_t st) {
   const int blocks = mlb_rmsnorm_bwd_blocks(rows);
-  const size_t sh = (size_t)C * sizeof(float);
+  const size_t sh = (size_t)(C > 1024 ? C : 1024) * sizeof(float);   // >= 8 warps x 128 floats for the final fold
 #define RB(V)                                                                                                         \
   rmsnorm_bwd_k<V><<<blocks, 256, sh, st>>>((bf16*)dx, dw, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,   \
                                             (const bf16*)add, rows, C, partial, ticket)

@@ -1,0 +1,128 @@
+"""CPU (no GPU) end-to-end checks of the explicit forward/backward engine against PyTorch autograd, the overfit modes
+with asserted thresholds, and gradient-accumulation semantics."""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from ml_b200 import Config, RunConfig, VisionConfig
+from ml_b200.models import GPT
+from ml_b200.trainer import Trainer
+from ml_b200.data import mm_batch
+from ml_b200.utils.rng import Stream
+
+
+def autograd_loss(g: GPT, ids, tgt):
+    """Plain nn.functional restatement of the decoder (same math as reference/bench_torch.py:8-61) on g's weights."""
+    c, L = g.cfg, g.layout
+    p = g.master.clone().requires_grad_(True)
+    B, T, C, H, hd, I = ids.numel() // c.T, c.T, c.C, c.H, c.hd, c.I
+
+    def W(off, *shape):
+        return p[off:off + math.prod(shape)].view(*shape)
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + c.eps) * w
+
+    cos, sin = g.cos, g.sin
+
+    def rope(x):  # [B,T,H,hd]
+        h2 = hd // 2
+        x0, x1 = x[..., :h2], x[..., h2:]
+        cc, ss = cos.view(1, T, 1, h2), sin.view(1, T, 1, h2)
+        return torch.cat([x0 * cc - x1 * ss, x1 * cc + x0 * ss], -1)
+
+    x = W(0, c.V, C)[ids.long()].view(B, T, C)
+    for l in range(c.L):
+        o = L.layer(l)
+        h = rms(x, W(o.ln1, C))
+        qkv = (h @ W(o.qkv, 3 * C, C).t()).view(B, T, 3, H, hd)
+        q, k, v = rope(qkv[:, :, 0]), rope(qkv[:, :, 1]), qkv[:, :, 2]
+        a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        x = x + a.transpose(1, 2).reshape(B, T, C) @ W(o.o, C, C).t()
+        h = rms(x, W(o.ln2, C))
+        gu = h @ W(o.gate, 2 * I, C).t()
+        x = x + (F.silu(gu[..., :I]) * gu[..., I:]) @ W(o.down, C, I).t()
+    logits = rms(x, W(L.off_lnf, C)) @ W(L.off_lm, c.V, C).t()
+    loss = F.cross_entropy(logits.view(B * T, c.V), tgt.long(), ignore_index=-1, reduction="sum") / (tgt >= 0).sum()
+    loss.backward()
+    return loss.item(), p.grad
+
+
+def test_engine_matches_autograd():
+    cfg = Config(V=97, C=48, L=2, H=4, I=80, T=16)
+    B = 3
+    g = GPT(cfg, B)
+    g.init_weights(1234)
+    ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+    tgt[::5] = -1
+    g.forward(ids)
+    valid = int((tgt >= 0).sum())
+    g.backward(ids, tgt, valid_tokens=valid)
+    loss_ref, grad_ref = autograd_loss(g, ids, tgt)
+    assert abs(g.mean_loss(valid_tokens=valid) - loss_ref) < 1e-5
+    assert (g.grads - grad_ref).abs().max() < 2e-5
+
+
+def test_overfit_cpu_matches_reference_curve():
+    """`overfit` mode: the reference prints 5.58087 -> 0.00133 after 200 steps (its todo.md:32)."""
+    cfg = Config(V=256, C=128, L=4, H=4, I=256, T=64)
+    tr = Trainer(cfg, 4, "cpu", lr=1e-3, wd=0.0)
+    ids, tgt = Stream(99).token_pairs(4 * 64, 256)
+    tr.set_batch(ids, tgt)
+    first = None
+    for s in range(200):
+        tr.step()
+        if s == 0:
+            first = tr.loss()
+    assert abs(first - 5.5808) < 2e-3
+    assert abs(tr.loss() - 0.00133) < 3e-4
+
+
+def test_mm_overfit_cpu():
+    """`mm_overfit`: gradients flow LM -> projector -> vision tower (reference: 5.56500 -> 0.00115)."""
+    cfg = Config(V=256, C=128, L=4, H=4, I=256, T=64)
+    vc = VisionConfig(vC=96, vL=3, vI=192, n_patch=16)
+    tr = Trainer(cfg, 2, "cpu", lr=1e-3, wd=0.0, vision=vc, n_text=48)
+    patches, ids, tgt = mm_batch(2, 16, 48, 256, vc.patch_dim)
+    tr.vision.patches.copy_(patches)
+    tr.set_batch(ids, tgt)
+    v0 = tr.vision.master.clone()
+    first = None
+    for s in range(120):
+        tr.step()
+        if s == 0:
+            first = tr.loss()
+    assert abs(first - 5.565) < 5e-3
+    assert tr.loss() < 0.02
+    assert (tr.vision.master - v0).abs().max() > 1e-3   # the tower really trains
+
+
+def test_accumulation_equals_big_batch():
+    cfg = Config(V=64, C=32, L=1, H=2, I=64, T=8)
+    ids, tgt = Stream(3).token_pairs(4 * 8, 64)
+    big = Trainer(cfg, 4, "cpu", lr=1e-2, wd=0.0)
+    big.set_batch(ids, tgt)
+    big.step()
+    r = RunConfig()
+    r.accum = 2
+    acc = Trainer(cfg, 2, "cpu", run=r, lr=1e-2, wd=0.0)
+    acc.set_batch(ids, tgt)
+    acc.step()
+    assert (big.model.master - acc.model.master).abs().max() < 5e-5   # fp32 summation order; Adam normalises the first update
+
+
+def test_vision_pixels_path_equals_patch_path():
+    from ml_b200.models import VisionTower
+    from ml_b200.ops import ref
+    vc = VisionConfig(vC=32, vL=1, vI=48, n_patch=4, patch=4)
+    vt = VisionTower(vc, 24, 2)
+    vt.init_weights()
+    px = torch.randn(2, 3, 8, 8)
+    a = vt.forward_pixels(px).clone()
+    patches = torch.empty(8, vc.patch_dim)
+    ref.patchify(patches, px, 4)
+    b = vt.forward(patches.clone())
+    assert torch.equal(a, b)
+    # patch (0,1) of image 0 is the pixel block rows 0..3, cols 4..7, channel-major
+    assert torch.equal(patches[1].view(3, 4, 4), px[0, :, 0:4, 4:8])

@@ -1,0 +1,205 @@
+"""Host runtime (C++): RNG recurrence, token loader + pipe, checkpoint layout / resume / corruption, metrics sinks,
+planner and lmce_check output."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from ml_b200 import Config
+from ml_b200.data import TokenLoader, BatchPipe, write_token_bin, bench_batch
+from ml_b200.layout import DecoderLayout, VisionLayout, flops_per_step
+from ml_b200.config import VisionConfig, RunConfig
+from ml_b200.utils import ckpt as ck
+from ml_b200.utils.metrics import MetricsLogger, read_tfevents
+from ml_b200.utils.rng import Stream, init_decoder
+
+
+def py_xorshift(seed, n):
+    st, out, M = seed, [], (1 << 64) - 1
+    for _ in range(n):
+        st ^= (st << 13) & M
+        st ^= st >> 7
+        st ^= (st << 17) & M
+        out.append(((st >> 16) & 0xFFFFFF) / float(1 << 24))
+    return out
+
+
+def test_rng_matches_recurrence():
+    u = Stream(1234).uniform(50)
+    exp = torch.tensor(py_xorshift(1234, 50), dtype=torch.float32)
+    assert torch.equal(u, exp)
+    t = Stream(7).tokens(20, 50304)
+    assert t.tolist() == [int(torch.tensor(x, dtype=torch.float32) * 50304) for x in py_xorshift(7, 20)]
+    n = Stream(99).normal(1000, 0.02)
+    assert abs(n.std().item() - 0.02) < 2e-3 and abs(n.mean().item()) < 2e-3
+
+
+def test_layout_and_param_counts():
+    assert DecoderLayout(Config(V=32768)).num_params == 135_285_504
+    assert DecoderLayout(Config(V=50304)).num_params == 162_220_800
+    big = Config(V=50304, C=2048, L=24, H=16, I=5504, T=2048)
+    lay = DecoderLayout(big)
+    assert lay.num_params == 1_420_396_544 and lay.layer_stride == 50_597_888
+    assert abs(flops_per_step(Config(V=50304), 16) / 1.400e13 - 1) < 1e-3
+    assert abs(flops_per_step(big, 8) / 1.493e14 - 1) < 1e-3
+    order = [n for n, _, _ in DecoderLayout(Config(V=128, C=16, L=3, H=2, I=32, T=8)).slices_backward_order()]
+    assert order == ["lm", "lnf", "layer2", "layer1", "layer0", "wte"]
+    vl = VisionLayout(VisionConfig(vC=768, vL=4, vI=2048, n_patch=196), 768)
+    assert vl.num_params == 768 * 768 + 196 * 768 + 4 * (768 + 3 * 2048 * 768) + 768 + 768 * 768
+
+
+def test_init_scales_and_norm_slots():
+    cfg = Config(V=64, C=16, L=2, H=2, I=32, T=8)
+    lay = DecoderLayout(cfg)
+    h = init_decoder(lay, 1234)
+    o = lay.layer(1)
+    assert (h[o.ln1:o.ln1 + 16] == 1).all() and (h[lay.off_lnf:lay.off_lnf + 16] == 1).all()
+    first = Stream(1234).normal(4, 0.02)
+    assert torch.equal(h[:4], first)          # wte consumes the stream first
+
+
+def test_loader_windows_wrap_and_errors(tmp_path):
+    toks = torch.arange(0, 1000, dtype=torch.int32) % 60000
+    p = str(tmp_path / "t.bin")
+    write_token_bin(p, toks)
+    B, T = 2, 8
+    ld = TokenLoader(p, B, T)
+    assert ld.ntok == 1000
+    ids, tgt = ld.next()
+    assert ids.tolist() == list(range(16)) and tgt.tolist() == list(range(1, 17))
+    ids, tgt = ld.next()
+    assert ids[0] == 16 and ld.pos == 32
+    ld.pos = 1000 - 16          # window of 17 no longer fits -> wrap to 0
+    ids, _ = ld.next()
+    assert ids[0] == 0
+    with pytest.raises(OSError):
+        TokenLoader(str(tmp_path / "missing.bin"), B, T)
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(b"\0" * 600)
+    with pytest.raises(OSError):
+        TokenLoader(str(bad), B, T)
+    with pytest.raises(OSError):
+        TokenLoader(p, 100, 100)      # needs 10001 tokens
+    # truncated payload: header promises more tokens than the file holds -> served from what is there
+    data = open(p, "rb").read()
+    tr = tmp_path / "trunc.bin"
+    tr.write_bytes(data[:256 + 2 * 100])
+    assert TokenLoader(str(tr), B, T).ntok == 100
+
+
+def test_batch_pipe_order_cpu(tmp_path):
+    toks = torch.arange(0, 500, dtype=torch.int32)
+    p = str(tmp_path / "t.bin")
+    write_token_bin(p, toks)
+    ld = TokenLoader(p, 1, 10)
+    pipe = BatchPipe(ld, "cpu")
+    seen = []
+    for step in range(6):
+        ids, tgt = pipe.acquire(step)
+        seen.append(int(ids[0]))
+        assert int(tgt[0]) == int(ids[0]) + 1
+        pipe.release(step)
+    assert seen == [0, 10, 20, 30, 40, 50]
+    pipe.close()
+
+
+def test_checkpoint_layout_roundtrip_and_corruption(tmp_path):
+    n = 1000
+    master, m, v = torch.randn(n), torch.rand(n), torch.rand(n)
+    w = ck.CheckpointWriter()
+    d = w.save(str(tmp_path), 40, 1.25, 123456, master, m, v, loader_pos=77, opt_t=41, wait=True)
+    w.close()
+    assert sorted(os.listdir(d)) == ["meta.bin", "optim_rank_0.bin", "state_rank_0.bin", "weights_rank_0.bin"]
+    raw = open(os.path.join(d, "meta.bin"), "rb").read()
+    assert len(raw) == 32
+    step, loss, tok, ver = struct.unpack("<q f 4x q i 4x", raw)      # {int64; float; pad; int64; int; pad}
+    assert (step, tok, ver) == (40, 123456, 1) and abs(loss - 1.25) < 1e-7
+    assert os.path.getsize(os.path.join(d, "weights_rank_0.bin")) == 4 * n
+    a, b, c = torch.zeros(n), torch.zeros(n), torch.zeros(n)
+    info = ck.load(str(tmp_path), 40, a, b, c)
+    assert torch.equal(a, master) and torch.equal(b, m) and torch.equal(c, v)
+    assert info == dict(step=40, loss=1.25, tokens_seen=123456, loader_pos=77, opt_t=41)
+    assert ck.latest_step(str(tmp_path)) == 40
+    assert ck.load(str(tmp_path), 41, a, b, c) is None          # missing step -> start fresh
+    with open(os.path.join(d, "weights_rank_0.bin"), "r+b") as f:   # truncated payload must be refused
+        f.truncate(100)
+    with pytest.raises(OSError):
+        ck.load(str(tmp_path), 40, a, b, c)
+    with open(os.path.join(d, "meta.bin"), "r+b") as f:
+        f.truncate(10)
+    with pytest.raises(OSError):
+        ck.read_meta(str(tmp_path), 40)
+
+
+def test_sharded_checkpoint(tmp_path):
+    n = 64
+    master, m, v = torch.arange(n, dtype=torch.float32), torch.ones(n), torch.ones(n) * 2
+    for r in range(2):
+        w = ck.CheckpointWriter()
+        w.save(str(tmp_path), 5, 0.0, 0, master, m, v, rank=r, shard=(r * 32, 32), write_meta=(r == 0), wait=True)
+        w.close()
+    a, b, c = torch.zeros(n), torch.zeros(n), torch.zeros(n)
+    for r in range(2):
+        ck.load(str(tmp_path), 5, a, b, c, rank=r, shard=(r * 32, 32))
+    assert torch.equal(a, master)
+    assert os.path.getsize(os.path.join(str(tmp_path), "step_5", "weights_rank_1.bin")) == 4 * n // 2
+
+
+def test_metrics_jsonl_and_tfevents(tmp_path):
+    lg = MetricsLogger(str(tmp_path), rank=0)
+    lg.log(10, 2.5, 3e-4, 1000, 12.5, {"mfu": 0.4})
+    lg.log(20, 2.0, 3e-4, 2000, 12.0, {"mfu": 0.41})
+    lg.close()
+    rows = [json.loads(l) for l in open(tmp_path / "metrics.jsonl")]
+    assert [r["step"] for r in rows] == [10, 20]
+    assert set(rows[0]) >= {"step", "wall_time", "loss", "lr", "tokens_seen", "step_time_ms", "cuda_mem_free", "cuda_mem_total", "mfu"}
+    ev = [f for f in os.listdir(tmp_path) if f.startswith("events.out.tfevents")]
+    assert len(ev) == 1
+    recs = read_tfevents(str(tmp_path / ev[0]))
+    tags = {t for _, t, _ in recs}
+    assert {"train/loss", "train/lr", "train/tokens_seen", "train/step_time_ms", "cuda/mem_free", "cuda/mem_total", "train/mfu"} <= tags
+    assert (20, "train/loss", 2.0) in recs
+    assert MetricsLogger(str(tmp_path / "r1"), rank=1).h is None       # only rank 0 writes
+
+
+def test_plan_and_lmce_and_knobs(capsys):
+    from ml_b200.parallel.plan import plan_from_env, make_plan
+    txt = plan_from_env({"ENTROPY_WORLD": "8", "ENTROPY_PP": "4", "ENTROPY_MICROBATCHES": "8", "ENTROPY_SPARE_GPUS": "1"})
+    assert "world=8 active=7 spare=1 pp=4 dp=1 remainder=3 microbatches=8" in txt
+    assert "1F1B pipeline bubble: 27.3%" in txt and "stage 3: layers [9,12)" in txt and "hot spare: keep 1 GPU(s)" in txt
+    p = make_plan(Config(), 5, 0, 1, 8, 8)
+    assert p.dp == 5 and p.bubble == 0.0 and abs(p.act_boundary_mib - 12.0) < 1e-9
+    from ml_b200.utils import lmce_check
+    assert lmce_check.main(env={}) == 0
+    assert "7/7 cases passed" in capsys.readouterr().out
+    assert lmce_check.main(env={"ENTROPY_CHECK_BT": "5", "ENTROPY_CHECK_V": "33", "ENTROPY_CHECK_CHUNK": "4"}) == 0
+    r = RunConfig.from_env({"ENTROPY_ACCUM": "16", "ENTROPY_BF16_REDUCE": "0", "ENTROPY_ATTN": "mat", "ENTROPY_PEAK_TFLOPS": "989"})
+    assert (r.accum, r.bf16_reduce, r.attn, r.peak_tflops) == (16, 0, "mat", 989.0)
+    c = Config.from_env({"ENTROPY_V": "50304", "ENTROPY_T": "2048"})
+    assert (c.V, c.T, c.C) == (50304, 2048, 768)
+
+
+def test_cli_train_checkpoint_resume(tmp_path):
+    import subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    toks = (torch.arange(0, 20000, dtype=torch.int64) * 7919 % 251).to(torch.int32)
+    p = str(tmp_path / "d.bin")
+    write_token_bin(p, toks)
+    env = dict(os.environ, ENTROPY_DEVICE="cpu", ENTROPY_V="256", ENTROPY_C="32", ENTROPY_L="1", ENTROPY_H="2", ENTROPY_I="64",
+               ENTROPY_T="16", ENTROPY_B="2", ENTROPY_LOG_EVERY="5", PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    base = [sys.executable, "-m", "ml_b200.gpt", "train", p]
+    a = subprocess.run(base + ["10", "--ckpt-dir", str(tmp_path / "ck"), "--save-every", "5", "--log-dir", str(tmp_path / "log")],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert a.returncode == 0, a.stdout + a.stderr
+    assert "step    10 | loss" in a.stdout
+    assert ck.latest_step(str(tmp_path / "ck")) == 10
+    b = subprocess.run(base + ["15", "--ckpt-dir", str(tmp_path / "ck"), "--resume", "-2"], env=env, capture_output=True, text=True, timeout=300)
+    assert b.returncode == 0, b.stdout + b.stderr
+    assert "resumed from step 10" in b.stdout and "step    15 | loss" in b.stdout
+    # an uninterrupted 15-step run ends at the same loss as 10 steps + resume + 5 steps
+    c = subprocess.run(base + ["15"], env=env, capture_output=True, text=True, timeout=300)
+    la = [l for l in b.stdout.splitlines() if l.startswith("step    15")][0].split("|")[1]
+    lc = [l for l in c.stdout.splitlines() if l.startswith("step    15")][0].split("|")[1]
+    assert la == lc, (la, lc)
