@@ -48,195 +48,241 @@ struct AttnArgs {
 };
 
 // ================================================================== forward
-// 512 threads: warp w reads TMEM lane group (w & 3) and column quarter (w >> 2), i.e. four threads share a query row,
-// each owning 32 of the 128 score columns and HD/4 of the output columns.  S for block j+1 is issued into the second
-// TMEM score buffer before the softmax of block j starts, so the tensor core works under the exponentials.
-constexpr int ATT_THREADS = 512;
+// Warp-specialised: 16 softmax warps + 1 control warp (one thread of it issues every TMA load and tcgen05.mma).
+// Softmax warp w reads TMEM lane group (w & 3) and score-column quarter (w >> 2): four threads share a query row, each
+// owning 32 of the 128 score columns and HD/4 of the output columns.  Scores, P tiles and P.V results are all double
+// buffered (TMEM: S0 S1 O0 O1), so the control warp runs two key blocks ahead and the softmax warps never wait for an
+// MMA they have just enabled: the accumulation O += P_j V_j is folded in one iteration late.
+constexpr int ATT_SOFTMAX_WARPS = 16;
+constexpr int ATT_THREADS = (ATT_SOFTMAX_WARPS + 1) * 32;
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
 template <int HD>
 struct FwdSmem {
   static constexpr int CH = HD / 64;
+  static constexpr int VBUF = (HD == 64) ? 2 : 1;
   static constexpr int Q = 0;
-  static constexpr int K0 = Q + CH * TILE_BYTES;
-  static constexpr int K1 = K0 + CH * TILE_BYTES;
-  static constexpr int V = K1 + CH * TILE_BYTES;
-  static constexpr int P = V + CH * TILE_BYTES;
-  static constexpr int RED = P + 2 * TILE_BYTES;   // 4 x 128 floats: per-quarter row maxima / row sums
-  static constexpr int BAR = RED + 2048;
-  static constexpr int TOTAL = BAR + 128 + 1024;
+  static constexpr int K = Q + CH * TILE_BYTES;                 // 2 slots
+  static constexpr int V = K + 2 * CH * TILE_BYTES;             // VBUF slots
+  static constexpr int P = V + VBUF * CH * TILE_BYTES;          // 2 buffers x [128 x 128] bf16
+  static constexpr int RED = P + 2 * 2 * TILE_BYTES;            // 2 x 4 x 128 floats: per-quarter row maxima / sums
+  static constexpr int BAR = RED + 4096;
+  static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
   using S = FwdSmem<HD>;
-  constexpr int CH = HD / 64, OC = HD / 4;
+  constexpr int CH = HD / 64, OC = HD / 4, VBUF = S::VBUF;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + S::BAR);
-  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 4, *bar_o = bars + 6;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 7);
+  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_p = bars + 7, *bar_o = bars + 9;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+  volatile int* s_abort = (volatile int*)(bars + 12);   // set by the first wait that runs out; later waits are skipped
   float* s_red = (float*)(smem + S::RED);
+  {   // an earlier CTA already gave up on a wait: do not queue more 4 s waits behind it (CTA-uniform decision)
+    __shared__ int s_skip;
+    if (threadIdx.x == 0) s_skip = *(volatile int*)&g_mlb_error;
+    __syncthreads();
+    if (s_skip != 0) return;
+  }
 
   const int nq = (a.T + 127) / 128;
   const int qt = nq - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = qt * 128;
   const int C = a.H * HD;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
   const int row0 = b * a.T;
+  const int nkb = qt + 1;
 
   if (tid == 0) {
-    tc::mbar_init(bar_q, 1); tc::mbar_init(&bar_k[0], 1); tc::mbar_init(&bar_k[1], 1); tc::mbar_init(bar_v, 1);
-    tc::mbar_init(&bar_s[0], 1); tc::mbar_init(&bar_s[1], 1); tc::mbar_init(bar_o, 1);
+    tc::mbar_init(bar_q, 1);
+    for (int i = 0; i < 2; i++) {
+      tc::mbar_init(&bar_k[i], 1); tc::mbar_init(&bar_v[i], 1); tc::mbar_init(&bar_s[i], 1);
+      tc::mbar_init(&bar_p[i], ATT_SOFTMAX_WARPS); tc::mbar_init(&bar_o[i], 1);
+    }
+    *s_abort = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tm);
   }
-  if (warp == 0) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == ATT_SOFTMAX_WARPS) tc::tmem_alloc(tmem_slot, TMEM_COLS);
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_o = tmem + 256;
-  const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
-  const int nkb = qt + 1;
-  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);
-  const uint32_t sQ = tc::smem_u32(smem + S::Q), sV = tc::smem_u32(smem + S::V), sP = tc::smem_u32(smem + S::P);
+  const uint32_t t_o = tmem + 256;   // O buffers at +256 and +256+HD
+  // Bounded, sticky wait: after the first expiry in this CTA every later wait returns at once, and all threads keep
+  // executing the same sequence of arrivals / named barriers, so nobody is left waiting for a thread that gave up.
+  auto wait = [&](uint64_t* bar, uint32_t phase, int where) -> bool {
+    if (*s_abort) return false;
+    if (!tc::mbar_wait(bar, phase, where)) { *s_abort = 1; return false; }
+    return true;
+  };
 
-  auto load_k = [&](int j, int buf) {
-    tc::mbar_expect_tx(&bar_k[buf], CH * TILE_BYTES);
-    for (int c = 0; c < CH; c++)
-      tc::tma_load_2d(smem + (buf ? S::K1 : S::K0) + c * TILE_BYTES, &tm, &bar_k[buf], C + h * HD + c * 64, row0 + j * 128);
-  };
-  auto load_v = [&](int j) {
-    tc::mbar_expect_tx(bar_v, CH * TILE_BYTES);
-    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::V + c * TILE_BYTES, &tm, bar_v, 2 * C + h * HD + c * 64, row0 + j * 128);
-  };
-  auto issue_s = [&](int j) {   // S(j) = Q K_j^T into score buffer j & 1
-    const uint32_t sK = tc::smem_u32(smem + ((j & 1) ? S::K1 : S::K0));
+  if (warp == ATT_SOFTMAX_WARPS) {
+    // ---------------------------------------------------------------- control warp
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);
+      const uint32_t sQ = tc::smem_u32(smem + S::Q);
+      auto load_k = [&](int j) {
+        const int sl = j & 1;
+        tc::mbar_expect_tx(&bar_k[sl], CH * TILE_BYTES);
+        for (int c = 0; c < CH; c++)
+          tc::tma_load_2d(smem + S::K + (sl * CH + c) * TILE_BYTES, &tm, &bar_k[sl], C + h * HD + c * 64, row0 + j * 128);
+      };
+      auto load_v = [&](int j) {
+        const int sl = j % VBUF;
+        tc::mbar_expect_tx(&bar_v[sl], CH * TILE_BYTES);
+        for (int c = 0; c < CH; c++)
+          tc::tma_load_2d(smem + S::V + (sl * CH + c) * TILE_BYTES, &tm, &bar_v[sl], 2 * C + h * HD + c * 64, row0 + j * 128);
+      };
+      auto issue_s = [&](int j) {   // S(j) = Q K_j^T into score buffer j & 1
+        const uint32_t sK = tc::smem_u32(smem + S::K + (j & 1) * CH * TILE_BYTES);
 #pragma unroll
-    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(tmem + (j & 1) * 128, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
-  };
-
-  if (tid == 0) {
-    tc::mbar_expect_tx(bar_q, CH * TILE_BYTES);
-    for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::Q + c * TILE_BYTES, &tm, bar_q, h * HD + c * 64, row0 + q0);
-    load_k(0, 0);
-    if (nkb > 1) load_k(1, 1);
-    load_v(0);
-    if (tc::mbar_wait(bar_q, 0, 10) && tc::mbar_wait(&bar_k[0], 0, 11)) {
-      tc::tc_fence_after();
-      issue_s(0);
-    }
-    tc::mma_commit(&bar_s[0]);
-  }
-
-  const float sl2 = a.scale * LOG2E;
-  float m = -INFINITY, l = 0.f;
-  float o[OC];
-#pragma unroll
-  for (int i = 0; i < OC; i++) o[i] = 0.f;
-  const int qrow = q0 + row;
-  bool ok = true;
-
-  for (int j = 0; j < nkb; j++) {
-    const int k0 = j * 128;
-    if (!tc::mbar_wait(&bar_s[j & 1], (j >> 1) & 1, 12)) { ok = false; break; }
-    tc::tc_fence_after();
-    if (tid == 0) {
-      if (j + 1 < nkb) {
-        if (tc::mbar_wait(&bar_k[(j + 1) & 1], ((j + 1) >> 1) & 1, 13)) {
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(tmem + (j & 1) * 128, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
+      };
+      tc::mbar_expect_tx(bar_q, CH * TILE_BYTES);
+      for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::Q + c * TILE_BYTES, &tm, bar_q, h * HD + c * 64, row0 + q0);
+      load_k(0);
+      if (nkb > 1) load_k(1);
+      load_v(0);
+      if (VBUF == 2 && nkb > 1) load_v(1);
+      if (wait(bar_q, 0, 10) && wait(&bar_k[0], 0, 11)) { tc::tc_fence_after(); issue_s(0); }
+      tc::mma_commit(&bar_s[0]);
+      if (nkb > 1) {
+        if (wait(&bar_k[1], 0, 11)) { tc::tc_fence_after(); issue_s(1); }
+        tc::mma_commit(&bar_s[1]);
+      }
+      for (int j = 0; j < nkb; j++) {
+        const int sl = j & 1, ph = (j >> 1) & 1;
+        // (a) S(j) is complete: its K slot can take K(j+2)
+        if (wait(&bar_s[sl], ph, 12) && j + 2 < nkb) load_k(j + 2);
+        // (b) P(j) written (and S(j) fully read) -> O_blk(j) = P_j V_j
+        if (wait(&bar_p[sl], ph, 13) && wait(&bar_v[j % VBUF], (j / VBUF) & 1, 14)) {
           tc::tc_fence_after();
-          issue_s(j + 1);
+          const uint32_t sP = tc::smem_u32(smem + S::P + sl * 2 * TILE_BYTES);
+          const uint32_t sV = tc::smem_u32(smem + S::V + (j % VBUF) * CH * TILE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_o + sl * HD, desc_k(sP, ks), desc_mn(sV, ks), idesc_o, ks > 0);
         }
-        tc::mma_commit(&bar_s[(j + 1) & 1]);
+        tc::mma_commit(&bar_o[sl]);
+        // (c) score buffer j&1 is free: S(j+2)
+        if (j + 2 < nkb) {
+          if (wait(&bar_k[sl], ((j + 2) >> 1) & 1, 15)) { tc::tc_fence_after(); issue_s(j + 2); }
+          tc::mma_commit(&bar_s[sl]);
+        }
+        // (d) V slot free once P_j V_j has completed
+        if (j + VBUF < nkb && wait(&bar_o[sl], ph, 16)) load_v(j + VBUF);
       }
-      if (j + 2 < nkb) load_k(j + 2, j & 1);   // S(j) has completed: its K buffer is free
     }
-    uint32_t r[32];
-    tc::tmem_ld32(tmem + (j & 1) * 128 + lane_addr + cq * 32, r);
-    tc::tmem_ld_wait();
-    const bool diag = (j == qt);
-    const int kc0 = k0 + cq * 32;
-    float mx = -INFINITY;
+  } else {
+    // ---------------------------------------------------------------- softmax warps
+    const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+    const float sl2 = a.scale * LOG2E;
+    const int qrow = q0 + row;
+    float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+    float o[OC];
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-      const float v = __uint_as_float(r[i]);
-      if (!diag || kc0 + i <= qrow) mx = fmaxf(mx, v);
-    }
-    s_red[cq * 128 + row] = mx;
-    __syncthreads();
-    mx = fmaxf(fmaxf(s_red[row], s_red[128 + row]), fmaxf(s_red[256 + row], s_red[384 + row]));
-    const float m_new = fmaxf(m, mx * sl2);
-    const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-    float rs = 0.f;
-    float pf[32];
+    for (int i = 0; i < OC; i++) o[i] = 0.f;
+    auto fold = [&](int jb, float alpha) {   // O = O * alpha + (P V) of block jb
+      if (OC == 16) {
+        uint32_t ro[16];
+        tc::tmem_ld16(t_o + (jb & 1) * HD + lane_addr + cq * 16, ro);
+        tc::tmem_ld_wait();
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-      const float v = exp2f(__uint_as_float(r[i]) * sl2 - m_new);
-      pf[i] = (!diag || kc0 + i <= qrow) ? v : 0.f;
-      rs += pf[i];
-    }
+        for (int i = 0; i < 16; i++) o[i] = o[i] * alpha + __uint_as_float(ro[i]);
+      } else {
+        uint32_t ro[32];
+        tc::tmem_ld32(t_o + (jb & 1) * HD + lane_addr + cq * 32, ro);
+        tc::tmem_ld_wait();
 #pragma unroll
-    for (int v8 = 0; v8 < 4; v8++) {
-      uint4 pk;
-      pk.x = pack_bf16(pf[v8 * 8 + 0], pf[v8 * 8 + 1]); pk.y = pack_bf16(pf[v8 * 8 + 2], pf[v8 * 8 + 3]);
-      pk.z = pack_bf16(pf[v8 * 8 + 4], pf[v8 * 8 + 5]); pk.w = pack_bf16(pf[v8 * 8 + 6], pf[v8 * 8 + 7]);
-      *reinterpret_cast<uint4*>(smem + S::P + sw_off(row, cq * 32 + v8 * 8)) = pk;
-    }
-    l = l * alpha + rs;
-    m = m_new;
-    tc::fence_async_smem();
-    tc::tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
+        for (int i = 0; i < 32; i++) o[i % OC] = o[i % OC] * alpha + __uint_as_float(ro[i]);
+      }
+      tc::tc_fence_before();
+    };
+    for (int j = 0; j < nkb; j++) {
+      const int sl = j & 1, ph = (j >> 1) & 1;
+      const int kc0 = j * 128 + cq * 32;
+      wait(&bar_s[sl], ph, 17);
       tc::tc_fence_after();
-      if (tc::mbar_wait(bar_v, j & 1, 14)) {
-        tc::tc_fence_after();
+      uint32_t r[32];
+      tc::tmem_ld32(tmem + sl * 128 + lane_addr + cq * 32, r);
+      tc::tmem_ld_wait();
+      float mx = -INFINITY;
+      if (j == qt) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_o, desc_k(sP, ks), desc_mn(sV, ks), idesc_o, ks > 0);
+        for (int i = 0; i < 32; i++) {
+          if (kc0 + i > qrow) r[i] = 0xff800000u;   // -inf: masked by causality
+          mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
       }
-      tc::mma_commit(bar_o);
+      float* red = s_red + sl * 512;
+      red[cq * 128 + row] = mx;
+      named_bar_sync(1 + lg, 128);
+      mx = fmaxf(fmaxf(red[row], red[128 + row]), fmaxf(red[256 + row], red[384 + row]));
+      const float m_new = fmaxf(m, mx * sl2);   // finite: key 0 is visible to every query
+      const float alpha = exp2f(m - m_new);     // exp2(-inf) = 0 on the first block
+      float rs = 0.f;
+      uint8_t* pbuf = smem + S::P + sl * 2 * TILE_BYTES;
+#pragma unroll
+      for (int v8 = 0; v8 < 4; v8++) {
+        float pf[8];
+#pragma unroll
+        for (int x = 0; x < 8; x++) {
+          pf[x] = exp2f(__uint_as_float(r[v8 * 8 + x]) * sl2 - m_new);
+          rs += pf[x];
+        }
+        uint4 pk;
+        pk.x = pack_bf16(pf[0], pf[1]); pk.y = pack_bf16(pf[2], pf[3]); pk.z = pack_bf16(pf[4], pf[5]); pk.w = pack_bf16(pf[6], pf[7]);
+        *reinterpret_cast<uint4*>(pbuf + sw_off(row, cq * 32 + v8 * 8)) = pk;
+      }
+      tc::fence_async_smem();
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&bar_p[sl]);
+      l = l * alpha + rs;
+      m = m_new;
+      if (j > 0) {   // fold in the previous block, whose P V product had a whole softmax to complete
+        wait(&bar_o[(j - 1) & 1], ((j - 1) >> 1) & 1, 18);
+        tc::tc_fence_after();
+        fold(j - 1, alpha_prev);
+      }
+      alpha_prev = alpha;
     }
-    if (!tc::mbar_wait(bar_o, j & 1, 15)) { ok = false; break; }
+    wait(&bar_o[(nkb - 1) & 1], ((nkb - 1) >> 1) & 1, 19);
     tc::tc_fence_after();
-    if (tid == 0 && j + 1 < nkb) load_v(j + 1);   // P V_j has completed: the V buffer is free
-    if (OC == 16) {
-      uint32_t ro[16];
-      tc::tmem_ld16(t_o + lane_addr + cq * 16, ro);
-      tc::tmem_ld_wait();
+    fold(nkb - 1, alpha_prev);
+    // combine the four partial row sums, normalise, store
+    float* red = s_red + (nkb & 1) * 512;
+    red[cq * 128 + row] = l;
+    named_bar_sync(1 + lg, 128);
+    const float L = red[row] + red[128 + row] + red[256 + row] + red[384 + row];
+    if (!*s_abort && qrow < a.T) {
+      const float inv = 1.f / L;
+      bf16* dst = a.out + ((size_t)(row0 + qrow)) * C + h * HD + cq * OC;
 #pragma unroll
-      for (int i = 0; i < 16; i++) o[i] = o[i] * alpha + __uint_as_float(ro[i]);
-    } else {
-      uint32_t ro[32];
-      tc::tmem_ld32(t_o + lane_addr + cq * 32, ro);
-      tc::tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; i++) o[i % OC] = o[i % OC] * alpha + __uint_as_float(ro[i]);
+      for (int v8 = 0; v8 < OC / 8; v8++) {
+        uint4 pk;
+        pk.x = pack_bf16(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv); pk.y = pack_bf16(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
+        pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
+      }
+      if (cq == 0) a.lse[((size_t)b * a.H + h) * a.T + qrow] = (m + log2f(L)) * LN2;
     }
-    tc::tc_fence_before();
-  }
-  // combine the four partial row sums, normalise, store
-  __syncthreads();
-  s_red[cq * 128 + row] = l;
-  __syncthreads();
-  const float L = s_red[row] + s_red[128 + row] + s_red[256 + row] + s_red[384 + row];
-  if (ok && qrow < a.T) {
-    const float inv = 1.f / L;
-    bf16* dst = a.out + ((size_t)(row0 + qrow)) * C + h * HD + cq * OC;
-#pragma unroll
-    for (int v8 = 0; v8 < OC / 8; v8++) {
-      uint4 pk;
-      pk.x = pack_bf16(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv); pk.y = pack_bf16(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
-      pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
-      *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
-    }
-    if (cq == 0) a.lse[((size_t)b * a.H + h) * a.T + qrow] = (m + log2f(L)) * LN2;
   }
   tc::tc_fence_before();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == ATT_SOFTMAX_WARPS) tc::tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // ================================================================== backward: delta = rowsum(dO * O)
@@ -319,6 +365,8 @@ __device__ __forceinline__ void store_pairs_rope(bf16* dst_row, uint32_t taddr, 
   }
 }
 
+constexpr int BWD_THREADS = 512;
+
 // ================================================================== backward: dK, dV (one CTA per 128-key tile)
 // 512 threads; thread (row = key, quarter cq) handles 32 of the 128 query columns of S^T / dP^T.  The MMAs of the next
 // query block are queued right behind the dV/dK MMAs of the current one, so one commit covers both.
@@ -338,7 +386,7 @@ struct BwdKVSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS, 1) attn_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kv_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
                                                                         const __grid_constant__ CUtensorMap tm_do,
                                                                         const AttnArgs a) {
   using S = BwdKVSmem<HD>;
@@ -509,7 +557,7 @@ struct BwdQSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(ATT_THREADS, 1) attn_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_q_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
                                                                        const __grid_constant__ CUtensorMap tm_do,
                                                                        const AttnArgs a) {
   using S = BwdQSmem<HD>;
@@ -799,14 +847,14 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
       static int o1 = set_smem(attn_bwd_kv_tc_kernel<64>, BwdKVSmem<64>::TOTAL);
       static int o2 = set_smem(attn_bwd_q_tc_kernel<64>, BwdQSmem<64>::TOTAL);
       (void)o1; (void)o2;
-      attn_bwd_kv_tc_kernel<64><<<grid, ATT_THREADS, BwdKVSmem<64>::TOTAL, st>>>(*tq, *td, a);
-      attn_bwd_q_tc_kernel<64><<<grid, ATT_THREADS, BwdQSmem<64>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_kv_tc_kernel<64><<<grid, BWD_THREADS, BwdKVSmem<64>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_q_tc_kernel<64><<<grid, BWD_THREADS, BwdQSmem<64>::TOTAL, st>>>(*tq, *td, a);
     } else {
       static int o1 = set_smem(attn_bwd_kv_tc_kernel<128>, BwdKVSmem<128>::TOTAL);
       static int o2 = set_smem(attn_bwd_q_tc_kernel<128>, BwdQSmem<128>::TOTAL);
       (void)o1; (void)o2;
-      attn_bwd_kv_tc_kernel<128><<<grid, ATT_THREADS, BwdKVSmem<128>::TOTAL, st>>>(*tq, *td, a);
-      attn_bwd_q_tc_kernel<128><<<grid, ATT_THREADS, BwdQSmem<128>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_kv_tc_kernel<128><<<grid, BWD_THREADS, BwdKVSmem<128>::TOTAL, st>>>(*tq, *td, a);
+      attn_bwd_q_tc_kernel<128><<<grid, BWD_THREADS, BwdQSmem<128>::TOTAL, st>>>(*tq, *td, a);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e + 1000;

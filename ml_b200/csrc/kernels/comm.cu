@@ -1,0 +1,199 @@
+// In-kernel collectives over NVLink peer memory, fused with the optimizer.
+//
+// ddp_bucket_kernel replaces, for one gradient bucket, the reference's chain
+//     cast_f2b -> ncclAllReduce -> cast_b2f_scale -> adamw           (train/gpt.cu:310-328, :348-367)
+// with ONE kernel and no library collective.  Every rank runs it on the same bucket:
+//   1. entry barrier: flags in every peer's symmetric flag array tell that the peer's gradients of this bucket are final;
+//   2. this rank owns 1/world of the bucket: it loads that shard of the fp32 gradients from every rank's buffer
+//      (plain peer loads over NVLink/NVSwitch), sums them in fp32 in rank order (deterministic, tighter than a bf16
+//      all-reduce), applies the 1/(world*accum) mean and the AdamW update to its shard of master / m / v, and stores the
+//      new bf16 parameters into every rank's parameter buffer (peer stores);
+//   3. exit barrier: the last CTA to finish signals every peer and waits for their signals, so when the kernel ends all
+//      peers have stopped reading this rank's gradients and this rank's parameters are complete.
+// The same kernel with world = 1 is a fused mean-scale + AdamW.  Reduce-scatter + sharded AdamW for ZeRO-style
+// sharding is the same kernel with `bcast` = 0 (parameters stay sharded).
+// Every wait on a peer flag is bounded (about 2 s): on expiry the kernel records MLB_ERR_FLAG_TIMEOUT and returns.
+#include "../common.cuh"
+
+MLB_DEFINE_ERROR_WORD(comm)
+
+namespace {
+
+constexpr int MAX_WORLD = 16;
+
+struct BucketArgs {
+  float* const* grads;       // device array [world]: base of each rank's flat fp32 gradient buffer
+  bf16* const* params;       // device array [world]: base of each rank's flat bf16 parameter buffer
+  int* const* flags;         // device array [world]: base of each rank's flag array: [2][max_buckets][MAX_WORLD] ints
+  float* master;
+  float* m;
+  float* v;
+  int* done_counter;         // local, one int per bucket, 0 between launches
+  int* epoch_ctr;            // local, one int per bucket: number of completed launches.  The epoch of a launch is
+                             // epoch_ctr[bucket] + 1, read from memory so that a replayed CUDA graph advances it.
+  long off, n;               // bucket range in elements
+  int rank, world, bucket, max_buckets, bcast;
+  float lr, b1, b2, eps, wd, inv_bc1, inv_bc2, scale;
+  const float* dev_hyper;    // optional {lr, 1/bc1, 1/bc2, scale} in device memory (CUDA-graph replay)
+  long spin_limit_ns;
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {   // system-scope relaxed load: never served from a stale L1 line
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t gtimer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits until *flag >= epoch.  Returns false (after recording the error) if that takes longer than limit_ns.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, long limit_ns, int detail) {
+  if (ld_acquire_sys(flag) >= epoch) return true;
+  const uint64_t t0 = gtimer();
+  for (;;) {
+    for (int i = 0; i < 64; i++) {
+      if (ld_acquire_sys(flag) >= epoch) return true;
+      __nanosleep(100);
+    }
+    if ((long)(gtimer() - t0) > limit_ns) {
+      mlb_set_error(MLB_ERR_FLAG_TIMEOUT, detail);
+      return false;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512) ddp_bucket_kernel(const BucketArgs a) {
+  __shared__ int s_ok, s_last;
+  const int W = a.world;
+  const int epoch = *((volatile int*)(a.epoch_ctr + a.bucket)) + 1;   // every CTA reads it before the last one bumps it
+  int* my_flags = a.flags[a.rank];
+  int* ready_row = my_flags + (0 * a.max_buckets + a.bucket) * MAX_WORLD;   // ready_row[w] written by rank w
+  int* done_row = my_flags + (1 * a.max_buckets + a.bucket) * MAX_WORLD;
+  // ---- 1. entry barrier
+  if (blockIdx.x == 0 && threadIdx.x < W) {
+    __threadfence_system();
+    int* peer_flags = a.flags[threadIdx.x];
+    st_release_sys(peer_flags + (0 * a.max_buckets + a.bucket) * MAX_WORLD + a.rank, epoch);
+  }
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < W) {
+    if (!wait_flag(ready_row + threadIdx.x, epoch, a.spin_limit_ns, (a.bucket << 8) | threadIdx.x)) s_ok = 0;
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  // ---- 2. reduce-scatter + mean + AdamW on this rank's shard, parameters stored to every rank
+  if (ok) {
+    float lr = a.lr, inv_bc1 = a.inv_bc1, inv_bc2 = a.inv_bc2, scale = a.scale;
+    if (a.dev_hyper) { lr = a.dev_hyper[0]; inv_bc1 = a.dev_hyper[1]; inv_bc2 = a.dev_hyper[2]; scale = a.dev_hyper[3]; }
+    const long chunk = ((a.n + W - 1) / W + 3) & ~3L;      // shard length, multiple of 4 elements
+    const long lo = a.off + (long)a.rank * chunk;
+    const long hi = min(a.off + a.n, lo + chunk);
+    const long nvec = (hi > lo) ? (hi - lo) / 4 : 0;       // the bucket offsets / sizes used here are multiples of 4
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+      const long e = lo + i * 4;
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int w = 0; w < W; w++) {
+        const float4 t = ld_peer_f4(a.grads[w] + e);
+        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+      }
+      float4 mm = *reinterpret_cast<const float4*>(a.m + e);
+      float4 vv = *reinterpret_cast<const float4*>(a.v + e);
+      float4 p = *reinterpret_cast<const float4*>(a.master + e);
+      float* gp = &g.x; float* mp = &mm.x; float* vp = &vv.x; float* pp = &p.x;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float gj = gp[j] * scale;
+        mp[j] = a.b1 * mp[j] + (1.f - a.b1) * gj;
+        vp[j] = a.b2 * vp[j] + (1.f - a.b2) * gj * gj;
+        pp[j] -= lr * (mp[j] * inv_bc1 / (sqrtf(vp[j] * inv_bc2) + a.eps) + a.wd * pp[j]);
+      }
+      *reinterpret_cast<float4*>(a.m + e) = mm;
+      *reinterpret_cast<float4*>(a.v + e) = vv;
+      *reinterpret_cast<float4*>(a.master + e) = p;
+      uint2 o;
+      o.x = pack_bf16(p.x, p.y);
+      o.y = pack_bf16(p.z, p.w);
+      if (a.bcast) {
+#pragma unroll 4
+        for (int w = 0; w < W; w++) *reinterpret_cast<uint2*>(a.params[w] + e) = o;
+      } else {
+        *reinterpret_cast<uint2*>(a.params[a.rank] + e) = o;
+      }
+    }
+    // scalar tail (bucket sizes that are not a multiple of 4 never occur with this model's layouts, but stay correct)
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      for (long e = lo + nvec * 4; e < hi; e++) {
+        float g = 0.f;
+        for (int w = 0; w < W; w++) g += *((volatile float*)(a.grads[w] + e));
+        g *= scale;
+        float mj = a.b1 * a.m[e] + (1.f - a.b1) * g, vj = a.b2 * a.v[e] + (1.f - a.b2) * g * g, pj = a.master[e];
+        pj -= lr * (mj * inv_bc1 / (sqrtf(vj * inv_bc2) + a.eps) + a.wd * pj);
+        a.m[e] = mj; a.v[e] = vj; a.master[e] = pj;
+        for (int w = 0; w < W; w++)
+          if (a.bcast || w == a.rank) a.params[w][e] = __float2bfloat16(pj);
+      }
+    }
+  }
+  // ---- 3. exit barrier (last CTA of this rank)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.done_counter + a.bucket, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x == 0) { a.done_counter[a.bucket] = 0; a.epoch_ctr[a.bucket] = epoch; }
+  if (threadIdx.x < W) {
+    __threadfence_system();
+    int* peer_flags = a.flags[threadIdx.x];
+    st_release_sys(peer_flags + (1 * a.max_buckets + a.bucket) * MAX_WORLD + a.rank, epoch);
+    if (ok) wait_flag(done_row + threadIdx.x, epoch, a.spin_limit_ns, 0x8000 | (a.bucket << 8) | threadIdx.x);
+  }
+}
+
+// Test hook: waits (bounded) on a flag that nothing sets, to exercise the timeout path on one GPU.
+__global__ void flag_timeout_probe_kernel(const int* flag, int epoch, long limit_ns, int* result) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *result = wait_flag(flag, epoch, limit_ns, 0x7777) ? 1 : 2;
+}
+
+}  // namespace
+
+MLB_API int mlb_comm_max_world() { return MAX_WORLD; }
+
+// One bucket of the fused data-parallel gradient step.  Pointer arrays live in device memory (world entries each).
+MLB_API int mlb_ddp_bucket(const void* grads_ptrs, const void* params_ptrs, const void* flags_ptrs, float* master, float* m, float* v,
+                           int* done_counter, int* epoch_ctr, long off, long n, int rank, int world, int bucket, int max_buckets,
+                           int bcast, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float scale,
+                           const float* dev_hyper, int ctas, double spin_limit_s, cudaStream_t st) {
+  if (world < 1 || world > MAX_WORLD || bucket < 0 || bucket >= max_buckets) return -1;
+  if ((off & 3) != 0) return -5;   // float4 path needs 16-byte aligned bucket starts
+  BucketArgs a;
+  a.grads = (float* const*)grads_ptrs; a.params = (bf16* const*)params_ptrs; a.flags = (int* const*)flags_ptrs;
+  a.master = master; a.m = m; a.v = v; a.done_counter = done_counter; a.epoch_ctr = epoch_ctr;
+  a.off = off; a.n = n; a.rank = rank; a.world = world; a.bucket = bucket; a.max_buckets = max_buckets;
+  a.bcast = bcast; a.lr = lr; a.b1 = b1; a.b2 = b2; a.eps = eps; a.wd = wd; a.inv_bc1 = 1.f / bc1; a.inv_bc2 = 1.f / bc2;
+  a.scale = scale; a.dev_hyper = dev_hyper; a.spin_limit_ns = (long)(spin_limit_s * 1e9);
+  const long chunk = ((n + world - 1) / world + 3) & ~3L;
+  long want = (chunk / 4 + 511) / 512;
+  if (want < 1) want = 1;
+  if (ctas < 1) ctas = 32;
+  const int grid = (int)(want < ctas ? want : ctas);
+  ddp_bucket_kernel<<<grid, 512, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// Runs the bounded flag wait against `flag` (device memory, never written) and stores 1 (seen) or 2 (timed out) in *result.
+MLB_API int mlb_flag_timeout_probe(const int* flag, int epoch, double limit_s, int* result, cudaStream_t st) {
+  flag_timeout_probe_kernel<<<1, 32, 0, st>>>(flag, epoch, (long)(limit_s * 1e9), result);
+  return (int)cudaGetLastError();
+}

@@ -124,9 +124,10 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, flo
 // ------------------------------------------------------------------ RMSNorm backward, ONE launch, deterministic
 // dx = add + rstd*w*dy - x*rstd^3/C * sum_c(dy*w*x);   dw[c] += sum_rows dy*x*rstd.
 // Each block walks a strided set of rows (warp per row) keeping per-column dw partial sums in registers/shared
-// memory, writes its partial row to `partial[block][C]`, and the last block to finish (atomic ticket) folds the
-// partials into dw in a fixed order.  `partial` is scratch: gridDim.x*C floats; `ticket` one int that is 0 on
-// entry and left 0 on exit.
+// memory, writes its partial row to `partial[block][C]`; the partial rows are then folded into dw in a fixed order
+// by whichever blocks finish last (see the end of the kernel).  Scratch: `partial` = (gridDim.x + RMS_GROUPS) * C
+// floats, `ticket` = 1 + RMS_GROUPS ints that are 0 on entry and left 0 on exit.
+constexpr int RMS_GROUPS = 16;
 template <int VPL>  // VPL = C / 256 (vectors of 8 per lane); 0 = generic C (scalar path)
 __global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, float* __restrict__ dw, const bf16* __restrict__ dy,
                                                      const bf16* __restrict__ x, const bf16* __restrict__ w,
@@ -214,49 +215,68 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, floa
     __syncthreads();
   }
   for (int i = threadIdx.x; i < C; i += blockDim.x) partial[(long)blockIdx.x * C + i] = sh[i];
+  // Two-level fold, deterministic and parallel: blocks form RMS_GROUPS groups by index; the block that arrives last in
+  // its group sums the group's partial rows in index order into gpartial[group]; the block that completes the last
+  // group sums the group rows in order into dw.  Who does the summing depends on timing, the summation order does not.
+  const int nb = (int)gridDim.x;
+  const int gsz = (nb + RMS_GROUPS - 1) / RMS_GROUPS;
+  const int grp = blockIdx.x / gsz;
+  const int g_lo = grp * gsz, g_hi = min(nb, g_lo + gsz);
+  const int ngroups = (nb + gsz - 1) / gsz;
+  float* gpartial = partial + (long)nb * C;
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) is_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
+  if (threadIdx.x == 0) is_last = (atomicAdd(&ticket[1 + grp], 1) == (g_hi - g_lo) - 1);
   __syncthreads();
-  if (is_last) {
-    // Fold the per-block partial rows into dw in a fixed order: warp w sums blocks w, w+8, ... for every column, the
-    // eight warp sums are then added in warp order through shared memory.
-    __threadfence();
-    const int nb = (int)gridDim.x;
-    for (int c0 = 0; c0 < C; c0 += 32 * 4) {
-      const int c = c0 + lane * 4;
-      float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (c + 3 < C) {
-        for (int b = warp; b < nb; b += nwarp) {
-          const float4 p = __ldcg(reinterpret_cast<const float4*>(&partial[(long)b * C + c]));
-          acc4.x += p.x; acc4.y += p.y; acc4.z += p.z; acc4.w += p.w;
-        }
-      } else {
-        for (int b = warp; b < nb; b += nwarp) {
-          if (c < C) acc4.x += __ldcg(&partial[(long)b * C + c]);
-          if (c + 1 < C) acc4.y += __ldcg(&partial[(long)b * C + c + 1]);
-          if (c + 2 < C) acc4.z += __ldcg(&partial[(long)b * C + c + 2]);
-        }
+  if (!is_last) return;
+  __threadfence();
+  const bool vec4 = ((C & 3) == 0) && ((reinterpret_cast<uintptr_t>(dw) & 15) == 0) && ((reinterpret_cast<uintptr_t>(partial) & 15) == 0);
+  for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+    if (vec4) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int b = g_lo; b < g_hi; b++) {
+        const float4 p = __ldcg(reinterpret_cast<const float4*>(&partial[(long)b * C + c]));
+        a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
       }
-      __syncthreads();
-      float* red = sh;  // the dynamic shared buffer holds at least nwarp x 128 floats (see the launcher)
-      red[warp * 128 + lane * 4 + 0] = acc4.x; red[warp * 128 + lane * 4 + 1] = acc4.y;
-      red[warp * 128 + lane * 4 + 2] = acc4.z; red[warp * 128 + lane * 4 + 3] = acc4.w;
-      __syncthreads();
-      if (warp == 0) {
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int w2 = 0; w2 < nwarp; w2++) {
-          t.x += red[w2 * 128 + lane * 4 + 0]; t.y += red[w2 * 128 + lane * 4 + 1];
-          t.z += red[w2 * 128 + lane * 4 + 2]; t.w += red[w2 * 128 + lane * 4 + 3];
-        }
-        if (c < C) dw[c] += t.x;
-        if (c + 1 < C) dw[c + 1] += t.y;
-        if (c + 2 < C) dw[c + 2] += t.z;
-        if (c + 3 < C) dw[c + 3] += t.w;
+      *reinterpret_cast<float4*>(&gpartial[(long)grp * C + c]) = a;
+    } else {
+      for (int cc = c; cc < min(C, c + 4); cc++) {
+        float a = 0.f;
+        for (int b = g_lo; b < g_hi; b++) a += __ldcg(&partial[(long)b * C + cc]);
+        gpartial[(long)grp * C + cc] = a;
       }
     }
-    if (threadIdx.x == 0) *ticket = 0;
   }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ticket[1 + grp] = 0;
+    is_last = (atomicAdd(&ticket[0], 1) == ngroups - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+    if (vec4) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int g2 = 0; g2 < ngroups; g2++) {
+        const float4 p = __ldcg(reinterpret_cast<const float4*>(&gpartial[(long)g2 * C + c]));
+        a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
+      }
+      float4 d = *reinterpret_cast<float4*>(&dw[c]);
+      d.x += a.x; d.y += a.y; d.z += a.z; d.w += a.w;
+      *reinterpret_cast<float4*>(&dw[c]) = d;
+    } else {
+      for (int cc = c; cc < min(C, c + 4); cc++) {
+        float a = 0.f;
+        for (int g2 = 0; g2 < ngroups; g2++) a += __ldcg(&gpartial[(long)g2 * C + cc]);
+        dw[cc] += a;
+      }
+    }
+  }
+  if (threadIdx.x == 0) ticket[0] = 0;
 }
 
 // ------------------------------------------------------------------ RoPE (in place on the Q and K slices of qkv[B*T, 3C])
@@ -569,7 +589,8 @@ MLB_API int mlb_add_rmsnorm_fwd(void* resid, void* out, float* rstd, const void*
   LAUNCH_RET;
 }
 
-// Number of blocks rmsnorm_bwd uses for `rows`; the caller provides scratch of blocks*C floats + one zeroed int.
+// Number of blocks rmsnorm_bwd uses for `rows`; the caller provides scratch of (blocks + 16) * C floats and
+// 17 zeroed ints.
 MLB_API int mlb_rmsnorm_bwd_blocks(long rows) {
   long b = (rows + 7) / 8;
   return (int)(b < 296 ? b : 296);
@@ -577,7 +598,7 @@ MLB_API int mlb_rmsnorm_bwd_blocks(long rows) {
 MLB_API int mlb_rmsnorm_bwd(void* dx, float* dw, const void* dy, const void* x, const void* w, const float* rstd, const void* add,
                             long rows, int C, float* partial, int* ticket, cudaStream_t st) {
   const int blocks = mlb_rmsnorm_bwd_blocks(rows);
-  const size_t sh = (size_t)(C > 1024 ? C : 1024) * sizeof(float);   // >= 8 warps x 128 floats for the final fold
+  const size_t sh = (size_t)C * sizeof(float);
 #define RB(V)                                                                                                         \
   rmsnorm_bwd_k<V><<<blocks, 256, sh, st>>>((bf16*)dx, dw, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,   \
                                             (const bf16*)add, rows, C, partial, ticket)
@@ -657,3 +678,4 @@ MLB_API int mlb_posembed_grad(float* dpos, const void* dx, long NP, int n_patch,
   posembed_grad_k<<<gs((long)n_patch * vC, 256), 256, 0, st>>>(dpos, (const bf16*)dx, NP, n_patch, vC);
   LAUNCH_RET;
 }
+

@@ -318,6 +318,7 @@ int num_sms() {
 
 int g_force_simt = 0;        // test hook: route everything through the SIMT kernel
 int g_max_ctas = 0;          // 0 = one CTA per SM; >0 caps the persistent grid (leaves SMs to a concurrent kernel)
+int g_force_splits = 0;      // tuning hook: >0 overrides the split-K heuristic of the weight-gradient GEMM
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
 int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, const GemmArgs& g, cudaStream_t st) {
@@ -372,6 +373,7 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
       if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
     }
     g.splits = best;
+    if (g_force_splits > 0) g.splits = g_force_splits;
   }
   g.kb_per_split = ceil_div_i(g.kb_total, g.splits);
   g.splits = ceil_div_i(g.kb_total, g.kb_per_split);
@@ -400,5 +402,6 @@ MLB_API int mlb_linear_dw(void* dW, const void* dout, const void* x, int M, int 
 
 MLB_API void mlb_gemm_force_simt(int on) { g_force_simt = on; }
 MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
+MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }
 
 MLB_DEFINE_ERROR_WORD(gemm)

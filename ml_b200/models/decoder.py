@@ -25,7 +25,9 @@ from ..utils import rng as _rng
 
 class GPT:
     def __init__(self, cfg: Config, B: int, device="cpu", dtype: Optional[torch.dtype] = None,
-                 opt_state: bool = True, alloc_grads: bool = True):
+                 opt_state: bool = True, alloc_grads: bool = True, alloc=None):
+        """alloc(numel, dtype) -> flat tensor: optional allocator for the parameter and gradient buffers (the
+        data-parallel engines pass a symmetric-memory allocator so peers can address them)."""
         cfg.validate()
         self.cfg = cfg
         self.B = B
@@ -37,8 +39,9 @@ class GPT:
         self.np = L.num_params
         dev = self.device
         self.master = torch.zeros(self.np, dtype=torch.float32, device=dev)
-        self.params = self.master if dtype == torch.float32 else torch.zeros(self.np, dtype=dtype, device=dev)
-        self.grads = torch.zeros(self.np, dtype=torch.float32, device=dev) if alloc_grads else None
+        mk = alloc if alloc is not None else (lambda n, dt: torch.empty(n, dtype=dt, device=dev))
+        self.params = self.master if dtype == torch.float32 else mk(self.np, dtype).zero_()
+        self.grads = mk(self.np, torch.float32).zero_() if alloc_grads else None
         self.m = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
         self.v = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
         self.cos, self.sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, dev)

@@ -31,6 +31,7 @@ def lib():
         "mlb_linear_dw": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
         "mlb_gemm_force_simt": [_i32],
         "mlb_gemm_set_max_ctas": [_i32],
+        "mlb_gemm_set_splits": [_i32],
         "mlb_attn_force_simt": [_i32],
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
@@ -203,8 +204,8 @@ def rmsnorm_bwd(dx, dw, dy, x, w, rstd, add=None):
     rows, Cc = x.shape
     L = lib()
     blocks = L.mlb_rmsnorm_bwd_blocks(rows)
-    part = scratch("rms_partial", blocks * Cc, torch.float32, x.device)
-    ticket = scratch("rms_ticket", 1, torch.int32, x.device, zero=True)
+    part = scratch("rms_partial", (blocks + 16) * Cc, torch.float32, x.device)
+    ticket = scratch("rms_ticket", 32, torch.int32, x.device, zero=True)
     _chk(L.mlb_rmsnorm_bwd(_b(dx), _f(dw), _b(dy), _b(x), _b(w), _f(rstd), _b(add) if add is not None else None,
                            rows, Cc, part.data_ptr(), ticket.data_ptr(), _st()), "rmsnorm_bwd")
 

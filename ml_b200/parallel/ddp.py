@@ -26,7 +26,7 @@ from .. import ops
 
 class DDP:
     def __init__(self, model, world: int, accum: int = 1, bf16_reduce: bool = True, comm: str = "nccl",
-                 group=None, overlap_opt: bool = False, opt_hyper: Optional[dict] = None):
+                 group=None, overlap_opt: bool = False, opt_hyper: Optional[dict] = None, rank: int = 0):
         self.model, self.world, self.accum = model, world, max(1, accum)
         self.cuda = model.device.type == "cuda"
         self.bf16_reduce = bool(bf16_reduce) and self.cuda
@@ -47,7 +47,7 @@ class DDP:
         self.fused = None
         if comm == "fused" and self.cuda:
             from .fused import FusedGradEngine
-            self.fused = FusedGradEngine(model, world, group)
+            self.fused = FusedGradEngine(model, world, rank, group)
         model.bucket_hook = self.on_bucket
 
     # ------------------------------------------------------------------
@@ -61,7 +61,7 @@ class DDP:
             return
         m = self.model
         if self.fused is not None:
-            self.fused.bucket(off, n, self.scale, self.hyper, self.t)
+            self.fused.bucket(off, n, self.scale, self.hyper, self.t, self.dev_hyper)
             return
         if self.world == 1:
             if self.overlap_opt:

@@ -26,7 +26,13 @@ class Trainer:
         self.cfg, self.B, self.run = cfg, B, run or RunConfig()
         self.device = torch.device(device)
         self.world, self.rank = world, rank
-        self.model = GPT(cfg, B, self.device)
+        cuda = self.device.type == "cuda"
+        comm = self.run.comm if cuda else "nccl"
+        alloc = None
+        if comm == "fused" and world > 1:
+            from .parallel import symm
+            alloc = lambda n, dt: symm.empty(n, dt, self.device, world)
+        self.model = GPT(cfg, B, self.device, alloc=alloc)
         self.model.init_weights(seed)
         self.vision = None
         if vision is not None:
@@ -37,13 +43,11 @@ class Trainer:
         else:
             self.n_pre = 0
         self.hyper = dict(lr=lr, b1=b1, b2=b2, eps=eps, wd=wd)
-        comm = self.run.comm if (self.device.type == "cuda" and world > 1) else "nccl"
         self.ddp = DDP(self.model, world, self.run.accum, bool(self.run.bf16_reduce), comm, group,
-                       overlap_opt=bool(self.run.ddp_overlap_opt), opt_hyper=self.hyper)
+                       overlap_opt=bool(self.run.ddp_overlap_opt), opt_hyper=self.hyper, rank=rank)
         self.accum = self.ddp.accum
         self.t = 1
         n = B * cfg.T
-        cuda = self.device.type == "cuda"
         self.ids = torch.zeros(self.accum, n, dtype=torch.int32, device=self.device)
         self.tgt = torch.zeros(self.accum, n, dtype=torch.int32, device=self.device)
         self.h_ids = torch.zeros(self.accum, n, dtype=torch.int32, pin_memory=cuda)
