@@ -5,6 +5,9 @@
 // (train/gpt_kernels.cuh: encoder :225-243, rmsnorm :275-458, rope :645-713, swiglu :589-640, CE :1169-1210,
 // adamw :1357-1400) but none of the code is shared with them.
 #include "../common.cuh"
+#include "../no_alloc.h"
+
+#include <cstdio>
 
 MLB_DEFINE_ERROR_WORD(elementwise)
 
@@ -679,3 +682,57 @@ MLB_API int mlb_posembed_grad(float* dpos, const void* dx, long NP, int n_patch,
   LAUNCH_RET;
 }
 
+// ------------------------------------------------------------------ allocation-free RMSNorm backward
+// See csrc/no_alloc.h.  Scratch layout inside the fixed array: (296 + RMS_GROUPS) partial rows of MLB_NOALLOC_RMS_MAX_C
+// floats, then 32 counters.  In host code the array's name only stands for the symbol; its device address is fetched
+// once per device with cudaGetSymbolAddress and that pointer is what the kernel receives.
+namespace {
+constexpr long NOALLOC_ROWS = 296 + RMS_GROUPS;
+constexpr long NOALLOC_FLOATS = NOALLOC_ROWS * MLB_NOALLOC_RMS_MAX_C;
+constexpr int NOALLOC_TICKETS = 32;
+constexpr int NOALLOC_MAX_DEVICES = 64;
+}  // namespace
+static __device__ __align__(256) float g_rms_noalloc_scratch[NOALLOC_FLOATS + NOALLOC_TICKETS];
+
+namespace {
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+thread_local char g_noalloc_msg[256] = "";
+}  // namespace
+
+MLB_API const char* mlb_rmsnorm_bwd_noalloc_error(void) { return g_noalloc_msg; }
+
+MLB_API int mlb_rmsnorm_bwd_noalloc(void* dx, float* dw, const void* dy, const void* x, const void* w, const float* rstd,
+                                    const void* add, long rows, int C, cudaStream_t st) {
+  g_noalloc_msg[0] = 0;
+  if (C < 1 || rows < 1) {
+    snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "rmsnorm_bwd_noalloc: rows=%ld C=%d must be positive", rows, C);
+    return MLB_NOALLOC_ERR_TOO_LARGE;
+  }
+  if (C > MLB_NOALLOC_RMS_MAX_C || (size_t)C * sizeof(float) > 48 * 1024) {
+    snprintf(g_noalloc_msg, sizeof g_noalloc_msg,
+             "rmsnorm_bwd_noalloc: C=%d exceeds the built-in scratch (max C = %d); use mlb_rmsnorm_bwd with caller scratch", C,
+             MLB_NOALLOC_RMS_MAX_C);
+    return MLB_NOALLOC_ERR_TOO_LARGE;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+    snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "rmsnorm_bwd_noalloc: cannot identify the current device (%d, cuda error %d)", dev, (int)e);
+    return MLB_NOALLOC_ERR_SETUP;
+  }
+  if (g_noalloc_ptr[dev] == nullptr) {   // first call on this device: resolve the symbol while that device is current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_rms_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_noalloc_msg, sizeof g_noalloc_msg, "rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed on device %d (cuda error %d)", dev, (int)e);
+      return MLB_NOALLOC_ERR_SETUP;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  float* partial = g_noalloc_ptr[dev];
+  int* ticket = reinterpret_cast<int*>(partial + NOALLOC_FLOATS);
+  // the counters must be zero on entry; the rest of the scratch is fully rewritten before it is read
+  e = cudaMemsetAsync(ticket, 0, NOALLOC_TICKETS * sizeof(int), st);
+  if (e != cudaSuccess) return (int)e;
+  return mlb_rmsnorm_bwd(dx, dw, dy, x, w, rstd, add, rows, C, partial, ticket, st);
+}
