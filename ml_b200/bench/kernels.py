@@ -1,0 +1,173 @@
+"""Kernel micro-benchmarks (counterparts of the reference's gemm_bench / attn_bench / norm_bench programs,
+train/gemm_bench.cu, train/attn_bench.cu, train/norm_bench2.cu).
+
+    python -m ml_b200.bench.kernels gemm  [--M 16384]           tcgen05 GEMMs on the model's shapes vs torch.matmul (cuBLAS)
+    python -m ml_b200.bench.kernels attn  [--B 16 --T 1024]     flash attention fwd / bwd vs torch SDPA
+    python -m ml_b200.bench.kernels norm                        RMSNorm fwd / add+norm / bwd, CE, AdamW, SwiGLU bandwidth
+    python -m ml_b200.bench.kernels once  --case attn|gemm      a few un-timed launches (what an `ncu` capture wraps)
+
+Timing: CUDA events on the launching stream, `--warm` warm-up launches, L2 flushed (256 MB write) before every timed
+launch, median of `--iters`.  Roofline denominators are printed from MEASURED_PEAKS.json when it is present.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..ops import native as nat
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        d = json.load(open(p))
+        return d.get("bf16_tflops", 1590.0), d.get("hbm_gbs", 6650.0), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+def timeit(fn, iters=20, warm=10, flush=True):
+    dev = torch.device("cuda")
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if flush else None
+    ts = []
+    for _ in range(iters):
+        if flush:
+            buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm(a):
+    dev = torch.device("cuda")
+    tf_peak, _, how = peaks()
+    M = a.M
+    shapes = [(3 * a.C, a.C, "qkv"), (a.C, a.C, "o"), (2 * a.I, a.C, "gate|up"), (a.C, a.I, "down"), (a.V, a.C, "lm_head")]
+    print(f"{'shape':<10}{'op':<5}{'ours us':>10}{'TFLOP/s':>10}{'frac of ' + how:>18}{'cuBLAS us':>11}{'TFLOP/s':>10}")
+    for N, K, nm in shapes:
+        x = torch.randn(M, K, device=dev).bfloat16()
+        W = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        dout = torch.randn(M, N, device=dev).bfloat16()
+        dx = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+        dW = torch.zeros(N, K, device=dev)
+        dWb = torch.empty(N, K, device=dev, dtype=torch.bfloat16)
+        fl = 2.0 * M * N * K
+        for op, ours, lib in (("fwd", lambda: nat.linear_fwd(out, x, W), lambda: torch.matmul(x, W.t(), out=out)),
+                              ("dX", lambda: nat.linear_dx(dx, dout, W), lambda: torch.matmul(dout, W, out=dx)),
+                              ("dW", lambda: nat.linear_dw(dW, dout, x), lambda: torch.matmul(dout.t(), x, out=dWb))):
+            t, tl = timeit(ours, a.iters, a.warm), timeit(lib, a.iters, a.warm)
+            print(f"{nm:<10}{op:<5}{t * 1e3:>10.1f}{fl / t / 1e9:>10.0f}{fl / t / 1e9 / tf_peak:>18.2f}{tl * 1e3:>11.1f}{fl / tl / 1e9:>10.0f}")
+        del x, W, out, dout, dx, dW, dWb
+    print("kernel error word:", nat.get_error())
+
+
+def attn_tensors(B, T, H, hd):
+    dev = torch.device("cuda")
+    C = H * hd
+    qkv = torch.randn(B * T, 3 * C, device=dev).bfloat16()
+    out = torch.empty(B * T, C, device=dev, dtype=torch.bfloat16)
+    lse = torch.empty(B, H, T, device=dev)
+    dout = torch.randn(B * T, C, device=dev).bfloat16()
+    dqkv = torch.empty_like(qkv)
+    return qkv, out, lse, dout, dqkv
+
+
+def bench_attn(a):
+    B, T, H, hd = a.B, a.T, a.H, a.hd
+    qkv, out, lse, dout, dqkv = attn_tensors(B, T, H, hd)
+    fl = 4.0 * B * H * T * T * hd / 2      # causal forward
+    t = timeit(lambda: nat.attn_fwd(out, lse, qkv, B, T, H, hd), a.iters, a.warm)
+    tb = timeit(lambda: nat.attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd), a.iters, a.warm)
+    q, k, v = [qkv.view(B, T, 3, H, hd)[:, :, i].permute(0, 2, 1, 3) for i in range(3)]
+    ts = timeit(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True), a.iters, a.warm)
+    print(f"B={B} T={T} H={H} hd={hd}")
+    print(f"fwd  ours {t * 1e3:8.1f} us {fl / t / 1e9:7.0f} TFLOP/s | torch SDPA {ts * 1e3:8.1f} us {fl / ts / 1e9:7.0f} TFLOP/s")
+    print(f"bwd  ours {tb * 1e3:8.1f} us {2.5 * fl / tb / 1e9:7.0f} TFLOP/s (2.5x forward FLOPs)")
+    print("kernel error word:", nat.get_error())
+
+
+def bench_norm(a):
+    dev = torch.device("cuda")
+    _, bw_peak, how = peaks()
+    rows, Cc, V, I = a.M, a.C, a.V, a.I
+    x = torch.randn(rows, Cc, device=dev).bfloat16()
+    w = torch.ones(Cc, device=dev).bfloat16()
+    o, o2 = torch.empty_like(x), torch.empty_like(x)
+    r = torch.empty(rows, device=dev)
+    dw = torch.zeros(Cc, device=dev)
+
+    def rep(name, t, nbytes):
+        print(f"{name:<16}{t * 1e3:9.1f} us {nbytes / t / 1e6:9.0f} GB/s  {nbytes / t / 1e6 / bw_peak:5.2f} of {how} copy bandwidth")
+    rep("rmsnorm_fwd", timeit(lambda: nat.rmsnorm_fwd(o, r, x, w, 1e-5), a.iters, a.warm), 2 * rows * Cc * 2)
+    rep("add_rmsnorm_fwd", timeit(lambda: nat.add_rmsnorm_fwd(o2, o, r, x, x, w, 1e-5), a.iters, a.warm), 4 * rows * Cc * 2)
+    rep("rmsnorm_bwd", timeit(lambda: nat.rmsnorm_bwd(o, dw, x, x, w, r, x), a.iters, a.warm), 4 * rows * Cc * 2)
+    lg = torch.randn(rows, V, device=dev).bfloat16()
+    tg = torch.randint(0, V, (rows,), device=dev, dtype=torch.int32)
+    ls = torch.empty(rows, device=dev)
+    rep("cross_entropy", timeit(lambda: nat.ce_fwd_bwd(ls, lg, tg, 1.0 / rows), a.iters, a.warm), 2 * rows * V * 2)
+    n = 162220800
+    ma, g, m, v = (torch.zeros(n, device=dev) for _ in range(4))
+    p = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+    rep("adamw", timeit(lambda: nat.adamw(ma, p, g, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.5, 1.0), a.iters, a.warm), n * 30)
+    gu = torch.randn(rows, 2 * I, device=dev).bfloat16()
+    so = torch.empty(rows, I, device=dev, dtype=torch.bfloat16)
+    rep("swiglu_fwd", timeit(lambda: nat.swiglu_fwd(so, gu), a.iters, a.warm), rows * 3 * I * 2)
+    rep("swiglu_bwd", timeit(lambda: nat.swiglu_bwd(gu, so, gu), a.iters, a.warm), rows * 5 * I * 2)
+
+
+def once(a):
+    """A handful of launches with no timing: the workload an `ncu` capture wraps (kept small on purpose)."""
+    dev = torch.device("cuda")
+    if a.case == "attn":
+        qkv, out, lse, dout, dqkv = attn_tensors(a.B, a.T, a.H, a.hd)
+        for _ in range(3):
+            nat.attn_fwd(out, lse, qkv, a.B, a.T, a.H, a.hd)
+            nat.attn_bwd(dqkv, dout, qkv, out, lse, a.B, a.T, a.H, a.hd)
+    else:
+        M, N, K = a.M, 3 * a.C, a.C
+        x = torch.randn(M, K, device=dev).bfloat16()
+        W = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        dout = torch.randn(M, N, device=dev).bfloat16()
+        dx = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+        dW = torch.zeros(N, K, device=dev)
+        for _ in range(3):
+            nat.linear_fwd(out, x, W)
+            nat.linear_dx(dx, dout, W)
+            nat.linear_dw(dW, dout, x)
+    torch.cuda.synchronize()
+    print("kernel error word:", nat.get_error())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn", "norm", "once"])
+    ap.add_argument("--case", default="attn", choices=["attn", "gemm"])
+    ap.add_argument("--M", type=int, default=16384)
+    ap.add_argument("--C", type=int, default=768)
+    ap.add_argument("--I", type=int, default=2048)
+    ap.add_argument("--V", type=int, default=50304)
+    ap.add_argument("--B", type=int, default=16)
+    ap.add_argument("--T", type=int, default=1024)
+    ap.add_argument("--H", type=int, default=12)
+    ap.add_argument("--hd", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warm", type=int, default=10)
+    a = ap.parse_args()
+    {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
+
+
+if __name__ == "__main__":
+    main()

@@ -64,26 +64,53 @@ template <int HD>
 struct FwdSmem {
   static constexpr int CH = HD / 64;
   static constexpr int VBUF = (HD == 64) ? 2 : 1;
-  static constexpr int Q = 0;
-  static constexpr int K = Q + CH * TILE_BYTES;                 // 2 slots
+  static constexpr int QBUF = (HD == 64) ? 2 : 1;
+  static constexpr int Q = 0;                                   // QBUF buffers
+  static constexpr int K = Q + QBUF * CH * TILE_BYTES;          // 2 slots
   static constexpr int V = K + 2 * CH * TILE_BYTES;             // VBUF slots
   static constexpr int P = V + VBUF * CH * TILE_BYTES;          // 2 buffers x [128 x 128] bf16
-  static constexpr int RED = P + 2 * 2 * TILE_BYTES;            // 2 x 4 x 128 floats: per-quarter row maxima / sums
-  static constexpr int BAR = RED + 4096;
+  static constexpr int RED = P + 2 * 2 * TILE_BYTES;            // 3 x 4 x 128 floats: per-quarter row maxima (x2) / sums
+  static constexpr int BAR = RED + 6144;
   static constexpr int TOTAL = BAR + 256 + 1024;
+};
+
+// Work item = one 128-query tile of one (sample, head).  Items are numbered heaviest first (most key blocks) and dealt
+// round-robin to the persistent CTAs; both warp roles walk the same sequence.
+struct FwdItem {
+  int w, li, qt, b, h, nkb;
+  bool valid;
+  __device__ __forceinline__ void set(int w_, int li_, int total, int nq, int BH, int H) {
+    w = w_; li = li_; valid = w_ < total;
+    if (valid) {
+      qt = nq - 1 - w_ / BH;
+      const int bh = w_ % BH;
+      b = bh / H; h = bh % H;
+      nkb = qt + 1;
+    } else {
+      qt = b = h = 0; nkb = 1;
+    }
+  }
+};
+struct FwdCursor {   // position of one key block in the flattened (item, block) sequence of this CTA
+  FwdItem it;
+  int j;
+  __device__ __forceinline__ void advance(int total, int nq, int BH, int H, int stride) {
+    if (!it.valid) return;
+    if (++j >= it.nkb) { it.set(it.w + stride, it.li + 1, total, nq, BH, H); j = 0; }
+  }
 };
 
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
   using S = FwdSmem<HD>;
-  constexpr int CH = HD / 64, OC = HD / 4, VBUF = S::VBUF;
+  constexpr int CH = HD / 64, OC = HD / 4, VBUF = S::VBUF, QBUF = S::QBUF;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + S::BAR);
-  uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_p = bars + 7, *bar_o = bars + 9;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 11);
-  volatile int* s_abort = (volatile int*)(bars + 12);   // set by the first wait that runs out; later waits are skipped
+  uint64_t *bar_q = bars, *bar_k = bars + 2, *bar_v = bars + 4, *bar_s = bars + 6, *bar_p = bars + 8, *bar_o = bars + 10;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  volatile int* s_abort = (volatile int*)(bars + 13);   // set by the first wait that runs out; later waits are skipped
   float* s_red = (float*)(smem + S::RED);
   {   // an earlier CTA already gave up on a wait: do not queue more 4 s waits behind it (CTA-uniform decision)
     __shared__ int s_skip;
@@ -93,17 +120,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
   }
 
   const int nq = (a.T + 127) / 128;
-  const int qt = nq - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int q0 = qt * 128;
+  const int BH = a.B * a.H, total = nq * BH, stride = gridDim.x;
   const int C = a.H * HD;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = b * a.T;
-  const int nkb = qt + 1;
 
   if (tid == 0) {
-    tc::mbar_init(bar_q, 1);
     for (int i = 0; i < 2; i++) {
-      tc::mbar_init(&bar_k[i], 1); tc::mbar_init(&bar_v[i], 1); tc::mbar_init(&bar_s[i], 1);
+      tc::mbar_init(&bar_q[i], 1); tc::mbar_init(&bar_k[i], 1); tc::mbar_init(&bar_v[i], 1); tc::mbar_init(&bar_s[i], 1);
       tc::mbar_init(&bar_p[i], ATT_SOFTMAX_WARPS); tc::mbar_init(&bar_o[i], 1);
     }
     *s_abort = 0;
@@ -126,59 +149,116 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
 
   if (warp == ATT_SOFTMAX_WARPS) {
     // ---------------------------------------------------------------- control warp
+    // Everything is indexed by g, the running number of the key block in this CTA's flattened sequence:
+    // K slot / score buffer / P buffer / O buffer = g & 1, V slot = g % VBUF, Q buffer = (local item number) % QBUF.
     if (lane == 0) {
       constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);
-      const uint32_t sQ = tc::smem_u32(smem + S::Q);
-      auto load_k = [&](int j) {
-        const int sl = j & 1;
+      auto load_q = [&](const FwdItem& it) {
+        const int qb = it.li % QBUF;
+        tc::mbar_expect_tx(&bar_q[qb], CH * TILE_BYTES);
+        for (int c = 0; c < CH; c++)
+          tc::tma_load_2d(smem + S::Q + (qb * CH + c) * TILE_BYTES, &tm, &bar_q[qb], it.h * HD + c * 64, it.b * a.T + it.qt * 128);
+      };
+      auto load_k = [&](const FwdCursor& c, int g) {
+        const int sl = g & 1;
         tc::mbar_expect_tx(&bar_k[sl], CH * TILE_BYTES);
-        for (int c = 0; c < CH; c++)
-          tc::tma_load_2d(smem + S::K + (sl * CH + c) * TILE_BYTES, &tm, &bar_k[sl], C + h * HD + c * 64, row0 + j * 128);
+        for (int x = 0; x < CH; x++)
+          tc::tma_load_2d(smem + S::K + (sl * CH + x) * TILE_BYTES, &tm, &bar_k[sl], C + c.it.h * HD + x * 64, c.it.b * a.T + c.j * 128);
       };
-      auto load_v = [&](int j) {
-        const int sl = j % VBUF;
+      auto load_v = [&](const FwdCursor& c, int g) {
+        const int sl = g % VBUF;
         tc::mbar_expect_tx(&bar_v[sl], CH * TILE_BYTES);
-        for (int c = 0; c < CH; c++)
-          tc::tma_load_2d(smem + S::V + (sl * CH + c) * TILE_BYTES, &tm, &bar_v[sl], 2 * C + h * HD + c * 64, row0 + j * 128);
+        for (int x = 0; x < CH; x++)
+          tc::tma_load_2d(smem + S::V + (sl * CH + x) * TILE_BYTES, &tm, &bar_v[sl], 2 * C + c.it.h * HD + x * 64, c.it.b * a.T + c.j * 128);
       };
-      auto issue_s = [&](int j) {   // S(j) = Q K_j^T into score buffer j & 1
-        const uint32_t sK = tc::smem_u32(smem + S::K + (j & 1) * CH * TILE_BYTES);
+      auto issue_s = [&](const FwdCursor& c, int g) {   // S(g) = Q K^T into score buffer g & 1
+        const uint32_t sQ = tc::smem_u32(smem + S::Q + (c.it.li % QBUF) * CH * TILE_BYTES);
+        const uint32_t sK = tc::smem_u32(smem + S::K + (g & 1) * CH * TILE_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(tmem + (j & 1) * 128, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(tmem + (g & 1) * 128, desc_k(sQ, ks), desc_k(sK, ks), idesc_s, ks > 0);
       };
-      tc::mbar_expect_tx(bar_q, CH * TILE_BYTES);
-      for (int c = 0; c < CH; c++) tc::tma_load_2d(smem + S::Q + c * TILE_BYTES, &tm, bar_q, h * HD + c * 64, row0 + q0);
-      load_k(0);
-      if (nkb > 1) load_k(1);
-      load_v(0);
-      if (VBUF == 2 && nkb > 1) load_v(1);
-      if (wait(bar_q, 0, 10) && wait(&bar_k[0], 0, 11)) { tc::tc_fence_after(); issue_s(0); }
+      FwdCursor c0, c1, c2;
+      c0.it.set(blockIdx.x, 0, total, nq, BH, a.H); c0.j = 0;
+      c1 = c0; c1.advance(total, nq, BH, a.H, stride);
+      c2 = c1; c2.advance(total, nq, BH, a.H, stride);
+      int pending_q_w = -1, pending_q_li = 0;   // Q tile to prefetch as soon as its buffer's previous S MMAs are known complete
+      // ---- prologue: first two key blocks
+      load_q(c0.it);
+      load_k(c0, 0);
+      load_v(c0, 0);
+      if (c1.it.valid) {
+        load_k(c1, 1);
+        if (VBUF == 2) load_v(c1, 1);
+        if (c1.it.li != c0.it.li && QBUF == 2) load_q(c1.it);
+      }
+      if (wait(&bar_q[0], 0, 10) && wait(&bar_k[0], 0, 11)) { tc::tc_fence_after(); issue_s(c0, 0); }
       tc::mma_commit(&bar_s[0]);
-      if (nkb > 1) {
-        if (wait(&bar_k[1], 0, 11)) { tc::tc_fence_after(); issue_s(1); }
+      if (c1.it.valid) {
+        bool okq = true;
+        if (c1.it.li != c0.it.li) {
+          if (QBUF == 1) {   // single Q buffer: S(0) must be done before the next item's Q may land
+            okq = wait(&bar_s[0], 0, 12);
+            if (okq) load_q(c1.it);
+          }
+          okq = okq && wait(&bar_q[c1.it.li % QBUF], (c1.it.li / QBUF) & 1, 10);
+        }
+        if (okq && wait(&bar_k[1], 0, 11)) { tc::tc_fence_after(); issue_s(c1, 1); }
         tc::mma_commit(&bar_s[1]);
       }
-      for (int j = 0; j < nkb; j++) {
-        const int sl = j & 1, ph = (j >> 1) & 1;
-        // (a) S(j) is complete: its K slot can take K(j+2)
-        if (wait(&bar_s[sl], ph, 12) && j + 2 < nkb) load_k(j + 2);
-        // (b) P(j) written (and S(j) fully read) -> O_blk(j) = P_j V_j
-        if (wait(&bar_p[sl], ph, 13) && wait(&bar_v[j % VBUF], (j / VBUF) & 1, 14)) {
+      int q_loaded_li = c1.it.valid ? c1.it.li : c0.it.li;   // highest local item whose Q load has been issued
+      if (QBUF == 2) {   // the item after the last loaded one can be prefetched once its buffer is free
+        FwdItem nx;
+        nx.set(blockIdx.x + (q_loaded_li + 1) * stride, q_loaded_li + 1, total, nq, BH, a.H);
+        if (nx.valid) { pending_q_w = nx.w; pending_q_li = nx.li; }
+      }
+      for (int g = 0; c0.it.valid; g++) {
+        const int sl = g & 1, ph = (g >> 1) & 1;
+        // (a) S(g) is complete (so is every earlier S): K slot g&1 can take the key block two ahead, and a pending Q
+        //     prefetch whose buffer was last read by an item that ended at or before g can go out
+        const bool s_done = wait(&bar_s[sl], ph, 12);
+        if (s_done && c2.it.valid) load_k(c2, g + 2);
+        if (s_done && QBUF == 2 && pending_q_w >= 0 && pending_q_li - 2 < c0.it.li + (c0.j == c0.it.nkb - 1 ? 1 : 0)) {
+          // buffer (pending_q_li & 1) was used by local item pending_q_li - 2, all of whose blocks are <= g here
+          FwdItem nx;
+          nx.set(pending_q_w, pending_q_li, total, nq, BH, a.H);
+          load_q(nx);
+          q_loaded_li = pending_q_li;
+          pending_q_w = -1;
+        }
+        // (b) P(g) written (and S(g) fully read) -> O_blk(g) = P V
+        if (wait(&bar_p[sl], ph, 13) && wait(&bar_v[g % VBUF], (g / VBUF) & 1, 14)) {
           tc::tc_fence_after();
           const uint32_t sP = tc::smem_u32(smem + S::P + sl * 2 * TILE_BYTES);
-          const uint32_t sV = tc::smem_u32(smem + S::V + (j % VBUF) * CH * TILE_BYTES);
+          const uint32_t sV = tc::smem_u32(smem + S::V + (g % VBUF) * CH * TILE_BYTES);
 #pragma unroll
           for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_o + sl * HD, desc_k(sP, ks), desc_mn(sV, ks), idesc_o, ks > 0);
         }
         tc::mma_commit(&bar_o[sl]);
-        // (c) score buffer j&1 is free: S(j+2)
-        if (j + 2 < nkb) {
-          if (wait(&bar_k[sl], ((j + 2) >> 1) & 1, 15)) { tc::tc_fence_after(); issue_s(j + 2); }
+        // (c) score buffer g&1 is free: S(g+2), possibly the first block of a later item
+        if (c2.it.valid) {
+          bool okq = true;
+          if (c2.j == 0) {
+            if (c2.it.li > q_loaded_li) {
+              // not prefetched (single Q buffer, or the prefetch condition never became true): the buffer's previous user
+              // ends at block g+1, whose S was issued in the previous iteration
+              okq = wait(&bar_s[(g + 1) & 1], ((g + 1) >> 1) & 1, 12);
+              if (okq) { load_q(c2.it); q_loaded_li = c2.it.li; if (pending_q_li == c2.it.li) pending_q_w = -1; }
+            }
+            okq = okq && wait(&bar_q[c2.it.li % QBUF], (c2.it.li / QBUF) & 1, 10);
+            if (QBUF == 2 && pending_q_w < 0) {
+              FwdItem nx;
+              nx.set(c2.it.w + stride, c2.it.li + 1, total, nq, BH, a.H);
+              if (nx.valid && nx.li > q_loaded_li) { pending_q_w = nx.w; pending_q_li = nx.li; }
+            }
+          }
+          if (okq && wait(&bar_k[sl], ((g + 2) >> 1) & 1, 15)) { tc::tc_fence_after(); issue_s(c2, g + 2); }
           tc::mma_commit(&bar_s[sl]);
         }
-        // (d) V slot free once P_j V_j has completed
-        if (j + VBUF < nkb && wait(&bar_o[sl], ph, 16)) load_v(j + VBUF);
+        // (d) V slot free once P V of block g has completed
+        const FwdCursor& cv = (VBUF == 2) ? c2 : c1;
+        if (cv.it.valid && wait(&bar_o[sl], ph, 16)) load_v(cv, g + VBUF);
+        c0 = c1; c1 = c2; c2.advance(total, nq, BH, a.H, stride);
       }
     }
   } else {
@@ -186,98 +266,105 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
     const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
     const float sl2 = a.scale * LOG2E;
-    const int qrow = q0 + row;
-    float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-    float o[OC];
+    int g = 0;
+    FwdItem it;
+    it.set(blockIdx.x, 0, total, nq, BH, a.H);
+    for (; it.valid; it.set(it.w + stride, it.li + 1, total, nq, BH, a.H)) {
+      const int qrow = it.qt * 128 + row;
+      float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+      float o[OC];
 #pragma unroll
-    for (int i = 0; i < OC; i++) o[i] = 0.f;
-    auto fold = [&](int jb, float alpha) {   // O = O * alpha + (P V) of block jb
-      if (OC == 16) {
-        uint32_t ro[16];
-        tc::tmem_ld16(t_o + (jb & 1) * HD + lane_addr + cq * 16, ro);
-        tc::tmem_ld_wait();
+      for (int i = 0; i < OC; i++) o[i] = 0.f;
+      auto fold = [&](int gb, float alpha) {   // O = O * alpha + (P V) of block gb
+        if (OC == 16) {
+          uint32_t ro[16];
+          tc::tmem_ld16(t_o + (gb & 1) * HD + lane_addr + cq * 16, ro);
+          tc::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; i++) o[i] = o[i] * alpha + __uint_as_float(ro[i]);
-      } else {
-        uint32_t ro[32];
-        tc::tmem_ld32(t_o + (jb & 1) * HD + lane_addr + cq * 32, ro);
-        tc::tmem_ld_wait();
+          for (int i = 0; i < 16; i++) o[i] = o[i] * alpha + __uint_as_float(ro[i]);
+        } else {
+          uint32_t ro[32];
+          tc::tmem_ld32(t_o + (gb & 1) * HD + lane_addr + cq * 32, ro);
+          tc::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i++) o[i % OC] = o[i % OC] * alpha + __uint_as_float(ro[i]);
-      }
-      tc::tc_fence_before();
-    };
-    for (int j = 0; j < nkb; j++) {
-      const int sl = j & 1, ph = (j >> 1) & 1;
-      const int kc0 = j * 128 + cq * 32;
-      wait(&bar_s[sl], ph, 17);
-      tc::tc_fence_after();
-      uint32_t r[32];
-      tc::tmem_ld32(tmem + sl * 128 + lane_addr + cq * 32, r);
-      tc::tmem_ld_wait();
-      float mx = -INFINITY;
-      if (j == qt) {
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-          if (kc0 + i > qrow) r[i] = 0xff800000u;   // -inf: masked by causality
-          mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i++) o[i % OC] = o[i % OC] * alpha + __uint_as_float(ro[i]);
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
-      }
-      float* red = s_red + sl * 512;
-      red[cq * 128 + row] = mx;
-      named_bar_sync(1 + lg, 128);
-      mx = fmaxf(fmaxf(red[row], red[128 + row]), fmaxf(red[256 + row], red[384 + row]));
-      const float m_new = fmaxf(m, mx * sl2);   // finite: key 0 is visible to every query
-      const float alpha = exp2f(m - m_new);     // exp2(-inf) = 0 on the first block
-      float rs = 0.f;
-      uint8_t* pbuf = smem + S::P + sl * 2 * TILE_BYTES;
-#pragma unroll
-      for (int v8 = 0; v8 < 4; v8++) {
-        float pf[8];
-#pragma unroll
-        for (int x = 0; x < 8; x++) {
-          pf[x] = exp2f(__uint_as_float(r[v8 * 8 + x]) * sl2 - m_new);
-          rs += pf[x];
-        }
-        uint4 pk;
-        pk.x = pack_bf16(pf[0], pf[1]); pk.y = pack_bf16(pf[2], pf[3]); pk.z = pack_bf16(pf[4], pf[5]); pk.w = pack_bf16(pf[6], pf[7]);
-        *reinterpret_cast<uint4*>(pbuf + sw_off(row, cq * 32 + v8 * 8)) = pk;
-      }
-      tc::fence_async_smem();
-      tc::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&bar_p[sl]);
-      l = l * alpha + rs;
-      m = m_new;
-      if (j > 0) {   // fold in the previous block, whose P V product had a whole softmax to complete
-        wait(&bar_o[(j - 1) & 1], ((j - 1) >> 1) & 1, 18);
+        tc::tc_fence_before();
+      };
+      for (int j = 0; j < it.nkb; j++, g++) {
+        const int sl = g & 1, ph = (g >> 1) & 1;
+        const int kc0 = j * 128 + cq * 32;
+        wait(&bar_s[sl], ph, 17);
         tc::tc_fence_after();
-        fold(j - 1, alpha_prev);
-      }
-      alpha_prev = alpha;
-    }
-    wait(&bar_o[(nkb - 1) & 1], ((nkb - 1) >> 1) & 1, 19);
-    tc::tc_fence_after();
-    fold(nkb - 1, alpha_prev);
-    // combine the four partial row sums, normalise, store
-    float* red = s_red + (nkb & 1) * 512;
-    red[cq * 128 + row] = l;
-    named_bar_sync(1 + lg, 128);
-    const float L = red[row] + red[128 + row] + red[256 + row] + red[384 + row];
-    if (!*s_abort && qrow < a.T) {
-      const float inv = 1.f / L;
-      bf16* dst = a.out + ((size_t)(row0 + qrow)) * C + h * HD + cq * OC;
+        uint32_t r[32];
+        tc::tmem_ld32(tmem + sl * 128 + lane_addr + cq * 32, r);
+        tc::tmem_ld_wait();
+        float mx = -INFINITY;
+        if (j == it.qt) {
 #pragma unroll
-      for (int v8 = 0; v8 < OC / 8; v8++) {
-        uint4 pk;
-        pk.x = pack_bf16(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv); pk.y = pack_bf16(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
-        pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
+          for (int i = 0; i < 32; i++) {
+            if (kc0 + i > qrow) r[i] = 0xff800000u;   // -inf: masked by causality
+            mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+        float* red = s_red + sl * 512;
+        red[cq * 128 + row] = mx;
+        named_bar_sync(1 + lg, 128);
+        mx = fmaxf(fmaxf(red[row], red[128 + row]), fmaxf(red[256 + row], red[384 + row]));
+        const float m_new = fmaxf(m, mx * sl2);   // finite: key 0 is visible to every query
+        const float alpha = exp2f(m - m_new);     // exp2(-inf) = 0 on the first block
+        float rs = 0.f;
+        uint8_t* pbuf = smem + S::P + sl * 2 * TILE_BYTES;
+#pragma unroll
+        for (int v8 = 0; v8 < 4; v8++) {
+          float pf[8];
+#pragma unroll
+          for (int x = 0; x < 8; x++) {
+            pf[x] = exp2f(__uint_as_float(r[v8 * 8 + x]) * sl2 - m_new);
+            rs += pf[x];
+          }
+          uint4 pk;
+          pk.x = pack_bf16(pf[0], pf[1]); pk.y = pack_bf16(pf[2], pf[3]); pk.z = pack_bf16(pf[4], pf[5]); pk.w = pack_bf16(pf[6], pf[7]);
+          *reinterpret_cast<uint4*>(pbuf + sw_off(row, cq * 32 + v8 * 8)) = pk;
+        }
+        tc::fence_async_smem();
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&bar_p[sl]);
+        l = l * alpha + rs;
+        m = m_new;
+        if (j > 0) {   // fold in the previous block, whose P V product had a whole softmax to complete
+          wait(&bar_o[(g - 1) & 1], ((g - 1) >> 1) & 1, 18);
+          tc::tc_fence_after();
+          fold(g - 1, alpha_prev);
+        }
+        alpha_prev = alpha;
       }
-      if (cq == 0) a.lse[((size_t)b * a.H + h) * a.T + qrow] = (m + log2f(L)) * LN2;
+      wait(&bar_o[(g - 1) & 1], ((g - 1) >> 1) & 1, 19);
+      tc::tc_fence_after();
+      fold(g - 1, alpha_prev);
+      // combine the four partial row sums (third exchange buffer: the max buffers may already be in use by a fast warp
+      // of the next item), normalise, store
+      float* red = s_red + 1024;
+      named_bar_sync(1 + lg, 128);   // everyone in the row group has finished reading the previous item's sums
+      red[cq * 128 + row] = l;
+      named_bar_sync(1 + lg, 128);
+      const float L = red[row] + red[128 + row] + red[256 + row] + red[384 + row];
+      if (!*s_abort && qrow < a.T) {
+        const float inv = 1.f / L;
+        bf16* dst = a.out + ((size_t)(it.b * a.T + qrow)) * C + it.h * HD + cq * OC;
+#pragma unroll
+        for (int v8 = 0; v8 < OC / 8; v8++) {
+          uint4 pk;
+          pk.x = pack_bf16(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv); pk.y = pack_bf16(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
+          pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
+        }
+        if (cq == 0) a.lse[((size_t)it.b * a.H + it.h) * a.T + qrow] = (m + log2f(L)) * LN2;
+      }
     }
   }
   tc::tc_fence_before();
@@ -806,7 +893,12 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
     const CUtensorMap* tm = mlb_tmap_cached(qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, 64);
     if (!tm) return -2;
     AttnArgs a{B, T, H, hd, scale, (bf16*)out, lse, nullptr, nullptr, nullptr};
-    dim3 grid((T + 127) / 128, H, B);
+    const long items = (long)((T + 127) / 128) * H * B;
+    int sms = 0, devid = 0;
+    cudaGetDevice(&devid);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devid);
+    if (sms <= 0) sms = 148;
+    dim3 grid((unsigned)(items < sms ? items : sms));   // persistent: one CTA per SM walks its share of the tiles
     if (hd == 64) {
       static int once = set_smem(attn_fwd_tc_kernel<64>, FwdSmem<64>::TOTAL);
       (void)once;

@@ -161,6 +161,21 @@ __global__ void __launch_bounds__(512) ddp_bucket_kernel(const BucketArgs a) {
   }
 }
 
+// All-gather by peer loads: dst[w*chunk_bytes ...] = shard of rank w, for every w; 16-byte vectors, system-scope loads.
+// No barrier is needed here: the producer of the shards (the reduce-scatter + AdamW kernel of the previous step) ends
+// with a barrier across all ranks, and this kernel is ordered after it on the same stream.
+__global__ void __launch_bounds__(512) allgather_pull_kernel(uint4* __restrict__ dst, const uint4* const* __restrict__ src,
+                                                             long chunk_vec, int world) {
+  const long total = chunk_vec * world;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int w = (int)(i / chunk_vec);
+    const long j = i - (long)w * chunk_vec;
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src[w] + j) : "memory");
+    dst[i] = v;
+  }
+}
+
 // Test hook: waits (bounded) on a flag that nothing sets, to exercise the timeout path on one GPU.
 __global__ void flag_timeout_probe_kernel(const int* flag, int epoch, long limit_ns, int* result) {
   if (threadIdx.x == 0 && blockIdx.x == 0) *result = wait_flag(flag, epoch, limit_ns, 0x7777) ? 1 : 2;
@@ -189,6 +204,18 @@ MLB_API int mlb_ddp_bucket(const void* grads_ptrs, const void* params_ptrs, cons
   if (ctas < 1) ctas = 32;
   const int grid = (int)(want < ctas ? want : ctas);
   ddp_bucket_kernel<<<grid, 512, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// dst (local) <- concatenation of the `world` shards whose device pointers are in src_ptrs (device array); every shard
+// is chunk_bytes long (a multiple of 16).
+MLB_API int mlb_allgather_pull(void* dst, const void* src_ptrs, long chunk_bytes, int world, int ctas, cudaStream_t st) {
+  if ((chunk_bytes & 15) != 0 || world < 1) return -1;
+  const long chunk_vec = chunk_bytes / 16;
+  long want = (chunk_vec * world + 511) / 512;
+  if (want < 1) want = 1;
+  if (ctas < 1) ctas = 32;
+  allgather_pull_kernel<<<(int)(want < ctas ? want : ctas), 512, 0, st>>>((uint4*)dst, (const uint4* const*)src_ptrs, chunk_vec, world);
   return (int)cudaGetLastError();
 }
 

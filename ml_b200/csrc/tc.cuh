@@ -1,4 +1,4 @@
-// Blackwell (sm_100a) primitives as inline PTX: mbarrier, TMA tiled loads (never cluster-multicast),
+// Blackwell (sm_100a) primitives as inline PTX: mbarrier, TMA tiled loads (each CTA fetches its own tiles),
 // tcgen05 MMA / TMEM alloc / TMEM load, and the shared-memory + instruction descriptors they take.
 #pragma once
 #include "common.cuh"

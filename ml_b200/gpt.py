@@ -279,6 +279,10 @@ def _train_loop(argv, ddp):
         tr.ddp.hyper["lr"] = tr.hyper["lr"]
         tr.step()
         pipe.release(step)
+        hb = os.environ.get("ENTROPY_HEARTBEAT_DIR")
+        if hb:
+            with open(os.path.join(hb, f"rank_{rank}"), "w") as f:
+                f.write(str(step))
         if world > 1:
             # the file is striped over ranks: skip the windows the other ranks consume
             loader.pos = (loader.pos + (world - 1) * win) % max(1, loader.ntok - win - 1)

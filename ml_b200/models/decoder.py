@@ -25,9 +25,11 @@ from ..utils import rng as _rng
 
 class GPT:
     def __init__(self, cfg: Config, B: int, device="cpu", dtype: Optional[torch.dtype] = None,
-                 opt_state: bool = True, alloc_grads: bool = True, alloc=None):
+                 opt_state: bool = True, alloc_grads: bool = True, alloc=None, sharded: bool = False):
         """alloc(numel, dtype) -> flat tensor: optional allocator for the parameter and gradient buffers (the
-        data-parallel engines pass a symmetric-memory allocator so peers can address them)."""
+        data-parallel engines pass a symmetric-memory allocator so peers can address them).
+        sharded=True: no flat master / params / grads / m / v are allocated here; a sharding engine
+        (ml_b200.parallel.fsdp) owns the storage and serves parameter / gradient views through `self.res`."""
         cfg.validate()
         self.cfg = cfg
         self.B = B
@@ -38,12 +40,18 @@ class GPT:
         self.layout = L = DecoderLayout(cfg)
         self.np = L.num_params
         dev = self.device
-        self.master = torch.zeros(self.np, dtype=torch.float32, device=dev)
-        mk = alloc if alloc is not None else (lambda n, dt: torch.empty(n, dtype=dt, device=dev))
-        self.params = self.master if dtype == torch.float32 else mk(self.np, dtype).zero_()
-        self.grads = mk(self.np, torch.float32).zero_() if alloc_grads else None
-        self.m = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
-        self.v = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
+        self.sharded = sharded
+        self.res = None          # optional view resolver: res.param(off, shape) / res.grad(off, shape)
+        self.pre_hook = None     # optional pre_hook(unit_name, phase) called before a unit's parameters are first used
+        if sharded:
+            self.master = self.params = self.grads = self.m = self.v = None
+        else:
+            self.master = torch.zeros(self.np, dtype=torch.float32, device=dev)
+            mk = alloc if alloc is not None else (lambda n, dt: torch.empty(n, dtype=dt, device=dev))
+            self.params = self.master if dtype == torch.float32 else mk(self.np, dtype).zero_()
+            self.grads = mk(self.np, torch.float32).zero_() if alloc_grads else None
+            self.m = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
+            self.v = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
         self.cos, self.sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, dev)
         self._alloc_acts(B)
         # hooks: called as hook(name, offset, numel) when a gradient bucket is final
@@ -84,18 +92,29 @@ class GPT:
         self.datty = e(BT, C)
 
     def P(self, off, *shape):
+        if self.res is not None:
+            return self.res.param(off, shape)
         n = math.prod(shape)
         return self.params[off:off + n].view(*shape)
 
     def G(self, off, *shape):
+        if self.res is not None:
+            return self.res.grad(off, shape)
         n = math.prod(shape)
         return self.grads[off:off + n].view(*shape)
+
+    def _pre(self, unit, phase):
+        if self.pre_hook is not None:
+            self.pre_hook(unit, phase)
 
     # ------------------------------------------------------------------ init
     def init_weights(self, seed: int = 1234):
         """Host xorshift64 / Box-Muller stream consumed in buffer order; std 0.02; o- and down-projections
         scaled by 1/sqrt(2L); norm weights 1 without consuming the stream (train/gpt.cu:775-806)."""
         h = _rng.init_decoder(self.layout, seed)
+        if self.sharded:
+            self.res.load_full(h)
+            return
         self.master.copy_(h.to(self.device))
         self.sync_params()
 
@@ -116,9 +135,11 @@ class GPT:
         assert B <= self.B
         sl = lambda t: t[:BT]
         x0 = sl(self.x0)
+        self._pre("wte", "fwd")
         ops.embed_fwd(x0, self.P(Lo.off_wte, c.V, C), ids)
         if prefix is not None and n_pre > 0:
             ops.set_prefix(x0, prefix, B, T, n_pre)
+        self._pre("layer0" if c.L > 0 else "head", "fwd")
         ops.rmsnorm_fwd(sl(self.ln1[0]), sl(self.rstd1[0]), x0, self.P(Lo.layer(0).ln1, C), c.eps)
         resid_in = x0
         for l in range(c.L):
@@ -137,6 +158,8 @@ class GPT:
             ops.linear_fwd(sl(self.gu[l]), sl(self.ln2[l]), self.P(o.gate, 2 * I, C))
             ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
             ops.linear_fwd(proj, sl(self.sw[l]), self.P(o.down, C, I))
+            # the fused add + norm uses the NEXT unit's norm weight: that unit has to be present from here on
+            self._pre(f"layer{l + 1}" if l + 1 < c.L else "head", "fwd")
             if l + 1 < c.L:
                 nw, nout, nrstd = self.P(Lo.layer(l + 1).ln1, C), sl(self.ln1[l + 1]), sl(self.rstd1[l + 1])
             else:
@@ -160,13 +183,14 @@ class GPT:
         T, C, I, H, hd, V = c.T, c.C, c.I, c.H, c.hd, c.V
         BT = B * T
         sl = lambda t: t[:BT]
-        if zero:
+        if zero and self.grads is not None:
             self.grads.zero_()
         valid = valid_tokens if valid_tokens is not None else BT - B * n_pre
         logits = self.logits[:BT]
         ops.ce_fwd_bwd(sl(self.losses), logits, tgt, 1.0 / float(valid))
         self._mark("B_ce")
         dln, dresid, dresid1 = sl(self.dln), sl(self.dresid), sl(self.dresid1)
+        self._pre("head", "bwd")
         ops.linear_dw(self.G(Lo.off_lm, V, C), logits, sl(self.lnf_out))
         ops.linear_dx(dln, logits, self.P(Lo.off_lm, V, C))
         self._mark("B_lmhead")
@@ -177,6 +201,7 @@ class GPT:
         self._hook("lnf", Lo.off_lnf, C)
         for l in range(c.L - 1, -1, -1):
             o = Lo.layer(l)
+            self._pre(f"layer{l}", "bwd")
             dsw, dgu, dqkv, datty = sl(self.dsw), sl(self.dgu), sl(self.dqkv), sl(self.datty)
             ops.linear_dw(self.G(o.down, C, I), dresid, sl(self.sw[l]))
             ops.linear_dx(dsw, dresid, self.P(o.down, C, I))
@@ -202,6 +227,7 @@ class GPT:
             ops.rmsnorm_bwd(dresid, self.G(o.ln1, C), dln, x_in, self.P(o.ln1, C), sl(self.rstd1[l]), dresid1)
             self._mark("B_norm")
             self._hook(f"layer{l}", Lo.layer_base(l), Lo.layer_stride)
+        self._pre("wte", "bwd")
         ops.embed_bwd(self.G(Lo.off_wte, V, C), dresid, ids, T, n_pre)
         self._hook("wte", Lo.off_wte, V * C)
 

@@ -1,0 +1,77 @@
+"""NVLink-native communication for the FSDP engine (no NCCL on these paths):
+
+* all-gather = `mlb_allgather_pull`: every rank pulls all shards of a unit from its peers' parameter-shard buffers by
+  peer loads into its local gather slot, prefetched one unit ahead on the communication stream;
+* reduce-scatter ⊕ mean ⊕ sharded AdamW = `mlb_ddp_bucket` with bcast = 0: one kernel per unit that sums this rank's
+  shard of every rank's fp32 gradient slot over peer loads and updates master / m / v / the bf16 shard in place.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ..ops import native
+from .fused import MAX_BUCKETS
+from .symm import PeerTable, empty as symm_empty
+
+
+class FusedFSDP:
+    def __init__(self, fs, gather_ctas: int = 32, rs_ctas: int = 32, spin_limit_s: float = 2.0):
+        self.fs = fs
+        self.gather_ctas, self.rs_ctas, self.spin_limit_s = gather_ctas, rs_ctas, spin_limit_s
+        dev, W, r = fs.dev, fs.world, fs.rank
+        L = native.lib()
+        L.mlb_ddp_bucket.argtypes = [C.c_void_p] * 8 + [C.c_long, C.c_long] + [C.c_int] * 5 + [C.c_float] * 8 + \
+                                    [C.c_void_p, C.c_int, C.c_double, C.c_void_p]
+        L.mlb_ddp_bucket.restype = C.c_int
+        L.mlb_allgather_pull.argtypes = [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_void_p]
+        L.mlb_allgather_pull.restype = C.c_int
+        assert len(fs.units) <= MAX_BUCKETS
+        maxw = L.mlb_comm_max_world()
+        self.flags = symm_empty(2 * MAX_BUCKETS * maxw, torch.int32, dev, W)
+        self.flags.zero_()
+        self.t_flags = PeerTable(self.flags, W, fs.group)
+        self.t_pshard = PeerTable(fs.pshard, W, fs.group)
+        self.t_dslot = [PeerTable(fs.dslot[i], W, fs.group) for i in range(2)]
+        self.done = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
+        self.epoch = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
+        es = fs.pshard.element_size()
+        # per unit: pointers to every rank's parameter shard of that unit (all-gather sources) and the pre-offset
+        # pointer that lets the bucket kernel index this rank's shard with absolute element positions
+        self.src_tables, self.param_tables = [], []
+        base = self.t_pshard.table.cpu()
+        for i, u in enumerate(fs.units):
+            self.src_tables.append((base + fs.shard_off[i] * es).to(dev))
+            self.param_tables.append((base + (fs.shard_off[i] - r * u.chunk) * es).to(dev))
+        if W > 1:
+            import torch.distributed as dist
+            torch.cuda.synchronize()
+            dist.barrier(group=fs.group)
+
+    def gather(self, ui: int, slot: int):
+        fs = self.fs
+        u = fs.units[ui]
+        rc = native.lib().mlb_allgather_pull(fs.gslot[slot].data_ptr(), self.src_tables[ui].data_ptr(),
+                                             u.chunk * fs.pshard.element_size(), fs.world, self.gather_ctas,
+                                             torch.cuda.current_stream().cuda_stream)
+        native.LAUNCHES += 1
+        if rc != 0:
+            raise RuntimeError(f"mlb_allgather_pull failed: {rc}")
+
+    def reduce_scatter_adamw(self, ui: int, d: int, scale: float, bc1: float, bc2: float):
+        fs = self.fs
+        u, h, r = fs.units[ui], fs.hyper, fs.rank
+        lo = r * u.chunk
+        sh = fs.shard_off[ui]
+        master = fs.master.data_ptr() + (sh - lo) * 4
+        m = fs.m.data_ptr() + (sh - lo) * 4
+        v = fs.v.data_ptr() + (sh - lo) * 4
+        rc = native.lib().mlb_ddp_bucket(
+            self.t_dslot[d].ptr, self.param_tables[ui].data_ptr(), self.t_flags.ptr, master, m, v,
+            self.done.data_ptr(), self.epoch.data_ptr(), 0, u.padded, r, fs.world, ui, MAX_BUCKETS, 0,
+            h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], bc1, bc2, scale, None, self.rs_ctas, self.spin_limit_s,
+            torch.cuda.current_stream().cuda_stream)
+        native.LAUNCHES += 1
+        if rc != 0:
+            raise RuntimeError(f"mlb_ddp_bucket (reduce-scatter + AdamW) failed: {rc}")

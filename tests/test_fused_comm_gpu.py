@@ -127,18 +127,18 @@ def test_fused_matches_nccl_two_gpus():
             tr.set_batch(ids.to(dev), tgt.to(dev))
             for _ in range(5): tr.step()
             torch.cuda.synchronize()
-            res[comm] = tr.model.master.clone()
-            w = tr.model.master.clone(); dist.all_reduce(w, op=dist.ReduceOp.MAX)
-            res[comm + "_same"] = bool((w == tr.model.master).all())
+            # the fused engine keeps fp32 master / AdamW state only for the shard a rank owns (the bf16 parameters are
+            # what every rank receives), so the comparison is on the parameters
+            res[comm] = tr.model.params.float().clone()
             p = tr.model.params.float().clone(); dist.all_reduce(p, op=dist.ReduceOp.MAX)
             res[comm + "_psame"] = bool((p == tr.model.params.float()).all())
         d = float((res["nccl"] - res["fused"]).abs().max())
-        if rank == 0: print("RESULT", d, res["fused_same"], res["fused_psame"], native.get_error())
+        if rank == 0: print("RESULT", d, res["nccl_psame"], res["fused_psame"], native.get_error())
         dist.barrier(); dist.destroy_process_group()
     """, n)
     assert rc == 0, out[-3000:]
     line = [l for l in out.splitlines() if l.startswith("RESULT")][0].split()
-    assert float(line[1]) < 3e-4, line
+    assert float(line[1]) < 2e-3, line        # one bf16 ulp at |w| ~ 0.1 is 5e-4
     assert line[2] == "True" and line[3] == "True" and line[4] == "0", line
 
 
@@ -172,3 +172,69 @@ def test_rank_leaves_between_steps_ends_with_error_not_hang():
         os._exit(0 if (err >> 24) == 2 else 3)
     """, 2, timeout=300)
     assert "SURVIVOR 2" in out, out[-3000:]
+
+
+def test_fsdp_fused_world1_matches_unsharded():
+    """FSDP engine on one GPU with the NVLink-native kernels (pull all-gather, reduce-scatter + sharded AdamW)."""
+    from ml_b200 import Config
+    from ml_b200.models import GPT
+    from ml_b200.parallel.fsdp import FSDP
+    from ml_b200.utils.rng import Stream
+    from ml_b200.ops import native
+    cfg = Config(V=512, C=256, L=3, H=4, I=512, T=128)
+    ids, tgt = Stream(3).token_pairs(2 * 128, 512)
+    di, dt = ids.cuda(), tgt.cuda()
+    ref = GPT(cfg, 2, "cuda:0")
+    ref.init_weights(1234)
+    outs = {}
+    for comm in ("nccl", "fused"):
+        g = GPT(cfg, 2, "cuda:0", sharded=True)
+        f = FSDP(g, 1, 0, comm=comm, hyper=dict(lr=1e-3, wd=0.1))
+        g.init_weights(1234)
+        for s in range(4):
+            f.step(di, dt)
+        torch.cuda.synchronize()
+        outs[comm] = (f.full_master(), g.mean_loss())
+    for s in range(4):
+        ref.forward(di)
+        ref.backward(di, dt)
+        ref.adamw(1e-3, wd=0.1, t=s + 1)
+    torch.cuda.synchronize()
+    assert native.get_error() == 0
+    for comm in outs:
+        assert (outs[comm][0] - ref.master).abs().max() < 2e-4, comm
+        assert abs(outs[comm][1] - ref.mean_loss()) < 2e-2
+
+
+@needs2
+def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state():
+    n = 2
+    rc, out = _torchrun("""
+        import torch, torch.distributed as dist
+        from ml_b200 import Config
+        from ml_b200.models import GPT
+        from ml_b200.parallel.bootstrap import init_distributed
+        from ml_b200.parallel.fsdp import FSDP
+        from ml_b200.data import bench_batch
+        from ml_b200.ops import native
+        rank, world, local, dev = init_distributed()
+        cfg = Config(V=512, C=256, L=3, H=4, I=512, T=128)
+        ids, tgt = bench_batch(2, 128, 512, rank)
+        res = {}
+        for comm in ("nccl", "fused"):
+            g = GPT(cfg, 2, dev, sharded=True)
+            f = FSDP(g, world, rank, comm=comm, hyper=dict(lr=1e-3, wd=0.1))
+            g.init_weights(1234)
+            for _ in range(4): f.step(ids.to(dev), tgt.to(dev))
+            torch.cuda.synchronize()
+            res[comm] = f.full_master()
+            res[comm + "_n"] = f.master.numel()
+        d = float((res["nccl"] - res["fused"]).abs().max())
+        if rank == 0: print("RESULT", d, res["fused_n"], g.np, native.get_error(), flush=True)
+        dist.barrier(); torch.cuda.synchronize()
+        import os; os._exit(0)
+    """, n)
+    assert rc == 0, out[-3000:]
+    line = [l for l in out.splitlines() if l.startswith("RESULT")][0].split()
+    assert float(line[1]) < 2e-4, line
+    assert int(line[2]) < 0.6 * int(line[3]) and line[4] == "0", line
