@@ -60,6 +60,35 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// packed fp32x2 arithmetic (two lanes per instruction on sm_100) and 3-input max
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 template <int HD>
 struct FwdSmem {
   static constexpr int CH = HD / 64;
@@ -266,7 +295,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
     const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
     const float sl2 = a.scale * LOG2E;
+    const uint64_t sl2x2 = pk2(sl2, sl2);
     int g = 0;
+    uint32_t r[32];
+    bool have_scores = false;
     FwdItem it;
     it.set(blockIdx.x, 0, total, nq, BH, a.H);
     for (; it.valid; it.set(it.w + stride, it.li + 1, total, nq, BH, a.H)) {
@@ -292,54 +324,70 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
         tc::tc_fence_before();
       };
       for (int j = 0; j < it.nkb; j++, g++) {
-        const int sl = g & 1, ph = (g >> 1) & 1;
+        const int sl = g & 1;
         const int kc0 = j * 128 + cq * 32;
-        wait(&bar_s[sl], ph, 17);
-        tc::tc_fence_after();
-        uint32_t r[32];
-        tc::tmem_ld32(tmem + sl * 128 + lane_addr + cq * 32, r);
-        tc::tmem_ld_wait();
+        if (!have_scores) {   // first block of this CTA: nothing was prefetched
+          wait(&bar_s[sl], (g >> 1) & 1, 17);
+          tc::tc_fence_after();
+          tc::tmem_ld32(tmem + sl * 128 + lane_addr + cq * 32, r);
+          tc::tmem_ld_wait();
+          have_scores = true;
+        }
         float mx = -INFINITY;
         if (j == it.qt) {
 #pragma unroll
-          for (int i = 0; i < 32; i++) {
+          for (int i = 0; i < 32; i++)
             if (kc0 + i > qrow) r[i] = 0xff800000u;   // -inf: masked by causality
-            mx = fmaxf(mx, __uint_as_float(r[i]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
         float* red = s_red + sl * 512;
         red[cq * 128 + row] = mx;
         named_bar_sync(1 + lg, 128);
         mx = fmaxf(fmaxf(red[row], red[128 + row]), fmaxf(red[256 + row], red[384 + row]));
         const float m_new = fmaxf(m, mx * sl2);   // finite: key 0 is visible to every query
         const float alpha = exp2f(m - m_new);     // exp2(-inf) = 0 on the first block
-        float rs = 0.f;
+        const uint64_t nm2 = pk2(-m_new, -m_new);
+        uint64_t rs2 = pk2(0.f, 0.f);
         uint8_t* pbuf = smem + S::P + sl * 2 * TILE_BYTES;
 #pragma unroll
         for (int v8 = 0; v8 < 4; v8++) {
-          float pf[8];
+          uint32_t pw[4];
 #pragma unroll
-          for (int x = 0; x < 8; x++) {
-            pf[x] = exp2f(__uint_as_float(r[v8 * 8 + x]) * sl2 - m_new);
-            rs += pf[x];
+          for (int x = 0; x < 4; x++) {
+            const int e = v8 * 8 + 2 * x;
+            float z0, z1;
+            upk2(fma2(pk2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), sl2x2, nm2), z0, z1);
+            const float p0 = exp2f(z0), p1 = exp2f(z1);
+            rs2 = add2(rs2, pk2(p0, p1));
+            pw[x] = pack_bf16(p0, p1);
           }
-          uint4 pk;
-          pk.x = pack_bf16(pf[0], pf[1]); pk.y = pack_bf16(pf[2], pf[3]); pk.z = pack_bf16(pf[4], pf[5]); pk.w = pack_bf16(pf[6], pf[7]);
-          *reinterpret_cast<uint4*>(pbuf + sw_off(row, cq * 32 + v8 * 8)) = pk;
+          *reinterpret_cast<uint4*>(pbuf + sw_off(row, cq * 32 + v8 * 8)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
         }
         tc::fence_async_smem();
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&bar_p[sl]);
-        l = l * alpha + rs;
+        float rs_lo, rs_hi;
+        upk2(rs2, rs_lo, rs_hi);
+        l = l * alpha + (rs_lo + rs_hi);
         m = m_new;
+        // the score registers are free again: start fetching the next block's scores (this item's or the next item's)
+        // so that the TMEM latency hides behind the fold below
+        const bool more = (j + 1 < it.nkb) || (it.w + stride < total);
+        if (more) {
+          wait(&bar_s[(g + 1) & 1], ((g + 1) >> 1) & 1, 17);
+          tc::tc_fence_after();
+          tc::tmem_ld32(tmem + ((g + 1) & 1) * 128 + lane_addr + cq * 32, r);
+        } else {
+          have_scores = false;
+        }
         if (j > 0) {   // fold in the previous block, whose P V product had a whole softmax to complete
           wait(&bar_o[(g - 1) & 1], ((g - 1) >> 1) & 1, 18);
           tc::tc_fence_after();
-          fold(g - 1, alpha_prev);
+          fold(g - 1, alpha_prev);     // its tcgen05.wait::ld also covers the score prefetch
+        } else if (more) {
+          tc::tmem_ld_wait();
         }
         alpha_prev = alpha;
       }
@@ -421,7 +469,7 @@ __global__ void attn_delta_scalar_k(float* __restrict__ delta, const bf16* __res
 // (i, i + HD/2).  With tables given, RoPE's backward rotation (d0' = d0 c + d1 s, d1' = d1 c - d0 s) is applied.
 template <int HD>
 __device__ __forceinline__ void store_pairs_rope(bf16* dst_row, uint32_t taddr, int c0, bool live, const float* cosT,
-                                                 const float* sinT, int t) {
+                                                 const float* sinT, int t, float out_scale = 1.f) {
   uint32_t ra[32], rb[32];
   tc::tmem_ld32(taddr + c0, ra);
   tc::tmem_ld32(taddr + c0 + HD / 2, rb);
@@ -429,7 +477,7 @@ __device__ __forceinline__ void store_pairs_rope(bf16* dst_row, uint32_t taddr, 
   if (!live) return;
   float x0[32], x1[32];
 #pragma unroll
-  for (int i = 0; i < 32; i++) { x0[i] = __uint_as_float(ra[i]); x1[i] = __uint_as_float(rb[i]); }
+  for (int i = 0; i < 32; i++) { x0[i] = __uint_as_float(ra[i]) * out_scale; x1[i] = __uint_as_float(rb[i]) * out_scale; }
   if (cosT) {
     const float* c = cosT + (size_t)t * (HD / 2) + c0;
     const float* s = sinT + (size_t)t * (HD / 2) + c0;
@@ -627,6 +675,298 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kv_tc_kernel(const __
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// ================================================================== backward, head size 64: ONE kernel, five GEMMs
+// One CTA per 128-key tile walks the query tiles i >= its own.  Per query tile:
+//     S^T = K Q^T, dP^T = V dO^T                       (two MMAs, scores never leave TMEM)
+//     P^T = exp2(S^T*c - lse), dS^T = P^T (dP^T - delta)   (512 threads, packed f32x2 math, bf16 into swizzled smem)
+//     dV += P^T dO, dK += dS^T Q                        (accumulated in TMEM over all query tiles)
+//     dQ_i  = dS K                                      (the dS^T tile is read again as an MN-major A operand)
+// dQ_i is a partial sum over key tiles: it is drained from TMEM through a swizzled staging buffer and added to an fp32
+// accumulator [B*T, C] with TMA add-reduce; a small second kernel turns the accumulator into bf16 dQ (scale, RoPE
+// backward) and zeroes it again.  The 1/sqrt(hd) factor is applied once per output element instead of once per score.
+// Compared with separate dK/dV and dQ kernels this computes S, dP and the exponentials once instead of twice.
+struct BwdFusedSmem {
+  static constexpr int K = 0;
+  static constexpr int V = K + TILE_BYTES;
+  static constexpr int Q = V + TILE_BYTES;               // 2 buffers
+  static constexpr int DO = Q + 2 * TILE_BYTES;          // 2 buffers
+  static constexpr int PT = DO + 2 * TILE_BYTES;         // [128 keys x 128 queries] bf16
+  static constexpr int DST = PT + 2 * TILE_BYTES;
+  static constexpr int DQS = DST + 2 * TILE_BYTES;       // fp32 staging for the dQ tile: 4 lane groups x 2 boxes x 4 KB
+  static constexpr int STAT = DQS + 2 * TILE_BYTES;      // -lse*log2e [128], -delta [128]
+  static constexpr int BAR = STAT + 1024;
+  static constexpr int TOTAL = BAR + 128 + 1024;
+};
+
+__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+                                                                           const __grid_constant__ CUtensorMap tm_do,
+                                                                           const __grid_constant__ CUtensorMap tm_dq, const AttnArgs a) {
+  using S = BwdFusedSmem;
+  constexpr int HD = 64;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + S::BAR);
+  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[2]*/, *bar_s = bars + 3;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 5);
+  volatile int* s_abort = (volatile int*)(bars + 6);
+  float* s_nlse = (float*)(smem + S::STAT);
+  float* s_ndelta = s_nlse + 128;
+  {
+    __shared__ int s_skip;
+    if (threadIdx.x == 0) s_skip = *(volatile int*)&g_mlb_error;
+    __syncthreads();
+    if (s_skip != 0) return;
+  }
+  const int nq = (a.T + 127) / 128;
+  // A CTA takes key tile x and its mirror nq-1-x: together they always cover nq+1 query blocks, so all CTAs carry the
+  // same load, and the second tile's loads overlap the first tile's epilogue.
+  const int kt_first = blockIdx.x, kt_second = nq - 1 - (int)blockIdx.x;
+  const int n_items = (kt_second != kt_first) ? 2 : 1;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int C = a.H * HD;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
+  const int row0 = b * a.T;
+
+  if (tid == 0) {
+    tc::mbar_init(bar_kv, 1); tc::mbar_init(&bar_q[0], 1); tc::mbar_init(&bar_q[1], 1); tc::mbar_init(bar_s, 1);
+    *s_abort = 0;
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tm_qkv);
+    tc::tma_prefetch_desc(&tm_do);
+    tc::tma_prefetch_desc(&tm_dq);
+  }
+  if (warp == 0) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_st = tmem, t_dpt = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 320, t_dq = tmem + 384;   // two dQ buffers: +384 and +448
+  const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T / dS^T), B MN-major (dO / Q)
+  constexpr uint32_t idesc_q = tc::idesc_bf16(128, HD, 1, 1);    // A MN-major (dS^T read as dS), B MN-major (K)
+  const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V);
+  const uint32_t sPT = tc::smem_u32(smem + S::PT), sDST = tc::smem_u32(smem + S::DST);
+  auto wait = [&](uint64_t* bar, uint32_t phase, int where) -> bool {
+    if (*s_abort) return false;
+    if (!tc::mbar_wait(bar, phase, where)) { *s_abort = 1; return false; }
+    return true;
+  };
+  auto load_kv = [&](int kt) {
+    tc::mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
+    tc::tma_load_2d(smem + S::K, &tm_qkv, bar_kv, C + h * HD, row0 + kt * 128);
+    tc::tma_load_2d(smem + S::V, &tm_qkv, bar_kv, 2 * C + h * HD, row0 + kt * 128);
+  };
+  auto load_q_do = [&](int i, int buf) {
+    tc::mbar_expect_tx(&bar_q[buf], 2 * TILE_BYTES);
+    tc::tma_load_2d(smem + S::Q + buf * TILE_BYTES, &tm_qkv, &bar_q[buf], h * HD, row0 + i * 128);
+    tc::tma_load_2d(smem + S::DO + buf * TILE_BYTES, &tm_do, &bar_q[buf], h * HD, row0 + i * 128);
+  };
+  auto issue_scores = [&](int buf) {
+    const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
+  };
+  // dQ tile of query block i: TMEM -> swizzled fp32 staging -> TMA add-reduce into the accumulator
+  uint8_t* stage = smem + S::DQS + lg * 8192 + (cq >> 1) * 4096;
+  auto drain_dq = [&](int i, int dbuf) {
+    if (cq == 0 && lane == 0) tc::tma_wait_group_read<0>();   // the previous reduce has finished reading the staging
+    named_bar_sync(1 + lg, 128);
+    uint32_t r[16];
+    tc::tmem_ld16(t_dq + dbuf * 64 + lane_addr + cq * 16, r);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int v = 0; v < 4; v++) {
+      const int unit = (cq & 1) * 4 + v;
+      *reinterpret_cast<uint4*>(stage + lane * 128 + ((unit ^ (lane & 7)) << 4)) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+    }
+    tc::fence_async_smem();
+    tc::tc_fence_before();
+    named_bar_sync(1 + lg, 128);
+    if (cq == 0 && lane == 0) {
+      tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192, h * HD, row0 + i * 128 + lg * 32);
+      tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192 + 4096, h * HD + 32, row0 + i * 128 + lg * 32);
+      tc::tma_commit_group();
+    }
+  };
+
+  const float sl2 = a.scale * LOG2E;
+  const uint64_t sl2x2 = pk2(sl2, sl2);
+  int blk = 0;      // running query-block number of this CTA: Q/dO buffer = blk & 1, its barrier phase = (blk >> 1) & 1
+  int s_cnt = 0;    // completions of bar_s consumed so far
+  if (tid == 0) {
+    load_kv(kt_first);
+    load_q_do(kt_first, 0);
+  }
+  for (int item = 0; item < n_items; item++) {
+    const int kt = item == 0 ? kt_first : kt_second;
+    const int k0 = kt * 128, krow = k0 + row;
+    const int n_it = nq - kt;
+    if (tid == 0) {
+      if (wait(bar_kv, item & 1, 40) && wait(&bar_q[blk & 1], (blk >> 1) & 1, 41)) { tc::tc_fence_after(); issue_scores(blk & 1); }
+      tc::mma_commit(bar_s);
+    }
+    // per-query statistics of a block, negated for the packed FMAs; queries past the end give P = 0.  Threads 0..127
+    // hold -lse*log2e, threads 128..255 hold -delta; the values for block i+1 are fetched while block i's MMAs run.
+    auto fetch_stat = [&](int i) -> float {
+      if (tid >= 256) return 0.f;
+      const int q = i * 128 + (tid & 127);
+      const size_t si = ((size_t)b * a.H + h) * a.T + q;
+      if (tid < 128) return (q < a.T) ? -a.lse[si] * LOG2E : -INFINITY;
+      return (q < a.T) ? -a.delta[si] : 0.f;
+    };
+    float stat = fetch_stat(kt);
+    for (int it = 0; it < n_it; it++, blk++) {
+      const int i = kt + it, q0 = i * 128, buf = blk & 1;
+      if (tid < 128) s_nlse[tid] = stat;
+      else if (tid < 256) s_ndelta[tid - 128] = stat;
+      __syncthreads();
+      wait(bar_s, s_cnt & 1, 42);       // S^T, dP^T of this block are complete, and so is everything issued before them
+      s_cnt++;
+      tc::tc_fence_after();
+      if (tid == 0 && it + 1 < n_it) load_q_do(i + 1, buf ^ 1);
+      {
+        uint32_t rs[32], rd[32];
+        tc::tmem_ld32(t_st + lane_addr + cq * 32, rs);
+        tc::tmem_ld32(t_dpt + lane_addr + cq * 32, rd);
+        tc::tmem_ld_wait();
+        const bool diag = (it == 0);
+#pragma unroll
+        for (int v8 = 0; v8 < 4; v8++) {
+          const int qc = cq * 32 + v8 * 8;
+          float nl[8], nd[8];
+          *reinterpret_cast<float4*>(nl) = *reinterpret_cast<const float4*>(s_nlse + qc);
+          *reinterpret_cast<float4*>(nl + 4) = *reinterpret_cast<const float4*>(s_nlse + qc + 4);
+          *reinterpret_cast<float4*>(nd) = *reinterpret_cast<const float4*>(s_ndelta + qc);
+          *reinterpret_cast<float4*>(nd + 4) = *reinterpret_cast<const float4*>(s_ndelta + qc + 4);
+          uint32_t pw[4], dw[4];
+#pragma unroll
+          for (int x = 0; x < 4; x++) {
+            const int e = v8 * 8 + 2 * x;
+            float z0, z1;
+            upk2(fma2(pk2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), sl2x2, pk2(nl[2 * x], nl[2 * x + 1])), z0, z1);
+            float p0 = exp2f(z0), p1 = exp2f(z1);
+            if (diag) {
+              if (q0 + qc + 2 * x < krow) p0 = 0.f;
+              if (q0 + qc + 2 * x + 1 < krow) p1 = 0.f;
+            }
+            const uint64_t t2 = add2(pk2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])), pk2(nd[2 * x], nd[2 * x + 1]));
+            float d0, d1;
+            upk2(mul2(pk2(p0, p1), t2), d0, d1);
+            pw[x] = pack_bf16(p0, p1);
+            dw[x] = pack_bf16(d0, d1);
+          }
+          const uint32_t off = sw_off(row, qc);
+          *reinterpret_cast<uint4*>(smem + S::PT + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+          *reinterpret_cast<uint4*>(smem + S::DST + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+        }
+      }
+      tc::fence_async_smem();
+      tc::tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc::tc_fence_after();
+        if (!*s_abort) {
+          const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dv, desc_k(sPT, ks), desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
+#pragma unroll
+          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, desc_k(sDST, ks), desc_mn(sQ, ks), idesc_d, (it > 0 || ks > 0));
+#pragma unroll
+          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq + (blk & 1) * 64, desc_mn(sDST, ks), desc_mn(sK, ks), idesc_q, ks > 0);
+        }
+        if (it + 1 < n_it && wait(&bar_q[buf ^ 1], ((blk + 1) >> 1) & 1, 43)) {
+          tc::tc_fence_after();
+          issue_scores(buf ^ 1);
+        }
+        tc::mma_commit(bar_s);
+      }
+      // while the tensor core works through this block's MMAs: fetch the next block's statistics and move the previous
+      // block's dQ tile (complete since the bar_s wait above, and in the other TMEM buffer) to the accumulator
+      if (it + 1 < n_it) stat = fetch_stat(i + 1);
+      if (it > 0) drain_dq(i - 1, (blk - 1) & 1);
+    }
+    wait(bar_s, s_cnt & 1, 44);   // dV, dK and the last dQ tile of this key tile are complete; K, V, Q, dO are free
+    s_cnt++;
+    tc::tc_fence_after();
+    if (tid == 0 && item + 1 < n_items) {   // the mirror tile's loads run under this tile's epilogue
+      load_kv(kt_second);
+      load_q_do(kt_second, blk & 1);
+    }
+    drain_dq(kt + n_it - 1, (blk - 1) & 1);   // earlier blocks were drained inside the loop
+    if (cq < 2) {   // warps 0-3: dK (scaled, RoPE backward); warps 4-7: dV
+      const bool is_k = cq == 0;
+      bf16* dst = a.out + ((size_t)(row0 + krow)) * 3 * C + (is_k ? C : 2 * C) + h * HD;
+      store_pairs_rope<HD>(dst, (is_k ? t_dk : t_dv) + lane_addr, 0, !*s_abort && krow < a.T, is_k ? a.cosT : nullptr,
+                           is_k ? a.sinT : nullptr, krow, is_k ? a.scale : 1.f);
+    }
+    tc::tc_fence_before();
+    __syncthreads();   // the accumulators have been read out before the next tile's first MMAs are issued
+  }
+  if (cq == 0 && lane == 0) tc::tma_wait_group<0>();
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
+// dQ accumulator (fp32 [rows, C]) -> bf16 Q slice of dqkv[rows, 3C], times `scale`, optional RoPE backward; the
+// accumulator is zeroed for its next use.  One thread per (row, head, group of 16 rotation pairs): eight 16-byte loads
+// in flight per thread.
+__global__ void __launch_bounds__(256) attn_dq_finish_k(bf16* __restrict__ dqkv, float* __restrict__ acc, long rows, int T, int H,
+                                                        int hd, float scale, const float* __restrict__ cosT,
+                                                        const float* __restrict__ sinT) {
+  const int h2 = hd >> 1, gph = h2 >> 4, gpr = H * gph;   // groups of 16 pairs per head / per row
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * gpr) return;
+  const long r = idx / gpr;
+  const int g = idx % gpr, h = g / gph, v = g % gph;
+  const int t = r % T, C = H * hd;
+  float4* p0 = reinterpret_cast<float4*>(acc + r * C + h * hd + v * 16);
+  float4* p1 = reinterpret_cast<float4*>(acc + r * C + h * hd + h2 + v * 16);
+  float4 a0[4], a1[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) { a0[i] = __ldcs(p0 + i); a1[i] = __ldcs(p1 + i); }
+  const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < 4; i++) { p0[i] = z; p1[i] = z; }
+  float x0[16], x1[16];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    x0[4 * i] = a0[i].x * scale; x0[4 * i + 1] = a0[i].y * scale; x0[4 * i + 2] = a0[i].z * scale; x0[4 * i + 3] = a0[i].w * scale;
+    x1[4 * i] = a1[i].x * scale; x1[4 * i + 1] = a1[i].y * scale; x1[4 * i + 2] = a1[i].z * scale; x1[4 * i + 3] = a1[i].w * scale;
+  }
+  if (cosT) {
+    const float4* c4 = reinterpret_cast<const float4*>(cosT + (long)t * h2 + v * 16);
+    const float4* s4 = reinterpret_cast<const float4*>(sinT + (long)t * h2 + v * 16);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float4 c = c4[i], sn = s4[i];
+      const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const float d0 = x0[4 * i + k], d1 = x1[4 * i + k];
+        x0[4 * i + k] = d0 * cc[k] + d1 * ss[k];
+        x1[4 * i + k] = d1 * cc[k] - d0 * ss[k];
+      }
+    }
+  }
+  bf16* o0 = dqkv + r * 3L * C + h * hd + v * 16;
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    uint4 w0, w1;
+    w0.x = pack_bf16(x0[8 * i], x0[8 * i + 1]); w0.y = pack_bf16(x0[8 * i + 2], x0[8 * i + 3]);
+    w0.z = pack_bf16(x0[8 * i + 4], x0[8 * i + 5]); w0.w = pack_bf16(x0[8 * i + 6], x0[8 * i + 7]);
+    w1.x = pack_bf16(x1[8 * i], x1[8 * i + 1]); w1.y = pack_bf16(x1[8 * i + 2], x1[8 * i + 3]);
+    w1.z = pack_bf16(x1[8 * i + 4], x1[8 * i + 5]); w1.w = pack_bf16(x1[8 * i + 6], x1[8 * i + 7]);
+    *reinterpret_cast<uint4*>(o0 + 8 * i) = w0;
+    *reinterpret_cast<uint4*>(o0 + h2 + 8 * i) = w1;
+  }
 }
 
 // ================================================================== backward: dQ (one CTA per 128-query tile)
@@ -915,11 +1255,13 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
   return (int)cudaGetLastError();
 }
 
-// dqkv[B,T,3C] from dout[B,T,C], qkv, out, lse.  `delta` is scratch of B*H*T floats.  If cosT/sinT are given, RoPE's
+// dqkv[B,T,3C] from dout[B,T,C], qkv, out, lse.  `delta` is scratch of B*H*T floats.  `dq_acc` (optional) is scratch of
+// B*T*C floats that must be all zero on entry (it is left all zero): with it and head size 64 the fused
+// single-kernel backward runs; without it the two-kernel backward (dK/dV kernel + dQ kernel) runs.  If cosT/sinT are given, RoPE's
 // backward rotation is applied to dQ and dK before they are stored (tensor-core path only; returns 1 if it was applied,
 // 0 if the caller still has to rotate, <0 or a CUDA error code > 1 on failure).
-MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, int B, int T,
-                         int H, int hd, const float* cosT, const float* sinT, cudaStream_t st) {
+MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, float* dq_acc,
+                         int B, int T, int H, int hd, const float* cosT, const float* sinT, cudaStream_t st) {
   const int C = H * hd;
   const float scale = 1.0f / sqrtf((float)hd);
   {
@@ -935,6 +1277,20 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
     if (!tq || !td) return -2;
     AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT};
     dim3 grid((T + 127) / 128, H, B);
+    if (hd == 64 && dq_acc != nullptr && ((uintptr_t)dq_acc % 16 == 0)) {
+      // single fused kernel + dQ finish; dq_acc is fp32 [B*T, C], all zero on entry and all zero again on exit
+      const CUtensorMap* tacc = mlb_tmap_cached(dq_acc, (uint64_t)B * T, C, C, 32, 32, 4);
+      if (!tacc) return -2;
+      static int o0 = set_smem(attn_bwd_fused_tc_kernel, BwdFusedSmem::TOTAL);
+      (void)o0;
+      dim3 grid_f(((T + 127) / 128 + 1) / 2, H, B);   // a CTA handles a key tile and its mirror
+      attn_bwd_fused_tc_kernel<<<grid_f, BWD_THREADS, BwdFusedSmem::TOTAL, st>>>(*tq, *td, *tacc, a);
+      const long groups = (long)B * T * H * (hd / 32);
+      attn_dq_finish_k<<<(unsigned)((groups + 255) / 256), 256, 0, st>>>((bf16*)dqkv, dq_acc, (long)B * T, T, H, hd, scale, cosT, sinT);
+      cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return (int)e + 1000;
+      return cosT ? 1 : 0;
+    }
     if (hd == 64) {
       static int o1 = set_smem(attn_bwd_kv_tc_kernel<64>, BwdKVSmem<64>::TOTAL);
       static int o2 = set_smem(attn_bwd_q_tc_kernel<64>, BwdQSmem<64>::TOTAL);

@@ -16,7 +16,7 @@ import signal
 import sys
 import time
 
-MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|plan|lmce_check"
+MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|bench_fsdp|plan|lmce_check"
 
 
 def _banner(mode, dev):
@@ -79,7 +79,7 @@ def mode_overfit(argv):
     return 0 if last is not None and last < 0.05 else 1
 
 
-def _mm_setup(B, dev, cfg_defaults, lr, wd, env_cfg):
+def _mm_setup(B, dev, cfg_defaults, lr, wd, env_cfg, world=1, rank=0):
     import torch
     from . import Config, VisionConfig
     from .config import env_int
@@ -95,8 +95,9 @@ def _mm_setup(B, dev, cfg_defaults, lr, wd, env_cfg):
     else:
         cfg = Config(V=256, C=128, L=4, H=4, I=256, T=T)
         vc = VisionConfig(vC=96, vL=3, vI=192, n_patch=n_patch)
-    tr = Trainer(cfg, B, dev, lr=lr, wd=wd, vision=vc, n_text=T_text)
-    patches, ids, tgt = mm_batch(B, n_patch, T_text, cfg.V, vc.patch_dim)
+    from . import RunConfig
+    tr = Trainer(cfg, B, dev, RunConfig.from_env(), lr=lr, wd=wd, vision=vc, n_text=T_text, world=world, rank=rank)
+    patches, ids, tgt = mm_batch(B, n_patch, T_text, cfg.V, vc.patch_dim, seed=5 + 131 * rank)
     tr.vision.patches.copy_(patches.to(tr.vision.dtype).to(dev))
     tr.set_batch(ids.to(dev), tgt.to(dev))
     return tr, cfg, vc, n_patch, T_text
@@ -138,17 +139,38 @@ def _timed(tr, steps, dev, warm=3):
 
 
 def mode_mm_bench(argv):
-    dev = _device()
-    _banner("mm_bench", dev)
+    """Joint multimodal step.  Under a multi-process launcher (WORLD_SIZE > 1) the step is data parallel over both the
+    decoder and the vision tower (the reference's mm modes are single-GPU only); throughput is then global."""
+    import torch
+    from .config import rank_world_local
+    rank, world, _ = rank_world_local()
+    if world > 1:
+        from .parallel.bootstrap import init_distributed
+        rank, world, _, dev = init_distributed()
+    else:
+        dev = _device()
+    if rank == 0:
+        _banner("mm_bench", dev)
     B = int(argv[0]) if argv else 2
     steps = int(argv[1]) if len(argv) > 1 else 50
-    tr, cfg, vc, n_patch, T_text = _mm_setup(B, dev, None, 1e-4, 0.1, True)
+    tr, cfg, vc, n_patch, T_text = _mm_setup(B, dev, None, 1e-4, 0.1, True, world, rank)
     tr.use_graph = dev.type == "cuda" and os.environ.get("ENTROPY_GRAPH", "1") != "0"
-    print(f"MM bench: B={B} patches={n_patch} text={T_text} LM {tr.model.np / 1e6:.1f}M params vision "
-          f"{tr.vision.np / 1e6:.1f}M params steps={steps}")
+    if rank == 0:
+        print(f"MM bench: B={B} patches={n_patch} text={T_text} LM {tr.model.np / 1e6:.1f}M params vision "
+              f"{tr.vision.np / 1e6:.1f}M params steps={steps} world={world}")
     dt = _timed(tr, steps, dev)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
     ls = tr.model.mean_loss(n_pre=n_patch, valid_tokens=B * T_text)
-    print(f"mm step: {dt * 1e3:.2f} ms | text tok/s {B * T_text / dt:.0f} | image tok/s {B * n_patch / dt:.0f} | loss {ls:.4f}")
+    if rank == 0:
+        print(f"mm step: {dt * 1e3:.2f} ms | text tok/s {world * B * T_text / dt:.0f} | image tok/s {world * B * n_patch / dt:.0f} | loss {ls:.4f}")
+    if world > 1:
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        os._exit(0)
     return 0
 
 
@@ -359,6 +381,60 @@ def mode_bench_ddp(argv):
     return 0
 
 
+def mode_bench_fsdp(argv):
+    """Sharded (ZeRO-3 style) training step of a llama-style model; defaults are the 1.3 B shape
+    L=24 C=2048 H=16 I=5504 V=50304 T=2048, B=8 per GPU.  ENTROPY_COMM=fused (default) uses the NVLink-native kernels,
+    ENTROPY_COMM=nccl the library collectives."""
+    import torch
+    import torch.distributed as dist
+    from . import Config, RunConfig
+    from .models import GPT
+    from .parallel.bootstrap import init_distributed
+    from .parallel.fsdp import FSDP
+    from .data import bench_batch
+    from .layout import flops_per_step
+    rank, world, local, dev = init_distributed()
+    if rank == 0:
+        _banner("bench_fsdp", dev)
+    cfg = Config.from_env(V=50304, C=2048, L=24, H=16, I=5504, T=2048)
+    B = int(argv[0]) if argv else 8
+    steps = int(argv[1]) if len(argv) > 1 else 10
+    run = RunConfig.from_env()
+    g = GPT(cfg, B, dev, sharded=True)
+    f = FSDP(g, world, rank, comm=run.comm, hyper=dict(lr=1e-4, wd=0.1))
+    g.init_weights(1234)
+    ids, tgt = bench_batch(B, cfg.T, cfg.V, rank)
+    ids, tgt = ids.to(dev), tgt.to(dev)
+    if rank == 0:
+        print(f"FSDP world={world} per-GPU B={B} params={g.np / 1e6:.1f}M shard={f.master.numel() / 1e6:.1f}M comm={f.comm}")
+    for _ in range(2):
+        f.step(ids, tgt)
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        f.step(ids, tgt)
+    e1.record()
+    torch.cuda.synchronize()
+    dt = e0.elapsed_time(e1) / steps / 1e3
+    if world > 1:
+        t = torch.tensor([dt], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    if rank == 0:
+        fl = flops_per_step(cfg, B) * world
+        print(f"fsdp step {dt * 1e3:.2f} ms | global {B * cfg.T * world / dt:.0f} tok/s | {fl / dt / 1e12:.1f} TFLOP/s agg | "
+              f"MFU {100 * fl / dt / (run.peak_tflops * 1e12 * world):.1f}% | loss {g.mean_loss():.4f}")
+    sys.stdout.flush()
+    if world > 1:
+        torch.cuda.synchronize()
+        os._exit(0)
+    return 0
+
+
 def main(argv=None):
     argv = list(sys.argv[1:] if argv is None else argv)
     mode = argv[0] if argv else "overfit"
@@ -371,7 +447,7 @@ def main(argv=None):
         print(plan_from_env())
         return 0
     table = {"overfit": mode_overfit, "mm_overfit": mode_mm_overfit, "mm_bench": mode_mm_bench, "bench": mode_bench,
-             "bench_ddp": mode_bench_ddp, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
+             "bench_ddp": mode_bench_ddp, "bench_fsdp": mode_bench_fsdp, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
     if mode not in table:
         print(f"usage: python -m ml_b200.gpt [{MODES}] [args]", file=sys.stderr)
         return 2

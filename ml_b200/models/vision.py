@@ -20,7 +20,7 @@ from ..utils import rng as _rng
 
 
 class VisionTower:
-    def __init__(self, vc: VisionConfig, C: int, B: int, device="cpu", dtype: Optional[torch.dtype] = None):
+    def __init__(self, vc: VisionConfig, C: int, B: int, device="cpu", dtype: Optional[torch.dtype] = None, alloc=None):
         self.vc, self.C, self.B = vc, C, B
         self.device = torch.device(device)
         if dtype is None:
@@ -30,8 +30,9 @@ class VisionTower:
         self.np = VL.num_params
         dev = self.device
         self.master = torch.zeros(self.np, dtype=torch.float32, device=dev)
-        self.params = self.master if dtype == torch.float32 else torch.zeros(self.np, dtype=dtype, device=dev)
-        self.grads = torch.zeros(self.np, dtype=torch.float32, device=dev)
+        mk = alloc if alloc is not None else (lambda n, dt: torch.empty(n, dtype=dt, device=dev))
+        self.params = self.master if dtype == torch.float32 else mk(self.np, dtype).zero_()
+        self.grads = mk(self.np, torch.float32).zero_()
         self.m = torch.zeros(self.np, dtype=torch.float32, device=dev)
         self.v = torch.zeros(self.np, dtype=torch.float32, device=dev)
         NP = B * vc.n_patch

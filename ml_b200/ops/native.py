@@ -34,7 +34,7 @@ def lib():
         "mlb_gemm_set_splits": [_i32],
         "mlb_attn_force_simt": [_i32],
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
-        "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
+        "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
         "mlb_embed_fwd": [_vp, _vp, _vp, _i64, _i32, _vp],
         "mlb_embed_bwd": [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp],
         "mlb_set_prefix": [_vp, _vp, _i32, _i32, _i32, _i32, _vp],
@@ -158,13 +158,20 @@ def attn_fwd(out, lse, qkv, B, T, H, hd):
     _chk(lib().mlb_attn_fwd(_b(out), _f(lse), _b(qkv), B, T, H, hd, _st()), "attn_fwd")
 
 
+FUSED_ATTN_BWD = True   # head size 64: single fused backward kernel (False = separate dK/dV and dQ kernels)
+
+
 def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
     """rope=(cos, sin): ask the kernel to apply RoPE's backward rotation to dQ/dK in its epilogue.
     Returns True if it did (tensor-core path), False if the caller still has to call rope_bwd."""
     delta = scratch("attn_delta", B * H * T, torch.float32, qkv.device)
+    acc = None
+    if hd == 64 and FUSED_ATTN_BWD:
+        # fp32 dQ accumulator of the fused backward: zero-filled once here, left zero by every call
+        acc = scratch(("attn_dq_acc", B * T * H * hd), B * T * H * hd, torch.float32, qkv.device, zero=True).data_ptr()
     cp = _f(rope[0]) if rope is not None else None
     sp = _f(rope[1]) if rope is not None else None
-    rc = lib().mlb_attn_bwd(_b(dqkv), _b(dout), _b(qkv), _b(out), _f(lse), _f(delta), B, T, H, hd, cp, sp, _st())
+    rc = lib().mlb_attn_bwd(_b(dqkv), _b(dout), _b(qkv), _b(out), _f(lse), _f(delta), acc, B, T, H, hd, cp, sp, _st())
     global LAUNCHES
     LAUNCHES += 3
     if rc < 0 or rc > 1:

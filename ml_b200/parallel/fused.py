@@ -19,7 +19,7 @@ MAX_BUCKETS = 64
 
 class FusedGradEngine:
     def __init__(self, model, world: int, rank: int, group=None, ctas: int = 0, bcast: bool = True, spin_limit_s: float = 2.0,
-                 overlap=None):
+                 overlap=None, buckets=None):
         """ctas: CTAs per bucket kernel (0 = policy below).  overlap: run bucket kernels on a side stream behind backward
         (ENTROPY_FUSED_OVERLAP=1).  Default off: measured on B200 with the 12-layer model, a few comm CTAs next to the
         persistent GEMMs cost more (stragglers among the statically scheduled GEMM tiles: 25.4 ms / step at 2 GPUs) than
@@ -51,7 +51,9 @@ class FusedGradEngine:
         self.done = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
         self.epoch = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
         self.bucket_ids = {}
-        for i, (name, off, n) in enumerate(model.layout.slices_backward_order()):
+        # `model` is anything with flat .grads / .params / .master / .m / .v on one device (decoder or vision tower);
+        # `buckets` = [(name, offset, numel)] defaults to the decoder's backward order
+        for i, (name, off, n) in enumerate(buckets if buckets is not None else model.layout.slices_backward_order()):
             if off % 4 != 0:
                 raise ValueError(f"bucket {name} starts at element {off}: the fused kernel needs 16-byte aligned buckets "
                                  "(use ENTROPY_COMM=nccl for this shape)")

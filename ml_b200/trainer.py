@@ -36,7 +36,7 @@ class Trainer:
         self.model.init_weights(seed)
         self.vision = None
         if vision is not None:
-            self.vision = VisionTower(vision, cfg.C, B, self.device)
+            self.vision = VisionTower(vision, cfg.C, B, self.device, alloc=alloc)
             self.vision.init_weights(777)
             self.n_pre = vision.n_patch
             self.n_text = n_text if n_text is not None else cfg.T - vision.n_patch
@@ -47,6 +47,11 @@ class Trainer:
                        overlap_opt=bool(self.run.ddp_overlap_opt), opt_hyper=self.hyper, rank=rank)
         self.accum = self.ddp.accum
         self.t = 1
+        # the vision tower's gradients are data-parallel too (the reference's multimodal modes are single-GPU only)
+        self.vfused = None
+        if self.vision is not None and self.ddp.fused is not None and self.vision.np % 4 == 0:
+            from .parallel.fused import FusedGradEngine
+            self.vfused = FusedGradEngine(self.vision, world, rank, group, buckets=[("vision", 0, self.vision.np)])
         n = B * cfg.T
         self.ids = torch.zeros(self.accum, n, dtype=torch.int32, device=self.device)
         self.tgt = torch.zeros(self.accum, n, dtype=torch.int32, device=self.device)
@@ -88,7 +93,15 @@ class Trainer:
             self.ddp.t = self.t
             self.ddp.step_optimizer()
         if self.vision is not None:
-            self.vision.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, 1.0 / self.accum, self.d_hyper_v)
+            if self.vfused is not None:
+                self.vfused.bucket(0, self.vision.np, 1.0 / (self.world * self.accum), h, self.t, self.d_hyper_v)
+                self.vfused.finish()
+            else:
+                if self.world > 1:
+                    import torch.distributed as dist
+                    dist.all_reduce(self.vision.grads, group=self.ddp.group)
+                self.vision.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, 1.0 / (self.world * self.accum),
+                                  self.d_hyper_v)
         # mean loss of the last micro-batch, reduced on the device (one float to read back)
         BT = self.B * self.cfg.T
         valid = self.B * self.n_text if self.vision is not None else BT
@@ -125,7 +138,7 @@ class Trainer:
         self.d_hyper.copy_(self.h_hyper, non_blocking=True)
         if self.vision is not None:
             self.h_hyper_v.copy_(self.h_hyper)
-            self.h_hyper_v[3] = 1.0 / self.accum
+            self.h_hyper_v[3] = 1.0 / (self.world * self.accum)
             self.d_hyper_v.copy_(self.h_hyper_v, non_blocking=True)
 
     def _capture(self):

@@ -117,8 +117,19 @@ ATTN_CASES = [(2, 128, 2, 64), (1, 256, 3, 64), (2, 384, 2, 64), (2, 192, 2, 64)
               (1, 256, 2, 128), (2, 320, 1, 128), (2, 64, 4, 32), (1, 100, 2, 16)]
 
 
+@pytest.fixture(params=[True, False], ids=["fused_bwd", "split_bwd"])
+def bwd_mode(request):
+    """Head size 64 has two backward implementations: one fused kernel, or separate dK/dV and dQ kernels."""
+    old = nat().FUSED_ATTN_BWD
+    nat().FUSED_ATTN_BWD = request.param
+    yield request.param
+    nat().FUSED_ATTN_BWD = old
+
+
 @pytest.mark.parametrize("B,T,H,hd", ATTN_CASES)
-def test_attn_fwd_bwd(B, T, H, hd):
+def test_attn_fwd_bwd(B, T, H, hd, bwd_mode):
+    if hd != 64 and not bwd_mode:
+        pytest.skip("only one backward implementation for this head size")
     torch.manual_seed(5)
     C = H * hd
     qkv = rnd(B * T, 3 * C, scale=1.0)
@@ -140,7 +151,7 @@ def test_attn_fwd_bwd(B, T, H, hd):
         close(d5[:, :, i], e5[:, :, i], rtol=3e-2, atol=3e-2, name=nm)
 
 
-def test_attn_bwd_fused_rope_matches_separate():
+def test_attn_bwd_fused_rope_matches_separate(bwd_mode):
     torch.manual_seed(6)
     B, T, H, hd = 2, 256, 2, 64
     C = H * hd
