@@ -127,7 +127,10 @@ class GPT:
         if self.prof is not None:
             self.prof.mark(name)
 
-    def forward(self, ids, B=None, prefix=None, n_pre=0):
+    def forward(self, ids, B=None, prefix=None, n_pre=0, x_in=None, has_head=True):
+        """x_in / has_head serve pipeline stages (ml_b200.parallel.pp): a stage that is not the first takes the
+        residual stream `x_in` [B*T, C] instead of embedding `ids`; a stage that is not the last stops after its last
+        layer's residual add and returns that residual stream instead of logits."""
         c, Lo = self.cfg, self.layout
         B = self.B if B is None else B
         T, C, I, H, hd = c.T, c.C, c.I, c.H, c.hd
@@ -135,10 +138,13 @@ class GPT:
         assert B <= self.B
         sl = lambda t: t[:BT]
         x0 = sl(self.x0)
-        self._pre("wte", "fwd")
-        ops.embed_fwd(x0, self.P(Lo.off_wte, c.V, C), ids)
-        if prefix is not None and n_pre > 0:
-            ops.set_prefix(x0, prefix, B, T, n_pre)
+        if x_in is not None:
+            x0.copy_(x_in)
+        else:
+            self._pre("wte", "fwd")
+            ops.embed_fwd(x0, self.P(Lo.off_wte, c.V, C), ids)
+            if prefix is not None and n_pre > 0:
+                ops.set_prefix(x0, prefix, B, T, n_pre)
         self._pre("layer0" if c.L > 0 else "head", "fwd")
         ops.rmsnorm_fwd(sl(self.ln1[0]), sl(self.rstd1[0]), x0, self.P(Lo.layer(0).ln1, C), c.eps)
         resid_in = x0
@@ -158,6 +164,10 @@ class GPT:
             ops.linear_fwd(sl(self.gu[l]), sl(self.ln2[l]), self.P(o.gate, 2 * I, C))
             ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
             ops.linear_fwd(proj, sl(self.sw[l]), self.P(o.down, C, I))
+            if l + 1 == c.L and not has_head:
+                # stage boundary: plain residual add; the next stage starts with its own first norm
+                ops.residual_add(sl(self.resid2[l]), sl(self.resid1[l]), proj)
+                return sl(self.resid2[l])
             # the fused add + norm uses the NEXT unit's norm weight: that unit has to be present from here on
             self._pre(f"layer{l + 1}" if l + 1 < c.L else "head", "fwd")
             if l + 1 < c.L:
@@ -176,8 +186,11 @@ class GPT:
         if self.bucket_hook is not None:
             self.bucket_hook(name, off, n)
 
-    def backward(self, ids, tgt, B=None, zero=True, n_pre=0, valid_tokens=None):
-        """Consumes the logits of the last forward (they are overwritten by dlogits)."""
+    def backward(self, ids, tgt, B=None, zero=True, n_pre=0, valid_tokens=None, d_out=None, has_embed=True):
+        """Consumes the logits of the last forward (they are overwritten by dlogits).
+        Pipeline stages: `d_out` [B*T, C] is the gradient of the residual stream this stage returned (the head part is
+        skipped); with has_embed=False the embedding scatter is skipped and the gradient of the stage input is left in
+        self.dresid for the previous stage."""
         c, Lo = self.cfg, self.layout
         B = self.B if B is None else B
         T, C, I, H, hd, V = c.T, c.C, c.I, c.H, c.hd, c.V
@@ -186,19 +199,22 @@ class GPT:
         if zero and self.grads is not None:
             self.grads.zero_()
         valid = valid_tokens if valid_tokens is not None else BT - B * n_pre
-        logits = self.logits[:BT]
-        ops.ce_fwd_bwd(sl(self.losses), logits, tgt, 1.0 / float(valid))
-        self._mark("B_ce")
         dln, dresid, dresid1 = sl(self.dln), sl(self.dresid), sl(self.dresid1)
-        self._pre("head", "bwd")
-        ops.linear_dw(self.G(Lo.off_lm, V, C), logits, sl(self.lnf_out))
-        ops.linear_dx(dln, logits, self.P(Lo.off_lm, V, C))
-        self._mark("B_lmhead")
-        last = sl(self.resid2[c.L - 1]) if c.L > 0 else sl(self.x0)
-        ops.rmsnorm_bwd(dresid, self.G(Lo.off_lnf, C), dln, last, self.P(Lo.off_lnf, C), sl(self.rstdf), None)
-        self._mark("B_norm")
-        self._hook("lm", Lo.off_lm, V * C)
-        self._hook("lnf", Lo.off_lnf, C)
+        if d_out is not None:
+            dresid.copy_(d_out)
+        else:
+            logits = self.logits[:BT]
+            ops.ce_fwd_bwd(sl(self.losses), logits, tgt, 1.0 / float(valid))
+            self._mark("B_ce")
+            self._pre("head", "bwd")
+            ops.linear_dw(self.G(Lo.off_lm, V, C), logits, sl(self.lnf_out))
+            ops.linear_dx(dln, logits, self.P(Lo.off_lm, V, C))
+            self._mark("B_lmhead")
+            last = sl(self.resid2[c.L - 1]) if c.L > 0 else sl(self.x0)
+            ops.rmsnorm_bwd(dresid, self.G(Lo.off_lnf, C), dln, last, self.P(Lo.off_lnf, C), sl(self.rstdf), None)
+            self._mark("B_norm")
+            self._hook("lm", Lo.off_lm, V * C)
+            self._hook("lnf", Lo.off_lnf, C)
         for l in range(c.L - 1, -1, -1):
             o = Lo.layer(l)
             self._pre(f"layer{l}", "bwd")
@@ -227,6 +243,8 @@ class GPT:
             ops.rmsnorm_bwd(dresid, self.G(o.ln1, C), dln, x_in, self.P(o.ln1, C), sl(self.rstd1[l]), dresid1)
             self._mark("B_norm")
             self._hook(f"layer{l}", Lo.layer_base(l), Lo.layer_stride)
+        if not has_embed:
+            return
         self._pre("wte", "bwd")
         ops.embed_bwd(self.G(Lo.off_wte, V, C), dresid, ids, T, n_pre)
         self._hook("wte", Lo.off_wte, V * C)

@@ -150,3 +150,39 @@ def test_gloo_fsdp_equals_single_process():
     line = [l for l in outs[0][1].splitlines() if l.startswith("DIFF")][0].split()
     assert float(line[1]) < 5e-5, line
     assert int(line[2]) < 0.6 * int(line[3])       # each rank holds about half of the optimizer state
+
+
+def test_gloo_pipeline_1f1b_equals_single_process():
+    """Two pipeline stages on CPU ranks, 4 micro-batches, 1F1B: after three optimizer steps every stage's parameters
+    equal the corresponding slice of a single process that accumulated the same micro-batches."""
+    outs = run_ranks("""
+        import torch, torch.distributed as dist
+        from ml_b200 import Config, RunConfig
+        from ml_b200.parallel.bootstrap import init_distributed, shutdown
+        from ml_b200.parallel.pp import PipelineStage
+        from ml_b200.trainer import Trainer
+        from ml_b200.utils.rng import Stream
+        rank, world, local, dev = init_distributed("cpu")
+        cfg = Config(V=64, C=32, L=4, H=2, I=64, T=8)
+        M, B = 4, 2
+        ids, tgt = Stream(5).token_pairs(M * B * 8, 64)
+        ids_mb = list(ids.view(M, -1)); tgt_mb = list(tgt.view(M, -1))
+        st = PipelineStage(cfg, B, world, rank, dev, microbatches=M, hyper=dict(lr=1e-2, wd=0.1))
+        for _ in range(3):
+            loss = st.step(ids_mb, tgt_mb)
+        run = RunConfig(); run.accum = M
+        one = Trainer(cfg, B, dev, run, lr=1e-2, wd=0.1)
+        one.set_batch(ids, tgt)
+        for _ in range(3): one.step()
+        d = 0.0
+        for so, fo, n in st.owned_ranges():
+            d = max(d, float((st.model.master[so:so + n] - one.model.master[fo:fo + n]).abs().max()))
+        print("PPDIFF", rank, d, loss, flush=True)
+        dist.barrier(); shutdown()
+    """, timeout=300)
+    assert all(rc == 0 for rc, _ in outs), outs
+    for rc, o in outs:
+        line = [l for l in o.splitlines() if l.startswith("PPDIFF")][0].split()
+        assert float(line[2]) < 5e-5, line
+    last = [l for l in outs[1][1].splitlines() if l.startswith("PPDIFF")][0].split()
+    assert last[3] != "None"
