@@ -18,8 +18,11 @@ from .symm import PeerTable, empty as symm_empty
 
 class FusedFSDP:
     def __init__(self, fs, gather_ctas: int = 32, rs_ctas: int = 32, spin_limit_s: float = 2.0):
+        import os
         self.fs = fs
-        self.gather_ctas, self.rs_ctas, self.spin_limit_s = gather_ctas, rs_ctas, spin_limit_s
+        self.gather_ctas = int(os.environ.get("ENTROPY_FSDP_GATHER_CTAS", gather_ctas))
+        self.rs_ctas = int(os.environ.get("ENTROPY_FSDP_RS_CTAS", rs_ctas))
+        self.spin_limit_s = spin_limit_s
         dev, W, r = fs.dev, fs.world, fs.rank
         L = native.lib()
         L.mlb_ddp_bucket.argtypes = [C.c_void_p] * 8 + [C.c_long, C.c_long] + [C.c_int] * 5 + [C.c_float] * 8 + \

@@ -138,7 +138,7 @@ def test_fused_matches_nccl_two_gpus():
     """, n)
     assert rc == 0, out[-3000:]
     line = [l for l in out.splitlines() if l.startswith("RESULT")][0].split()
-    assert float(line[1]) < 2e-3, line        # one bf16 ulp at |w| ~ 0.1 is 5e-4
+    assert float(line[1]) < 8e-3, line        # one bf16 ulp at |w| ~ 1 (norm weights) is 3.9e-3
     assert line[2] == "True" and line[3] == "True" and line[4] == "0", line
 
 
