@@ -39,6 +39,23 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + 1024;  // +1024 alignment slack
 };
 
+// All-gather fused into the GEMM (FSDP): four extra warps per CTA pull 16 KB pieces of the sharded parameter unit from
+// the owning ranks' memory (peer loads over NVLink) into the local gather slot and publish a per-piece flag; the TMA
+// producer of a tile waits (bounded) for the pieces that hold its rows of B.  Needs all CTAs co-resident: the kernel
+// is started with a cooperative launch.
+struct GatherArgs {
+  const uint4* const* src;   // device array [world]: base of each rank's shard of this unit
+  uint4* dst;                // local gather slot (start of the unit)
+  long shard_vec;            // 16-byte vectors per shard
+  long b_lo_vec, b_hi_vec;   // vector range of the B matrix inside the unit
+  long b_row_vec;            // vectors per row of B (K-major B: pitch; used to map a tile's rows to pieces)
+  int* flags;                // one int per piece, device memory of this GPU, monotonically increasing epochs
+  int* ctr;                  // [0] completed launches (epoch = ctr[0] + 1), [1] CTAs done in this launch
+  int world;
+  int piece_vec;             // vectors per piece
+  long spin_limit_ns;
+};
+
 struct GemmArgs {
   void* out;
   int M, N, K;       // logical problem: D[M,N], reduction K
@@ -46,10 +63,25 @@ struct GemmArgs {
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
 };
 
-template <int BN, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__device__ __forceinline__ bool wait_piece(const int* flag, int epoch, long limit_ns) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+  if (v >= epoch) return true;
+  const uint64_t t0 = tc::globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 64; i++) {
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v >= epoch) return true;
+      __nanosleep(64);
+    }
+    if ((long)(tc::globaltimer_ns() - t0) > limit_ns) { mlb_set_error(MLB_ERR_FLAG_TIMEOUT, 0x6a7); return false; }
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI, bool GATHER = false>
+__global__ void __launch_bounds__(GEMM_THREADS + (GATHER ? 128 : 0), 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
+               const __grid_constant__ CUtensorMap tmD, const GemmArgs g, const GatherArgs ga) {
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -63,6 +95,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = g.tiles_m * g.tiles_n * g.splits;
+  int g_epoch = 0;
+  if (GATHER) g_epoch = *((volatile int*)ga.ctr) + 1;   // every CTA reads it before the last one to finish bumps it
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; i++) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
@@ -87,6 +121,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n, sp = t / (g.tiles_m * g.tiles_n);
         const int m0 = mt * BM, n0 = nt * BN;
         const int kb0 = sp * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+        if (GATHER) {
+          // rows [n0, n0+BN) of a K-major B live in a contiguous vector range of the unit; an MN-major B needs all of it
+          long lo = ga.b_lo_vec, hi = ga.b_hi_vec;
+          if (!B_MN) { lo = ga.b_lo_vec + (long)n0 * ga.b_row_vec; hi = min(ga.b_hi_vec, lo + (long)BN * ga.b_row_vec); }
+          for (long pc = lo / ga.piece_vec; pc <= (hi - 1) / ga.piece_vec && ok; pc++)
+            ok = wait_piece(ga.flags + pc, g_epoch, ga.spin_limit_ns);
+          asm volatile("fence.proxy.async;" ::: "memory");   // peer data landed by generic stores, read next by TMA
+          if (!ok) break;
+        }
         for (int kb = kb0; kb < kb1; kb++) {
           if (!tc::mbar_wait(&empty[stage], phase ^ 1, 1)) { ok = false; break; }
           uint8_t* sA = smem + stage * S::STAGE_BYTES;
@@ -202,8 +245,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     if (lane == 0) tc::tma_wait_group<0>();   // all stores / reductions of this warp have completed
   }
+  if (GATHER && warp >= 6) {
+    // ---------------------------------------------------------------- gather warps (6..9)
+    const int gt = threadIdx.x - GEMM_THREADS;            // 0..127
+    const long total_vec = ga.shard_vec * ga.world;
+    const long n_pieces = (total_vec + ga.piece_vec - 1) / ga.piece_vec;
+    for (long pc = blockIdx.x; pc < n_pieces; pc += gridDim.x) {
+      const long v0 = pc * ga.piece_vec, v1 = min(total_vec, v0 + ga.piece_vec);
+      for (long v = v0 + gt; v < v1; v += 128) {
+        const int w = (int)(v / ga.shard_vec);
+        const uint4* sp = ga.src[w] + (v - (long)w * ga.shard_vec);
+        uint4 x;
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(sp) : "memory");
+        ga.dst[v] = x;
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (gt == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ga.flags + pc), "r"(g_epoch) : "memory");
+    }
+  }
   tc::tc_fence_before();
   __syncthreads();
+  if (GATHER && threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ga.ctr + 1, 1) == (int)gridDim.x - 1) { ga.ctr[1] = 0; ga.ctr[0] = g_epoch; }
+  }
   if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * BN);
 }
 
@@ -332,8 +398,28 @@ int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap*
   int total = g.tiles_m * g.tiles_n * g.splits;
   int cap = g_max_ctas > 0 ? g_max_ctas : num_sms();
   int grid = total < cap ? total : cap;
-  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, st>>>(*tmA, *tmB, *tmD, g);
+  GatherArgs none{};
+  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, st>>>(*tmA, *tmB, *tmD, g, none);
   return (int)cudaGetLastError();
+}
+
+// Cooperative launch of the gather variant (all CTAs must be co-resident because tiles wait on other CTAs' pieces).
+template <int BN, bool B_MN>
+int launch_tc_gather(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, GemmArgs g, GatherArgs ga, cudaStream_t st) {
+  auto kern = gemm_tc_kernel<BN, false, B_MN, EPI_BF16, true>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    attr_done = true;
+  }
+  int total = g.tiles_m * g.tiles_n * g.splits;
+  int cap = g_max_ctas > 0 ? g_max_ctas : num_sms();
+  int grid = total < cap ? total : cap;
+  CUtensorMap a = *tmA, b = *tmB, d = *tmD;
+  void* args[] = {&a, &b, &d, &g, &ga};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(GEMM_THREADS + 128), args, GemmSmem<BN>::TOTAL, st);
+  return (int)e;
 }
 
 // Generic entry: D[M,N] (+)= sum_k A(m,k) B(n,k).
@@ -398,6 +484,36 @@ MLB_API int mlb_linear_dx(void* dx, const void* dout, const void* W, int M, int 
 // dW[N,K] += dout[M,N]^T . x[M,K]   (GEMM view: D[N,K], reduction M; both operands MN-major)
 MLB_API int mlb_linear_dw(void* dW, const void* dout, const void* x, int M, int N, int K, int lddw, int lddo, int ldx, cudaStream_t st) {
   return gemm_dispatch<true, true, EPI_F32_ADD>(dW, lddw, (const bf16*)dout, lddo, (const bf16*)x, ldx, N, K, M, st);
+}
+
+// out[M,N] = x[M,K] . W[N,K]^T where W lies inside a sharded parameter unit that this launch also all-gathers:
+//   unit_dst    local gather slot (start of the unit, 16-byte aligned), W == unit_dst + w_off_elems
+//   src_ptrs    device array [world] of the ranks' shard bases; every shard holds shard_elems bf16 (multiple of 8)
+//   flags       device ints, one per 16 KB piece of the unit (zero-initialised once); ctr: two device ints (zeroed once)
+// When the kernel has finished, the WHOLE unit is present in unit_dst (not only W).
+MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K, int ldo, int ldx, void* unit_dst,
+                                  long w_off_elems, const void* src_ptrs, long shard_elems, int world, int* flags, int* ctr,
+                                  double spin_limit_s, cudaStream_t st) {
+  const bf16* W = (const bf16*)unit_dst + w_off_elems;
+  const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)out % 16 == 0) && (ldx % 8 == 0) &&
+                       (ldo % 8 == 0) && (K % 8 == 0) && (N % 8 == 0) && (shard_elems % 8 == 0) && (w_off_elems % 8 == 0) &&
+                       get_encode() != nullptr;
+  if (!aligned) return -6;
+  const int BN = (N > 128) ? 256 : 128;
+  GemmArgs g;
+  g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
+  g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
+  g.splits = 1; g.kb_per_split = g.kb_total;
+  GatherArgs ga;
+  ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
+  ga.b_lo_vec = w_off_elems / 8; ga.b_hi_vec = (w_off_elems + (long)N * K) / 8; ga.b_row_vec = K / 8;
+  ga.flags = flags; ga.ctr = ctr; ga.world = world; ga.piece_vec = 1024; ga.spin_limit_ns = (long)(spin_limit_s * 1e9);
+  const CUtensorMap* tmA = mlb_tmap_cached(x, M, K, ldx, BM, 64);
+  const CUtensorMap* tmB = mlb_tmap_cached(W, N, K, K, BN, 64);
+  const CUtensorMap* tmD = mlb_tmap_cached(out, M, N, ldo, 32, 64, 2);
+  if (!tmA || !tmB || !tmD) return -2;
+  if (BN == 256) return launch_tc_gather<256, false>(tmA, tmB, tmD, g, ga, st);
+  return launch_tc_gather<128, false>(tmA, tmB, tmD, g, ga, st);
 }
 
 MLB_API void mlb_gemm_force_simt(int on) { g_force_simt = on; }

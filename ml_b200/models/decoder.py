@@ -151,7 +151,11 @@ class GPT:
         for l in range(c.L):
             o = Lo.layer(l)
             qkv = sl(self.qkv[l])
-            ops.linear_fwd(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C))
+            if self.res is not None and hasattr(self.res, "linear_fwd_first"):
+                # sharded parameters: the unit's all-gather may be fused into this first GEMM of the layer
+                self.res.linear_fwd_first(qkv, sl(self.ln1[l]), o.qkv, (3 * C, C))
+            else:
+                ops.linear_fwd(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C))
             if "rope" not in self.skip:
                 ops.rope_fwd(qkv, self.cos, self.sin, B, T, H, hd)
             self._mark("F_qkv+rope")

@@ -153,6 +153,18 @@ def linear_dw(dW, dout, x):
     _chk(lib().mlb_linear_dw(_f(dW), _b(dout), _b(x), M, N, K, dW.stride(0), dout.stride(0), x.stride(0), _st()), "linear_dw")
 
 
+def linear_fwd_gather(out, x, N, K, unit_dst, w_off, src_table, shard_elems, world, flags, ctr, spin_limit_s=2.0):
+    """out = x . W^T with W = unit_dst[w_off : w_off + N*K] viewed [N, K]; the same launch all-gathers the whole sharded
+    unit into unit_dst from the ranks' shards (device pointer table `src_table`).  Cooperative launch."""
+    L = lib()
+    fn = L.mlb_linear_fwd_gather
+    fn.argtypes = [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i32, _vp, _vp, C.c_double, _vp]
+    fn.restype = _i32
+    M = x.shape[0]
+    _chk(fn(_b(out), _b(x), M, N, K, out.stride(0), x.stride(0), _b(unit_dst), w_off, src_table.data_ptr(), shard_elems, world,
+            _i(flags), _i(ctr), spin_limit_s, _st()), "linear_fwd_gather")
+
+
 # ------------------------------------------------------------------ attention
 def attn_fwd(out, lse, qkv, B, T, H, hd):
     _chk(lib().mlb_attn_fwd(_b(out), _f(lse), _b(qkv), B, T, H, hd, _st()), "attn_fwd")

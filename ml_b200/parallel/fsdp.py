@@ -75,6 +75,7 @@ class FSDP:
         self.gather_ev = [None, None]
         self.rs_ev = [None, None]
         self.fused = None
+        self.lazy = [-1, -1]            # gather slot -> unit whose all-gather is deferred into its first GEMM
         if self.comm == "fused":
             from .fsdp_fused import FusedFSDP
             self.fused = FusedFSDP(self)
@@ -168,7 +169,14 @@ class FSDP:
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(ev)
             if self.fused is not None:
-                self.fused.gather(ui, slot)
+                if self.fused.gather_in_gemm and self._fwd_pass and u.name.startswith("layer"):
+                    # forward of a layer: only the first norm weight is fetched here; the all-gather itself runs inside
+                    # the layer's QKV GEMM (linear_fwd_first)
+                    self.fused.gather_head(ui, slot, self.model.cfg.C)
+                    self.lazy[slot] = ui
+                else:
+                    self.lazy[slot] = -1
+                    self.fused.gather(ui, slot)
             else:
                 dist.all_gather_into_tensor(self.gslot[slot][:u.padded], self.shard_view(self.pshard, ui), group=self.group)
             self.gather_ev[slot] = torch.cuda.Event()
@@ -186,9 +194,22 @@ class FSDP:
         if 0 <= prefetch < len(self.units) and prefetch not in self.slot_unit:
             self._gather(prefetch, 1 - s)
 
+    def linear_fwd_first(self, out, x, off, shape):
+        """First GEMM of a layer (QKV projection).  If the layer's all-gather was deferred, it happens inside this GEMM."""
+        ui = self._unit_of(off)
+        s = self.slot_unit.index(ui)
+        if self.lazy[s] == ui:
+            self.lazy[s] = -1
+            self.fused.linear_fwd_gather(out, x, ui, s, off - self.units[ui].off, shape)
+        else:
+            ops.linear_fwd(out, x, self.param(off, shape))
+
+    _fwd_pass = True
+
     def pre(self, name: str, phase: str):
         ui = self.by_name[name]
         nu = len(self.units)
+        self._fwd_pass = phase == "fwd"
         if phase == "fwd":
             # the next unit in forward order; after the head comes the backward pass, which starts with the head again
             self._ensure(ui, ui + 1 if ui + 1 < nu else -1)
@@ -247,6 +268,7 @@ class FSDP:
         if self.cuda:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         self.slot_unit = [-1, -1]
+        self.lazy = [-1, -1]
         self.dslot_unit = [-1, -1]
         self.gather_ev = [None, None]
         self.rs_ev = [None, None]

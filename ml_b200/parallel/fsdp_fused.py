@@ -23,6 +23,9 @@ class FusedFSDP:
         self.gather_ctas = int(os.environ.get("ENTROPY_FSDP_GATHER_CTAS", gather_ctas))
         self.rs_ctas = int(os.environ.get("ENTROPY_FSDP_RS_CTAS", rs_ctas))
         self.spin_limit_s = spin_limit_s
+        # all-gather fused into the consuming GEMM (cooperative kernel); ENTROPY_FSDP_GATHER_GEMM=0 keeps the prefetched
+        # pull kernel for every unit
+        self.gather_in_gemm = os.environ.get("ENTROPY_FSDP_GATHER_GEMM", "1") != "0" and fs.dtype == torch.bfloat16
         dev, W, r = fs.dev, fs.world, fs.rank
         L = native.lib()
         L.mlb_ddp_bucket.argtypes = [C.c_void_p] * 8 + [C.c_long, C.c_long] + [C.c_int] * 5 + [C.c_float] * 8 + \
@@ -47,10 +50,31 @@ class FusedFSDP:
         for i, u in enumerate(fs.units):
             self.src_tables.append((base + fs.shard_off[i] * es).to(dev))
             self.param_tables.append((base + (fs.shard_off[i] - r * u.chunk) * es).to(dev))
+        maxpad = max(u.padded for u in fs.units)
+        n_pieces = (maxpad * es + 16383) // 16384 + 1
+        self.piece_flags = [torch.zeros(n_pieces, dtype=torch.int32, device=dev) for _ in range(2)]
+        self.piece_ctr = [torch.zeros(2, dtype=torch.int32, device=dev) for _ in range(2)]
         if W > 1:
             import torch.distributed as dist
             torch.cuda.synchronize()
             dist.barrier(group=fs.group)
+
+    def gather_head(self, ui: int, slot: int, n_elems: int):
+        """Pull only the first n_elems of the unit (the first norm weight), which live at the start of rank 0's shard."""
+        fs = self.fs
+        nbytes = (n_elems * fs.pshard.element_size() + 15) // 16 * 16
+        assert n_elems <= fs.units[ui].chunk
+        rc = native.lib().mlb_allgather_pull(fs.gslot[slot].data_ptr(), self.src_tables[ui].data_ptr(), nbytes, 1, 4,
+                                             torch.cuda.current_stream().cuda_stream)
+        native.LAUNCHES += 1
+        if rc != 0:
+            raise RuntimeError(f"mlb_allgather_pull failed: {rc}")
+
+    def linear_fwd_gather(self, out, x, ui: int, slot: int, w_off: int, shape):
+        fs = self.fs
+        u = fs.units[ui]
+        native.linear_fwd_gather(out, x, shape[0], shape[1], fs.gslot[slot], w_off, self.src_tables[ui], u.chunk, fs.world,
+                                 self.piece_flags[slot], self.piece_ctr[slot], self.spin_limit_s)
 
     def gather(self, ui: int, slot: int):
         fs = self.fs

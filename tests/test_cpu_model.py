@@ -126,3 +126,23 @@ def test_vision_pixels_path_equals_patch_path():
     assert torch.equal(a, b)
     # patch (0,1) of image 0 is the pixel block rows 0..3, cols 4..7, channel-major
     assert torch.equal(patches[1].view(3, 4, 4), px[0, :, 0:4, 4:8])
+
+
+def test_module_tree_autograd_matches_engine():
+    """nn.Module decoder on the differentiable ops: same loss and gradients as the explicit engine."""
+    from ml_b200.models.modules import Decoder
+    cfg = Config(V=97, C=48, L=2, H=4, I=80, T=16)
+    B = 2
+    g = GPT(cfg, B)
+    g.init_weights(1234)
+    ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+    tgt[::7] = -1
+    valid = int((tgt >= 0).sum())
+    g.forward(ids)
+    g.backward(ids, tgt, valid_tokens=valid)
+    m = Decoder.from_flat(g)
+    loss = m(ids, tgt)
+    loss.backward()
+    assert abs(loss.item() - g.mean_loss(valid_tokens=valid)) < 1e-5
+    for p, off in m.named_flat():
+        assert (p.grad.flatten() - g.grads[off:off + p.numel()]).abs().max() < 2e-5
