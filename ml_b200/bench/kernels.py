@@ -135,6 +135,23 @@ def once(a):
         for _ in range(3):
             nat.attn_fwd(out, lse, qkv, a.B, a.T, a.H, a.hd)
             nat.attn_bwd(dqkv, dout, qkv, out, lse, a.B, a.T, a.H, a.hd)
+    elif a.case == "norm":
+        rows, Cc, V = a.M, a.C, a.V
+        x = torch.randn(rows, Cc, device=dev).bfloat16()
+        w = torch.ones(Cc, device=dev).bfloat16()
+        o, r, dw = torch.empty_like(x), torch.empty(rows, device=dev), torch.zeros(Cc, device=dev)
+        lg = torch.randn(rows // 8, V, device=dev).bfloat16()      # 200 MB of logits: larger than L2
+        tg = torch.randint(0, V, (rows // 8,), device=dev, dtype=torch.int32)
+        ls = torch.empty(rows // 8, device=dev)
+        n = 32 * 1024 * 1024
+        ma, g, m, v = (torch.zeros(n, device=dev) for _ in range(4))
+        p = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            nat.rmsnorm_fwd(o, r, x, w, 1e-5)
+            nat.add_rmsnorm_fwd(o, o, r, x, x, w, 1e-5)
+            nat.rmsnorm_bwd(o, dw, x, x, w, r, x)
+            nat.ce_fwd_bwd(ls, lg, tg, 1.0 / rows)
+            nat.adamw(ma, p, g, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.5, 1.0)
     else:
         M, N, K = a.M, 3 * a.C, a.C
         x = torch.randn(M, K, device=dev).bfloat16()
@@ -154,7 +171,7 @@ def once(a):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "attn", "norm", "once"])
-    ap.add_argument("--case", default="attn", choices=["attn", "gemm"])
+    ap.add_argument("--case", default="attn", choices=["attn", "gemm", "norm"])
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--C", type=int, default=768)
     ap.add_argument("--I", type=int, default=2048)

@@ -695,25 +695,27 @@ struct BwdFusedSmem {
   static constexpr int PT = DO + 2 * TILE_BYTES;         // [128 keys x 128 queries] bf16
   static constexpr int DST = PT + 2 * TILE_BYTES;
   static constexpr int DQS = DST + 2 * TILE_BYTES;       // fp32 staging for the dQ tile: 4 lane groups x 2 boxes x 4 KB
-  static constexpr int STAT = DQS + 2 * TILE_BYTES;      // -lse*log2e [128], -delta [128]
-  static constexpr int BAR = STAT + 1024;
+  static constexpr int STAT = DQS + 2 * TILE_BYTES;      // 2 buffers x (-lse*log2e [128], -delta [128])
+  static constexpr int BAR = STAT + 2048;
   static constexpr int TOTAL = BAR + 128 + 1024;
 };
 
-__global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
-                                                                           const __grid_constant__ CUtensorMap tm_do,
-                                                                           const __grid_constant__ CUtensorMap tm_dq, const AttnArgs a) {
+constexpr int BWDF_WORK_WARPS = 16;
+constexpr int BWDF_THREADS = (BWDF_WORK_WARPS + 1) * 32;   // 16 element-wise warps + 1 control warp
+
+__global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+                                                                            const __grid_constant__ CUtensorMap tm_do,
+                                                                            const __grid_constant__ CUtensorMap tm_dq, const AttnArgs a) {
   using S = BwdFusedSmem;
   constexpr int HD = 64;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + S::BAR);
-  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[2]*/, *bar_s = bars + 3;
+  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[2]*/, *bar_s = bars + 3, *bar_p = bars + 4;
   uint32_t* tmem_slot = (uint32_t*)(bars + 5);
   volatile int* s_abort = (volatile int*)(bars + 6);
-  float* s_nlse = (float*)(smem + S::STAT);
-  float* s_ndelta = s_nlse + 128;
+  float* s_stat = (float*)(smem + S::STAT);   // [2 buffers][-lse*log2e x128 | -delta x128]
   {
     __shared__ int s_skip;
     if (threadIdx.x == 0) s_skip = *(volatile int*)&g_mlb_error;
@@ -728,92 +730,129 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_fused_tc_kernel(const
   const int h = blockIdx.y, b = blockIdx.z;
   const int C = a.H * HD;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
   const int row0 = b * a.T;
 
   if (tid == 0) {
     tc::mbar_init(bar_kv, 1); tc::mbar_init(&bar_q[0], 1); tc::mbar_init(&bar_q[1], 1); tc::mbar_init(bar_s, 1);
+    tc::mbar_init(bar_p, BWDF_WORK_WARPS);
     *s_abort = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tm_qkv);
     tc::tma_prefetch_desc(&tm_do);
     tc::tma_prefetch_desc(&tm_dq);
   }
-  if (warp == 0) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == BWDF_WORK_WARPS) tc::tmem_alloc(tmem_slot, TMEM_COLS);
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_st = tmem, t_dpt = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 320, t_dq = tmem + 384;   // two dQ buffers: +384 and +448
-  const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
-  constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T / dS^T), B MN-major (dO / Q)
-  constexpr uint32_t idesc_q = tc::idesc_bf16(128, HD, 1, 1);    // A MN-major (dS^T read as dS), B MN-major (K)
-  const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V);
-  const uint32_t sPT = tc::smem_u32(smem + S::PT), sDST = tc::smem_u32(smem + S::DST);
+  const uint32_t t_st = tmem, t_dpt = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 320, t_dq = tmem + 384;   // two dQ buffers: +384, +448
   auto wait = [&](uint64_t* bar, uint32_t phase, int where) -> bool {
     if (*s_abort) return false;
     if (!tc::mbar_wait(bar, phase, where)) { *s_abort = 1; return false; }
     return true;
   };
-  auto load_kv = [&](int kt) {
-    tc::mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
-    tc::tma_load_2d(smem + S::K, &tm_qkv, bar_kv, C + h * HD, row0 + kt * 128);
-    tc::tma_load_2d(smem + S::V, &tm_qkv, bar_kv, 2 * C + h * HD, row0 + kt * 128);
-  };
-  auto load_q_do = [&](int i, int buf) {
-    tc::mbar_expect_tx(&bar_q[buf], 2 * TILE_BYTES);
-    tc::tma_load_2d(smem + S::Q + buf * TILE_BYTES, &tm_qkv, &bar_q[buf], h * HD, row0 + i * 128);
-    tc::tma_load_2d(smem + S::DO + buf * TILE_BYTES, &tm_do, &bar_q[buf], h * HD, row0 + i * 128);
-  };
-  auto issue_scores = [&](int buf) {
-    const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
-  };
-  // dQ tile of query block i: TMEM -> swizzled fp32 staging -> TMA add-reduce into the accumulator
-  uint8_t* stage = smem + S::DQS + lg * 8192 + (cq >> 1) * 4096;
-  auto drain_dq = [&](int i, int dbuf) {
-    if (cq == 0 && lane == 0) tc::tma_wait_group_read<0>();   // the previous reduce has finished reading the staging
-    named_bar_sync(1 + lg, 128);
-    uint32_t r[16];
-    tc::tmem_ld16(t_dq + dbuf * 64 + lane_addr + cq * 16, r);
-    tc::tmem_ld_wait();
-#pragma unroll
-    for (int v = 0; v < 4; v++) {
-      const int unit = (cq & 1) * 4 + v;
-      *reinterpret_cast<uint4*>(stage + lane * 128 + ((unit ^ (lane & 7)) << 4)) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-    }
-    tc::fence_async_smem();
-    tc::tc_fence_before();
-    named_bar_sync(1 + lg, 128);
-    if (cq == 0 && lane == 0) {
-      tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192, h * HD, row0 + i * 128 + lg * 32);
-      tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192 + 4096, h * HD + 32, row0 + i * 128 + lg * 32);
-      tc::tma_commit_group();
-    }
-  };
 
-  const float sl2 = a.scale * LOG2E;
-  const uint64_t sl2x2 = pk2(sl2, sl2);
-  int blk = 0;      // running query-block number of this CTA: Q/dO buffer = blk & 1, its barrier phase = (blk >> 1) & 1
-  int s_cnt = 0;    // completions of bar_s consumed so far
-  if (tid == 0) {
-    load_kv(kt_first);
-    load_q_do(kt_first, 0);
-  }
-  for (int item = 0; item < n_items; item++) {
-    const int kt = item == 0 ? kt_first : kt_second;
-    const int k0 = kt * 128, krow = k0 + row;
-    const int n_it = nq - kt;
-    if (tid == 0) {
-      if (wait(bar_kv, item & 1, 40) && wait(&bar_q[blk & 1], (blk >> 1) & 1, 41)) { tc::tc_fence_after(); issue_scores(blk & 1); }
-      tc::mma_commit(bar_s);
+  if (warp == BWDF_WORK_WARPS) {
+    // ---------------------------------------------------------------- control warp: every TMA load and every MMA
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T / dS^T), B MN-major (dO / Q)
+      constexpr uint32_t idesc_q = tc::idesc_bf16(128, HD, 1, 1);    // A MN-major (dS^T read as dS), B MN-major (K)
+      const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V);
+      const uint32_t sPT = tc::smem_u32(smem + S::PT), sDST = tc::smem_u32(smem + S::DST);
+      auto load_kv = [&](int kt) {
+        tc::mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
+        tc::tma_load_2d(smem + S::K, &tm_qkv, bar_kv, C + h * HD, row0 + kt * 128);
+        tc::tma_load_2d(smem + S::V, &tm_qkv, bar_kv, 2 * C + h * HD, row0 + kt * 128);
+      };
+      auto load_q_do = [&](int i, int buf) {
+        tc::mbar_expect_tx(&bar_q[buf], 2 * TILE_BYTES);
+        tc::tma_load_2d(smem + S::Q + buf * TILE_BYTES, &tm_qkv, &bar_q[buf], h * HD, row0 + i * 128);
+        tc::tma_load_2d(smem + S::DO + buf * TILE_BYTES, &tm_do, &bar_q[buf], h * HD, row0 + i * 128);
+      };
+      auto issue_scores = [&](int buf) {
+        const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
+      };
+      int blk = 0, s_cnt = 0, p_cnt = 0;
+      load_kv(kt_first);
+      load_q_do(kt_first, 0);
+      for (int item = 0; item < n_items; item++) {
+        const int kt = item == 0 ? kt_first : kt_second;
+        const int n_it = nq - kt;
+        if (wait(bar_kv, item & 1, 40) && wait(&bar_q[blk & 1], (blk >> 1) & 1, 41)) { tc::tc_fence_after(); issue_scores(blk & 1); }
+        tc::mma_commit(bar_s);
+        for (int it = 0; it < n_it; it++, blk++) {
+          const int i = kt + it, buf = blk & 1;
+          // scores of this block complete => every earlier MMA is complete: the other Q/dO buffer is free
+          wait(bar_s, s_cnt & 1, 42);
+          s_cnt++;
+          if (it + 1 < n_it) load_q_do(i + 1, buf ^ 1);
+          // P^T and dS^T of this block are in shared memory (and S^T / dP^T have been read out of TMEM)
+          const bool p_ok = wait(bar_p, p_cnt & 1, 45);
+          p_cnt++;
+          if (p_ok) {
+            tc::tc_fence_after();
+            const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dv, desc_k(sPT, ks), desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, desc_k(sDST, ks), desc_mn(sQ, ks), idesc_d, (it > 0 || ks > 0));
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq + (blk & 1) * 64, desc_mn(sDST, ks), desc_mn(sK, ks), idesc_q, ks > 0);
+          }
+          if (it + 1 < n_it && wait(&bar_q[buf ^ 1], ((blk + 1) >> 1) & 1, 43)) {
+            tc::tc_fence_after();
+            issue_scores(buf ^ 1);
+          }
+          tc::mma_commit(bar_s);
+        }
+        // all MMAs of this key tile complete => K, V, Q, dO are free: the mirror tile's loads run under the epilogue
+        wait(bar_s, s_cnt & 1, 44);
+        s_cnt++;
+        if (item + 1 < n_items) {
+          load_kv(kt_second);
+          load_q_do(kt_second, blk & 1);
+        }
+        // the work warps have seen that completion too (otherwise the next commit could lap their parity wait)
+        wait(bar_p, p_cnt & 1, 46);
+        p_cnt++;
+      }
     }
+  } else {
+    // ---------------------------------------------------------------- 16 element-wise warps
+    const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+    const float sl2 = a.scale * LOG2E;
+    const uint64_t sl2x2 = pk2(sl2, sl2);
+    // dQ tile of query block i: TMEM -> swizzled fp32 staging -> TMA add-reduce into the accumulator
+    uint8_t* stage = smem + S::DQS + lg * 8192 + (cq >> 1) * 4096;
+    auto drain_dq = [&](int i, int dbuf) {
+      if (cq == 0 && lane == 0) tc::tma_wait_group_read<0>();   // the previous reduce has finished reading the staging
+      named_bar_sync(1 + lg, 128);
+      uint32_t r[16];
+      tc::tmem_ld16(t_dq + dbuf * 64 + lane_addr + cq * 16, r);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int v = 0; v < 4; v++) {
+        const int unit = (cq & 1) * 4 + v;
+        *reinterpret_cast<uint4*>(stage + lane * 128 + ((unit ^ (lane & 7)) << 4)) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+      }
+      tc::fence_async_smem();
+      tc::tc_fence_before();
+      named_bar_sync(1 + lg, 128);
+      if (cq == 0 && lane == 0) {
+        tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192, h * HD, row0 + i * 128 + lg * 32);
+        tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192 + 4096, h * HD + 32, row0 + i * 128 + lg * 32);
+        tc::tma_commit_group();
+      }
+    };
     // per-query statistics of a block, negated for the packed FMAs; queries past the end give P = 0.  Threads 0..127
-    // hold -lse*log2e, threads 128..255 hold -delta; the values for block i+1 are fetched while block i's MMAs run.
+    // fetch -lse*log2e, threads 128..255 fetch -delta; the values for block i+1 are fetched while block i's MMAs run.
     auto fetch_stat = [&](int i) -> float {
       if (tid >= 256) return 0.f;
       const int q = i * 128 + (tid & 127);
@@ -821,98 +860,86 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_fused_tc_kernel(const
       if (tid < 128) return (q < a.T) ? -a.lse[si] * LOG2E : -INFINITY;
       return (q < a.T) ? -a.delta[si] : 0.f;
     };
-    float stat = fetch_stat(kt);
-    for (int it = 0; it < n_it; it++, blk++) {
-      const int i = kt + it, q0 = i * 128, buf = blk & 1;
-      if (tid < 128) s_nlse[tid] = stat;
-      else if (tid < 256) s_ndelta[tid - 128] = stat;
-      __syncthreads();
-      wait(bar_s, s_cnt & 1, 42);       // S^T, dP^T of this block are complete, and so is everything issued before them
+    int blk = 0, s_cnt = 0;
+    for (int item = 0; item < n_items; item++) {
+      const int kt = item == 0 ? kt_first : kt_second;
+      const int k0 = kt * 128, krow = k0 + row;
+      const int n_it = nq - kt;
+      float stat = fetch_stat(kt);
+      for (int it = 0; it < n_it; it++, blk++) {
+        const int i = kt + it, q0 = i * 128;
+        float* st_buf = s_stat + (blk & 1) * 256;     // double buffered: a fast warp may already write block i+1's values
+        if (tid < 256) st_buf[tid] = stat;
+        named_bar_sync(5, BWDF_WORK_WARPS * 32);
+        const float* s_nlse = st_buf;
+        const float* s_ndelta = st_buf + 128;
+        wait(bar_s, s_cnt & 1, 42);       // S^T, dP^T of this block are complete, and so is everything issued before them
+        s_cnt++;
+        tc::tc_fence_after();
+        {
+          uint32_t rs[32], rd[32];
+          tc::tmem_ld32(t_st + lane_addr + cq * 32, rs);
+          tc::tmem_ld32(t_dpt + lane_addr + cq * 32, rd);
+          tc::tmem_ld_wait();
+          const bool diag = (it == 0);
+#pragma unroll
+          for (int v8 = 0; v8 < 4; v8++) {
+            const int qc = cq * 32 + v8 * 8;
+            float nl[8], nd[8];
+            *reinterpret_cast<float4*>(nl) = *reinterpret_cast<const float4*>(s_nlse + qc);
+            *reinterpret_cast<float4*>(nl + 4) = *reinterpret_cast<const float4*>(s_nlse + qc + 4);
+            *reinterpret_cast<float4*>(nd) = *reinterpret_cast<const float4*>(s_ndelta + qc);
+            *reinterpret_cast<float4*>(nd + 4) = *reinterpret_cast<const float4*>(s_ndelta + qc + 4);
+            uint32_t pw[4], dw[4];
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+              const int e = v8 * 8 + 2 * x;
+              float z0, z1;
+              upk2(fma2(pk2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), sl2x2, pk2(nl[2 * x], nl[2 * x + 1])), z0, z1);
+              float p0 = exp2f(z0), p1 = exp2f(z1);
+              if (diag) {
+                if (q0 + qc + 2 * x < krow) p0 = 0.f;
+                if (q0 + qc + 2 * x + 1 < krow) p1 = 0.f;
+              }
+              const uint64_t t2 = add2(pk2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])), pk2(nd[2 * x], nd[2 * x + 1]));
+              float d0, d1;
+              upk2(mul2(pk2(p0, p1), t2), d0, d1);
+              pw[x] = pack_bf16(p0, p1);
+              dw[x] = pack_bf16(d0, d1);
+            }
+            const uint32_t off = sw_off(row, qc);
+            *reinterpret_cast<uint4*>(smem + S::PT + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+            *reinterpret_cast<uint4*>(smem + S::DST + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+          }
+        }
+        tc::fence_async_smem();
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(bar_p);
+        // while the tensor core works through this block's MMAs: fetch the next block's statistics and move the previous
+        // block's dQ tile (complete since the bar_s wait above, and in the other TMEM buffer) to the accumulator
+        if (it + 1 < n_it) stat = fetch_stat(i + 1);
+        if (it > 0) drain_dq(i - 1, (blk - 1) & 1);
+      }
+      wait(bar_s, s_cnt & 1, 44);   // dV, dK and the last dQ tile of this key tile are complete
       s_cnt++;
       tc::tc_fence_after();
-      if (tid == 0 && it + 1 < n_it) load_q_do(i + 1, buf ^ 1);
-      {
-        uint32_t rs[32], rd[32];
-        tc::tmem_ld32(t_st + lane_addr + cq * 32, rs);
-        tc::tmem_ld32(t_dpt + lane_addr + cq * 32, rd);
-        tc::tmem_ld_wait();
-        const bool diag = (it == 0);
-#pragma unroll
-        for (int v8 = 0; v8 < 4; v8++) {
-          const int qc = cq * 32 + v8 * 8;
-          float nl[8], nd[8];
-          *reinterpret_cast<float4*>(nl) = *reinterpret_cast<const float4*>(s_nlse + qc);
-          *reinterpret_cast<float4*>(nl + 4) = *reinterpret_cast<const float4*>(s_nlse + qc + 4);
-          *reinterpret_cast<float4*>(nd) = *reinterpret_cast<const float4*>(s_ndelta + qc);
-          *reinterpret_cast<float4*>(nd + 4) = *reinterpret_cast<const float4*>(s_ndelta + qc + 4);
-          uint32_t pw[4], dw[4];
-#pragma unroll
-          for (int x = 0; x < 4; x++) {
-            const int e = v8 * 8 + 2 * x;
-            float z0, z1;
-            upk2(fma2(pk2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), sl2x2, pk2(nl[2 * x], nl[2 * x + 1])), z0, z1);
-            float p0 = exp2f(z0), p1 = exp2f(z1);
-            if (diag) {
-              if (q0 + qc + 2 * x < krow) p0 = 0.f;
-              if (q0 + qc + 2 * x + 1 < krow) p1 = 0.f;
-            }
-            const uint64_t t2 = add2(pk2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])), pk2(nd[2 * x], nd[2 * x + 1]));
-            float d0, d1;
-            upk2(mul2(pk2(p0, p1), t2), d0, d1);
-            pw[x] = pack_bf16(p0, p1);
-            dw[x] = pack_bf16(d0, d1);
-          }
-          const uint32_t off = sw_off(row, qc);
-          *reinterpret_cast<uint4*>(smem + S::PT + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-          *reinterpret_cast<uint4*>(smem + S::DST + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
-        }
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(bar_p);   // tells the control warp that this completion has been consumed
+      drain_dq(kt + n_it - 1, (blk - 1) & 1);   // earlier blocks were drained inside the loop
+      if (cq < 2) {   // warps 0-3: dK (scaled, RoPE backward); warps 4-7: dV
+        const bool is_k = cq == 0;
+        bf16* dst = a.out + ((size_t)(row0 + krow)) * 3 * C + (is_k ? C : 2 * C) + h * HD;
+        store_pairs_rope<HD>(dst, (is_k ? t_dk : t_dv) + lane_addr, 0, !*s_abort && krow < a.T, is_k ? a.cosT : nullptr,
+                             is_k ? a.sinT : nullptr, krow, is_k ? a.scale : 1.f);
       }
-      tc::fence_async_smem();
       tc::tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
-        tc::tc_fence_after();
-        if (!*s_abort) {
-          const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
-#pragma unroll
-          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dv, desc_k(sPT, ks), desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
-#pragma unroll
-          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, desc_k(sDST, ks), desc_mn(sQ, ks), idesc_d, (it > 0 || ks > 0));
-#pragma unroll
-          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq + (blk & 1) * 64, desc_mn(sDST, ks), desc_mn(sK, ks), idesc_q, ks > 0);
-        }
-        if (it + 1 < n_it && wait(&bar_q[buf ^ 1], ((blk + 1) >> 1) & 1, 43)) {
-          tc::tc_fence_after();
-          issue_scores(buf ^ 1);
-        }
-        tc::mma_commit(bar_s);
-      }
-      // while the tensor core works through this block's MMAs: fetch the next block's statistics and move the previous
-      // block's dQ tile (complete since the bar_s wait above, and in the other TMEM buffer) to the accumulator
-      if (it + 1 < n_it) stat = fetch_stat(i + 1);
-      if (it > 0) drain_dq(i - 1, (blk - 1) & 1);
     }
-    wait(bar_s, s_cnt & 1, 44);   // dV, dK and the last dQ tile of this key tile are complete; K, V, Q, dO are free
-    s_cnt++;
-    tc::tc_fence_after();
-    if (tid == 0 && item + 1 < n_items) {   // the mirror tile's loads run under this tile's epilogue
-      load_kv(kt_second);
-      load_q_do(kt_second, blk & 1);
-    }
-    drain_dq(kt + n_it - 1, (blk - 1) & 1);   // earlier blocks were drained inside the loop
-    if (cq < 2) {   // warps 0-3: dK (scaled, RoPE backward); warps 4-7: dV
-      const bool is_k = cq == 0;
-      bf16* dst = a.out + ((size_t)(row0 + krow)) * 3 * C + (is_k ? C : 2 * C) + h * HD;
-      store_pairs_rope<HD>(dst, (is_k ? t_dk : t_dv) + lane_addr, 0, !*s_abort && krow < a.T, is_k ? a.cosT : nullptr,
-                           is_k ? a.sinT : nullptr, krow, is_k ? a.scale : 1.f);
-    }
-    tc::tc_fence_before();
-    __syncthreads();   // the accumulators have been read out before the next tile's first MMAs are issued
+    if (cq == 0 && lane == 0) tc::tma_wait_group<0>();
   }
-  if (cq == 0 && lane == 0) tc::tma_wait_group<0>();
   tc::tc_fence_before();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == BWDF_WORK_WARPS) tc::tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // dQ accumulator (fp32 [rows, C]) -> bf16 Q slice of dqkv[rows, 3C], times `scale`, optional RoPE backward; the
@@ -1284,7 +1311,7 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
       static int o0 = set_smem(attn_bwd_fused_tc_kernel, BwdFusedSmem::TOTAL);
       (void)o0;
       dim3 grid_f(((T + 127) / 128 + 1) / 2, H, B);   // a CTA handles a key tile and its mirror
-      attn_bwd_fused_tc_kernel<<<grid_f, BWD_THREADS, BwdFusedSmem::TOTAL, st>>>(*tq, *td, *tacc, a);
+      attn_bwd_fused_tc_kernel<<<grid_f, BWDF_THREADS, BwdFusedSmem::TOTAL, st>>>(*tq, *td, *tacc, a);
       const long groups = (long)B * T * H * (hd / 32);
       attn_dq_finish_k<<<(unsigned)((groups + 255) / 256), 256, 0, st>>>((bf16*)dqkv, dq_acc, (long)B * T, T, H, hd, scale, cosT, sinT);
       cudaError_t e = cudaGetLastError();

@@ -35,6 +35,8 @@ struct BucketArgs {
   int rank, world, bucket, max_buckets, bcast;
   float lr, b1, b2, eps, wd, inv_bc1, inv_bc2, scale;
   const float* dev_hyper;    // optional {lr, 1/bc1, 1/bc2, scale} in device memory (CUDA-graph replay)
+  float* grads_mc;           // optional NVLS multicast address of the gradient buffers: the switch sums all ranks' values
+  bf16* params_mc;           // optional NVLS multicast address of the parameter buffers: one store reaches every rank
   long spin_limit_ns;
 };
 
@@ -103,10 +105,16 @@ __global__ void __launch_bounds__(512) ddp_bucket_kernel(const BucketArgs a) {
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
       const long e = lo + i * 4;
       float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a.grads_mc) {
+        // in-switch reduction: one load returns the fp32 sum over all ranks
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(g.x), "=f"(g.y), "=f"(g.z), "=f"(g.w) : "l"(a.grads_mc + e) : "memory");
+      } else {
 #pragma unroll 4
-      for (int w = 0; w < W; w++) {
-        const float4 t = ld_peer_f4(a.grads[w] + e);
-        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        for (int w = 0; w < W; w++) {
+          const float4 t = ld_peer_f4(a.grads[w] + e);
+          g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        }
       }
       float4 mm = *reinterpret_cast<const float4*>(a.m + e);
       float4 vv = *reinterpret_cast<const float4*>(a.v + e);
@@ -125,7 +133,9 @@ __global__ void __launch_bounds__(512) ddp_bucket_kernel(const BucketArgs a) {
       uint2 o;
       o.x = pack_bf16(p.x, p.y);
       o.y = pack_bf16(p.z, p.w);
-      if (a.bcast) {
+      if (a.bcast && a.params_mc) {
+        asm volatile("multimem.st.relaxed.sys.global.v2.bf16x2 [%0], {%1, %2};" ::"l"(a.params_mc + e), "r"(o.x), "r"(o.y) : "memory");
+      } else if (a.bcast) {
 #pragma unroll 4
         for (int w = 0; w < W; w++) *reinterpret_cast<uint2*>(a.params[w] + e) = o;
       } else {
@@ -189,7 +199,8 @@ MLB_API int mlb_comm_max_world() { return MAX_WORLD; }
 MLB_API int mlb_ddp_bucket(const void* grads_ptrs, const void* params_ptrs, const void* flags_ptrs, float* master, float* m, float* v,
                            int* done_counter, int* epoch_ctr, long off, long n, int rank, int world, int bucket, int max_buckets,
                            int bcast, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2, float scale,
-                           const float* dev_hyper, int ctas, double spin_limit_s, cudaStream_t st) {
+                           const float* dev_hyper, int ctas, double spin_limit_s, float* grads_mc, void* params_mc,
+                           cudaStream_t st) {
   if (world < 1 || world > MAX_WORLD || bucket < 0 || bucket >= max_buckets) return -1;
   if ((off & 3) != 0) return -5;   // float4 path needs 16-byte aligned bucket starts
   BucketArgs a;
@@ -197,7 +208,7 @@ MLB_API int mlb_ddp_bucket(const void* grads_ptrs, const void* params_ptrs, cons
   a.master = master; a.m = m; a.v = v; a.done_counter = done_counter; a.epoch_ctr = epoch_ctr;
   a.off = off; a.n = n; a.rank = rank; a.world = world; a.bucket = bucket; a.max_buckets = max_buckets;
   a.bcast = bcast; a.lr = lr; a.b1 = b1; a.b2 = b2; a.eps = eps; a.wd = wd; a.inv_bc1 = 1.f / bc1; a.inv_bc2 = 1.f / bc2;
-  a.scale = scale; a.dev_hyper = dev_hyper; a.spin_limit_ns = (long)(spin_limit_s * 1e9);
+  a.scale = scale; a.dev_hyper = dev_hyper; a.grads_mc = grads_mc; a.params_mc = (bf16*)params_mc; a.spin_limit_ns = (long)(spin_limit_s * 1e9);
   const long chunk = ((n + world - 1) / world + 3) & ~3L;
   long want = (chunk / 4 + 511) / 512;
   if (want < 1) want = 1;

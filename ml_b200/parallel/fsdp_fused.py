@@ -29,7 +29,7 @@ class FusedFSDP:
         dev, W, r = fs.dev, fs.world, fs.rank
         L = native.lib()
         L.mlb_ddp_bucket.argtypes = [C.c_void_p] * 8 + [C.c_long, C.c_long] + [C.c_int] * 5 + [C.c_float] * 8 + \
-                                    [C.c_void_p, C.c_int, C.c_double, C.c_void_p]
+                                    [C.c_void_p, C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p]
         L.mlb_ddp_bucket.restype = C.c_int
         L.mlb_allgather_pull.argtypes = [C.c_void_p, C.c_void_p, C.c_long, C.c_int, C.c_int, C.c_void_p]
         L.mlb_allgather_pull.restype = C.c_int
@@ -98,7 +98,7 @@ class FusedFSDP:
             self.t_dslot[d].ptr, self.param_tables[ui].data_ptr(), self.t_flags.ptr, master, m, v,
             self.done.data_ptr(), self.epoch.data_ptr(), 0, u.padded, r, fs.world, ui, MAX_BUCKETS, 0,
             h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], bc1, bc2, scale, None, self.rs_ctas, self.spin_limit_s,
-            torch.cuda.current_stream().cuda_stream)
+            None, None, torch.cuda.current_stream().cuda_stream)
         native.LAUNCHES += 1
         if rc != 0:
             raise RuntimeError(f"mlb_ddp_bucket (reduce-scatter + AdamW) failed: {rc}")

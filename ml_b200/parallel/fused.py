@@ -37,7 +37,7 @@ class FusedGradEngine:
         dev = model.device
         L = native.lib()
         L.mlb_ddp_bucket.argtypes = [C.c_void_p] * 8 + [C.c_long, C.c_long] + [C.c_int] * 5 + [C.c_float] * 8 + \
-                                    [C.c_void_p, C.c_int, C.c_double, C.c_void_p]
+                                    [C.c_void_p, C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p]
         L.mlb_ddp_bucket.restype = C.c_int
         maxw = L.mlb_comm_max_world()
         if world > maxw:
@@ -48,6 +48,11 @@ class FusedGradEngine:
         self.t_grads = PeerTable(model.grads, world, group)
         self.t_params = PeerTable(model.params, world, group)
         self.t_flags = PeerTable(self.flags, world, group)
+        # NVLS (in-switch reduction / multicast store) is opt-in: ENTROPY_FUSED_MULTIMEM=1 and a multicast mapping exists
+        self.grads_mc = self.params_mc = None
+        if os.environ.get("ENTROPY_FUSED_MULTIMEM", "0") == "1" and world > 1:
+            if self.t_grads.multicast_ptr and self.t_params.multicast_ptr:
+                self.grads_mc, self.params_mc = self.t_grads.multicast_ptr, self.t_params.multicast_ptr
         self.done = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
         self.epoch = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
         self.bucket_ids = {}
@@ -86,7 +91,7 @@ class FusedGradEngine:
                 self.done.data_ptr(), self.epoch.data_ptr(), off, n, self.rank, self.world, self.bucket_ids[off], MAX_BUCKETS,
                 1 if self.bcast else 0, hyper["lr"], b1, b2, hyper["eps"], hyper["wd"], 1.0 - b1 ** t, 1.0 - b2 ** t, scale,
                 dev_hyper.data_ptr() if dev_hyper is not None else None, self.ctas, self.spin_limit_s,
-                torch.cuda.current_stream().cuda_stream)
+                self.grads_mc, self.params_mc, torch.cuda.current_stream().cuda_stream)
             native.LAUNCHES += 1
             if rc != 0:
                 raise RuntimeError(f"mlb_ddp_bucket failed: {rc}")

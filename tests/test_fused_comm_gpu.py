@@ -238,3 +238,37 @@ def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state():
     line = [l for l in out.splitlines() if l.startswith("RESULT")][0].split()
     assert float(line[1]) < 2e-4, line
     assert int(line[2]) < 0.6 * int(line[3]) and line[4] == "0", line
+
+
+def test_linear_fwd_gather_world1_and_two_shards_on_one_gpu():
+    """All-gather fused into the GEMM: the weight matrix sits inside a sharded unit; the kernel's gather warps pull the
+    shards (here two "ranks" whose shards both live on this GPU, read through the same pointer table a multi-GPU run
+    uses) while the tiles wait on per-piece flags.  Checked against the plain GEMM on the assembled unit, twice
+    (the flags carry epochs, so the second launch must not see stale 'ready' pieces)."""
+    from ml_b200.ops import native
+    from ml_b200.ops import ref
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    M, N, K, pre = 512, 768, 256, 256            # W starts `pre` elements into the unit (a norm weight comes first)
+    world = 2
+    unit_elems = pre + N * K + 1024               # trailing parameters after W
+    shard = (unit_elems + world - 1) // world
+    shard = (shard + 7) // 8 * 8
+    flags = torch.zeros((shard * world * 2 + 16383) // 16384 + 1, dtype=torch.int32, device=dev)
+    ctr = torch.zeros(2, dtype=torch.int32, device=dev)
+    for call in range(2):
+        full = (torch.randn(shard * world, device=dev) * 0.05).to(torch.bfloat16)
+        shards = [full[i * shard:(i + 1) * shard].clone() for i in range(world)]
+        table = torch.tensor([t.data_ptr() for t in shards], dtype=torch.int64, device=dev)
+        slot = torch.zeros(shard * world, dtype=torch.bfloat16, device=dev)
+        x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        native.linear_fwd_gather(out, x, N, K, slot, pre, table, shard, world, flags, ctr)
+        torch.cuda.synchronize()
+        assert native.get_error() == 0
+        assert torch.equal(slot, full)            # the whole unit was gathered, not only W
+        exp = torch.empty(M, N, device=dev)
+        ref.linear_fwd(exp, x, full[pre:pre + N * K].view(N, K))
+        err = (out.float() - exp).abs().max().item()
+        assert err <= 2e-2 + 2e-2 * exp.abs().max().item(), (call, err)
+    assert int(ctr[0]) == 2 and int(ctr[1]) == 0
