@@ -130,3 +130,37 @@ class BatchPipe:
             self.close()
         except Exception:
             pass
+
+
+class RawTokenLoader:
+    """The prototype loader's formats (csrc/src/data_loader.cu:13-180): a `.bin` / `.tokens` file of raw little-endian
+    uint32 tokens without header, or a whitespace-separated text file of token ids.  `next()` returns input ids,
+    position ids and labels shifted within the sample (the last label of a sample is its own token).  Shuffling permutes
+    whole samples (the reference shuffles single tokens, which destroys the sequences)."""
+
+    def __init__(self, path: str, B: int, T: int, shuffle: bool = False, seed: int = 0):
+        import numpy as np
+        if path.endswith(".bin") or path.endswith(".tokens"):
+            arr = np.fromfile(path, dtype="<u4")
+        else:
+            with open(path) as f:
+                arr = np.array([int(t) for t in f.read().split()], dtype=np.uint32)
+        n = arr.size // T
+        if n < B:
+            raise OSError(f"{path}: {arr.size} tokens are fewer than one batch of {B}x{T}")
+        self.samples = torch.from_numpy(arr[:n * T].astype("int64")).view(n, T)
+        self.B, self.T, self.pos = B, T, 0
+        self.order = torch.arange(n)
+        if shuffle:
+            g = torch.Generator().manual_seed(seed)
+            self.order = torch.randperm(n, generator=g)
+
+    def next(self):
+        n = self.order.numel()
+        if self.pos + self.B > n:
+            self.pos = 0
+        ids = self.samples[self.order[self.pos:self.pos + self.B]]
+        self.pos += self.B
+        labels = torch.cat([ids[:, 1:], ids[:, -1:]], dim=1)
+        pos_ids = torch.arange(self.T).expand(self.B, self.T)
+        return ids.to(torch.int32).reshape(-1), pos_ids.to(torch.int32).reshape(-1), labels.to(torch.int32).reshape(-1)

@@ -191,6 +191,7 @@ def mode_bench(argv):
     tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, use_graph=bool(run.graph))
     ids, tgt = bench_batch(B, cfg.T, cfg.V)
     tr.set_batch(ids.to(dev), tgt.to(dev))
+    tr.model.skip = {k for k in ("attn", "mlp", "head", "rope", "norm", "swiglu") if getattr(run, "skip_" + k)}
     print(f"config: V={cfg.V} C={cfg.C} L={cfg.L} H={cfg.H} I={cfg.I} T={cfg.T} B={B}  params={tr.model.np / 1e6:.1f}M")
     for _ in range(3):
         tr.step()

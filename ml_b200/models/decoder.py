@@ -159,15 +159,18 @@ class GPT:
             if "rope" not in self.skip:
                 ops.rope_fwd(qkv, self.cos, self.sin, B, T, H, hd)
             self._mark("F_qkv+rope")
-            ops.attn_fwd(sl(self.atty[l]), self.lse[l][:B], qkv, B, T, H, hd)
+            if "attn" not in self.skip:   # ENTROPY_SKIP_* ablations remove a stage to attribute its time (results are then meaningless)
+                ops.attn_fwd(sl(self.atty[l]), self.lse[l][:B], qkv, B, T, H, hd)
             self._mark("F_attn")
             proj = sl(self.proj)
             ops.linear_fwd(proj, sl(self.atty[l]), self.P(o.o, C, C))
             ops.add_rmsnorm_fwd(sl(self.resid1[l]), sl(self.ln2[l]), sl(self.rstd2[l]), resid_in, proj,
                                 self.P(o.ln2, C), c.eps)
-            ops.linear_fwd(sl(self.gu[l]), sl(self.ln2[l]), self.P(o.gate, 2 * I, C))
-            ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
-            ops.linear_fwd(proj, sl(self.sw[l]), self.P(o.down, C, I))
+            if "mlp" not in self.skip:
+                ops.linear_fwd(sl(self.gu[l]), sl(self.ln2[l]), self.P(o.gate, 2 * I, C))
+                if "swiglu" not in self.skip:
+                    ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
+                ops.linear_fwd(proj, sl(self.sw[l]), self.P(o.down, C, I))
             if l + 1 == c.L and not has_head:
                 # stage boundary: plain residual add; the next stage starts with its own first norm
                 ops.residual_add(sl(self.resid2[l]), sl(self.resid1[l]), proj)
@@ -181,7 +184,8 @@ class GPT:
             ops.add_rmsnorm_fwd(sl(self.resid2[l]), nout, nrstd, sl(self.resid1[l]), proj, nw, c.eps)
             resid_in = sl(self.resid2[l])
             self._mark("F_mlp+norm")
-        ops.linear_fwd(self.logits[:BT], sl(self.lnf_out), self.P(Lo.off_lm, c.V, C))
+        if "head" not in self.skip:
+            ops.linear_fwd(self.logits[:BT], sl(self.lnf_out), self.P(Lo.off_lm, c.V, C))
         self._mark("F_lmhead")
         return self.logits[:BT]
 

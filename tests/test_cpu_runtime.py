@@ -203,3 +203,20 @@ def test_cli_train_checkpoint_resume(tmp_path):
     la = [l for l in b.stdout.splitlines() if l.startswith("step    15")][0].split("|")[1]
     lc = [l for l in c.stdout.splitlines() if l.startswith("step    15")][0].split("|")[1]
     assert la == lc, (la, lc)
+
+
+def test_raw_token_loader_formats(tmp_path):
+    import numpy as np
+    from ml_b200.data import RawTokenLoader
+    arr = np.arange(0, 64, dtype="<u4")
+    p = tmp_path / "t.tokens"
+    arr.tofile(p)
+    ld = RawTokenLoader(str(p), B=2, T=8)
+    ids, pos, lab = ld.next()
+    assert ids.view(2, 8)[1].tolist() == list(range(8, 16))
+    assert lab.view(2, 8)[0].tolist() == [1, 2, 3, 4, 5, 6, 7, 7] and pos.view(2, 8)[1].tolist() == list(range(8))
+    txt = tmp_path / "t.txt"
+    txt.write_text(" ".join(str(i) for i in range(40)))
+    ld2 = RawTokenLoader(str(txt), B=1, T=10, shuffle=True, seed=1)
+    seen = {int(ld2.next()[0][0]) for _ in range(4)}
+    assert seen == {0, 10, 20, 30}          # whole samples are permuted, sequences stay intact
