@@ -171,7 +171,7 @@ def run_ours(args):
     n = args.gpus
     cfg = Config(**MODEL)
     run = RunConfig.from_env()
-    run.comm = os.environ.get("ENTROPY_COMM", "fused")
+    run.comm = os.environ.get("ENTROPY_COMM", "fused" if world > 1 else "nccl")   # one GPU: nothing to reduce, plain AdamW
     B, T = B_PER_GPU, cfg.T
     tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, world=world, rank=rank, use_graph=not args.no_graph)
     ids, tgt = bench_batch(B, T, 50257, rank)

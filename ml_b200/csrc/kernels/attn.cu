@@ -873,6 +873,8 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
         named_bar_sync(5, BWDF_WORK_WARPS * 32);
         const float* s_nlse = st_buf;
         const float* s_ndelta = st_buf + 128;
+        // the next block's statistics are requested now, a whole element-wise phase before they are needed
+        if (it + 1 < n_it) stat = fetch_stat(i + 1);
         wait(bar_s, s_cnt & 1, 42);       // S^T, dP^T of this block are complete, and so is everything issued before them
         s_cnt++;
         tc::tc_fence_after();
@@ -916,9 +918,8 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(bar_p);
-        // while the tensor core works through this block's MMAs: fetch the next block's statistics and move the previous
-        // block's dQ tile (complete since the bar_s wait above, and in the other TMEM buffer) to the accumulator
-        if (it + 1 < n_it) stat = fetch_stat(i + 1);
+        // while the tensor core works through this block's MMAs: move the previous block's dQ tile (complete since the
+        // bar_s wait above, and in the other TMEM buffer) to the accumulator
         if (it > 0) drain_dq(i - 1, (blk - 1) & 1);
       }
       wait(bar_s, s_cnt & 1, 44);   // dV, dK and the last dQ tile of this key tile are complete

@@ -61,6 +61,7 @@ struct GemmArgs {
   int M, N, K;       // logical problem: D[M,N], reduction K
   int ldo;           // output row pitch in elements
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
+  int a3d, b3d;      // MN-major operand fetched through a 3-D tensor map (one TMA per stage) instead of 64-wide 2-D boxes
 };
 
 __device__ __forceinline__ bool wait_piece(const int* flag, int epoch, long limit_ns) {
@@ -139,13 +140,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc::tma_load_2d(sA, &tmA, &full[stage], kb * BK, m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BM / 64; c++) tc::tma_load_2d(sA + c * 8192, &tmA, &full[stage], m0 + c * 64, kb * BK);
+            if (g.a3d) tc::tma_load_3d(sA, &tmA, &full[stage], 0, kb * BK, m0 / 64);
+            else
+              for (int c = 0; c < BM / 64; c++) tc::tma_load_2d(sA + c * 8192, &tmA, &full[stage], m0 + c * 64, kb * BK);
           }
           if (!B_MN) {
             tc::tma_load_2d(sB, &tmB, &full[stage], kb * BK, n0);
           } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; c++) tc::tma_load_2d(sB + c * 8192, &tmB, &full[stage], n0 + c * 64, kb * BK);
+            if (g.b3d) tc::tma_load_3d(sB, &tmB, &full[stage], 0, kb * BK, n0 / 64);
+            else
+              for (int c = 0; c < BN / 64; c++) tc::tma_load_2d(sB + c * 8192, &tmB, &full[stage], n0 + c * 64, kb * BK);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -181,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (ok) tc::mma_commit(&acc_full[acc]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     // Each warp owns 32 accumulator rows (its TMEM lane group).  A 128-byte-wide slab of those rows (64 bf16 or
     // 32 fp32 columns) is converted into a swizzled 4 KB staging buffer and handed to TMA: a tiled store for bf16
@@ -369,8 +374,29 @@ const CUtensorMap* mlb_tmap_cached(const void* base, uint64_t rows, uint64_t col
   return m;
 }
 
+const CUtensorMap* mlb_tmap_mn3d_cached(const void* base, uint64_t k_rows, uint64_t mn_cols, uint64_t pitch_elems, uint32_t chunks) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc || (mn_cols % 64) != 0 || ((uintptr_t)base & 15) || ((pitch_elems * 2) & 15)) return nullptr;
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  TmapKey key(base, k_rows, mn_cols, pitch_elems, chunks, 0xffffffffu, -3);
+  auto it = g_tmaps.find(key);
+  if (it != g_tmaps.end()) return it->second;
+  CUtensorMap* m = new CUtensorMap;
+  cuuint64_t dims[3] = {64, k_rows, mn_cols / 64};
+  cuuint64_t strides[2] = {pitch_elems * 2, 128};
+  cuuint32_t box[3] = {64, 64, chunks};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { delete m; g_tmaps[key] = nullptr; return nullptr; }
+  g_tmaps[key] = m;
+  return m;
+}
+
 namespace {
 
+int g_use_3d = 1;            // tuning hook: 0 = always use 64-wide 2-D boxes for MN-major operands
 int g_num_sms = 0;
 int num_sms() {
   if (!g_num_sms) {
@@ -463,8 +489,13 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   }
   g.kb_per_split = ceil_div_i(g.kb_total, g.splits);
   g.splits = ceil_div_i(g.kb_total, g.kb_per_split);
-  const CUtensorMap* tmA = A_MN ? mlb_tmap_cached(A, K, M, lda, 64, 64) : mlb_tmap_cached(A, M, K, lda, BM, 64);
-  const CUtensorMap* tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, BN, 64);
+  g.a3d = g.b3d = 0;
+  const CUtensorMap* tmA = nullptr;
+  const CUtensorMap* tmB = nullptr;
+  if (A_MN && g_use_3d) { tmA = mlb_tmap_mn3d_cached(A, K, M, lda, BM / 64); g.a3d = tmA != nullptr; }
+  if (B_MN && g_use_3d) { tmB = mlb_tmap_mn3d_cached(B, K, N, ldb, BN / 64); g.b3d = tmB != nullptr; }
+  if (!tmA) tmA = A_MN ? mlb_tmap_cached(A, K, M, lda, 64, 64) : mlb_tmap_cached(A, M, K, lda, BM, 64);
+  if (!tmB) tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, BN, 64);
   const CUtensorMap* tmD = (EPI == EPI_BF16) ? mlb_tmap_cached(out, M, N, ldo, 32, 64, 2) : mlb_tmap_cached(out, M, N, ldo, 32, 32, 4);
   if (!tmA || !tmB || !tmD) return -2;
   if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
@@ -503,7 +534,7 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   GemmArgs g;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
-  g.splits = 1; g.kb_per_split = g.kb_total;
+  g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0;
   GatherArgs ga;
   ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
   ga.b_lo_vec = w_off_elems / 8; ga.b_hi_vec = (w_off_elems + (long)N * K) / 8; ga.b_row_vec = K / 8;
@@ -519,5 +550,6 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
 MLB_API void mlb_gemm_force_simt(int on) { g_force_simt = on; }
 MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
 MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }
+MLB_API void mlb_gemm_use_3d_maps(int on) { g_use_3d = on; }
 
 MLB_DEFINE_ERROR_WORD(gemm)

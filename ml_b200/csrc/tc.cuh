@@ -93,6 +93,12 @@ template <int N>
 __device__ __forceinline__ void tma_wait_group() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -191,6 +197,11 @@ __device__ __forceinline__ bool elect_one() {
 // `elem_bytes` = 2 (bf16) or 4 (fp32; box_cols is then 32 so that a box row is still 128 bytes).
 bool mlb_make_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
                    uint32_t box_rows, uint32_t box_cols, int elem_bytes);
+// MN-major operand stored [k_rows, mn_cols] (mn contiguous, mn_cols a multiple of 64): a 3-D view
+// {64 columns, k rows (pitch), mn_cols/64 chunks (128 bytes apart)} whose box {64, 64, chunks} lands in shared memory as
+// `chunks` consecutive [64 rows x 128 B] swizzled blocks: the MN-major UMMA layout, fetched by ONE TMA instruction.
+// Returns nullptr if the shape does not allow it or the driver rejects the map (callers fall back to 2-D boxes).
+const CUtensorMap* mlb_tmap_mn3d_cached(const void* base, uint64_t k_rows, uint64_t mn_cols, uint64_t pitch_elems, uint32_t chunks);
 // Cached lookup (key = all arguments); the returned pointer stays valid for the life of the process.
 const CUtensorMap* mlb_tmap_cached(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
                                    uint32_t box_rows, uint32_t box_cols = 64, int elem_bytes = 2);

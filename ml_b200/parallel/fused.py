@@ -56,6 +56,10 @@ class FusedGradEngine:
         self.done = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
         self.epoch = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
         self.bucket_ids = {}
+        bl = buckets if buckets is not None else model.layout.slices_backward_order()
+        lo = min(off for _, off, _ in bl)
+        hi = max(off + n for _, off, n in bl)
+        self.whole = (lo, hi - lo)          # the union of all buckets is one contiguous range of the flat buffer
         # `model` is anything with flat .grads / .params / .master / .m / .v on one device (decoder or vision tower);
         # `buckets` = [(name, offset, numel)] defaults to the decoder's backward order
         for i, (name, off, n) in enumerate(buckets if buckets is not None else model.layout.slices_backward_order()):
@@ -63,6 +67,7 @@ class FusedGradEngine:
                 raise ValueError(f"bucket {name} starts at element {off}: the fused kernel needs 16-byte aligned buckets "
                                  "(use ENTROPY_COMM=nccl for this shape)")
             self.bucket_ids[off] = i
+        self.bucket_ids.setdefault(self.whole[0], 0)
         assert len(self.bucket_ids) <= MAX_BUCKETS
         self.stream = torch.cuda.Stream(dev, priority=-1)
         self.used = False
@@ -97,8 +102,11 @@ class FusedGradEngine:
                 raise RuntimeError(f"mlb_ddp_bucket failed: {rc}")
 
     def finish(self):
-        for args in self.pending:
-            self._launch(*args)
+        if self.pending:
+            # not overlapped: every bucket is final by now, so ONE launch (one barrier pair) covers the whole flat buffer
+            _, _, scale, hyper, t, dev_hyper = self.pending[-1]
+            total = self.whole[1]
+            self._launch(self.whole[0], total, scale, hyper, t, dev_hyper)
         self.pending = []
         if self.used:
             torch.cuda.current_stream().wait_stream(self.stream)
