@@ -53,6 +53,8 @@ def bench_gemm(a):
     dev = torch.device("cuda")
     tf_peak, _, how = peaks()
     M = a.M
+    nat.lib().mlb_gemm_use_pairs(a.pairs)
+    print("kernel:", "256x256 tile per CTA pair (cta_group::2)" if a.pairs else "128x256 tile per CTA")
     shapes = [(3 * a.C, a.C, "qkv"), (a.C, a.C, "o"), (2 * a.I, a.C, "gate|up"), (a.C, a.I, "down"), (a.V, a.C, "lm_head")]
     print(f"{'shape':<10}{'op':<5}{'ours us':>10}{'TFLOP/s':>10}{'frac of ' + how:>18}{'cuBLAS us':>11}{'TFLOP/s':>10}")
     for N, K, nm in shapes:
@@ -153,6 +155,7 @@ def once(a):
             nat.ce_fwd_bwd(ls, lg, tg, 1.0 / rows)
             nat.adamw(ma, p, g, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.5, 1.0)
     else:
+        nat.lib().mlb_gemm_use_pairs(a.pairs)
         M, N, K = a.M, 3 * a.C, a.C
         x = torch.randn(M, K, device=dev).bfloat16()
         W = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
@@ -182,6 +185,7 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
+    ap.add_argument("--pairs", type=int, default=1, help="GEMM: 1 = CTA-pair kernel (cta_group::2), 0 = one CTA per tile")
     a = ap.parse_args()
     {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
 

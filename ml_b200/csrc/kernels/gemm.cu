@@ -278,6 +278,191 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * BN);
 }
 
+// ------------------------------------------------------------------ CTA-pair variant (cta_group::2)
+// A 1-CTA 128x256 tile needs 48 KB of operands per 64-deep K step, more than an SM can pull from L2 in the ~512 cycles
+// the MMAs of that step take.  Here two CTAs of a cluster share a 256 x 256 tile: each stages its 128 rows of A and
+// 128 of the 256 rows of B (32 KB per step and SM, a third less L2 traffic per FLOP), the leader issues
+// tcgen05.mma.cta_group::2 with M = 256, and each CTA drains its own 128 TMEM lanes x 256 columns.
+//   full[s]      leader only: one arrive.expect_tx by the leader's producer for BOTH CTAs' bytes; both producers' TMA
+//                loads complete on it
+//   empty[s]     one per CTA; the leader's MMA thread commits to both
+//   acc_full[a]  one per CTA; committed to both
+//   acc_empty[a] leader only, 8 arrivals: the four epilogue warps of each CTA (the peer's arrive remotely)
+// Persistent: cluster c handles pair-tiles c, c + nclusters, ...; all waits are bounded as in the 1-CTA kernel, and both
+// CTAs meet at a cluster barrier before TMEM is released so neither outlives remote accesses to it.
+struct Gemm2Smem {
+  static constexpr int A_BYTES = 128 * BK * 2;    // this CTA's rows of A
+  static constexpr int B_BYTES = 128 * BK * 2;    // this CTA's half of B
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 6;
+  static constexpr int STAGING_BYTES = 4 * 2 * 4096;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + 1024;
+};
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
+  using S = Gemm2Smem;
+  constexpr int STAGES = S::STAGES;
+  constexpr int BN = 256, PM = 256;    // pair tile
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* full = (uint64_t*)(staging + S::STAGING_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = tc::cluster_ctarank();          // 0 = leader
+  const int cid = (int)tc::cluster_id_x(), ncl = (int)tc::cluster_count_x();
+  const int total_tiles = g.tiles_m * g.tiles_n * g.splits;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; i++) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; i++) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 8); }
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tmA);
+    tc::tma_prefetch_desc(&tmB);
+    tc::tma_prefetch_desc(&tmD);
+  }
+  if (warp == 1) tc::tmem_alloc_pair(tmem_slot, 2 * BN);
+  tc::tc_fence_before();
+  tc::cluster_sync();      // barriers of both CTAs initialised, TMEM of both allocated
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (one per CTA)
+    if (tc::elect_one()) {
+      int stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = cid; t < total_tiles && ok; t += ncl) {
+        const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n, sp = t / (g.tiles_m * g.tiles_n);
+        const int m0 = mt * PM + (int)rank * 128, n0 = nt * BN + (int)rank * 128;
+        const int kb0 = sp * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+        for (int kb = kb0; kb < kb1; kb++) {
+          if (!tc::mbar_wait(&empty[stage], phase ^ 1, 0x21)) { ok = false; break; }
+          uint8_t* sA = smem + stage * S::STAGE_BYTES;
+          uint8_t* sB = sA + S::A_BYTES;
+          const uint32_t bar = tc::mapa_u32(tc::smem_u32(&full[stage]), 0);
+          if (rank == 0) tc::mbar_expect_tx(&full[stage], 2 * S::STAGE_BYTES);
+          if (!A_MN) {
+            tc::tma_load_2d_pair(sA, &tmA, bar, kb * BK, m0);
+          } else {
+            if (g.a3d) tc::tma_load_3d_pair(sA, &tmA, bar, 0, kb * BK, m0 / 64);
+            else
+              for (int c = 0; c < 2; c++) tc::tma_load_2d_pair(sA + c * 8192, &tmA, bar, m0 + c * 64, kb * BK);
+          }
+          if (!B_MN) {
+            tc::tma_load_2d_pair(sB, &tmB, bar, kb * BK, n0);
+          } else {
+            if (g.b3d) tc::tma_load_3d_pair(sB, &tmB, bar, 0, kb * BK, n0 / 64);
+            else
+              for (int c = 0; c < 2; c++) tc::tma_load_2d_pair(sB + c * 8192, &tmB, bar, n0 + c * 64, kb * BK);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+    if (rank == 0 && tc::elect_one()) {
+      constexpr uint32_t idesc = tc::idesc_bf16(PM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      for (int t = cid; t < total_tiles && ok; t += ncl, it++) {
+        const int sp = t / (g.tiles_m * g.tiles_n);
+        const int kb0 = sp * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+        const int acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, 0x22)) { ok = false; break; }
+        tc::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; kb++) {
+          if (!tc::mbar_wait(&full[stage], phase, 0x23)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t sA = tc::smem_u32(smem + stage * S::STAGE_BYTES);
+          const uint32_t sB = sA + S::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; k++) {
+            const uint64_t da = A_MN ? tc::smem_desc_sw128(sA + k * 2048, 8192, 1024) : tc::smem_desc_sw128(sA + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? tc::smem_desc_sw128(sB + k * 2048, 8192, 1024) : tc::smem_desc_sw128(sB + k * 32, 16, 1024);
+            tc::mma_bf16_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc::mma_commit_pair(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc::mma_commit_pair(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5 of each CTA)
+    const int lg = warp & 3;
+    uint8_t* my_stage = staging + lg * 8192;
+    constexpr int SLAB_COLS = (EPI == EPI_BF16) ? 64 : 32;
+    int it = 0, slab = 0;
+    bool ok = true;
+    for (int t = cid; t < total_tiles && ok; t += ncl, it++) {
+      const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n;
+      const int m0 = mt * PM + (int)rank * 128, n0 = nt * BN;
+      const int acc = it & 1, acc_phase = (it >> 1) & 1;
+      if (!tc::mbar_wait(&acc_full[acc], acc_phase, 0x24)) { ok = false; break; }
+      tc::tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
+      const bool rows_live = (m0 + lg * 32) < g.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / SLAB_COLS; c++) {
+        uint8_t* buf = my_stage + (slab & 1) * 4096;
+        uint32_t r[32], r2[32];
+        tc::tmem_ld32(taddr + c * SLAB_COLS, r);
+        if (EPI == EPI_BF16) tc::tmem_ld32(taddr + c * SLAB_COLS + 32, r2);
+        tc::tmem_ld_wait();
+        const int col0 = n0 + c * SLAB_COLS;
+        if (!rows_live || col0 >= g.N) continue;   // warp-uniform
+        if (lane == 0) tc::tma_wait_group_read<1>();
+        __syncwarp();
+        uint8_t* rowp = buf + lane * 128;
+        if (EPI == EPI_BF16) {
+#pragma unroll
+          for (int v = 0; v < 8; v++) {
+            const uint32_t* src = (v < 4) ? &r[v * 8] : &r2[(v - 4) * 8];
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1]));
+            pk.y = pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3]));
+            pk.z = pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5]));
+            pk.w = pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7]));
+            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < 8; v++) {
+            uint4 pk = make_uint4(r[v * 4 + 0], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+            *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = pk;
+          }
+        }
+        tc::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (EPI == EPI_BF16) tc::tma_store_2d(&tmD, buf, col0, m0 + lg * 32);
+          else tc::tma_reduce_add_2d(&tmD, buf, col0, m0 + lg * 32);
+          tc::tma_commit_group();
+        }
+        slab++;
+      }
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_empty[acc]), 0));
+    }
+    if (lane == 0) tc::tma_wait_group<0>();
+  }
+  tc::tc_fence_before();
+  tc::cluster_sync();      // no CTA frees TMEM or exits while its peer may still signal or read it
+  if (warp == 1) tc::tmem_dealloc_pair(tmem_base, 2 * BN);
+}
+
 // ------------------------------------------------------------------ SIMT fallback (any shape / alignment)
 // D[m,n] = sum_k A[m*sam + k*sak] * B[n*sbn + k*sbk]; 64x64 tile, 16x16 threads, 4x4 per thread.
 template <int EPI>
@@ -429,6 +614,35 @@ int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap*
   return (int)cudaGetLastError();
 }
 
+// CTA-pair kernel: one cluster of two CTAs per SM pair; the grid is sized from the number of clusters that can be
+// resident at once (a GPC with an odd number of usable SMs leaves one without a partner), so the static tile
+// schedule never waits for a second wave of CTAs.
+int g_use_pairs = 1;         // tuning hook: 0 = always the 1-CTA kernel
+template <bool A_MN, bool B_MN, int EPI>
+int launch_tc2(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, const GemmArgs& g, cudaStream_t st) {
+  auto kern = gemm_tc2_kernel<A_MN, B_MN, EPI>;
+  static int max_clusters = -1;
+  if (max_clusters < 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Smem::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_sms() & ~1);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Gemm2Smem::TOTAL;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = num_sms() / 2; }
+    max_clusters = n < num_sms() / 2 ? n : num_sms() / 2;
+  }
+  int total = g.tiles_m * g.tiles_n * g.splits;
+  int cap = max_clusters;
+  if (g_max_ctas > 0 && g_max_ctas / 2 < cap) cap = g_max_ctas / 2 > 0 ? g_max_ctas / 2 : 1;
+  int clusters = total < cap ? total : cap;
+  kern<<<2 * clusters, GEMM_THREADS, Gemm2Smem::TOTAL, st>>>(*tmA, *tmB, *tmD, g);
+  return (int)cudaGetLastError();
+}
+int pair_clusters() { return (g_max_ctas > 0 ? g_max_ctas : num_sms()) / 2; }
+
 // Cooperative launch of the gather variant (all CTAs must be co-resident because tiles wait on other CTAs' pieces).
 template <int BN, bool B_MN>
 int launch_tc_gather(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, GemmArgs g, GatherArgs ga, cudaStream_t st) {
@@ -467,15 +681,16 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
     return (int)cudaGetLastError();
   }
   const int BN = (N > 128) ? 256 : 128;
+  const bool pairs = g_use_pairs && BN == 256 && M > 128;   // 256 x 256 tile shared by a CTA pair
   GemmArgs g;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
-  g.tiles_m = ceil_div_i(M, BM);
+  g.tiles_m = ceil_div_i(M, pairs ? 256 : BM);
   g.tiles_n = ceil_div_i(N, BN);
   g.kb_total = ceil_div_i(K, BK);
   g.splits = 1;
   if (EPI == EPI_F32_ADD) {
     // split the reduction so the persistent grid is filled: choose the split count with the best last-wave fill
-    int tiles = g.tiles_m * g.tiles_n, sms = g_max_ctas > 0 ? g_max_ctas : num_sms();
+    int tiles = g.tiles_m * g.tiles_n, sms = pairs ? pair_clusters() : (g_max_ctas > 0 ? g_max_ctas : num_sms());
     int best = 1;
     double best_eff = 0;
     for (int s = 1; s <= 32; s++) {
@@ -493,11 +708,13 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   const CUtensorMap* tmA = nullptr;
   const CUtensorMap* tmB = nullptr;
   if (A_MN && g_use_3d) { tmA = mlb_tmap_mn3d_cached(A, K, M, lda, BM / 64); g.a3d = tmA != nullptr; }
-  if (B_MN && g_use_3d) { tmB = mlb_tmap_mn3d_cached(B, K, N, ldb, BN / 64); g.b3d = tmB != nullptr; }
+  const int b_rows = pairs ? 128 : BN;   // rows of B one CTA stages
+  if (B_MN && g_use_3d) { tmB = mlb_tmap_mn3d_cached(B, K, N, ldb, b_rows / 64); g.b3d = tmB != nullptr; }
   if (!tmA) tmA = A_MN ? mlb_tmap_cached(A, K, M, lda, 64, 64) : mlb_tmap_cached(A, M, K, lda, BM, 64);
-  if (!tmB) tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, BN, 64);
+  if (!tmB) tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, b_rows, 64);
   const CUtensorMap* tmD = (EPI == EPI_BF16) ? mlb_tmap_cached(out, M, N, ldo, 32, 64, 2) : mlb_tmap_cached(out, M, N, ldo, 32, 32, 4);
   if (!tmA || !tmB || !tmD) return -2;
+  if (pairs) return launch_tc2<A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
   if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
   return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
 }
@@ -551,5 +768,6 @@ MLB_API void mlb_gemm_force_simt(int on) { g_force_simt = on; }
 MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
 MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }
 MLB_API void mlb_gemm_use_3d_maps(int on) { g_use_3d = on; }
+MLB_API void mlb_gemm_use_pairs(int on) { g_use_pairs = on; }
 
 MLB_DEFINE_ERROR_WORD(gemm)

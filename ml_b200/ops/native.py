@@ -32,6 +32,8 @@ def lib():
         "mlb_gemm_force_simt": [_i32],
         "mlb_gemm_set_max_ctas": [_i32],
         "mlb_gemm_set_splits": [_i32],
+        "mlb_gemm_use_3d_maps": [_i32],
+        "mlb_gemm_use_pairs": [_i32],
         "mlb_attn_force_simt": [_i32],
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],

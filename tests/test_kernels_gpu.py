@@ -42,11 +42,19 @@ def _no_kernel_error():
 
 # ------------------------------------------------------------------ GEMM
 GEMM_SHAPES = [(256, 256, 128), (384, 768, 768), (1024, 2304, 768), (512, 4096, 768), (300, 520, 264), (128, 128, 64),
-               (2048, 768, 2048), (256, 1000, 512)]
+               (2048, 768, 2048), (256, 1000, 512), (4096 + 136, 776, 392)]
+
+
+@pytest.fixture(params=[1, 0], ids=["cta_pair", "single_cta"])
+def gemm_mode(request):
+    """Large products have two tcgen05 kernels: a 256x256 tile shared by a CTA pair (cta_group::2), or 128x256 per CTA."""
+    nat().lib().mlb_gemm_use_pairs(request.param)
+    yield request.param
+    nat().lib().mlb_gemm_use_pairs(1)
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-def test_linear_fwd(M, N, K):
+def test_linear_fwd(M, N, K, gemm_mode):
     torch.manual_seed(0)
     x, W = rnd(M, K), rnd(N, K, scale=0.05)
     out, exp = torch.empty(M, N, device=dev(), dtype=torch.bfloat16), torch.empty(M, N, device=dev())
@@ -56,7 +64,7 @@ def test_linear_fwd(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-def test_linear_dx(M, N, K):
+def test_linear_dx(M, N, K, gemm_mode):
     torch.manual_seed(1)
     dout, W = rnd(M, N), rnd(N, K, scale=0.05)
     dx, exp = torch.empty(M, K, device=dev(), dtype=torch.bfloat16), torch.empty(M, K, device=dev())
@@ -66,7 +74,7 @@ def test_linear_dx(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES + [(16384, 768, 768)])
-def test_linear_dw_accumulates(M, N, K):
+def test_linear_dw_accumulates(M, N, K, gemm_mode):
     torch.manual_seed(2)
     dout, x = rnd(M, N, scale=0.1), rnd(M, K)
     dW = torch.randn(N, K, device=dev())

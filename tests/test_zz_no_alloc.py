@@ -6,6 +6,7 @@ check is against the regular entry point (caller-provided scratch), twice in a r
 the previous call's contents.  This file sorts last on purpose, so a run that stops at the first failure has already
 run every other test; it also passes on its own in a fresh process."""
 import ctypes as C
+import gc
 
 import pytest
 import torch
@@ -41,12 +42,19 @@ def test_no_alloc_entry_matches_regular_entry_twice(rows, Cw):
         native.rmsnorm_bwd(dx_ref, dw_ref, dy, x, w, rstd, add)          # regular entry point, caller scratch
         dx, dw = torch.empty_like(x), dw0.clone()
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated(dev)
-        rc = fn(dx.data_ptr(), dw.data_ptr(), dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), add.data_ptr(),
-                rows, Cw, st)
-        assert rc == 0, (rc, L.mlb_rmsnorm_bwd_noalloc_error())
-        torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated(dev) == before
+        # tensors of earlier tests must not be collected between the two readings: collect now, then hold the collector
+        gc.collect()
+        gc.disable()
+        try:
+            before, free_before = torch.cuda.memory_allocated(dev), torch.cuda.mem_get_info(dev)[0]
+            rc = fn(dx.data_ptr(), dw.data_ptr(), dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), add.data_ptr(),
+                    rows, Cw, st)
+            assert rc == 0, (rc, L.mlb_rmsnorm_bwd_noalloc_error())
+            torch.cuda.synchronize()
+            assert torch.cuda.memory_allocated(dev) == before
+            assert torch.cuda.mem_get_info(dev)[0] >= free_before     # the driver handed out no device memory either
+        finally:
+            gc.enable()
         err = (dx.float() - dx_ref.float()).abs().max().item()
         assert err <= 2e-2 + 2e-2 * dx_ref.float().abs().max().item(), (call, err)
         errw = (dw - dw_ref).abs().max().item()
