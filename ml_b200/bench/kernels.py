@@ -2,6 +2,7 @@
 train/gemm_bench.cu, train/attn_bench.cu, train/norm_bench2.cu).
 
     python -m ml_b200.bench.kernels gemm  [--M 16384]           tcgen05 GEMMs on the model's shapes vs torch.matmul (cuBLAS)
+    python -m ml_b200.bench.kernels layouts [--K 8192]          main-loop cost per 64-deep step for K-major / MN-major operands
     python -m ml_b200.bench.kernels attn  [--B 16 --T 1024]     flash attention fwd / bwd vs torch SDPA
     python -m ml_b200.bench.kernels norm                        RMSNorm fwd / add+norm / bwd, CE, AdamW, SwiGLU bandwidth
     python -m ml_b200.bench.kernels once  --case attn|gemm      a few un-timed launches (what an `ncu` capture wraps)
@@ -54,7 +55,9 @@ def bench_gemm(a):
     tf_peak, _, how = peaks()
     M = a.M
     nat.lib().mlb_gemm_use_pairs(a.pairs)
-    print("kernel:", "256x256 tile per CTA pair (cta_group::2)" if a.pairs else "128x256 tile per CTA")
+    nat.lib().mlb_gemm_epilogue_mode(a.epi)
+    nat.lib().mlb_gemm_streamk(a.streamk)
+    print("kernel:", f"256x256 tile per CTA pair (cta_group::2), epilogue mode {a.epi}" if a.pairs else "128x256 tile per CTA")
     shapes = [(3 * a.C, a.C, "qkv"), (a.C, a.C, "o"), (2 * a.I, a.C, "gate|up"), (a.C, a.I, "down"), (a.V, a.C, "lm_head")]
     print(f"{'shape':<10}{'op':<5}{'ours us':>10}{'TFLOP/s':>10}{'frac of ' + how:>18}{'cuBLAS us':>11}{'TFLOP/s':>10}")
     for N, K, nm in shapes:
@@ -72,6 +75,41 @@ def bench_gemm(a):
             t, tl = timeit(ours, a.iters, a.warm), timeit(lib, a.iters, a.warm)
             print(f"{nm:<10}{op:<5}{t * 1e3:>10.1f}{fl / t / 1e9:>10.0f}{fl / t / 1e9 / tf_peak:>18.2f}{tl * 1e3:>11.1f}{fl / tl / 1e9:>10.0f}")
         del x, W, out, dout, dx, dW, dWb
+    print("kernel error word:", nat.get_error())
+
+
+def bench_layouts(a):
+    """Main-loop rate of the four operand layouts: every CTA pair gets exactly one 256x256 tile with a long reduction
+    (one epilogue per cluster), so time / k-blocks is the cost of one 64-deep step."""
+    dev = torch.device("cuda")
+    nat.lib().mlb_gemm_use_pairs(a.pairs)
+    M, N, K = 256 * 74, 256, a.K
+    print(f"M={M} N={N} K={K}: one tile per CTA pair, {K // 64} k-blocks each")
+    for a_mn in (False, True):
+        for b_mn in (False, True):
+            A = torch.randn((K, M) if a_mn else (M, K), device=dev).bfloat16()
+            B = torch.randn((K, N) if b_mn else (N, K), device=dev).bfloat16()
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            t = timeit(lambda: nat.gemm(out, A, B, a_mn, b_mn), a.iters, a.warm)
+            ref = (A.t() if a_mn else A)[:512].float() @ (B if b_mn else B.t()).float()
+            err = (out[:512].float() - ref).abs().max().item() / ref.abs().max().item()
+            fl = 2.0 * M * N * K
+            print(f"A {'MN' if a_mn else 'K '}-major  B {'MN' if b_mn else 'K '}-major: {t * 1e3:8.1f} us  {fl / t / 1e9:6.0f} TFLOP/s  "
+                  f"{t * 1e6 / (K // 64):6.1f} ns per k-block   rel err {err:.1e}")
+            del A, B, out
+    # epilogue-bound case: one k-block per tile, so the time is the output traffic (bf16 stores / fp32 add-reduces at L2)
+    M, N, K = 16384, 2048, 64
+    A, B = torch.randn(M, K, device=dev).bfloat16(), torch.randn(N, K, device=dev).bfloat16()
+    for acc in (False, True):
+        out = torch.zeros(M, N, device=dev, dtype=torch.float32 if acc else torch.bfloat16)
+        for epi in (1, 0):
+            nat.lib().mlb_gemm_epilogue_mode(epi)
+            t = timeit(lambda: nat.gemm(out, A, B, False, False, acc), a.iters, a.warm)
+            nbytes = out.numel() * out.element_size()
+            print(f"K=64 epilogue only, {'fp32 add-reduce' if acc else 'bf16 store'}, mode {epi} ({'warp stores' if epi else 'TMA'}): "
+                  f"{t * 1e3:7.1f} us  {nbytes / t / 1e9:6.2f} TB/s of output")
+        del out
+    nat.lib().mlb_gemm_epilogue_mode(1)
     print("kernel error word:", nat.get_error())
 
 
@@ -156,6 +194,7 @@ def once(a):
             nat.adamw(ma, p, g, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.5, 1.0)
     else:
         nat.lib().mlb_gemm_use_pairs(a.pairs)
+        nat.lib().mlb_gemm_epilogue_mode(a.epi)
         M, N, K = a.M, 3 * a.C, a.C
         x = torch.randn(M, K, device=dev).bfloat16()
         W = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
@@ -173,7 +212,8 @@ def once(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn", "norm", "once"])
+    ap.add_argument("what", choices=["gemm", "layouts", "attn", "norm", "once"])
+    ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--case", default="attn", choices=["attn", "gemm", "norm"])
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--C", type=int, default=768)
@@ -185,9 +225,11 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
+    ap.add_argument("--streamk", type=int, default=1, help="pair GEMM, weight gradients: 1 = equal k-block ranges per cluster, 0 = fixed split count")
+    ap.add_argument("--epi", type=int, default=1, help="pair GEMM epilogue: 1 = coalesced stores by the warps, 0 = TMA store / add-reduce")
     ap.add_argument("--pairs", type=int, default=1, help="GEMM: 1 = CTA-pair kernel (cta_group::2), 0 = one CTA per tile")
     a = ap.parse_args()
-    {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
+    {"gemm": bench_gemm, "layouts": bench_layouts, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
 
 
 if __name__ == "__main__":

@@ -45,6 +45,8 @@ struct AttnArgs {
   const float* delta; // [B,H,T] (bwd)
   const float* cosT;  // optional fused RoPE-backward tables [T, hd/2]
   const float* sinT;
+  bf16* dq_part;       // fused backward: dQ partial tiles [B][nq(nq+1)/2 (query tile i, key tile kt <= i)][128][C]
+  long long* timeline; // optional: SM cycle stamps of CTA (0,0,0) of the fused backward, eight per (query block) step
 };
 
 // ================================================================== forward
@@ -678,44 +680,59 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kv_tc_kernel(const __
 }
 
 // ================================================================== backward, head size 64: ONE kernel, five GEMMs
-// One CTA per 128-key tile walks the query tiles i >= its own.  Per query tile:
-//     S^T = K Q^T, dP^T = V dO^T                       (two MMAs, scores never leave TMEM)
-//     P^T = exp2(S^T*c - lse), dS^T = P^T (dP^T - delta)   (512 threads, packed f32x2 math, bf16 into swizzled smem)
-//     dV += P^T dO, dK += dS^T Q                        (accumulated in TMEM over all query tiles)
-//     dQ_i  = dS K                                      (the dS^T tile is read again as an MN-major A operand)
-// dQ_i is a partial sum over key tiles: it is drained from TMEM through a swizzled staging buffer and added to an fp32
-// accumulator [B*T, C] with TMA add-reduce; a small second kernel turns the accumulator into bf16 dQ (scale, RoPE
-// backward) and zeroes it again.  The 1/sqrt(hd) factor is applied once per output element instead of once per score.
-// Compared with separate dK/dV and dQ kernels this computes S, dP and the exponentials once instead of twice.
+// One CTA per 128-key tile (and its mirror tile, so every CTA walks nq+1 query blocks) loops over the query tiles
+// i >= its own.  Per query block:
+//     S^T = K Q^T, dP^T = V dO^T                            (two MMAs into TMEM)
+//     P^T = exp2(S^T*c - lse), dS^T = P^T (dP^T - delta)    (512 threads, packed f32x2 math)
+//     dV += P^T dO   (P^T stays in TMEM as the bf16 A operand),   dK += dS^T Q,   dQ_i = dS K   (dS^T in shared memory)
+// The pipeline keeps the tensor core and the element-wise warps busy at the same time:
+//   * as soon as the element-wise warps have S^T / dP^T of block j in registers they release the TMEM columns and the
+//     control thread issues the score MMAs of block j+1 (Q / dO tiles are triple buffered so they are already there);
+//   * the exponentials of block j+1 are computed while dV / dK / dQ of block j run; only the stores of P^T / dS^T wait
+//     for those MMAs (one TMEM region, one shared-memory tile);
+//   * dQ_j is a partial sum over key tiles.  fp32 add-reduces into one accumulator (TMA or vector red) ran into the
+//     L2's atomic throughput (32 KB per block and SM); instead every (query tile, key tile) pair owns a bf16 tile of a
+//     partial buffer, written with plain stores right after block j+1's operands are handed over, and a second
+//     kernel adds the partials of a query row in fp32 in key-tile order (deterministic), applies the scale and RoPE's
+//     backward rotation and writes bf16 dQ.
+// Warps: 8 element-wise (TMEM lane group x 64-query half), 4 drain (dQ partial tiles, dK / dV epilogue), 1 control.
+// mbarriers: bar_s scores complete (commit) | bar_free S^T/dP^T read out (8 warps) | bar_p P^T/dS^T stored (8 warps) |
+// bar_d dV/dK/dQ MMAs complete (commit) | bar_dqf dQ read out (4 warps) | bar_epi dK/dV of a key tile read out (4 warps).
 struct BwdFusedSmem {
   static constexpr int K = 0;
   static constexpr int V = K + TILE_BYTES;
-  static constexpr int Q = V + TILE_BYTES;               // 2 buffers
-  static constexpr int DO = Q + 2 * TILE_BYTES;          // 2 buffers
-  static constexpr int PT = DO + 2 * TILE_BYTES;         // [128 keys x 128 queries] bf16
-  static constexpr int DST = PT + 2 * TILE_BYTES;
-  static constexpr int DQS = DST + 2 * TILE_BYTES;       // fp32 staging for the dQ tile: 4 lane groups x 2 boxes x 4 KB
-  static constexpr int STAT = DQS + 2 * TILE_BYTES;      // 2 buffers x (-lse*log2e [128], -delta [128])
-  static constexpr int BAR = STAT + 2048;
-  static constexpr int TOTAL = BAR + 128 + 1024;
+  static constexpr int Q = V + TILE_BYTES;               // 3 buffers
+  static constexpr int DO = Q + 3 * TILE_BYTES;          // 3 buffers
+  static constexpr int DST = DO + 3 * TILE_BYTES;        // [128 keys x 128 queries] bf16
+  static constexpr int STAT = DST + 2 * TILE_BYTES;      // 8 warps x (-lse*log2e [64], -delta [64])
+  static constexpr int BAR = STAT + 4096;
+  static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
-constexpr int BWDF_WORK_WARPS = 16;
-constexpr int BWDF_THREADS = (BWDF_WORK_WARPS + 1) * 32;   // 16 element-wise warps + 1 control warp
+constexpr int BWDF_E_WARPS = 8;       // element-wise warps: TMEM lane group (w & 3) x 64-query column half (w >> 2)
+constexpr int BWDF_D_WARPS = 4;       // drain warps: dQ partial tiles and the dK / dV epilogue, one TMEM lane group each
+constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS;
+constexpr int BWDF_THREADS = (BWDF_CTRL_WARP + 1) * 32;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
-                                                                            const __grid_constant__ CUtensorMap tm_do,
-                                                                            const __grid_constant__ CUtensorMap tm_dq, const AttnArgs a) {
+                                                                            const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
   using S = BwdFusedSmem;
   constexpr int HD = 64;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + S::BAR);
-  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[2]*/, *bar_s = bars + 3, *bar_p = bars + 4;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 5);
-  volatile int* s_abort = (volatile int*)(bars + 6);
-  float* s_stat = (float*)(smem + S::STAT);   // [2 buffers][-lse*log2e x128 | -delta x128]
+  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[3]*/, *bar_s = bars + 4, *bar_free = bars + 5, *bar_p = bars + 6, *bar_d = bars + 7,
+           *bar_dqf = bars + 8, *bar_epi = bars + 9;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+  volatile int* s_abort = (volatile int*)(bars + 11);
+  float* s_stat = (float*)(smem + S::STAT);   // [8 warps][-lse*log2e x64 | -delta x64]
   {
     __shared__ int s_skip;
     if (threadIdx.x == 0) s_skip = *(volatile int*)&g_mlb_error;
@@ -723,8 +740,6 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
     if (s_skip != 0) return;
   }
   const int nq = (a.T + 127) / 128;
-  // A CTA takes key tile x and its mirror nq-1-x: together they always cover nq+1 query blocks, so all CTAs carry the
-  // same load, and the second tile's loads overlap the first tile's epilogue.
   const int kt_first = blockIdx.x, kt_second = nq - 1 - (int)blockIdx.x;
   const int n_items = (kt_second != kt_first) ? 2 : 1;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -733,172 +748,179 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
   const int row0 = b * a.T;
 
   if (tid == 0) {
-    tc::mbar_init(bar_kv, 1); tc::mbar_init(&bar_q[0], 1); tc::mbar_init(&bar_q[1], 1); tc::mbar_init(bar_s, 1);
-    tc::mbar_init(bar_p, BWDF_WORK_WARPS);
+    tc::mbar_init(bar_kv, 1);
+    for (int i = 0; i < 3; i++) tc::mbar_init(&bar_q[i], 1);
+    tc::mbar_init(bar_s, 1); tc::mbar_init(bar_d, 1);
+    tc::mbar_init(bar_free, BWDF_E_WARPS); tc::mbar_init(bar_p, BWDF_E_WARPS);
+    tc::mbar_init(bar_dqf, BWDF_D_WARPS); tc::mbar_init(bar_epi, BWDF_D_WARPS);
     *s_abort = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tm_qkv);
     tc::tma_prefetch_desc(&tm_do);
-    tc::tma_prefetch_desc(&tm_dq);
   }
-  if (warp == BWDF_WORK_WARPS) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == BWDF_CTRL_WARP) tc::tmem_alloc(tmem_slot, TMEM_COLS);
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_st = tmem, t_dpt = tmem + 128, t_dv = tmem + 256, t_dk = tmem + 320, t_dq = tmem + 384;   // two dQ buffers: +384, +448
+  // S^T 128 | dP^T 128 | P^T (bf16 pairs) 64 | dV 64 | dK 64 | dQ 64
+  const uint32_t t_st = tmem, t_dpt = tmem + 128, t_pt = tmem + 256, t_dv = tmem + 320, t_dk = tmem + 384, t_dq = tmem + 448;
   auto wait = [&](uint64_t* bar, uint32_t phase, int where) -> bool {
     if (*s_abort) return false;
-    if (!tc::mbar_wait(bar, phase, where)) { *s_abort = 1; return false; }
+    if (!tc::mbar_wait_sleep(bar, phase, where)) { *s_abort = 1; return false; }
     return true;
   };
+  long long* tl = (a.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) ? a.timeline : nullptr;
 
-  if (warp == BWDF_WORK_WARPS) {
+  if (warp == BWDF_CTRL_WARP) {
     // ---------------------------------------------------------------- control warp: every TMA load and every MMA
     if (lane == 0) {
       constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T / dS^T), B MN-major (dO / Q)
+      constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T in TMEM / dS^T), B MN-major (dO / Q)
       constexpr uint32_t idesc_q = tc::idesc_bf16(128, HD, 1, 1);    // A MN-major (dS^T read as dS), B MN-major (K)
-      const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V);
-      const uint32_t sPT = tc::smem_u32(smem + S::PT), sDST = tc::smem_u32(smem + S::DST);
+      const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V), sDST = tc::smem_u32(smem + S::DST);
       auto load_kv = [&](int kt) {
         tc::mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
         tc::tma_load_2d(smem + S::K, &tm_qkv, bar_kv, C + h * HD, row0 + kt * 128);
         tc::tma_load_2d(smem + S::V, &tm_qkv, bar_kv, 2 * C + h * HD, row0 + kt * 128);
       };
-      auto load_q_do = [&](int i, int buf) {
+      auto load_q_do = [&](int i, int g) {          // g: running block number, buffer g % 3
+        const int buf = g % 3;
         tc::mbar_expect_tx(&bar_q[buf], 2 * TILE_BYTES);
         tc::tma_load_2d(smem + S::Q + buf * TILE_BYTES, &tm_qkv, &bar_q[buf], h * HD, row0 + i * 128);
         tc::tma_load_2d(smem + S::DO + buf * TILE_BYTES, &tm_do, &bar_q[buf], h * HD, row0 + i * 128);
       };
-      auto issue_scores = [&](int buf) {
+      auto issue_scores = [&](int g) {
+        const int buf = g % 3;
+        if (!wait(&bar_q[buf], (g / 3) & 1, 41)) return;
+        tc::tc_fence_after();
         const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
       };
-      int blk = 0, s_cnt = 0, p_cnt = 0;
+      int blk = 0;
       load_kv(kt_first);
       load_q_do(kt_first, 0);
+      if (nq - kt_first > 1) load_q_do(kt_first + 1, 1);
       for (int item = 0; item < n_items; item++) {
         const int kt = item == 0 ? kt_first : kt_second;
         const int n_it = nq - kt;
-        if (wait(bar_kv, item & 1, 40) && wait(&bar_q[blk & 1], (blk >> 1) & 1, 41)) { tc::tc_fence_after(); issue_scores(blk & 1); }
+        if (wait(bar_kv, item & 1, 40)) issue_scores(blk);
         tc::mma_commit(bar_s);
         for (int it = 0; it < n_it; it++, blk++) {
-          const int i = kt + it, buf = blk & 1;
-          // scores of this block complete => every earlier MMA is complete: the other Q/dO buffer is free
-          wait(bar_s, s_cnt & 1, 42);
-          s_cnt++;
-          if (it + 1 < n_it) load_q_do(i + 1, buf ^ 1);
-          // P^T and dS^T of this block are in shared memory (and S^T / dP^T have been read out of TMEM)
-          const bool p_ok = wait(bar_p, p_cnt & 1, 45);
-          p_cnt++;
-          if (p_ok) {
+          const int buf = blk % 3;
+          // S^T / dP^T of this block are in registers: the score MMAs of the next block may overwrite them
+          wait(bar_free, blk & 1, 42);
+          if (it + 1 < n_it) {
+            tc::tc_fence_after();
+            issue_scores(blk + 1);
+            tc::mma_commit(bar_s);
+          }
+          // the tiles of block it+2 go where block it-1's were: its dV / dK MMAs must have finished reading them
+          if (it + 2 < n_it) {
+            if (blk > 0) wait(bar_d, (blk - 1) & 1, 43);
+            load_q_do(kt + it + 2, blk + 2);
+          }
+          bool go = wait(bar_p, blk & 1, 45);     // P^T in TMEM, dS^T in shared memory
+          if (tl) tl[blk * 8 + 5] = clock64();
+          if (it == 0 && item > 0) go = wait(bar_epi, (item - 1) & 1, 46) && go;   // previous tile's dK / dV have been read out
+          if (go) {
             tc::tc_fence_after();
             const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dv, desc_k(sPT, ks), desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(t_dv, t_pt + ks * 8, desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, desc_k(sDST, ks), desc_mn(sQ, ks), idesc_d, (it > 0 || ks > 0));
+            if (blk > 0) go = wait(bar_dqf, (blk - 1) & 1, 47);   // the previous dQ tile has left TMEM
+            if (go) {
+              tc::tc_fence_after();
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq + (blk & 1) * 64, desc_mn(sDST, ks), desc_mn(sK, ks), idesc_q, ks > 0);
+              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, desc_mn(sDST, ks), desc_mn(sK, ks), idesc_q, ks > 0);
+            }
           }
-          if (it + 1 < n_it && wait(&bar_q[buf ^ 1], ((blk + 1) >> 1) & 1, 43)) {
-            tc::tc_fence_after();
-            issue_scores(buf ^ 1);
-          }
-          tc::mma_commit(bar_s);
+          tc::mma_commit(bar_d);
+          if (tl) tl[blk * 8 + 6] = clock64();
         }
-        // all MMAs of this key tile complete => K, V, Q, dO are free: the mirror tile's loads run under the epilogue
-        wait(bar_s, s_cnt & 1, 44);
-        s_cnt++;
         if (item + 1 < n_items) {
+          // every MMA of this key tile is complete: K, V and all Q / dO buffers are free for the mirror tile
+          wait(bar_d, (blk - 1) & 1, 44);
           load_kv(kt_second);
-          load_q_do(kt_second, blk & 1);
+          load_q_do(kt_second, blk);
+          if (nq - kt_second > 1) load_q_do(kt_second + 1, blk + 1);
         }
-        // the work warps have seen that completion too (otherwise the next commit could lap their parity wait)
-        wait(bar_p, p_cnt & 1, 46);
-        p_cnt++;
       }
     }
-  } else {
-    // ---------------------------------------------------------------- 16 element-wise warps
-    const int lg = warp & 3, cq = warp >> 2, row = lg * 32 + lane;
+  } else if (warp < BWDF_E_WARPS) {
+    // ---------------------------------------------------------------- 8 element-wise warps
+    const int lg = warp & 3, ch = warp >> 2, row = lg * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
     const float sl2 = a.scale * LOG2E;
     const uint64_t sl2x2 = pk2(sl2, sl2);
-    // dQ tile of query block i: TMEM -> swizzled fp32 staging -> TMA add-reduce into the accumulator
-    uint8_t* stage = smem + S::DQS + lg * 8192 + (cq >> 1) * 4096;
-    auto drain_dq = [&](int i, int dbuf) {
-      if (cq == 0 && lane == 0) tc::tma_wait_group_read<0>();   // the previous reduce has finished reading the staging
-      named_bar_sync(1 + lg, 128);
-      uint32_t r[16];
-      tc::tmem_ld16(t_dq + dbuf * 64 + lane_addr + cq * 16, r);
-      tc::tmem_ld_wait();
+    // per-query statistics: each warp keeps the 64 queries of its column half in a private shared-memory slot
+    // (-lse*log2e, -delta; queries past the end give P = 0).  Lane l fetches queries l and l+32 of the NEXT block while
+    // this block is processed, so neither the load latency nor a CTA-wide barrier sits between two blocks.
+    float* my_stat = s_stat + warp * 128;
+    auto fetch_stat = [&](int i, float (&l)[2], float (&d)[2]) {
 #pragma unroll
-      for (int v = 0; v < 4; v++) {
-        const int unit = (cq & 1) * 4 + v;
-        *reinterpret_cast<uint4*>(stage + lane * 128 + ((unit ^ (lane & 7)) << 4)) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-      }
-      tc::fence_async_smem();
-      tc::tc_fence_before();
-      named_bar_sync(1 + lg, 128);
-      if (cq == 0 && lane == 0) {
-        tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192, h * HD, row0 + i * 128 + lg * 32);
-        tc::tma_reduce_add_2d(&tm_dq, smem + S::DQS + lg * 8192 + 4096, h * HD + 32, row0 + i * 128 + lg * 32);
-        tc::tma_commit_group();
+      for (int u = 0; u < 2; u++) {
+        const int q = i * 128 + ch * 64 + u * 32 + lane;
+        const size_t si = ((size_t)b * a.H + h) * a.T + q;
+        l[u] = (q < a.T) ? a.lse[si] : INFINITY;
+        d[u] = (q < a.T) ? a.delta[si] : 0.f;
       }
     };
-    // per-query statistics of a block, negated for the packed FMAs; queries past the end give P = 0.  Threads 0..127
-    // fetch -lse*log2e, threads 128..255 fetch -delta; the values for block i+1 are fetched while block i's MMAs run.
-    auto fetch_stat = [&](int i) -> float {
-      if (tid >= 256) return 0.f;
-      const int q = i * 128 + (tid & 127);
-      const size_t si = ((size_t)b * a.H + h) * a.T + q;
-      if (tid < 128) return (q < a.T) ? -a.lse[si] * LOG2E : -INFINITY;
-      return (q < a.T) ? -a.delta[si] : 0.f;
-    };
-    int blk = 0, s_cnt = 0;
+    int blk = 0;
     for (int item = 0; item < n_items; item++) {
       const int kt = item == 0 ? kt_first : kt_second;
       const int k0 = kt * 128, krow = k0 + row;
       const int n_it = nq - kt;
-      float stat = fetch_stat(kt);
+      float st_l[2], st_d[2];
+      fetch_stat(kt, st_l, st_d);
       for (int it = 0; it < n_it; it++, blk++) {
         const int i = kt + it, q0 = i * 128;
-        float* st_buf = s_stat + (blk & 1) * 256;     // double buffered: a fast warp may already write block i+1's values
-        if (tid < 256) st_buf[tid] = stat;
-        named_bar_sync(5, BWDF_WORK_WARPS * 32);
-        const float* s_nlse = st_buf;
-        const float* s_ndelta = st_buf + 128;
-        // the next block's statistics are requested now, a whole element-wise phase before they are needed
-        if (it + 1 < n_it) stat = fetch_stat(i + 1);
-        wait(bar_s, s_cnt & 1, 42);       // S^T, dP^T of this block are complete, and so is everything issued before them
-        s_cnt++;
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          my_stat[u * 32 + lane] = -st_l[u] * LOG2E;
+          my_stat[64 + u * 32 + lane] = -st_d[u];
+        }
+        __syncwarp();
+        if (it + 1 < n_it) fetch_stat(i + 1, st_l, st_d);
+        if (tl && warp == 0) tl[blk * 8 + 0] = clock64();
+        wait(bar_s, blk & 1, 48);          // S^T, dP^T of this block are complete
         tc::tc_fence_after();
-        {
+        if (tl && warp == 0) tl[blk * 8 + 1] = clock64();
+        uint32_t pw[2][16], dw[2][16];
+        const bool diag = (it == 0);
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
           uint32_t rs[32], rd[32];
-          tc::tmem_ld32(t_st + lane_addr + cq * 32, rs);
-          tc::tmem_ld32(t_dpt + lane_addr + cq * 32, rd);
+          const int c0 = ch * 64 + hf * 32;      // first query column of this pass
+          tc::tmem_ld32(t_st + lane_addr + c0, rs);
+          tc::tmem_ld32(t_dpt + lane_addr + c0, rd);
           tc::tmem_ld_wait();
-          const bool diag = (it == 0);
+          if (hf == 1) {
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(bar_free);
+          }
 #pragma unroll
           for (int v8 = 0; v8 < 4; v8++) {
-            const int qc = cq * 32 + v8 * 8;
+            const int qc = c0 + v8 * 8;
+            const float* sn = my_stat + hf * 32 + v8 * 8;
             float nl[8], nd[8];
-            *reinterpret_cast<float4*>(nl) = *reinterpret_cast<const float4*>(s_nlse + qc);
-            *reinterpret_cast<float4*>(nl + 4) = *reinterpret_cast<const float4*>(s_nlse + qc + 4);
-            *reinterpret_cast<float4*>(nd) = *reinterpret_cast<const float4*>(s_ndelta + qc);
-            *reinterpret_cast<float4*>(nd + 4) = *reinterpret_cast<const float4*>(s_ndelta + qc + 4);
-            uint32_t pw[4], dw[4];
+            *reinterpret_cast<float4*>(nl) = *reinterpret_cast<const float4*>(sn);
+            *reinterpret_cast<float4*>(nl + 4) = *reinterpret_cast<const float4*>(sn + 4);
+            *reinterpret_cast<float4*>(nd) = *reinterpret_cast<const float4*>(sn + 64);
+            *reinterpret_cast<float4*>(nd + 4) = *reinterpret_cast<const float4*>(sn + 68);
 #pragma unroll
             for (int x = 0; x < 4; x++) {
               const int e = v8 * 8 + 2 * x;
               float z0, z1;
               upk2(fma2(pk2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), sl2x2, pk2(nl[2 * x], nl[2 * x + 1])), z0, z1);
-              float p0 = exp2f(z0), p1 = exp2f(z1);
+              float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
               if (diag) {
                 if (q0 + qc + 2 * x < krow) p0 = 0.f;
                 if (q0 + qc + 2 * x + 1 < krow) p1 = 0.f;
@@ -906,47 +928,91 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
               const uint64_t t2 = add2(pk2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])), pk2(nd[2 * x], nd[2 * x + 1]));
               float d0, d1;
               upk2(mul2(pk2(p0, p1), t2), d0, d1);
-              pw[x] = pack_bf16(p0, p1);
-              dw[x] = pack_bf16(d0, d1);
+              pw[hf][v8 * 4 + x] = pack_bf16(p0, p1);
+              dw[hf][v8 * 4 + x] = pack_bf16(d0, d1);
             }
-            const uint32_t off = sw_off(row, qc);
-            *reinterpret_cast<uint4*>(smem + S::PT + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-            *reinterpret_cast<uint4*>(smem + S::DST + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
           }
         }
+        if (tl && warp == 0) tl[blk * 8 + 2] = clock64();
+        // P^T's TMEM columns and the dS^T tile belong to the previous block's MMAs until they complete
+        if (blk > 0) { wait(bar_d, (blk - 1) & 1, 49); tc::tc_fence_after(); }
+        if (tl && warp == 0) tl[blk * 8 + 3] = clock64();
+#pragma unroll
+        for (int v8 = 0; v8 < 8; v8++)
+          *reinterpret_cast<uint4*>(smem + S::DST + sw_off(row, ch * 64 + v8 * 8)) =
+              make_uint4(dw[v8 >> 2][(v8 & 3) * 4], dw[v8 >> 2][(v8 & 3) * 4 + 1], dw[v8 >> 2][(v8 & 3) * 4 + 2], dw[v8 >> 2][(v8 & 3) * 4 + 3]);
+        tc::tmem_st16(t_pt + lane_addr + ch * 32, pw[0]);
+        tc::tmem_st16(t_pt + lane_addr + ch * 32 + 16, pw[1]);
+        tc::tmem_st_wait();
         tc::fence_async_smem();
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(bar_p);
-        // while the tensor core works through this block's MMAs: move the previous block's dQ tile (complete since the
-        // bar_s wait above, and in the other TMEM buffer) to the accumulator
-        if (it > 0) drain_dq(i - 1, (blk - 1) & 1);
+        if (tl && warp == 0) tl[blk * 8 + 4] = clock64();
       }
-      wait(bar_s, s_cnt & 1, 44);   // dV, dK and the last dQ tile of this key tile are complete
-      s_cnt++;
-      tc::tc_fence_after();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(bar_p);   // tells the control warp that this completion has been consumed
-      drain_dq(kt + n_it - 1, (blk - 1) & 1);   // earlier blocks were drained inside the loop
-      if (cq < 2) {   // warps 0-3: dK (scaled, RoPE backward); warps 4-7: dV
-        const bool is_k = cq == 0;
-        bf16* dst = a.out + ((size_t)(row0 + krow)) * 3 * C + (is_k ? C : 2 * C) + h * HD;
-        store_pairs_rope<HD>(dst, (is_k ? t_dk : t_dv) + lane_addr, 0, !*s_abort && krow < a.T, is_k ? a.cosT : nullptr,
-                             is_k ? a.sinT : nullptr, krow, is_k ? a.scale : 1.f);
+    }
+  } else {
+    // ---------------------------------------------------------------- 4 drain warps
+    // dQ partial of (query block i, this key tile): TMEM -> bf16 -> its own tile of the partial buffer (a full 128-byte
+    // row per thread; no atomics, the finishing kernel adds the key tiles' partials in a fixed order); after the last
+    // block of a key tile also dK (scaled, RoPE backward) and dV.
+    const int lg = warp & 3, row = lg * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+    const int npairs = nq * (nq + 1) / 2;
+    if (warp != BWDF_E_WARPS) tl = nullptr;
+    int blk = 0;
+    for (int item = 0; item < n_items; item++) {
+      const int kt = item == 0 ? kt_first : kt_second;
+      const int krow = kt * 128 + row;
+      const int n_it = nq - kt;
+      for (int it = 0; it < n_it; it++, blk++) {
+        const int i = kt + it;
+        wait(bar_d, blk & 1, 50);          // dV, dK, dQ MMAs of this block are complete
+        tc::tc_fence_after();
+        uint32_t r0[32], r1[32];
+        tc::tmem_ld32(t_dq + lane_addr, r0);
+        tc::tmem_ld32(t_dq + lane_addr + 32, r1);
+        tc::tmem_ld_wait();
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(bar_dqf);
+        bf16* dst = a.dq_part + (((size_t)b * npairs + (i * (i + 1) / 2 + kt)) * 128 + row) * C + h * HD;
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+          uint4 w0, w1;
+          w0.x = pack_bf16(__uint_as_float(r0[v * 8 + 0]), __uint_as_float(r0[v * 8 + 1]));
+          w0.y = pack_bf16(__uint_as_float(r0[v * 8 + 2]), __uint_as_float(r0[v * 8 + 3]));
+          w0.z = pack_bf16(__uint_as_float(r0[v * 8 + 4]), __uint_as_float(r0[v * 8 + 5]));
+          w0.w = pack_bf16(__uint_as_float(r0[v * 8 + 6]), __uint_as_float(r0[v * 8 + 7]));
+          w1.x = pack_bf16(__uint_as_float(r1[v * 8 + 0]), __uint_as_float(r1[v * 8 + 1]));
+          w1.y = pack_bf16(__uint_as_float(r1[v * 8 + 2]), __uint_as_float(r1[v * 8 + 3]));
+          w1.z = pack_bf16(__uint_as_float(r1[v * 8 + 4]), __uint_as_float(r1[v * 8 + 5]));
+          w1.w = pack_bf16(__uint_as_float(r1[v * 8 + 6]), __uint_as_float(r1[v * 8 + 7]));
+          *reinterpret_cast<uint4*>(dst + v * 8) = w0;
+          *reinterpret_cast<uint4*>(dst + 32 + v * 8) = w1;
+        }
+        if (tl && warp == BWDF_E_WARPS) tl[blk * 8 + 7] = clock64();
+      }
+      // the wait above covered the last block: dV and dK of this key tile are final
+      {
+        bf16* dk = a.out + ((size_t)(row0 + krow)) * 3 * C + C + h * HD;
+        store_pairs_rope<HD>(dk, t_dk + lane_addr, 0, !*s_abort && krow < a.T, a.cosT, a.sinT, krow, a.scale);
+        store_pairs_rope<HD>(dk + C, t_dv + lane_addr, 0, !*s_abort && krow < a.T, nullptr, nullptr, krow, 1.f);
       }
       tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(bar_epi);
     }
-    if (cq == 0 && lane == 0) tc::tma_wait_group<0>();
   }
   tc::tc_fence_before();
   __syncthreads();
-  if (warp == BWDF_WORK_WARPS) tc::tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == BWDF_CTRL_WARP) tc::tmem_dealloc(tmem, TMEM_COLS);
 }
 
-// dQ accumulator (fp32 [rows, C]) -> bf16 Q slice of dqkv[rows, 3C], times `scale`, optional RoPE backward; the
-// accumulator is zeroed for its next use.  One thread per (row, head, group of 16 rotation pairs): eight 16-byte loads
-// in flight per thread.
-__global__ void __launch_bounds__(256) attn_dq_finish_k(bf16* __restrict__ dqkv, float* __restrict__ acc, long rows, int T, int H,
+// dQ partial tiles -> bf16 Q slice of dqkv[rows, 3C]: sum over the key tiles kt <= i of query tile i (fp32, fixed
+// order), times `scale`, optional RoPE backward.  One thread per (row, head, group of 16 rotation pairs); the partial
+// layout is [B][i(i+1)/2 + kt][128][C] bf16.
+__global__ void __launch_bounds__(256) attn_dq_finish_k(bf16* __restrict__ dqkv, const bf16* __restrict__ part, long rows, int T, int H,
                                                         int hd, float scale, const float* __restrict__ cosT,
                                                         const float* __restrict__ sinT) {
   const int h2 = hd >> 1, gph = h2 >> 4, gpr = H * gph;   // groups of 16 pairs per head / per row
@@ -955,45 +1021,51 @@ __global__ void __launch_bounds__(256) attn_dq_finish_k(bf16* __restrict__ dqkv,
   const long r = idx / gpr;
   const int g = idx % gpr, h = g / gph, v = g % gph;
   const int t = r % T, C = H * hd;
-  float4* p0 = reinterpret_cast<float4*>(acc + r * C + h * hd + v * 16);
-  float4* p1 = reinterpret_cast<float4*>(acc + r * C + h * hd + h2 + v * 16);
-  float4 a0[4], a1[4];
-#pragma unroll
-  for (int i = 0; i < 4; i++) { a0[i] = __ldcs(p0 + i); a1[i] = __ldcs(p1 + i); }
-  const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-  for (int i = 0; i < 4; i++) { p0[i] = z; p1[i] = z; }
+  const long b = r / T;
+  const int nq = (T + 127) / 128, npairs = nq * (nq + 1) / 2, i = t >> 7;
+  const bf16* base = part + ((b * npairs + (long)i * (i + 1) / 2) * 128 + (t & 127)) * C + h * hd + v * 16;
   float x0[16], x1[16];
 #pragma unroll
-  for (int i = 0; i < 4; i++) {
-    x0[4 * i] = a0[i].x * scale; x0[4 * i + 1] = a0[i].y * scale; x0[4 * i + 2] = a0[i].z * scale; x0[4 * i + 3] = a0[i].w * scale;
-    x1[4 * i] = a1[i].x * scale; x1[4 * i + 1] = a1[i].y * scale; x1[4 * i + 2] = a1[i].z * scale; x1[4 * i + 3] = a1[i].w * scale;
+  for (int k = 0; k < 16; k++) { x0[k] = 0.f; x1[k] = 0.f; }
+  for (int kt = 0; kt <= i; kt++) {
+    const uint4* p0 = reinterpret_cast<const uint4*>(base + (long)kt * 128 * C);
+    const uint4* p1 = reinterpret_cast<const uint4*>(base + (long)kt * 128 * C + h2);
+    const uint4 a0 = __ldcs(p0), a1 = __ldcs(p0 + 1), b0 = __ldcs(p1), b1 = __ldcs(p1 + 1);
+    const uint32_t wa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint32_t wb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      x0[2 * k] += __uint_as_float(wa[k] << 16); x0[2 * k + 1] += __uint_as_float(wa[k] & 0xffff0000u);
+      x1[2 * k] += __uint_as_float(wb[k] << 16); x1[2 * k + 1] += __uint_as_float(wb[k] & 0xffff0000u);
+    }
   }
+#pragma unroll
+  for (int k = 0; k < 16; k++) { x0[k] *= scale; x1[k] *= scale; }
   if (cosT) {
     const float4* c4 = reinterpret_cast<const float4*>(cosT + (long)t * h2 + v * 16);
     const float4* s4 = reinterpret_cast<const float4*>(sinT + (long)t * h2 + v * 16);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const float4 c = c4[i], sn = s4[i];
+    for (int i4 = 0; i4 < 4; i4++) {
+      const float4 c = c4[i4], sn = s4[i4];
       const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
 #pragma unroll
       for (int k = 0; k < 4; k++) {
-        const float d0 = x0[4 * i + k], d1 = x1[4 * i + k];
-        x0[4 * i + k] = d0 * cc[k] + d1 * ss[k];
-        x1[4 * i + k] = d1 * cc[k] - d0 * ss[k];
+        const float d0 = x0[4 * i4 + k], d1 = x1[4 * i4 + k];
+        x0[4 * i4 + k] = d0 * cc[k] + d1 * ss[k];
+        x1[4 * i4 + k] = d1 * cc[k] - d0 * ss[k];
       }
     }
   }
   bf16* o0 = dqkv + r * 3L * C + h * hd + v * 16;
 #pragma unroll
-  for (int i = 0; i < 2; i++) {
+  for (int i2 = 0; i2 < 2; i2++) {
     uint4 w0, w1;
-    w0.x = pack_bf16(x0[8 * i], x0[8 * i + 1]); w0.y = pack_bf16(x0[8 * i + 2], x0[8 * i + 3]);
-    w0.z = pack_bf16(x0[8 * i + 4], x0[8 * i + 5]); w0.w = pack_bf16(x0[8 * i + 6], x0[8 * i + 7]);
-    w1.x = pack_bf16(x1[8 * i], x1[8 * i + 1]); w1.y = pack_bf16(x1[8 * i + 2], x1[8 * i + 3]);
-    w1.z = pack_bf16(x1[8 * i + 4], x1[8 * i + 5]); w1.w = pack_bf16(x1[8 * i + 6], x1[8 * i + 7]);
-    *reinterpret_cast<uint4*>(o0 + 8 * i) = w0;
-    *reinterpret_cast<uint4*>(o0 + h2 + 8 * i) = w1;
+    w0.x = pack_bf16(x0[8 * i2], x0[8 * i2 + 1]); w0.y = pack_bf16(x0[8 * i2 + 2], x0[8 * i2 + 3]);
+    w0.z = pack_bf16(x0[8 * i2 + 4], x0[8 * i2 + 5]); w0.w = pack_bf16(x0[8 * i2 + 6], x0[8 * i2 + 7]);
+    w1.x = pack_bf16(x1[8 * i2], x1[8 * i2 + 1]); w1.y = pack_bf16(x1[8 * i2 + 2], x1[8 * i2 + 3]);
+    w1.z = pack_bf16(x1[8 * i2 + 4], x1[8 * i2 + 5]); w1.w = pack_bf16(x1[8 * i2 + 6], x1[8 * i2 + 7]);
+    *reinterpret_cast<uint4*>(o0 + 8 * i2) = w0;
+    *reinterpret_cast<uint4*>(o0 + h2 + 8 * i2) = w1;
   }
 }
 
@@ -1251,7 +1323,13 @@ bool tc_ok(const void* qkv, const void* other, int H, int hd) {
 
 }  // namespace
 
+static long long* g_timeline = nullptr;
 MLB_API void mlb_attn_force_simt(int on) { g_attn_force_simt = on; }
+// Diagnostic: device buffer of at least 8 * (query blocks per CTA) int64 that CTA (0,0,0) of the fused backward fills
+// with SM cycle stamps, eight per block: element-wise warp 0 before / after the score wait, after its exponentials,
+// after the previous block's MMAs completed, after P^T / dS^T are stored; control thread when it saw P^T and when the
+// block's MMAs were issued; first drain warp when the dQ partial was stored.  nullptr switches it off.
+MLB_API void mlb_attn_set_timeline(void* buf) { g_timeline = (long long*)buf; }
 
 // out[B,T,C], lse[B,H,T] from qkv[B,T,3C].
 MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, int H, int hd, cudaStream_t st) {
@@ -1283,12 +1361,19 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
   return (int)cudaGetLastError();
 }
 
-// dqkv[B,T,3C] from dout[B,T,C], qkv, out, lse.  `delta` is scratch of B*H*T floats.  `dq_acc` (optional) is scratch of
-// B*T*C floats that must be all zero on entry (it is left all zero): with it and head size 64 the fused
+// Bytes of dQ-partial scratch the fused backward needs for this shape (0: no fused backward for it).
+MLB_API long mlb_attn_bwd_scratch_bytes(int B, int T, int H, int hd) {
+  if (hd != 64) return 0;
+  const long nq = (T + 127) / 128;
+  return (long)B * (nq * (nq + 1) / 2) * 128 * H * hd * 2;
+}
+
+// dqkv[B,T,3C] from dout[B,T,C], qkv, out, lse.  `delta` is scratch of B*H*T floats.  `dq_part` (optional) is scratch of
+// mlb_attn_bwd_scratch_bytes() bytes whose contents do not matter: with it and head size 64 the fused
 // single-kernel backward runs; without it the two-kernel backward (dK/dV kernel + dQ kernel) runs.  If cosT/sinT are given, RoPE's
 // backward rotation is applied to dQ and dK before they are stored (tensor-core path only; returns 1 if it was applied,
 // 0 if the caller still has to rotate, <0 or a CUDA error code > 1 on failure).
-MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, float* dq_acc,
+MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, void* dq_part,
                          int B, int T, int H, int hd, const float* cosT, const float* sinT, cudaStream_t st) {
   const int C = H * hd;
   const float scale = 1.0f / sqrtf((float)hd);
@@ -1303,18 +1388,16 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
     const CUtensorMap* tq = mlb_tmap_cached(qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, 64);
     const CUtensorMap* td = mlb_tmap_cached(dout, (uint64_t)B * T, C, C, 128, 64);
     if (!tq || !td) return -2;
-    AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT};
+    AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT, (bf16*)dq_part, g_timeline};
     dim3 grid((T + 127) / 128, H, B);
-    if (hd == 64 && dq_acc != nullptr && ((uintptr_t)dq_acc % 16 == 0)) {
-      // single fused kernel + dQ finish; dq_acc is fp32 [B*T, C], all zero on entry and all zero again on exit
-      const CUtensorMap* tacc = mlb_tmap_cached(dq_acc, (uint64_t)B * T, C, C, 32, 32, 4);
-      if (!tacc) return -2;
+    if (hd == 64 && dq_part != nullptr && ((uintptr_t)dq_part % 16 == 0)) {
+      // single fused kernel + dQ finish
       static int o0 = set_smem(attn_bwd_fused_tc_kernel, BwdFusedSmem::TOTAL);
       (void)o0;
       dim3 grid_f(((T + 127) / 128 + 1) / 2, H, B);   // a CTA handles a key tile and its mirror
-      attn_bwd_fused_tc_kernel<<<grid_f, BWDF_THREADS, BwdFusedSmem::TOTAL, st>>>(*tq, *td, *tacc, a);
+      attn_bwd_fused_tc_kernel<<<grid_f, BWDF_THREADS, BwdFusedSmem::TOTAL, st>>>(*tq, *td, a);
       const long groups = (long)B * T * H * (hd / 32);
-      attn_dq_finish_k<<<(unsigned)((groups + 255) / 256), 256, 0, st>>>((bf16*)dqkv, dq_acc, (long)B * T, T, H, hd, scale, cosT, sinT);
+      attn_dq_finish_k<<<(unsigned)((groups + 255) / 256), 256, 0, st>>>((bf16*)dqkv, (const bf16*)dq_part, (long)B * T, T, H, hd, scale, cosT, sinT);
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return (int)e + 1000;
       return cosT ? 1 : 0;

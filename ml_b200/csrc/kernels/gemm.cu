@@ -62,6 +62,42 @@ struct GemmArgs {
   int ldo;           // output row pitch in elements
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
   int a3d, b3d;      // MN-major operand fetched through a 3-D tensor map (one TMA per stage) instead of 64-wide 2-D boxes
+  int streamk;       // pair kernel, fp32 add epilogue: every cluster takes an equal contiguous share of all (tile, k-block) units
+};
+
+// Work items of one cluster of the pair kernel.  Static mode: items c, c + nclusters, ... of tiles x splits.
+// Stream-K mode: the tiles' k-blocks are laid end to end (tile-major) and cut into nclusters equal ranges, so a cluster
+// gets at most a tail piece of one tile, whole tiles, and a head piece of another; every piece is add-reduced into the
+// fp32 output, which is what the split-K epilogue does anyway.
+struct WorkItem { int mt, nt, kb0, kb1; };
+struct WorkIter {
+  int t, step, total, tiles_m, tiles_n, kb_per_split, kb_total;
+  long u, u1;
+  bool sk;
+  __device__ WorkIter(const GemmArgs& g, int cid, int ncl)
+      : t(cid), step(ncl), total(g.tiles_m * g.tiles_n * g.splits), tiles_m(g.tiles_m), tiles_n(g.tiles_n),
+        kb_per_split(g.kb_per_split), kb_total(g.kb_total), sk(g.streamk != 0) {
+    const long units = (long)g.tiles_m * g.tiles_n * g.kb_total;
+    u = units * cid / ncl;
+    u1 = units * (cid + 1) / ncl;
+  }
+  __device__ bool next(WorkItem& w) {
+    if (sk) {
+      if (u >= u1) return false;
+      const int tile = (int)(u / kb_total);
+      w.kb0 = (int)(u % kb_total);
+      w.kb1 = (int)min((long)kb_total, w.kb0 + (u1 - u));
+      w.mt = tile % tiles_m; w.nt = tile / tiles_m;
+      u += w.kb1 - w.kb0;
+      return true;
+    }
+    if (t >= total) return false;
+    const int sp = t / (tiles_m * tiles_n);
+    w.mt = t % tiles_m; w.nt = (t / tiles_m) % tiles_n;
+    w.kb0 = sp * kb_per_split; w.kb1 = min(w.kb0 + kb_per_split, kb_total);
+    t += step;
+    return true;
+  }
 };
 
 __device__ __forceinline__ bool wait_piece(const int* flag, int epoch, long limit_ns) {
@@ -290,21 +326,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 //   acc_empty[a] leader only, 8 arrivals: the four epilogue warps of each CTA (the peer's arrive remotely)
 // Persistent: cluster c handles pair-tiles c, c + nclusters, ...; all waits are bounded as in the 1-CTA kernel, and both
 // CTAs meet at a cluster barrier before TMEM is released so neither outlives remote accesses to it.
+template <int EMODE>
 struct Gemm2Smem {
   static constexpr int A_BYTES = 128 * BK * 2;    // this CTA's rows of A
   static constexpr int B_BYTES = 128 * BK * 2;    // this CTA's half of B
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 6;
-  static constexpr int STAGING_BYTES = 4 * 2 * 4096;
+  static constexpr int STAGES = EMODE == 0 ? 5 : 6;
+  static constexpr int BUFS = EMODE == 0 ? 2 : 1;               // staging buffers per epilogue warp
+  static constexpr int STAGING_BYTES = 8 * BUFS * 4096;
   static constexpr int BAR_BYTES = 256;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + BAR_BYTES + 1024;
 };
+constexpr int GEMM2_THREADS = 64 + 8 * 32;   // producer warp, MMA warp, eight epilogue warps
 
-template <bool A_MN, bool B_MN, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+// Epilogue: eight warps per CTA; warp w reads TMEM lanes 32*(w%4).. (the lane group the hardware lets it read) and one
+// 128-column half of the accumulator.  A slab of 32 rows x 128 bytes goes through a swizzled staging buffer, then
+//   EMODE 0: TMA tiled store / fp32 add-reduce (two buffers per warp, one transfer in flight)
+//   EMODE 1: the warp itself writes it out, four full 128-byte rows per instruction (st.global.v4 / red.global.add.v4.f32)
+template <bool A_MN, bool B_MN, int EPI, int EMODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
-  using S = Gemm2Smem;
+  using S = Gemm2Smem<EMODE>;
   constexpr int STAGES = S::STAGES;
   constexpr int BN = 256, PM = 256;    // pair tile
   extern __shared__ uint8_t smem_raw[];
@@ -319,15 +362,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = tc::cluster_ctarank();          // 0 = leader
   const int cid = (int)tc::cluster_id_x(), ncl = (int)tc::cluster_count_x();
-  const int total_tiles = g.tiles_m * g.tiles_n * g.splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; i++) { tc::mbar_init(&full[i], 1); tc::mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; i++) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 8); }
+    for (int i = 0; i < 2; i++) { tc::mbar_init(&acc_full[i], 1); tc::mbar_init(&acc_empty[i], 16); }
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tmA);
     tc::tma_prefetch_desc(&tmB);
-    tc::tma_prefetch_desc(&tmD);
+    if (EMODE == 0) tc::tma_prefetch_desc(&tmD);
   }
   if (warp == 1) tc::tmem_alloc_pair(tmem_slot, 2 * BN);
   tc::tc_fence_before();
@@ -340,11 +382,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (tc::elect_one()) {
       int stage = 0, phase = 0;
       bool ok = true;
-      for (int t = cid; t < total_tiles && ok; t += ncl) {
-        const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n, sp = t / (g.tiles_m * g.tiles_n);
-        const int m0 = mt * PM + (int)rank * 128, n0 = nt * BN + (int)rank * 128;
-        const int kb0 = sp * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, g.kb_total);
-        for (int kb = kb0; kb < kb1; kb++) {
+      WorkIter iter(g, cid, ncl);
+      WorkItem w;
+      while (ok && iter.next(w)) {
+        const int m0 = w.mt * PM + (int)rank * 128, n0 = w.nt * BN + (int)rank * 128;
+        for (int kb = w.kb0; kb < w.kb1; kb++) {
           if (!tc::mbar_wait(&empty[stage], phase ^ 1, 0x21)) { ok = false; break; }
           uint8_t* sA = smem + stage * S::STAGE_BYTES;
           uint8_t* sB = sA + S::A_BYTES;
@@ -374,9 +416,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       constexpr uint32_t idesc = tc::idesc_bf16(PM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0, phase = 0, it = 0;
       bool ok = true;
-      for (int t = cid; t < total_tiles && ok; t += ncl, it++) {
-        const int sp = t / (g.tiles_m * g.tiles_n);
-        const int kb0 = sp * g.kb_per_split, kb1 = min(kb0 + g.kb_per_split, g.kb_total);
+      WorkIter iter(g, cid, ncl);
+      WorkItem w;
+      for (; ok && iter.next(w); it++) {
+        const int kb0 = w.kb0, kb1 = w.kb1;
         const int acc = it & 1, acc_phase = (it >> 1) & 1;
         if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, 0x22)) { ok = false; break; }
         tc::tc_fence_after();
@@ -399,31 +442,36 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (warps 2..5 of each CTA)
-    const int lg = warp & 3;
-    uint8_t* my_stage = staging + lg * 8192;
+    // ---------------------------------------------------------------- epilogue (warps 2..9 of each CTA)
+    const int lg = warp & 3, half = (warp - 2) >> 2;
+    uint8_t* my_stage = staging + (warp - 2) * (S::BUFS * 4096);
     constexpr int SLAB_COLS = (EPI == EPI_BF16) ? 64 : 32;
+    constexpr int SLABS = 128 / SLAB_COLS;       // per warp and tile
+    constexpr int ELEM = (EPI == EPI_BF16) ? 2 : 4;
     int it = 0, slab = 0;
     bool ok = true;
-    for (int t = cid; t < total_tiles && ok; t += ncl, it++) {
-      const int mt = t % g.tiles_m, nt = (t / g.tiles_m) % g.tiles_n;
-      const int m0 = mt * PM + (int)rank * 128, n0 = nt * BN;
+    WorkIter iter(g, cid, ncl);
+    WorkItem w;
+    for (; ok && iter.next(w); it++) {
+      const int m0 = w.mt * PM + (int)rank * 128 + lg * 32, n0 = w.nt * BN + half * 128;
       const int acc = it & 1, acc_phase = (it >> 1) & 1;
       if (!tc::mbar_wait(&acc_full[acc], acc_phase, 0x24)) { ok = false; break; }
       tc::tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN;
-      const bool rows_live = (m0 + lg * 32) < g.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN + half * 128;
+      const bool rows_live = m0 < g.M;
 #pragma unroll 1
-      for (int c = 0; c < BN / SLAB_COLS; c++) {
-        uint8_t* buf = my_stage + (slab & 1) * 4096;
+      for (int c = 0; c < SLABS; c++) {
+        uint8_t* buf = my_stage + (EMODE == 0 ? (slab & 1) * 4096 : 0);
         uint32_t r[32], r2[32];
         tc::tmem_ld32(taddr + c * SLAB_COLS, r);
         if (EPI == EPI_BF16) tc::tmem_ld32(taddr + c * SLAB_COLS + 32, r2);
         tc::tmem_ld_wait();
         const int col0 = n0 + c * SLAB_COLS;
         if (!rows_live || col0 >= g.N) continue;   // warp-uniform
-        if (lane == 0) tc::tma_wait_group_read<1>();
-        __syncwarp();
+        if (EMODE == 0) {
+          if (lane == 0) tc::tma_wait_group_read<1>();   // the transfer that last used this buffer has read it
+          __syncwarp();
+        }
         uint8_t* rowp = buf + lane * 128;
         if (EPI == EPI_BF16) {
 #pragma unroll
@@ -443,12 +491,33 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = pk;
           }
         }
-        tc::fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (EPI == EPI_BF16) tc::tma_store_2d(&tmD, buf, col0, m0 + lg * 32);
-          else tc::tma_reduce_add_2d(&tmD, buf, col0, m0 + lg * 32);
-          tc::tma_commit_group();
+        if (EMODE == 0) {
+          tc::fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (EPI == EPI_BF16) tc::tma_store_2d(&tmD, buf, col0, m0);
+            else tc::tma_reduce_add_2d(&tmD, buf, col0, m0);
+            tc::tma_commit_group();
+          }
+        } else {
+          __syncwarp();
+          const int ch = lane & 7, gcol = col0 + ch * (16 / ELEM);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const int row = i * 4 + (lane >> 3);
+            const uint4 v = *reinterpret_cast<const uint4*>(buf + row * 128 + ((ch ^ (row & 7)) << 4));
+            if (m0 + row < g.M && gcol < g.N) {
+              uint8_t* dst = (uint8_t*)g.out + ((size_t)(m0 + row) * g.ldo + gcol) * ELEM;
+              if (EPI == EPI_BF16) {
+                *reinterpret_cast<uint4*>(dst) = v;
+              } else {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(v.x)),
+                             "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                             : "memory");
+              }
+            }
+          }
+          __syncwarp();   // the buffer is rewritten by the next slab
         }
         slab++;
       }
@@ -456,7 +525,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       __syncwarp();
       if (lane == 0) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_empty[acc]), 0));
     }
-    if (lane == 0) tc::tma_wait_group<0>();
+    if (EMODE == 0 && lane == 0) tc::tma_wait_group<0>();
   }
   tc::tc_fence_before();
   tc::cluster_sync();      // no CTA frees TMEM or exits while its peer may still signal or read it
@@ -618,27 +687,30 @@ int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap*
 // resident at once (a GPC with an odd number of usable SMs leaves one without a partner), so the static tile
 // schedule never waits for a second wave of CTAs.
 int g_use_pairs = 1;         // tuning hook: 0 = always the 1-CTA kernel
-template <bool A_MN, bool B_MN, int EPI>
+int g_streamk = 1;           // tuning hook: weight-gradient products cut into equal k-block ranges per cluster
+int g_epi_mode = 1;          // tuning hook: pair kernel's epilogue, 0 = TMA store / reduce, 1 = coalesced stores by the warps
+template <bool A_MN, bool B_MN, int EPI, int EMODE>
 int launch_tc2(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, const GemmArgs& g, cudaStream_t st) {
-  auto kern = gemm_tc2_kernel<A_MN, B_MN, EPI>;
+  using Gemm2Smem = Gemm2Smem<EMODE>;
+  auto kern = gemm_tc2_kernel<A_MN, B_MN, EPI, EMODE>;
   static int max_clusters = -1;
   if (max_clusters < 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Smem::TOTAL);
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_sms() & ~1);
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(GEMM2_THREADS);
     cfg.dynamicSmemBytes = Gemm2Smem::TOTAL;
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
     if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = num_sms() / 2; }
     max_clusters = n < num_sms() / 2 ? n : num_sms() / 2;
   }
-  int total = g.tiles_m * g.tiles_n * g.splits;
+  int total = g.streamk ? g.tiles_m * g.tiles_n * g.kb_total : g.tiles_m * g.tiles_n * g.splits;
   int cap = max_clusters;
   if (g_max_ctas > 0 && g_max_ctas / 2 < cap) cap = g_max_ctas / 2 > 0 ? g_max_ctas / 2 : 1;
   int clusters = total < cap ? total : cap;
-  kern<<<2 * clusters, GEMM_THREADS, Gemm2Smem::TOTAL, st>>>(*tmA, *tmB, *tmD, g);
+  kern<<<2 * clusters, GEMM2_THREADS, Gemm2Smem::TOTAL, st>>>(*tmA, *tmB, *tmD, g);
   return (int)cudaGetLastError();
 }
 int pair_clusters() { return (g_max_ctas > 0 ? g_max_ctas : num_sms()) / 2; }
@@ -705,6 +777,7 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   g.kb_per_split = ceil_div_i(g.kb_total, g.splits);
   g.splits = ceil_div_i(g.kb_total, g.kb_per_split);
   g.a3d = g.b3d = 0;
+  g.streamk = (pairs && EPI == EPI_F32_ADD && g_streamk && g_force_splits == 0) ? 1 : 0;
   const CUtensorMap* tmA = nullptr;
   const CUtensorMap* tmB = nullptr;
   if (A_MN && g_use_3d) { tmA = mlb_tmap_mn3d_cached(A, K, M, lda, BM / 64); g.a3d = tmA != nullptr; }
@@ -714,7 +787,8 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   if (!tmB) tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, b_rows, 64);
   const CUtensorMap* tmD = (EPI == EPI_BF16) ? mlb_tmap_cached(out, M, N, ldo, 32, 64, 2) : mlb_tmap_cached(out, M, N, ldo, 32, 32, 4);
   if (!tmA || !tmB || !tmD) return -2;
-  if (pairs) return launch_tc2<A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
+  if (pairs && g_epi_mode == 0) return launch_tc2<A_MN, B_MN, EPI, 0>(tmA, tmB, tmD, g, st);
+  if (pairs) return launch_tc2<A_MN, B_MN, EPI, 1>(tmA, tmB, tmD, g, st);
   if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
   return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
 }
@@ -734,6 +808,25 @@ MLB_API int mlb_linear_dw(void* dW, const void* dout, const void* x, int M, int 
   return gemm_dispatch<true, true, EPI_F32_ADD>(dW, lddw, (const bf16*)dout, lddo, (const bf16*)x, ldx, N, K, M, st);
 }
 
+// General entry: D[M,N] = sum_k A(m,k) B(n,k), bf16 store (accumulate = 0) or fp32 += (accumulate = 1).
+//   a_mn = 0: A stored [M,K] (K contiguous, pitch lda);  a_mn = 1: A stored [K,M] (M contiguous, pitch lda); same for B with N.
+MLB_API int mlb_gemm(void* out, const void* A, const void* B, int M, int N, int K, int ldo, int lda, int ldb, int a_mn, int b_mn,
+                     int accumulate, cudaStream_t st) {
+  const bf16* a = (const bf16*)A;
+  const bf16* b = (const bf16*)B;
+  const int sel = (a_mn ? 4 : 0) | (b_mn ? 2 : 0) | (accumulate ? 1 : 0);
+  switch (sel) {
+    case 0: return gemm_dispatch<false, false, EPI_BF16>(out, ldo, a, lda, b, ldb, M, N, K, st);
+    case 1: return gemm_dispatch<false, false, EPI_F32_ADD>(out, ldo, a, lda, b, ldb, M, N, K, st);
+    case 2: return gemm_dispatch<false, true, EPI_BF16>(out, ldo, a, lda, b, ldb, M, N, K, st);
+    case 3: return gemm_dispatch<false, true, EPI_F32_ADD>(out, ldo, a, lda, b, ldb, M, N, K, st);
+    case 4: return gemm_dispatch<true, false, EPI_BF16>(out, ldo, a, lda, b, ldb, M, N, K, st);
+    case 5: return gemm_dispatch<true, false, EPI_F32_ADD>(out, ldo, a, lda, b, ldb, M, N, K, st);
+    case 6: return gemm_dispatch<true, true, EPI_BF16>(out, ldo, a, lda, b, ldb, M, N, K, st);
+    default: return gemm_dispatch<true, true, EPI_F32_ADD>(out, ldo, a, lda, b, ldb, M, N, K, st);
+  }
+}
+
 // out[M,N] = x[M,K] . W[N,K]^T where W lies inside a sharded parameter unit that this launch also all-gathers:
 //   unit_dst    local gather slot (start of the unit, 16-byte aligned), W == unit_dst + w_off_elems
 //   src_ptrs    device array [world] of the ranks' shard bases; every shard holds shard_elems bf16 (multiple of 8)
@@ -751,7 +844,7 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   GemmArgs g;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
-  g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0;
+  g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0;
   GatherArgs ga;
   ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
   ga.b_lo_vec = w_off_elems / 8; ga.b_hi_vec = (w_off_elems + (long)N * K) / 8; ga.b_row_vec = K / 8;
@@ -769,5 +862,7 @@ MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
 MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }
 MLB_API void mlb_gemm_use_3d_maps(int on) { g_use_3d = on; }
 MLB_API void mlb_gemm_use_pairs(int on) { g_use_pairs = on; }
+MLB_API void mlb_gemm_epilogue_mode(int m) { g_epi_mode = m; }
+MLB_API void mlb_gemm_streamk(int on) { g_streamk = on; }
 
 MLB_DEFINE_ERROR_WORD(gemm)

@@ -59,6 +59,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int wh
   }
 }
 
+// Same bound, but the polling thread sleeps between probes so that it does not compete for issue slots with warps that
+// share its scheduler (for waits that are expected to last hundreds of cycles or more).
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, int where = 0, unsigned ns = 40) {
+  if (mbar_try(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; i++) {
+      __nanosleep(ns);
+      if (mbar_try(bar, parity)) return true;
+    }
+    if (globaltimer_ns() - t0 > MLB_MBAR_TIMEOUT_NS) {
+      mlb_set_error(MLB_ERR_MBAR_TIMEOUT, where);
+      return false;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ fences
 __device__ __forceinline__ void fence_async_smem() {  // generic-proxy smem writes -> visible to TMA / tcgen05
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -135,6 +153,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// Warp-collective store: lane i writes 16 consecutive 32-bit columns of TMEM lane 32*w+i.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------ descriptors
@@ -170,6 +198,16 @@ __device__ __forceinline__ void mma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, ui
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same with the A operand in TMEM: [128 lanes = M rows] x K, bf16 pairs packed into 32-bit columns (k even in the low
+// half), i.e. 8 columns per K = 16 step; always K-major.
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive on `bar` once every tcgen05.mma issued so far by this thread has completed.

@@ -29,14 +29,18 @@ def lib():
         "mlb_linear_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
         "mlb_linear_dx": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
         "mlb_linear_dw": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
+        "mlb_gemm": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
         "mlb_gemm_force_simt": [_i32],
         "mlb_gemm_set_max_ctas": [_i32],
         "mlb_gemm_set_splits": [_i32],
         "mlb_gemm_use_3d_maps": [_i32],
         "mlb_gemm_use_pairs": [_i32],
+        "mlb_gemm_epilogue_mode": [_i32],
+        "mlb_gemm_streamk": [_i32],
         "mlb_attn_force_simt": [_i32],
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
+        "mlb_attn_bwd_scratch_bytes": [_i32, _i32, _i32, _i32],
         "mlb_embed_fwd": [_vp, _vp, _vp, _i64, _i32, _vp],
         "mlb_embed_bwd": [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp],
         "mlb_set_prefix": [_vp, _vp, _i32, _i32, _i32, _i32, _vp],
@@ -155,6 +159,15 @@ def linear_dw(dW, dout, x):
     _chk(lib().mlb_linear_dw(_f(dW), _b(dout), _b(x), M, N, K, dW.stride(0), dout.stride(0), x.stride(0), _st()), "linear_dw")
 
 
+def gemm(out, A, B, a_mn=False, b_mn=False, accumulate=False):
+    """D[M,N] = sum_k A(m,k) B(n,k).  A is [M,K] (a_mn=False) or stored transposed [K,M] (a_mn=True); B likewise with N.
+    `out` is bf16 (overwritten) or, with accumulate=True, fp32 (added to)."""
+    M, K = (A.shape[1], A.shape[0]) if a_mn else A.shape
+    N = B.shape[1] if b_mn else B.shape[0]
+    _chk(lib().mlb_gemm(out.data_ptr(), _b(A), _b(B), M, N, K, out.stride(0), A.stride(0), B.stride(0), int(a_mn), int(b_mn),
+                        int(accumulate), _st()), "gemm")
+
+
 def linear_fwd_gather(out, x, N, K, unit_dst, w_off, src_table, shard_elems, world, flags, ctr, spin_limit_s=2.0):
     """out = x . W^T with W = unit_dst[w_off : w_off + N*K] viewed [N, K]; the same launch all-gathers the whole sharded
     unit into unit_dst from the ranks' shards (device pointer table `src_table`).  Cooperative launch."""
@@ -173,6 +186,7 @@ def attn_fwd(out, lse, qkv, B, T, H, hd):
 
 
 FUSED_ATTN_BWD = True   # head size 64: single fused backward kernel (False = separate dK/dV and dQ kernels)
+FUSED_ATTN_BWD_MAX_SCRATCH = 4 << 30   # bytes of dQ partials (grows with B*T*T) the fused backward may use
 
 
 def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
@@ -181,8 +195,12 @@ def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
     delta = scratch("attn_delta", B * H * T, torch.float32, qkv.device)
     acc = None
     if hd == 64 and FUSED_ATTN_BWD:
-        # fp32 dQ accumulator of the fused backward: zero-filled once here, left zero by every call
-        acc = scratch(("attn_dq_acc", B * T * H * hd), B * T * H * hd, torch.float32, qkv.device, zero=True).data_ptr()
+        # per-(query tile, key tile) bf16 partials of dQ; past FUSED_ATTN_BWD_MAX_SCRATCH the two-kernel backward runs
+        L = lib()
+        L.mlb_attn_bwd_scratch_bytes.restype = C.c_long
+        nbytes = L.mlb_attn_bwd_scratch_bytes(B, T, H, hd)
+        if 0 < nbytes <= FUSED_ATTN_BWD_MAX_SCRATCH:
+            acc = scratch(("attn_dq_part", nbytes), nbytes // 2, torch.bfloat16, qkv.device).data_ptr()
     cp = _f(rope[0]) if rope is not None else None
     sp = _f(rope[1]) if rope is not None else None
     rc = lib().mlb_attn_bwd(_b(dqkv), _b(dout), _b(qkv), _b(out), _f(lse), _f(delta), acc, B, T, H, hd, cp, sp, _st())

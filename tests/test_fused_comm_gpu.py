@@ -21,19 +21,25 @@ def test_fused_engine_world1_matches_separate_adamw():
     from ml_b200.trainer import Trainer
     from ml_b200.utils.rng import Stream
     cfg = Config(V=512, C=256, L=2, H=4, I=512, T=128)
+    from ml_b200.ops import native
     ids, tgt = Stream(3).token_pairs(2 * 128, 512)
     res = []
-    for comm in ("nccl", "fused"):
-        r = RunConfig()
-        r.comm = comm
-        tr = Trainer(cfg, 2, "cuda:0", r, lr=1e-3, wd=0.1)
-        assert (tr.ddp.fused is not None) == (comm == "fused")
-        tr.set_batch(ids.cuda(), tgt.cuda())
-        for _ in range(5):
-            tr.step()
-        torch.cuda.synchronize()
-        res.append((tr.model.master.clone(), tr.model.params.clone(), tr.loss()))
-    # same gradients, same update formula; only the GEMM split-K reduction order may differ
+    # one work item per weight-gradient tile: no fp32 add-reduces whose order could differ between the two runs
+    native.lib().mlb_gemm_set_splits(1)
+    try:
+        for comm in ("nccl", "fused"):
+            r = RunConfig()
+            r.comm = comm
+            tr = Trainer(cfg, 2, "cuda:0", r, lr=1e-3, wd=0.1)
+            assert (tr.ddp.fused is not None) == (comm == "fused")
+            tr.set_batch(ids.cuda(), tgt.cuda())
+            for _ in range(5):
+                tr.step()
+            torch.cuda.synchronize()
+            res.append((tr.model.master.clone(), tr.model.params.clone(), tr.loss()))
+    finally:
+        native.lib().mlb_gemm_set_splits(0)
+    # same gradients, same update formula
     assert (res[0][0] - res[1][0]).abs().max() < 2e-4
     assert abs(res[0][2] - res[1][2]) < 2e-2
     assert torch.equal(res[1][1], res[1][0].to(torch.bfloat16))     # bf16 copy written by the fused kernel
@@ -118,6 +124,7 @@ def test_fused_matches_nccl_two_gpus():
         from ml_b200.data import bench_batch
         from ml_b200.ops import native
         rank, world, local, dev = init_distributed()
+        native.lib().mlb_gemm_set_splits(1)   # deterministic weight gradients: the two runs may only differ by the reduction
         cfg = Config(V=512, C=256, L=2, H=4, I=512, T=128)
         ids, tgt = bench_batch(2, 128, 512, rank)
         res = {}
@@ -154,6 +161,7 @@ def test_rank_leaves_between_steps_ends_with_error_not_hang():
         from ml_b200.data import bench_batch
         from ml_b200.ops import native
         rank, world, local, dev = init_distributed()
+        native.lib().mlb_gemm_set_splits(1)   # deterministic weight gradients: the two runs may only differ by the reduction
         cfg = Config(V=256, C=128, L=1, H=2, I=256, T=128)
         r = RunConfig(); r.comm = "fused"
         tr = Trainer(cfg, 1, dev, r, lr=1e-3, wd=0.0, world=world, rank=rank)
@@ -187,19 +195,24 @@ def test_fsdp_fused_world1_matches_unsharded():
     ref = GPT(cfg, 2, "cuda:0")
     ref.init_weights(1234)
     outs = {}
-    for comm in ("nccl", "fused"):
-        g = GPT(cfg, 2, "cuda:0", sharded=True)
-        f = FSDP(g, 1, 0, comm=comm, hyper=dict(lr=1e-3, wd=0.1))
-        g.init_weights(1234)
+    # one work item per weight-gradient tile: no fp32 add-reduces whose order could differ between the runs
+    native.lib().mlb_gemm_set_splits(1)
+    try:
+        for comm in ("nccl", "fused"):
+            g = GPT(cfg, 2, "cuda:0", sharded=True)
+            f = FSDP(g, 1, 0, comm=comm, hyper=dict(lr=1e-3, wd=0.1))
+            g.init_weights(1234)
+            for s in range(4):
+                f.step(di, dt)
+            torch.cuda.synchronize()
+            outs[comm] = (f.full_master(), g.mean_loss())
         for s in range(4):
-            f.step(di, dt)
+            ref.forward(di)
+            ref.backward(di, dt)
+            ref.adamw(1e-3, wd=0.1, t=s + 1)
         torch.cuda.synchronize()
-        outs[comm] = (f.full_master(), g.mean_loss())
-    for s in range(4):
-        ref.forward(di)
-        ref.backward(di, dt)
-        ref.adamw(1e-3, wd=0.1, t=s + 1)
-    torch.cuda.synchronize()
+    finally:
+        native.lib().mlb_gemm_set_splits(0)
     assert native.get_error() == 0
     for comm in outs:
         assert (outs[comm][0] - ref.master).abs().max() < 2e-4, comm
@@ -218,6 +231,7 @@ def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state():
         from ml_b200.data import bench_batch
         from ml_b200.ops import native
         rank, world, local, dev = init_distributed()
+        native.lib().mlb_gemm_set_splits(1)   # deterministic weight gradients: the two runs may only differ by the reduction
         cfg = Config(V=512, C=256, L=3, H=4, I=512, T=128)
         ids, tgt = bench_batch(2, 128, 512, rank)
         res = {}

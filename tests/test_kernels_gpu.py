@@ -45,12 +45,18 @@ GEMM_SHAPES = [(256, 256, 128), (384, 768, 768), (1024, 2304, 768), (512, 4096, 
                (2048, 768, 2048), (256, 1000, 512), (4096 + 136, 776, 392)]
 
 
-@pytest.fixture(params=[1, 0], ids=["cta_pair", "single_cta"])
+@pytest.fixture(params=[(1, 1, 1), (1, 0, 0), (0, 0, 0)], ids=["cta_pair", "cta_pair_tma_epilogue_splitk", "single_cta"])
 def gemm_mode(request):
-    """Large products have two tcgen05 kernels: a 256x256 tile shared by a CTA pair (cta_group::2), or 128x256 per CTA."""
-    nat().lib().mlb_gemm_use_pairs(request.param)
+    """Large products have two tcgen05 kernels: a 256x256 tile shared by a CTA pair (cta_group::2) whose epilogue either
+    writes coalesced rows itself or hands slabs to TMA (weight gradients: equal k-block ranges per cluster, or a fixed
+    split count), or 128x256 per CTA."""
+    nat().lib().mlb_gemm_use_pairs(request.param[0])
+    nat().lib().mlb_gemm_epilogue_mode(request.param[1])
+    nat().lib().mlb_gemm_streamk(request.param[2])
     yield request.param
     nat().lib().mlb_gemm_use_pairs(1)
+    nat().lib().mlb_gemm_epilogue_mode(1)
+    nat().lib().mlb_gemm_streamk(1)
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
@@ -82,6 +88,25 @@ def test_linear_dw_accumulates(M, N, K, gemm_mode):
     nat().linear_dw(dW, dout, x)
     ref.linear_dw(exp, dout, x)
     close(dW, exp, rtol=1e-2, atol=1e-2, name="linear_dw")
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("acc", [False, True])
+def test_gemm_general_entry_all_layouts(a_mn, b_mn, acc, gemm_mode):
+    """D = A.B^T with either operand stored transposed, bf16 store or fp32 accumulate."""
+    torch.manual_seed(5)
+    M, N, K = 640, 520, 328
+    A = rnd(K, M) if a_mn else rnd(M, K)
+    B = rnd(K, N, scale=0.05) if b_mn else rnd(N, K, scale=0.05)
+    exp = (A.t() if a_mn else A).float() @ (B if b_mn else B.t()).float()
+    if acc:
+        out = torch.randn(M, N, device=dev())
+        exp = exp + out
+    else:
+        out = torch.empty(M, N, device=dev(), dtype=torch.bfloat16)
+    nat().gemm(out, A, B, a_mn, b_mn, acc)
+    close(out, exp, name="gemm")
 
 
 def test_gemm_simt_path_odd_shape():
