@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, flo
 // floats, `ticket` = 1 + RMS_GROUPS ints that are 0 on entry and left 0 on exit.
 constexpr int RMS_GROUPS = 16;
 template <int VPL>  // VPL = C / 256 (vectors of 8 per lane); 0 = generic C (scalar path)
-__global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, float* __restrict__ dw, const bf16* __restrict__ dy,
+__global__ void __launch_bounds__(256, (VPL <= 3) ? 2 : 1) rmsnorm_bwd_k(bf16* __restrict__ dx, float* __restrict__ dw, const bf16* __restrict__ dy,
                                                      const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                      const float* __restrict__ rstd, const bf16* __restrict__ add, long rows,
                                                      int C, float* __restrict__ partial, int* __restrict__ ticket) {
@@ -144,13 +144,15 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, floa
   const float invC = 1.f / (float)C;
   if (VPL > 0) {
     constexpr int NV = VPL > 0 ? VPL : 1;
-    constexpr bool CACHE = NV <= 4;  // wider rows re-read w/x/dy from L1 instead of holding them in registers
+    constexpr bool CACHE = NV <= 4;    // x / dy of the row stay in registers between the two passes (wider rows re-read them from L1)
+    constexpr bool CACHE_W = NV <= 2;  // the weight vector too (two resident blocks per SM leave 128 registers per thread)
     constexpr int NC = CACHE ? NV : 1;
+    constexpr int NW = CACHE_W ? NV : 1;
     float acc[NV][8];
-    float ww[NC][8];
+    float ww[NW][8];
 #pragma unroll
     for (int v = 0; v < NV; v++) {
-      if (CACHE) load8(w + (v * 32 + lane) * 8, ww[v]);
+      if (CACHE_W) load8(w + (v * 32 + lane) * 8, ww[v]);
 #pragma unroll
       for (int j = 0; j < 8; j++) acc[v][j] = 0.f;
     }
@@ -161,20 +163,21 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, floa
 #pragma unroll
       for (int v = 0; v < NV; v++) {
         const long off = row * C + (v * 32 + lane) * 8;
-        const int cv = CACHE ? v : 0;
+        const int cv = CACHE ? v : 0, cw = CACHE_W ? v : 0;
         load8(x + off, xv[cv]);
         load8(dy + off, dv[cv]);
-        if (!CACHE) load8(w + (v * 32 + lane) * 8, ww[0]);
+        if (!CACHE_W) load8(w + (v * 32 + lane) * 8, ww[0]);
 #pragma unroll
-        for (int j = 0; j < 8; j++) dot += dv[cv][j] * ww[cv][j] * xv[cv][j];
+        for (int j = 0; j < 8; j++) dot += dv[cv][j] * ww[cw][j] * xv[cv][j];
       }
       dot = warp_sum(dot);
       const float k = r * r * r * invC * dot;
 #pragma unroll
       for (int v = 0; v < NV; v++) {
         const long off = row * C + (v * 32 + lane) * 8;
-        const int cv = CACHE ? v : 0;
-        if (!CACHE) { load8(x + off, xv[0]); load8(dy + off, dv[0]); load8(w + (v * 32 + lane) * 8, ww[0]); }
+        const int cv = CACHE ? v : 0, cw = CACHE_W ? v : 0;
+        if (!CACHE) { load8(x + off, xv[0]); load8(dy + off, dv[0]); }
+        if (!CACHE_W) load8(w + (v * 32 + lane) * 8, ww[0]);
         float o[8];
         if (add) load8(add + off, o);
         else {
@@ -183,7 +186,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(bf16* __restrict__ dx, floa
         }
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-          o[j] += dv[cv][j] * ww[cv][j] * r - xv[cv][j] * k;
+          o[j] += dv[cv][j] * ww[cw][j] * r - xv[cv][j] * k;
           acc[v][j] += dv[cv][j] * xv[cv][j] * r;
         }
         store8(dx + off, o);
