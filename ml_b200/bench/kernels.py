@@ -3,6 +3,7 @@ train/gemm_bench.cu, train/attn_bench.cu, train/norm_bench2.cu).
 
     python -m ml_b200.bench.kernels gemm  [--M 16384]           tcgen05 GEMMs on the model's shapes vs torch.matmul (cuBLAS)
     python -m ml_b200.bench.kernels layouts [--K 8192]          main-loop cost per 64-deep step for K-major / MN-major operands
+    python -m ml_b200.bench.kernels mma                         cycles per tcgen05.mma by N and A-operand source
     python -m ml_b200.bench.kernels attn  [--B 16 --T 1024]     flash attention fwd / bwd vs torch SDPA
     python -m ml_b200.bench.kernels norm                        RMSNorm fwd / add+norm / bwd, CE, AdamW, SwiGLU bandwidth
     python -m ml_b200.bench.kernels once  --case attn|gemm      a few un-timed launches (what an `ncu` capture wraps)
@@ -113,6 +114,26 @@ def bench_layouts(a):
     print("kernel error word:", nat.get_error())
 
 
+def bench_mma(a):
+    """Cycles per tcgen05.mma (M=128, K=16) issued back to back by one thread, by N and by where A lives."""
+    import ctypes as C
+    L = nat.lib()
+    L.mlb_mma_probe.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    cyc = torch.zeros(256, dtype=torch.int64, device="cuda")
+    reps = 256
+    for N in (64, 128, 256):
+        for ts in (0, 1):
+            for _ in range(2):
+                rc = L.mlb_mma_probe(cyc.data_ptr(), N, ts, reps, torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            assert rc == 0
+            c = cyc[:148].float()
+            per = c.median().item() / (reps * 4)
+            print(f"M=128 N={N:3d} K=16  A from {'TMEM' if ts else 'smem'}: {per:6.1f} cycles per MMA  "
+                  f"({2 * 128 * N * 16 / per:6.0f} FLOP/cycle/SM; dense bf16 peak 8192)")
+    print("kernel error word:", nat.get_error())
+
+
 def attn_tensors(B, T, H, hd):
     dev = torch.device("cuda")
     C = H * hd
@@ -128,6 +149,7 @@ def bench_attn(a):
     B, T, H, hd = a.B, a.T, a.H, a.hd
     qkv, out, lse, dout, dqkv = attn_tensors(B, T, H, hd)
     fl = 4.0 * B * H * T * T * hd / 2      # causal forward
+    nat.lib().mlb_attn_fwd_mode(a.fwd_mode)
     t = timeit(lambda: nat.attn_fwd(out, lse, qkv, B, T, H, hd), a.iters, a.warm)
     tb = timeit(lambda: nat.attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd), a.iters, a.warm)
     q, k, v = [qkv.view(B, T, 3, H, hd)[:, :, i].permute(0, 2, 1, 3) for i in range(3)]
@@ -212,7 +234,7 @@ def once(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "layouts", "attn", "norm", "once"])
+    ap.add_argument("what", choices=["gemm", "layouts", "mma", "attn", "norm", "once"])
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--case", default="attn", choices=["attn", "gemm", "norm"])
     ap.add_argument("--M", type=int, default=16384)
@@ -225,11 +247,12 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
+    ap.add_argument("--fwd-mode", type=int, default=1, help="attention forward, head size 64: 1/2 = thread-per-row kernel (2: tiles staggered), 0 = four threads per row")
     ap.add_argument("--streamk", type=int, default=1, help="pair GEMM, weight gradients: 1 = equal k-block ranges per cluster, 0 = fixed split count")
     ap.add_argument("--epi", type=int, default=1, help="pair GEMM epilogue: 1 = coalesced stores by the warps, 0 = TMA store / add-reduce")
     ap.add_argument("--pairs", type=int, default=1, help="GEMM: 1 = CTA-pair kernel (cta_group::2), 0 = one CTA per tile")
     a = ap.parse_args()
-    {"gemm": bench_gemm, "layouts": bench_layouts, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
+    {"gemm": bench_gemm, "layouts": bench_layouts, "mma": bench_mma, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
 
 
 if __name__ == "__main__":

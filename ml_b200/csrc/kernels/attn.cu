@@ -27,6 +27,10 @@ constexpr int TILE_BYTES = 128 * 64 * 2;  // one [128 rows x 64 bf16] swizzled c
 __device__ __forceinline__ uint64_t desc_k(uint32_t base, int ks) {
   return tc::smem_desc_sw128(base + (ks >> 2) * TILE_BYTES + (ks & 3) * 32, 16, 1024);
 }
+// The same descriptors with the address arithmetic left to the caller: base + (byte offset >> 4).  K-major: +2 per
+// 16-element k-step inside a 64-column chunk, + TILE_BYTES/16 per chunk; MN-major: +128 per 16-row k-step.
+__device__ __forceinline__ uint64_t desc_base_k(uint32_t base) { return tc::smem_desc_sw128(base, 16, 1024); }
+__device__ __forceinline__ uint64_t desc_base_mn(uint32_t base) { return tc::smem_desc_sw128(base, TILE_BYTES, 1024); }
 // MN-major view of a [128 contraction rows x (64*chunks)] tile: k-step ks covers 16 rows.
 __device__ __forceinline__ uint64_t desc_mn(uint32_t base, int ks) {
   return tc::smem_desc_sw128(base + ks * 2048, TILE_BYTES, 1024);
@@ -46,6 +50,7 @@ struct AttnArgs {
   const float* cosT;  // optional fused RoPE-backward tables [T, hd/2]
   const float* sinT;
   bf16* dq_part;       // fused backward: dQ partial tiles [B][nq(nq+1)/2 (query tile i, key tile kt <= i)][128][C]
+  int variant;         // forward tuning switch (see the kernel)
   long long* timeline; // optional: SM cycle stamps of CTA (0,0,0) of the fused backward, eight per (query block) step
 };
 
@@ -83,6 +88,12 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
   uint64_t r;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -422,6 +433,329 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
   if (warp == ATT_SOFTMAX_WARPS) tc::tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// ================================================================== forward, head size 64: one thread per query row
+// A CTA works on PAIRS of 128-query tiles of one (sample, head): tile 0 is owned by warps 0-3, tile 1 by warps 4-7
+// (thread = one query row: no cross-thread reductions, no shared-memory exchange), warp 8 issues every TMA load and MMA.
+// Per key block j and tile t:   S_t = Q_t K_j^T (TMEM) -> row max, p = exp2(s*c - m) in 32-column chunks straight out of
+// TMEM -> P_t written as packed bf16 into its own TMEM columns (the A operand of the next MMA never touches shared
+// memory, and the next block's scores can be issued before P_t V_j) -> O_blk = P_t V_j -> folded into the row's 64 fp32
+// accumulators in registers with the usual running-max rescale.
+// The two tiles share K_j / V_j (one load per 256 queries) and run out of phase: while one tile's threads compute
+// exponentials the tensor core works for the other tile.  Both tiles walk the same key blocks; the block past tile
+// 0's diagonal is fully masked for it (its threads write P = 0 without computing anything).
+// mbarriers per tile: bar_s S complete (commit) | bar_p P stored (4 warps) | bar_o O_blk complete (commit) |
+// bar_of O_blk folded (4 warps).  K has 2 slots, V 3: block g+2 is fetched as soon as both tiles have consumed S(g),
+// which (in-order tensor pipe) also means P V of block g-1 has finished.
+struct Fwd2Smem {
+  static constexpr int Q = 0;                          // 2 buffers x 2 tiles
+  static constexpr int KN = 3;                         // K slots; V has one more
+  static constexpr int K = Q + 4 * TILE_BYTES;
+  static constexpr int V = K + KN * TILE_BYTES;
+  static constexpr int BAR = V + (KN + 1) * TILE_BYTES;
+  static constexpr int TOTAL = BAR + 256 + 1024;
+};
+constexpr int FWD2_THREADS = 10 * 32;   // 8 softmax warps, MMA warp, loader warp
+
+struct Fwd2Step {   // one key block of one item in this CTA's flattened sequence
+  int w, li, p, b, h, nkb, j;
+  bool valid;
+  __device__ __forceinline__ void set_item(int w_, int li_, int total, int npair, int nq, int BH, int H) {
+    w = w_; li = li_; valid = w_ < total; j = 0;
+    if (valid) {
+      p = npair - 1 - w_ / BH;                 // heaviest pairs first
+      const int bh = w_ % BH;
+      b = bh / H; h = bh % H;
+      nkb = min(2 * p + 2, nq);
+    } else {
+      p = b = h = 0; nkb = 1;
+    }
+  }
+  __device__ __forceinline__ void advance(int total, int npair, int nq, int BH, int H, int stride) {
+    if (!valid) return;
+    if (++j >= nkb) set_item(w + stride, li + 1, total, npair, nq, BH, H);
+  }
+};
+
+__global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
+  using S = Fwd2Smem;
+  constexpr int HD = 64;
+  constexpr uint32_t TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + S::BAR);
+  constexpr int KN = S::KN, VN = S::KN + 1;
+  uint64_t *bar_q = bars /*[2]*/, *bar_s = bars + 2 /*[2]*/, *bar_p = bars + 4 /*[2]*/, *bar_o = bars + 6 /*[2]*/, *bar_of = bars + 8 /*[2]*/,
+           *bar_k = bars + 10 /*[KN]*/, *bar_v = bars + 10 + KN /*[VN]*/;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 10 + KN + VN);
+  volatile int* s_abort = (volatile int*)(bars + 11 + KN + VN);
+  {
+    __shared__ int s_skip;
+    if (threadIdx.x == 0) s_skip = *(volatile int*)&g_mlb_error;
+    __syncthreads();
+    if (s_skip != 0) return;
+  }
+  const int nq = (a.T + 127) / 128, npair = (nq + 1) / 2;
+  const int BH = a.B * a.H, total = npair * BH, stride = gridDim.x;
+  const int C = a.H * HD;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; i++) {
+      tc::mbar_init(&bar_q[i], 1); tc::mbar_init(&bar_s[i], 1); tc::mbar_init(&bar_o[i], 1);
+      tc::mbar_init(&bar_p[i], 4); tc::mbar_init(&bar_of[i], 4);
+    }
+    for (int i = 0; i < KN; i++) tc::mbar_init(&bar_k[i], 1);
+    for (int i = 0; i < VN; i++) tc::mbar_init(&bar_v[i], 1);
+    *s_abort = 0;
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tm);
+  }
+  if (warp == 8) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;     // S0 @0, S1 @128, P0 @256, P1 @320 (bf16 pairs), O0 @384, O1 @448
+  auto wait = [&](uint64_t* bar, uint32_t phase, int where) -> bool {
+    if (*s_abort) return false;
+    if (!tc::mbar_wait(bar, phase, where)) { *s_abort = 1; return false; }
+    return true;
+  };
+
+  if (warp == 9) {
+    // ---------------------------------------------------------------- loader warp: every TMA load (and the index arithmetic)
+    if (lane == 0) {
+      auto load_q = [&](const Fwd2Step& s) {
+        const int qb = s.li & 1;
+        tc::mbar_expect_tx(&bar_q[qb], 2 * TILE_BYTES);
+        for (int t = 0; t < 2; t++)
+          tc::tma_load_2d(smem + S::Q + (qb * 2 + t) * TILE_BYTES, &tm, &bar_q[qb], s.h * HD, s.b * a.T + (2 * s.p + t) * 128);
+      };
+      auto load_kv = [&](const Fwd2Step& s, int g) {
+        tc::mbar_expect_tx(&bar_k[g % KN], TILE_BYTES);
+        tc::tma_load_2d(smem + S::K + (g % KN) * TILE_BYTES, &tm, &bar_k[g % KN], C + s.h * HD, s.b * a.T + s.j * 128);
+        tc::mbar_expect_tx(&bar_v[g % VN], TILE_BYTES);
+        tc::tma_load_2d(smem + S::V + (g % VN) * TILE_BYTES, &tm, &bar_v[g % VN], 2 * C + s.h * HD, s.b * a.T + s.j * 128);
+      };
+      Fwd2Step c0, c3;      // steps g and g + KN
+      c0.set_item(blockIdx.x, 0, total, npair, nq, BH, a.H);
+      c3 = c0;
+      if (c0.valid) {
+        load_q(c0);
+        Fwd2Step nx;
+        nx.set_item(blockIdx.x + stride, 1, total, npair, nq, BH, a.H);
+        if (nx.valid) load_q(nx);          // the second item's Q goes into the other buffer right away
+        for (int i = 0; i < KN; i++) {
+          if (c3.valid) load_kv(c3, i);
+          c3.advance(total, npair, nq, BH, a.H, stride);
+        }
+      }
+      for (int g = 0; c0.valid; g++) {
+        // both tiles have consumed S(g): K slot g % KN is free; they folded O_blk(g-1) before storing P(g): V slot
+        // (g-1) % VN is free.  Block g + KN goes into both.
+        wait(&bar_p[0], g & 1, 70);
+        wait(&bar_p[1], g & 1, 71);
+        if (c3.valid) load_kv(c3, g + KN);
+        if (c0.j == c0.nkb - 1) {
+          // this item's last scores have been consumed: its Q buffer takes the item after next
+          Fwd2Step nx;
+          nx.set_item(c0.w + 2 * stride, c0.li + 2, total, npair, nq, BH, a.H);
+          if (nx.valid) load_q(nx);
+        }
+        c0.advance(total, npair, nq, BH, a.H, stride);
+        c3.advance(total, npair, nq, BH, a.H, stride);
+      }
+    }
+  } else if (warp == 8) {
+    // ---------------------------------------------------------------- MMA warp: waits, tcgen05.mma, commits, nothing else
+    // (the MMAs here are short, 50-65 cycles each: every instruction this thread spends between two of them shows)
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);     // A = P (TMEM, K-major), B = V (MN-major)
+      const uint64_t dq0 = desc_base_k(tc::smem_u32(smem + S::Q)), dk0 = desc_base_k(tc::smem_u32(smem + S::K));
+      const uint64_t dv0 = desc_base_mn(tc::smem_u32(smem + S::V));
+      constexpr uint64_t TILE_D = TILE_BYTES >> 4;     // one tile further, in descriptor address units
+      int li = 0, j = 0, w = blockIdx.x;
+      auto item_nkb = [&](int w_) { return min(2 * (npair - 1 - w_ / BH) + 2, nq); };
+      int nkb = w < total ? item_nkb(w) : 0;
+      bool valid = w < total;
+      if (valid) {
+        const bool ok0 = wait(&bar_q[0], 0, 60) && wait(&bar_k[0], 0, 61);
+        for (int t = 0; t < 2; t++) {
+          if (ok0) {
+            tc::tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) tc::mma_bf16_ss(tmem + t * 128, dq0 + t * TILE_D + ks * 2, dk0 + ks * 2, idesc_s, ks > 0);
+          }
+          tc::mma_commit(&bar_s[t]);
+        }
+      }
+      for (int g = 0; valid; g++) {
+        // next step: same item, or the first block of this CTA's next item
+        int nli = li, nj = j + 1, nw = w;
+        if (nj >= nkb) { nli = li + 1; nj = 0; nw = w + stride; }
+        const bool has_next = nw < total;
+        bool next_ok = has_next;
+        if (has_next) {
+          next_ok = wait(&bar_k[(g + 1) % KN], ((g + 1) / KN) & 1, 62);
+          if (next_ok && nj == 0) next_ok = wait(&bar_q[nli & 1], (nli >> 1) & 1, 63);
+        }
+        const bool v_ok = wait(&bar_v[g % VN], (g / VN) & 1, 64);
+        const uint64_t dqn = dq0 + (uint64_t)((nli & 1) * 2) * TILE_D, dkn = dk0 + (uint64_t)((g + 1) % KN) * TILE_D;
+        const uint64_t dvg = dv0 + (uint64_t)(g % VN) * TILE_D;
+        for (int t = 0; t < 2; t++) {
+          bool go = wait(&bar_p[t], g & 1, 65);        // P_t(g) is in TMEM and S_t(g) has been read out
+          if (has_next) {                              // the next scores first: the tile's threads wait for nothing else
+            if (go && next_ok) {
+              tc::tc_fence_after();
+#pragma unroll
+              for (int ks = 0; ks < 4; ks++) tc::mma_bf16_ss(tmem + t * 128, dqn + t * TILE_D + ks * 2, dkn + ks * 2, idesc_s, ks > 0);
+            }
+            tc::mma_commit(&bar_s[t]);
+          }
+          if (go && g > 0) go = wait(&bar_of[t], (g - 1) & 1, 66);   // O_blk_t(g-1) has been folded
+          if (go && v_ok) {
+            tc::tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(tmem + 384 + t * HD, tmem + 256 + t * 64 + ks * 8, dvg + ks * 128, idesc_o, ks > 0);
+          }
+          tc::mma_commit(&bar_o[t]);
+        }
+        if (nj == 0 && has_next) nkb = item_nkb(nw);
+        li = nli; j = nj; w = nw; valid = has_next;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax warps: tile t = warp >> 2
+    const int t = warp >> 2, lg = warp & 3, row = lg * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
+    const uint32_t t_s = tmem + t * 128 + lane_addr, t_p = tmem + 256 + t * 64 + lane_addr, t_o = tmem + 384 + t * HD + lane_addr;
+    const float sl2 = a.scale * LOG2E;
+    const uint64_t sl2x2 = pk2(sl2, sl2);
+    int g = 0;
+    long long* tl = (a.timeline && blockIdx.x == 0 && tid == 0) ? a.timeline : nullptr;   // first 16 blocks of CTA 0, warp 0
+    Fwd2Step it;
+    it.set_item(blockIdx.x, 0, total, npair, nq, BH, a.H);
+    for (; it.valid; it.set_item(it.w + stride, it.li + 1, total, npair, nq, BH, a.H)) {
+      const int qt = 2 * it.p + t, qrow = qt * 128 + row;
+      float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
+      float o[HD];
+#pragma unroll
+      for (int i = 0; i < HD; i++) o[i] = 0.f;
+      auto fold = [&](float alpha) {   // O = O * alpha + (P V) of the previous block
+        uint32_t r0[32], r1[32];
+        tc::tmem_ld32(t_o, r0);
+        tc::tmem_ld32(t_o + 32, r1);
+        tc::tmem_ld_wait();
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&bar_of[t]);
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          o[i] = o[i] * alpha + __uint_as_float(r0[i]);
+          o[32 + i] = o[32 + i] * alpha + __uint_as_float(r1[i]);
+        }
+      };
+      for (int j = 0; j < it.nkb; j++, g++) {
+        if (tl && g < 16) tl[g * 8 + 0] = clock64();
+        wait(&bar_s[t], g & 1, 67);
+        tc::tc_fence_after();
+        if (tl && g < 16) tl[g * 8 + 1] = clock64();
+        float alpha = 1.f;
+        const bool masked = j > qt;      // past the diagonal: every key of this block is masked for every row of the tile
+        const bool diag = (j == qt);
+        const int kc0 = j * 128;
+        float m_new = m;
+        if (!masked) {
+          // pass 1: row maximum
+          float mx = -INFINITY;
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            uint32_t r[32];
+            tc::tmem_ld32(t_s + c * 32, r);
+            tc::tmem_ld_wait();
+            if (diag) {
+#pragma unroll
+              for (int i = 0; i < 32; i++)
+                if (kc0 + c * 32 + i > qrow) r[i] = 0xff800000u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+          }
+          m_new = fmaxf(m, mx * sl2);               // finite: key 0 is visible to every query
+          alpha = ex2_approx(m - m_new);            // exp2(-inf) = 0 on the first block
+        }
+        if (tl && g < 16) tl[g * 8 + 2] = clock64();
+        if (j > 0) {   // the previous block's P V has had the whole row-maximum pass to complete; P's columns are free after it
+          wait(&bar_o[t], (g - 1) & 1, 68);
+          tc::tc_fence_after();
+          if (tl && g < 16) tl[g * 8 + 5] = clock64();
+          fold(alpha_prev);
+          if (tl && g < 16) tl[g * 8 + 6] = clock64();
+        }
+        if (masked) {
+          uint32_t z[16];
+#pragma unroll
+          for (int i = 0; i < 16; i++) z[i] = 0u;
+#pragma unroll
+          for (int c = 0; c < 4; c++) tc::tmem_st16(t_p + c * 16, z);
+        } else {
+          const uint64_t nm2 = pk2(-m_new, -m_new);
+          uint64_t rs2 = pk2(0.f, 0.f);
+          // pass 2: exponentials, row sum, P as bf16 pairs into its own TMEM columns
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            uint32_t r[32], pw[16];
+            tc::tmem_ld32(t_s + c * 32, r);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int x = 0; x < 16; x++) {
+              float z0, z1;
+              upk2(fma2(pk2(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1])), sl2x2, nm2), z0, z1);
+              float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
+              if (diag) {
+                if (kc0 + c * 32 + 2 * x > qrow) p0 = 0.f;
+                if (kc0 + c * 32 + 2 * x + 1 > qrow) p1 = 0.f;
+              }
+              rs2 = add2(rs2, pk2(p0, p1));
+              pw[x] = pack_bf16(p0, p1);
+            }
+            tc::tmem_st16(t_p + c * 16, pw);
+          }
+          float rs_lo, rs_hi;
+          upk2(rs2, rs_lo, rs_hi);
+          l = l * alpha + (rs_lo + rs_hi);
+          m = m_new;
+        }
+        if (tl && g < 16) tl[g * 8 + 3] = clock64();
+        tc::tmem_st_wait();
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&bar_p[t]);
+        if (tl && g < 16) tl[g * 8 + 4] = clock64();
+        alpha_prev = alpha;
+      }
+      wait(&bar_o[t], (g - 1) & 1, 69);
+      tc::tc_fence_after();
+      fold(alpha_prev);
+      if (!*s_abort && qrow < a.T) {
+        const float inv = 1.f / l;
+        bf16* dst = a.out + ((size_t)(it.b * a.T + qrow)) * C + it.h * HD;
+#pragma unroll
+        for (int v8 = 0; v8 < HD / 8; v8++) {
+          uint4 pk;
+          pk.x = pack_bf16(o[v8 * 8 + 0] * inv, o[v8 * 8 + 1] * inv); pk.y = pack_bf16(o[v8 * 8 + 2] * inv, o[v8 * 8 + 3] * inv);
+          pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
+        }
+        a.lse[((size_t)it.b * a.H + it.h) * a.T + qrow] = (m + log2f(l)) * LN2;
+      }
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tc::tmem_dealloc(tmem, TMEM_COLS);
+}
+
 // ================================================================== backward: delta = rowsum(dO * O)
 __global__ void attn_delta_k(float* __restrict__ delta, const bf16* __restrict__ dout, const bf16* __restrict__ out, int B, int T,
                              int H, int hd) {
@@ -695,7 +1029,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kv_tc_kernel(const __
 //     partial buffer, written with plain stores right after block j+1's operands are handed over, and a second
 //     kernel adds the partials of a query row in fp32 in key-tile order (deterministic), applies the scale and RoPE's
 //     backward rotation and writes bf16 dQ.
-// Warps: 8 element-wise (TMEM lane group x 64-query half), 4 drain (dQ partial tiles, dK / dV epilogue), 1 control.
+// Warps: 8 element-wise (TMEM lane group x 64-query half), 4 drain (dQ partial tiles, dK / dV epilogue), 1 MMA issuer, 1 loader.
 // mbarriers: bar_s scores complete (commit) | bar_free S^T/dP^T read out (8 warps) | bar_p P^T/dS^T stored (8 warps) |
 // bar_d dV/dK/dQ MMAs complete (commit) | bar_dqf dQ read out (4 warps) | bar_epi dK/dV of a key tile read out (4 warps).
 struct BwdFusedSmem {
@@ -711,14 +1045,9 @@ struct BwdFusedSmem {
 
 constexpr int BWDF_E_WARPS = 8;       // element-wise warps: TMEM lane group (w & 3) x 64-query column half (w >> 2)
 constexpr int BWDF_D_WARPS = 4;       // drain warps: dQ partial tiles and the dK / dV epilogue, one TMEM lane group each
-constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS;
-constexpr int BWDF_THREADS = (BWDF_CTRL_WARP + 1) * 32;
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
+constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS;   // issues every MMA
+constexpr int BWDF_LOAD_WARP = BWDF_CTRL_WARP + 1;            // issues every TMA load
+constexpr int BWDF_THREADS = (BWDF_LOAD_WARP + 1) * 32;
 
 __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
                                                                             const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
@@ -772,13 +1101,9 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
   };
   long long* tl = (a.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) ? a.timeline : nullptr;
 
-  if (warp == BWDF_CTRL_WARP) {
-    // ---------------------------------------------------------------- control warp: every TMA load and every MMA
+  if (warp == BWDF_LOAD_WARP) {
+    // ---------------------------------------------------------------- loader warp: every TMA load
     if (lane == 0) {
-      constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T in TMEM / dS^T), B MN-major (dO / Q)
-      constexpr uint32_t idesc_q = tc::idesc_bf16(128, HD, 1, 1);    // A MN-major (dS^T read as dS), B MN-major (K)
-      const uint32_t sK = tc::smem_u32(smem + S::K), sV = tc::smem_u32(smem + S::V), sDST = tc::smem_u32(smem + S::DST);
       auto load_kv = [&](int kt) {
         tc::mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
         tc::tma_load_2d(smem + S::K, &tm_qkv, bar_kv, C + h * HD, row0 + kt * 128);
@@ -790,16 +1115,6 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
         tc::tma_load_2d(smem + S::Q + buf * TILE_BYTES, &tm_qkv, &bar_q[buf], h * HD, row0 + i * 128);
         tc::tma_load_2d(smem + S::DO + buf * TILE_BYTES, &tm_do, &bar_q[buf], h * HD, row0 + i * 128);
       };
-      auto issue_scores = [&](int g) {
-        const int buf = g % 3;
-        if (!wait(&bar_q[buf], (g / 3) & 1, 41)) return;
-        tc::tc_fence_after();
-        const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, desc_k(sK, ks), desc_k(sQ, ks), idesc_s, ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, desc_k(sV, ks), desc_k(sDO, ks), idesc_s, ks > 0);
-      };
       int blk = 0;
       load_kv(kt_first);
       load_q_do(kt_first, 0);
@@ -807,41 +1122,11 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
       for (int item = 0; item < n_items; item++) {
         const int kt = item == 0 ? kt_first : kt_second;
         const int n_it = nq - kt;
-        if (wait(bar_kv, item & 1, 40)) issue_scores(blk);
-        tc::mma_commit(bar_s);
         for (int it = 0; it < n_it; it++, blk++) {
-          const int buf = blk % 3;
-          // S^T / dP^T of this block are in registers: the score MMAs of the next block may overwrite them
-          wait(bar_free, blk & 1, 42);
-          if (it + 1 < n_it) {
-            tc::tc_fence_after();
-            issue_scores(blk + 1);
-            tc::mma_commit(bar_s);
-          }
           // the tiles of block it+2 go where block it-1's were: its dV / dK MMAs must have finished reading them
-          if (it + 2 < n_it) {
-            if (blk > 0) wait(bar_d, (blk - 1) & 1, 43);
-            load_q_do(kt + it + 2, blk + 2);
-          }
-          bool go = wait(bar_p, blk & 1, 45);     // P^T in TMEM, dS^T in shared memory
-          if (tl) tl[blk * 8 + 5] = clock64();
-          if (it == 0 && item > 0) go = wait(bar_epi, (item - 1) & 1, 46) && go;   // previous tile's dK / dV have been read out
-          if (go) {
-            tc::tc_fence_after();
-            const uint32_t sQ = tc::smem_u32(smem + S::Q + buf * TILE_BYTES), sDO = tc::smem_u32(smem + S::DO + buf * TILE_BYTES);
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(t_dv, t_pt + ks * 8, desc_mn(sDO, ks), idesc_d, (it > 0 || ks > 0));
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, desc_k(sDST, ks), desc_mn(sQ, ks), idesc_d, (it > 0 || ks > 0));
-            if (blk > 0) go = wait(bar_dqf, (blk - 1) & 1, 47);   // the previous dQ tile has left TMEM
-            if (go) {
-              tc::tc_fence_after();
-#pragma unroll
-              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, desc_mn(sDST, ks), desc_mn(sK, ks), idesc_q, ks > 0);
-            }
-          }
-          tc::mma_commit(bar_d);
-          if (tl) tl[blk * 8 + 6] = clock64();
+          // (every completion of bar_d is observed, so this thread's parity never falls a whole period behind)
+          if (blk > 0) wait(bar_d, (blk - 1) & 1, 43);
+          if (it + 2 < n_it) load_q_do(kt + it + 2, blk + 2);
         }
         if (item + 1 < n_items) {
           // every MMA of this key tile is complete: K, V and all Q / dO buffers are free for the mirror tile
@@ -849,6 +1134,69 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
           load_kv(kt_second);
           load_q_do(kt_second, blk);
           if (nq - kt_second > 1) load_q_do(kt_second + 1, blk + 1);
+        }
+      }
+    }
+  } else if (warp == BWDF_CTRL_WARP) {
+    // ---------------------------------------------------------------- MMA warp: waits, tcgen05.mma, commits, nothing else
+    // (these MMAs take 50-65 cycles each: every instruction this thread spends between two of them shows, so the
+    // descriptors are formed by adding small constants to per-buffer bases)
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T in TMEM / dS^T), B MN-major (dO / Q)
+      constexpr uint32_t idesc_q = tc::idesc_bf16(128, HD, 1, 1);    // A MN-major (dS^T read as dS), B MN-major (K)
+      constexpr uint64_t TILE_D = TILE_BYTES >> 4;
+      const uint64_t dKk = desc_base_k(tc::smem_u32(smem + S::K)), dVk = desc_base_k(tc::smem_u32(smem + S::V));
+      const uint64_t dQk = desc_base_k(tc::smem_u32(smem + S::Q)), dDOk = desc_base_k(tc::smem_u32(smem + S::DO));
+      const uint64_t dQmn = desc_base_mn(tc::smem_u32(smem + S::Q)), dDOmn = desc_base_mn(tc::smem_u32(smem + S::DO));
+      const uint64_t dKmn = desc_base_mn(tc::smem_u32(smem + S::K));
+      const uint64_t dSTk = desc_base_k(tc::smem_u32(smem + S::DST)), dSTmn = desc_base_mn(tc::smem_u32(smem + S::DST));
+      auto issue_scores = [&](int buf, uint32_t q_phase) {
+        if (!wait(&bar_q[buf], q_phase, 41)) return;
+        tc::tc_fence_after();
+        const uint64_t o = (uint64_t)buf * TILE_D;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_st, dKk + ks * 2, dQk + o + ks * 2, idesc_s, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, dVk + ks * 2, dDOk + o + ks * 2, idesc_s, ks > 0);
+      };
+      int blk = 0, buf = 0, q_use = 0;     // buffer blk % 3 and how many times it has been filled before (blk / 3)
+      for (int item = 0; item < n_items; item++) {
+        const int kt = item == 0 ? kt_first : kt_second;
+        const int n_it = nq - kt;
+        if (wait(bar_kv, item & 1, 40)) issue_scores(buf, q_use & 1);
+        tc::mma_commit(bar_s);
+        for (int it = 0; it < n_it; it++, blk++) {
+          int nbuf = buf + 1, nq_use = q_use;
+          if (nbuf == 3) { nbuf = 0; nq_use++; }
+          // S^T / dP^T of this block are in registers: the score MMAs of the next block may overwrite them
+          wait(bar_free, blk & 1, 42);
+          if (it + 1 < n_it) {
+            tc::tc_fence_after();
+            issue_scores(nbuf, nq_use & 1);
+            tc::mma_commit(bar_s);
+          }
+          bool go = wait(bar_p, blk & 1, 45);     // P^T in TMEM, dS^T in shared memory
+          if (tl) tl[blk * 8 + 5] = clock64();
+          if (it == 0 && item > 0) go = wait(bar_epi, (item - 1) & 1, 46) && go;   // previous tile's dK / dV have been read out
+          if (go) {
+            tc::tc_fence_after();
+            const uint64_t o = (uint64_t)buf * TILE_D;
+            const uint32_t acc = it > 0;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(t_dv, t_pt + ks * 8, dDOmn + o + ks * 128, idesc_d, acc | (ks > 0));
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, dSTk + (ks >> 2) * TILE_D + (ks & 3) * 2, dQmn + o + ks * 128, idesc_d, acc | (ks > 0));
+            if (blk > 0) go = wait(bar_dqf, (blk - 1) & 1, 47);   // the previous dQ tile has left TMEM
+            if (go) {
+              tc::tc_fence_after();
+#pragma unroll
+              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, dSTmn + ks * 128, dKmn + ks * 128, idesc_q, ks > 0);
+            }
+          }
+          tc::mma_commit(bar_d);
+          if (tl) tl[blk * 8 + 6] = clock64();
+          buf = nbuf; q_use = nq_use;
         }
       }
     }
@@ -951,7 +1299,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
         if (tl && warp == 0) tl[blk * 8 + 4] = clock64();
       }
     }
-  } else {
+  } else if (warp < BWDF_CTRL_WARP) {
     // ---------------------------------------------------------------- 4 drain warps
     // dQ partial of (query block i, this key tile): TMEM -> bf16 -> its own tile of the partial buffer (a full 128-byte
     // row per thread; no atomics, the finishing kernel adds the key tiles' partials in a fixed order); after the last
@@ -1310,6 +1658,7 @@ __global__ void attn_bwd_kv_simt_k(bf16* __restrict__ dqkv, const bf16* __restri
 }
 
 int g_attn_force_simt = 0;
+int g_fwd_rows = 1;   // head size 64: 1 = thread-per-row forward over tile pairs, 0 = four-threads-per-row forward
 
 template <typename K>
 int set_smem(K kern, int bytes) {
@@ -1325,6 +1674,7 @@ bool tc_ok(const void* qkv, const void* other, int H, int hd) {
 
 static long long* g_timeline = nullptr;
 MLB_API void mlb_attn_force_simt(int on) { g_attn_force_simt = on; }
+MLB_API void mlb_attn_fwd_mode(int rows) { g_fwd_rows = rows; }
 // Diagnostic: device buffer of at least 8 * (query blocks per CTA) int64 that CTA (0,0,0) of the fused backward fills
 // with SM cycle stamps, eight per block: element-wise warp 0 before / after the score wait, after its exponentials,
 // after the previous block's MMAs completed, after P^T / dS^T are stored; control thread when it saw P^T and when the
@@ -1338,14 +1688,19 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
   if (tc_ok(qkv, out, H, hd)) {
     const CUtensorMap* tm = mlb_tmap_cached(qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, 64);
     if (!tm) return -2;
-    AttnArgs a{B, T, H, hd, scale, (bf16*)out, lse, nullptr, nullptr, nullptr};
+    AttnArgs a{B, T, H, hd, scale, (bf16*)out, lse, nullptr, nullptr, nullptr, nullptr, g_fwd_rows, g_timeline};
     const long items = (long)((T + 127) / 128) * H * B;
     int sms = 0, devid = 0;
     cudaGetDevice(&devid);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devid);
     if (sms <= 0) sms = 148;
     dim3 grid((unsigned)(items < sms ? items : sms));   // persistent: one CTA per SM walks its share of the tiles
-    if (hd == 64) {
+    if (hd == 64 && g_fwd_rows) {
+      static int once = set_smem(attn_fwd_rows_tc_kernel, Fwd2Smem::TOTAL);
+      (void)once;
+      const long pairs = (long)(((T + 127) / 128 + 1) / 2) * H * B;
+      attn_fwd_rows_tc_kernel<<<(unsigned)(pairs < sms ? pairs : sms), FWD2_THREADS, Fwd2Smem::TOTAL, st>>>(*tm, a);
+    } else if (hd == 64) {
       static int once = set_smem(attn_fwd_tc_kernel<64>, FwdSmem<64>::TOTAL);
       (void)once;
       attn_fwd_tc_kernel<64><<<grid, ATT_THREADS, FwdSmem<64>::TOTAL, st>>>(*tm, a);
@@ -1388,7 +1743,7 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
     const CUtensorMap* tq = mlb_tmap_cached(qkv, (uint64_t)B * T, 3 * C, 3 * C, 128, 64);
     const CUtensorMap* td = mlb_tmap_cached(dout, (uint64_t)B * T, C, C, 128, 64);
     if (!tq || !td) return -2;
-    AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT, (bf16*)dq_part, g_timeline};
+    AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT, (bf16*)dq_part, 0, g_timeline};
     dim3 grid((T + 127) / 128, H, B);
     if (hd == 64 && dq_part != nullptr && ((uintptr_t)dq_part % 16 == 0)) {
       // single fused kernel + dQ finish

@@ -857,6 +857,64 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   return launch_tc_gather<128, false>(tmA, tmB, tmD, g, ga, st);
 }
 
+// ------------------------------------------------------------------ tensor-pipe micro-benchmark
+// One CTA per SM; one thread issues `reps` groups of four tcgen05.mma (M = 128, K = 16 each, N given) on resident
+// shared-memory (or TMEM, for A) operands and waits for their completion: cycles[blockIdx.x] = SM cycles for all of them.
+namespace {
+template <int N, bool A_TMEM>
+__global__ void __launch_bounds__(128, 1) mma_probe_kernel(long long* cycles, int reps) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bar = (uint64_t*)(smem + 16384 + 32768);
+  uint32_t* slot = (uint32_t*)(bar + 1);
+  for (int i = threadIdx.x; i < (16384 + 32768) / 16; i += 128) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) { tc::mbar_init(bar, 1); tc::mbar_fence_init(); }
+  if (threadIdx.x < 32) tc::tmem_alloc(slot, 512);
+  tc::fence_async_smem();
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem = *slot;
+  if (threadIdx.x == 0) {
+    constexpr uint32_t idesc = tc::idesc_bf16(128, N, 0, 0);
+    const uint32_t sA = tc::smem_u32(smem), sB = sA + 16384;
+    const long long t0 = clock64();
+    for (int r = 0; r < reps; r++) {
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const uint64_t db = tc::smem_desc_sw128(sB + k * 32, 16, 1024);
+        if (A_TMEM) tc::mma_bf16_ts(tmem, tmem + 256 + k * 8, db, idesc, 1u);
+        else tc::mma_bf16_ss(tmem, tc::smem_desc_sw128(sA + k * 32, 16, 1024), db, idesc, 1u);
+      }
+    }
+    tc::mma_commit(bar);
+    tc::mbar_wait(bar, 0, 0x70);
+    cycles[blockIdx.x] = clock64() - t0;
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) tc::tmem_dealloc(tmem, 512);
+}
+}  // namespace
+// N in {64, 128, 256}; a_tmem: A operand from TMEM instead of shared memory.  `cycles` holds one int64 per SM.
+MLB_API int mlb_mma_probe(long long* cycles, int N, int a_tmem, int reps, cudaStream_t st) {
+  const int smem = 16384 + 32768 + 64 + 1024;
+#define PROBE(NN, TS)                                                                                         \
+  {                                                                                                           \
+    cudaFuncSetAttribute(mma_probe_kernel<NN, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);        \
+    mma_probe_kernel<NN, TS><<<num_sms(), 128, smem, st>>>(cycles, reps);                                     \
+  }
+  if (N == 64 && !a_tmem) PROBE(64, false)
+  else if (N == 64) PROBE(64, true)
+  else if (N == 128 && !a_tmem) PROBE(128, false)
+  else if (N == 128) PROBE(128, true)
+  else if (N == 256 && !a_tmem) PROBE(256, false)
+  else if (N == 256) PROBE(256, true)
+  else return -1;
+#undef PROBE
+  return (int)cudaGetLastError();
+}
+
 MLB_API void mlb_gemm_force_simt(int on) { g_force_simt = on; }
 MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
 MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }

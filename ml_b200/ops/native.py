@@ -38,6 +38,7 @@ def lib():
         "mlb_gemm_epilogue_mode": [_i32],
         "mlb_gemm_streamk": [_i32],
         "mlb_attn_force_simt": [_i32],
+        "mlb_attn_fwd_mode": [_i32],
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
         "mlb_attn_bwd_scratch_bytes": [_i32, _i32, _i32, _i32],

@@ -159,6 +159,26 @@ def bwd_mode(request):
     nat().FUSED_ATTN_BWD = old
 
 
+@pytest.mark.parametrize("B,T,H,hd", [c for c in ATTN_CASES if c[3] == 64] + [(3, 640, 2, 64), (1, 1100, 1, 64)])
+@pytest.mark.parametrize("rows", [1, 0], ids=["thread_per_row", "four_threads_per_row"])
+def test_attn_fwd_variants_hd64(B, T, H, hd, rows):
+    """Head size 64 has two forward kernels: thread-per-row over tile pairs (P kept in TMEM) and four threads per row."""
+    torch.manual_seed(15)
+    C = H * hd
+    qkv = rnd(B * T, 3 * C, scale=1.0)
+    out = torch.empty(B * T, C, device=dev(), dtype=torch.bfloat16)
+    lse = torch.empty(B, H, T, device=dev())
+    nat().lib().mlb_attn_fwd_mode(rows)
+    try:
+        nat().attn_fwd(out, lse, qkv, B, T, H, hd)
+    finally:
+        nat().lib().mlb_attn_fwd_mode(1)
+    eo, el = torch.empty(B * T, C, device=dev()), torch.empty(B, H, T, device=dev())
+    ref.attn_fwd(eo, el, qkv, B, T, H, hd)
+    close(out, eo, name="attn out")
+    close(lse, el, rtol=1e-3, atol=2e-2, name="attn lse")
+
+
 @pytest.mark.parametrize("B,T,H,hd", ATTN_CASES)
 def test_attn_fwd_bwd(B, T, H, hd, bwd_mode):
     if hd != 64 and not bwd_mode:
