@@ -477,6 +477,7 @@ struct Fwd2Step {   // one key block of one item in this CTA's flattened sequenc
 };
 
 __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
+  mlb_pdl_sync();
   using S = Fwd2Smem;
   constexpr int HD = 64;
   constexpr uint32_t TMEM_COLS = 512;
@@ -759,6 +760,7 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
 // ================================================================== backward: delta = rowsum(dO * O)
 __global__ void attn_delta_k(float* __restrict__ delta, const bf16* __restrict__ dout, const bf16* __restrict__ out, int B, int T,
                              int H, int hd) {
+  mlb_pdl_sync();
   // one group of hd/8 consecutive lanes per (row, head): 16-byte loads, shuffle reduction inside the group
   const int gsz = hd >> 3;  // lanes per head (8 for hd=64, 16 for hd=128); a power of two <= 32 on this path
   const long gidx = ((long)blockIdx.x * blockDim.x + threadIdx.x) / gsz;
@@ -1051,6 +1053,7 @@ constexpr int BWDF_THREADS = (BWDF_LOAD_WARP + 1) * 32;
 
 __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
                                                                             const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
+  mlb_pdl_sync();
   using S = BwdFusedSmem;
   constexpr int HD = 64;
   constexpr uint32_t TMEM_COLS = 512;
@@ -1363,6 +1366,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
 __global__ void __launch_bounds__(256) attn_dq_finish_k(bf16* __restrict__ dqkv, const bf16* __restrict__ part, long rows, int T, int H,
                                                         int hd, float scale, const float* __restrict__ cosT,
                                                         const float* __restrict__ sinT) {
+  mlb_pdl_sync();
   const int h2 = hd >> 1, gph = h2 >> 4, gpr = H * gph;   // groups of 16 pairs per head / per row
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * gpr) return;
@@ -1699,7 +1703,7 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
       static int once = set_smem(attn_fwd_rows_tc_kernel, Fwd2Smem::TOTAL);
       (void)once;
       const long pairs = (long)(((T + 127) / 128 + 1) / 2) * H * B;
-      attn_fwd_rows_tc_kernel<<<(unsigned)(pairs < sms ? pairs : sms), FWD2_THREADS, Fwd2Smem::TOTAL, st>>>(*tm, a);
+      mlb_launch(attn_fwd_rows_tc_kernel, dim3((unsigned)(pairs < sms ? pairs : sms)), dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
     } else if (hd == 64) {
       static int once = set_smem(attn_fwd_tc_kernel<64>, FwdSmem<64>::TOTAL);
       (void)once;
@@ -1736,7 +1740,7 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
     const long heads = (long)B * T * H;
     const int gsz = hd / 8;
     const bool vec = (hd % 8 == 0) && gsz <= 32 && (gsz & (gsz - 1)) == 0 && ((uintptr_t)dout % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec) attn_delta_k<<<(unsigned)((heads * gsz + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
+    if (vec) mlb_launch(attn_delta_k, dim3((unsigned)((heads * gsz + 255) / 256)), dim3(256), 0, st, delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
     else attn_delta_scalar_k<<<(unsigned)((heads * 32 + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
   }
   if (tc_ok(qkv, dout, H, hd) && ((uintptr_t)dqkv % 16 == 0)) {
@@ -1750,9 +1754,9 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
       static int o0 = set_smem(attn_bwd_fused_tc_kernel, BwdFusedSmem::TOTAL);
       (void)o0;
       dim3 grid_f(((T + 127) / 128 + 1) / 2, H, B);   // a CTA handles a key tile and its mirror
-      attn_bwd_fused_tc_kernel<<<grid_f, BWDF_THREADS, BwdFusedSmem::TOTAL, st>>>(*tq, *td, a);
+      mlb_launch(attn_bwd_fused_tc_kernel, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, a);
       const long groups = (long)B * T * H * (hd / 32);
-      attn_dq_finish_k<<<(unsigned)((groups + 255) / 256), 256, 0, st>>>((bf16*)dqkv, (const bf16*)dq_part, (long)B * T, T, H, hd, scale, cosT, sinT);
+      mlb_launch(attn_dq_finish_k, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, st, (bf16*)dqkv, (const bf16*)dq_part, (long)B * T, T, H, hd, scale, cosT, sinT);
       cudaError_t e = cudaGetLastError();
       if (e != cudaSuccess) return (int)e + 1000;
       return cosT ? 1 : 0;

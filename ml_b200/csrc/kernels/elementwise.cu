@@ -27,6 +27,7 @@ __device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
 
 // ------------------------------------------------------------------ embedding
 __global__ void embed_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ wte, const int* __restrict__ ids, int C) {
+  mlb_pdl_sync();
   const long row = blockIdx.x;
   const bf16* src = wte + (long)ids[row] * C;
   bf16* dst = out + row * C;
@@ -39,6 +40,7 @@ __global__ void embed_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ wte
 }
 __global__ void embed_bwd_k(float* __restrict__ dwte, const bf16* __restrict__ dout, const int* __restrict__ ids, int C,
                             int T, int n_pre) {
+  mlb_pdl_sync();
   const long row = blockIdx.x;
   if ((int)(row % T) < n_pre) return;
   float* dst = dwte + (long)ids[row] * C;
@@ -46,6 +48,7 @@ __global__ void embed_bwd_k(float* __restrict__ dwte, const bf16* __restrict__ d
   for (int i = threadIdx.x; i < C; i += blockDim.x) atomicAdd(dst + i, __bfloat162float(src[i]));
 }
 __global__ void set_prefix_k(bf16* __restrict__ x, const bf16* __restrict__ prefix, int B, int T, int n_pre, int C) {
+  mlb_pdl_sync();
   long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   long n = (long)B * n_pre * C;
   if (i >= n) return;
@@ -55,6 +58,7 @@ __global__ void set_prefix_k(bf16* __restrict__ x, const bf16* __restrict__ pref
   x[((long)b * T + p) * C + c] = prefix[i];
 }
 __global__ void gather_prefix_k(bf16* __restrict__ dprefix, const bf16* __restrict__ dresid, int B, int T, int n_pre, int C) {
+  mlb_pdl_sync();
   long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   long n = (long)B * n_pre * C;
   if (i >= n) return;
@@ -70,6 +74,7 @@ template <bool ADD>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, float* __restrict__ rstd, bf16* __restrict__ resid,
                                                      const bf16* __restrict__ a, const bf16* __restrict__ b,
                                                      const bf16* __restrict__ w, long rows, int C, float eps) {
+  mlb_pdl_sync();
   const int lane = threadIdx.x & 31;
   const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -136,6 +141,7 @@ __global__ void __launch_bounds__(256, (VPL <= 3) ? 2 : 1) rmsnorm_bwd_k(bf16* _
                                                      const bf16* __restrict__ x, const bf16* __restrict__ w,
                                                      const float* __restrict__ rstd, const bf16* __restrict__ add, long rows,
                                                      int C, float* __restrict__ partial, int* __restrict__ ticket) {
+  mlb_pdl_sync();
   extern __shared__ float sh[];  // C floats: block-level dw partial
   __shared__ int is_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -289,6 +295,7 @@ __global__ void __launch_bounds__(256, (VPL <= 3) ? 2 : 1) rmsnorm_bwd_k(bf16* _
 // pairs (i, i + hd/2); fwd: x0' = x0 c - x1 s, x1' = x1 c + x0 s; bwd uses -s.
 __global__ void rope_k(bf16* __restrict__ qkv, const float* __restrict__ cosT, const float* __restrict__ sinT, long rows, int T,
                        int H, int hd, float sign) {
+  mlb_pdl_sync();
   const int h2 = hd >> 1;
   const int per_row = 2 * H * (h2 >> 3);  // vectors of 8 pairs per row (q and k)
   long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -340,6 +347,7 @@ __global__ void rope_scalar_k(bf16* __restrict__ qkv, const float* __restrict__ 
 
 // ------------------------------------------------------------------ SwiGLU on gu[rows, 2I] = [gate | up]
 __global__ void swiglu_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ gu, long rows, int I) {
+  mlb_pdl_sync();
   const int vpr = I >> 3;
   long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * vpr) return;
@@ -353,6 +361,7 @@ __global__ void swiglu_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ gu
   store8(out + row * (long)I + v * 8, o);
 }
 __global__ void swiglu_bwd_k(bf16* __restrict__ dgu, const bf16* __restrict__ dout, const bf16* __restrict__ gu, long rows, int I) {
+  mlb_pdl_sync();
   const int vpr = I >> 3;
   long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= rows * vpr) return;
@@ -396,6 +405,7 @@ __global__ void swiglu_bwd_scalar_k(bf16* dgu, const bf16* dout, const bf16* gu,
 // Rows with tgt < 0: loss 0, gradient row zeroed.
 __global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, bf16* __restrict__ logits,
                                                     const int* __restrict__ tgt, int V, long ld, float dscale) {
+  mlb_pdl_sync();
   __shared__ float red[32];
   const long row = blockIdx.x;
   bf16* z = logits + row * ld;
@@ -456,6 +466,7 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, 
 __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, const float* __restrict__ grads,
                         float* __restrict__ m, float* __restrict__ v, long n, float lr, float b1, float b2, float eps, float wd,
                         float inv_bc1, float inv_bc2, float grad_scale, const float* __restrict__ dev_hyper) {
+  mlb_pdl_sync();
   // dev_hyper (optional, device memory): {lr, 1/bc1, 1/bc2, grad_scale} override the launch arguments, so a captured
   // CUDA graph can be replayed with the step-dependent bias corrections of the current step.
   if (dev_hyper) { lr = dev_hyper[0]; inv_bc1 = dev_hyper[1]; inv_bc2 = dev_hyper[2]; grad_scale = dev_hyper[3]; }
@@ -495,6 +506,7 @@ __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, c
 
 // ------------------------------------------------------------------ casts / utilities
 __global__ void cast_f2b_k(bf16* __restrict__ out, const float* __restrict__ in, long n, float scale) {
+  mlb_pdl_sync();
   long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i + 3 < n) {
     float4 f = *reinterpret_cast<const float4*>(in + i);
@@ -515,6 +527,7 @@ __global__ void scale_f32_k(float* __restrict__ x, long n, float scale) {
   if (i < n) x[i] *= scale;
 }
 __global__ void residual_add_k(bf16* __restrict__ out, const bf16* __restrict__ a, const bf16* __restrict__ b, long n) {
+  mlb_pdl_sync();
   long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i + 7 < n) {
     float x[8], y[8];
@@ -565,32 +578,32 @@ inline int gs(long n, int per_block) { return (int)((n + per_block - 1) / per_bl
 #define LAUNCH_RET return (int)cudaGetLastError()
 
 MLB_API int mlb_embed_fwd(void* out, const void* wte, const int* ids, long BT, int C, cudaStream_t st) {
-  embed_fwd_k<<<(unsigned)BT, 96, 0, st>>>((bf16*)out, (const bf16*)wte, ids, C);
+  mlb_launch(embed_fwd_k, dim3((unsigned)BT), dim3(96), 0, st, (bf16*)out, (const bf16*)wte, ids, C);
   LAUNCH_RET;
 }
 MLB_API int mlb_embed_bwd(float* dwte, const void* dout, const int* ids, long BT, int C, int T, int n_pre, cudaStream_t st) {
-  embed_bwd_k<<<(unsigned)BT, 256, 0, st>>>(dwte, (const bf16*)dout, ids, C, T, n_pre);
+  mlb_launch(embed_bwd_k, dim3((unsigned)BT), dim3(256), 0, st, dwte, (const bf16*)dout, ids, C, T, n_pre);
   LAUNCH_RET;
 }
 MLB_API int mlb_set_prefix(void* x, const void* prefix, int B, int T, int n_pre, int C, cudaStream_t st) {
   long n = (long)B * n_pre * C;
   if (n == 0) return 0;
-  set_prefix_k<<<gs(n, 256), 256, 0, st>>>((bf16*)x, (const bf16*)prefix, B, T, n_pre, C);
+  mlb_launch(set_prefix_k, dim3(gs(n, 256)), dim3(256), 0, st, (bf16*)x, (const bf16*)prefix, B, T, n_pre, C);
   LAUNCH_RET;
 }
 MLB_API int mlb_gather_prefix_grad(void* dprefix, const void* dresid, int B, int T, int n_pre, int C, cudaStream_t st) {
   long n = (long)B * n_pre * C;
   if (n == 0) return 0;
-  gather_prefix_k<<<gs(n, 256), 256, 0, st>>>((bf16*)dprefix, (const bf16*)dresid, B, T, n_pre, C);
+  mlb_launch(gather_prefix_k, dim3(gs(n, 256)), dim3(256), 0, st, (bf16*)dprefix, (const bf16*)dresid, B, T, n_pre, C);
   LAUNCH_RET;
 }
 MLB_API int mlb_rmsnorm_fwd(void* out, float* rstd, const void* x, const void* w, long rows, int C, float eps, cudaStream_t st) {
-  rmsnorm_fwd_k<false><<<gs(rows, 8), 256, 0, st>>>((bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w, rows, C, eps);
+  mlb_launch(rmsnorm_fwd_k<false>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w, rows, C, eps);
   LAUNCH_RET;
 }
 MLB_API int mlb_add_rmsnorm_fwd(void* resid, void* out, float* rstd, const void* a, const void* b, const void* w, long rows, int C,
                                 float eps, cudaStream_t st) {
-  rmsnorm_fwd_k<true><<<gs(rows, 8), 256, 0, st>>>((bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b, (const bf16*)w,
+  mlb_launch(rmsnorm_fwd_k<true>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b, (const bf16*)w,
                                                    rows, C, eps);
   LAUNCH_RET;
 }
@@ -606,7 +619,7 @@ MLB_API int mlb_rmsnorm_bwd(void* dx, float* dw, const void* dy, const void* x, 
   const int blocks = mlb_rmsnorm_bwd_blocks(rows);
   const size_t sh = (size_t)C * sizeof(float);
 #define RB(V)                                                                                                         \
-  rmsnorm_bwd_k<V><<<blocks, 256, sh, st>>>((bf16*)dx, dw, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,   \
+  mlb_launch(rmsnorm_bwd_k<V>, dim3(blocks), dim3(256), sh, st, (bf16*)dx, dw, (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,   \
                                             (const bf16*)add, rows, C, partial, ticket)
   if (sh > 48 * 1024) return -3;
   switch ((C % 256 == 0) ? C / 256 : 0) {
@@ -625,7 +638,7 @@ MLB_API int mlb_rope(void* qkv, const float* cosT, const float* sinT, long rows,
   const int h2 = hd / 2;
   if (h2 % 8 == 0 && (H * hd) % 8 == 0) {
     long n = rows * 2L * H * (h2 / 8);
-    rope_k<<<gs(n, 256), 256, 0, st>>>((bf16*)qkv, cosT, sinT, rows, T, H, hd, sign);
+    mlb_launch(rope_k, dim3(gs(n, 256)), dim3(256), 0, st, (bf16*)qkv, cosT, sinT, rows, T, H, hd, sign);
   } else {
     long n = rows * 2L * H * h2;
     rope_scalar_k<<<gs(n, 256), 256, 0, st>>>((bf16*)qkv, cosT, sinT, rows, T, H, hd, sign);
@@ -633,30 +646,30 @@ MLB_API int mlb_rope(void* qkv, const float* cosT, const float* sinT, long rows,
   LAUNCH_RET;
 }
 MLB_API int mlb_swiglu_fwd(void* out, const void* gu, long rows, int I, cudaStream_t st) {
-  if (I % 8 == 0) swiglu_fwd_k<<<gs(rows * (I / 8), 256), 256, 0, st>>>((bf16*)out, (const bf16*)gu, rows, I);
+  if (I % 8 == 0) mlb_launch(swiglu_fwd_k, dim3(gs(rows * (I / 8), 256)), dim3(256), 0, st, (bf16*)out, (const bf16*)gu, rows, I);
   else swiglu_fwd_scalar_k<<<gs(rows * I, 256), 256, 0, st>>>((bf16*)out, (const bf16*)gu, rows, I);
   LAUNCH_RET;
 }
 MLB_API int mlb_swiglu_bwd(void* dgu, const void* dout, const void* gu, long rows, int I, cudaStream_t st) {
-  if (I % 8 == 0) swiglu_bwd_k<<<gs(rows * (I / 8), 256), 256, 0, st>>>((bf16*)dgu, (const bf16*)dout, (const bf16*)gu, rows, I);
+  if (I % 8 == 0) mlb_launch(swiglu_bwd_k, dim3(gs(rows * (I / 8), 256)), dim3(256), 0, st, (bf16*)dgu, (const bf16*)dout, (const bf16*)gu, rows, I);
   else swiglu_bwd_scalar_k<<<gs(rows * I, 256), 256, 0, st>>>((bf16*)dgu, (const bf16*)dout, (const bf16*)gu, rows, I);
   LAUNCH_RET;
 }
 MLB_API int mlb_ce_fwd_bwd(float* losses, void* logits, const int* tgt, long rows, int V, long ld, float dscale, int threads,
                            cudaStream_t st) {
   if (threads != 128 && threads != 256 && threads != 512) threads = 512;
-  ce_fwd_bwd_k<<<(unsigned)rows, threads, 0, st>>>(losses, (bf16*)logits, tgt, V, ld, dscale);
+  mlb_launch(ce_fwd_bwd_k, dim3((unsigned)rows), dim3(threads), 0, st, losses, (bf16*)logits, tgt, V, ld, dscale);
   LAUNCH_RET;
 }
 MLB_API int mlb_adamw(float* master, void* params, const float* grads, float* m, float* v, long n, float lr, float b1, float b2,
                       float eps, float wd, float bc1, float bc2, float grad_scale, const float* dev_hyper, cudaStream_t st) {
   if (n == 0) return 0;
-  adamw_k<<<gs((n + 3) / 4, 256), 256, 0, st>>>(master, (bf16*)params, grads, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2,
+  mlb_launch(adamw_k, dim3(gs((n + 3) / 4, 256)), dim3(256), 0, st, master, (bf16*)params, grads, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2,
                                                 grad_scale, dev_hyper);
   LAUNCH_RET;
 }
 MLB_API int mlb_cast_f2b(void* out, const float* in, long n, float scale, cudaStream_t st) {
-  cast_f2b_k<<<gs((n + 3) / 4, 256), 256, 0, st>>>((bf16*)out, in, n, scale);
+  mlb_launch(cast_f2b_k, dim3(gs((n + 3) / 4, 256)), dim3(256), 0, st, (bf16*)out, in, n, scale);
   LAUNCH_RET;
 }
 MLB_API int mlb_cast_b2f(float* out, const void* in, long n, float scale, cudaStream_t st) {
@@ -668,7 +681,7 @@ MLB_API int mlb_scale_f32(float* x, long n, float scale, cudaStream_t st) {
   LAUNCH_RET;
 }
 MLB_API int mlb_residual_add(void* out, const void* a, const void* b, long n, cudaStream_t st) {
-  residual_add_k<<<gs((n + 7) / 8, 256), 256, 0, st>>>((bf16*)out, (const bf16*)a, (const bf16*)b, n);
+  mlb_launch(residual_add_k, dim3(gs((n + 7) / 8, 256)), dim3(256), 0, st, (bf16*)out, (const bf16*)a, (const bf16*)b, n);
   LAUNCH_RET;
 }
 MLB_API int mlb_patchify(void* out, const float* px, int B, int Cin, int Himg, int Wimg, int P, cudaStream_t st) {

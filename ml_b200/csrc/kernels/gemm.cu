@@ -148,6 +148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (!GATHER) mlb_pdl_sync();   // set-up done; operands written by the previous kernel are read from here on
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -376,6 +377,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   tc::cluster_sync();      // barriers of both CTAs initialised, TMEM of both allocated
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  mlb_pdl_sync();          // set-up done; operands written by the previous kernel are read from here on
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer (one per CTA)
@@ -679,8 +681,7 @@ int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap*
   int cap = g_max_ctas > 0 ? g_max_ctas : num_sms();
   int grid = total < cap ? total : cap;
   GatherArgs none{};
-  kern<<<grid, GEMM_THREADS, GemmSmem<BN>::TOTAL, st>>>(*tmA, *tmB, *tmD, g, none);
-  return (int)cudaGetLastError();
+  return (int)mlb_launch(kern, dim3(grid), dim3(GEMM_THREADS), GemmSmem<BN>::TOTAL, st, *tmA, *tmB, *tmD, g, none);
 }
 
 // CTA-pair kernel: one cluster of two CTAs per SM pair; the grid is sized from the number of clusters that can be
@@ -710,8 +711,7 @@ int launch_tc2(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap
   int cap = max_clusters;
   if (g_max_ctas > 0 && g_max_ctas / 2 < cap) cap = g_max_ctas / 2 > 0 ? g_max_ctas / 2 : 1;
   int clusters = total < cap ? total : cap;
-  kern<<<2 * clusters, GEMM2_THREADS, Gemm2Smem::TOTAL, st>>>(*tmA, *tmB, *tmD, g);
-  return (int)cudaGetLastError();
+  return (int)mlb_launch(kern, dim3(2 * clusters), dim3(GEMM2_THREADS), Gemm2Smem::TOTAL, st, *tmA, *tmB, *tmD, g);
 }
 int pair_clusters() { return (g_max_ctas > 0 ? g_max_ctas : num_sms()) / 2; }
 
