@@ -5,6 +5,7 @@
 // (train/gpt_kernels.cuh: encoder :225-243, rmsnorm :275-458, rope :645-713, swiglu :589-640, CE :1169-1210,
 // adamw :1357-1400) but none of the code is shared with them.
 #include "../common.cuh"
+#include <cuda_fp16.h>
 #include "../no_alloc.h"
 
 #include <cstdio>
@@ -462,6 +463,74 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, 
   }
 }
 
+// Same result with ONE exponential per logit (the two-pass kernel above spends 2 x rows x V of them and is limited by
+// the special-function unit, not by memory): the row is parked in shared memory.
+//   pass 1  global -> shared (raw bf16) + row maximum            (no exponential)
+//   pass 2  shared: e = exp(x - max) in fp32 -> row sum; e parked as fp16 (11-bit mantissa; the output is bf16)
+//   pass 3  shared -> global: e / sum * dscale - onehot
+// Needs V % 8 == 0, ld % 8 == 0 and V * 2 bytes of dynamic shared memory (two blocks per SM up to V ~ 56 k).
+__global__ void __launch_bounds__(512) ce_fwd_bwd_smem_k(float* __restrict__ losses, bf16* __restrict__ logits,
+                                                         const int* __restrict__ tgt, int V, long ld, float dscale) {
+  mlb_pdl_sync();
+  extern __shared__ uint4 ce_row[];      // V / 8 vectors of 8 x 16 bit
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  bf16* z = logits + row * ld;
+  const int t = tgt[row];
+  const int nv = V >> 3;
+  if (t < 0) {
+    if (threadIdx.x == 0) losses[row] = 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) reinterpret_cast<uint4*>(z)[i] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(z) + i);
+    ce_row[i] = v;
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) m = fmaxf(m, fmaxf(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u)));
+  }
+  const float M = block_max(m, red);       // contains a __syncthreads: the whole row is in shared memory after it
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 v = ce_row[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float e0 = __expf(__uint_as_float(w[j] << 16) - M), e1 = __expf(__uint_as_float(w[j] & 0xffff0000u) - M);
+      s += e0 + e1;
+      const __half2 h = __floats2half2_rn(e0, e1);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    ce_row[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  const float S = block_sum(s, red);
+  const float zt = __bfloat162float(z[t]);   // global memory still holds the logits
+  if (threadIdx.x == 0) losses[row] = __logf(S) + M - zt;
+  __syncthreads();                            // z[t] has been read by everyone before it is overwritten
+  const float inv = dscale / S;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const uint4 v = ce_row[i];
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+      x[2 * j] = f.x * inv;
+      x[2 * j + 1] = f.y * inv;
+    }
+    const int d = t - i * 8;
+    if (d >= 0 && d < 8) {
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (j == d) x[j] -= dscale;
+    }
+    store8(z + i * 8, x);
+  }
+}
+
 // ------------------------------------------------------------------ AdamW (fp32 master/m/v, bf16 copy written in the same pass)
 __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, const float* __restrict__ grads,
                         float* __restrict__ m, float* __restrict__ v, long n, float lr, float b1, float b2, float eps, float wd,
@@ -576,6 +645,8 @@ inline int gs(long n, int per_block) { return (int)((n + per_block - 1) / per_bl
 }  // namespace
 
 #define LAUNCH_RET return (int)cudaGetLastError()
+static int g_ce_smem = 1;     // tuning hook: 0 = always the two-pass cross-entropy kernel
+MLB_API void mlb_ce_mode(int smem_row) { g_ce_smem = smem_row; }
 
 MLB_API int mlb_embed_fwd(void* out, const void* wte, const int* ids, long BT, int C, cudaStream_t st) {
   mlb_launch(embed_fwd_k, dim3((unsigned)BT), dim3(96), 0, st, (bf16*)out, (const bf16*)wte, ids, C);
@@ -658,6 +729,16 @@ MLB_API int mlb_swiglu_bwd(void* dgu, const void* dout, const void* gu, long row
 MLB_API int mlb_ce_fwd_bwd(float* losses, void* logits, const int* tgt, long rows, int V, long ld, float dscale, int threads,
                            cudaStream_t st) {
   if (threads != 128 && threads != 256 && threads != 512) threads = 512;
+  const size_t sh = (size_t)V * 2;
+  if (g_ce_smem && (V % 8 == 0) && (ld % 8 == 0) && ((uintptr_t)logits % 16 == 0) && sh <= 112 * 1024) {
+    static bool attr_done = false;
+    if (!attr_done) {
+      if (cudaFuncSetAttribute(ce_fwd_bwd_smem_k, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess) return -5;
+      attr_done = true;
+    }
+    mlb_launch(ce_fwd_bwd_smem_k, dim3((unsigned)rows), dim3(512), sh, st, losses, (bf16*)logits, tgt, V, ld, dscale);
+    LAUNCH_RET;
+  }
   mlb_launch(ce_fwd_bwd_k, dim3((unsigned)rows), dim3(threads), 0, st, losses, (bf16*)logits, tgt, V, ld, dscale);
   LAUNCH_RET;
 }

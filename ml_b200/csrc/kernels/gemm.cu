@@ -63,6 +63,11 @@ struct GemmArgs {
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
   int a3d, b3d;      // MN-major operand fetched through a 3-D tensor map (one TMA per stage) instead of 64-wide 2-D boxes
   int streamk;       // pair kernel, fp32 add epilogue: every cluster takes an equal contiguous share of all (tile, k-block) units
+  // optional rotary embedding in the bf16 epilogue (pair kernel): output columns [0, rope_cols) are heads of 64 columns
+  // whose halves (i, i + 32) are rotated by the angle table row (output row % rope_T)
+  const float* cosT;
+  const float* sinT;
+  int rope_T, rope_cols;
 };
 
 // Work items of one cluster of the pair kernel.  Static mode: items c, c + nclusters, ... of tiles x splits.
@@ -476,6 +481,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         uint8_t* rowp = buf + lane * 128;
         if (EPI == EPI_BF16) {
+          if (g.cosT != nullptr && col0 < g.rope_cols) {   // warp-uniform; the slab is one head: r = first half, r2 = second
+            const int t = (m0 + lane) % g.rope_T;
+            const float4* c4 = reinterpret_cast<const float4*>(g.cosT + (size_t)t * 32);
+            const float4* s4 = reinterpret_cast<const float4*>(g.sinT + (size_t)t * 32);
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+              const float4 c = __ldg(c4 + q), sn = __ldg(s4 + q);
+              const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                const float x0 = __uint_as_float(r[q * 4 + e]), x1 = __uint_as_float(r2[q * 4 + e]);
+                r[q * 4 + e] = __float_as_uint(x0 * cc[e] - x1 * ss[e]);
+                r2[q * 4 + e] = __float_as_uint(x1 * cc[e] + x0 * ss[e]);
+              }
+            }
+          }
 #pragma unroll
           for (int v = 0; v < 8; v++) {
             const uint32_t* src = (v < 4) ? &r[v * 8] : &r2[(v - 4) * 8];
@@ -737,8 +758,10 @@ int launch_tc_gather(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUten
 // Generic entry: D[M,N] (+)= sum_k A(m,k) B(n,k).
 // A_MN=false: A is [M,K] row-major with pitch lda.  A_MN=true: A is stored [K,M] row-major with pitch lda.
 // Same for B with N.  EPI_BF16 stores bf16; EPI_F32_ADD accumulates into fp32.
+struct RopeEpi { const float* cosT; const float* sinT; int T, cols; };
 template <bool A_MN, bool B_MN, int EPI>
-int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st) {
+int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st,
+                  const RopeEpi* rope = nullptr) {
   bool aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && (lda % 8 == 0) && (ldb % 8 == 0) &&
                  ((uintptr_t)out % 16 == 0) && (ldo % 8 == 0) && (N % 8 == 0) && M > 0 && N > 0 && K > 0;
   // MN-major operands are fetched in 64-wide chunks along M/N: the global extent must be a multiple of 8 elements
@@ -746,6 +769,7 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   if (A_MN) aligned = aligned && (M % 8 == 0);
   if (B_MN) aligned = aligned && (N % 8 == 0);
   if (!A_MN || !B_MN) aligned = aligned && (K % 8 == 0);
+  if (rope && (g_force_simt || !aligned || get_encode() == nullptr)) return -7;   // caller rotates separately
   if (g_force_simt || !aligned || get_encode() == nullptr) {
     dim3 grid(ceil_div_i(N, 64), ceil_div_i(M, 64));
     long sam = A_MN ? 1 : lda, sak = A_MN ? lda : 1, sbn = B_MN ? 1 : ldb, sbk = B_MN ? ldb : 1;
@@ -754,7 +778,10 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   }
   const int BN = (N > 128) ? 256 : 128;
   const bool pairs = g_use_pairs && BN == 256 && M > 128;   // 256 x 256 tile shared by a CTA pair
+  if (rope && !(pairs && rope->cols % 64 == 0 && N % 64 == 0)) return -7;
   GemmArgs g;
+  g.cosT = rope ? rope->cosT : nullptr; g.sinT = rope ? rope->sinT : nullptr;
+  g.rope_T = rope ? rope->T : 1; g.rope_cols = rope ? rope->cols : 0;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, pairs ? 256 : BM);
   g.tiles_n = ceil_div_i(N, BN);
@@ -798,6 +825,14 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
 // out[M,N] = x[M,K] . W[N,K]^T
 MLB_API int mlb_linear_fwd(void* out, const void* x, const void* W, int M, int N, int K, int ldo, int ldx, int ldw, cudaStream_t st) {
   return gemm_dispatch<false, false, EPI_BF16>(out, ldo, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, st);
+}
+// out[M,N] = x[M,K] . W[N,K]^T, then rotary embedding on output columns [0, rope_cols): heads of 64 columns, halves
+// (i, i + 32) rotated by the angle of position (row % T); cosT / sinT are [T, 32] fp32.  Returns -7 (nothing launched)
+// when the shape does not take the CTA-pair tensor-core path; the caller then runs the plain product and rotates.
+MLB_API int mlb_linear_fwd_rope(void* out, const void* x, const void* W, int M, int N, int K, int ldo, int ldx, int ldw,
+                                const float* cosT, const float* sinT, int T, int rope_cols, cudaStream_t st) {
+  RopeEpi r{cosT, sinT, T, rope_cols};
+  return gemm_dispatch<false, false, EPI_BF16>(out, ldo, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, st, &r);
 }
 // dx[M,K] = dout[M,N] . W[N,K]      (GEMM view: D[M,K], reduction N; B(n=k_in, k=n_out) is MN-major)
 MLB_API int mlb_linear_dx(void* dx, const void* dout, const void* W, int M, int N, int K, int lddx, int lddo, int ldw, cudaStream_t st) {
@@ -845,6 +880,7 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
   g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0;
+  g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0;
   GatherArgs ga;
   ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
   ga.b_lo_vec = w_off_elems / 8; ga.b_hi_vec = (w_off_elems + (long)N * K) / 8; ga.b_row_vec = K / 8;

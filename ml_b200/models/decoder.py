@@ -22,6 +22,8 @@ from ..config import Config
 from ..layout import DecoderLayout, flops_per_step
 from ..utils import rng as _rng
 
+FUSE_ROPE_INTO_QKV = True   # head size 64 on the GPU: RoPE in the QKV GEMM's epilogue instead of a separate in-place pass
+
 
 class GPT:
     def __init__(self, cfg: Config, B: int, device="cpu", dtype: Optional[torch.dtype] = None,
@@ -154,9 +156,14 @@ class GPT:
             if self.res is not None and hasattr(self.res, "linear_fwd_first"):
                 # sharded parameters: the unit's all-gather may be fused into this first GEMM of the layer
                 self.res.linear_fwd_first(qkv, sl(self.ln1[l]), o.qkv, (3 * C, C))
+                roped = False
             else:
-                ops.linear_fwd(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C))
-            if "rope" not in self.skip:
+                # head size 64 on the GPU: the rotation runs in the GEMM's epilogue, on the fp32 accumulators
+                roped = (hd == 64 and qkv.is_cuda and "rope" not in self.skip and FUSE_ROPE_INTO_QKV and
+                         ops.native_module().linear_fwd_rope(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C), self.cos, self.sin, T, 2 * C))
+                if not roped:
+                    ops.linear_fwd(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C))
+            if "rope" not in self.skip and not roped:
                 ops.rope_fwd(qkv, self.cos, self.sin, B, T, H, hd)
             self._mark("F_qkv+rope")
             if "attn" not in self.skip:   # ENTROPY_SKIP_* ablations remove a stage to attribute its time (results are then meaningless)

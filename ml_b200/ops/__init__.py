@@ -42,3 +42,8 @@ for _n in _NAMES:
     globals()[_n] = _make(_n)
 
 rope_tables = ref.rope_tables
+
+
+def native_module():
+    """The ctypes binding module (CUDA tensors only): entry points that have no CPU counterpart live there."""
+    return _load_native()

@@ -148,6 +148,22 @@ def linear_fwd(out, x, W):
     _chk(lib().mlb_linear_fwd(_b(out), _b(x), _b(W), M, N, K, out.stride(0), x.stride(0), W.stride(0), _st()), "linear_fwd")
 
 
+def linear_fwd_rope(out, x, W, cos, sin, T, rope_cols):
+    """out = x . W^T with rotary embedding applied to output columns [0, rope_cols) in the GEMM epilogue (heads of 64
+    columns, position = row % T).  Returns False when the shape does not take that path (nothing was launched)."""
+    M, K = x.shape
+    N = W.shape[0]
+    L = lib()
+    fn = L.mlb_linear_fwd_rope
+    fn.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _vp]
+    fn.restype = _i32
+    rc = fn(_b(out), _b(x), _b(W), M, N, K, out.stride(0), x.stride(0), W.stride(0), _f(cos), _f(sin), T, rope_cols, _st())
+    if rc == -7:
+        return False
+    _chk(rc, "linear_fwd_rope")
+    return True
+
+
 def linear_dx(dx, dout, W):
     M, N = dout.shape
     K = W.shape[1]

@@ -109,6 +109,28 @@ def test_gemm_general_entry_all_layouts(a_mn, b_mn, acc, gemm_mode):
     close(out, exp, name="gemm")
 
 
+def test_linear_fwd_with_rope_epilogue_matches_separate_rope():
+    """QKV product with the rotation applied in the GEMM epilogue vs product, then the in-place RoPE kernel."""
+    torch.manual_seed(8)
+    B, T, H, hd = 3, 160, 4, 64
+    C = H * hd
+    x, W = rnd(B * T, C), rnd(3 * C, C, scale=0.05)
+    cos, sin = ref.rope_tables(T, hd, 10000.0, dev())
+    fused = torch.empty(B * T, 3 * C, device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_rope(fused, x, W, cos, sin, T, 2 * C) is True
+    exp = torch.empty(B * T, 3 * C, device=dev())
+    ref.linear_fwd(exp, x, W)
+    ref.rope_fwd(exp, cos, sin, B, T, H, hd)
+    close(fused, exp, name="qkv + rope")
+    # V columns are untouched by the rotation
+    plain = torch.empty_like(fused)
+    nat().linear_fwd(plain, x, W)
+    assert torch.equal(plain[:, 2 * C:], fused[:, 2 * C:])
+    # a shape that does not take the CTA-pair path reports it instead of launching
+    small = torch.empty(64, 3 * C, device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_rope(small, x[:64], W, cos, sin, T, 2 * C) is False
+
+
 def test_gemm_simt_path_odd_shape():
     torch.manual_seed(3)
     M, N, K = 130, 100, 100   # C=100-style odd sizes: no 16-byte pitch, SIMT kernel
