@@ -645,7 +645,7 @@ inline int gs(long n, int per_block) { return (int)((n + per_block - 1) / per_bl
 }  // namespace
 
 #define LAUNCH_RET return (int)cudaGetLastError()
-static int g_ce_smem = 1;     // tuning hook: 0 = always the two-pass cross-entropy kernel
+static int g_ce_smem = 0;     // tuning hook: 0 = always the two-pass cross-entropy kernel
 MLB_API void mlb_ce_mode(int smem_row) { g_ce_smem = smem_row; }
 
 MLB_API int mlb_embed_fwd(void* out, const void* wte, const int* ids, long BT, int C, cudaStream_t st) {

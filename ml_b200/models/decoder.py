@@ -22,7 +22,7 @@ from ..config import Config
 from ..layout import DecoderLayout, flops_per_step
 from ..utils import rng as _rng
 
-FUSE_ROPE_INTO_QKV = True   # head size 64 on the GPU: RoPE in the QKV GEMM's epilogue instead of a separate in-place pass
+FUSE_ROPE_INTO_QKV = False   # head size 64 on the GPU: RoPE in the QKV GEMM's epilogue instead of a separate in-place pass
 
 
 class GPT:

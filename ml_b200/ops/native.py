@@ -39,6 +39,7 @@ def lib():
         "mlb_gemm_streamk": [_i32],
         "mlb_attn_force_simt": [_i32],
         "mlb_attn_fwd_mode": [_i32],
+        "mlb_ce_mode": [_i32],
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
         "mlb_attn_bwd_scratch_bytes": [_i32, _i32, _i32, _i32],

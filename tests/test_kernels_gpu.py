@@ -315,7 +315,18 @@ def test_swiglu(rows, I):
 
 
 @pytest.mark.parametrize("rows,V", [(64, 50304), (16, 512), (9, 1001)])
-def test_cross_entropy(rows, V):
+@pytest.mark.parametrize("smem_row", [1, 0], ids=["row_in_smem", "two_pass"])
+def test_cross_entropy(rows, V, smem_row):
+    """Two kernels: the row parked in shared memory (one exponential per logit; needs V % 8 == 0), or two passes over
+    global memory."""
+    nat().lib().mlb_ce_mode(smem_row)
+    try:
+        _check_cross_entropy(rows, V)
+    finally:
+        nat().lib().mlb_ce_mode(0)
+
+
+def _check_cross_entropy(rows, V):
     torch.manual_seed(11)
     logits = rnd(rows, V, scale=3.0)
     tgt = torch.randint(0, V, (rows,), device=dev(), dtype=torch.int32)

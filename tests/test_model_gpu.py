@@ -75,6 +75,38 @@ def test_overfit_gpu_graph_tc_paths():
     assert _native().get_error() == 0
 
 
+def test_programmatic_dependent_launch_gives_the_same_losses():
+    """MLB_PDL=1 starts the hot kernels with the programmatic-serialization attribute (each waits for its predecessor
+    after its own set-up); a few captured steps must reproduce the default run's loss."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from ml_b200 import Config\n"
+        "from ml_b200.trainer import Trainer\n"
+        "from ml_b200.utils.rng import Stream\n"
+        "from ml_b200.ops import native\n"
+        "native.lib().mlb_gemm_set_splits(1)\n"
+        "cfg = Config(V=512, C=256, L=2, H=4, I=512, T=128)\n"
+        "tr = Trainer(cfg, 4, 'cuda:0', lr=1e-3, wd=0.0, use_graph=True)\n"
+        "ids, tgt = Stream(7).token_pairs(4 * 128, 512)\n"
+        "tr.set_batch(ids.cuda(), tgt.cuda())\n"
+        "for _ in range(12): tr.step()\n"
+        "torch.cuda.synchronize()\n"
+        "print('LOSS', tr.loss(), native.get_error())\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = {}
+    for pdl in ("0", "1"):
+        env = dict(os.environ, MLB_PDL=pdl, PYTHONPATH=root)
+        r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        line = [l for l in r.stdout.splitlines() if l.startswith("LOSS")][0].split()
+        assert line[2] == "0", line
+        out[pdl] = float(line[1])
+    assert abs(out["0"] - out["1"]) < 2e-2, out
+
+
 def test_mm_overfit_gpu():
     cfg = Config(V=256, C=128, L=4, H=4, I=256, T=64)
     vc = VisionConfig(vC=96, vL=3, vI=192, n_patch=16)
