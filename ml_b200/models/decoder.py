@@ -22,7 +22,10 @@ from ..config import Config
 from ..layout import DecoderLayout, flops_per_step
 from ..utils import rng as _rng
 
-FUSE_ROPE_INTO_QKV = False   # head size 64 on the GPU: RoPE in the QKV GEMM's epilogue instead of a separate in-place pass
+import os as _os
+
+# head size 64 on the GPU: RoPE in the QKV GEMM's epilogue instead of a separate in-place pass (MLB_NO_ROPE_FUSE=1: off)
+FUSE_ROPE_INTO_QKV = _os.environ.get("MLB_NO_ROPE_FUSE", "0") != "1"
 
 
 class GPT:
