@@ -58,6 +58,8 @@ def bench_gemm(a):
     nat.lib().mlb_gemm_use_pairs(a.pairs)
     nat.lib().mlb_gemm_epilogue_mode(a.epi)
     nat.lib().mlb_gemm_streamk(a.streamk)
+    nat.lib().mlb_gemm_tile_order(a.tile_order)
+    nat.lib().mlb_gemm_streamk_groups(a.sk_groups)
     print("kernel:", f"256x256 tile per CTA pair (cta_group::2), epilogue mode {a.epi}" if a.pairs else "128x256 tile per CTA")
     shapes = [(3 * a.C, a.C, "qkv"), (a.C, a.C, "o"), (2 * a.I, a.C, "gate|up"), (a.C, a.I, "down"), (a.V, a.C, "lm_head")]
     print(f"{'shape':<10}{'op':<5}{'ours us':>10}{'TFLOP/s':>10}{'frac of ' + how:>18}{'cuBLAS us':>11}{'TFLOP/s':>10}")
@@ -248,6 +250,8 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
     ap.add_argument("--fwd-mode", type=int, default=1, help="attention forward, head size 64: 1/2 = thread-per-row kernel (2: tiles staggered), 0 = four threads per row")
+    ap.add_argument("--tile-order", type=int, default=0, help="pair GEMM static schedule: 0 = by operand size, 1 = M first, 2 = N first")
+    ap.add_argument("--sk-groups", type=int, default=1, help="pair GEMM stream-K: 1 = clusters in groups that share the wide operand's k-range")
     ap.add_argument("--streamk", type=int, default=1, help="pair GEMM, weight gradients: 1 = equal k-block ranges per cluster, 0 = fixed split count")
     ap.add_argument("--epi", type=int, default=1, help="pair GEMM epilogue: 1 = coalesced stores by the warps, 0 = TMA store / add-reduce")
     ap.add_argument("--pairs", type=int, default=1, help="GEMM: 1 = CTA-pair kernel (cta_group::2), 0 = one CTA per tile")

@@ -62,7 +62,9 @@ struct GemmArgs {
   int ldo;           // output row pitch in elements
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
   int a3d, b3d;      // MN-major operand fetched through a 3-D tensor map (one TMA per stage) instead of 64-wide 2-D boxes
-  int streamk;       // pair kernel, fp32 add epilogue: every cluster takes an equal contiguous share of all (tile, k-block) units
+  int streamk;       // pair kernel, fp32 add epilogue: every cluster (group) takes an equal contiguous share of all (tile, k-block) units
+  int sk_group, sk_group_m;   // stream-K group size (tiles along the short dimension) and whether that dimension is M
+  int nt_fast;       // static schedule: consecutive work items walk N first (tiles in flight share rows of A) instead of M
   // optional rotary embedding in the bf16 epilogue (pair kernel): output columns [0, rope_cols) are heads of 64 columns
   // whose halves (i, i + 32) are rotated by the angle table row (output row % rope_T)
   const float* cosT;
@@ -77,28 +79,44 @@ struct GemmArgs {
 struct WorkItem { int mt, nt, kb0, kb1; };
 struct WorkIter {
   int t, step, total, tiles_m, tiles_n, kb_per_split, kb_total;
+  int member, G, grouped_m;     // stream-K: this cluster's tile index along the grouped dimension
   long u, u1;
-  bool sk;
+  bool sk, nt_fast;
   __device__ WorkIter(const GemmArgs& g, int cid, int ncl)
       : t(cid), step(ncl), total(g.tiles_m * g.tiles_n * g.splits), tiles_m(g.tiles_m), tiles_n(g.tiles_n),
-        kb_per_split(g.kb_per_split), kb_total(g.kb_total), sk(g.streamk != 0) {
-    const long units = (long)g.tiles_m * g.tiles_n * g.kb_total;
-    u = units * cid / ncl;
-    u1 = units * (cid + 1) / ncl;
+        kb_per_split(g.kb_per_split), kb_total(g.kb_total), sk(g.streamk != 0), nt_fast(g.nt_fast != 0) {
+    // Stream-K in groups: the G tiles that share the wide operand (same index along the long dimension) are given to G
+    // neighbouring clusters with IDENTICAL (long-dimension tile, k-block) ranges, so that operand is fetched from DRAM
+    // once and found in L2 by the other members; the narrow operand is small enough to live in L2.
+    G = g.sk_group > 0 ? g.sk_group : 1;
+    grouped_m = g.sk_group_m;
+    const int ngroups = ncl / G, grp = cid / G;
+    member = cid % G;
+    const int long_tiles = G == 1 ? g.tiles_m * g.tiles_n : (grouped_m ? g.tiles_n : g.tiles_m);   // G == 1: every tile on its own
+    const long units = (long)long_tiles * g.kb_total;
+    if (sk && grp < ngroups) {
+      u = units * grp / ngroups;
+      u1 = units * (grp + 1) / ngroups;
+    } else {
+      u = u1 = 0;
+    }
   }
   __device__ bool next(WorkItem& w) {
     if (sk) {
       if (u >= u1) return false;
-      const int tile = (int)(u / kb_total);
+      const int lt = (int)(u / kb_total);
       w.kb0 = (int)(u % kb_total);
       w.kb1 = (int)min((long)kb_total, w.kb0 + (u1 - u));
-      w.mt = tile % tiles_m; w.nt = tile / tiles_m;
+      if (G == 1) { w.mt = lt % tiles_m; w.nt = lt / tiles_m; }
+      else if (grouped_m) { w.mt = member; w.nt = lt; }
+      else { w.mt = lt; w.nt = member; }
       u += w.kb1 - w.kb0;
       return true;
     }
     if (t >= total) return false;
     const int sp = t / (tiles_m * tiles_n);
-    w.mt = t % tiles_m; w.nt = (t / tiles_m) % tiles_n;
+    if (nt_fast) { w.nt = t % tiles_n; w.mt = (t / tiles_n) % tiles_m; }
+    else { w.mt = t % tiles_m; w.nt = (t / tiles_m) % tiles_n; }
     w.kb0 = sp * kb_per_split; w.kb1 = min(w.kb0 + kb_per_split, kb_total);
     t += step;
     return true;
@@ -709,6 +727,8 @@ int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap*
 // resident at once (a GPC with an odd number of usable SMs leaves one without a partner), so the static tile
 // schedule never waits for a second wave of CTAs.
 int g_use_pairs = 1;         // tuning hook: 0 = always the 1-CTA kernel
+int g_tile_order = 0;        // tuning hook: 0 = by operand size, 1 = M first, 2 = N first
+int g_sk_groups = 1;         // tuning hook: 0 = stream-K without groups (one linear range per cluster)
 int g_streamk = 1;           // tuning hook: weight-gradient products cut into equal k-block ranges per cluster
 int g_epi_mode = 1;          // tuning hook: pair kernel's epilogue, 0 = TMA store / reduce, 1 = coalesced stores by the warps
 template <bool A_MN, bool B_MN, int EPI, int EMODE>
@@ -805,6 +825,14 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   g.splits = ceil_div_i(g.kb_total, g.kb_per_split);
   g.a3d = g.b3d = 0;
   g.streamk = (pairs && EPI == EPI_F32_ADD && g_streamk && g_force_splits == 0) ? 1 : 0;
+  // Tiles in flight should share the operand that does not fit in L2: walk N first when A is the larger one.
+  g.nt_fast = (g_tile_order == 2) ? 1 : (g_tile_order == 1 ? 0 : ((long)M > (long)N ? 1 : 0));
+  g.sk_group = 1; g.sk_group_m = 0;
+  if (g.streamk) {
+    // group along the dimension with fewer tiles (its operand is the narrow one); at most 4 members, else plain stream-K
+    const int short_tiles = g.tiles_m < g.tiles_n ? g.tiles_m : g.tiles_n;
+    if (g_sk_groups && short_tiles <= 4 && short_tiles >= 1 && pair_clusters() >= 4 * short_tiles) { g.sk_group = short_tiles; g.sk_group_m = g.tiles_m < g.tiles_n ? 1 : 0; }
+  }
   const CUtensorMap* tmA = nullptr;
   const CUtensorMap* tmB = nullptr;
   if (A_MN && g_use_3d) { tmA = mlb_tmap_mn3d_cached(A, K, M, lda, BM / 64); g.a3d = tmA != nullptr; }
@@ -879,7 +907,7 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   GemmArgs g;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
-  g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0;
+  g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0; g.sk_group = 1; g.sk_group_m = 0; g.nt_fast = 0;
   g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0;
   GatherArgs ga;
   ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
@@ -958,5 +986,7 @@ MLB_API void mlb_gemm_use_3d_maps(int on) { g_use_3d = on; }
 MLB_API void mlb_gemm_use_pairs(int on) { g_use_pairs = on; }
 MLB_API void mlb_gemm_epilogue_mode(int m) { g_epi_mode = m; }
 MLB_API void mlb_gemm_streamk(int on) { g_streamk = on; }
+MLB_API void mlb_gemm_tile_order(int mode) { g_tile_order = mode; }
+MLB_API void mlb_gemm_streamk_groups(int on) { g_sk_groups = on; }
 
 MLB_DEFINE_ERROR_WORD(gemm)

@@ -37,6 +37,8 @@ def lib():
         "mlb_gemm_use_pairs": [_i32],
         "mlb_gemm_epilogue_mode": [_i32],
         "mlb_gemm_streamk": [_i32],
+        "mlb_gemm_tile_order": [_i32],
+        "mlb_gemm_streamk_groups": [_i32],
         "mlb_attn_force_simt": [_i32],
         "mlb_attn_fwd_mode": [_i32],
         "mlb_ce_mode": [_i32],

@@ -45,18 +45,23 @@ GEMM_SHAPES = [(256, 256, 128), (384, 768, 768), (1024, 2304, 768), (512, 4096, 
                (2048, 768, 2048), (256, 1000, 512), (4096 + 136, 776, 392)]
 
 
-@pytest.fixture(params=[(1, 1, 1), (1, 0, 0), (0, 0, 0)], ids=["cta_pair", "cta_pair_tma_epilogue_splitk", "single_cta"])
+@pytest.fixture(params=[(1, 1, 1), (1, 0, 0), (0, 0, 0), (1, 1, 2)],
+                ids=["cta_pair", "cta_pair_tma_epilogue_splitk", "single_cta", "cta_pair_ungrouped_streamk_m_first"])
 def gemm_mode(request):
     """Large products have two tcgen05 kernels: a 256x256 tile shared by a CTA pair (cta_group::2) whose epilogue either
     writes coalesced rows itself or hands slabs to TMA (weight gradients: equal k-block ranges per cluster, or a fixed
     split count), or 128x256 per CTA."""
     nat().lib().mlb_gemm_use_pairs(request.param[0])
     nat().lib().mlb_gemm_epilogue_mode(request.param[1])
-    nat().lib().mlb_gemm_streamk(request.param[2])
+    nat().lib().mlb_gemm_streamk(1 if request.param[2] else 0)
+    nat().lib().mlb_gemm_streamk_groups(0 if request.param[2] == 2 else 1)
+    nat().lib().mlb_gemm_tile_order(1 if request.param[2] == 2 else 0)
     yield request.param
     nat().lib().mlb_gemm_use_pairs(1)
     nat().lib().mlb_gemm_epilogue_mode(1)
     nat().lib().mlb_gemm_streamk(1)
+    nat().lib().mlb_gemm_streamk_groups(1)
+    nat().lib().mlb_gemm_tile_order(0)
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
