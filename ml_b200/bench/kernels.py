@@ -133,6 +133,17 @@ def bench_mma(a):
             per = c.median().item() / (reps * 4)
             print(f"M=128 N={N:3d} K=16  A from {'TMEM' if ts else 'smem'}: {per:6.1f} cycles per MMA  "
                   f"({2 * 128 * N * 16 / per:6.0f} FLOP/cycle/SM; dense bf16 peak 8192)")
+    # special-function unit: exponentials per cycle and SM, fp32 vs packed bf16x2
+    L.mlb_mufu_probe.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    sink = torch.zeros(4, device="cuda")
+    iters = 2048
+    for mode, nm, per in ((0, "ex2.approx.ftz.f32", 1), (1, "ex2.approx.ftz.bf16x2", 2)):
+        for _ in range(2):
+            rc = L.mlb_mufu_probe(cyc.data_ptr(), sink.data_ptr(), mode, iters, 148, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert rc == 0
+        c = cyc[:148].float().median().item()
+        print(f"{nm:<24} {512 * 8 * iters * per / c:6.1f} exponentials per cycle and SM (512 threads per SM)")
     print("kernel error word:", nat.get_error())
 
 

@@ -531,6 +531,51 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_smem_k(float* __restrict__ los
   }
 }
 
+// ------------------------------------------------------------------ special-function-unit micro-benchmark
+// Every thread runs `iters` rounds of eight independent exponentials: fp32 `ex2.approx.ftz.f32` (mode 0) or packed
+// `ex2.approx.ftz.bf16x2` (mode 1, two results per instruction).  cycles[block] = SM cycles of the block.
+__global__ void __launch_bounds__(512) mufu_probe_k(long long* cycles, float* sink, int mode, int iters) {
+  float acc = 0.f;
+  float x[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) x[j] = -0.001f * (float)(threadIdx.x + j);
+  __syncthreads();
+  const long long t0 = clock64();
+  if (mode == 0) {
+    for (int i = 0; i < iters; i++) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        float y;
+        asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x[j]));
+        x[j] = y - 1.0f;
+      }
+    }
+  } else {
+    uint32_t h[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) h[j] = pack_bf16(x[j], x[j] * 0.5f);
+    for (int i = 0; i < iters; i++) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        uint32_t y;
+        asm volatile("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(h[j]));
+        h[j] = y ^ 0x80008000u;   // negate both halves: keeps the argument in (-1, 0]
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) x[j] = __uint_as_float(h[j] << 16);
+  }
+  const long long t1 = clock64();
+#pragma unroll
+  for (int j = 0; j < 8; j++) acc += x[j];
+  if (threadIdx.x == 0) cycles[blockIdx.x] = t1 - t0;
+  if (acc == 12345.678f) sink[0] = acc;
+}
+MLB_API int mlb_mufu_probe(long long* cycles, float* sink, int mode, int iters, int blocks, cudaStream_t st) {
+  mufu_probe_k<<<blocks, 512, 0, st>>>(cycles, sink, mode, iters);
+  return (int)cudaGetLastError();
+}
+
 // ------------------------------------------------------------------ AdamW (fp32 master/m/v, bf16 copy written in the same pass)
 __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, const float* __restrict__ grads,
                         float* __restrict__ m, float* __restrict__ v, long n, float lr, float b1, float b2, float eps, float wd,

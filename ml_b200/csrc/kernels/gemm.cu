@@ -515,24 +515,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               }
             }
           }
-          if (EMODE == 2) {
-            // no staging: every lane writes its own row's 128 bytes (eight 16-byte stores; rows are ldo apart)
-            if (m0 + lane < g.M) {
-              bf16* dst = (bf16*)g.out + (size_t)(m0 + lane) * g.ldo + col0;
-#pragma unroll
-              for (int v = 0; v < 8; v++) {
-                const uint32_t* src = (v < 4) ? &r[v * 8] : &r2[(v - 4) * 8];
-                uint4 pk;
-                pk.x = pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1]));
-                pk.y = pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3]));
-                pk.z = pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5]));
-                pk.w = pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7]));
-                if (col0 + v * 8 < g.N) *reinterpret_cast<uint4*>(dst + v * 8) = pk;
-              }
-            }
-            slab++;
-            continue;
-          }
 #pragma unroll
           for (int v = 0; v < 8; v++) {
             const uint32_t* src = (v < 4) ? &r[v * 8] : &r2[(v - 4) * 8];
@@ -861,7 +843,6 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   const CUtensorMap* tmD = (EPI == EPI_BF16) ? mlb_tmap_cached(out, M, N, ldo, 32, 64, 2) : mlb_tmap_cached(out, M, N, ldo, 32, 32, 4);
   if (!tmA || !tmB || !tmD) return -2;
   if (pairs && g_epi_mode == 0) return launch_tc2<A_MN, B_MN, EPI, 0>(tmA, tmB, tmD, g, st);
-  if (pairs && g_epi_mode == 2 && EPI == EPI_BF16) return launch_tc2<A_MN, B_MN, EPI, 2>(tmA, tmB, tmD, g, st);
   if (pairs) return launch_tc2<A_MN, B_MN, EPI, 1>(tmA, tmB, tmD, g, st);
   if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
   return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
