@@ -27,6 +27,9 @@ CUDA_LIB = LIB / "libmlb_cuda.so"
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "--use_fast_math", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
               "-I", str(CSRC)]
+# what goes into the staleness hashes: the flags without anything that depends on where the tree is checked out, so
+# a library built in one directory is still fresh after the tree has been copied elsewhere
+_FLAGS_FOR_HASH = " ".join(f for f in NVCC_FLAGS if f != str(CSRC))
 # Files that must not travel to multi-GPU runs are listed in .gpurunignore.multi; nothing here needs that.
 
 
@@ -62,7 +65,7 @@ def host_hash():
 
 
 def cuda_hash():
-    return _hash(cuda_sources() + _headers(), " ".join(NVCC_FLAGS))
+    return _hash(cuda_sources() + _headers(), _FLAGS_FOR_HASH)
 
 
 def _stamp(lib: Path) -> Path:
@@ -78,12 +81,37 @@ def build_host(verbose=False):
     h = host_hash()
     if is_fresh(HOST_LIB, h):
         return HOST_LIB
-    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", *map(str, host_sources()), "-o", str(HOST_LIB)]
-    if verbose:
-        print(" ".join(cmd))
-    subprocess.run(cmd, check=True)
-    _stamp(HOST_LIB).write_text(h)
+    with _BuildLock("host.lock"):
+        if is_fresh(HOST_LIB, h):
+            return HOST_LIB
+        tmp = HOST_LIB.with_suffix(".so.tmp%d" % os.getpid())
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", *map(str, host_sources()), "-o", str(tmp)]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.run(cmd, check=True)
+        os.replace(tmp, HOST_LIB)
+        _stamp(HOST_LIB).write_text(h)
     return HOST_LIB
+
+
+class _BuildLock:
+    """Exclusive lock on a file in _lib/: several ranks of one job may find the library stale at the same moment; one
+    builds, the others wait and then find it fresh."""
+
+    def __init__(self, name):
+        LIB.mkdir(exist_ok=True)
+        self.path = LIB / name
+
+    def __enter__(self):
+        import fcntl
+        self.f = open(self.path, "w")
+        fcntl.flock(self.f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+        fcntl.flock(self.f, fcntl.LOCK_UN)
+        self.f.close()
 
 
 def build_cuda(verbose=False, force=False):
@@ -91,12 +119,19 @@ def build_cuda(verbose=False, force=False):
     h = cuda_hash()
     if not force and is_fresh(CUDA_LIB, h):
         return CUDA_LIB
+    with _BuildLock("cuda.lock"):
+        if not force and is_fresh(CUDA_LIB, h):      # another process built it while this one waited
+            return CUDA_LIB
+        return _build_cuda_locked(h, verbose, force)
+
+
+def _build_cuda_locked(h, verbose, force):
     nvcc = _nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libmlb_cuda.so")
     objdir = LIB / "obj"
     objdir.mkdir(exist_ok=True)
-    hdr_hash = _hash(_headers(), " ".join(NVCC_FLAGS))
+    hdr_hash = _hash(_headers(), _FLAGS_FOR_HASH)
     logs = {}
 
     def compile_one(src: Path):
@@ -116,8 +151,10 @@ def build_cuda(verbose=False, force=False):
 
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
         objs = list(ex.map(compile_one, cuda_sources()))
-    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(CUDA_LIB), *map(str, objs), "-lcudart"]
+    tmp = CUDA_LIB.with_suffix(".so.tmp%d" % os.getpid())
+    cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp), *map(str, objs), "-lcudart"]
     subprocess.run(cmd, check=True)
+    os.replace(tmp, CUDA_LIB)          # a process that is loading the old file keeps its inode; nobody sees a partial one
     _stamp(CUDA_LIB).write_text(h)
     if verbose:
         for k, v in logs.items():
