@@ -220,3 +220,31 @@ def test_raw_token_loader_formats(tmp_path):
     ld2 = RawTokenLoader(str(txt), B=1, T=10, shuffle=True, seed=1)
     seen = {int(ld2.next()[0][0]) for _ in range(4)}
     assert seen == {0, 10, 20, 30}          # whole samples are permuted, sequences stay intact
+
+
+def test_native_build_stamps_survive_relocation_and_concurrent_builders(tmp_path):
+    """The staleness hash of the native libraries must not depend on where the tree lives (a job copies the tree to
+    a scratch directory and several ranks import it at once), and two processes that build at the same time must both
+    end with a complete library."""
+    import shutil
+    import subprocess
+    import sys
+    from ml_b200 import build as b
+    b.build_host()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    dst = tmp_path / "copy"
+    shutil.copytree(os.path.join(root, "ml_b200"), dst / "ml_b200", ignore=shutil.ignore_patterns("obj", "__pycache__"))
+    code = ("from ml_b200 import build as b\n"
+            "print('FRESH', b.is_fresh(b.HOST_LIB, b.host_hash()), "
+            "(not b.CUDA_LIB.exists()) or b.is_fresh(b.CUDA_LIB, b.cuda_hash()))\n")
+    r = subprocess.run([sys.executable, "-c", code], cwd=dst, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "FRESH True True" in r.stdout, r.stdout
+    # two builders at once on a stale host library: both must succeed and leave a loadable file
+    (dst / "ml_b200" / "_lib" / "libmlb_host.hash").write_text("stale")
+    code2 = ("from ml_b200 import build as b\nimport ctypes\nb.build_host()\nctypes.CDLL(str(b.HOST_LIB))\nprint('OK')\n")
+    ps = [subprocess.Popen([sys.executable, "-c", code2], cwd=dst, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+          for _ in range(3)]
+    for p in ps:
+        out, err = p.communicate(timeout=300)
+        assert p.returncode == 0 and "OK" in out, err[-2000:]
