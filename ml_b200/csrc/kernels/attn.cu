@@ -1039,20 +1039,24 @@ struct BwdFusedSmem {
   static constexpr int V = K + TILE_BYTES;
   static constexpr int Q = V + TILE_BYTES;               // 3 buffers
   static constexpr int DO = Q + 3 * TILE_BYTES;          // 3 buffers
-  static constexpr int DST = DO + 3 * TILE_BYTES;        // [128 keys x 128 queries] bf16
-  static constexpr int STAT = DST + 2 * TILE_BYTES;      // 8 warps x (-lse*log2e [64], -delta [64])
+  static constexpr int DST = DO + 3 * TILE_BYTES;        // 2 buffers x [128 keys x 128 queries] bf16
+  static constexpr int DQS = DST + 4 * TILE_BYTES;       // dQ staging: 4 drain warps x [32 rows x 128 B] bf16, swizzled
+  static constexpr int STAT = DQS + TILE_BYTES;          // 8 warps x (-lse*log2e [64], -delta [64])
   static constexpr int BAR = STAT + 4096;
   static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
 constexpr int BWDF_E_WARPS = 8;       // element-wise warps: TMEM lane group (w & 3) x 64-query column half (w >> 2)
 constexpr int BWDF_D_WARPS = 4;       // drain warps: dQ partial tiles and the dK / dV epilogue, one TMEM lane group each
-constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS;   // issues every MMA
-constexpr int BWDF_LOAD_WARP = BWDF_CTRL_WARP + 1;            // issues every TMA load
+// Warp w runs on scheduler w % 4.  Warps 12 and 13 stay idle so that the MMA warp (14) and the loader warp (15) land on
+// schedulers 2 and 3: every scheduler then carries two element-wise warps, one drain warp and one light warp.
+constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS + 2;   // issues every MMA
+constexpr int BWDF_LOAD_WARP = BWDF_CTRL_WARP + 1;                // issues every TMA load
 constexpr int BWDF_THREADS = (BWDF_LOAD_WARP + 1) * 32;
 
 __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
-                                                                            const __grid_constant__ CUtensorMap tm_do, const AttnArgs a) {
+                                                                            const __grid_constant__ CUtensorMap tm_do,
+                                                                            const __grid_constant__ CUtensorMap tm_dq, const AttnArgs a) {
   mlb_pdl_sync();
   using S = BwdFusedSmem;
   constexpr int HD = 64;
@@ -1089,6 +1093,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tm_qkv);
     tc::tma_prefetch_desc(&tm_do);
+    tc::tma_prefetch_desc(&tm_dq);
   }
   if (warp == BWDF_CTRL_WARP) tc::tmem_alloc(tmem_slot, TMEM_COLS);
   tc::tc_fence_before();
@@ -1185,16 +1190,17 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
           if (go) {
             tc::tc_fence_after();
             const uint64_t o = (uint64_t)buf * TILE_D;
+            const uint64_t od = (uint64_t)(blk & 1) * 2 * TILE_D;     // dS^T buffer of this block
             const uint32_t acc = it > 0;
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(t_dv, t_pt + ks * 8, dDOmn + o + ks * 128, idesc_d, acc | (ks > 0));
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, dSTk + (ks >> 2) * TILE_D + (ks & 3) * 2, dQmn + o + ks * 128, idesc_d, acc | (ks > 0));
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, dSTk + od + (ks >> 2) * TILE_D + (ks & 3) * 2, dQmn + o + ks * 128, idesc_d, acc | (ks > 0));
             if (blk > 0) go = wait(bar_dqf, (blk - 1) & 1, 47);   // the previous dQ tile has left TMEM
             if (go) {
               tc::tc_fence_after();
 #pragma unroll
-              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, dSTmn + ks * 128, dKmn + ks * 128, idesc_q, ks > 0);
+              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, dSTmn + od + ks * 128, dKmn + ks * 128, idesc_q, ks > 0);
             }
           }
           tc::mma_commit(bar_d);
@@ -1243,7 +1249,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
         wait(bar_s, blk & 1, 48);          // S^T, dP^T of this block are complete
         tc::tc_fence_after();
         if (tl && warp == 0) tl[blk * 8 + 1] = clock64();
-        uint32_t pw[2][16], dw[2][16];
+        uint32_t pw[2][16];
         const bool diag = (it == 0);
 #pragma unroll
         for (int hf = 0; hf < 2; hf++) {
@@ -1262,6 +1268,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
             const int qc = c0 + v8 * 8;
             const float* sn = my_stat + hf * 32 + v8 * 8;
             float nl[8], nd[8];
+            uint32_t dw[4];
             *reinterpret_cast<float4*>(nl) = *reinterpret_cast<const float4*>(sn);
             *reinterpret_cast<float4*>(nl + 4) = *reinterpret_cast<const float4*>(sn + 4);
             *reinterpret_cast<float4*>(nd) = *reinterpret_cast<const float4*>(sn + 64);
@@ -1280,29 +1287,29 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
               float d0, d1;
               upk2(mul2(pk2(p0, p1), t2), d0, d1);
               pw[hf][v8 * 4 + x] = pack_bf16(p0, p1);
-              dw[hf][v8 * 4 + x] = pack_bf16(d0, d1);
+              dw[x] = pack_bf16(d0, d1);
             }
+            // dS^T goes straight into the buffer that block blk-2 used (its MMAs completed before block blk-1's P^T
+            // was stored): only the two TMEM stores of P^T are left to do once the previous block's MMAs are out of the way
+            *reinterpret_cast<uint4*>(smem + S::DST + (blk & 1) * 2 * TILE_BYTES + sw_off(row, qc)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
           }
         }
+        tc::fence_async_smem();
         if (tl && warp == 0) tl[blk * 8 + 2] = clock64();
-        // P^T's TMEM columns and the dS^T tile belong to the previous block's MMAs until they complete
+        // P^T's TMEM columns belong to the previous block's dV MMAs until they complete
         if (blk > 0) { wait(bar_d, (blk - 1) & 1, 49); tc::tc_fence_after(); }
         if (tl && warp == 0) tl[blk * 8 + 3] = clock64();
-#pragma unroll
-        for (int v8 = 0; v8 < 8; v8++)
-          *reinterpret_cast<uint4*>(smem + S::DST + sw_off(row, ch * 64 + v8 * 8)) =
-              make_uint4(dw[v8 >> 2][(v8 & 3) * 4], dw[v8 >> 2][(v8 & 3) * 4 + 1], dw[v8 >> 2][(v8 & 3) * 4 + 2], dw[v8 >> 2][(v8 & 3) * 4 + 3]);
         tc::tmem_st16(t_pt + lane_addr + ch * 32, pw[0]);
         tc::tmem_st16(t_pt + lane_addr + ch * 32 + 16, pw[1]);
         tc::tmem_st_wait();
-        tc::fence_async_smem();
+
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(bar_p);
         if (tl && warp == 0) tl[blk * 8 + 4] = clock64();
       }
     }
-  } else if (warp < BWDF_CTRL_WARP) {
+  } else if (warp < BWDF_E_WARPS + BWDF_D_WARPS) {
     // ---------------------------------------------------------------- 4 drain warps
     // dQ partial of (query block i, this key tile): TMEM -> bf16 -> its own tile of the partial buffer (a full 128-byte
     // row per thread; no atomics, the finishing kernel adds the key tiles' partials in a fixed order); after the last
@@ -1310,6 +1317,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
     const int lg = warp & 3, row = lg * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(lg * 32) << 16;
     const int npairs = nq * (nq + 1) / 2;
+    uint8_t* stage = smem + S::DQS + lg * 4096;
     if (warp != BWDF_E_WARPS) tl = nullptr;
     int blk = 0;
     for (int item = 0; item < n_items; item++) {
@@ -1327,20 +1335,26 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
         tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(bar_dqf);
-        bf16* dst = a.dq_part + (((size_t)b * npairs + (i * (i + 1) / 2 + kt)) * 128 + row) * C + h * HD;
+        // bf16 rows go through a swizzled staging tile and leave with ONE TMA store per warp: per-lane stores to 32
+        // different lines would occupy the load/store unit that the element-wise warps need at the same moment
+        if (lane == 0) tc::tma_wait_group_read<0>();      // the previous tile has been read out of the staging buffer
+        __syncwarp();
+        uint8_t* rowp = stage + lane * 128;
 #pragma unroll
-        for (int v = 0; v < 4; v++) {
-          uint4 w0, w1;
-          w0.x = pack_bf16(__uint_as_float(r0[v * 8 + 0]), __uint_as_float(r0[v * 8 + 1]));
-          w0.y = pack_bf16(__uint_as_float(r0[v * 8 + 2]), __uint_as_float(r0[v * 8 + 3]));
-          w0.z = pack_bf16(__uint_as_float(r0[v * 8 + 4]), __uint_as_float(r0[v * 8 + 5]));
-          w0.w = pack_bf16(__uint_as_float(r0[v * 8 + 6]), __uint_as_float(r0[v * 8 + 7]));
-          w1.x = pack_bf16(__uint_as_float(r1[v * 8 + 0]), __uint_as_float(r1[v * 8 + 1]));
-          w1.y = pack_bf16(__uint_as_float(r1[v * 8 + 2]), __uint_as_float(r1[v * 8 + 3]));
-          w1.z = pack_bf16(__uint_as_float(r1[v * 8 + 4]), __uint_as_float(r1[v * 8 + 5]));
-          w1.w = pack_bf16(__uint_as_float(r1[v * 8 + 6]), __uint_as_float(r1[v * 8 + 7]));
-          *reinterpret_cast<uint4*>(dst + v * 8) = w0;
-          *reinterpret_cast<uint4*>(dst + 32 + v * 8) = w1;
+        for (int v = 0; v < 8; v++) {
+          const uint32_t* src = (v < 4) ? &r0[v * 8] : &r1[(v - 4) * 8];
+          uint4 pk;
+          pk.x = pack_bf16(__uint_as_float(src[0]), __uint_as_float(src[1]));
+          pk.y = pack_bf16(__uint_as_float(src[2]), __uint_as_float(src[3]));
+          pk.z = pack_bf16(__uint_as_float(src[4]), __uint_as_float(src[5]));
+          pk.w = pack_bf16(__uint_as_float(src[6]), __uint_as_float(src[7]));
+          *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = pk;
+        }
+        tc::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tc::tma_store_2d(&tm_dq, stage, h * HD, (int)((((long)b * npairs + (i * (i + 1) / 2 + kt)) * 128) + lg * 32));
+          tc::tma_commit_group();
         }
         if (tl && warp == BWDF_E_WARPS) tl[blk * 8 + 7] = clock64();
       }
@@ -1354,6 +1368,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(bar_epi);
     }
+    if (lane == 0) tc::tma_wait_group<0>();     // every partial tile of this warp has been written
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -1750,11 +1765,14 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
     AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT, (bf16*)dq_part, 0, g_timeline};
     dim3 grid((T + 127) / 128, H, B);
     if (hd == 64 && dq_part != nullptr && ((uintptr_t)dq_part % 16 == 0)) {
-      // single fused kernel + dQ finish
+      // single fused kernel + dQ finish; the partial buffer is [B * nq(nq+1)/2 * 128 rows, C] bf16
+      const long nqh = (T + 127) / 128;
+      const CUtensorMap* tpart = mlb_tmap_cached(dq_part, (uint64_t)B * (nqh * (nqh + 1) / 2) * 128, C, C, 32, 64, 2);
+      if (!tpart) return -2;
       static int o0 = set_smem(attn_bwd_fused_tc_kernel, BwdFusedSmem::TOTAL);
       (void)o0;
       dim3 grid_f(((T + 127) / 128 + 1) / 2, H, B);   // a CTA handles a key tile and its mirror
-      mlb_launch(attn_bwd_fused_tc_kernel, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, a);
+      mlb_launch(attn_bwd_fused_tc_kernel, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
       const long groups = (long)B * T * H * (hd / 32);
       mlb_launch(attn_dq_finish_k, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, st, (bf16*)dqkv, (const bf16*)dq_part, (long)B * T, T, H, hd, scale, cosT, sinT);
       cudaError_t e = cudaGetLastError();
