@@ -406,6 +406,12 @@ def mode_bench_fsdp(argv):
     g.init_weights(1234)
     ids, tgt = bench_batch(B, cfg.T, cfg.V, rank)
     ids, tgt = ids.to(dev), tgt.to(dev)
+    if world > 1:
+        # ranks finish the host-side weight initialisation seconds apart; the peer-memory kernels bound their waits, so
+        # line the ranks up before the first step instead of spending that bound on start-up skew
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        dist.barrier()
     if rank == 0:
         print(f"FSDP world={world} per-GPU B={B} params={g.np / 1e6:.1f}M shard={f.master.numel() / 1e6:.1f}M comm={f.comm}")
     for _ in range(2):
@@ -429,6 +435,12 @@ def mode_bench_fsdp(argv):
         fl = flops_per_step(cfg, B) * world
         print(f"fsdp step {dt * 1e3:.2f} ms | global {B * cfg.T * world / dt:.0f} tok/s | {fl / dt / 1e12:.1f} TFLOP/s agg | "
               f"MFU {100 * fl / dt / (run.peak_tflops * 1e12 * world):.1f}% | loss {g.mean_loss():.4f}")
+    if dev.type == "cuda":
+        from .ops import native
+        err = native.get_error()
+        if err:
+            print(f"rank {rank}: kernel error word {err:#x} (a bounded wait expired or a kernel refused its arguments); "
+                  f"the numbers above are not valid")
     sys.stdout.flush()
     if world > 1:
         torch.cuda.synchronize()

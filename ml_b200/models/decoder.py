@@ -281,7 +281,16 @@ class GPT:
         B = self.B if B is None else B
         BT = B * self.cfg.T
         valid = valid_tokens if valid_tokens is not None else BT - B * n_pre
-        return float(self.losses[:BT].double().sum().item() / valid)
+        loss = float(self.losses[:BT].double().sum().item() / valid)
+        if self.losses.is_cuda:
+            # the readback above synchronised the device: this is where a kernel that gave up (a bounded wait that
+            # expired, arguments it refused) surfaces instead of a silently wrong loss
+            from ..ops import native
+            err = native.get_error()
+            if err:
+                raise RuntimeError(f"kernel error word {err:#x} (code {err >> 24}, detail {err & 0xFFFFFF:#x}); "
+                                   f"results since the last check are invalid")
+        return loss
 
     def flops_per_step(self, B=None) -> float:
         return flops_per_step(self.cfg, self.B if B is None else B)

@@ -188,7 +188,7 @@ def gemm(out, A, B, a_mn=False, b_mn=False, accumulate=False):
                         int(accumulate), _st()), "gemm")
 
 
-def linear_fwd_gather(out, x, N, K, unit_dst, w_off, src_table, shard_elems, world, flags, ctr, spin_limit_s=2.0):
+def linear_fwd_gather(out, x, N, K, unit_dst, w_off, src_table, shard_elems, world, flags, ctr, spin_limit_s=20.0):
     """out = x . W^T with W = unit_dst[w_off : w_off + N*K] viewed [N, K]; the same launch all-gathers the whole sharded
     unit into unit_dst from the ranks' shards (device pointer table `src_table`).  Cooperative launch."""
     L = lib()

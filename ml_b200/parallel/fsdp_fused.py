@@ -17,7 +17,7 @@ from .symm import PeerTable, empty as symm_empty
 
 
 class FusedFSDP:
-    def __init__(self, fs, gather_ctas: int = 32, rs_ctas: int = 64, spin_limit_s: float = 2.0):
+    def __init__(self, fs, gather_ctas: int = 32, rs_ctas: int = 64, spin_limit_s: float = 20.0):
         import os
         self.fs = fs
         self.gather_ctas = int(os.environ.get("ENTROPY_FSDP_GATHER_CTAS", gather_ctas))

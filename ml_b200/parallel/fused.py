@@ -18,7 +18,7 @@ MAX_BUCKETS = 64
 
 
 class FusedGradEngine:
-    def __init__(self, model, world: int, rank: int, group=None, ctas: int = 0, bcast: bool = True, spin_limit_s: float = 2.0,
+    def __init__(self, model, world: int, rank: int, group=None, ctas: int = 0, bcast: bool = True, spin_limit_s: float = 20.0,
                  overlap=None, buckets=None):
         """ctas: CTAs per bucket kernel (0 = policy below).  overlap: run bucket kernels on a side stream behind backward
         (ENTROPY_FUSED_OVERLAP=1).  Default off: measured on B200 with the 12-layer model, a few comm CTAs next to the
