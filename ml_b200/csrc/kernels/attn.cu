@@ -761,29 +761,30 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
 __global__ void attn_delta_k(float* __restrict__ delta, const bf16* __restrict__ dout, const bf16* __restrict__ out, int B, int T,
                              int H, int hd) {
   mlb_pdl_sync();
-  // one group of hd/8 consecutive lanes per (row, head): 16-byte loads, shuffle reduction inside the group
-  const int gsz = hd >> 3;  // lanes per head (8 for hd=64, 16 for hd=128); a power of two <= 32 on this path
-  const long gidx = ((long)blockIdx.x * blockDim.x + threadIdx.x) / gsz;
-  const int gl = threadIdx.x % gsz;
-  const long total = (long)B * T * H;
+  // one group of hd/8 consecutive lanes per (row, head): 16-byte loads, shuffle reduction inside the group.  The host
+  // launches this kernel only when B*T*H*hd/8 fits 31 bits, so all index arithmetic is 32-bit (a 64-bit division by
+  // a run-time value costs more instructions than the rest of the thread's work).
+  const unsigned gsz = (unsigned)hd >> 3;  // lanes per head (8 for hd=64, 16 for hd=128); a power of two <= 32 on this path
+  const unsigned tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned gidx = tid / gsz, gl = tid % gsz;
+  const unsigned total = (unsigned)B * T * H;
   float s = 0.f;
   if (gidx < total) {
-    const uint4 a = *reinterpret_cast<const uint4*>(out + gidx * hd + gl * 8);
-    const uint4 d = *reinterpret_cast<const uint4*>(dout + gidx * hd + gl * 8);
-    const bf162* pa = reinterpret_cast<const bf162*>(&a);
-    const bf162* pd = reinterpret_cast<const bf162*>(&d);
+    const size_t e = (size_t)gidx * hd + gl * 8;
+    const uint4 a = __ldcs(reinterpret_cast<const uint4*>(out + e));
+    const uint4 d = __ldcs(reinterpret_cast<const uint4*>(dout + e));
+    const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wd[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pd[i]);
-      s += x.x * y.x + x.y * y.y;
+      s = fmaf(__uint_as_float(wa[i] << 16), __uint_as_float(wd[i] << 16), s);
+      s = fmaf(__uint_as_float(wa[i] & 0xffff0000u), __uint_as_float(wd[i] & 0xffff0000u), s);
     }
   }
-  for (int o = gsz >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  for (unsigned o = gsz >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if (gidx < total && gl == 0) {
-    const int h = gidx % H;
-    const long bt = gidx / H;
-    const int b = bt / T, t = bt % T;
-    delta[((long)b * H + h) * T + t] = s;
+    const unsigned h = gidx % (unsigned)H, bt = gidx / (unsigned)H;
+    const unsigned b = bt / (unsigned)T, t = bt % (unsigned)T;
+    delta[((size_t)b * H + h) * T + t] = s;
   }
 }
 __global__ void attn_delta_scalar_k(float* __restrict__ delta, const bf16* __restrict__ dout, const bf16* __restrict__ out, int B,
@@ -1383,17 +1384,19 @@ __global__ void __launch_bounds__(256) attn_dq_finish_k(bf16* __restrict__ dqkv,
                                                         const float* __restrict__ sinT) {
   mlb_pdl_sync();
   const int h2 = hd >> 1, gph = h2 >> 4, gpr = H * gph;   // groups of 16 pairs per head / per row
-  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= rows * gpr) return;
-  const long r = idx / gpr;
-  const int g = idx % gpr, h = g / gph, v = g % gph;
-  const int t = r % T, C = H * hd;
-  const long b = r / T;
+  // rows * gpr fits 31 bits (checked by the host): 32-bit index arithmetic
+  const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (unsigned)rows * gpr) return;
+  const unsigned r = idx / (unsigned)gpr;
+  const int g = idx % (unsigned)gpr, h = g / gph, v = g % gph;
+  const int t = r % (unsigned)T, C = H * hd;
+  const long b = r / (unsigned)T;
   const int nq = (T + 127) / 128, npairs = nq * (nq + 1) / 2, i = t >> 7;
   const bf16* base = part + ((b * npairs + (long)i * (i + 1) / 2) * 128 + (t & 127)) * C + h * hd + v * 16;
   float x0[16], x1[16];
 #pragma unroll
   for (int k = 0; k < 16; k++) { x0[k] = 0.f; x1[k] = 0.f; }
+#pragma unroll 2
   for (int kt = 0; kt <= i; kt++) {
     const uint4* p0 = reinterpret_cast<const uint4*>(base + (long)kt * 128 * C);
     const uint4* p1 = reinterpret_cast<const uint4*>(base + (long)kt * 128 * C + h2);
@@ -1423,7 +1426,7 @@ __global__ void __launch_bounds__(256) attn_dq_finish_k(bf16* __restrict__ dqkv,
       }
     }
   }
-  bf16* o0 = dqkv + r * 3L * C + h * hd + v * 16;
+  bf16* o0 = dqkv + (long)r * 3L * C + h * hd + v * 16;
 #pragma unroll
   for (int i2 = 0; i2 < 2; i2++) {
     uint4 w0, w1;
@@ -1754,7 +1757,7 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
   {
     const long heads = (long)B * T * H;
     const int gsz = hd / 8;
-    const bool vec = (hd % 8 == 0) && gsz <= 32 && (gsz & (gsz - 1)) == 0 && ((uintptr_t)dout % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const bool vec = (hd % 8 == 0) && heads * gsz < (1L << 31) && gsz <= 32 && (gsz & (gsz - 1)) == 0 && ((uintptr_t)dout % 16 == 0) && ((uintptr_t)out % 16 == 0);
     if (vec) mlb_launch(attn_delta_k, dim3((unsigned)((heads * gsz + 255) / 256)), dim3(256), 0, st, delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
     else attn_delta_scalar_k<<<(unsigned)((heads * 32 + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
   }
@@ -1764,7 +1767,7 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
     if (!tq || !td) return -2;
     AttnArgs a{B, T, H, hd, scale, (bf16*)dqkv, const_cast<float*>(lse), delta, cosT, sinT, (bf16*)dq_part, 0, g_timeline};
     dim3 grid((T + 127) / 128, H, B);
-    if (hd == 64 && dq_part != nullptr && ((uintptr_t)dq_part % 16 == 0)) {
+    if (hd == 64 && dq_part != nullptr && ((uintptr_t)dq_part % 16 == 0) && (long)B * T * H * (hd / 32) < (1L << 31)) {
       // single fused kernel + dQ finish; the partial buffer is [B * nq(nq+1)/2 * 128 rows, C] bf16
       const long nqh = (T + 127) / 128;
       const CUtensorMap* tpart = mlb_tmap_cached(dq_part, (uint64_t)B * (nqh * (nqh + 1) / 2) * 128, C, C, 32, 64, 2);
