@@ -163,6 +163,7 @@ def bench_attn(a):
     qkv, out, lse, dout, dqkv = attn_tensors(B, T, H, hd)
     fl = 4.0 * B * H * T * T * hd / 2      # causal forward
     nat.lib().mlb_attn_fwd_mode(a.fwd_mode)
+    nat.lib().mlb_attn_fwd_balance(a.fwd_balance)
     t = timeit(lambda: nat.attn_fwd(out, lse, qkv, B, T, H, hd), a.iters, a.warm)
     tb = timeit(lambda: nat.attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd), a.iters, a.warm)
     q, k, v = [qkv.view(B, T, 3, H, hd)[:, :, i].permute(0, 2, 1, 3) for i in range(3)]
@@ -260,7 +261,8 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
-    ap.add_argument("--fwd-mode", type=int, default=1, help="attention forward, head size 64: 1/2 = thread-per-row kernel (2: tiles staggered), 0 = four threads per row")
+    ap.add_argument("--fwd-balance", type=int, default=1, help="attention forward over tile pairs: 1 = balanced work schedule from the host, 0 = round robin")
+    ap.add_argument("--fwd-mode", type=int, default=2, help="attention forward, head size 64: 1 = thread-per-row kernel, O folded into registers; 2 = O accumulated in TMEM with lazy rescale; 0 = four threads per row")
     ap.add_argument("--tile-order", type=int, default=0, help="pair GEMM static schedule: 0 = by operand size, 1 = M first, 2 = N first")
     ap.add_argument("--sk-groups", type=int, default=1, help="pair GEMM stream-K: 1 = clusters in groups that share the wide operand's k-range")
     ap.add_argument("--streamk", type=int, default=1, help="pair GEMM, weight gradients: 1 = equal k-block ranges per cluster, 0 = fixed split count")

@@ -14,6 +14,10 @@
 // RoPE's backward rotation of dQ/dK can be applied in the epilogue (each thread holds a full head row).
 // Head sizes other than 64/128 (or unaligned strides) use a plain SIMT implementation further down.
 #include "../tc.cuh"
+#include <algorithm>
+#include <mutex>
+#include <queue>
+#include <vector>
 
 MLB_DEFINE_ERROR_WORD(attn)
 
@@ -52,6 +56,8 @@ struct AttnArgs {
   bf16* dq_part;       // fused backward: dQ partial tiles [B][nq(nq+1)/2 (query tile i, key tile kt <= i)][128][C]
   int variant;         // forward tuning switch (see the kernel)
   long long* timeline; // optional: SM cycle stamps of CTA (0,0,0) of the fused backward, eight per (query block) step
+  const int* sched;    // forward over tile pairs: per CTA the work items in order, -1 terminated; nullptr = round robin
+  int sched_stride;    // entries per CTA in `sched`
 };
 
 // ================================================================== forward
@@ -460,7 +466,7 @@ struct Fwd2Step {   // one key block of one item in this CTA's flattened sequenc
   int w, li, p, b, h, nkb, j;
   bool valid;
   __device__ __forceinline__ void set_item(int w_, int li_, int total, int npair, int nq, int BH, int H) {
-    w = w_; li = li_; valid = w_ < total; j = 0;
+    w = w_; li = li_; valid = w_ >= 0 && w_ < total; j = 0;
     if (valid) {
       p = npair - 1 - w_ / BH;                 // heaviest pairs first
       const int bh = w_ % BH;
@@ -470,15 +476,18 @@ struct Fwd2Step {   // one key block of one item in this CTA's flattened sequenc
       p = b = h = 0; nkb = 1;
     }
   }
-  __device__ __forceinline__ void advance(int total, int npair, int nq, int BH, int H, int stride) {
+  template <class F>   // item_at(li): this CTA's li-th work item or -1
+  __device__ __forceinline__ void advance(F&& item_at, int total, int npair, int nq, int BH, int H) {
     if (!valid) return;
-    if (++j >= nkb) set_item(w + stride, li + 1, total, npair, nq, BH, H);
+    if (++j >= nkb) set_item(item_at(li + 1), li + 1, total, npair, nq, BH, H);
   }
 };
 
+template <int MODE>   // 1: O folded into registers every block | 2: O in TMEM, lazy rescale, two passes | 3: one pass
 __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
   mlb_pdl_sync();
   using S = Fwd2Smem;
+  constexpr bool LAZY = MODE >= 2;
   constexpr int HD = 64;
   constexpr uint32_t TMEM_COLS = 512;
   extern __shared__ uint8_t smem_raw[];
@@ -499,6 +508,14 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
   const int BH = a.B * a.H, total = npair * BH, stride = gridDim.x;
   const int C = a.H * HD;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // This CTA's sequence of work items (item w = pair p of (sample, head) bh, heaviest pairs first): from the host's
+  // balanced schedule if there is one, else round robin over the grid.  The rows of the schedule end with -1 entries.
+  const int* srow = a.sched ? a.sched + (size_t)blockIdx.x * a.sched_stride : nullptr;
+  auto item_at = [&](int li) -> int {
+    if (srow) return __ldg(srow + li);
+    const int x = blockIdx.x + li * stride;
+    return x < total ? x : -1;
+  };
 
   if (tid == 0) {
     for (int i = 0; i < 2; i++) {
@@ -538,16 +555,16 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
         tc::tma_load_2d(smem + S::V + (g % VN) * TILE_BYTES, &tm, &bar_v[g % VN], 2 * C + s.h * HD, s.b * a.T + s.j * 128);
       };
       Fwd2Step c0, c3;      // steps g and g + KN
-      c0.set_item(blockIdx.x, 0, total, npair, nq, BH, a.H);
+      c0.set_item(item_at(0), 0, total, npair, nq, BH, a.H);
       c3 = c0;
       if (c0.valid) {
         load_q(c0);
         Fwd2Step nx;
-        nx.set_item(blockIdx.x + stride, 1, total, npair, nq, BH, a.H);
+        nx.set_item(item_at(1), 1, total, npair, nq, BH, a.H);
         if (nx.valid) load_q(nx);          // the second item's Q goes into the other buffer right away
         for (int i = 0; i < KN; i++) {
           if (c3.valid) load_kv(c3, i);
-          c3.advance(total, npair, nq, BH, a.H, stride);
+          c3.advance(item_at, total, npair, nq, BH, a.H);
         }
       }
       for (int g = 0; c0.valid; g++) {
@@ -559,11 +576,11 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
         if (c0.j == c0.nkb - 1) {
           // this item's last scores have been consumed: its Q buffer takes the item after next
           Fwd2Step nx;
-          nx.set_item(c0.w + 2 * stride, c0.li + 2, total, npair, nq, BH, a.H);
+          nx.set_item(item_at(c0.li + 2), c0.li + 2, total, npair, nq, BH, a.H);
           if (nx.valid) load_q(nx);
         }
-        c0.advance(total, npair, nq, BH, a.H, stride);
-        c3.advance(total, npair, nq, BH, a.H, stride);
+        c0.advance(item_at, total, npair, nq, BH, a.H);
+        c3.advance(item_at, total, npair, nq, BH, a.H);
       }
     }
   } else if (warp == 8) {
@@ -575,10 +592,10 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
       const uint64_t dq0 = desc_base_k(tc::smem_u32(smem + S::Q)), dk0 = desc_base_k(tc::smem_u32(smem + S::K));
       const uint64_t dv0 = desc_base_mn(tc::smem_u32(smem + S::V));
       constexpr uint64_t TILE_D = TILE_BYTES >> 4;     // one tile further, in descriptor address units
-      int li = 0, j = 0, w = blockIdx.x;
+      int li = 0, j = 0, w = item_at(0), w_next = item_at(1);   // the next item's index is fetched an item ahead
       auto item_nkb = [&](int w_) { return min(2 * (npair - 1 - w_ / BH) + 2, nq); };
-      int nkb = w < total ? item_nkb(w) : 0;
-      bool valid = w < total;
+      bool valid = w >= 0;
+      int nkb = valid ? item_nkb(w) : 0;
       if (valid) {
         const bool ok0 = wait(&bar_q[0], 0, 60) && wait(&bar_k[0], 0, 61);
         for (int t = 0; t < 2; t++) {
@@ -593,8 +610,8 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
       for (int g = 0; valid; g++) {
         // next step: same item, or the first block of this CTA's next item
         int nli = li, nj = j + 1, nw = w;
-        if (nj >= nkb) { nli = li + 1; nj = 0; nw = w + stride; }
-        const bool has_next = nw < total;
+        if (nj >= nkb) { nli = li + 1; nj = 0; nw = w_next; }
+        const bool has_next = nw >= 0;
         bool next_ok = has_next;
         if (has_next) {
           next_ok = wait(&bar_k[(g + 1) % KN], ((g + 1) / KN) & 1, 62);
@@ -613,15 +630,19 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
             }
             tc::mma_commit(&bar_s[t]);
           }
-          if (go && g > 0) go = wait(&bar_of[t], (g - 1) & 1, 66);   // O_blk_t(g-1) has been folded
+          if constexpr (!LAZY) {
+            if (go && g > 0) go = wait(&bar_of[t], (g - 1) & 1, 66);   // O_blk_t(g-1) has been folded
+          }
           if (go && v_ok) {
             tc::tc_fence_after();
+            // LAZY: O accumulates in TMEM over the item's key blocks (the softmax warps rescale it in place when needed)
+            const bool acc0 = LAZY && j > 0;
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(tmem + 384 + t * HD, tmem + 256 + t * 64 + ks * 8, dvg + ks * 128, idesc_o, ks > 0);
+            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(tmem + 384 + t * HD, tmem + 256 + t * 64 + ks * 8, dvg + ks * 128, idesc_o, ks > 0 || acc0);
           }
           tc::mma_commit(&bar_o[t]);
         }
-        if (nj == 0 && has_next) nkb = item_nkb(nw);
+        if (nj == 0 && has_next) { nkb = item_nkb(nw); w_next = item_at(nli + 1); }
         li = nli; j = nj; w = nw; valid = has_next;
       }
     }
@@ -635,33 +656,148 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
     int g = 0;
     long long* tl = (a.timeline && blockIdx.x == 0 && tid == 0) ? a.timeline : nullptr;   // first 16 blocks of CTA 0, warp 0
     Fwd2Step it;
-    it.set_item(blockIdx.x, 0, total, npair, nq, BH, a.H);
-    for (; it.valid; it.set_item(it.w + stride, it.li + 1, total, npair, nq, BH, a.H)) {
+    it.set_item(item_at(0), 0, total, npair, nq, BH, a.H);
+    for (; it.valid; it.set_item(item_at(it.li + 1), it.li + 1, total, npair, nq, BH, a.H)) {
       const int qt = 2 * it.p + t, qrow = qt * 128 + row;
       float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-      float o[HD];
+      float o[LAZY ? 1 : HD];
 #pragma unroll
-      for (int i = 0; i < HD; i++) o[i] = 0.f;
+      for (int i = 0; i < (LAZY ? 1 : HD); i++) o[i] = 0.f;
       auto fold = [&](float alpha) {   // O = O * alpha + (P V) of the previous block
-        uint32_t r0[32], r1[32];
-        tc::tmem_ld32(t_o, r0);
-        tc::tmem_ld32(t_o + 32, r1);
-        tc::tmem_ld_wait();
-        tc::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&bar_of[t]);
+        if constexpr (!LAZY) {
+          uint32_t r0[32], r1[32];
+          tc::tmem_ld32(t_o, r0);
+          tc::tmem_ld32(t_o + 32, r1);
+          tc::tmem_ld_wait();
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&bar_of[t]);
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-          o[i] = o[i] * alpha + __uint_as_float(r0[i]);
-          o[32 + i] = o[32 + i] * alpha + __uint_as_float(r1[i]);
+          for (int i = 0; i < 32; i++) {
+            o[i] = o[i] * alpha + __uint_as_float(r0[i]);
+            o[32 + i] = o[32 + i] * alpha + __uint_as_float(r1[i]);
+          }
+        }
+      };
+      auto rescale = [&](float alpha) {   // LAZY: O (TMEM, sum over the blocks so far) *= alpha, in place
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          uint32_t r[32], w0[16], w1[16];
+          tc::tmem_ld32(t_o + c * 32, r);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            w0[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            w1[i] = __float_as_uint(__uint_as_float(r[16 + i]) * alpha);
+          }
+          tc::tmem_st16(t_o + c * 32, w0);
+          tc::tmem_st16(t_o + c * 32 + 16, w1);
         }
       };
       for (int j = 0; j < it.nkb; j++, g++) {
+        if constexpr (MODE == 3) {
+          // One pass per key block: exponentials against the reference maximum of an earlier block while the row
+          // maximum of this block is tracked next to them; only if some row of the warp has grown past the reference by
+          // more than 2^8 is the block redone the exact way (row maximum first, O and l rescaled, exponentials again).
+          // The first block of an item always takes the exact way.  j, qt and the votes are uniform over the warp.
+          if (tl && g < 16) tl[g * 8 + 0] = clock64();
+          wait(&bar_s[t], g & 1, 67);
+          tc::tc_fence_after();
+          if (tl && g < 16) tl[g * 8 + 1] = clock64();
+          const bool diag = (j == qt);
+          const int kc0 = j * 128;
+          bool p_free = (j == 0);        // P's columns are free once the previous block's P V has completed
+          auto free_p = [&]() {
+            if (!p_free) {
+              wait(&bar_o[t], (g - 1) & 1, 68);
+              tc::tc_fence_after();
+              p_free = true;
+            }
+          };
+          if (j > qt) {                  // past the diagonal: every key of this block is masked for every row of the tile
+            free_p();
+            uint32_t z[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) z[i] = 0u;
+#pragma unroll
+            for (int c = 0; c < 4; c++) tc::tmem_st16(t_p + c * 16, z);
+          } else {
+            bool exact = (j == 0);
+            for (int attempt = 0; attempt < 2; attempt++) {
+              if (exact) {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                  uint32_t r[32];
+                  tc::tmem_ld32(t_s + c * 32, r);
+                  tc::tmem_ld_wait();
+                  if (diag) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                      if (kc0 + c * 32 + i > qrow) r[i] = 0xff800000u;
+                  }
+#pragma unroll
+                  for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                }
+                const float m_new = fmaxf(m, mx * sl2);   // finite: key 0 is visible to every query
+                if (j > 0) {
+                  const float alpha = ex2_approx(m - m_new);
+                  l *= alpha;
+                  free_p();
+                  rescale(alpha);
+                }
+                m = m_new;
+              }
+              if (tl && g < 16) tl[g * 8 + 2] = clock64();
+              const uint64_t nm2 = pk2(-m, -m);
+              uint64_t rs2 = pk2(0.f, 0.f);
+              float mx = -INFINITY;
+#pragma unroll
+              for (int c = 0; c < 4; c++) {
+                uint32_t r[32], pw[16];
+                tc::tmem_ld32(t_s + c * 32, r);
+                tc::tmem_ld_wait();
+                if (diag) {
+#pragma unroll
+                  for (int i = 0; i < 32; i++)
+                    if (kc0 + c * 32 + i > qrow) r[i] = 0xff800000u;     // exp2(-inf) = 0
+                }
+#pragma unroll
+                for (int x = 0; x < 16; x++) {
+                  float z0, z1;
+                  mx = max3(mx, __uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
+                  upk2(fma2(pk2(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1])), sl2x2, nm2), z0, z1);
+                  const float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
+                  rs2 = add2(rs2, pk2(p0, p1));
+                  pw[x] = pack_bf16(p0, p1);
+                }
+                if (c == 0) free_p();
+                tc::tmem_st16(t_p + c * 16, pw);
+              }
+              if (!exact && __any_sync(0xffffffffu, mx * sl2 - m > 8.f)) {
+                exact = true;           // this attempt's P is overwritten and its row sum dropped
+                continue;
+              }
+              float rs_lo, rs_hi;
+              upk2(rs2, rs_lo, rs_hi);
+              l += rs_lo + rs_hi;
+              break;
+            }
+          }
+          if (tl && g < 16) tl[g * 8 + 3] = clock64();
+          tc::tmem_st_wait();
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&bar_p[t]);
+          if (tl && g < 16) tl[g * 8 + 4] = clock64();
+          continue;
+        }
         if (tl && g < 16) tl[g * 8 + 0] = clock64();
         wait(&bar_s[t], g & 1, 67);
         tc::tc_fence_after();
         if (tl && g < 16) tl[g * 8 + 1] = clock64();
         float alpha = 1.f;
+        bool resc = false;
         const bool masked = j > qt;      // past the diagonal: every key of this block is masked for every row of the tile
         const bool diag = (j == qt);
         const int kc0 = j * 128;
@@ -683,14 +819,33 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
             for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
           }
           m_new = fmaxf(m, mx * sl2);               // finite: key 0 is visible to every query
-          alpha = ex2_approx(m - m_new);            // exp2(-inf) = 0 on the first block
+          if constexpr (LAZY) {
+            // The exponentials keep the reference maximum of an earlier block while no row of this warp has grown past
+            // it by more than 2^8 (p <= 256 is harmless in bf16 / fp32); only then is O rescaled, for the whole warp
+            // (the TMEM accesses are warp-wide).  `masked` and j are the same for the whole warp.
+            if (j == 0) {
+              m = m_new;
+            } else if (__any_sync(0xffffffffu, m_new - m > 8.f)) {
+              resc = true;
+              alpha = ex2_approx(m - m_new);
+              l *= alpha;
+              m = m_new;
+            }
+            m_new = m;
+          } else {
+            alpha = ex2_approx(m - m_new);            // exp2(-inf) = 0 on the first block
+          }
         }
         if (tl && g < 16) tl[g * 8 + 2] = clock64();
         if (j > 0) {   // the previous block's P V has had the whole row-maximum pass to complete; P's columns are free after it
           wait(&bar_o[t], (g - 1) & 1, 68);
           tc::tc_fence_after();
           if (tl && g < 16) tl[g * 8 + 5] = clock64();
-          fold(alpha_prev);
+          if constexpr (LAZY) {
+            if (resc) rescale(alpha);
+          } else {
+            fold(alpha_prev);
+          }
           if (tl && g < 16) tl[g * 8 + 6] = clock64();
         }
         if (masked) {
@@ -724,7 +879,7 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
           }
           float rs_lo, rs_hi;
           upk2(rs2, rs_lo, rs_hi);
-          l = l * alpha + (rs_lo + rs_hi);
+          l = LAZY ? l + (rs_lo + rs_hi) : l * alpha + (rs_lo + rs_hi);
           m = m_new;
         }
         if (tl && g < 16) tl[g * 8 + 3] = clock64();
@@ -738,9 +893,30 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
       wait(&bar_o[t], (g - 1) & 1, 69);
       tc::tc_fence_after();
       fold(alpha_prev);
-      if (!*s_abort && qrow < a.T) {
-        const float inv = 1.f / l;
-        bf16* dst = a.out + ((size_t)(it.b * a.T + qrow)) * C + it.h * HD;
+      const float inv = 1.f / l;
+      const bool store = !*s_abort && qrow < a.T;
+      bf16* dst = a.out + ((size_t)(it.b * a.T + qrow)) * C + it.h * HD;
+      if constexpr (LAZY) {
+        // the accumulated O leaves TMEM here; the next item's first P V (accumulate off) is ordered behind these loads
+        // by this warp's arrival on bar_p for that block
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          uint32_t r[32];
+          tc::tmem_ld32(t_o + c * 32, r);
+          tc::tmem_ld_wait();
+          if (store) {
+#pragma unroll
+            for (int v8 = 0; v8 < 4; v8++) {
+              uint4 pk;
+              pk.x = pack_bf16(__uint_as_float(r[v8 * 8 + 0]) * inv, __uint_as_float(r[v8 * 8 + 1]) * inv);
+              pk.y = pack_bf16(__uint_as_float(r[v8 * 8 + 2]) * inv, __uint_as_float(r[v8 * 8 + 3]) * inv);
+              pk.z = pack_bf16(__uint_as_float(r[v8 * 8 + 4]) * inv, __uint_as_float(r[v8 * 8 + 5]) * inv);
+              pk.w = pack_bf16(__uint_as_float(r[v8 * 8 + 6]) * inv, __uint_as_float(r[v8 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + v8 * 8) = pk;
+            }
+          }
+        }
+      } else if (store) {
 #pragma unroll
         for (int v8 = 0; v8 < HD / 8; v8++) {
           uint4 pk;
@@ -748,6 +924,8 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
           pk.z = pack_bf16(o[v8 * 8 + 4] * inv, o[v8 * 8 + 5] * inv); pk.w = pack_bf16(o[v8 * 8 + 6] * inv, o[v8 * 8 + 7] * inv);
           *reinterpret_cast<uint4*>(dst + v8 * 8) = pk;
         }
+      }
+      if (store) {
         a.lse[((size_t)it.b * a.H + it.h) * a.T + qrow] = (m + log2f(l)) * LN2;
       }
     }
@@ -1680,7 +1858,7 @@ __global__ void attn_bwd_kv_simt_k(bf16* __restrict__ dqkv, const bf16* __restri
 }
 
 int g_attn_force_simt = 0;
-int g_fwd_rows = 1;   // head size 64: 1 = thread-per-row forward over tile pairs, 0 = four-threads-per-row forward
+int g_fwd_rows = 2;   // head size 64: 1 / 2 / 3 = thread-per-row forward over tile pairs (variants at the launch), 0 = four-threads-per-row forward
 
 template <typename K>
 int set_smem(K kern, int bytes) {
@@ -1703,6 +1881,57 @@ MLB_API void mlb_attn_fwd_mode(int rows) { g_fwd_rows = rows; }
 // block's MMAs were issued; first drain warp when the dQ partial was stored.  nullptr switches it off.
 MLB_API void mlb_attn_set_timeline(void* buf) { g_timeline = (long long*)buf; }
 
+// Balanced static schedule for the forward over tile pairs: work items (pair p of a (sample, head), heaviest first, cost
+// = its key blocks plus a fixed part for the Q load, pipeline refill and epilogue) go one by one to the CTA with the
+// least work so far.  Round robin leaves the slowest CTA with 30 key-block steps where the average is 26 (B=16, H=12,
+// T=1024, 148 CTAs); this assignment gets 26.  The table lives in device memory, one row of `stride` entries per CTA,
+// -1 terminated (with room for the loader's look-ahead of two items), cached per shape; it is built with a blocking
+// copy, so while the stream is being captured into a graph and the shape is new, nullptr is returned and the kernel
+// falls back to round robin.
+struct FwdSchedule { int dev, B, H, T, grid, stride; int* table; };
+static std::mutex g_sched_mu;
+static std::vector<FwdSchedule> g_sched;
+static int g_fwd_balance = 1;
+MLB_API void mlb_attn_fwd_balance(int on) { g_fwd_balance = on; }
+static const int* fwd_schedule(int B, int H, int T, int grid, int* stride_out, cudaStream_t st) {
+  if (!g_fwd_balance) return nullptr;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(g_sched_mu);
+  for (const FwdSchedule& e : g_sched)
+    if (e.dev == dev && e.B == B && e.H == H && e.T == T && e.grid == grid) { *stride_out = e.stride; return e.table; }
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
+  const int nq = (T + 127) / 128, npair = (nq + 1) / 2, BH = B * H, total = npair * BH;
+  std::vector<std::vector<int>> rows(grid);
+  using Bin = std::pair<long, int>;     // (work so far in half key blocks, CTA)
+  std::priority_queue<Bin, std::vector<Bin>, std::greater<Bin>> heap;
+  for (int c = 0; c < grid; c++) heap.push({0, c});
+  for (int w = 0; w < total; w++) {     // items are in descending cost order by construction
+    const int p = npair - 1 - w / BH;
+    const long cost = 2L * std::min(2 * p + 2, nq) + 1;
+    Bin b = heap.top();
+    heap.pop();
+    rows[b.second].push_back(w);
+    heap.push({b.first + cost, b.second});
+  }
+  size_t longest = 0;
+  for (const auto& r : rows) longest = std::max(longest, r.size());
+  const int stride = (int)longest + 3;
+  std::vector<int> host((size_t)grid * stride, -1);
+  for (int c = 0; c < grid; c++) std::copy(rows[c].begin(), rows[c].end(), host.begin() + (size_t)c * stride);
+  int* table = nullptr;
+  if (cudaMalloc(&table, host.size() * sizeof(int)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (cudaMemcpy(table, host.data(), host.size() * sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(table);
+    return nullptr;
+  }
+  g_sched.push_back({dev, B, H, T, grid, stride, table});
+  *stride_out = stride;
+  return table;
+}
+
 // out[B,T,C], lse[B,H,T] from qkv[B,T,3C].
 MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, int H, int hd, cudaStream_t st) {
   const int C = H * hd;
@@ -1718,10 +1947,17 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
     if (sms <= 0) sms = 148;
     dim3 grid((unsigned)(items < sms ? items : sms));   // persistent: one CTA per SM walks its share of the tiles
     if (hd == 64 && g_fwd_rows) {
-      static int once = set_smem(attn_fwd_rows_tc_kernel, Fwd2Smem::TOTAL);
+      // mode 1: O folded into registers every block; 2: O accumulated in TMEM, rescaled only when a row maximum grows by
+      // more than 2^8; 3: as 2 with the row maximum tracked inside the exponential pass (one pass per key block)
+      static int once = set_smem(attn_fwd_rows_tc_kernel<1>, Fwd2Smem::TOTAL) + set_smem(attn_fwd_rows_tc_kernel<2>, Fwd2Smem::TOTAL) +
+                        set_smem(attn_fwd_rows_tc_kernel<3>, Fwd2Smem::TOTAL);
       (void)once;
       const long pairs = (long)(((T + 127) / 128 + 1) / 2) * H * B;
-      mlb_launch(attn_fwd_rows_tc_kernel, dim3((unsigned)(pairs < sms ? pairs : sms)), dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
+      const dim3 grid2((unsigned)(pairs < sms ? pairs : sms));
+      a.sched = pairs > sms ? fwd_schedule(B, H, T, (int)grid2.x, &a.sched_stride, st) : nullptr;
+      if (g_fwd_rows == 3) mlb_launch(attn_fwd_rows_tc_kernel<3>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
+      else if (g_fwd_rows == 2) mlb_launch(attn_fwd_rows_tc_kernel<2>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
+      else mlb_launch(attn_fwd_rows_tc_kernel<1>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
     } else if (hd == 64) {
       static int once = set_smem(attn_fwd_tc_kernel<64>, FwdSmem<64>::TOTAL);
       (void)once;

@@ -41,6 +41,7 @@ def lib():
         "mlb_gemm_streamk_groups": [_i32],
         "mlb_attn_force_simt": [_i32],
         "mlb_attn_fwd_mode": [_i32],
+        "mlb_attn_fwd_balance": [_i32],
         "mlb_ce_mode": [_i32],
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
