@@ -261,8 +261,8 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
-    ap.add_argument("--fwd-balance", type=int, default=1, help="attention forward over tile pairs: 1 = balanced work schedule from the host, 0 = round robin")
-    ap.add_argument("--fwd-mode", type=int, default=2, help="attention forward, head size 64: 1 = thread-per-row kernel, O folded into registers; 2 = O accumulated in TMEM with lazy rescale; 0 = four threads per row")
+    ap.add_argument("--fwd-balance", type=int, default=1, help="persistent attention kernels: 1 = balanced work schedule from the host, 0 = round robin")
+    ap.add_argument("--fwd-mode", type=int, default=3, help="attention forward, head size 64: 1 = thread-per-row kernel, O folded into registers; 2 = O accumulated in TMEM with lazy rescale; 3 = 2 in one pass per key block; 0 = four threads per row")
     ap.add_argument("--tile-order", type=int, default=0, help="pair GEMM static schedule: 0 = by operand size, 1 = M first, 2 = N first")
     ap.add_argument("--sk-groups", type=int, default=1, help="pair GEMM stream-K: 1 = clusters in groups that share the wide operand's k-range")
     ap.add_argument("--streamk", type=int, default=1, help="pair GEMM, weight gradients: 1 = equal k-block ranges per cluster, 0 = fixed split count")

@@ -58,6 +58,7 @@ struct AttnArgs {
   long long* timeline; // optional: SM cycle stamps of CTA (0,0,0) of the fused backward, eight per (query block) step
   const int* sched;    // forward over tile pairs: per CTA the work items in order, -1 terminated; nullptr = round robin
   int sched_stride;    // entries per CTA in `sched`
+  int out_tma;         // forward over tile pairs: O leaves through a staging tile and TMA stores (needs T % 128 == 0)
 };
 
 // ================================================================== forward
@@ -440,25 +441,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
 }
 
 // ================================================================== forward, head size 64: one thread per query row
-// A CTA works on PAIRS of 128-query tiles of one (sample, head): tile 0 is owned by warps 0-3, tile 1 by warps 4-7
-// (thread = one query row: no cross-thread reductions, no shared-memory exchange), warp 8 issues every TMA load and MMA.
-// Per key block j and tile t:   S_t = Q_t K_j^T (TMEM) -> row max, p = exp2(s*c - m) in 32-column chunks straight out of
-// TMEM -> P_t written as packed bf16 into its own TMEM columns (the A operand of the next MMA never touches shared
-// memory, and the next block's scores can be issued before P_t V_j) -> O_blk = P_t V_j -> folded into the row's 64 fp32
-// accumulators in registers with the usual running-max rescale.
+// A persistent CTA works on PAIRS of 128-query tiles of one (sample, head): tile 0 is owned by warps 0-3, tile 1 by
+// warps 4-7 (thread = one query row: no cross-thread reductions, no shared-memory exchange), warp 8 issues every MMA,
+// warp 9 every TMA load.  Per key block j and tile t:   S_t = Q_t K_j^T (TMEM) -> p = exp2(s*c - m) in 32-column chunks
+// straight out of TMEM -> P_t written as packed bf16 into its own TMEM columns (the A operand of the next MMA never
+// touches shared memory, and the next block's scores can be issued before P_t V_j) -> O_t += P_t V_j.
+// Where O lives and what m is depends on the variant (template MODE):
+//   1  O_blk = P V is folded into 64 fp32 registers per row after every block with the usual running-max rescale;
+//   2  O accumulates in TMEM over the item's blocks; m is the maximum of an EARLIER block as long as no row of the warp
+//      has grown past it by more than 2^8 (then p <= 256, harmless in bf16 / fp32), and only when one has are O (in
+//      place, TMEM load / multiply / store) and l rescaled - rare after the first blocks;
+//   3  as 2, but the row maximum is tracked inside the exponential pass and a block is redone the exact way when the
+//      threshold is passed (the default: one TMEM read of the scores per block instead of two).
 // The two tiles share K_j / V_j (one load per 256 queries) and run out of phase: while one tile's threads compute
 // exponentials the tensor core works for the other tile.  Both tiles walk the same key blocks; the block past tile
 // 0's diagonal is fully masked for it (its threads write P = 0 without computing anything).
-// mbarriers per tile: bar_s S complete (commit) | bar_p P stored (4 warps) | bar_o O_blk complete (commit) |
-// bar_of O_blk folded (4 warps).  K has 2 slots, V 3: block g+2 is fetched as soon as both tiles have consumed S(g),
-// which (in-order tensor pipe) also means P V of block g-1 has finished.
+// A CTA's items come from a balanced schedule built on the host (attn_schedule), the finished O rows leave through a
+// swizzled staging tile and one TMA store per warp.
+// mbarriers per tile: bar_s S complete (commit) | bar_p P stored (4 warps) | bar_o P V complete (commit) |
+// bar_of O_blk folded (4 warps, mode 1 only).  K has 3 slots, V 4: block g+3 is fetched as soon as both tiles have
+// consumed S(g), which (in-order tensor pipe) also means P V of block g-1 has finished.
 struct Fwd2Smem {
   static constexpr int Q = 0;                          // 2 buffers x 2 tiles
   static constexpr int KN = 3;                         // K slots; V has one more
   static constexpr int K = Q + 4 * TILE_BYTES;
   static constexpr int V = K + KN * TILE_BYTES;
-  static constexpr int BAR = V + (KN + 1) * TILE_BYTES;
-  static constexpr int TOTAL = BAR + 256 + 1024;
+  static constexpr int OST = V + (KN + 1) * TILE_BYTES;   // O staging: 8 warps x [32 rows x 128 B] bf16, swizzled
+  static constexpr int BAR = OST + 2 * TILE_BYTES;
+  static constexpr int SCHED = BAR + 256;                 // this CTA's first 64 work items
+  static constexpr int TOTAL = SCHED + 256 + 1024;
 };
 constexpr int FWD2_THREADS = 10 * 32;   // 8 softmax warps, MMA warp, loader warp
 
@@ -483,8 +494,13 @@ struct Fwd2Step {   // one key block of one item in this CTA's flattened sequenc
   }
 };
 
-template <int MODE>   // 1: O folded into registers every block | 2: O in TMEM, lazy rescale, two passes | 3: one pass
-__global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const AttnArgs a) {
+// MODE 1: O folded into registers every block | 2: O in TMEM, lazy rescale, two passes | 3: the same in one pass.
+// (Measured without gain on top of mode 3 and taken out again: the next chunk's TMEM load in flight during the current
+// chunk's arithmetic; 4, 6 or 8 of every 16 exponential pairs as a cubic on the FMA pipe instead of the special-function
+// unit - equal, 5 % and 10 % slower.)
+template <int MODE>
+__global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tm_out,
+                                                                           const AttnArgs a) {
   mlb_pdl_sync();
   using S = Fwd2Smem;
   constexpr bool LAZY = MODE >= 2;
@@ -511,8 +527,10 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
   // This CTA's sequence of work items (item w = pair p of (sample, head) bh, heaviest pairs first): from the host's
   // balanced schedule if there is one, else round robin over the grid.  The rows of the schedule end with -1 entries.
   const int* srow = a.sched ? a.sched + (size_t)blockIdx.x * a.sched_stride : nullptr;
+  int* s_sched = (int*)(smem + S::SCHED);     // the row's first 64 entries: a global load at an item boundary stalls
+  if (srow && tid < 64) s_sched[tid] = tid < a.sched_stride ? __ldg(srow + tid) : -1;   // its warp for a DRAM latency
   auto item_at = [&](int li) -> int {
-    if (srow) return __ldg(srow + li);
+    if (srow) return li < 64 ? s_sched[li] : __ldg(srow + li);
     const int x = blockIdx.x + li * stride;
     return x < total ? x : -1;
   };
@@ -527,6 +545,7 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
     *s_abort = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tm);
+    tc::tma_prefetch_desc(&tm_out);
   }
   if (warp == 8) tc::tmem_alloc(tmem_slot, TMEM_COLS);
   tc::tc_fence_before();
@@ -654,7 +673,8 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
     const float sl2 = a.scale * LOG2E;
     const uint64_t sl2x2 = pk2(sl2, sl2);
     int g = 0;
-    long long* tl = (a.timeline && blockIdx.x == 0 && tid == 0) ? a.timeline : nullptr;   // first 16 blocks of CTA 0, warp 0
+    // first 16 blocks of CTA 0: thread 0 (tile 0) and thread 128 (tile 1), 8 stamps per block, tile 1 behind tile 0's 128
+    long long* tl = (a.timeline && blockIdx.x == 0 && (tid & 127) == 0) ? a.timeline + (tid >> 7) * 128 : nullptr;
     Fwd2Step it;
     it.set_item(item_at(0), 0, total, npair, nq, BH, a.H);
     for (; it.valid; it.set_item(item_at(it.li + 1), it.li + 1, total, npair, nq, BH, a.H)) {
@@ -723,14 +743,19 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
             for (int c = 0; c < 4; c++) tc::tmem_st16(t_p + c * 16, z);
           } else {
             bool exact = (j == 0);
+            auto for_chunks = [&](auto&& fn) {   // fn(c, r): chunk c of this row's 128 scores in r[32]
+#pragma unroll
+              for (int c = 0; c < 4; c++) {
+                uint32_t r[32];
+                tc::tmem_ld32(t_s + c * 32, r);
+                tc::tmem_ld_wait();
+                fn(c, r);
+              }
+            };
             for (int attempt = 0; attempt < 2; attempt++) {
               if (exact) {
                 float mx = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                  uint32_t r[32];
-                  tc::tmem_ld32(t_s + c * 32, r);
-                  tc::tmem_ld_wait();
+                for_chunks([&](int c, uint32_t (&r)[32]) {
                   if (diag) {
 #pragma unroll
                     for (int i = 0; i < 32; i++)
@@ -738,7 +763,7 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
                   }
 #pragma unroll
                   for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                }
+                });
                 const float m_new = fmaxf(m, mx * sl2);   // finite: key 0 is visible to every query
                 if (j > 0) {
                   const float alpha = ex2_approx(m - m_new);
@@ -748,15 +773,11 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
                 }
                 m = m_new;
               }
-              if (tl && g < 16) tl[g * 8 + 2] = clock64();
               const uint64_t nm2 = pk2(-m, -m);
               uint64_t rs2 = pk2(0.f, 0.f);
               float mx = -INFINITY;
-#pragma unroll
-              for (int c = 0; c < 4; c++) {
-                uint32_t r[32], pw[16];
-                tc::tmem_ld32(t_s + c * 32, r);
-                tc::tmem_ld_wait();
+              for_chunks([&](int c, uint32_t (&r)[32]) {
+                uint32_t pw[16];
                 if (diag) {
 #pragma unroll
                   for (int i = 0; i < 32; i++)
@@ -773,7 +794,8 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
                 }
                 if (c == 0) free_p();
                 tc::tmem_st16(t_p + c * 16, pw);
-              }
+                if (tl && g < 16) tl[g * 8 + 2 + c] = clock64();     // mode 3: stamps 2..5 = chunks done
+              });
               if (!exact && __any_sync(0xffffffffu, mx * sl2 - m > 8.f)) {
                 exact = true;           // this attempt's P is overwritten and its row sum dropped
                 continue;
@@ -784,12 +806,11 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
               break;
             }
           }
-          if (tl && g < 16) tl[g * 8 + 3] = clock64();
           tc::tmem_st_wait();
           tc::tc_fence_before();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(&bar_p[t]);
-          if (tl && g < 16) tl[g * 8 + 4] = clock64();
+          if (tl && g < 16) tl[g * 8 + 6] = clock64();
           continue;
         }
         if (tl && g < 16) tl[g * 8 + 0] = clock64();
@@ -898,22 +919,36 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
       bf16* dst = a.out + ((size_t)(it.b * a.T + qrow)) * C + it.h * HD;
       if constexpr (LAZY) {
         // the accumulated O leaves TMEM here; the next item's first P V (accumulate off) is ordered behind these loads
-        // by this warp's arrival on bar_p for that block
+        // by this warp's arrival on bar_p for that block.  With whole tiles (T a multiple of 128) the bf16 rows go
+        // through a swizzled staging tile and leave with one TMA store per warp: a store instruction whose lanes hit 32
+        // different lines keeps the load/store unit busy for tens of cycles, eight of them per thread.
+        uint8_t* stage = smem + S::OST + warp * 4096;
+        if (a.out_tma) {
+          if (lane == 0) tc::tma_wait_group_read<0>();      // the previous item's rows have been read out of the staging tile
+          __syncwarp();
+        }
 #pragma unroll
         for (int c = 0; c < 2; c++) {
           uint32_t r[32];
           tc::tmem_ld32(t_o + c * 32, r);
           tc::tmem_ld_wait();
-          if (store) {
 #pragma unroll
-            for (int v8 = 0; v8 < 4; v8++) {
-              uint4 pk;
-              pk.x = pack_bf16(__uint_as_float(r[v8 * 8 + 0]) * inv, __uint_as_float(r[v8 * 8 + 1]) * inv);
-              pk.y = pack_bf16(__uint_as_float(r[v8 * 8 + 2]) * inv, __uint_as_float(r[v8 * 8 + 3]) * inv);
-              pk.z = pack_bf16(__uint_as_float(r[v8 * 8 + 4]) * inv, __uint_as_float(r[v8 * 8 + 5]) * inv);
-              pk.w = pack_bf16(__uint_as_float(r[v8 * 8 + 6]) * inv, __uint_as_float(r[v8 * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + c * 32 + v8 * 8) = pk;
-            }
+          for (int v8 = 0; v8 < 4; v8++) {
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(r[v8 * 8 + 0]) * inv, __uint_as_float(r[v8 * 8 + 1]) * inv);
+            pk.y = pack_bf16(__uint_as_float(r[v8 * 8 + 2]) * inv, __uint_as_float(r[v8 * 8 + 3]) * inv);
+            pk.z = pack_bf16(__uint_as_float(r[v8 * 8 + 4]) * inv, __uint_as_float(r[v8 * 8 + 5]) * inv);
+            pk.w = pack_bf16(__uint_as_float(r[v8 * 8 + 6]) * inv, __uint_as_float(r[v8 * 8 + 7]) * inv);
+            if (a.out_tma) *reinterpret_cast<uint4*>(stage + lane * 128 + (((c * 4 + v8) ^ (lane & 7)) << 4)) = pk;
+            else if (store) *reinterpret_cast<uint4*>(dst + c * 32 + v8 * 8) = pk;
+          }
+        }
+        if (a.out_tma) {
+          tc::fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && !*s_abort && qt * 128 < a.T) {   // (an odd number of query tiles leaves the last pair's second tile empty)
+            tc::tma_store_2d(&tm_out, stage, it.h * HD, it.b * a.T + qt * 128 + lg * 32);
+            tc::tma_commit_group();
           }
         }
       } else if (store) {
@@ -928,7 +963,9 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const
       if (store) {
         a.lse[((size_t)it.b * a.H + it.h) * a.T + qrow] = (m + log2f(l)) * LN2;
       }
+      if (tl && g <= 16) tl[(g - 1) * 8 + 7] = clock64();     // stamp 7 of an item's last block: its epilogue is done
     }
+    if (lane == 0) tc::tma_wait_group<0>();     // this warp's TMA stores of O have completed before the CTA's shared memory goes
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -1195,8 +1232,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kv_tc_kernel(const __
 }
 
 // ================================================================== backward, head size 64: ONE kernel, five GEMMs
-// One CTA per 128-key tile (and its mirror tile, so every CTA walks nq+1 query blocks) loops over the query tiles
-// i >= its own.  Per query block:
+// Persistent CTAs, one per SM; a work item is one 128-key tile of a (sample, head) and loops over the query tiles
+// i >= its own; the items of a CTA come from a balanced schedule built on the host (attn_schedule).  Per query block:
 //     S^T = K Q^T, dP^T = V dO^T                            (two MMAs into TMEM)
 //     P^T = exp2(S^T*c - lse), dS^T = P^T (dP^T - delta)    (512 threads, packed f32x2 math)
 //     dV += P^T dO   (P^T stays in TMEM as the bf16 A operand),   dK += dS^T Q,   dQ_i = dS K   (dS^T in shared memory)
@@ -1222,7 +1259,8 @@ struct BwdFusedSmem {
   static constexpr int DQS = DST + 4 * TILE_BYTES;       // dQ staging: 4 drain warps x [32 rows x 128 B] bf16, swizzled
   static constexpr int STAT = DQS + TILE_BYTES;          // 8 warps x (-lse*log2e [64], -delta [64])
   static constexpr int BAR = STAT + 4096;
-  static constexpr int TOTAL = BAR + 256 + 1024;
+  static constexpr int SCHED = BAR + 256;                // this CTA's first 64 work items
+  static constexpr int TOTAL = SCHED + 256 + 1024;
 };
 
 constexpr int BWDF_E_WARPS = 8;       // element-wise warps: TMEM lane group (w & 3) x 64-query column half (w >> 2)
@@ -1255,12 +1293,30 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
     if (s_skip != 0) return;
   }
   const int nq = (a.T + 127) / 128;
-  const int kt_first = blockIdx.x, kt_second = nq - 1 - (int)blockIdx.x;
-  const int n_items = (kt_second != kt_first) ? 2 : 1;
-  const int h = blockIdx.y, b = blockIdx.z;
   const int C = a.H * HD;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = b * a.T;
+  // Persistent CTAs: work item w = key tile kt = w / (B*H) of (sample, head) w % (B*H), so the items are in descending
+  // cost order (a key tile meets the nq - kt query tiles at or after it).  A CTA's items come from the host's balanced
+  // schedule (rows end with -1 entries; the first 64 are copied to shared memory), else round robin over the grid.
+  const int BH = a.B * a.H, total = nq * BH;
+  const int* srow = a.sched ? a.sched + (size_t)blockIdx.x * a.sched_stride : nullptr;
+  int* s_sched = (int*)(smem + S::SCHED);
+  if (srow && tid < 64) s_sched[tid] = tid < a.sched_stride ? __ldg(srow + tid) : -1;
+  struct Item { int kt, b, h, row0; bool valid; };
+  auto item_at = [&](int li) -> Item {
+    int w;
+    if (srow) w = li < 64 ? s_sched[li] : __ldg(srow + li);
+    else { w = blockIdx.x + li * gridDim.x; if (w >= total) w = -1; }
+    Item r;
+    r.valid = w >= 0;
+    if (!r.valid) w = 0;
+    r.kt = w / BH;
+    const int bh = w - r.kt * BH;
+    r.b = bh / a.H;
+    r.h = bh - r.b * a.H;
+    r.row0 = r.b * a.T;
+    return r;
+  };
 
   if (tid == 0) {
     tc::mbar_init(bar_kv, 1);
@@ -1286,42 +1342,47 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
     if (!tc::mbar_wait_sleep(bar, phase, where)) { *s_abort = 1; return false; }
     return true;
   };
-  long long* tl = (a.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) ? a.timeline : nullptr;
+  long long* tl = (a.timeline && blockIdx.x == 0 && lane == 0) ? a.timeline : nullptr;
 
   if (warp == BWDF_LOAD_WARP) {
     // ---------------------------------------------------------------- loader warp: every TMA load
     if (lane == 0) {
-      auto load_kv = [&](int kt) {
+      auto load_kv = [&](const Item& w) {
         tc::mbar_expect_tx(bar_kv, 2 * TILE_BYTES);
-        tc::tma_load_2d(smem + S::K, &tm_qkv, bar_kv, C + h * HD, row0 + kt * 128);
-        tc::tma_load_2d(smem + S::V, &tm_qkv, bar_kv, 2 * C + h * HD, row0 + kt * 128);
+        tc::tma_load_2d(smem + S::K, &tm_qkv, bar_kv, C + w.h * HD, w.row0 + w.kt * 128);
+        tc::tma_load_2d(smem + S::V, &tm_qkv, bar_kv, 2 * C + w.h * HD, w.row0 + w.kt * 128);
       };
-      auto load_q_do = [&](int i, int g) {          // g: running block number, buffer g % 3
+      auto load_q_do = [&](const Item& w, int i, int g) {          // g: running block number, buffer g % 3
         const int buf = g % 3;
         tc::mbar_expect_tx(&bar_q[buf], 2 * TILE_BYTES);
-        tc::tma_load_2d(smem + S::Q + buf * TILE_BYTES, &tm_qkv, &bar_q[buf], h * HD, row0 + i * 128);
-        tc::tma_load_2d(smem + S::DO + buf * TILE_BYTES, &tm_do, &bar_q[buf], h * HD, row0 + i * 128);
+        tc::tma_load_2d(smem + S::Q + buf * TILE_BYTES, &tm_qkv, &bar_q[buf], w.h * HD, w.row0 + i * 128);
+        tc::tma_load_2d(smem + S::DO + buf * TILE_BYTES, &tm_do, &bar_q[buf], w.h * HD, w.row0 + i * 128);
       };
       int blk = 0;
-      load_kv(kt_first);
-      load_q_do(kt_first, 0);
-      if (nq - kt_first > 1) load_q_do(kt_first + 1, 1);
-      for (int item = 0; item < n_items; item++) {
-        const int kt = item == 0 ? kt_first : kt_second;
+      Item cur = item_at(0);
+      if (cur.valid) {
+        load_kv(cur);
+        load_q_do(cur, cur.kt, 0);
+        if (nq - cur.kt > 1) load_q_do(cur, cur.kt + 1, 1);
+      }
+      for (int li = 0; cur.valid; li++) {
+        const int kt = cur.kt;
         const int n_it = nq - kt;
         for (int it = 0; it < n_it; it++, blk++) {
           // the tiles of block it+2 go where block it-1's were: its dV / dK MMAs must have finished reading them
           // (every completion of bar_d is observed, so this thread's parity never falls a whole period behind)
           if (blk > 0) wait(bar_d, (blk - 1) & 1, 43);
-          if (it + 2 < n_it) load_q_do(kt + it + 2, blk + 2);
+          if (it + 2 < n_it) load_q_do(cur, kt + it + 2, blk + 2);
         }
-        if (item + 1 < n_items) {
-          // every MMA of this key tile is complete: K, V and all Q / dO buffers are free for the mirror tile
+        const Item nx = item_at(li + 1);
+        if (nx.valid) {
+          // every MMA of this key tile is complete: K, V and all Q / dO buffers are free for the next item
           wait(bar_d, (blk - 1) & 1, 44);
-          load_kv(kt_second);
-          load_q_do(kt_second, blk);
-          if (nq - kt_second > 1) load_q_do(kt_second + 1, blk + 1);
+          load_kv(nx);
+          load_q_do(nx, nx.kt, blk);
+          if (nq - nx.kt > 1) load_q_do(nx, nx.kt + 1, blk + 1);
         }
+        cur = nx;
       }
     }
   } else if (warp == BWDF_CTRL_WARP) {
@@ -1348,9 +1409,10 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
         for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, dVk + ks * 2, dDOk + o + ks * 2, idesc_s, ks > 0);
       };
       int blk = 0, buf = 0, q_use = 0;     // buffer blk % 3 and how many times it has been filled before (blk / 3)
-      for (int item = 0; item < n_items; item++) {
-        const int kt = item == 0 ? kt_first : kt_second;
-        const int n_it = nq - kt;
+      for (int item = 0;; item++) {
+        const Item cur = item_at(item);
+        if (!cur.valid) break;
+        const int n_it = nq - cur.kt;
         if (wait(bar_kv, item & 1, 40)) issue_scores(buf, q_use & 1);
         tc::mma_commit(bar_s);
         for (int it = 0; it < n_it; it++, blk++) {
@@ -1398,22 +1460,24 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
     // (-lse*log2e, -delta; queries past the end give P = 0).  Lane l fetches queries l and l+32 of the NEXT block while
     // this block is processed, so neither the load latency nor a CTA-wide barrier sits between two blocks.
     float* my_stat = s_stat + warp * 128;
-    auto fetch_stat = [&](int i, float (&l)[2], float (&d)[2]) {
+    auto fetch_stat = [&](const Item& w, int i, float (&l)[2], float (&d)[2]) {
 #pragma unroll
       for (int u = 0; u < 2; u++) {
         const int q = i * 128 + ch * 64 + u * 32 + lane;
-        const size_t si = ((size_t)b * a.H + h) * a.T + q;
+        const size_t si = ((size_t)w.b * a.H + w.h) * a.T + q;
         l[u] = (q < a.T) ? a.lse[si] : INFINITY;
         d[u] = (q < a.T) ? a.delta[si] : 0.f;
       }
     };
     int blk = 0;
-    for (int item = 0; item < n_items; item++) {
-      const int kt = item == 0 ? kt_first : kt_second;
+    for (int item = 0;; item++) {
+      const Item cur = item_at(item);
+      if (!cur.valid) break;
+      const int kt = cur.kt;
       const int k0 = kt * 128, krow = k0 + row;
       const int n_it = nq - kt;
       float st_l[2], st_d[2];
-      fetch_stat(kt, st_l, st_d);
+      fetch_stat(cur, kt, st_l, st_d);
       for (int it = 0; it < n_it; it++, blk++) {
         const int i = kt + it, q0 = i * 128;
         __syncwarp();
@@ -1423,7 +1487,7 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
           my_stat[64 + u * 32 + lane] = -st_d[u];
         }
         __syncwarp();
-        if (it + 1 < n_it) fetch_stat(i + 1, st_l, st_d);
+        if (it + 1 < n_it) fetch_stat(cur, i + 1, st_l, st_d);
         if (tl && warp == 0) tl[blk * 8 + 0] = clock64();
         wait(bar_s, blk & 1, 48);          // S^T, dP^T of this block are complete
         tc::tc_fence_after();
@@ -1499,8 +1563,10 @@ __global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(cons
     uint8_t* stage = smem + S::DQS + lg * 4096;
     if (warp != BWDF_E_WARPS) tl = nullptr;
     int blk = 0;
-    for (int item = 0; item < n_items; item++) {
-      const int kt = item == 0 ? kt_first : kt_second;
+    for (int item = 0;; item++) {
+      const Item cur = item_at(item);
+      if (!cur.valid) break;
+      const int kt = cur.kt, b = cur.b, h = cur.h, row0 = cur.row0;
       const int krow = kt * 128 + row;
       const int n_it = nq - kt;
       for (int it = 0; it < n_it; it++, blk++) {
@@ -1858,7 +1924,7 @@ __global__ void attn_bwd_kv_simt_k(bf16* __restrict__ dqkv, const bf16* __restri
 }
 
 int g_attn_force_simt = 0;
-int g_fwd_rows = 2;   // head size 64: 1 / 2 / 3 = thread-per-row forward over tile pairs (variants at the launch), 0 = four-threads-per-row forward
+int g_fwd_rows = 3;   // head size 64: 1 / 2 / 3 = thread-per-row forward over tile pairs (variants at the launch), 0 = four-threads-per-row forward
 
 template <typename K>
 int set_smem(K kern, int bytes) {
@@ -1881,35 +1947,40 @@ MLB_API void mlb_attn_fwd_mode(int rows) { g_fwd_rows = rows; }
 // block's MMAs were issued; first drain warp when the dQ partial was stored.  nullptr switches it off.
 MLB_API void mlb_attn_set_timeline(void* buf) { g_timeline = (long long*)buf; }
 
-// Balanced static schedule for the forward over tile pairs: work items (pair p of a (sample, head), heaviest first, cost
-// = its key blocks plus a fixed part for the Q load, pipeline refill and epilogue) go one by one to the CTA with the
-// least work so far.  Round robin leaves the slowest CTA with 30 key-block steps where the average is 26 (B=16, H=12,
-// T=1024, 148 CTAs); this assignment gets 26.  The table lives in device memory, one row of `stride` entries per CTA,
-// -1 terminated (with room for the loader's look-ahead of two items), cached per shape; it is built with a blocking
-// copy, so while the stream is being captured into a graph and the shape is new, nullptr is returned and the kernel
-// falls back to round robin.
-struct FwdSchedule { int dev, B, H, T, grid, stride; int* table; };
+// Balanced static schedules for the persistent attention kernels.  Work items (forward: pair p of a (sample, head);
+// backward: key tile kt of a (sample, head); both numbered so that the cost falls with the item number; cost = the item's
+// 128x128 blocks plus a fixed part for loads, pipeline refill and epilogue) go one by one to the CTA with the least work
+// so far.  Forward, B=16 H=12 T=1024, 148 CTAs: round robin leaves the slowest CTA with 30 key-block steps where the
+// average is 26, this assignment gets 26.  Backward: 768 equal CTAs of 9 blocks each ran as 5.2 waves (54 blocks on the
+// slowest SM); 1536 single-tile items scheduled this way give 47.  The table lives in device memory, one row of `stride`
+// entries per CTA, -1 terminated (with room for a look-ahead of two items), cached per shape; it is built with a
+// blocking copy, so while the stream is being captured into a graph and the shape is new, nullptr is returned and the
+// kernels fall back to round robin.
+struct AttnSchedule { int kind, dev, B, H, T, grid, stride; int* table; };
 static std::mutex g_sched_mu;
-static std::vector<FwdSchedule> g_sched;
+static std::vector<AttnSchedule> g_sched;
 static int g_fwd_balance = 1;
-MLB_API void mlb_attn_fwd_balance(int on) { g_fwd_balance = on; }
-static const int* fwd_schedule(int B, int H, int T, int grid, int* stride_out, cudaStream_t st) {
+MLB_API void mlb_attn_fwd_balance(int on) { g_fwd_balance = on; }   // (both directions)
+static const int* attn_schedule(int kind /*0 forward pairs, 1 backward key tiles*/, int B, int H, int T, int grid, int* stride_out,
+                                cudaStream_t st) {
   if (!g_fwd_balance) return nullptr;
   int dev = 0;
   cudaGetDevice(&dev);
   std::lock_guard<std::mutex> lk(g_sched_mu);
-  for (const FwdSchedule& e : g_sched)
-    if (e.dev == dev && e.B == B && e.H == H && e.T == T && e.grid == grid) { *stride_out = e.stride; return e.table; }
+  for (const AttnSchedule& e : g_sched)
+    if (e.kind == kind && e.dev == dev && e.B == B && e.H == H && e.T == T && e.grid == grid) { *stride_out = e.stride; return e.table; }
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
-  const int nq = (T + 127) / 128, npair = (nq + 1) / 2, BH = B * H, total = npair * BH;
+  const int nq = (T + 127) / 128, npair = (nq + 1) / 2, BH = B * H;
+  const int total = (kind == 0 ? npair : nq) * BH;
   std::vector<std::vector<int>> rows(grid);
-  using Bin = std::pair<long, int>;     // (work so far in half key blocks, CTA)
+  using Bin = std::pair<long, int>;     // (work so far in quarter blocks, CTA)
   std::priority_queue<Bin, std::vector<Bin>, std::greater<Bin>> heap;
   for (int c = 0; c < grid; c++) heap.push({0, c});
   for (int w = 0; w < total; w++) {     // items are in descending cost order by construction
-    const int p = npair - 1 - w / BH;
-    const long cost = 2L * std::min(2 * p + 2, nq) + 1;
+    long cost;
+    if (kind == 0) cost = 4L * std::min(2 * (npair - 1 - w / BH) + 2, nq) + 2;
+    else cost = 4L * (nq - w / BH) + 3;
     Bin b = heap.top();
     heap.pop();
     rows[b.second].push_back(w);
@@ -1927,7 +1998,7 @@ static const int* fwd_schedule(int B, int H, int T, int grid, int* stride_out, c
     cudaFree(table);
     return nullptr;
   }
-  g_sched.push_back({dev, B, H, T, grid, stride, table});
+  g_sched.push_back({kind, dev, B, H, T, grid, stride, table});
   *stride_out = stride;
   return table;
 }
@@ -1949,15 +2020,24 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
     if (hd == 64 && g_fwd_rows) {
       // mode 1: O folded into registers every block; 2: O accumulated in TMEM, rescaled only when a row maximum grows by
       // more than 2^8; 3: as 2 with the row maximum tracked inside the exponential pass (one pass per key block)
-      static int once = set_smem(attn_fwd_rows_tc_kernel<1>, Fwd2Smem::TOTAL) + set_smem(attn_fwd_rows_tc_kernel<2>, Fwd2Smem::TOTAL) +
-                        set_smem(attn_fwd_rows_tc_kernel<3>, Fwd2Smem::TOTAL);
-      (void)once;
       const long pairs = (long)(((T + 127) / 128 + 1) / 2) * H * B;
       const dim3 grid2((unsigned)(pairs < sms ? pairs : sms));
-      a.sched = pairs > sms ? fwd_schedule(B, H, T, (int)grid2.x, &a.sched_stride, st) : nullptr;
-      if (g_fwd_rows == 3) mlb_launch(attn_fwd_rows_tc_kernel<3>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
-      else if (g_fwd_rows == 2) mlb_launch(attn_fwd_rows_tc_kernel<2>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
-      else mlb_launch(attn_fwd_rows_tc_kernel<1>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, a);
+      a.sched = pairs > sms ? attn_schedule(0, B, H, T, (int)grid2.x, &a.sched_stride, st) : nullptr;
+      const CUtensorMap* to = (T % 128 == 0 && g_fwd_rows >= 2) ? mlb_tmap_cached(out, (uint64_t)B * T, C, C, 32, 64, 2) : nullptr;
+      a.out_tma = to != nullptr;
+      if (!to) to = tm;      // unused by the kernel then
+#define MLB_FWD2(MODE)                                                                                                             \
+  {                                                                                                                            \
+    static int once = set_smem(attn_fwd_rows_tc_kernel<MODE>, Fwd2Smem::TOTAL);                                          \
+    (void)once;                                                                                                                \
+    mlb_launch(attn_fwd_rows_tc_kernel<MODE>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, *to, a);              \
+  }
+      switch (g_fwd_rows) {
+        case 1: MLB_FWD2(1) break;
+        case 2: MLB_FWD2(2) break;
+        default: MLB_FWD2(3) break;
+      }
+#undef MLB_FWD2
     } else if (hd == 64) {
       static int once = set_smem(attn_fwd_tc_kernel<64>, FwdSmem<64>::TOTAL);
       (void)once;
@@ -2010,7 +2090,14 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
       if (!tpart) return -2;
       static int o0 = set_smem(attn_bwd_fused_tc_kernel, BwdFusedSmem::TOTAL);
       (void)o0;
-      dim3 grid_f(((T + 127) / 128 + 1) / 2, H, B);   // a CTA handles a key tile and its mirror
+      // persistent CTAs, one per SM, over the (key tile, sample, head) items
+      int sms = 0, devid = 0;
+      cudaGetDevice(&devid);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devid);
+      if (sms <= 0) sms = 148;
+      const long n_items = nqh * H * B;
+      dim3 grid_f((unsigned)(n_items < sms ? n_items : sms));
+      a.sched = n_items > sms ? attn_schedule(1, B, H, T, (int)grid_f.x, &a.sched_stride, st) : nullptr;
       mlb_launch(attn_bwd_fused_tc_kernel, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
       const long groups = (long)B * T * H * (hd / 32);
       mlb_launch(attn_dq_finish_k, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, st, (bf16*)dqkv, (const bf16*)dq_part, (long)B * T, T, H, hd, scale, cosT, sinT);

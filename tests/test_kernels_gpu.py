@@ -205,14 +205,15 @@ def test_attn_fwd_variants_hd64(B, T, H, hd, rows, qscale):
     try:
         nat().attn_fwd(out, lse, qkv, B, T, H, hd)
     finally:
-        nat().lib().mlb_attn_fwd_mode(2)
+        nat().lib().mlb_attn_fwd_mode(3)
     eo, el = torch.empty(B * T, C, device=dev()), torch.empty(B, H, T, device=dev())
     ref.attn_fwd(eo, el, qkv, B, T, H, hd)
     close(out, eo, name="attn out")
     close(lse, el, rtol=1e-3, atol=2e-2, name="attn lse")
 
 
-@pytest.mark.parametrize("B,T,H,hd", ATTN_CASES)
+# the last two cases have more work items than the GPU has SMs: the persistent kernels walk the host's balanced schedule
+@pytest.mark.parametrize("B,T,H,hd", ATTN_CASES + [(4, 1024, 12, 64), (3, 640, 13, 64)])
 def test_attn_fwd_bwd(B, T, H, hd, bwd_mode):
     if hd != 64 and not bwd_mode:
         pytest.skip("only one backward implementation for this head size")
