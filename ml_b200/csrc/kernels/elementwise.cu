@@ -463,6 +463,59 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, 
   }
 }
 
+// ------------------------------------------------------------------ cross-entropy over vocabulary chunks
+// The LM head's logits exist only one [rows, n] chunk at a time (columns off .. off+n of the vocabulary).
+// ce_chunk_stats_k folds a chunk into the running per-row maximum m, sum s = sum exp(z - m) and target logit zt
+// (train/gpt_kernels.cuh:1244-1277); after the last chunk the row's loss is log(s) + m - zt.
+// ce_chunk_grad_k turns a recomputed chunk into dlogits = (exp(z - m) / s - onehot) * dscale in place and writes the
+// loss (train/gpt_kernels.cuh:1279-1299).  Rows with tgt < 0: loss 0, zero gradient.  One block per row.
+__global__ void __launch_bounds__(256) ce_chunk_stats_k(float* __restrict__ rowmax, float* __restrict__ rowsum,
+                                                        float* __restrict__ tgt_logit, const bf16* __restrict__ chunk,
+                                                        const int* __restrict__ tgt, int n, long ld, int off) {
+  __shared__ float red[32];
+  const long row = blockIdx.x;
+  const int t = tgt[row];
+  if (t < 0) return;                    // (uniform over the block)
+  const bf16* z = chunk + row * ld;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float x = __bfloat162float(z[i]);
+    if (x > m) { s *= __expf(m - x); m = x; }
+    s += __expf(x - m);
+  }
+  const float M = block_max(m, red);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - M);
+  const float S = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const float m0 = rowmax[row], s0 = rowsum[row];
+    const float mn = fmaxf(m0, M);
+    rowsum[row] = ((m0 == -INFINITY) ? 0.f : s0 * __expf(m0 - mn)) + S * __expf(M - mn);
+    rowmax[row] = mn;
+    if (t >= off && t < off + n) tgt_logit[row] = __bfloat162float(z[t - off]);
+  }
+}
+__global__ void __launch_bounds__(256) ce_chunk_grad_k(float* __restrict__ losses, bf16* __restrict__ chunk,
+                                                       const int* __restrict__ tgt, const float* __restrict__ rowmax,
+                                                       const float* __restrict__ rowsum, const float* __restrict__ tgt_logit,
+                                                       int n, long ld, int off, float dscale) {
+  const long row = blockIdx.x;
+  const int t = tgt[row];
+  bf16* z = chunk + row * ld;
+  if (t < 0) {
+    if (threadIdx.x == 0) losses[row] = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) z[i] = __float2bfloat16(0.f);
+    return;
+  }
+  const float M = rowmax[row], S = rowsum[row];
+  if (threadIdx.x == 0) losses[row] = __logf(S) + M - tgt_logit[row];
+  const float inv = dscale / S;
+  const int tl = t - off;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float x = __bfloat162float(z[i]);
+    z[i] = __float2bfloat16(__expf(x - M) * inv - ((i == tl) ? dscale : 0.f));
+  }
+}
+
 // Same result with ONE exponential per logit (the two-pass kernel above spends 2 x rows x V of them and is limited by
 // the special-function unit, not by memory): the row is parked in shared memory.
 //   pass 1  global -> shared (raw bf16) + row maximum            (no exponential)
@@ -785,6 +838,18 @@ MLB_API int mlb_ce_fwd_bwd(float* losses, void* logits, const int* tgt, long row
     LAUNCH_RET;
   }
   mlb_launch(ce_fwd_bwd_k, dim3((unsigned)rows), dim3(threads), 0, st, losses, (bf16*)logits, tgt, V, ld, dscale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_ce_chunk_stats(float* rowmax, float* rowsum, float* tgt_logit, const void* chunk, const int* tgt, long rows, int n,
+                               long ld, int off, cudaStream_t st) {
+  if (rows <= 0 || n <= 0) return 0;
+  ce_chunk_stats_k<<<(unsigned)rows, 256, 0, st>>>(rowmax, rowsum, tgt_logit, (const bf16*)chunk, tgt, n, ld, off);
+  LAUNCH_RET;
+}
+MLB_API int mlb_ce_chunk_grad(float* losses, void* chunk, const int* tgt, const float* rowmax, const float* rowsum,
+                              const float* tgt_logit, long rows, int n, long ld, int off, float dscale, cudaStream_t st) {
+  if (rows <= 0 || n <= 0) return 0;
+  ce_chunk_grad_k<<<(unsigned)rows, 256, 0, st>>>(losses, (bf16*)chunk, tgt, rowmax, rowsum, tgt_logit, n, ld, off, dscale);
   LAUNCH_RET;
 }
 MLB_API int mlb_adamw(float* master, void* params, const float* grads, float* m, float* v, long n, float lr, float b1, float b2,

@@ -30,14 +30,20 @@ FUSE_ROPE_INTO_QKV = _os.environ.get("MLB_NO_ROPE_FUSE", "0") != "1"
 
 class GPT:
     def __init__(self, cfg: Config, B: int, device="cpu", dtype: Optional[torch.dtype] = None,
-                 opt_state: bool = True, alloc_grads: bool = True, alloc=None, sharded: bool = False):
+                 opt_state: bool = True, alloc_grads: bool = True, alloc=None, sharded: bool = False,
+                 lmce_chunk: Optional[int] = None):
         """alloc(numel, dtype) -> flat tensor: optional allocator for the parameter and gradient buffers (the
         data-parallel engines pass a symmetric-memory allocator so peers can address them).
         sharded=True: no flat master / params / grads / m / v are allocated here; a sharding engine
-        (ml_b200.parallel.fsdp) owns the storage and serves parameter / gradient views through `self.res`."""
+        (ml_b200.parallel.fsdp) owns the storage and serves parameter / gradient views through `self.res`.
+        lmce_chunk > 0 (default: ENTROPY_LMCE_CHUNK): the LM head and its cross-entropy run over vocabulary chunks of
+        that many columns inside backward, and the [B*T, V] logits buffer is never allocated (train/gpt.cu:221-239,396-445)."""
         cfg.validate()
         self.cfg = cfg
         self.B = B
+        if lmce_chunk is None:
+            lmce_chunk = int(_os.environ.get("ENTROPY_LMCE_CHUNK", "0") or 0)
+        self.lmce_chunk = max(0, min(int(lmce_chunk), cfg.V))
         self.device = torch.device(device)
         if dtype is None:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
@@ -84,7 +90,14 @@ class GPT:
         self.lse = [f(B, c.H, c.T) for _ in range(Lh)]
         self.lnf_out = e(BT, C)
         self.rstdf = f(BT)
-        self.logits = e(BT, V)
+        if self.lmce_chunk > 0:
+            # chunked LM head: one [BT, chunk] logits tile, running softmax statistics, fp32 accumulator of d(lnf_out)
+            self.logits = None
+            self.logits_chunk = e(BT * self.lmce_chunk)
+            self.ce_rowmax, self.ce_rowsum, self.ce_tgt_logit = f(BT), f(BT), f(BT)
+            self.dln_accum = f(BT, C)
+        else:
+            self.logits = e(BT, V)
         self.losses = f(BT)
         # scratch
         self.proj = e(BT, C)
@@ -194,6 +207,8 @@ class GPT:
             ops.add_rmsnorm_fwd(sl(self.resid2[l]), nout, nrstd, sl(self.resid1[l]), proj, nw, c.eps)
             resid_in = sl(self.resid2[l])
             self._mark("F_mlp+norm")
+        if self.lmce_chunk > 0:
+            return None          # the head runs chunk by chunk inside backward; no logits are materialised
         if "head" not in self.skip:
             ops.linear_fwd(self.logits[:BT], sl(self.lnf_out), self.P(Lo.off_lm, c.V, C))
         self._mark("F_lmhead")
@@ -221,13 +236,17 @@ class GPT:
         if d_out is not None:
             dresid.copy_(d_out)
         else:
-            logits = self.logits[:BT]
-            ops.ce_fwd_bwd(sl(self.losses), logits, tgt, 1.0 / float(valid))
-            self._mark("B_ce")
-            self._pre("head", "bwd")
-            ops.linear_dw(self.G(Lo.off_lm, V, C), logits, sl(self.lnf_out))
-            ops.linear_dx(dln, logits, self.P(Lo.off_lm, V, C))
-            self._mark("B_lmhead")
+            if self.lmce_chunk > 0:
+                self._pre("head", "bwd")
+                self._lmhead_ce_backward_chunked(tgt, BT, valid, dln)
+            else:
+                logits = self.logits[:BT]
+                ops.ce_fwd_bwd(sl(self.losses), logits, tgt, 1.0 / float(valid))
+                self._mark("B_ce")
+                self._pre("head", "bwd")
+                ops.linear_dw(self.G(Lo.off_lm, V, C), logits, sl(self.lnf_out))
+                ops.linear_dx(dln, logits, self.P(Lo.off_lm, V, C))
+                self._mark("B_lmhead")
             last = sl(self.resid2[c.L - 1]) if c.L > 0 else sl(self.x0)
             ops.rmsnorm_bwd(dresid, self.G(Lo.off_lnf, C), dln, last, self.P(Lo.off_lnf, C), sl(self.rstdf), None)
             self._mark("B_norm")
@@ -266,6 +285,40 @@ class GPT:
         self._pre("wte", "bwd")
         ops.embed_bwd(self.G(Lo.off_wte, V, C), dresid, ids, T, n_pre)
         self._hook("wte", Lo.off_wte, V * C)
+
+    def _lmhead_ce_backward_chunked(self, tgt, BT, valid, dln):
+        """LM head + cross-entropy over vocabulary chunks (train/gpt.cu:396-445): pass 1 computes each chunk of logits
+        and folds it into per-row running max / sum-exp / target logit; pass 2 recomputes each chunk, turns it into
+        dlogits in place, and feeds the two gradient GEMMs (dW of the chunk's rows of the head weight; d(lnf_out)
+        accumulated in fp32 over the chunks, then rounded once to the activation dtype).  Costs one extra LM-head forward;
+        saves the [B*T, V] logits buffer."""
+        c, Lo = self.cfg, self.layout
+        V, C, ch = c.V, c.C, self.lmce_chunk
+        x = self.lnf_out[:BT]
+        W, dW = self.P(Lo.off_lm, V, C), self.G(Lo.off_lm, V, C)
+        m, s, zt = self.ce_rowmax[:BT], self.ce_rowsum[:BT], self.ce_tgt_logit[:BT]
+        m.fill_(float("-inf"))
+        s.zero_()
+        zt.zero_()
+        tile = lambda n: self.logits_chunk[:BT * n].view(BT, n)
+        for off in range(0, V, ch):
+            n = min(ch, V - off)
+            ops.linear_fwd(tile(n), x, W[off:off + n])
+            ops.ce_chunk_stats(m, s, zt, tile(n), tgt, off)
+        self._mark("B_lmce_stats")
+        acc = self.dln_accum[:BT]
+        acc.zero_()
+        for off in range(0, V, ch):
+            n = min(ch, V - off)
+            ops.linear_fwd(tile(n), x, W[off:off + n])
+            ops.ce_chunk_grad(self.losses[:BT], tile(n), tgt, m, s, zt, off, 1.0 / float(valid))
+            ops.linear_dw(dW[off:off + n], tile(n), x)
+            ops.gemm(acc, tile(n), W[off:off + n], False, True, True)
+        if dln.dtype == acc.dtype:
+            dln.copy_(acc)
+        else:
+            ops.cast(dln, acc)
+        self._mark("B_lmce_grad")
 
     # ------------------------------------------------------------------ optimizer / loss
     def adamw(self, lr, b1=0.9, b2=0.95, eps=1e-8, wd=0.1, t=1, grad_scale=1.0, off=0, n=None, dev_hyper=None):

@@ -9,8 +9,8 @@ _NAMES = [
     "embed_fwd", "embed_bwd", "set_prefix", "gather_prefix_grad",
     "rmsnorm_fwd", "add_rmsnorm_fwd", "rmsnorm_bwd",
     "rope_fwd", "rope_bwd", "swiglu_fwd", "swiglu_bwd",
-    "linear_fwd", "linear_dx", "linear_dw", "attn_fwd", "attn_bwd",
-    "ce_fwd_bwd", "adamw", "patchify", "add_posembed", "posembed_grad", "residual_add", "cast",
+    "linear_fwd", "linear_dx", "linear_dw", "gemm", "attn_fwd", "attn_bwd",
+    "ce_fwd_bwd", "ce_chunk_stats", "ce_chunk_grad", "adamw", "patchify", "add_posembed", "posembed_grad", "residual_add", "cast",
 ]
 
 _native_mod = None

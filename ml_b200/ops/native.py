@@ -58,6 +58,8 @@ def lib():
         "mlb_swiglu_fwd": [_vp, _vp, _i64, _i32, _vp],
         "mlb_swiglu_bwd": [_vp, _vp, _vp, _i64, _i32, _vp],
         "mlb_ce_fwd_bwd": [_vp, _vp, _vp, _i64, _i32, _i64, _f32, _i32, _vp],
+        "mlb_ce_chunk_stats": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _i32, _vp],
+        "mlb_ce_chunk_grad": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _i32, _f32, _vp],
         "mlb_adamw": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp],
         "mlb_cast_f2b": [_vp, _vp, _i64, _f32, _vp],
         "mlb_cast_b2f": [_vp, _vp, _i64, _f32, _vp],
@@ -293,6 +295,18 @@ def ce_fwd_bwd(losses, logits, tgt, dscale, V_valid=None, threads=512):
     rows, V = logits.shape
     _chk(lib().mlb_ce_fwd_bwd(_f(losses), _b(logits), _i(tgt), rows, V if V_valid is None else V_valid, logits.stride(0),
                               dscale, threads, _st()), "ce_fwd_bwd")
+
+
+def ce_chunk_stats(rowmax, rowsum, tgt_logit, chunk, tgt, off):
+    rows, n = chunk.shape
+    _chk(lib().mlb_ce_chunk_stats(_f(rowmax), _f(rowsum), _f(tgt_logit), _b(chunk), _i(tgt), rows, n, chunk.stride(0), off, _st()),
+         "ce_chunk_stats")
+
+
+def ce_chunk_grad(losses, chunk, tgt, rowmax, rowsum, tgt_logit, off, dscale):
+    rows, n = chunk.shape
+    _chk(lib().mlb_ce_chunk_grad(_f(losses), _b(chunk), _i(tgt), _f(rowmax), _f(rowsum), _f(tgt_logit), rows, n, chunk.stride(0),
+                                 off, dscale, _st()), "ce_chunk_grad")
 
 
 def adamw(master, params, grads, m, v, lr, b1, b2, eps, wd, bc1, bc2, grad_scale=1.0, dev_hyper=None):

@@ -132,6 +132,17 @@ def linear_dw(dW, dout, x):
     dW.add_(_f(dout).t() @ _f(x))
 
 
+def gemm(out, A, B, a_mn=False, b_mn=False, accumulate=False):
+    """D[M,N] = sum_k A(m,k) B(n,k); A is [M,K] or, with a_mn, stored [K,M]; B is [N,K] or, with b_mn, stored [K,N].
+    `out` is overwritten, or (accumulate, fp32) added to."""
+    a = _f(A).t() if a_mn else _f(A)
+    b = _f(B) if b_mn else _f(B).t()
+    if accumulate:
+        out.add_(a @ b)
+    else:
+        out.copy_(a @ b)
+
+
 # ------------------------------------------------------------------ attention
 def attn_fwd(out, lse, qkv, B, T, H, hd):
     """Causal SDPA reading Q/K/V strided from qkv[B,T,3C]; out[B,T,C]; lse[B,H,T] = log-sum-exp of the
@@ -189,6 +200,39 @@ def ce_fwd_bwd(losses, logits, tgt, dscale, V_valid=None):
     p = p * dscale
     p[~valid] = 0
     logits.copy_(p)
+
+
+def ce_chunk_stats(rowmax, rowsum, tgt_logit, chunk, tgt, off):
+    """Folds columns off .. off+n of the vocabulary (chunk[rows, n]) into the running per-row maximum, sum of
+    exp(z - max) and target logit (train/gpt_kernels.cuh:1244-1277).  Rows with tgt < 0 are left alone."""
+    z = _f(chunk)
+    n = z.shape[1]
+    valid = tgt >= 0
+    mc = z.max(-1).values
+    mn = torch.maximum(rowmax, mc)
+    old = torch.where(torch.isinf(rowmax), torch.zeros_like(rowsum), rowsum * torch.exp(rowmax - mn))
+    new_s = old + torch.exp(z - mn[:, None]).sum(-1)
+    inside = valid & (tgt >= off) & (tgt < off + n)
+    zt = z.gather(1, (tgt.long() - off).clamp(0, n - 1)[:, None])[:, 0]
+    rowsum.copy_(torch.where(valid, new_s, rowsum))
+    rowmax.copy_(torch.where(valid, mn, rowmax))
+    tgt_logit.copy_(torch.where(inside, zt, tgt_logit))
+
+
+def ce_chunk_grad(losses, chunk, tgt, rowmax, rowsum, tgt_logit, off, dscale):
+    """chunk <- (exp(z - max) / sum - onehot) * dscale for the vocabulary columns off .. off+n, and losses = log(sum) +
+    max - target logit (train/gpt_kernels.cuh:1279-1299); rows with tgt < 0: loss 0, zero gradient."""
+    z = _f(chunk)
+    n = z.shape[1]
+    valid = tgt >= 0
+    p = torch.exp(z - rowmax[:, None]) / rowsum[:, None]
+    inside = valid & (tgt >= off) & (tgt < off + n)
+    idx = (tgt.long() - off).clamp(0, n - 1)[:, None]
+    p.scatter_add_(1, idx, -inside.to(p.dtype)[:, None])
+    p = p * dscale
+    p[~valid] = 0
+    chunk.copy_(p)
+    losses.copy_(torch.where(valid, torch.log(rowsum) + rowmax - tgt_logit, torch.zeros_like(rowsum)))
 
 
 # ------------------------------------------------------------------ AdamW

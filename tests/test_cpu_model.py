@@ -146,3 +146,50 @@ def test_module_tree_autograd_matches_engine():
     assert abs(loss.item() - g.mean_loss(valid_tokens=valid)) < 1e-5
     for p, off in m.named_flat():
         assert (p.grad.flatten() - g.grads[off:off + p.numel()]).abs().max() < 2e-5
+
+
+def test_chunked_lm_head_ce_matches_full_logits():
+    """ENTROPY_LMCE_CHUNK semantics (train/gpt.cu:396-445): the LM head + cross-entropy over vocabulary chunks gives the
+    loss and every gradient of the path with materialised logits; chunk sizes that divide V, that do not, and one chunk;
+    ignored rows included."""
+    import pytest
+    cfg = Config(V=97, C=48, L=2, H=4, I=80, T=16)
+    B = 3
+    ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+    tgt[::5] = -1
+    valid = int((tgt >= 0).sum())
+    full = GPT(cfg, B, lmce_chunk=0)
+    full.init_weights(1234)
+    full.forward(ids)
+    full.backward(ids, tgt, valid_tokens=valid)
+    for chunk in (32, 97, 50, 1000):
+        g = GPT(cfg, B, lmce_chunk=chunk)
+        assert g.logits is None and g.lmce_chunk == min(chunk, cfg.V)
+        g.init_weights(1234)
+        assert g.forward(ids) is None
+        g.backward(ids, tgt, valid_tokens=valid)
+        assert g.mean_loss(valid_tokens=valid) == pytest.approx(full.mean_loss(valid_tokens=valid), rel=1e-5)
+        assert torch.allclose(g.losses, full.losses, atol=2e-5, rtol=1e-5)
+        assert torch.allclose(g.grads, full.grads, atol=2e-6, rtol=1e-4), (g.grads - full.grads).abs().max()
+
+
+def test_chunk_ce_ops_match_fused_ce():
+    """ce_chunk_stats / ce_chunk_grad over the chunks of a logits matrix reproduce ce_fwd_bwd on the whole matrix."""
+    from ml_b200.ops import ref
+    torch.manual_seed(3)
+    rows, V = 37, 101
+    z = torch.randn(rows, V) * 3
+    tgt = torch.randint(0, V, (rows,), dtype=torch.int32)
+    tgt[::7] = -1
+    exp_l, exp_d = torch.empty(rows), z.clone()
+    ref.ce_fwd_bwd(exp_l, exp_d, tgt, 0.25)
+    m, s, zt = torch.full((rows,), float("-inf")), torch.zeros(rows), torch.zeros(rows)
+    for off in range(0, V, 24):
+        ref.ce_chunk_stats(m, s, zt, z[:, off:off + 24].contiguous(), tgt, off)
+    losses, d = torch.empty(rows), torch.empty_like(z)
+    for off in range(0, V, 24):
+        c = z[:, off:off + 24].contiguous()
+        ref.ce_chunk_grad(losses, c, tgt, m, s, zt, off, 0.25)
+        d[:, off:off + 24] = c
+    assert torch.allclose(losses, exp_l, atol=1e-5)
+    assert torch.allclose(d, exp_d, atol=1e-6)

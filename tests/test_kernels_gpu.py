@@ -353,6 +353,38 @@ def _check_cross_entropy(rows, V):
     assert (a[::4] == 0).all() and (la[::4] == 0).all()
 
 
+@pytest.mark.parametrize("rows,V,chunk", [(64, 1024, 256), (37, 1000, 384), (5, 130, 130), (33, 257, 64)])
+def test_cross_entropy_over_vocabulary_chunks(rows, V, chunk):
+    """ce_chunk_stats / ce_chunk_grad (the LM head without a [rows, V] logits buffer) against the fp32 oracle of the same
+    two ops, and against the fused whole-row cross-entropy: widths that divide V and that do not, ignored rows."""
+    torch.manual_seed(13)
+    logits = rnd(rows, V, scale=3.0)
+    tgt = torch.randint(0, V, (rows,), device=dev(), dtype=torch.int32)
+    tgt[::4] = -1
+    dscale = 1.0 / 29
+    mk = lambda: (torch.full((rows,), float("-inf"), device=dev()), torch.zeros(rows, device=dev()), torch.zeros(rows, device=dev()))
+    m, s, zt = mk()
+    em, es, ezt = mk()
+    for off in range(0, V, chunk):
+        c = logits[:, off:off + chunk].clone()     # (a full-width slice is the tensor itself)
+        nat().ce_chunk_stats(m, s, zt, c, tgt, off)
+        ref.ce_chunk_stats(em, es, ezt, c.float(), tgt, off)
+    v = tgt >= 0
+    close(m[v], em[v], rtol=0, atol=0, name="row max")
+    close(s[v], es[v], rtol=1e-3, atol=1e-4, name="row sum")
+    close(zt[v], ezt[v], rtol=0, atol=0, name="target logit")
+    la, d = torch.empty(rows, device=dev()), torch.empty_like(logits)
+    for off in range(0, V, chunk):
+        c = logits[:, off:off + chunk].clone()     # (a full-width slice is the tensor itself)
+        nat().ce_chunk_grad(la, c, tgt, m, s, zt, off, dscale)
+        d[:, off:off + chunk] = c
+    e, le = logits.float().clone(), torch.empty(rows, device=dev())
+    ref.ce_fwd_bwd(le, e, tgt, dscale)
+    close(la, le, rtol=1e-3, atol=1e-3, name="chunked ce loss")
+    close(d, e, rtol=2e-2, atol=1e-4, name="chunked dlogits")
+    assert (d[::4] == 0).all() and (la[::4] == 0).all()
+
+
 @pytest.mark.parametrize("n", [4096 * 3, 1001])
 def test_adamw(n):
     torch.manual_seed(12)

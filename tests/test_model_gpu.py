@@ -47,6 +47,36 @@ def test_gpu_step_matches_cpu_oracle(cfg, B):
         assert (a - b).abs().max().item() / denom < 6e-2, f"grad mismatch in {name}"
 
 
+@pytest.mark.parametrize("chunk", [128, 200])
+def test_chunked_lm_head_ce_matches_full_logits_gpu(chunk):
+    """LM head + cross-entropy over vocabulary chunks (no [B*T, V] logits buffer) against the path with materialised
+    logits, same kernels otherwise: equal loss, gradients equal up to the bf16 rounding of d(lnf_out) (the chunked path
+    accumulates it in fp32 over the chunks and rounds once)."""
+    cfg, B = Config(V=512, C=256, L=2, H=4, I=512, T=256), 2
+    ids, tgt = Stream(99).token_pairs(B * cfg.T, cfg.V)
+    tgt[::9] = -1
+    valid = int((tgt >= 0).sum())
+    di, dt = ids.cuda(), tgt.cuda()
+    out = []
+    for ch in (0, chunk):
+        g = GPT(cfg, B, "cuda:0", lmce_chunk=ch)
+        g.init_weights(1234)
+        g.forward(di)
+        g.backward(di, dt, valid_tokens=valid)
+        torch.cuda.synchronize()
+        assert _native().get_error() == 0
+        out.append((g.mean_loss(valid_tokens=valid), g.grads.clone(), g))
+    (l0, g0, m0), (l1, g1, m1) = out
+    assert m1.logits is None
+    assert abs(l0 - l1) < 2e-3
+    for name, off, shape in m0.layout.named_ranges():
+        n = 1
+        for sdim in shape:
+            n *= sdim
+        a, b = g1[off:off + n], g0[off:off + n]
+        assert (a - b).abs().max().item() / (b.abs().max().item() + 1e-6) < 3e-2, f"grad mismatch in {name}"
+
+
 def test_overfit_gpu():
     cfg = Config(V=256, C=128, L=4, H=4, I=256, T=64)
     tr = Trainer(cfg, 4, "cuda:0", lr=1e-3, wd=0.0)
