@@ -140,6 +140,19 @@ void mlb_metrics_log(void* h, int64_t step, double loss, double lr, int64_t toke
   }
 }
 
+// One scalar under its own tag (e.g. "eval/loss"): a JSONL line {"step", "wall_time", "<tag>"} and a TensorBoard event.
+void mlb_metrics_scalar(void* h, int64_t step, const char* tag, double value) {
+  Metrics* m = (Metrics*)h;
+  if (!m) return;
+  double wall = now_s();
+  fprintf(m->jsonl, "{\"step\":%lld,\"wall_time\":%.6f,\"%s\":%.8g}\n", (long long)step, wall, tag, value);
+  fflush(m->jsonl);
+  if (m->tb) {
+    tb_scalar(m->tb, wall, step, tag, (float)value);
+    fflush(m->tb);
+  }
+}
+
 void mlb_metrics_close(void* h) {
   Metrics* m = (Metrics*)h;
   if (!m) return;

@@ -245,7 +245,17 @@ def _train_loop(argv, ddp):
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
     ap.add_argument("--warmup-ratio", type=float, default=0.0)
+    ap.add_argument("--max-steps", type=int, default=0, help="same as the positional step count")
+    ap.add_argument("--batch-size", type=int, default=0, help="per-GPU micro-batch (default ENTROPY_B or 16)")
+    ap.add_argument("--seq-len", type=int, default=0, help="sequence length (default ENTROPY_T)")
+    ap.add_argument("--eval-bin", default="", help="held-out token file for --eval-every")
+    ap.add_argument("--eval-every", type=int, default=0, help="evaluate every N steps (forward only)")
+    ap.add_argument("--eval-batches", type=int, default=8, help="micro-batches per evaluation")
+    ap.add_argument("--tensorboard", action="store_true", help="accepted for compatibility: --log-dir always gets event files")
+    ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args(argv)
+    if a.max_steps > 0:
+        a.steps = a.max_steps
     if ddp:
         rank, world, local, dev = init_distributed()
     else:
@@ -253,8 +263,10 @@ def _train_loop(argv, ddp):
     if rank == 0:
         _banner("train_ddp" if ddp else "train", dev)
     cfg = Config.from_env()
+    if a.seq_len > 0:
+        cfg.T = a.seq_len
     run = RunConfig.from_env()
-    B = run.B if "ENTROPY_B" in os.environ else 16
+    B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
     tr = Trainer(cfg, B, dev, run, lr=a.lr, wd=a.weight_decay, world=world, rank=rank,
                  use_graph=bool(run.train_graph) and a.warmup_ratio <= 0)
     loader = TokenLoader(a.bin, B * tr.accum, cfg.T)
@@ -276,6 +288,31 @@ def _train_loop(argv, ddp):
         elif rank == 0:
             print("no checkpoint to resume from; starting fresh")
     pipe = BatchPipe(loader, dev)
+    eval_loader = None
+    if a.eval_every > 0:
+        # held-out file if given, else the tail of the training file read from its last windows backwards in file order
+        eval_loader = TokenLoader(a.eval_bin or a.bin, B, cfg.T)
+        if rank == 0 and a.verbose:
+            print(f"eval: {a.eval_bin or a.bin}  {eval_loader.ntok} tokens, {a.eval_batches} batches every {a.eval_every} steps")
+
+    def evaluate():
+        """Mean loss over --eval-batches micro-batches per rank (forward only), averaged over the ranks; every call
+        reads the same windows so that successive numbers are comparable."""
+        ewin = B * cfg.T
+        span = max(1, eval_loader.ntok - ewin - 1)
+        base = 0 if a.eval_bin else max(0, span - a.eval_batches * world * ewin)
+        tot = 0.0
+        for k in range(a.eval_batches):
+            eval_loader.pos = (base + (k * world + rank) * ewin) % span
+            ids, tgt = eval_loader.next()
+            tot += tr.model.eval_loss(ids.to(dev).view(-1), tgt.to(dev).view(-1), B=B)
+        ev = tot / max(1, a.eval_batches)
+        if world > 1:
+            t = torch.tensor([ev], device=dev)
+            dist.all_reduce(t)
+            ev = float(t.item()) / world
+        return ev
+
     writer = ck.CheckpointWriter() if (a.ckpt_dir and rank == 0) else None
     logger = MetricsLogger(a.log_dir, rank, wandb=a.wandb) if a.log_dir else None
     stop = {"flag": False}
@@ -324,6 +361,12 @@ def _train_loop(argv, ddp):
                       f"{fl / dt / 1e12:.1f} TFLOP/s | MFU {100 * fl / dt / peak:.1f}%")
                 if logger:
                     logger.log(step + 1, loss, tr.hyper["lr"], tokens_seen, dt * 1e3, {"mfu": fl / dt / peak, "tflops": fl / dt / 1e12})
+        if eval_loader is not None and ((step + 1) % a.eval_every == 0 or step + 1 == a.steps):
+            ev = evaluate()
+            if rank == 0:
+                print(f"step {step + 1:5d} | eval loss {ev:.4f}")
+                if logger:
+                    logger.log_scalar(step + 1, "eval/loss", ev)
         if writer and a.save_every > 0 and (step + 1) % a.save_every == 0:
             writer.save(a.ckpt_dir, step + 1, loss if loss == loss else 0.0, tokens_seen, tr.model.master, tr.model.m,
                         tr.model.v, loader_pos=pipe.slot_pos[(step + 1) % pipe.n], opt_t=tr.t)

@@ -286,6 +286,41 @@ class GPT:
         ops.embed_bwd(self.G(Lo.off_wte, V, C), dresid, ids, T, n_pre)
         self._hook("wte", Lo.off_wte, V * C)
 
+    def eval_loss(self, ids, tgt, B=None) -> float:
+        """Mean cross-entropy of `tgt` (rows with -1 are ignored) under the current weights: forward only, no gradient
+        buffer is touched.  The logits (or, in chunked mode, the logits tile and the row statistics) are consumed."""
+        c, Lo = self.cfg, self.layout
+        B = self.B if B is None else B
+        BT = B * c.T
+        self.forward(ids, B=B)
+        valid = int((tgt[:BT] >= 0).sum().item())
+        if valid == 0:
+            return 0.0
+        if self.lmce_chunk > 0:
+            m, s, zt = self._lmhead_chunk_stats(tgt, BT)
+            ok = tgt[:BT] >= 0
+            self.losses[:BT].copy_(torch.where(ok, torch.log(s) + m - zt, torch.zeros_like(s)))
+        else:
+            ops.ce_fwd_bwd(self.losses[:BT], self.logits[:BT], tgt, 1.0)
+        return self.mean_loss(B=B, valid_tokens=valid)
+
+    def _lmhead_chunk_stats(self, tgt, BT):
+        """Pass 1 of the chunked LM head: per-row running maximum, sum of exponentials and target logit over the
+        vocabulary chunks (the logits tile is overwritten chunk after chunk)."""
+        c, Lo = self.cfg, self.layout
+        V, C, ch = c.V, c.C, self.lmce_chunk
+        x, W = self.lnf_out[:BT], self.P(Lo.off_lm, V, C)
+        m, s, zt = self.ce_rowmax[:BT], self.ce_rowsum[:BT], self.ce_tgt_logit[:BT]
+        m.fill_(float("-inf"))
+        s.zero_()
+        zt.zero_()
+        for off in range(0, V, ch):
+            n = min(ch, V - off)
+            tile = self.logits_chunk[:BT * n].view(BT, n)
+            ops.linear_fwd(tile, x, W[off:off + n])
+            ops.ce_chunk_stats(m, s, zt, tile, tgt, off)
+        return m, s, zt
+
     def _lmhead_ce_backward_chunked(self, tgt, BT, valid, dln):
         """LM head + cross-entropy over vocabulary chunks (train/gpt.cu:396-445): pass 1 computes each chunk of logits
         and folds it into per-row running max / sum-exp / target logit; pass 2 recomputes each chunk, turns it into
@@ -296,15 +331,8 @@ class GPT:
         V, C, ch = c.V, c.C, self.lmce_chunk
         x = self.lnf_out[:BT]
         W, dW = self.P(Lo.off_lm, V, C), self.G(Lo.off_lm, V, C)
-        m, s, zt = self.ce_rowmax[:BT], self.ce_rowsum[:BT], self.ce_tgt_logit[:BT]
-        m.fill_(float("-inf"))
-        s.zero_()
-        zt.zero_()
+        m, s, zt = self._lmhead_chunk_stats(tgt, BT)
         tile = lambda n: self.logits_chunk[:BT * n].view(BT, n)
-        for off in range(0, V, ch):
-            n = min(ch, V - off)
-            ops.linear_fwd(tile(n), x, W[off:off + n])
-            ops.ce_chunk_stats(m, s, zt, tile(n), tgt, off)
         self._mark("B_lmce_stats")
         acc = self.dln_accum[:BT]
         acc.zero_()

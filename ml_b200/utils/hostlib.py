@@ -41,6 +41,7 @@ def lib():
         "mlb_crc32c": (C.c_uint32, [vp, i64]),
         "mlb_metrics_open": (vp, [cp, i32]),
         "mlb_metrics_log": (None, [vp, i64, f64, f64, i64, f64, i64, i64, i32, C.POINTER(cp), C.POINTER(f64)]),
+        "mlb_metrics_scalar": (None, [vp, i64, cp, f64]),
         "mlb_metrics_close": (None, [vp]),
     }
     for name, (res, args) in sig.items():

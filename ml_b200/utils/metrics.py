@@ -36,6 +36,11 @@ class MetricsLogger:
         vals = (C.c_double * len(extra))(*[float(x) for x in extra.values()])
         lib().mlb_metrics_log(self.h, step, loss, lr, tokens_seen, step_time_ms, free, total, len(extra), names, vals)
 
+    def log_scalar(self, step: int, tag: str, value: float):
+        """One scalar under its own tag (evaluation loss and the like) in both sinks."""
+        if self.h:
+            lib().mlb_metrics_scalar(self.h, step, tag.encode(), float(value))
+
     def close(self):
         if self.h:
             lib().mlb_metrics_close(self.h)

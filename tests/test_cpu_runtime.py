@@ -205,6 +205,42 @@ def test_cli_train_checkpoint_resume(tmp_path):
     assert la == lc, (la, lc)
 
 
+def test_cli_train_eval_flags_and_chunked_head(tmp_path):
+    """--eval-every / --eval-bin print a forward-only held-out loss, log it under eval/loss, and leave the training
+    trajectory untouched; --max-steps / --batch-size / --seq-len override the positional / environment values; the same
+    run with ENTROPY_LMCE_CHUNK goes through the chunked LM head and lands on the same losses."""
+    import subprocess, sys, json
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    toks = (torch.arange(0, 20000, dtype=torch.int64) * 7919 % 251).to(torch.int32)
+    p, q = str(tmp_path / "d.bin"), str(tmp_path / "e.bin")
+    write_token_bin(p, toks)
+    write_token_bin(q, (toks * 3 + 1) % 251)
+    env = dict(os.environ, ENTROPY_DEVICE="cpu", ENTROPY_V="256", ENTROPY_C="32", ENTROPY_L="1", ENTROPY_H="2", ENTROPY_I="64",
+               ENTROPY_T="32", ENTROPY_B="4", ENTROPY_LOG_EVERY="5", PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    base = [sys.executable, "-m", "ml_b200.gpt", "train", p, "99", "--max-steps", "10", "--batch-size", "2", "--seq-len", "16"]
+    plain = subprocess.run(base, env=env, capture_output=True, text=True, timeout=300)
+    assert plain.returncode == 0, plain.stdout + plain.stderr
+    assert "B=2 T=16" in plain.stdout and "step    10 | loss" in plain.stdout and "step    15" not in plain.stdout
+    ev = subprocess.run(base + ["--eval-bin", q, "--eval-every", "5", "--eval-batches", "3", "--log-dir", str(tmp_path / "log"), "--verbose"],
+                        env=env, capture_output=True, text=True, timeout=300)
+    assert ev.returncode == 0, ev.stdout + ev.stderr
+    evals = [l for l in ev.stdout.splitlines() if "eval loss" in l]
+    assert len(evals) == 2 and evals[0].startswith("step     5") and evals[1].startswith("step    10")
+    v5, v10 = (float(l.split("eval loss")[1]) for l in evals)
+    assert 0 < v10 < v5 + 1.0
+    tr = lambda out: [l for l in out.splitlines() if l.startswith("step") and "| loss" in l]
+    assert [l.split("|")[1] for l in tr(ev.stdout)] == [l.split("|")[1] for l in tr(plain.stdout)]
+    rows = [json.loads(l) for l in open(tmp_path / "log" / "metrics.jsonl")]
+    assert [r["eval/loss"] for r in rows if "eval/loss" in r] == pytest.approx([v5, v10], abs=1e-4)
+    ch = subprocess.run(base + ["--eval-bin", q, "--eval-every", "5", "--eval-batches", "3"], env=dict(env, ENTROPY_LMCE_CHUNK="96"),
+                        capture_output=True, text=True, timeout=300)
+    assert ch.returncode == 0, ch.stdout + ch.stderr
+    import re
+    num = lambda line: float(re.search(r"loss ([0-9.]+)", line).group(1))
+    for a_, b_ in zip(tr(ch.stdout) + [l for l in ch.stdout.splitlines() if "eval loss" in l], tr(ev.stdout) + evals):
+        assert num(a_) == pytest.approx(num(b_), abs=2e-4), (a_, b_)
+
+
 def test_raw_token_loader_formats(tmp_path):
     import numpy as np
     from ml_b200.data import RawTokenLoader
