@@ -193,3 +193,33 @@ def test_chunk_ce_ops_match_fused_ce():
         d[:, off:off + 24] = c
     assert torch.allclose(losses, exp_l, atol=1e-5)
     assert torch.allclose(d, exp_d, atol=1e-6)
+
+
+def test_torch_baseline_module_is_a_whole_model_oracle(capsys):
+    """The nn.Module restatement (bench/torch_baseline.py) loaded from the engine's flat parameter buffer gives the
+    engine's loss and gradients; its timed entry point runs on CPU with a tiny configuration."""
+    from ml_b200.bench.torch_baseline import TorchDecoder, main
+    cfg = Config(V=97, C=48, L=2, H=4, I=80, T=16)
+    B = 3
+    g = GPT(cfg, B)
+    g.init_weights(1234)
+    ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+    tgt[::5] = -1
+    valid = int((tgt >= 0).sum())
+    g.forward(ids)
+    g.backward(ids, tgt, valid_tokens=valid)
+    m = TorchDecoder(cfg).load_flat(g.master)
+    assert torch.equal(m.flat_like("param"), g.master)
+    loss = m(ids.view(B, cfg.T), tgt.view(B, cfg.T))
+    loss.backward()
+    assert abs(loss.item() - g.mean_loss(valid_tokens=valid)) < 1e-5
+    assert (m.flat_like("grad") - g.grads).abs().max() < 2e-5
+    import os
+    old = dict(os.environ)
+    os.environ.update(ENTROPY_V="64", ENTROPY_C="32", ENTROPY_L="1", ENTROPY_H="2", ENTROPY_I="64", ENTROPY_T="16")
+    try:
+        assert main(["--B", "2", "--steps", "2", "--warmup", "1", "--device", "cpu"]) == 0
+    finally:
+        os.environ.clear()
+        os.environ.update(old)
+    assert "tok/s" in capsys.readouterr().out
