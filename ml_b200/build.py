@@ -30,7 +30,7 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a",
 # what goes into the staleness hashes: the flags without anything that depends on where the tree is checked out, so
 # a library built in one directory is still fresh after the tree has been copied elsewhere
 _FLAGS_FOR_HASH = " ".join(f for f in NVCC_FLAGS if f != str(CSRC))
-# Files that must not travel to multi-GPU runs are listed in .gpurunignore.multi; nothing here needs that.
+# No source of this library uses a cluster-multicast TMA load, so the same library serves 1-GPU and multi-GPU runs.
 
 
 def _nvcc():
