@@ -6,6 +6,7 @@
 // adamw :1357-1400) but none of the code is shared with them.
 #include "../common.cuh"
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include "../no_alloc.h"
 
 #include <cstdio>
@@ -685,6 +686,16 @@ __global__ void cast_f2b_k(bf16* __restrict__ out, const float* __restrict__ in,
     for (; i < n; i++) out[i] = __float2bfloat16(in[i] * scale);
   }
 }
+// E4M3 rounding of a bf16 tensor, kept in bf16: out = e4m3_saturate(x * scale) / scale (round to nearest even, +-448
+// saturation; train/gpt_kernels.cuh:203-218 is the reference's cast to FP8 storage).  With a power-of-two scale the
+// result is exact in bf16 (3 mantissa bits), so a bf16 GEMM on such operands has the numerics of an E4M3 x E4M3 GEMM
+// with fp32 accumulation.
+__global__ void fp8_qdq_k(bf16* __restrict__ out, const bf16* __restrict__ in, long n, float scale, float inv_scale) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const __nv_fp8_e4m3 q(__bfloat162float(in[i]) * scale);
+  out[i] = __float2bfloat16(float(q) * inv_scale);
+}
 __global__ void cast_b2f_k(float* __restrict__ out, const bf16* __restrict__ in, long n, float scale) {
   long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __bfloat162float(in[i]) * scale;
@@ -861,6 +872,12 @@ MLB_API int mlb_adamw(float* master, void* params, const float* grads, float* m,
 }
 MLB_API int mlb_cast_f2b(void* out, const float* in, long n, float scale, cudaStream_t st) {
   mlb_launch(cast_f2b_k, dim3(gs((n + 3) / 4, 256)), dim3(256), 0, st, (bf16*)out, in, n, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_fp8_qdq(void* out, const void* in, long n, float scale, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (!(scale > 0.f)) return -3;
+  fp8_qdq_k<<<gs(n, 256), 256, 0, st>>>((bf16*)out, (const bf16*)in, n, scale, 1.0f / scale);
   LAUNCH_RET;
 }
 MLB_API int mlb_cast_b2f(float* out, const void* in, long n, float scale, cudaStream_t st) {

@@ -31,7 +31,7 @@ FUSE_ROPE_INTO_QKV = _os.environ.get("MLB_NO_ROPE_FUSE", "0") != "1"
 class GPT:
     def __init__(self, cfg: Config, B: int, device="cpu", dtype: Optional[torch.dtype] = None,
                  opt_state: bool = True, alloc_grads: bool = True, alloc=None, sharded: bool = False,
-                 lmce_chunk: Optional[int] = None):
+                 lmce_chunk: Optional[int] = None, fp8_fwd: Optional[bool] = None):
         """alloc(numel, dtype) -> flat tensor: optional allocator for the parameter and gradient buffers (the
         data-parallel engines pass a symmetric-memory allocator so peers can address them).
         sharded=True: no flat master / params / grads / m / v are allocated here; a sharding engine
@@ -44,6 +44,18 @@ class GPT:
         if lmce_chunk is None:
             lmce_chunk = int(_os.environ.get("ENTROPY_LMCE_CHUNK", "0") or 0)
         self.lmce_chunk = max(0, min(int(lmce_chunk), cfg.V))
+        # ENTROPY_FP8_FWD=1 (train/gpt.cu:146-150,463-567): the forward products QKV, gate|up, down and LM head see their
+        # operands rounded to E4M3, x * ENTROPY_FP8_ACT_SCALE and W * ENTROPY_FP8_W_SCALE before rounding, the scales
+        # divided out again; backward uses the unrounded bf16 activations and weights.  The rounded operands are kept
+        # in the working dtype and multiplied by the bf16 tensor-core kernel (fp32 accumulation): the numerics of the
+        # reference's opt-in path, not an 8-bit tensor-core product.
+        if fp8_fwd is None:
+            fp8_fwd = (_os.environ.get("ENTROPY_FP8_FWD", "0") or "0") not in ("0", "")
+        self.fp8_fwd = bool(fp8_fwd)
+        pos = lambda name: max(float(_os.environ.get(name, "1.0") or 1.0), 0.0) or 1.0
+        self.fp8_act_scale, self.fp8_w_scale = pos("ENTROPY_FP8_ACT_SCALE"), pos("ENTROPY_FP8_W_SCALE")
+        if self.fp8_fwd and (sharded or self.lmce_chunk > 0):
+            raise ValueError("ENTROPY_FP8_FWD is implemented for the unsharded model with materialised logits only")
         self.device = torch.device(device)
         if dtype is None:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
@@ -99,6 +111,9 @@ class GPT:
         else:
             self.logits = e(BT, V)
         self.losses = f(BT)
+        if self.fp8_fwd:
+            self.fp8_x = e(BT * max(C, I))                              # E4M3-rounded GEMM input of the moment
+            self.fp8_w = e(max(3 * C * C, 2 * I * C, V * C))           # E4M3-rounded weight of the moment
         # scratch
         self.proj = e(BT, C)
         self.dresid = e(BT, C)
@@ -108,6 +123,17 @@ class GPT:
         self.dgu = e(BT, 2 * I)
         self.dqkv = e(BT, 3 * C)
         self.datty = e(BT, C)
+
+    def _fwd_operands(self, x, off, N, K):
+        """(x, W[N, K]) of a forward product; with fp8_fwd both rounded to E4M3 (into scratch that the next call reuses)."""
+        W = self.P(off, N, K)
+        if not self.fp8_fwd:
+            return x, W
+        xq = self.fp8_x[:x.numel()].view_as(x)
+        wq = self.fp8_w[:N * K].view(N, K)
+        ops.fp8_qdq(xq, x, self.fp8_act_scale)
+        ops.fp8_qdq(wq, W, self.fp8_w_scale)
+        return xq, wq
 
     def P(self, off, *shape):
         if self.res is not None:
@@ -175,10 +201,11 @@ class GPT:
                 roped = False
             else:
                 # head size 64 on the GPU: the rotation runs in the GEMM's epilogue, on the fp32 accumulators
+                xin, Wq = self._fwd_operands(sl(self.ln1[l]), o.qkv, 3 * C, C)
                 roped = (hd == 64 and qkv.is_cuda and "rope" not in self.skip and FUSE_ROPE_INTO_QKV and
-                         ops.native_module().linear_fwd_rope(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C), self.cos, self.sin, T, 2 * C))
+                         ops.native_module().linear_fwd_rope(qkv, xin, Wq, self.cos, self.sin, T, 2 * C))
                 if not roped:
-                    ops.linear_fwd(qkv, sl(self.ln1[l]), self.P(o.qkv, 3 * C, C))
+                    ops.linear_fwd(qkv, xin, Wq)
             if "rope" not in self.skip and not roped:
                 ops.rope_fwd(qkv, self.cos, self.sin, B, T, H, hd)
             self._mark("F_qkv+rope")
@@ -190,10 +217,10 @@ class GPT:
             ops.add_rmsnorm_fwd(sl(self.resid1[l]), sl(self.ln2[l]), sl(self.rstd2[l]), resid_in, proj,
                                 self.P(o.ln2, C), c.eps)
             if "mlp" not in self.skip:
-                ops.linear_fwd(sl(self.gu[l]), sl(self.ln2[l]), self.P(o.gate, 2 * I, C))
+                ops.linear_fwd(sl(self.gu[l]), *self._fwd_operands(sl(self.ln2[l]), o.gate, 2 * I, C))
                 if "swiglu" not in self.skip:
                     ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
-                ops.linear_fwd(proj, sl(self.sw[l]), self.P(o.down, C, I))
+                ops.linear_fwd(proj, *self._fwd_operands(sl(self.sw[l]), o.down, C, I))
             if l + 1 == c.L and not has_head:
                 # stage boundary: plain residual add; the next stage starts with its own first norm
                 ops.residual_add(sl(self.resid2[l]), sl(self.resid1[l]), proj)
@@ -210,7 +237,7 @@ class GPT:
         if self.lmce_chunk > 0:
             return None          # the head runs chunk by chunk inside backward; no logits are materialised
         if "head" not in self.skip:
-            ops.linear_fwd(self.logits[:BT], sl(self.lnf_out), self.P(Lo.off_lm, c.V, C))
+            ops.linear_fwd(self.logits[:BT], *self._fwd_operands(sl(self.lnf_out), Lo.off_lm, c.V, C))
         self._mark("F_lmhead")
         return self.logits[:BT]
 

@@ -58,6 +58,7 @@ def lib():
         "mlb_swiglu_fwd": [_vp, _vp, _i64, _i32, _vp],
         "mlb_swiglu_bwd": [_vp, _vp, _vp, _i64, _i32, _vp],
         "mlb_ce_fwd_bwd": [_vp, _vp, _vp, _i64, _i32, _i64, _f32, _i32, _vp],
+        "mlb_fp8_qdq": [_vp, _vp, _i64, _f32, _vp],
         "mlb_ce_chunk_stats": [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _i32, _vp],
         "mlb_ce_chunk_grad": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _i32, _f32, _vp],
         "mlb_adamw": [_vp, _vp, _vp, _vp, _vp, _i64, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _vp, _vp],
@@ -346,6 +347,10 @@ def cast(out, x, scale=1.0):
         _chk(lib().mlb_cast_b2f(_f(out), _b(x), n, scale, _st()), "cast_b2f")
     else:
         raise TypeError(f"cast {x.dtype} -> {out.dtype} is not a kernel of this library")
+
+
+def fp8_qdq(out, x, scale=1.0):
+    _chk(lib().mlb_fp8_qdq(_b(out), _b(x), x.numel(), scale, _st()), "fp8_qdq")
 
 
 def scale_(x, s):

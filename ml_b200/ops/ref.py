@@ -132,6 +132,13 @@ def linear_dw(dW, dout, x):
     dW.add_(_f(dout).t() @ _f(x))
 
 
+def fp8_qdq(out, x, scale=1.0):
+    """out = e4m3(x * scale) / scale: operands as an FP8 (E4M3, round to nearest even, saturating at +-448) GEMM would
+    see them, kept in the working dtype (train/gpt_kernels.cuh:203-218 is the reference's cast to FP8 storage)."""
+    q = (_f(x) * scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).float()
+    out.copy_(q / scale)
+
+
 def gemm(out, A, B, a_mn=False, b_mn=False, accumulate=False):
     """D[M,N] = sum_k A(m,k) B(n,k); A is [M,K] or, with a_mn, stored [K,M]; B is [N,K] or, with b_mn, stored [K,N].
     `out` is overwritten, or (accumulate, fp32) added to."""

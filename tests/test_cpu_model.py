@@ -223,3 +223,35 @@ def test_torch_baseline_module_is_a_whole_model_oracle(capsys):
         os.environ.clear()
         os.environ.update(old)
     assert "tok/s" in capsys.readouterr().out
+
+
+def test_fp8_forward_option_rounds_forward_operands_only():
+    """ENTROPY_FP8_FWD semantics (train/gpt.cu:463-567): QKV, gate|up, down and LM-head products see E4M3-rounded
+    operands in the forward pass; the loss moves a little, backward still uses the unrounded tensors (so with the
+    forward's activations given, gradients follow the same formulas), and scales that are powers of two commute with
+    the rounding."""
+    from ml_b200.ops import ref
+    x = torch.tensor([0.0, 1.0, 1.06, 1.07, -3.3, 500.0, -1e4, 2.0 ** -9, 3e-4])
+    q = torch.empty_like(x)
+    ref.fp8_qdq(q, x, 1.0)
+    # 3 mantissa bits (1.06 -> 1.0, 1.07 -> 1.125), saturation at 448, subnormal step 2^-9 (3e-4 is below half of it)
+    assert q.tolist() == [0.0, 1.0, 1.0, 1.125, -3.25, 448.0, -448.0, 2.0 ** -9, 0.0]
+    q2 = torch.empty(5)
+    ref.fp8_qdq(q2, x[:5], 4.0)
+    assert torch.equal(q2, q[:5])
+    cfg = Config(V=97, C=48, L=2, H=4, I=80, T=16)
+    B = 3
+    ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+    losses = []
+    for fp8 in (False, True):
+        g = GPT(cfg, B, fp8_fwd=fp8)
+        g.init_weights(1234)
+        g.forward(ids)
+        g.backward(ids, tgt)
+        losses.append(g.mean_loss())
+        grads = g.grads.clone()
+    assert losses[0] != losses[1] and abs(losses[0] - losses[1]) < 0.05
+    assert torch.isfinite(grads).all() and grads.abs().max() > 0
+    import pytest
+    with pytest.raises(ValueError):
+        GPT(cfg, B, fp8_fwd=True, lmce_chunk=32)

@@ -385,6 +385,21 @@ def test_cross_entropy_over_vocabulary_chunks(rows, V, chunk):
     assert (d[::4] == 0).all() and (la[::4] == 0).all()
 
 
+@pytest.mark.parametrize("scale", [1.0, 8.0, 0.37])
+def test_e4m3_rounding_kernel(scale):
+    """fp8_qdq against the oracle (torch's float8_e4m3fn conversion after the same saturation): normal range,
+    subnormals, saturation, zeros, both signs."""
+    torch.manual_seed(14)
+    x = torch.cat([rnd(4096, scale=1.0), rnd(2048, scale=300.0), rnd(2048, scale=2e-3),
+                   torch.tensor([0.0, -0.0, 448.0, -448.0, 1e4, -1e4, 2.0 ** -9, 2.0 ** -10], device=dev()).bfloat16()])
+    out = torch.empty_like(x)
+    nat().fp8_qdq(out, x, scale)
+    exp = torch.empty(x.numel(), device=dev())
+    ref.fp8_qdq(exp, x, scale)
+    # the kernel's result is rounded to bf16; with a power-of-two scale that is exact
+    close(out, exp.bfloat16(), rtol=0 if scale in (1.0, 8.0) else 8e-3, atol=0 if scale in (1.0, 8.0) else 1e-6, name="e4m3 rounding")
+
+
 @pytest.mark.parametrize("n", [4096 * 3, 1001])
 def test_adamw(n):
     torch.manual_seed(12)

@@ -77,6 +77,36 @@ def test_chunked_lm_head_ce_matches_full_logits_gpu(chunk):
         assert (a - b).abs().max().item() / (b.abs().max().item() + 1e-6) < 3e-2, f"grad mismatch in {name}"
 
 
+def test_fp8_forward_option_gpu_matches_cpu_oracle():
+    """ENTROPY_FP8_FWD path on the GPU (E4M3 rounding kernel in front of the forward GEMMs) against the CPU oracle with
+    the same option."""
+    cfg, B = Config(V=512, C=256, L=2, H=4, I=512, T=256), 2
+    ids, tgt = Stream(99).token_pairs(B * cfg.T, cfg.V)
+    ref = GPT(cfg, B, "cpu", fp8_fwd=True)
+    ref.init_weights(1234)
+    ref.forward(ids)
+    ref.backward(ids, tgt)
+    plain = GPT(cfg, B, "cpu", fp8_fwd=False)
+    plain.init_weights(1234)
+    plain.forward(ids)
+    plain.backward(ids, tgt)
+    g = GPT(cfg, B, "cuda:0", fp8_fwd=True)
+    g.init_weights(1234)
+    g.forward(ids.cuda())
+    g.backward(ids.cuda(), tgt.cuda())
+    torch.cuda.synchronize()
+    assert _native().get_error() == 0
+    assert abs(g.mean_loss() - ref.mean_loss()) < 2e-2
+    assert ref.mean_loss() != plain.mean_loss()
+    gg, rg = g.grads.cpu(), ref.grads
+    for name, off, shape in g.layout.named_ranges():
+        n = 1
+        for sdim in shape:
+            n *= sdim
+        a, b = gg[off:off + n], rg[off:off + n]
+        assert (a - b).abs().max().item() / (b.abs().max().item() + 1e-6) < 8e-2, f"grad mismatch in {name}"
+
+
 def test_overfit_gpu():
     cfg = Config(V=256, C=128, L=4, H=4, I=256, T=64)
     tr = Trainer(cfg, 4, "cuda:0", lr=1e-3, wd=0.0)
