@@ -104,7 +104,11 @@ def test_fp8_forward_option_gpu_matches_cpu_oracle():
         for sdim in shape:
             n *= sdim
         a, b = gg[off:off + n], rg[off:off + n]
-        assert (a - b).abs().max().item() / (b.abs().max().item() + 1e-6) < 8e-2, f"grad mismatch in {name}"
+        # an activation that differs in the last bf16 bit between the two devices can land on the other side of an
+        # E4M3 rounding boundary (a 6 % step), so single elements are held to a looser bound than in the bf16 test and
+        # the tensor as a whole to a norm bound (the norm weights, sums over all rows of such products, are the noisiest)
+        assert (a - b).abs().max().item() / (b.abs().max().item() + 1e-6) < 0.2, f"grad mismatch in {name}"
+        assert ((a - b).norm() / (b.norm() + 1e-12)).item() < 0.15, f"grad mismatch (norm) in {name}"
 
 
 def test_overfit_gpu():
