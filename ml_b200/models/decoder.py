@@ -66,6 +66,7 @@ class GPT:
         self.sharded = sharded
         self.res = None          # optional view resolver: res.param(off, shape) / res.grad(off, shape)
         self.pre_hook = None     # optional pre_hook(unit_name, phase) called before a unit's parameters are first used
+        self.cp = None           # optional sequence-parallel attention (ml_b200.parallel.cp.SequenceParallel)
         if sharded:
             self.master = self.params = self.grads = self.m = self.v = None
         else:
@@ -210,7 +211,10 @@ class GPT:
                 ops.rope_fwd(qkv, self.cos, self.sin, B, T, H, hd)
             self._mark("F_qkv+rope")
             if "attn" not in self.skip:   # ENTROPY_SKIP_* ablations remove a stage to attribute its time (results are then meaningless)
-                ops.attn_fwd(sl(self.atty[l]), self.lse[l][:B], qkv, B, T, H, hd)
+                if self.cp is not None:     # sequence shards: attention runs head-sharded over the full sequences
+                    self.cp.attn_fwd(self, l, sl(self.atty[l]), qkv, B)
+                else:
+                    ops.attn_fwd(sl(self.atty[l]), self.lse[l][:B], qkv, B, T, H, hd)
             self._mark("F_attn")
             proj = sl(self.proj)
             ops.linear_fwd(proj, sl(self.atty[l]), self.P(o.o, C, C))
@@ -295,8 +299,12 @@ class GPT:
             ops.linear_dw(self.G(o.o, C, C), dresid1, sl(self.atty[l]))
             ops.linear_dx(datty, dresid1, self.P(o.o, C, C))
             want_rope = "rope" not in self.skip
-            fused = ops.attn_bwd(dqkv, datty, sl(self.qkv[l]), sl(self.atty[l]), self.lse[l][:B], B, T, H, hd,
-                                 rope=(self.cos, self.sin) if want_rope else None)
+            if self.cp is not None:
+                self.cp.attn_bwd(self, l, dqkv, datty, B)
+                fused = False
+            else:
+                fused = ops.attn_bwd(dqkv, datty, sl(self.qkv[l]), sl(self.atty[l]), self.lse[l][:B], B, T, H, hd,
+                                     rope=(self.cos, self.sin) if want_rope else None)
             if want_rope and not fused:
                 ops.rope_bwd(dqkv, self.cos, self.sin, B, T, H, hd)
             self._mark("B_attn")

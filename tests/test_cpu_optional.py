@@ -1,4 +1,5 @@
-"""Optional capability blocks on CPU: tensor-parallel linears (gloo, 2 ranks), top-k MoE block, logger."""
+"""Optional capability blocks on CPU: tensor-parallel linears and sequence parallelism (gloo, 2 ranks), top-k MoE
+block, logger."""
 import io
 
 import torch
@@ -69,3 +70,54 @@ def test_logger_format_and_check():
     except mlog.CheckError:
         pass
     mlog.set_level("INFO")
+
+
+def test_sequence_parallel_model_equals_full_sequence_model():
+    """Two ranks, each with half of every sequence (all-to-all to a head-sharded layout around attention): loss and
+    every gradient equal the single-process model on the full sequences; ignored targets included."""
+    outs = run_ranks("""
+        import torch, torch.distributed as dist
+        from ml_b200 import Config
+        from ml_b200.models import GPT
+        from ml_b200.parallel.bootstrap import init_distributed, shutdown
+        from ml_b200.parallel import cp
+        from ml_b200.utils.rng import Stream
+        torch.set_num_threads(2)
+        rank, world, local, dev = init_distributed("cpu")
+        cfg = Config(V=97, C=48, L=2, H=4, I=80, T=32)
+        B = 3
+        ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+        tgt[::5] = -1
+        valid = int((tgt >= 0).sum())
+        full = GPT(cfg, B)
+        full.init_weights(1234)
+        full.forward(ids)
+        full.backward(ids, tgt, valid_tokens=valid)
+        m = cp.make_model(cfg, B, "cpu")
+        assert m.cfg.T == 16 and m.cp.Hc == 2
+        m.init_weights(1234)
+        li, lt = cp.local_tokens(ids, B, cfg.T, rank, world), cp.local_tokens(tgt, B, cfg.T, rank, world)
+        m.forward(li)
+        m.backward(li, lt, valid_tokens=valid)
+        cp.reduce_grads(m)
+        loss = cp.global_mean_loss(m, valid)
+        print("CP", abs(loss - full.mean_loss(valid_tokens=valid)), float((m.grads - full.grads).abs().max()),
+              float(full.grads.abs().max()), flush=True)
+        shutdown()
+    """)
+    assert all(rc == 0 for rc, _ in outs), outs
+    for _, o in outs:
+        line = [l for l in o.splitlines() if l.startswith("CP")][0].split()
+        assert float(line[1]) < 1e-5 and float(line[2]) < 2e-5 and float(line[3]) > 1e-3
+
+
+def test_sequence_parallel_single_rank_layouts_coincide():
+    from ml_b200 import Config
+    from ml_b200.parallel.cp import SequenceParallel
+    sp = SequenceParallel(Config(V=64, C=32, L=1, H=4, I=64, T=16), 2, "cpu", torch.float32)
+    assert (sp.world, sp.Tl, sp.Hc) == (1, 16, 4)
+    x = torch.randn(2 * 16, 3 * 32)
+    h, back = torch.empty_like(x), torch.empty_like(x)
+    sp.seq_to_heads(h, x, 2, 3)
+    sp.heads_to_seq(back, h, 2, 3)
+    assert torch.equal(h, x) and torch.equal(back, x)        # one rank: both layouts coincide
