@@ -33,49 +33,87 @@ SITE = os.path.join(os.path.dirname(os.path.dirname(os.__file__)), "site-package
 
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """`nvidia-smi` polled every 100 ms in a child process.  It is started well before the timed region (the tool needs
+    a few hundred ms to come up, and a timed region of 20 steps lasts about as long); `mark()` notes when the timed region
+    begins, and `stop()` summarises the samples taken from then on.  If none fell inside (or no mark was set: the
+    reference program times itself), the samples taken under load - power within 60 % of the highest seen - are used and
+    the summary says so."""
+    Q = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.idx, self.p, self.path = gpu_index, None, f"/tmp/mlb_clocks_{os.getpid()}.csv"
+        self.idx, self.p, self.path, self.t_mark = gpu_index, None, f"/tmp/mlb_clocks_{os.getpid()}.csv", None
 
     def start(self):
         try:
             self.f = open(self.path, "w")
             self.p = subprocess.Popen(["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "200"], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-lms", "100"], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.p = None
 
-    def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.p is None:
+    def mark(self):
+        import datetime
+        self.t_mark = datetime.datetime.now()
+
+    @classmethod
+    def summarise(cls, lines, since=None):
+        """lines: CSV rows of the query above.  Returns the JSON fragment for the bench line."""
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": None}
+        rows = []
+        for ln in lines:
+            c = [x.strip() for x in ln.split(",")]
+            if len(c) < 10:
+                continue
+            try:
+                sm, mx = float(c[2]), float(c[3])
+            except ValueError:
+                continue
+            try:
+                ts = datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f")
+            except ValueError:
+                ts = None            # unknown time format: the row still counts for the under-load fallback
+            try:
+                pw = float(c[4])
+            except ValueError:
+                pw = 0.0
+            rows.append((ts, sm, mx, pw, {n for n, v in zip(cls.REASONS, c[6:10]) if v.lower().startswith("active")}))
+        if not rows:
             return out
+        sel = [r for r in rows if since is not None and r[0] is not None and r[0] >= since]
+        window = "timed region"
+        if not sel:
+            top = max(r[3] for r in rows)
+            sel = [r for r in rows if r[3] >= 0.6 * top] or rows
+            window = ("under load around the timed region (no sample fell inside it)" if since is not None
+                      else "under load, whole run of the program")
+        reasons = set()
+        for r in sel:
+            reasons |= r[4]
+        out.update(sm_mhz=statistics.median(r[1] for r in sel), sm_max_mhz=max(r[2] for r in sel), reasons=sorted(reasons),
+                   samples=len(sel), window=window)
+        return out
+
+    def stop(self):
+        if self.p is None:
+            return self.summarise([])
         self.p.terminate()
         try:
             self.p.wait(timeout=5)
         except Exception:
             self.p.kill()
         self.f.close()
-        sm, mx, reasons = [], [], set()
-        for ln in open(self.path):
-            c = [x.strip() for x in ln.split(",")]
-            if len(c) < 9:
-                continue
-            try:
-                sm.append(float(c[1]))
-                mx.append(float(c[2]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
+        try:
+            with open(self.path) as f:
+                out = self.summarise(f.readlines(), self.t_mark)
+        except OSError:
+            out = self.summarise([])
         try:
             os.remove(self.path)
         except OSError:
             pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
         return out
 
 
@@ -198,12 +236,13 @@ def run_ours(args):
         return ms
 
     # ---- device-timed steps (inputs resident)
+    sampler = ClockSampler(local)
+    sampler.start()                       # before the warm-up: the tool is up and polling when the timed region starts
     for _ in range(max(args.warmup, 3)):
         tr.step()
     l0 = native.LAUNCHES
-    tr_launch_probe = Trainer.__dict__  # noqa: F841
-    sampler = ClockSampler(local)
-    sampler.start()
+    barrier()
+    sampler.mark()
     ms = timed(lambda i: tr.step(), args.steps)
     clocks = sampler.stop()
     launches = tr.launches_per_step * args.steps if tr.use_graph else native.LAUNCHES - l0

@@ -284,3 +284,26 @@ def test_native_build_stamps_survive_relocation_and_concurrent_builders(tmp_path
     for p in ps:
         out, err = p.communicate(timeout=300)
         assert p.returncode == 0 and "OK" in out, err[-2000:]
+
+
+def test_bench_clock_summary_picks_samples_of_the_timed_region():
+    """bench.py's nvidia-smi summary: samples from the mark on; if none fell inside, the ones under load; throttle
+    reasons collected; unparsable rows and unknown time formats tolerated."""
+    import datetime
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(root, "bench.py"))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    rows = ["2026/11/25 12:00:00.100, 0, 210, 1965, 140.5, 0x1, Not Active, Not Active, Not Active, Not Active\n",
+            "2026/11/25 12:00:00.600, 0, 1830, 1965, 990.1, 0x4, Not Active, Not Active, Not Active, Active\n",
+            "2026/11/25 12:00:00.700, 0, 1800, 1965, 1001.0, 0x4, Not Active, Active, Not Active, Active\n", "garbage\n"]
+    s = b.ClockSampler.summarise(rows, datetime.datetime(2026, 11, 25, 12, 0, 0, 650000))
+    assert (s["sm_mhz"], s["samples"], s["window"]) == (1800.0, 1, "timed region")
+    assert s["reasons"] == ["hw_thermal_slowdown", "sw_power_cap"]
+    s = b.ClockSampler.summarise(rows, datetime.datetime(2026, 11, 25, 12, 0, 5))
+    assert (s["sm_mhz"], s["samples"]) == (1815.0, 2) and "under load" in s["window"]      # the idle sample is left out
+    assert b.ClockSampler.summarise(rows, None)["samples"] == 2
+    assert b.ClockSampler.summarise(["x, 0, 1500, 1965, 900, 0x4, Not Active, Not Active, Not Active, Active\n"],
+                                    datetime.datetime(2026, 1, 1))["sm_mhz"] == 1500.0
+    assert b.ClockSampler.summarise([], None) == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": None}
