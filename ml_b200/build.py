@@ -30,7 +30,7 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a",
 # what goes into the staleness hashes: the flags without anything that depends on where the tree is checked out, so
 # a library built in one directory is still fresh after the tree has been copied elsewhere
 _FLAGS_FOR_HASH = " ".join(f for f in NVCC_FLAGS if f != str(CSRC))
-# No source of this library uses a cluster-multicast TMA load, so the same library serves 1-GPU and multi-GPU runs.
+# One library serves single- and multi-GPU runs: every TMA load in these sources is a plain per-CTA load.
 
 
 def _nvcc():
