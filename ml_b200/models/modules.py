@@ -3,6 +3,11 @@
 Same architecture and parameter order as the flat-buffer engine (`GPT`): `from_flat` builds a module whose weights
 are copies of an engine's parameters, so both can be checked against each other.  Use this when the model has to live
 inside ordinary PyTorch code (custom losses, torch optimizers); use `Trainer` / `GPT` for the tuned training step.
+
+Two options of the reference's prototype model configuration (csrc/include/model.h:17-60: grouped-query attention and
+QKV biases, Qwen2.5 style) exist only here: `Decoder(cfg, n_kv_heads=..., qkv_bias=True)`.  K / V heads are repeated up
+to the H query heads in front of the attention op, so the attention kernels see the usual [B*T, 3C] layout; such a
+module has no flat-buffer counterpart (`from_flat` / `load_flat` are for the default architecture).
 """
 from __future__ import annotations
 
@@ -18,33 +23,51 @@ from ..ops import autograd as F
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: Config, dtype, device):
+    def __init__(self, cfg: Config, dtype, device, n_kv_heads=None, qkv_bias=False):
         super().__init__()
-        C, I = cfg.C, cfg.I
+        C, I, H, hd = cfg.C, cfg.I, cfg.H, cfg.hd
+        self.Hkv = H if n_kv_heads is None else int(n_kv_heads)
+        if self.Hkv <= 0 or H % self.Hkv:
+            raise ValueError(f"n_kv_heads={n_kv_heads} must divide H={H}")
         mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
-        self.ln1, self.qkv, self.o = mk(C), mk(3 * C, C), mk(C, C)
+        self.ln1, self.qkv, self.o = mk(C), mk((H + 2 * self.Hkv) * hd, C), mk(C, C)
+        self.qkv_bias = nn.Parameter(torch.zeros((H + 2 * self.Hkv) * hd, dtype=dtype, device=device)) if qkv_bias else None
         self.ln2, self.gate_up, self.down = mk(C), mk(2 * I, C), mk(C, I)
         self.cfg = cfg
+
+    def _full_qkv(self, qkv):
+        """[N, (H + 2 Hkv) hd] -> [N, 3 H hd]: every K / V head serves H / Hkv consecutive query heads."""
+        c = self.cfg
+        if self.Hkv == c.H:
+            return qkv
+        N, H, hd, rep = qkv.shape[0], c.H, c.hd, c.H // self.Hkv
+        q, k, v = qkv.split([H * hd, self.Hkv * hd, self.Hkv * hd], dim=1)
+        grow = lambda t: t.view(N, self.Hkv, 1, hd).expand(N, self.Hkv, rep, hd).reshape(N, H * hd)
+        return torch.cat([q, grow(k), grow(v)], dim=1)
 
     def forward(self, x, cos, sin, B):
         c = self.cfg
         h = F.rmsnorm(x, self.ln1, c.eps)
-        a = F.rope_causal_attention(F.linear(h, self.qkv), cos, sin, B, c.T, c.H, c.hd)
+        qkv = F.linear(h, self.qkv)
+        if self.qkv_bias is not None:
+            qkv = qkv + self.qkv_bias
+        a = F.rope_causal_attention(self._full_qkv(qkv).contiguous(), cos, sin, B, c.T, c.H, c.hd)
         x = x + F.linear(a, self.o)
         h = F.rmsnorm(x, self.ln2, c.eps)
         return x + F.linear(F.swiglu(F.linear(h, self.gate_up)), self.down)
 
 
 class Decoder(nn.Module):
-    def __init__(self, cfg: Config, device="cpu", dtype=None):
+    def __init__(self, cfg: Config, device="cpu", dtype=None, n_kv_heads=None, qkv_bias=False):
         super().__init__()
         cfg.validate()
+        self.flat_compatible = (n_kv_heads in (None, cfg.H)) and not qkv_bias
         device = torch.device(device)
         if dtype is None:
             dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
         self.cfg = cfg
         self.wte = nn.Parameter(torch.empty(cfg.V, cfg.C, dtype=dtype, device=device))
-        self.blocks = nn.ModuleList([Block(cfg, dtype, device) for _ in range(cfg.L)])
+        self.blocks = nn.ModuleList([Block(cfg, dtype, device, n_kv_heads, qkv_bias) for _ in range(cfg.L)])
         self.lnf = nn.Parameter(torch.empty(cfg.C, dtype=dtype, device=device))
         self.lm = nn.Parameter(torch.empty(cfg.V, cfg.C, dtype=dtype, device=device))
         cos, sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, device)
@@ -69,6 +92,8 @@ class Decoder(nn.Module):
 
     @torch.no_grad()
     def load_flat(self, flat: torch.Tensor):
+        if not self.flat_compatible:
+            raise ValueError("grouped-query / biased modules have no flat-buffer layout")
         for p, off in self.named_flat():
             p.copy_(flat[off:off + p.numel()].view(p.shape))
 

@@ -255,3 +255,49 @@ def test_fp8_forward_option_rounds_forward_operands_only():
     import pytest
     with pytest.raises(ValueError):
         GPT(cfg, B, fp8_fwd=True, lmce_chunk=32)
+
+
+def test_module_tree_grouped_query_attention_and_qkv_bias():
+    """Decoder(n_kv_heads=2, qkv_bias=True) (the prototype model's Qwen-style options, csrc/include/model.h:17-60)
+    against a plain PyTorch restatement with SDPA over repeated K / V heads: loss and all parameter gradients."""
+    import pytest
+    from ml_b200.models.modules import Decoder
+    cfg = Config(V=61, C=32, L=2, H=4, I=48, T=8)
+    B, Hkv, hd = 2, 2, cfg.hd
+    torch.manual_seed(0)
+    m = Decoder(cfg, n_kv_heads=Hkv, qkv_bias=True)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.copy_(torch.ones_like(p) + 0.1 * torch.randn_like(p) if p.dim() == 1 and "bias" not in n else 0.05 * torch.randn_like(p))
+    assert m.blocks[0].qkv.shape == ((cfg.H + 2 * Hkv) * hd, cfg.C) and not m.flat_compatible
+    with pytest.raises(ValueError):
+        m.load_flat(torch.zeros(10))
+    ids = torch.randint(0, cfg.V, (B * cfg.T,), dtype=torch.int32)
+    tgt = torch.randint(0, cfg.V, (B * cfg.T,), dtype=torch.int32)
+    loss = m(ids, tgt)
+    loss.backward()
+
+    # plain restatement on detached copies of the same parameters
+    P = {n: p.detach().clone().requires_grad_(True) for n, p in m.named_parameters()}
+    rms = lambda x, w: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.eps) * w
+    h2 = hd // 2
+    cc, ss = m.cos.view(1, cfg.T, 1, h2), m.sin.view(1, cfg.T, 1, h2)
+    rope = lambda x: torch.cat([x[..., :h2] * cc - x[..., h2:] * ss, x[..., h2:] * cc + x[..., :h2] * ss], -1)
+    x = P["wte"][ids.long()].view(B, cfg.T, cfg.C)
+    for l in range(cfg.L):
+        g = lambda n: P[f"blocks.{l}.{n}"]
+        qkv = rms(x, g("ln1")) @ g("qkv").t() + g("qkv_bias")
+        q, k, v = qkv.split([cfg.H * hd, Hkv * hd, Hkv * hd], dim=-1)
+        q = rope(q.view(B, cfg.T, cfg.H, hd))
+        k = rope(k.view(B, cfg.T, Hkv, hd)).repeat_interleave(cfg.H // Hkv, dim=2)
+        v = v.view(B, cfg.T, Hkv, hd).repeat_interleave(cfg.H // Hkv, dim=2)
+        a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
+        x = x + a.transpose(1, 2).reshape(B, cfg.T, cfg.C) @ g("o").t()
+        gu = rms(x, g("ln2")) @ g("gate_up").t()
+        x = x + (F.silu(gu[..., :cfg.I]) * gu[..., cfg.I:]) @ g("down").t()
+    logits = rms(x, P["lnf"]) @ P["lm"].t()
+    ref = F.cross_entropy(logits.view(-1, cfg.V), tgt.long())
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 1e-5
+    for n, p in m.named_parameters():
+        assert torch.allclose(p.grad, P[n].grad, atol=2e-5, rtol=1e-4), n
