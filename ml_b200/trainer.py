@@ -32,7 +32,9 @@ class Trainer:
         if comm == "fused" and world > 1:
             from .parallel import symm
             alloc = lambda n, dt: symm.empty(n, dt, self.device, world)
-        self.model = GPT(cfg, B, self.device, alloc=alloc)
+        # chunked LM head / FP8-rounded forward: from the run configuration if set there, else from the environment
+        self.model = GPT(cfg, B, self.device, alloc=alloc, lmce_chunk=(self.run.lmce_chunk or None),
+                         fp8_fwd=(True if self.run.fp8_fwd else None))
         self.model.init_weights(seed)
         self.vision = None
         if vision is not None:
