@@ -307,3 +307,28 @@ def test_bench_clock_summary_picks_samples_of_the_timed_region():
     assert b.ClockSampler.summarise(["x, 0, 1500, 1965, 900, 0x4, Not Active, Not Active, Not Active, Active\n"],
                                     datetime.datetime(2026, 1, 1))["sm_mhz"] == 1500.0
     assert b.ClockSampler.summarise([], None) == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": None}
+
+
+def test_event_profiler_regions_cover_a_step():
+    """`Prof.mark` charges the time since the previous mark to the named region (train/gpt.cu:33-51); a decoder step
+    with the profiler attached reports the reference's region names, and the chunked LM head reports its own."""
+    from ml_b200.models import GPT
+    from ml_b200.utils.prof import Prof
+    from ml_b200.utils.rng import Stream
+    cfg = Config(V=64, C=32, L=2, H=2, I=64, T=16)
+    ids, tgt = Stream(1).token_pairs(2 * cfg.T, cfg.V)
+    for chunk, expect in ((0, {"F_qkv+rope", "F_attn", "F_mlp+norm", "F_lmhead", "B_ce", "B_lmhead", "B_mlp_gemm", "B_norm",
+                               "B_attn", "B_qkv_gemm"}),
+                          (24, {"F_qkv+rope", "F_attn", "F_mlp+norm", "B_lmce_stats", "B_lmce_grad", "B_mlp_gemm", "B_norm",
+                                "B_attn", "B_qkv_gemm"})):
+        g = GPT(cfg, 2, lmce_chunk=chunk)
+        g.init_weights(1)
+        g.prof = Prof("cpu")
+        g.prof.mark("start")
+        g.forward(ids)
+        g.backward(ids, tgt)
+        lines = []
+        agg = g.prof.report(out=lines.append)
+        assert expect <= set(agg), expect - set(agg)
+        assert all(v >= 0 for v in agg.values()) and lines[-1].split()[0] == "total"
+        assert abs(sum(agg.values()) - float(lines[-1].split()[1])) < 1e-2
