@@ -143,7 +143,12 @@ class RunConfig:
     @classmethod
     def from_env(cls, env=None) -> "RunConfig":
         e = env
+        src = os.environ if env is None else env
+        # which knobs were set explicitly (a few defaults differ by engine: e.g. the fused gradient step reduces in fp32
+        # unless ENTROPY_BF16_REDUCE=1 is asked for)
+        explicit = {k for k in src if k.startswith("ENTROPY_") and src.get(k, "") != ""}
         return cls(
+            extra={"explicit": explicit},
             accum=max(1, env_int("ENTROPY_ACCUM", 1, e)),
             log_every=max(1, env_int("ENTROPY_LOG_EVERY", 10, e)),
             bf16_reduce=env_int("ENTROPY_BF16_REDUCE", 1, e),
@@ -185,6 +190,37 @@ class RunConfig:
             B=env_int("ENTROPY_B", 16, e),
             comm=env_str("ENTROPY_COMM", "fused", e),
         )
+
+    # Knobs of the reference that are read here but change nothing in this design, with the reason.
+    NO_EFFECT = {
+        "ENTROPY_ATTN": "one tcgen05 flash-attention kernel replaces the cudnn / mat / packed / flash back ends",
+        "ENTROPY_RMS_ATOMIC": "RMSNorm backward is one deterministic kernel (no atomic / atomic-free pair)",
+        "ENTROPY_CE_ONLINE": "cross-entropy is always the fused online-softmax kernel",
+        "ENTROPY_CE_THREADS": "the cross-entropy kernel's block size is fixed",
+        "ENTROPY_MLP_DUAL": "weight-gradient and input-gradient GEMMs already run as separate persistent kernels",
+        "ENTROPY_BETA0_GRADS": "weight gradients are add-reduced by stream-K pieces, which needs the zero-fill",
+        "ENTROPY_AUTOTUNE": "the GEMMs are hand-written kernels with static shape heuristics (no library plans to time)",
+        "ENTROPY_AUTOTUNE_K": "see ENTROPY_AUTOTUNE",
+        "ENTROPY_LT_WS_MB": "no library workspace is used",
+        "ENTROPY_SKIP_GEMM_BWD": "read and never used by the reference either (train/gpt.cu:583)",
+        "ENTROPY_LMCE_FUSED_DX": "the chunked head feeds the tensor-core GEMMs; the direct dX kernel is not rebuilt",
+        "ENTROPY_LMCE_FUSED_DW": "the chunked head feeds the tensor-core GEMMs; the direct dW kernel is not rebuilt",
+    }
+
+    def ineffective_knobs(self):
+        """[(name, reason)] for every knob that was set explicitly and has no effect here."""
+        return sorted((k, v) for k, v in self.NO_EFFECT.items() if k in self.extra.get("explicit", ()))
+
+    def warn_ineffective(self, log=None):
+        """One line naming the knobs that are set but do nothing in this design (printed once by the CLI modes)."""
+        bad = self.ineffective_knobs()
+        if bad:
+            (log or print)("note: set but without effect here: " + "; ".join(f"{k} ({why})" for k, why in bad))
+        return bad
+
+    def skip_set(self):
+        """Stages removed by the ENTROPY_SKIP_* ablation knobs (train/gpt.cu:456-461,582), as the decoder's skip set."""
+        return {k for k in ("attn", "mlp", "head", "rope", "norm", "swiglu", "norm_bwd") if getattr(self, "skip_" + k)}
 
     def describe(self) -> str:
         d = asdict(self)

@@ -29,6 +29,9 @@ struct Loader {
   const uint16_t* tok = nullptr;
   int64_t ntok = 0, pos = 0;
   int B = 0, T = 0;
+  // Data-parallel striping: this reader serves windows `first`, `first + every`, `first + 2*every`, ... of the file (a
+  // window is B*T tokens), so `every` ranks with first = 0..every-1 read disjoint windows, prefetch included.
+  int64_t first = 0, every = 1;
 };
 
 struct Job { int slot; int32_t* ids; int32_t* tgt; };
@@ -47,10 +50,10 @@ struct Pipe {
 
 void fill(Loader* ld, int32_t* ids, int32_t* tgt) {
   const int64_t n = (int64_t)ld->B * ld->T;
-  if (ld->pos + n + 1 > ld->ntok) ld->pos = 0;
+  if (ld->pos + n + 1 > ld->ntok) ld->pos = ld->first * n;   // wrap to this reader's first window
   const uint16_t* w = ld->tok + ld->pos;
   for (int64_t i = 0; i < n; i++) { ids[i] = w[i]; tgt[i] = w[i + 1]; }
-  ld->pos += n;
+  ld->pos += n * ld->every;
 }
 
 void worker(Pipe* p) {
@@ -103,6 +106,15 @@ void* mlb_loader_open(const char* path, int B, int T, int* err) {
 int64_t mlb_loader_ntok(void* h) { return ((Loader*)h)->ntok; }
 int64_t mlb_loader_pos(void* h) { return ((Loader*)h)->pos; }
 void mlb_loader_set_pos(void* h, int64_t pos) { ((Loader*)h)->pos = pos; }
+// Reader `first` of `every` (data-parallel rank / world).  Returns 1 if the file is too short for that many disjoint
+// readers (fewer than `every` whole windows), else 0; the position moves to the reader's first window.
+int mlb_loader_set_stride(void* h, int64_t first, int64_t every) {
+  Loader* ld = (Loader*)h;
+  const int64_t n = (int64_t)ld->B * ld->T;
+  if (every < 1 || first < 0 || first >= every || every * n + 1 > ld->ntok) return 1;
+  ld->first = first; ld->every = every; ld->pos = first * n;
+  return 0;
+}
 void mlb_loader_next(void* h, int32_t* ids, int32_t* tgt) { fill((Loader*)h, ids, tgt); }
 void mlb_loader_close(void* h) {
   Loader* ld = (Loader*)h;

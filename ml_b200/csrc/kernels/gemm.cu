@@ -18,6 +18,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <vector>
 
 
 namespace {
@@ -639,6 +640,21 @@ EncodeTiledFn get_encode() {
 std::mutex g_tmap_mu;
 typedef std::tuple<const void*, uint64_t, uint64_t, uint64_t, uint32_t, uint32_t, int> TmapKey;
 std::map<TmapKey, CUtensorMap*> g_tmaps;
+// The cache is keyed on base pointers.  A training step uses a few hundred distinct (pointer, shape) pairs; a caller
+// whose allocator hands out ever new addresses would grow it without bound, so it is emptied when it reaches this many
+// entries.  The maps themselves are never freed before that point is long past: kernels receive them BY VALUE
+// (__grid_constant__ parameters), so a launch that is still queued does not read this memory; entries dropped here are
+// parked on a retired list that is released at the following reset.
+constexpr size_t TMAP_CACHE_MAX = 8192;
+std::vector<CUtensorMap*> g_tmaps_retired;
+void tmap_cache_trim_locked() {
+  if (g_tmaps.size() < TMAP_CACHE_MAX) return;
+  for (CUtensorMap* m : g_tmaps_retired) delete m;
+  g_tmaps_retired.clear();
+  for (auto& kv : g_tmaps)
+    if (kv.second) g_tmaps_retired.push_back(kv.second);
+  g_tmaps.clear();
+}
 
 }  // namespace
 
@@ -663,6 +679,7 @@ const CUtensorMap* mlb_tmap_cached(const void* base, uint64_t rows, uint64_t col
   TmapKey key(base, rows, cols, pitch_elems, box_rows, box_cols, elem_bytes);
   auto it = g_tmaps.find(key);
   if (it != g_tmaps.end()) return it->second;
+  tmap_cache_trim_locked();
   CUtensorMap* m = new CUtensorMap;
   if (!mlb_make_tmap(m, base, rows, cols, pitch_elems, box_rows, box_cols, elem_bytes)) { delete m; return nullptr; }
   g_tmaps[key] = m;
@@ -676,6 +693,7 @@ const CUtensorMap* mlb_tmap_mn3d_cached(const void* base, uint64_t k_rows, uint6
   TmapKey key(base, k_rows, mn_cols, pitch_elems, chunks, 0xffffffffu, -3);
   auto it = g_tmaps.find(key);
   if (it != g_tmaps.end()) return it->second;
+  tmap_cache_trim_locked();
   CUtensorMap* m = new CUtensorMap;
   cuuint64_t dims[3] = {64, k_rows, mn_cols / 64};
   cuuint64_t strides[2] = {pitch_elems * 2, 128};
@@ -979,6 +997,7 @@ MLB_API int mlb_mma_probe(long long* cycles, int N, int a_tmem, int reps, cudaSt
   return (int)cudaGetLastError();
 }
 
+MLB_API int mlb_tmap_cache_size() { std::lock_guard<std::mutex> lk(g_tmap_mu); return (int)g_tmaps.size(); }
 MLB_API void mlb_gemm_force_simt(int on) { g_force_simt = on; }
 MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
 MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }

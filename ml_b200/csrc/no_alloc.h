@@ -13,7 +13,9 @@
 //   * C (row width) must be at most MLB_NOALLOC_RMS_MAX_C, and C * 4 bytes of shared memory must fit the default 48 KB;
 //     anything larger is refused with MLB_NOALLOC_ERR_TOO_LARGE and a message (mlb_rmsnorm_bwd_noalloc_error()).
 //   * The first call on each device looks up the device address of the scratch array (cudaGetSymbolAddress) with that
-//     device current.  Make that first call outside of any stream capture.
+//     device current.  Make that first call outside of any stream capture.  Host threads that make their first calls
+//     on one device at the same moment may each run that look-up; they all obtain and store the same address (a plain
+//     pointer-sized write of an identical value), so the set-up needs no lock and the order does not matter.
 //   * All calls on a device share the one scratch array, and the array keeps whatever the previous call left in it.
 //     The entry point clears the counters that have to start at zero on the caller's stream before each launch.
 //     Two calls that overlap on the GPU (different streams, no ordering between them) race on the scratch.

@@ -35,6 +35,12 @@ class TokenLoader:
         self.B, self.T, self.path = B, T, path
         self.ntok = lib().mlb_loader_ntok(self.h)
 
+    def set_stride(self, first: int, every: int):
+        """Data-parallel striping: this loader serves windows first, first + every, ... (rank, world); the ranks' windows
+        are disjoint, the prefetched ones included, and the position wraps to the loader's own first window."""
+        if lib().mlb_loader_set_stride(self.h, int(first), int(every)):
+            raise OSError(f"{self.path}: {self.ntok} tokens are fewer than {every} windows of {self.B}x{self.T}")
+
     @property
     def pos(self) -> int:
         return lib().mlb_loader_pos(self.h)

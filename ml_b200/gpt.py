@@ -191,7 +191,9 @@ def mode_bench(argv):
     tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, use_graph=bool(run.graph))
     ids, tgt = bench_batch(B, cfg.T, cfg.V)
     tr.set_batch(ids.to(dev), tgt.to(dev))
-    tr.model.skip = {k for k in ("attn", "mlp", "head", "rope", "norm", "swiglu") if getattr(run, "skip_" + k)}
+    tr.model.skip = run.skip_set()
+    tr.skip_adamw = bool(run.skip_adamw)      # ENTROPY_SKIP_ADAMW (train/gpt.cu:1398): time forward + backward alone
+    run.warn_ineffective()
     print(f"config: V={cfg.V} C={cfg.C} L={cfg.L} H={cfg.H} I={cfg.I} T={cfg.T} B={B}  params={tr.model.np / 1e6:.1f}M")
     for _ in range(3):
         tr.step()
@@ -271,10 +273,13 @@ def _train_loop(argv, ddp):
                  use_graph=bool(run.train_graph) and a.warmup_ratio <= 0)
     loader = TokenLoader(a.bin, B * tr.accum, cfg.T)
     if rank == 0:
+        run.warn_ineffective()
         print(f"loader: {a.bin}  {loader.ntok} tokens")
-    # every rank reads a disjoint stride of the file: rank r starts r windows in, and skips world windows per step
+    # every rank reads a disjoint stride of the file: rank r serves windows r, r + world, r + 2*world, ... (the stride
+    # lives in the loader, so the pipe's prefetched windows follow it too)
     win = B * tr.accum * cfg.T
-    loader.pos = (rank * win) % max(1, loader.ntok - win - 1)
+    if world > 1:
+        loader.set_stride(rank, world)
     start_step, tokens_seen = 0, 0
     if a.ckpt_dir and a.resume != -1:
         st = ck.latest_step(a.ckpt_dir) if a.resume == -2 else a.resume
@@ -282,7 +287,9 @@ def _train_loop(argv, ddp):
         if info is not None:
             tr.model.sync_params()
             start_step, tokens_seen, tr.t = info["step"], info["tokens_seen"], info["opt_t"]
-            loader.pos = info["loader_pos"]
+            # the payload is rank 0's (complete after consolidate_state); the data position is per rank
+            own = ck.load_state(a.ckpt_dir, st, rank)
+            loader.pos = own["loader_pos"] if own is not None else info["loader_pos"] + rank * win
             if rank == 0:
                 print(f"resumed from step {start_step} (loss {info['loss']:.4f}, {tokens_seen} tokens seen)")
         elif rank == 0:
@@ -343,9 +350,6 @@ def _train_loop(argv, ddp):
         if hb:
             with open(os.path.join(hb, f"rank_{rank}"), "w") as f:
                 f.write(str(step))
-        if world > 1:
-            # the file is striped over ranks: skip the windows the other ranks consume
-            loader.pos = (loader.pos + (world - 1) * win) % max(1, loader.ntok - win - 1)
         tokens_seen += win * world
         if (step + 1) % run.log_every == 0 or step + 1 == a.steps:
             loss = tr.loss()
@@ -367,14 +371,25 @@ def _train_loop(argv, ddp):
                 print(f"step {step + 1:5d} | eval loss {ev:.4f}")
                 if logger:
                     logger.log_scalar(step + 1, "eval/loss", ev)
-        if writer and a.save_every > 0 and (step + 1) % a.save_every == 0:
-            writer.save(a.ckpt_dir, step + 1, loss if loss == loss else 0.0, tokens_seen, tr.model.master, tr.model.m,
-                        tr.model.v, loader_pos=pipe.slot_pos[(step + 1) % pipe.n], opt_t=tr.t)
+        if a.ckpt_dir and a.save_every > 0 and (step + 1) % a.save_every == 0:
+            # the fused data-parallel step keeps master / m / v current only for the shard a rank owns: make every rank's
+            # copy complete first (a collective: all ranks take part), then rank 0 writes the payload; every rank
+            # records its own data position; meta.bin is published once all of that is on disk
+            tr.consolidate_state()
+            next_pos = pipe.slot_pos[(step + 1) % pipe.n]
+            if rank != 0:
+                ck.save_state(a.ckpt_dir, step + 1, rank, next_pos, tr.t)
+            if world > 1:
+                dist.barrier()
+            if writer:
+                writer.save(a.ckpt_dir, step + 1, loss if loss == loss else 0.0, tokens_seen, tr.model.master, tr.model.m,
+                            tr.model.v, loader_pos=next_pos, opt_t=tr.t)
     if writer:
         writer.close()
     if logger:
         logger.close()
     pipe.close()
+    tr.close()
     if ddp:
         shutdown()
     return 0
@@ -397,6 +412,8 @@ def mode_bench_ddp(argv):
     steps = int(argv[1]) if len(argv) > 1 else 30
     run = RunConfig.from_env()
     tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, world=world, rank=rank, use_graph=bool(run.graph))
+    if rank == 0:
+        run.warn_ineffective()
     ids, tgt = [], []
     for k in range(tr.accum):
         a, b = bench_batch(B, cfg.T, cfg.V, rank)

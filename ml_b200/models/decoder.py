@@ -191,7 +191,12 @@ class GPT:
             if prefix is not None and n_pre > 0:
                 ops.set_prefix(x0, prefix, B, T, n_pre)
         self._pre("layer0" if c.L > 0 else "head", "fwd")
-        ops.rmsnorm_fwd(sl(self.ln1[0]), sl(self.rstd1[0]), x0, self.P(Lo.layer(0).ln1, C), c.eps)
+        # ENTROPY_SKIP_NORM (train/gpt.cu:460,474-481): the normalisations are left out (the residual adds stay, the norm
+        # outputs keep whatever they held) to attribute their time; ENTROPY_SKIP_NORM_BWD (:582) does the same for the
+        # three RMSNorm backward calls.  Results are meaningless under either.
+        skip_norm = "norm" in self.skip
+        if not skip_norm:
+            ops.rmsnorm_fwd(sl(self.ln1[0]), sl(self.rstd1[0]), x0, self.P(Lo.layer(0).ln1, C), c.eps)
         resid_in = x0
         for l in range(c.L):
             o = Lo.layer(l)
@@ -218,8 +223,11 @@ class GPT:
             self._mark("F_attn")
             proj = sl(self.proj)
             ops.linear_fwd(proj, sl(self.atty[l]), self.P(o.o, C, C))
-            ops.add_rmsnorm_fwd(sl(self.resid1[l]), sl(self.ln2[l]), sl(self.rstd2[l]), resid_in, proj,
-                                self.P(o.ln2, C), c.eps)
+            if skip_norm:
+                ops.residual_add(sl(self.resid1[l]), resid_in, proj)
+            else:
+                ops.add_rmsnorm_fwd(sl(self.resid1[l]), sl(self.ln2[l]), sl(self.rstd2[l]), resid_in, proj,
+                                    self.P(o.ln2, C), c.eps)
             if "mlp" not in self.skip:
                 ops.linear_fwd(sl(self.gu[l]), *self._fwd_operands(sl(self.ln2[l]), o.gate, 2 * I, C))
                 if "swiglu" not in self.skip:
@@ -235,7 +243,10 @@ class GPT:
                 nw, nout, nrstd = self.P(Lo.layer(l + 1).ln1, C), sl(self.ln1[l + 1]), sl(self.rstd1[l + 1])
             else:
                 nw, nout, nrstd = self.P(Lo.off_lnf, C), sl(self.lnf_out), sl(self.rstdf)
-            ops.add_rmsnorm_fwd(sl(self.resid2[l]), nout, nrstd, sl(self.resid1[l]), proj, nw, c.eps)
+            if skip_norm:
+                ops.residual_add(sl(self.resid2[l]), sl(self.resid1[l]), proj)
+            else:
+                ops.add_rmsnorm_fwd(sl(self.resid2[l]), nout, nrstd, sl(self.resid1[l]), proj, nw, c.eps)
             resid_in = sl(self.resid2[l])
             self._mark("F_mlp+norm")
         if self.lmce_chunk > 0:
@@ -264,6 +275,7 @@ class GPT:
             self.grads.zero_()
         valid = valid_tokens if valid_tokens is not None else BT - B * n_pre
         dln, dresid, dresid1 = sl(self.dln), sl(self.dresid), sl(self.dresid1)
+        skip_nb = "norm_bwd" in self.skip
         if d_out is not None:
             dresid.copy_(d_out)
         else:
@@ -279,7 +291,8 @@ class GPT:
                 ops.linear_dx(dln, logits, self.P(Lo.off_lm, V, C))
                 self._mark("B_lmhead")
             last = sl(self.resid2[c.L - 1]) if c.L > 0 else sl(self.x0)
-            ops.rmsnorm_bwd(dresid, self.G(Lo.off_lnf, C), dln, last, self.P(Lo.off_lnf, C), sl(self.rstdf), None)
+            if not skip_nb:
+                ops.rmsnorm_bwd(dresid, self.G(Lo.off_lnf, C), dln, last, self.P(Lo.off_lnf, C), sl(self.rstdf), None)
             self._mark("B_norm")
             self._hook("lm", Lo.off_lm, V * C)
             self._hook("lnf", Lo.off_lnf, C)
@@ -293,8 +306,9 @@ class GPT:
             ops.linear_dw(self.G(o.gate, 2 * I, C), dgu, sl(self.ln2[l]))
             ops.linear_dx(dln, dgu, self.P(o.gate, 2 * I, C))
             self._mark("B_mlp_gemm")
-            ops.rmsnorm_bwd(dresid1, self.G(o.ln2, C), dln, sl(self.resid1[l]), self.P(o.ln2, C),
-                            sl(self.rstd2[l]), dresid)
+            if not skip_nb:
+                ops.rmsnorm_bwd(dresid1, self.G(o.ln2, C), dln, sl(self.resid1[l]), self.P(o.ln2, C),
+                                sl(self.rstd2[l]), dresid)
             self._mark("B_norm")
             ops.linear_dw(self.G(o.o, C, C), dresid1, sl(self.atty[l]))
             ops.linear_dx(datty, dresid1, self.P(o.o, C, C))
@@ -312,7 +326,8 @@ class GPT:
             ops.linear_dx(dln, dqkv, self.P(o.qkv, 3 * C, C))
             self._mark("B_qkv_gemm")
             x_in = sl(self.resid2[l - 1]) if l > 0 else sl(self.x0)
-            ops.rmsnorm_bwd(dresid, self.G(o.ln1, C), dln, x_in, self.P(o.ln1, C), sl(self.rstd1[l]), dresid1)
+            if not skip_nb:
+                ops.rmsnorm_bwd(dresid, self.G(o.ln1, C), dln, x_in, self.P(o.ln1, C), sl(self.rstd1[l]), dresid1)
             self._mark("B_norm")
             self._hook(f"layer{l}", Lo.layer_base(l), Lo.layer_stride)
         if not has_embed:

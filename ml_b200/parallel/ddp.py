@@ -11,8 +11,10 @@ comm modes
           buffer, all-reduced, and cast back with the mean scale folded in (cast_f2b -> ncclAllReduce ->
           cast_b2f_scale in the reference).  This is the baseline mode.
   "fused" one sm_100a kernel per bucket over NVLink peer memory (ml_b200.parallel.fused): reduce-scatter of the
-          bucket by peer loads, mean scale, AdamW on this rank's shard of master/m/v, and the updated bf16
-          parameters written to every peer; no NCCL call and no separate optimizer pass.
+          bucket by peer loads or in-switch reduction, mean scale, AdamW on this rank's shard of master/m/v, and the
+          updated bf16 parameters written to every peer; no NCCL call and no separate optimizer pass.  The kernels run
+          behind backward on a side stream.  fused_bf16 selects the bf16 staging form of the reduction
+          (ENTROPY_BF16_REDUCE=1 set explicitly); the default sums the fp32 gradients (exact mean).
 """
 from __future__ import annotations
 
@@ -26,7 +28,8 @@ from .. import ops
 
 class DDP:
     def __init__(self, model, world: int, accum: int = 1, bf16_reduce: bool = True, comm: str = "nccl",
-                 group=None, overlap_opt: bool = False, opt_hyper: Optional[dict] = None, rank: int = 0):
+                 group=None, overlap_opt: bool = False, opt_hyper: Optional[dict] = None, rank: int = 0,
+                 fused_bf16: bool = False):
         self.model, self.world, self.accum = model, world, max(1, accum)
         self.cuda = model.device.type == "cuda"
         self.bf16_reduce = bool(bf16_reduce) and self.cuda
@@ -47,7 +50,7 @@ class DDP:
         self.fused = None
         if comm == "fused" and self.cuda:
             from .fused import FusedGradEngine
-            self.fused = FusedGradEngine(model, world, rank, group)
+            self.fused = FusedGradEngine(model, world, rank, group, bf16_reduce=fused_bf16)
         model.bucket_hook = self.on_bucket
 
     # ------------------------------------------------------------------

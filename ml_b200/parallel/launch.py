@@ -52,6 +52,9 @@ class Supervisor:
         for r in range(self.nproc):
             e = dict(self.env, RANK=str(r), WORLD_SIZE=str(self.nproc), WORLD=str(self.nproc), LOCAL_RANK=str(self.devices[r]),
                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), ENTROPY_ATTEMPT=str(self.attempts))
+            # this supervisor stops ranks while their peers may still run: no NVLink multicast bindings in the children
+            # (a rank that dies bound to a multicast object faults its peers' GPUs), in NCCL, torch or our own kernels
+            e.update(NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", ENTROPY_FUSED_MULTIMEM="0")
             if self.hb_dir:
                 e["ENTROPY_HEARTBEAT_DIR"] = self.hb_dir
                 try:

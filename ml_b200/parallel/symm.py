@@ -7,11 +7,26 @@ the pointer table has one entry.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
 
+def multimem_wanted() -> bool:
+    """NVLS policy of the fused kernels (ENTROPY_FUSED_MULTIMEM, default on): when on, symmetric buffers are bound to an
+    NVLink multicast object where the fabric offers one and the kernels use `multimem.ld_reduce` / `multimem.st`.
+    Elastic set-ups, where a rank may go away while its peers keep running (the supervisor of parallel/launch.py, the
+    rank-leaves tests), turn it off: a rank that dies while its memory is bound to a multicast object raises NVLink
+    faults on its peers' GPUs, plain peer mappings do not."""
+    return os.environ.get("ENTROPY_FUSED_MULTIMEM", "1") not in ("0", "false", "")
+
+
 def _symm():
+    if not multimem_wanted():
+        # torch binds symmetric allocations to a multicast object at rendezvous unless told not to, whatever the
+        # kernels use afterwards; the switch has to be in the environment before the first allocation
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
     import torch.distributed._symmetric_memory as symm_mem
     return symm_mem
 
@@ -42,7 +57,7 @@ class PeerTable:
             ptrs = [int(p) for p in self.handle.buffer_ptrs]
             off = tensor.data_ptr() - ptrs[self.handle.rank]     # the tensor may start inside the allocation
             self.table = torch.tensor([p + off for p in ptrs], dtype=torch.int64, device=tensor.device)
-            mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+            mc = int(getattr(self.handle, "multicast_ptr", 0) or 0) if multimem_wanted() else 0
             self.multicast_ptr = mc + off if mc else 0
 
     @property

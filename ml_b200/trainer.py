@@ -45,10 +45,14 @@ class Trainer:
         else:
             self.n_pre = 0
         self.hyper = dict(lr=lr, b1=b1, b2=b2, eps=eps, wd=wd)
+        fused_bf16 = bool(self.run.bf16_reduce) and "ENTROPY_BF16_REDUCE" in self.run.extra.get("explicit", ())
         self.ddp = DDP(self.model, world, self.run.accum, bool(self.run.bf16_reduce), comm, group,
-                       overlap_opt=bool(self.run.ddp_overlap_opt), opt_hyper=self.hyper, rank=rank)
+                       overlap_opt=bool(self.run.ddp_overlap_opt) if world > 1 else self.run.overlap_opt == 1,   # train/gpt.cu:1016-1023,1569
+                       opt_hyper=self.hyper, rank=rank,
+                       fused_bf16=fused_bf16 or bool(self.run.extra.get("fused_bf16", False)))
         self.accum = self.ddp.accum
         self.t = 1
+        self.skip_adamw = False    # ablation: leave the optimizer out (single GPU, library-collective mode)
         # the vision tower's gradients are data-parallel too (the reference's multimodal modes are single-GPU only)
         self.vfused = None
         if self.vision is not None and self.ddp.fused is not None and self.vision.np % 4 == 0:
@@ -91,7 +95,7 @@ class Trainer:
             self._micro(k)
         done = self.ddp.finish()
         h = self.hyper
-        if not done:
+        if not done and not self.skip_adamw:
             self.ddp.t = self.t
             self.ddp.step_optimizer()
         if self.vision is not None:
@@ -116,8 +120,9 @@ class Trainer:
         self._push_hyper()
         if self.use_graph:
             if self.graph is None:
-                self._capture()
-            self.graph.replay()
+                self._capture()          # runs this step eagerly (it is the warm-up of the capture), then records
+            else:
+                self.graph.replay()
         else:
             self._step_body()
         self.t += 1
@@ -144,7 +149,9 @@ class Trainer:
             self.d_hyper_v.copy_(self.h_hyper_v, non_blocking=True)
 
     def _capture(self):
-        # warm the allocator / tensor-map caches outside capture, then record the step once
+        """Runs the current step eagerly on a side stream (that warms the allocator and the tensor-map caches, and it IS
+        this step: the caller does not replay after a capture, so the first optimizer step is applied once), then
+        records the same work into a graph; recording executes nothing."""
         s = torch.cuda.Stream(self.device)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -166,11 +173,45 @@ class Trainer:
         self.h_loss.copy_(self.d_loss, non_blocking=True)
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()
+            self._check_kernels()
         return float(self.h_loss[0])
+
+    def _check_kernels(self):
+        """After a synchronisation: a kernel that gave up (a bounded wait on a peer that ran out, arguments it refused)
+        has left a non-zero error word.  The step it belonged to is invalid - in the fused data-parallel step that rank
+        skipped its update while its peers went on - so raise and let the caller (or the supervisor) restart from a
+        checkpoint instead of training on with diverged ranks."""
+        from .ops import native
+        err = native.get_error()
+        if err:
+            raise RuntimeError(f"kernel error word {err:#x} (code {err >> 24}, detail {err & 0xFFFFFF:#x}); "
+                               f"the results since the last check are invalid")
+
+    def consolidate_state(self):
+        """Makes the fp32 master weights and AdamW moments complete on every rank.  The fused data-parallel step keeps
+        them current only for the shard a rank owns (the bf16 parameters are what every rank receives), so this runs
+        before a checkpoint is written; a collective, every rank must call it.  No-op in the other modes."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        for eng in (self.ddp.fused, self.vfused):
+            if eng is not None:
+                eng.consolidate()
+
+    def close(self):
+        """Drops the captured graph (a communicator cannot be torn down while a graph that recorded its collectives is
+        alive) and waits for the device."""
+        if self.graph is not None:
+            self.graph.reset()
+            self.graph = None
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
 
     def set_batch(self, ids: torch.Tensor, tgt: torch.Tensor):
         self.ids.copy_(ids.view(self.accum, -1))
         self.tgt.copy_(tgt.view(self.accum, -1))
 
     def loss(self) -> float:
-        return float(self.d_loss.item())
+        v = float(self.d_loss.item())
+        if self.device.type == "cuda":
+            self._check_kernels()
+        return v

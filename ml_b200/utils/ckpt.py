@@ -134,6 +134,28 @@ def _read(path: str, numel: int, dtype=torch.float32) -> torch.Tensor:
     return t
 
 
+def save_state(root: str, step: int, rank: int, loader_pos: int, opt_t: int):
+    """state_rank_<r>.bin of a rank that writes no payload (data-parallel ranks other than 0 record where their own
+    reader stands): int64 {loader position, optimizer step, 0, 0}."""
+    d = step_dir(root, step)
+    rc = lib().mlb_mkdirs(d.encode())
+    if rc:
+        raise OSError(rc, f"mkdir {d}")
+    st = torch.tensor([loader_pos, opt_t, 0, 0], dtype=torch.int64)
+    rc = lib().mlb_write_blob(os.path.join(d, f"state_rank_{rank}.bin").encode(), st.data_ptr(), 32)
+    if rc:
+        raise OSError(rc, "write state_rank")
+
+
+def load_state(root: str, step: int, rank: int):
+    """dict(loader_pos, opt_t) of `rank`, or None when that rank left no state file."""
+    try:
+        st = _read(os.path.join(step_dir(root, step), f"state_rank_{rank}.bin"), 4, torch.int64)
+    except FileNotFoundError:
+        return None
+    return dict(loader_pos=int(st[0]), opt_t=int(st[1]))
+
+
 def load(root: str, step: int, master, m, v, rank: int = 0, shard=None, vision=None):
     """Restores buffers in place; returns dict(step, loss, tokens_seen, loader_pos, opt_t)."""
     meta = read_meta(root, step)

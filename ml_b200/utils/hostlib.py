@@ -22,6 +22,7 @@ def lib():
         "mlb_loader_ntok": (i64, [vp]),
         "mlb_loader_pos": (i64, [vp]),
         "mlb_loader_set_pos": (None, [vp, i64]),
+        "mlb_loader_set_stride": (i32, [vp, i64, i64]),
         "mlb_loader_next": (None, [vp, vp, vp]),
         "mlb_loader_close": (None, [vp]),
         "mlb_pipe_create": (vp, [vp, i32]),

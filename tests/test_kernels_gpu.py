@@ -23,12 +23,22 @@ def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
     return (torch.randn(*shape, device=dev(), dtype=torch.float32) * scale).to(dtype)
 
 
-def close(a, b, rtol=2e-2, atol=2e-2, name=""):
+def close(a, b, rtol=2e-2, atol=2e-2, name="", fro=None):
+    """Two bounds.  Max norm: no single element is off by more than atol + rtol * max|ref|.  Relative Frobenius norm:
+    ||a - ref|| / ||ref|| <= fro, which catches what the first cannot - an error confined to small-magnitude elements, a
+    bias of a percent of the peak, a wrong low-order bit pattern spread over the tensor.  Default fro: 4e-3 for bf16
+    outputs (one bf16 rounding is 2^-9 relative at worst, ~1.1e-3 rms), 1e-3 for fp32 outputs."""
+    if fro is None:
+        fro = 4e-3 if a.dtype == torch.bfloat16 else 1e-3
     a, b = a.float(), b.float()
     err = (a - b).abs().max().item()
     ref_mag = b.abs().max().item()
     assert torch.isfinite(a).all(), f"{name}: non-finite output"
     assert err <= atol + rtol * ref_mag, f"{name}: max err {err} vs ref magnitude {ref_mag}"
+    den = b.double().norm().item()
+    if den > 0:
+        rel = (a.double() - b.double()).norm().item() / den
+        assert rel <= fro, f"{name}: relative Frobenius error {rel:.3e} > {fro:.1e}"
 
 
 @pytest.fixture(autouse=True)
