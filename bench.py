@@ -1,15 +1,23 @@
 #!/usr/bin/env python
-"""Headline benchmark: training tokens/s of the 12-layer / 768-wide decoder (`bench 16 20` / `bench_ddp`).
+"""Benchmarks of the named configurations; the default is the headline one.
 
-    python bench.py --gpus N --steps K --warmup W            # this framework
-    python bench.py --impl reference --gpus N ...            # the unmodified reference binary (baseline/_ref/gpt)
+    python bench.py --gpus N --steps K --warmup W                    # this framework, config `lm`
+    python bench.py --impl reference --gpus N ...                    # the unmodified reference binary (baseline/_ref/gpt)
+    python bench.py --config accum|mm|fsdp ...                       # the other configurations (both arms where one exists)
 
-Config (fixed): L=12 C=768 H=12 I=2048 T=1024 V=50304, B=16 per GPU, bf16 compute, fp32 master/grads/AdamW,
-synthetic uniform tokens, random-init weights.  One "step" = forward + backward + gradient reduction + AdamW.
-Timing: W untimed warm-up steps, then exactly K steps between CUDA events bracketed by barrier + synchronize,
-max over ranks.  Every step streams several GB of activations and gradients (far more than the 126 MB L2), so
-no extra L2 flush is needed between iterations.  `e2e` repeats the measurement through `Trainer.step_host`:
-each step copies its tokens from pinned host memory and reads the loss back.
+Configurations (all: bf16 compute, fp32 master / gradients / AdamW, synthetic uniform tokens, random-init weights):
+  lm     `bench 16` / `bench_ddp`: L=12 C=768 H=12 I=2048 T=1024 V=50304, B=16 per GPU.  One step = forward + backward +
+         gradient reduction + AdamW.
+  accum  the same decoder, B=48 per GPU, 16 micro-batches per optimizer step, bf16 gradient reduction, CUDA-graph
+         replay; one step = one optimizer step (reference: `ENTROPY_ACCUM=16 ENTROPY_BF16_REDUCE=1 gpt bench_ddp 48 K`).
+  mm     `mm_bench 2 K`: the same decoder behind a vision tower (196 patches of 16x16x3 fp32 pixels per image, 768 wide,
+         4 blocks, I=2048, projector), 828 text tokens, B=2 per GPU; loss on text positions.
+  fsdp   sharded 1.3 B decoder L=24 C=2048 H=16 I=5504 T=2048 V=50304, B=8 per GPU (the reference has no sharded path:
+         its arm prints `unavailable`; `--comm nccl` runs this framework's schedule on library collectives instead).
+Timing: W untimed warm-up steps (at least 3), then exactly K steps between CUDA events bracketed by barrier +
+synchronize, max over ranks.  Every step streams several GB of activations and gradients (far more than the 126 MB L2),
+so no extra L2 flush is needed between iterations.  `e2e` repeats the measurement through the public step call of the
+configuration: each step copies its inputs from pinned host memory and reads the loss back.
 """
 from __future__ import annotations
 
@@ -20,15 +28,20 @@ import re
 import statistics
 import subprocess
 import sys
+import sysconfig
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MODEL = dict(V=50304, C=768, L=12, H=12, I=2048, T=1024)
-B_PER_GPU = 16
+MODEL_FSDP = dict(V=50304, C=2048, L=24, H=16, I=5504, T=2048)
+B_PER_GPU = {"lm": 16, "accum": 48, "mm": 2, "fsdp": 8}
+ACCUM = {"lm": 1, "accum": 16, "mm": 1, "fsdp": 1}
+MM = dict(n_patch=196, n_text=828, vC=768, vL=4, vI=2048)
 PUBLISHED_TOK_S_1GPU = 135866.0   # reference `bench 16` on 1x RTX 6000 Ada (its todo.md:36-37), V=32768
-SITE = os.path.join(os.path.dirname(os.path.dirname(os.__file__)), "site-packages")
+SITE = sysconfig.get_paths()["purelib"]
 
 
 # ------------------------------------------------------------------ clocks
@@ -139,31 +152,90 @@ def ref_env():
     nv = os.path.join(SITE, "nvidia")
     if os.path.isdir(nv):
         libs = [os.path.join(nv, d, "lib") for d in os.listdir(nv) if os.path.isdir(os.path.join(nv, d, "lib"))]
-    e["LD_LIBRARY_PATH"] = ":".join(libs + [e.get("LD_LIBRARY_PATH", "")])
+    e["LD_LIBRARY_PATH"] = ":".join([e.get("LD_LIBRARY_PATH", "")] + libs)
     e["ENTROPY_PEAK_TFLOPS"] = "2250"
     return e
 
 
+def write_llmc_bin(path, n_tokens, vocab, seed=3):
+    """A synthetic llm.c token file (64 x int32 header with magic 20240520 and the token count, then uint16 tokens),
+    written with numpy only so that the reference arm loads none of this framework's libraries."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    hdr = np.zeros(64, dtype=np.int32)
+    hdr[0], hdr[1], hdr[2] = 20240520, 1, n_tokens
+    with open(path, "wb") as f:
+        f.write(hdr.tobytes())
+        f.write(rng.integers(0, vocab, size=n_tokens, dtype=np.uint16).tobytes())
+
+
+def ref_e2e(exe, env, steps, warmup):
+    """The reference's stock real-data loop (`gpt train <bin> K`, train/gpt.cu:1454-1536) on a synthetic token file with
+    ENTROPY_LOG_EVERY=1: every step its double-buffered pipe copies ids + targets from pinned host memory (2 x B*T int32)
+    and the loss read-back copies the B*T per-row losses to the host.  Its own per-step host wall-clock is reported."""
+    B, T = B_PER_GPU["lm"], MODEL["T"]
+    path = f"/tmp/mlb_ref_tokens_{os.getpid()}.bin"
+    warm = max(warmup, 3)
+    try:
+        write_llmc_bin(path, B * T * 48 + 1, 50257)
+        e = dict(env, ENTROPY_V=str(MODEL["V"]), ENTROPY_B=str(B), ENTROPY_LOG_EVERY="1")
+        r = subprocess.run([exe, "train", path, str(warm + steps)], env=e, capture_output=True, text=True, cwd=os.path.dirname(exe))
+    finally:
+        try:
+            os.remove(path)
+        except OSError:
+            pass
+    ms = [float(m.group(1)) for m in re.finditer(r"^step\s+\d+\s+loss\s+[\d.]+\s+([\d.]+) ms/step", r.stdout, re.M)]
+    if r.returncode != 0 or len(ms) < warm + steps:
+        return {"unavailable": f"gpt train failed rc={r.returncode}: {(r.stderr or r.stdout)[-200:]!r}"}
+    ms = ms[-steps:]
+    mean = sum(ms) / len(ms)
+    return {"value": B * T / (mean * 1e-3), "unit": "tokens/s", "ms_per_step": mean, "h2d_bytes_per_step": 2 * B * T * 4,
+            "d2h_bytes_per_step": B * T * 4, "api": "gpt train <llm.c .bin> K with ENTROPY_LOG_EVERY=1 (stock real-data loop)",
+            "timing": f"the program's own host wall-clock per step, mean of the last {steps} of {warm + steps} steps"}
+
+
 def run_reference(args):
     rank, world, local = env_rank()
-    n = args.gpus
+    n, cname = args.gpus, args.config
+    say = lambda d: print(json.dumps(dict({"impl": "reference", "config_name": cname}, **d))) if rank == 0 else None
+    if cname == "fsdp":
+        say({"unavailable": "the reference has no sharded path (csrc/src/fsdp.cu:37-112 replicates every parameter); the baseline "
+                            "of this configuration is this framework's own schedule on library collectives: --comm nccl"})
+        return 0
+    if cname == "mm" and n > 1:
+        say({"unavailable": "the reference's multimodal modes are single-GPU only (train/gpt.cu:1291-1378, reduce=false)"})
+        return 0
     exe = ref_binary()
     if exe is None:
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/gpt is missing and could not be built (nvcc + cuDNN frontend headers needed)"}))
+        say({"unavailable": "baseline/_ref/gpt is missing and could not be built (nvcc + cuDNN frontend headers needed)"})
         return 0
     e = ref_env()
-    sampler = ClockSampler(local)
-    if n == 1:
-        e["ENTROPY_V"] = str(MODEL["V"])
-        cmd = [exe, "bench", str(B_PER_GPU), str(args.steps)]
-        V = MODEL["V"]
-    else:
+    B, T = B_PER_GPU[cname], MODEL["T"]
+    ddp_env = dict(RANK=str(rank), WORLD=str(world), LOCAL_RANK=str(local),
+                   ENTROPY_NCCL_ID=f"/tmp/entropy_nccl_id_{os.environ.get('MASTER_PORT', '0')}_{os.environ.get('TORCHELASTIC_RUN_ID', str(os.getpid()))}")
+    V, accum, note = MODEL["V"], 1, ""
+    if cname == "lm" and n == 1:
+        e["ENTROPY_V"] = str(V)
+        cmd = [exe, "bench", str(B), str(args.steps)]
+        pat = r"step time:\s*([\d.]+) ms\s+throughput:\s*([\d.]+) tok/s\s+TFLOP/s:\s*([\d.]+)\s+MFU:\s*([\d.]+)%"
+    elif cname in ("lm", "accum"):
         # bench_ddp pins V=32768 in the unmodified source (train/gpt.cu:1563); reported as such in `config`
-        e.update(RANK=str(rank), WORLD=str(world), LOCAL_RANK=str(local),
-                 ENTROPY_NCCL_ID=f"/tmp/entropy_nccl_id_{os.environ.get('MASTER_PORT', '0')}_{os.environ.get('TORCHELASTIC_RUN_ID', 'x')}")
-        cmd = [exe, "bench_ddp", str(B_PER_GPU), str(args.steps)]
-        V = 32768
+        e.update(ddp_env)
+        V, note = 32768, "; bench_ddp pins V=32768"
+        if cname == "accum":
+            accum = ACCUM["accum"]
+            e.update(ENTROPY_ACCUM=str(accum), ENTROPY_BF16_REDUCE="1")
+        cmd = [exe, "bench_ddp", str(B), str(args.steps)]
+        pat = r"opt-step\s*([\d.]+) ms \| global\s*([\d.]+) tok/s \|\s*([\d.]+) TFLOP/s agg \| MFU\s*([\d.]+)%"
+    else:
+        e.update(ENTROPY_V=str(V), ENTROPY_C="768", ENTROPY_L="12", ENTROPY_H="12", ENTROPY_I="2048",
+                 ENTROPY_MM_PATCHES=str(MM["n_patch"]), ENTROPY_MM_TEXT=str(MM["n_text"]), ENTROPY_VC=str(MM["vC"]),
+                 ENTROPY_VL=str(MM["vL"]), ENTROPY_VI=str(MM["vI"]))
+        cmd = [exe, "mm_bench", str(B), str(args.steps)]
+        pat = r"mm step:\s*([\d.]+) ms \| text tok/s\s*([\d.]+) \| image tok/s\s*([\d.]+) \| loss\s*([\d.]+)"
+        note = "; takes pre-patchified bf16 patch rows resident on the device (no pixel input path)"
+    sampler = ClockSampler(local)
     sampler.start()
     t0 = time.time()
     r = subprocess.run(cmd, env=e, capture_output=True, text=True, cwd=os.path.dirname(exe))
@@ -171,25 +243,34 @@ def run_reference(args):
     clocks = sampler.stop()
     if rank != 0:
         return 0
-    out = r.stdout
-    if n == 1:
-        m = re.search(r"step time:\s*([\d.]+) ms\s+throughput:\s*([\d.]+) tok/s\s+TFLOP/s:\s*([\d.]+)\s+MFU:\s*([\d.]+)%", out)
-    else:
-        m = re.search(r"opt-step\s*([\d.]+) ms \| global\s*([\d.]+) tok/s \|\s*([\d.]+) TFLOP/s agg \| MFU\s*([\d.]+)%", out)
+    m = re.search(pat, r.stdout)
     if r.returncode != 0 or not m:
-        print(json.dumps({"impl": "reference", "unavailable": f"reference run failed rc={r.returncode}: {(r.stderr or out)[-300:]!r}"}))
+        say({"unavailable": f"reference run failed rc={r.returncode}: {(r.stderr or r.stdout)[-300:]!r}"})
         return 0
-    ms, tok, tf, mfu = (float(x) for x in m.groups())
-    print(json.dumps({
-        "impl": "reference", "metric": "train_tokens_per_sec", "value": tok, "unit": "tokens/s", "n_gpus": n,
+    if cname == "mm":
+        ms = float(m.group(1))
+        tok = (float(m.group(2)) + float(m.group(3)))
+        tf = mfu = None
+    else:
+        ms, tok, tf, mfu = (float(x) for x in m.groups())
+    e2e = None
+    if cname == "lm" and n == 1:
+        e2e = ref_e2e(exe, ref_env(), args.steps, args.warmup)
+    elif cname == "lm":
+        e2e = {"unavailable": "the reference has no multi-GPU real-data loop (train_ddp is an alias of bench_ddp, train/gpt.cu:1258,1538)"}
+    else:
+        e2e = {"unavailable": "the reference has no host-fed loop for this configuration (device-resident synthetic batch only)"}
+    say({
+        "metric": "train_tokens_per_sec", "value": tok, "unit": "tokens/s", "n_gpus": n,
         "steps": args.steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": (tok / PUBLISHED_TOK_S_1GPU) if n == 1 else None, "dtype": "bf16", "data": "synthetic",
-        "tflops": tf, "mfu_nominal_2250": mfu / 100.0, "clocks": clocks, "wall_s": wall,
+        "vs_baseline": (tok / PUBLISHED_TOK_S_1GPU) if (n == 1 and cname == "lm") else None, "dtype": "bf16", "data": "synthetic",
+        "tflops": tf, "mfu_nominal_2250": (mfu / 100.0) if mfu is not None else None, "clocks": clocks, "wall_s": wall, "e2e": e2e,
         "timing": "the reference's own host wall-clock around cudaDeviceSynchronize (its only timer); warm-up fixed at 3 in its source",
-        "config": {"model": f"llama-style L12 C768 H12 I2048 T1024 V{V}", "global_batch": B_PER_GPU * n, "seq_len": MODEL["T"],
-                   "parallelism": f"dp{n}", "command": " ".join(os.path.basename(c) if i == 0 else c for i, c in enumerate(cmd)),
-                   "note": "unmodified train/gpt.cu built -arch=sm_100 with cuBLASLt + cuDNN + NCCL" + ("; bench_ddp pins V=32768" if n > 1 else "")},
-    }))
+        "config": {"model": f"llama-style L12 C768 H12 I2048 T1024 V{V}" + (" + vision tower 196 patches vC768 vL4 vI2048" if cname == "mm" else ""),
+                   "global_batch": B * n * accum, "seq_len": T, "parallelism": f"dp{n}", "per_gpu_batch": B, "accum": accum,
+                   "command": " ".join(os.path.basename(c) if i == 0 else c for i, c in enumerate(cmd)),
+                   "note": "unmodified train/gpt.cu built -arch=sm_100 with cuBLASLt + cuDNN + NCCL" + note},
+    })
     return 0
 
 
@@ -197,23 +278,23 @@ def run_reference(args):
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from ml_b200 import Config, RunConfig
+    from ml_b200 import Config, RunConfig, VisionConfig
     from ml_b200.layout import flops_per_step
-    from ml_b200.parallel.bootstrap import init_distributed
+    from ml_b200.parallel.bootstrap import init_distributed, shutdown
     from ml_b200.trainer import Trainer
-    from ml_b200.data import bench_batch
+    from ml_b200.data import bench_batch, mm_batch, random_pixels
     from ml_b200.ops import native
 
     rank, world, local, dev = init_distributed()
     assert dev.type == "cuda", "bench.py needs a GPU"
-    n = args.gpus
-    cfg = Config(**MODEL)
+    n, cname = args.gpus, args.config
+    B, accum = B_PER_GPU[cname], ACCUM[cname]
     run = RunConfig.from_env()
-    run.comm = os.environ.get("ENTROPY_COMM", "fused" if world > 1 else "nccl")   # one GPU: nothing to reduce, plain AdamW
-    B, T = B_PER_GPU, cfg.T
-    tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, world=world, rank=rank, use_graph=not args.no_graph)
-    ids, tgt = bench_batch(B, T, 50257, rank)
-    tr.set_batch(ids.to(dev), tgt.to(dev))
+    run.comm = args.comm or os.environ.get("ENTROPY_COMM", "fused" if world > 1 else "nccl")   # one GPU: nothing to reduce
+    run.accum = accum
+    if cname == "accum" and "ENTROPY_BF16_REDUCE" not in os.environ:
+        run.extra["fused_bf16"] = True          # the configuration names bf16 gradient reduction
+    warm = max(args.warmup, 3)
 
     def barrier():
         if world > 1:
@@ -235,57 +316,133 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
+    extra, tr, fs = {}, None, None
+    pool = 4
+    if cname == "fsdp":
+        from ml_b200.models import GPT
+        from ml_b200.parallel.fsdp import FSDP
+        cfg = Config(**MODEL_FSDP)
+        T = cfg.T
+        g = GPT(cfg, B, dev, sharded=True)
+        fs = FSDP(g, world, rank, comm=run.comm, hyper=dict(lr=1e-4, wd=0.1))
+        g.init_weights(1234)
+        ids, tgt = bench_batch(B, T, 50257, rank)
+        d_ids, d_tgt = ids.to(dev), tgt.to(dev)
+        barrier()                      # ranks finish the host-side weight initialisation seconds apart
+        step = lambda i: fs.step(d_ids, d_tgt)
+        h_in = [tuple(t.pin_memory() for t in bench_batch(B, T, 50257, rank, seed=100 + i)) for i in range(pool)]
+
+        def step_host(i):
+            a, b = h_in[i % pool]
+            d_ids.copy_(a, non_blocking=True)
+            d_tgt.copy_(b, non_blocking=True)
+            fs.step(d_ids, d_tgt)
+            return g.mean_loss()
+        launches = lambda l0: native.LAUNCHES - l0
+        model_name = "llama-style L24 C2048 H16 I5504 T2048 V50304 (1.42 B parameters), ZeRO-3 sharded"
+        h2d, d2h, api = 2 * B * T * 4, 8, "ml_b200.parallel.fsdp.FSDP.step + GPT.mean_loss"
+        fl = flops_per_step(cfg, B) * world
+        tokens = B * T * world
+        loss_fn = lambda: g.mean_loss()
+        extra["params_per_rank_M"] = fs.master.numel() / 1e6
+    else:
+        cfg = Config(**MODEL)
+        T = cfg.T
+        vc = VisionConfig(vC=MM["vC"], vL=MM["vL"], vI=MM["vI"], n_patch=MM["n_patch"]) if cname == "mm" else None
+        tr = Trainer(cfg, B, dev, run, lr=1e-4, wd=0.1, world=world, rank=rank, use_graph=not args.no_graph, vision=vc,
+                     n_text=MM["n_text"] if vc else None)
+        if vc is None:
+            a = [bench_batch(B, T, 50257, rank, seed=7 + k) for k in range(accum)]
+            tr.set_batch(torch.stack([x[0] for x in a]).to(dev), torch.stack([x[1] for x in a]).to(dev))
+            h_in = []
+            for i in range(pool):
+                a = [bench_batch(B, T, 50257, rank, seed=100 + i * accum + k) for k in range(accum)]
+                h_in.append((torch.stack([x[0] for x in a]).pin_memory(), torch.stack([x[1] for x in a]).pin_memory(), None))
+            h2d = accum * 2 * B * T * 4 + 16
+            model_name = "llama-style L12 C768 H12 I2048 T1024 V50304"
+        else:
+            _, ids, tgt = mm_batch(B, vc.n_patch, MM["n_text"], 50257, vc.patch_dim, seed=5 + 131 * rank)
+            tr.set_batch(ids.to(dev), tgt.to(dev))
+            tr.pixels = random_pixels(B, vc.image_hw, vc.channels, seed=5 + 131 * rank).to(dev)
+            h_in = []
+            for i in range(pool):
+                _, a, b = mm_batch(B, vc.n_patch, MM["n_text"], 50257, vc.patch_dim, seed=100 + i + 131 * rank)
+                h_in.append((a.pin_memory(), b.pin_memory(), random_pixels(B, vc.image_hw, vc.channels, seed=200 + i).pin_memory()))
+            h2d = 2 * B * T * 4 + 32 + B * vc.channels * vc.image_hw ** 2 * 4
+            model_name = "llama-style L12 C768 H12 I2048 T1024 V50304 + vision tower 196 patches vC768 vL4 vI2048 (fp32 pixels in)"
+        step = lambda i: tr.step()
+        step_host = lambda i: tr.step_host(*h_in[i % pool])
+        launches = lambda l0: tr.launches_per_step * args.steps if tr.use_graph else native.LAUNCHES - l0
+        d2h, api = 4, "ml_b200.trainer.Trainer.step_host"
+        fl = flops_per_step(cfg, B) * world * accum
+        tokens = B * T * world * accum
+        loss_fn = lambda: tr.loss()
+
     # ---- device-timed steps (inputs resident)
     sampler = ClockSampler(local)
     sampler.start()                       # before the warm-up: the tool is up and polling when the timed region starts
-    for _ in range(max(args.warmup, 3)):
-        tr.step()
+    for i in range(warm):
+        step(i)
     l0 = native.LAUNCHES
     barrier()
     sampler.mark()
-    ms = timed(lambda i: tr.step(), args.steps)
+    ms = timed(step, args.steps)
     clocks = sampler.stop()
-    launches = tr.launches_per_step * args.steps if tr.use_graph else native.LAUNCHES - l0
-    loss_dev = tr.loss()
-    # ---- end to end: fresh tokens from pinned host memory every step, loss read back every step
-    pool = 4
-    h_ids = torch.empty(pool, B * T, dtype=torch.int32).pin_memory()
-    h_tgt = torch.empty(pool, B * T, dtype=torch.int32).pin_memory()
-    for i in range(pool):
-        a, b = bench_batch(B, T, 50257, rank, seed=100 + i)
-        h_ids[i].copy_(a)
-        h_tgt[i].copy_(b)
+    n_launch = launches(l0)
+    loss_dev = loss_fn()
+    # ---- end to end: fresh inputs from pinned host memory every step, loss read back every step
     for i in range(3):
-        tr.step_host(h_ids[i % pool], h_tgt[i % pool])
+        step_host(i)
     losses = []
-    ms_e2e = timed(lambda i: losses.append(tr.step_host(h_ids[i % pool], h_tgt[i % pool])), args.steps)
+    ms_e2e = timed(lambda i: losses.append(step_host(i)), args.steps)
+    # ---- gradient step: what of it is left after backward (eager steps, events around the tail)
+    grad = None
+    if tr is not None:
+        grad = tr.probe_grad_step(3)
+        if world > 1:
+            t = torch.tensor([grad["exposed_ms"]], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            grad["exposed_ms"] = float(t.item())
+            eq = tr.params_equal_across_ranks()
+            extra["params_equal_across_ranks"] = bool(eq)
     err = native.get_error()
     if rank == 0:
-        tok = B * T * world
-        fl = flops_per_step(cfg, B) * world
-        val = tok / (ms * 1e-3)
-        print(json.dumps({
+        val = tokens / (ms * 1e-3)
+        line = {
             "metric": "train_tokens_per_sec", "value": val, "unit": "tokens/s", "n_gpus": n, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": val / PUBLISHED_TOK_S_1GPU if n == 1 else None, "dtype": "bf16", "data": "synthetic",
+            "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": val / PUBLISHED_TOK_S_1GPU if (n == 1 and cname == "lm") else None, "dtype": "bf16", "data": "synthetic",
             "tflops": fl / (ms * 1e-3) / 1e12, "mfu_nominal_2250": fl / (ms * 1e-3) / (2250e12 * world),
             "clocks": clocks,
-            "e2e": {"value": tok / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": int(2 * B * T * 4 + 16), "d2h_bytes_per_step": 4,
-                    "api": "ml_b200.trainer.Trainer.step_host", "last_loss": losses[-1] if losses else None},
-            "gpu_launches": int(launches), "kernel_error_word": err, "loss": loss_dev,
-            "config": {"model": "llama-style L12 C768 H12 I2048 T1024 V50304", "global_batch": B * world, "seq_len": T,
-                       "parallelism": f"dp{world}", "per_gpu_batch": B, "cuda_graph": bool(tr.use_graph), "comm": run.comm,
+            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "api": api,
+                    "last_loss": losses[-1] if losses else None},
+            "gpu_launches": int(n_launch), "kernel_error_word": err, "loss": loss_dev, "config_name": cname,
+            "config": {"model": model_name, "global_batch": B * world * accum, "seq_len": T,
+                       "parallelism": (f"fsdp{world}" if cname == "fsdp" else f"dp{world}"), "per_gpu_batch": B, "accum": accum,
+                       "cuda_graph": bool(tr.use_graph) if tr is not None else False, "comm": run.comm,
                        "l2": "per-step working set (>10 GB of activations/grads) exceeds the 126 MB L2; no explicit flush",
                        "optimizer": "AdamW lr1e-4 b(0.9,0.95) wd0.1, fp32 master/m/v"},
-        }))
+        }
+        if grad is not None:
+            line["grad_step"] = grad
+            line["exposed_comm_ms"] = grad["exposed_ms"]
+        line.update(extra)
+        print(json.dumps(line))
     sys.stdout.flush()
+    # ---- teardown: a communicator cannot be destroyed while a CUDA graph that recorded its collectives is alive, so the
+    # graph goes first; the destroy runs under a watchdog so that a teardown that blocks cannot hold the benchmark
+    if tr is not None:
+        tr.close()
     if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
-        # process-group teardown after NCCL work was captured in CUDA graphs has been seen to block; the measurement is
-        # complete and flushed, so leave without it
-        os._exit(0)
+        barrier()
+        th = threading.Thread(target=shutdown, daemon=True)
+        th.start()
+        th.join(timeout=20.0)
+        if th.is_alive():
+            sys.stderr.write("process-group teardown did not return within 20 s; leaving without it\n")
+            sys.stderr.flush()
+            os._exit(0)
     return 0
 
 
@@ -295,6 +452,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="lm", choices=["lm", "accum", "mm", "fsdp"])
+    ap.add_argument("--comm", default="", choices=["", "fused", "nccl"], help="gradient / parameter collectives: in-kernel NVLink (default) or library")
     ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

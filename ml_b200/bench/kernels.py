@@ -7,6 +7,7 @@ train/gemm_bench.cu, train/attn_bench.cu, train/norm_bench2.cu).
     python -m ml_b200.bench.kernels attn  [--B 16 --T 1024]     flash attention fwd / bwd vs torch SDPA
     python -m ml_b200.bench.kernels norm                        RMSNorm fwd / add+norm / bwd, CE, AdamW, SwiGLU bandwidth
     python -m ml_b200.bench.kernels once  --case attn|gemm      a few un-timed launches (what an `ncu` capture wraps)
+    python -m ml_b200.bench.kernels corun                       tensor-core GEMMs next to a small kernel on a second stream
 
 Timing: CUDA events on the launching stream, `--warm` warm-up launches, L2 flushed (256 MB write) before every timed
 launch, median of `--iters`.  Roofline denominators are printed from MEASURED_PEAKS.json when it is present.
@@ -51,6 +52,49 @@ def timeit(fn, iters=20, warm=10, flush=True):
     return ts[len(ts) // 2]
 
 
+def bench_corun(a):
+    """How much a small kernel on a second stream costs the tensor-core GEMMs: 24 QKV-shaped products on one stream,
+    timed alone and next to a probe kernel (no shared memory, 32 registers) that idles or streams memory meanwhile."""
+    import ctypes as C
+    dev = torch.device("cuda")
+    L = nat.lib()
+    L.mlb_corun_probe.argtypes = [C.c_void_p, C.c_long, C.c_double, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    L.mlb_corun_probe.restype = C.c_int
+    M, N, K = a.M, 3 * a.C, a.C
+    x = torch.randn(M, K, device=dev).bfloat16()
+    W = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+    outs = [torch.empty(M, N, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+    buf = torch.zeros(256 * 1024 * 1024, device=dev)          # 1 GB: far beyond L2
+    side = torch.cuda.Stream(dev, priority=-1)
+    reps = 24
+
+    def gemms():
+        for i in range(reps):
+            nat.linear_fwd(outs[i % 4], x, W)
+
+    def run(mode, ctas, carve, threads=128):
+        for _ in range(2):
+            gemms()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if mode >= 0:
+            with torch.cuda.stream(side):
+                L.mlb_corun_probe(buf.data_ptr(), buf.numel(), 0.004, mode, ctas, threads, carve, side.cuda_stream)
+        e0.record()
+        gemms()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    print(f"{reps} x linear_fwd M={M} N={N} K={K}, us per product")
+    print(f"  alone                                  {run(-1, 0, 0):8.1f}")
+    for threads in (128, 256):
+        for ctas in (32, 148):
+            for carve in (1, 0):
+                for mode, nm in ((0, "idle"), (1, "stream"), (2, "stream evict-first")):
+                    print(f"  + {ctas:3d} CTAs x {threads} thr {nm:<18} carve={'max-shared' if carve else 'default   '} {run(mode, ctas, carve, threads):8.1f}")
+
+
 def bench_gemm(a):
     dev = torch.device("cuda")
     tf_peak, _, how = peaks()
@@ -72,10 +116,14 @@ def bench_gemm(a):
         dW = torch.zeros(N, K, device=dev)
         dWb = torch.empty(N, K, device=dev, dtype=torch.bfloat16)
         fl = 2.0 * M * N * K
-        for op, ours, lib in (("fwd", lambda: nat.linear_fwd(out, x, W), lambda: torch.matmul(x, W.t(), out=out)),
+        ops_list = [("fwd", lambda: nat.linear_fwd(out, x, W), lambda: torch.matmul(x, W.t(), out=out))]
+        if nm == "gate|up":
+            sw = torch.empty(M, N // 2, device=dev, dtype=torch.bfloat16)
+            ops_list.append(("f+sw", lambda: nat.linear_fwd_swiglu(out, sw, x, W), lambda: (torch.matmul(x, W.t(), out=out), nat.swiglu_fwd(sw, out))))
+        for op, ours, lib in (*ops_list,
                               ("dX", lambda: nat.linear_dx(dx, dout, W), lambda: torch.matmul(dout, W, out=dx)),
                               ("dW", lambda: nat.linear_dw(dW, dout, x), lambda: torch.matmul(dout.t(), x, out=dWb))):
-            t, tl = timeit(ours, a.iters, a.warm), timeit(lib, a.iters, a.warm)
+            t, tl = timeit(ours, a.iters, a.warm, not a.hot), timeit(lib, a.iters, a.warm, not a.hot)
             print(f"{nm:<10}{op:<5}{t * 1e3:>10.1f}{fl / t / 1e9:>10.0f}{fl / t / 1e9 / tf_peak:>18.2f}{tl * 1e3:>11.1f}{fl / tl / 1e9:>10.0f}")
         del x, W, out, dout, dx, dW, dWb
     print("kernel error word:", nat.get_error())
@@ -248,7 +296,7 @@ def once(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "layouts", "mma", "attn", "norm", "once"])
+    ap.add_argument("what", choices=["gemm", "corun", "layouts", "mma", "attn", "norm", "once"])
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--case", default="attn", choices=["attn", "gemm", "norm"])
     ap.add_argument("--M", type=int, default=16384)
@@ -261,6 +309,7 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
+    ap.add_argument("--hot", action="store_true", help="gemm: no L2 flush between launches (operands that fit stay in L2, as behind a producer kernel)")
     ap.add_argument("--fwd-balance", type=int, default=1, help="persistent attention kernels: 1 = balanced work schedule from the host, 0 = round robin")
     ap.add_argument("--fwd-mode", type=int, default=3, help="attention forward, head size 64: 1 = thread-per-row kernel, O folded into registers; 2 = O accumulated in TMEM with lazy rescale; 3 = 2 in one pass per key block; 0 = four threads per row")
     ap.add_argument("--tile-order", type=int, default=0, help="pair GEMM static schedule: 0 = by operand size, 1 = M first, 2 = N first")
@@ -269,7 +318,7 @@ def main():
     ap.add_argument("--epi", type=int, default=1, help="pair GEMM epilogue: 1 = coalesced stores by the warps, 0 = TMA store / add-reduce")
     ap.add_argument("--pairs", type=int, default=1, help="GEMM: 1 = CTA-pair kernel (cta_group::2), 0 = one CTA per tile")
     a = ap.parse_args()
-    {"gemm": bench_gemm, "layouts": bench_layouts, "mma": bench_mma, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
+    {"gemm": bench_gemm, "corun": bench_corun, "layouts": bench_layouts, "mma": bench_mma, "attn": bench_attn, "norm": bench_norm, "once": once}[a.what](a)
 
 
 if __name__ == "__main__":

@@ -499,7 +499,7 @@ struct Fwd2Step {   // one key block of one item in this CTA's flattened sequenc
 // chunk's arithmetic; 4, 6 or 8 of every 16 exponential pairs as a cubic on the FMA pipe instead of the special-function
 // unit - equal, 5 % and 10 % slower.)
 template <int MODE>
-__global__ void __launch_bounds__(FWD2_THREADS, 1) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tm_out,
+__global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tm_out,
                                                                            const AttnArgs a) {
   mlb_pdl_sync();
   using S = Fwd2Smem;
@@ -1271,7 +1271,7 @@ constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS + 2;   // issues ever
 constexpr int BWDF_LOAD_WARP = BWDF_CTRL_WARP + 1;                // issues every TMA load
 constexpr int BWDF_THREADS = (BWDF_LOAD_WARP + 1) * 32;
 
-__global__ void __launch_bounds__(BWDF_THREADS, 1) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
+__global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
                                                                             const __grid_constant__ CUtensorMap tm_do,
                                                                             const __grid_constant__ CUtensorMap tm_dq, const AttnArgs a) {
   mlb_pdl_sync();

@@ -162,12 +162,16 @@ __device__ __forceinline__ void store_params4(const BucketArgs& a, long e, uint2
   }
 }
 
-// 256 threads and at most 32 registers per thread: a CTA of this kernel fits beside a resident CTA of the tensor-core
-// kernels (which take one SM each but leave about 8 K registers free), so bucket kernels launched behind backward
-// on a second stream share SMs with the GEMMs instead of keeping whole SMs, and the GEMMs' clusters, waiting.
+// Lean form: 128 threads and at most 32 registers per thread, no shared memory.  That is one warp per SM sub-partition
+// with 1 K registers each, which is what a resident CTA of the persistent tensor-core kernels (GEMM, attention: capped
+// at 160 / 120 registers for this purpose) leaves free; so bucket kernels launched behind backward on a second stream
+// share SMs with those kernels instead of keeping whole SMs - and with them clusters of a statically scheduled
+// persistent grid - waiting.
+// The body uses NO shared memory (block-wide decisions go through __syncthreads_and / __syncthreads_or): a tensor-core
+// CTA leaves less than 2 KB of an SM's shared memory free, and a CTA that declares even one shared variable is charged
+// a full allocation unit on top of the per-CTA reserve, so it would not fit beside one.
 template <int GM>
 __device__ __forceinline__ void ddp_bucket_body(const BucketArgs& a) {
-  __shared__ int s_ok, s_last;
   const int W = a.world;
   const int epoch = *((volatile int*)(a.epoch_ctr + a.bucket)) + 1;   // every CTA reads it before the last one bumps it
   int* my_flags = a.flags[a.rank];
@@ -188,9 +192,9 @@ __device__ __forceinline__ void ddp_bucket_body(const BucketArgs& a) {
     }
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(a.done_counter + a.max_buckets + a.bucket, 1) == (int)gridDim.x - 1);
-    __syncthreads();
-    if (s_last) {
+    int last = 0;
+    if (threadIdx.x == 0) last = (atomicAdd(a.done_counter + a.max_buckets + a.bucket, 1) == (int)gridDim.x - 1);
+    if (__syncthreads_or(last)) {
       if (threadIdx.x == 0) a.done_counter[a.max_buckets + a.bucket] = 0;
       if (threadIdx.x < W) {
         __threadfence_system();
@@ -202,13 +206,9 @@ __device__ __forceinline__ void ddp_bucket_body(const BucketArgs& a) {
     __threadfence_system();
     st_release_sys(a.flags[threadIdx.x] + (0 * a.max_buckets + a.bucket) * MAX_WORLD + a.rank, epoch);
   }
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if (threadIdx.x < W) {
-    if (!wait_flag(ready_row + threadIdx.x, epoch, a.spin_limit_ns, (a.bucket << 8) | threadIdx.x)) s_ok = 0;
-  }
-  __syncthreads();
-  const bool ok = s_ok != 0;
+  int seen = 1;
+  if (threadIdx.x < W) seen = wait_flag(ready_row + threadIdx.x, epoch, a.spin_limit_ns, (a.bucket << 8) | threadIdx.x) ? 1 : 0;
+  const bool ok = __syncthreads_and(seen) != 0;
   // ---- 2. reduce-scatter + mean + AdamW on this rank's shard, parameters stored to every rank
   if (ok) {
     float lr = a.lr, inv_bc1 = a.inv_bc1, inv_bc2 = a.inv_bc2, scale = a.scale;
@@ -247,9 +247,9 @@ __device__ __forceinline__ void ddp_bucket_body(const BucketArgs& a) {
   // ---- 3. exit barrier (last CTA of this rank)
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(a.done_counter + a.bucket, 1) == (int)gridDim.x - 1);
-  __syncthreads();
-  if (!s_last) return;
+  int last = 0;
+  if (threadIdx.x == 0) last = (atomicAdd(a.done_counter + a.bucket, 1) == (int)gridDim.x - 1);
+  if (!__syncthreads_or(last)) return;
   if (threadIdx.x == 0) { a.done_counter[a.bucket] = 0; a.epoch_ctr[a.bucket] = epoch; }
   if (threadIdx.x < W) {
     __threadfence_system();
@@ -277,6 +277,31 @@ __global__ void __launch_bounds__(512) allgather_pull_kernel(uint4* __restrict__
     uint4 v;
     asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src[w] + j) : "memory");
     dst[i] = v;
+  }
+}
+
+// Co-residency probe (micro-benchmark hook): a small kernel without shared memory, at most 32 registers per thread, that
+// keeps its CTAs busy for `dur_ns` - mode 0 by watching the clock, modes 1 / 2 by streaming `n4` float4 of `buf` through
+// x = x * 1.0000001f over and over (default caching / evict-first hints) - so that its effect on a tensor-core kernel
+// running at the same time on another stream can be measured.  CARVE selects the shared-memory split it asks for.
+template <bool CARVE>
+__global__ void __maxnreg__(32) corun_probe_kernel(float4* buf, long n4, long dur_ns, int mode) {
+  const uint64_t t0 = gtimer();
+  if (mode == 0) {
+    while ((long)(gtimer() - t0) < dur_ns) __nanosleep(200);
+    return;
+  }
+  for (;;) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+      float4 x;
+      if (mode == 2) asm volatile("ld.global.cs.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "l"(buf + i));
+      else x = buf[i];
+      x.x *= 1.0000001f; x.y *= 1.0000001f; x.z *= 1.0000001f; x.w *= 1.0000001f;
+      if (mode == 2) asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(buf + i), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
+      else buf[i] = x;
+      if ((i & 0xfff) == 0 && (long)(gtimer() - t0) >= dur_ns) return;
+    }
+    if ((long)(gtimer() - t0) >= dur_ns) return;
   }
 }
 
@@ -312,15 +337,26 @@ MLB_API int mlb_ddp_bucket2(const void* grads_ptrs, const void* params_ptrs, con
   a.scale = scale; a.dev_hyper = dev_hyper; a.grads_mc = grads_mc; a.params_mc = (bf16*)params_mc; a.spin_limit_ns = (long)(spin_limit_s * 1e9);
   a.gstage = (bf16* const*)gstage_ptrs; a.gstage_mc = (bf16*)gstage_mc;
   const long chunk = ((n + world - 1) / world + 7) & ~7L;
-  long want = (chunk / 4 + 255) / 256;
+  long want = (chunk / 4 + 127) / 128;
   if (want < 1) want = 1;
   if (ctas < 1) ctas = 64;
   const int grid = (int)(want < ctas ? want : ctas);
-#define MLB_BUCKET_CASE(GMV)                                                    \
-  case GMV:                                                                    \
-    if (lean) ddp_bucket_lean_kernel<GMV><<<grid, 256, 0, st>>>(a);            \
-    else ddp_bucket_kernel<GMV><<<grid, 256, 0, st>>>(a);                      \
-    break;
+  // An SM's split between L1 and shared memory is fixed while CTAs are resident on it.  The tensor-core kernels need the
+  // largest shared-memory split; a bucket CTA that got onto an idle SM first with the default (L1-heavy) split would keep
+  // their CTAs (and with them whole clusters of a persistent grid) waiting until it leaves.  So these kernels ask for
+  // the largest shared-memory split too, although they use none.
+#define MLB_BUCKET_CASE(GMV)                                                                                              \
+  case GMV: {                                                                                                             \
+    static bool carve = false;                                                                                            \
+    if (!carve) {                                                                                                         \
+      cudaFuncSetAttribute(ddp_bucket_lean_kernel<GMV>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared); \
+      cudaFuncSetAttribute(ddp_bucket_kernel<GMV>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);      \
+      carve = true;                                                                                                       \
+    }                                                                                                                     \
+    if (lean) ddp_bucket_lean_kernel<GMV><<<grid, 128, 0, st>>>(a);                                                       \
+    else ddp_bucket_kernel<GMV><<<grid, 256, 0, st>>>(a);                                                                 \
+    break;                                                                                                                \
+  }
   switch (gmode) {
     MLB_BUCKET_CASE(GM_F32_PEER)
     MLB_BUCKET_CASE(GM_F32_MC)
@@ -352,6 +388,17 @@ MLB_API int mlb_allgather_pull(void* dst, const void* src_ptrs, long chunk_bytes
   if (want < 1) want = 1;
   if (ctas < 1) ctas = 32;
   allgather_pull_kernel<<<(int)(want < ctas ? want : ctas), 512, 0, st>>>((uint4*)dst, (const uint4* const*)src_ptrs, chunk_vec, world);
+  return (int)cudaGetLastError();
+}
+
+MLB_API int mlb_corun_probe(float* buf, long n_floats, double dur_s, int mode, int ctas, int threads, int max_shared_carveout, cudaStream_t st) {
+  if (dur_s > 0.05) dur_s = 0.05;          // a probe, not a load generator: 50 ms at most
+  if (max_shared_carveout) {
+    cudaFuncSetAttribute(corun_probe_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    corun_probe_kernel<true><<<ctas, threads, 0, st>>>((float4*)buf, n_floats / 4, (long)(dur_s * 1e9), mode);
+  } else {
+    corun_probe_kernel<false><<<ctas, threads, 0, st>>>((float4*)buf, n_floats / 4, (long)(dur_s * 1e9), mode);
+  }
   return (int)cudaGetLastError();
 }
 

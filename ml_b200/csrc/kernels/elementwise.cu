@@ -26,6 +26,15 @@ __device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
   u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
   *reinterpret_cast<uint4*>(p) = u;
 }
+// 8 floats * scale -> 8 E4M3 bytes (round to nearest even, saturating at +-448), one 8-byte store
+__device__ __forceinline__ void store8_e4m3(uint8_t* p, const float (&f)[8], float scale) {
+  uint2 u;
+  u.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[0] * scale, f[1] * scale), __NV_SATFINITE, __NV_E4M3) |
+        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[2] * scale, f[3] * scale), __NV_SATFINITE, __NV_E4M3) << 16);
+  u.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[4] * scale, f[5] * scale), __NV_SATFINITE, __NV_E4M3) |
+        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[6] * scale, f[7] * scale), __NV_SATFINITE, __NV_E4M3) << 16);
+  *reinterpret_cast<uint2*>(p) = u;
+}
 
 // ------------------------------------------------------------------ embedding
 __global__ void embed_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ wte, const int* __restrict__ ids, int C) {
@@ -72,10 +81,11 @@ __global__ void gather_prefix_k(bf16* __restrict__ dprefix, const bf16* __restri
 
 // ------------------------------------------------------------------ RMSNorm forward (one warp per row)
 // ADD: resid = a + b is stored (bf16) and the norm is taken over the un-rounded fp32 sum.
-template <bool ADD>
+template <bool ADD, bool F8 = false>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, float* __restrict__ rstd, bf16* __restrict__ resid,
                                                      const bf16* __restrict__ a, const bf16* __restrict__ b,
-                                                     const bf16* __restrict__ w, long rows, int C, float eps) {
+                                                     const bf16* __restrict__ w, long rows, int C, float eps,
+                                                     uint8_t* __restrict__ out8 = nullptr, float s8 = 1.f) {
   mlb_pdl_sync();
   const int lane = threadIdx.x & 31;
   const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -113,6 +123,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, flo
 #pragma unroll
       for (int j = 0; j < 8; j++) x[j] = x[j] * r * ww[j];
       store8(out + row * C + i, x);
+      if (F8) store8_e4m3(out8 + row * C + i, x, s8);     // E4M3 copy of the fp32 values for the 8-bit forward GEMM
     }
   } else {
     for (int i = lane; i < C; i += 32) {
@@ -126,7 +137,9 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, flo
     for (int i = lane; i < C; i += 32) {
       float x = __bfloat162float(pa[i]);
       if (ADD) x += __bfloat162float(pb[i]);
-      out[row * C + i] = __float2bfloat16(x * r * __bfloat162float(w[i]));
+      const float y = x * r * __bfloat162float(w[i]);
+      out[row * C + i] = __float2bfloat16(y);
+      if (F8) out8[row * C + i] = (uint8_t)__nv_cvt_float_to_fp8(y * s8, __NV_SATFINITE, __NV_E4M3);
     }
   }
 }
@@ -361,6 +374,22 @@ __global__ void swiglu_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ gu
 #pragma unroll
   for (int j = 0; j < 8; j++) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
   store8(out + row * (long)I + v * 8, o);
+}
+// The same with an E4M3 copy of the fp32 result (x scale) for the 8-bit down projection (train/gpt_kernels.cuh:605-613).
+__global__ void swiglu_fwd_fp8_k(bf16* __restrict__ out, uint8_t* __restrict__ out8, const bf16* __restrict__ gu, long rows, int I, float s8) {
+  mlb_pdl_sync();
+  const int vpr = I >> 3;
+  long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * vpr) return;
+  const long row = idx / vpr;
+  const int v = idx % vpr;
+  float g[8], u[8], o[8];
+  load8(gu + row * 2L * I + v * 8, g);
+  load8(gu + row * 2L * I + I + v * 8, u);
+#pragma unroll
+  for (int j = 0; j < 8; j++) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+  store8(out + row * (long)I + v * 8, o);
+  store8_e4m3(out8 + row * (long)I + v * 8, o, s8);
 }
 __global__ void swiglu_bwd_k(bf16* __restrict__ dgu, const bf16* __restrict__ dout, const bf16* __restrict__ gu, long rows, int I) {
   mlb_pdl_sync();
@@ -633,8 +662,10 @@ MLB_API int mlb_mufu_probe(long long* cycles, float* sink, int mode, int iters, 
 // ------------------------------------------------------------------ AdamW (fp32 master/m/v, bf16 copy written in the same pass)
 __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, const float* __restrict__ grads,
                         float* __restrict__ m, float* __restrict__ v, long n, float lr, float b1, float b2, float eps, float wd,
-                        float inv_bc1, float inv_bc2, float grad_scale, const float* __restrict__ dev_hyper) {
+                        float inv_bc1, float inv_bc2, float grad_scale, const float* __restrict__ dev_hyper,
+                        uint8_t* __restrict__ params8 = nullptr, float s8 = 1.f) {
   mlb_pdl_sync();
+  // params8 (optional): E4M3 copy of the updated fp32 weights x s8 for the 8-bit forward (train/gpt_kernels.cuh:1402-1416)
   // dev_hyper (optional, device memory): {lr, 1/bc1, 1/bc2, grad_scale} override the launch arguments, so a captured
   // CUDA graph can be replayed with the step-dependent bias corrections of the current step.
   if (dev_hyper) { lr = dev_hyper[0]; inv_bc1 = dev_hyper[1]; inv_bc2 = dev_hyper[2]; grad_scale = dev_hyper[3]; }
@@ -661,6 +692,11 @@ __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, c
       o.y = pack_bf16(p.z, p.w);
       *reinterpret_cast<uint2*>(params + i) = o;
     }
+    if (params8) {
+      const uint32_t q = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.x * s8, p.y * s8), __NV_SATFINITE, __NV_E4M3) |
+                         ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(p.z * s8, p.w * s8), __NV_SATFINITE, __NV_E4M3) << 16);
+      *reinterpret_cast<uint32_t*>(params8 + i) = q;
+    }
   } else {
     for (; i < n; i++) {
       const float gj = grads[i] * grad_scale;
@@ -668,11 +704,23 @@ __global__ void adamw_k(float* __restrict__ master, bf16* __restrict__ params, c
       pj -= lr * (mj * inv_bc1 / (sqrtf(vj * inv_bc2) + eps) + wd * pj);
       m[i] = mj; v[i] = vj; master[i] = pj;
       if (params) params[i] = __float2bfloat16(pj);
+      if (params8) params8[i] = (uint8_t)__nv_cvt_float_to_fp8(pj * s8, __NV_SATFINITE, __NV_E4M3);
     }
   }
 }
 
 // ------------------------------------------------------------------ casts / utilities
+// bf16 -> E4M3 storage (x scale), 8 elements per thread (train/gpt_kernels.cuh:211-214)
+__global__ void cast_b2e4m3_k(uint8_t* __restrict__ out, const bf16* __restrict__ in, long n, float scale) {
+  long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i + 7 < n) {
+    float x[8];
+    load8(in + i, x);
+    store8_e4m3(out + i, x, scale);
+  } else {
+    for (; i < n; i++) out[i] = (uint8_t)__nv_cvt_float_to_fp8(__bfloat162float(in[i]) * scale, __NV_SATFINITE, __NV_E4M3);
+  }
+}
 __global__ void cast_f2b_k(bf16* __restrict__ out, const float* __restrict__ in, long n, float scale) {
   mlb_pdl_sync();
   long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -778,13 +826,48 @@ MLB_API int mlb_gather_prefix_grad(void* dprefix, const void* dresid, int B, int
   LAUNCH_RET;
 }
 MLB_API int mlb_rmsnorm_fwd(void* out, float* rstd, const void* x, const void* w, long rows, int C, float eps, cudaStream_t st) {
-  mlb_launch(rmsnorm_fwd_k<false>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w, rows, C, eps);
+  mlb_launch(rmsnorm_fwd_k<false>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w, rows, C, eps,
+             (uint8_t*)nullptr, 1.f);
   LAUNCH_RET;
 }
 MLB_API int mlb_add_rmsnorm_fwd(void* resid, void* out, float* rstd, const void* a, const void* b, const void* w, long rows, int C,
                                 float eps, cudaStream_t st) {
   mlb_launch(rmsnorm_fwd_k<true>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b, (const bf16*)w,
-                                                   rows, C, eps);
+                                                   rows, C, eps, (uint8_t*)nullptr, 1.f);
+  LAUNCH_RET;
+}
+
+// The two forward norms with an additional E4M3 copy of the output (x scale) for the 8-bit forward GEMMs
+// (train/gpt_kernels.cuh:291-312, :474-493).  C must be a multiple of 8 for the vector path; other widths take the
+// scalar path of the same kernel.
+MLB_API int mlb_rmsnorm_fwd_fp8(void* out, void* out8, float* rstd, const void* x, const void* w, long rows, int C, float eps, float scale,
+                                cudaStream_t st) {
+  mlb_launch(rmsnorm_fwd_k<false, true>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w,
+             rows, C, eps, (uint8_t*)out8, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_add_rmsnorm_fwd_fp8(void* resid, void* out, void* out8, float* rstd, const void* a, const void* b, const void* w, long rows,
+                                    int C, float eps, float scale, cudaStream_t st) {
+  mlb_launch(rmsnorm_fwd_k<true, true>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b,
+             (const bf16*)w, rows, C, eps, (uint8_t*)out8, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_swiglu_fwd_fp8(void* out, void* out8, const void* gu, long rows, int I, float scale, cudaStream_t st) {
+  if (I % 8 != 0) return -1;
+  mlb_launch(swiglu_fwd_fp8_k, dim3(gs(rows * (I / 8), 256)), dim3(256), 0, st, (bf16*)out, (uint8_t*)out8, (const bf16*)gu, rows, I, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_cast_bf16_fp8(void* out8, const void* in, long n, float scale, cudaStream_t st) {
+  if (n <= 0) return 0;
+  cast_b2e4m3_k<<<gs((n + 7) / 8, 256), 256, 0, st>>>((uint8_t*)out8, (const bf16*)in, n, scale);
+  LAUNCH_RET;
+}
+MLB_API int mlb_adamw_fp8(float* master, void* params, void* params8, const float* grads, float* m, float* v, long n, float lr, float b1,
+                          float b2, float eps, float wd, float bc1, float bc2, float grad_scale, float w_scale, const float* dev_hyper,
+                          cudaStream_t st) {
+  if (n == 0) return 0;
+  mlb_launch(adamw_k, dim3(gs((n + 3) / 4, 256)), dim3(256), 0, st, master, (bf16*)params, grads, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2,
+             grad_scale, dev_hyper, (uint8_t*)params8, w_scale);
   LAUNCH_RET;
 }
 
@@ -867,7 +950,7 @@ MLB_API int mlb_adamw(float* master, void* params, const float* grads, float* m,
                       float eps, float wd, float bc1, float bc2, float grad_scale, const float* dev_hyper, cudaStream_t st) {
   if (n == 0) return 0;
   mlb_launch(adamw_k, dim3(gs((n + 3) / 4, 256)), dim3(256), 0, st, master, (bf16*)params, grads, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2,
-                                                grad_scale, dev_hyper);
+                                                grad_scale, dev_hyper, (uint8_t*)nullptr, 1.f);
   LAUNCH_RET;
 }
 MLB_API int mlb_cast_f2b(void* out, const float* in, long n, float scale, cudaStream_t st) {

@@ -71,6 +71,13 @@ struct GemmArgs {
   const float* cosT;
   const float* sinT;
   int rope_T, rope_cols;
+  // optional SwiGLU in the bf16 epilogue (pair kernel, forward product with N = 2 * sw_I = [gate | up] columns): a pair
+  // tile holds gate columns [nt*128, +128) in accumulator columns 0..127 and the matching up columns in 128..255 (the
+  // leader CTA stages the gate rows of W, its peer the up rows), so silu(gate) * up is formed where both are at hand
+  // and written to sw_out[M, sw_I] beside the [gate | up] output that backward needs
+  bf16* sw_out;
+  int sw_I;
+  float out_scale;   // 8-bit form: accumulators are multiplied by this (1 / (activation scale * weight scale))
 };
 
 // Work items of one cluster of the pair kernel.  Static mode: items c, c + nclusters, ... of tiles x splits.
@@ -364,14 +371,56 @@ struct Gemm2Smem {
 };
 constexpr int GEMM2_THREADS = 64 + 8 * 32;   // producer warp, MMA warp, eight epilogue warps
 
+// One warp writes a slab of 32 rows x 64 bf16 (lane = row, pk = that row's 64 values packed in pairs) through its
+// swizzled 4 KB staging buffer to out[m0 + row, col0 .. col0 + 63]: four full 128-byte rows per store instruction.
+__device__ __forceinline__ void slab_store_bf16(uint8_t* buf, int lane, const uint32_t (&pk)[32], bf16* out, int ldo, int m0,
+                                                int col0, int M, int ncols) {
+  uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+  for (int v = 0; v < 8; v++)
+    *reinterpret_cast<uint4*>(rowp + ((v ^ (lane & 7)) << 4)) = make_uint4(pk[v * 4], pk[v * 4 + 1], pk[v * 4 + 2], pk[v * 4 + 3]);
+  __syncwarp();
+  const int ch = lane & 7, gcol = col0 + ch * 8;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int row = i * 4 + (lane >> 3);
+    const uint4 v = *reinterpret_cast<const uint4*>(buf + row * 128 + ((ch ^ (row & 7)) << 4));
+    if (m0 + row < M && gcol < ncols) *reinterpret_cast<uint4*>(out + (size_t)(m0 + row) * ldo + gcol) = v;
+  }
+  __syncwarp();   // the buffer is rewritten by the next slab
+}
+__device__ __forceinline__ void scale64(uint32_t (&r)[32], uint32_t (&r2)[32], float s) {
+#pragma unroll
+  for (int i = 0; i < 32; i++) {
+    r[i] = __float_as_uint(__uint_as_float(r[i]) * s);
+    r2[i] = __float_as_uint(__uint_as_float(r2[i]) * s);
+  }
+}
+__device__ __forceinline__ void pack64(const uint32_t (&r)[32], const uint32_t (&r2)[32], uint32_t (&pk)[32]) {
+#pragma unroll
+  for (int i = 0; i < 16; i++) {
+    pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    pk[16 + i] = pack_bf16(__uint_as_float(r2[2 * i]), __uint_as_float(r2[2 * i + 1]));
+  }
+}
+
 // Epilogue: eight warps per CTA; warp w reads TMEM lanes 32*(w%4).. (the lane group the hardware lets it read) and one
 // 128-column half of the accumulator.  A slab of 32 rows x 128 bytes goes through a swizzled staging buffer, then
 //   EMODE 0: TMA tiled store / fp32 add-reduce (two buffers per warp, one transfer in flight)
 //   EMODE 1: the warp itself writes it out, four full 128-byte rows per instruction (st.global.v4 / red.global.add.v4.f32)
-template <bool A_MN, bool B_MN, int EPI, int EMODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM2_THREADS, 1)
+// Register budget: the ten warps land three on two of the SM's four sub-partitions (16 K registers each).  At 160
+// registers per thread those three warps leave 1 K registers, room for one 32-register warp of a small kernel from
+// another stream (the gradient-bucket kernels that run behind backward use 128-thread CTAs for that reason); at the 168
+// the compiler takes when left alone nothing else fits on the SM and such a kernel and this one exclude each other.
+// F8: both operands are E4M3 bytes, K-major; a 128-byte shared-memory row then holds 128 elements of K, one stage 128
+// of K (four K = 32 instructions), and the accumulators are multiplied by g.out_scale (the product of the two dequant
+// scales) on their way out.  Everything else - tiles, ring, barriers, epilogue - is shared with the bf16 form.
+template <bool A_MN, bool B_MN, int EPI, int EMODE, bool F8 = false>
+__global__ void __cluster_dims__(2, 1, 1) __maxnreg__(160)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
+  static_assert(!F8 || (!A_MN && !B_MN && EPI == EPI_BF16), "the 8-bit form is a forward product: K-major operands, bf16 out");
+  constexpr int KSTEP = F8 ? 128 : BK;     // elements of K per stage
   using S = Gemm2Smem<EMODE>;
   constexpr int STAGES = S::STAGES;
   constexpr int BN = 256, PM = 256;    // pair tile
@@ -411,7 +460,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       WorkIter iter(g, cid, ncl);
       WorkItem w;
       while (ok && iter.next(w)) {
-        const int m0 = w.mt * PM + (int)rank * 128, n0 = w.nt * BN + (int)rank * 128;
+        const int m0 = w.mt * PM + (int)rank * 128;
+        // SwiGLU form: tile nt pairs gate rows [nt*128, +128) of W (leader) with up rows [I + nt*128, +128) (peer)
+        const int n0 = g.sw_out ? (w.nt * 128 + (int)rank * g.sw_I) : (w.nt * BN + (int)rank * 128);
         for (int kb = w.kb0; kb < w.kb1; kb++) {
           if (!tc::mbar_wait(&empty[stage], phase ^ 1, 0x21)) { ok = false; break; }
           uint8_t* sA = smem + stage * S::STAGE_BYTES;
@@ -419,14 +470,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const uint32_t bar = tc::mapa_u32(tc::smem_u32(&full[stage]), 0);
           if (rank == 0) tc::mbar_expect_tx(&full[stage], 2 * S::STAGE_BYTES);
           if (!A_MN) {
-            tc::tma_load_2d_pair(sA, &tmA, bar, kb * BK, m0);
+            tc::tma_load_2d_pair(sA, &tmA, bar, kb * KSTEP, m0);
           } else {
             if (g.a3d) tc::tma_load_3d_pair(sA, &tmA, bar, 0, kb * BK, m0 / 64);
             else
               for (int c = 0; c < 2; c++) tc::tma_load_2d_pair(sA + c * 8192, &tmA, bar, m0 + c * 64, kb * BK);
           }
           if (!B_MN) {
-            tc::tma_load_2d_pair(sB, &tmB, bar, kb * BK, n0);
+            tc::tma_load_2d_pair(sB, &tmB, bar, kb * KSTEP, n0);
           } else {
             if (g.b3d) tc::tma_load_3d_pair(sB, &tmB, bar, 0, kb * BK, n0 / 64);
             else
@@ -439,7 +490,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer (leader CTA only)
     if (rank == 0 && tc::elect_one()) {
-      constexpr uint32_t idesc = tc::idesc_bf16(PM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = F8 ? tc::idesc_e4m3(PM, BN) : tc::idesc_bf16(PM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0, phase = 0, it = 0;
       bool ok = true;
       WorkIter iter(g, cid, ncl);
@@ -459,7 +510,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int k = 0; k < BK / 16; k++) {
             const uint64_t da = A_MN ? tc::smem_desc_sw128(sA + k * 2048, 8192, 1024) : tc::smem_desc_sw128(sA + k * 32, 16, 1024);
             const uint64_t db = B_MN ? tc::smem_desc_sw128(sB + k * 2048, 8192, 1024) : tc::smem_desc_sw128(sB + k * 32, 16, 1024);
-            tc::mma_bf16_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (F8) tc::mma_e4m3_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else tc::mma_bf16_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc::mma_commit_pair(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -485,6 +537,42 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc::tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN + half * 128;
       const bool rows_live = m0 < g.M;
+      if (EPI == EPI_BF16 && EMODE == 1 && g.sw_out != nullptr) {
+        // this warp: columns [half*64, +64) of the tile's gate block and of its up block; gate and up go out rounded to
+        // bf16, and silu(gate) * up is computed from those rounded values (what a separate pass over the output reads)
+        const uint32_t tg = tmem_base + ((uint32_t)(lg * 32) << 16) + acc * BN + half * 64;
+        const int cg = w.nt * 128 + half * 64;                 // column of the gate slab; the up slab sits sw_I further
+        uint32_t gp[32], up[32];
+        {
+          uint32_t r[32], r2[32];
+          tc::tmem_ld32(tg, r);
+          tc::tmem_ld32(tg + 32, r2);
+          tc::tmem_ld_wait();
+          if (F8) scale64(r, r2, g.out_scale);
+          pack64(r, r2, gp);
+          tc::tmem_ld32(tg + 128, r);
+          tc::tmem_ld32(tg + 160, r2);
+          tc::tmem_ld_wait();
+          if (F8) scale64(r, r2, g.out_scale);
+          pack64(r, r2, up);
+        }
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive_cluster(tc::mapa_u32(tc::smem_u32(&acc_empty[acc]), 0));   // accumulator is in registers
+        if (rows_live) {
+          bf16* o = (bf16*)g.out;
+          slab_store_bf16(my_stage, lane, gp, o, g.ldo, m0, cg, g.M, g.sw_I);
+          slab_store_bf16(my_stage, lane, up, o + g.sw_I, g.ldo, m0, cg, g.M, g.sw_I);
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            const float g0 = __uint_as_float(gp[i] << 16), g1 = __uint_as_float(gp[i] & 0xffff0000u);
+            const float u0 = __uint_as_float(up[i] << 16), u1 = __uint_as_float(up[i] & 0xffff0000u);
+            gp[i] = pack_bf16(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+          }
+          slab_store_bf16(my_stage, lane, gp, g.sw_out, g.sw_I, m0, cg, g.M, g.sw_I);
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < SLABS; c++) {
         uint8_t* buf = my_stage + (EMODE == 0 ? (slab & 1) * 4096 : 0);
@@ -500,6 +588,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         uint8_t* rowp = buf + lane * 128;
         if (EPI == EPI_BF16) {
+          if (F8) scale64(r, r2, g.out_scale);
           if (g.cosT != nullptr && col0 < g.rope_cols) {   // warp-uniform; the slab is one head: r = first half, r2 = second
             const int t = (m0 + lane) % g.rope_T;
             const float4* c4 = reinterpret_cast<const float4*>(g.cosT + (size_t)t * 32);
@@ -667,7 +756,9 @@ bool mlb_make_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t c
   cuuint64_t strides[1] = {pitch_elems * elem_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(out, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : (elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -797,9 +888,10 @@ int launch_tc_gather(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUten
 // A_MN=false: A is [M,K] row-major with pitch lda.  A_MN=true: A is stored [K,M] row-major with pitch lda.
 // Same for B with N.  EPI_BF16 stores bf16; EPI_F32_ADD accumulates into fp32.
 struct RopeEpi { const float* cosT; const float* sinT; int T, cols; };
+struct SwigluEpi { bf16* out; int I; };
 template <bool A_MN, bool B_MN, int EPI>
 int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st,
-                  const RopeEpi* rope = nullptr) {
+                  const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr) {
   bool aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && (lda % 8 == 0) && (ldb % 8 == 0) &&
                  ((uintptr_t)out % 16 == 0) && (ldo % 8 == 0) && (N % 8 == 0) && M > 0 && N > 0 && K > 0;
   // MN-major operands are fetched in 64-wide chunks along M/N: the global extent must be a multiple of 8 elements
@@ -808,6 +900,9 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   if (B_MN) aligned = aligned && (N % 8 == 0);
   if (!A_MN || !B_MN) aligned = aligned && (K % 8 == 0);
   if (rope && (g_force_simt || !aligned || get_encode() == nullptr)) return -7;   // caller rotates separately
+  if (swi && (g_force_simt || !aligned || get_encode() == nullptr || g_epi_mode != 1 || !g_use_pairs || A_MN || B_MN ||
+              EPI != EPI_BF16 || N != 2 * swi->I || swi->I % 128 != 0 || M <= 128 || ((uintptr_t)swi->out & 15)))
+    return -7;                                                                       // caller runs the separate kernel
   if (g_force_simt || !aligned || get_encode() == nullptr) {
     dim3 grid(ceil_div_i(N, 64), ceil_div_i(M, 64));
     long sam = A_MN ? 1 : lda, sak = A_MN ? lda : 1, sbn = B_MN ? 1 : ldb, sbk = B_MN ? ldb : 1;
@@ -820,9 +915,10 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   GemmArgs g;
   g.cosT = rope ? rope->cosT : nullptr; g.sinT = rope ? rope->sinT : nullptr;
   g.rope_T = rope ? rope->T : 1; g.rope_cols = rope ? rope->cols : 0;
+  g.sw_out = swi ? swi->out : nullptr; g.sw_I = swi ? swi->I : 0; g.out_scale = 1.f;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, pairs ? 256 : BM);
-  g.tiles_n = ceil_div_i(N, BN);
+  g.tiles_n = swi ? swi->I / 128 : ceil_div_i(N, BN);
   g.kb_total = ceil_div_i(K, BK);
   g.splits = 1;
   if (EPI == EPI_F32_ADD) {
@@ -866,7 +962,72 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
 }
 
+// 8-bit forward product on the CTA-pair kernel: out[M,N] (bf16) = out_scale * x8[M,K] . W8[N,K]^T, operands E4M3 bytes.
+int gemm_fp8_dispatch(void* out, int ldo, const uint8_t* A, int lda, const uint8_t* B, int ldb, int M, int N, int K, float out_scale,
+                      cudaStream_t st, const SwigluEpi* swi, const RopeEpi* rope = nullptr) {
+  const bool ok = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && (lda % 16 == 0) && (ldb % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                  (ldo % 8 == 0) && (N % 8 == 0) && (K % 16 == 0) && M > 128 && N > 128 && K > 0 && get_encode() != nullptr &&
+                  g_use_pairs && g_epi_mode == 1 && !g_force_simt;
+  if (!ok) return -7;
+  if (swi && (N != 2 * swi->I || swi->I % 128 != 0 || ((uintptr_t)swi->out & 15))) return -7;
+  if (rope && !(rope->cols % 64 == 0 && N % 64 == 0)) return -7;
+  GemmArgs g;
+  g.cosT = rope ? rope->cosT : nullptr; g.sinT = rope ? rope->sinT : nullptr;
+  g.rope_T = rope ? rope->T : 1; g.rope_cols = rope ? rope->cols : 0;
+  g.sw_out = swi ? swi->out : nullptr; g.sw_I = swi ? swi->I : 0; g.out_scale = out_scale;
+  g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
+  g.tiles_m = ceil_div_i(M, 256);
+  g.tiles_n = swi ? swi->I / 128 : ceil_div_i(N, 256);
+  g.kb_total = ceil_div_i(K, 128);
+  g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0; g.sk_group = 1; g.sk_group_m = 0;
+  g.nt_fast = (g_tile_order == 2) ? 1 : (g_tile_order == 1 ? 0 : ((long)M > (long)N ? 1 : 0));
+  const CUtensorMap* tmA = mlb_tmap_cached(A, M, K, lda, 128, 128, 1);
+  const CUtensorMap* tmB = mlb_tmap_cached(B, N, K, ldb, 128, 128, 1);
+  const CUtensorMap* tmD = mlb_tmap_cached(out, M, N, ldo, 32, 64, 2);
+  if (!tmA || !tmB || !tmD) return -2;
+  using Smem = Gemm2Smem<1>;
+  auto kern = gemm_tc2_kernel<false, false, EPI_BF16, 1, true>;
+  static int max_clusters = -1;
+  if (max_clusters < 0) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(num_sms() & ~1);
+    cfg.blockDim = dim3(GEMM2_THREADS);
+    cfg.dynamicSmemBytes = Smem::TOTAL;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = num_sms() / 2; }
+    max_clusters = n < num_sms() / 2 ? n : num_sms() / 2;
+  }
+  int total = g.tiles_m * g.tiles_n;
+  int cap = max_clusters;
+  if (g_max_ctas > 0 && g_max_ctas / 2 < cap) cap = g_max_ctas / 2 > 0 ? g_max_ctas / 2 : 1;
+  int clusters = total < cap ? total : cap;
+  return (int)mlb_launch(kern, dim3(2 * clusters), dim3(GEMM2_THREADS), Smem::TOTAL, st, *tmA, *tmB, *tmD, g);
+}
+
 }  // namespace
+
+// out[M,N] (bf16) = out_scale * x8[M,K] . W8[N,K]^T with E4M3 operands (tcgen05.mma kind::f8f6f4): the reference's opt-in
+// 8-bit forward (linear_forward_fp8, train/gpt_kernels.cuh:171-176, scalar dequant scales :103-112).  Returns -7
+// (nothing launched) for shapes the CTA-pair kernel does not take (M, N > 128; K and the pitches multiples of 16).
+MLB_API int mlb_linear_fwd_fp8(void* out, const void* x8, const void* W8, int M, int N, int K, int ldo, int ldx, int ldw, float out_scale,
+                               cudaStream_t st) {
+  return gemm_fp8_dispatch(out, ldo, (const uint8_t*)x8, ldx, (const uint8_t*)W8, ldw, M, N, K, out_scale, st, nullptr);
+}
+// The QKV product in 8 bits with the rotary embedding in the epilogue (see mlb_linear_fwd_rope).
+MLB_API int mlb_linear_fwd_fp8_rope(void* out, const void* x8, const void* W8, int M, int N, int K, int ldo, int ldx, int ldw, float out_scale,
+                                    const float* cosT, const float* sinT, int T, int rope_cols, cudaStream_t st) {
+  RopeEpi r{cosT, sinT, T, rope_cols};
+  return gemm_fp8_dispatch(out, ldo, (const uint8_t*)x8, ldx, (const uint8_t*)W8, ldw, M, N, K, out_scale, st, nullptr, &r);
+}
+// The gate|up product in 8 bits with silu(gate) * up from the epilogue (see mlb_linear_fwd_swiglu).
+MLB_API int mlb_linear_fwd_fp8_swiglu(void* gu, void* sw, const void* x8, const void* W8, int M, int I, int K, int ldgu, int ldx, int ldw,
+                                      float out_scale, cudaStream_t st) {
+  SwigluEpi e{(bf16*)sw, I};
+  return gemm_fp8_dispatch(gu, ldgu, (const uint8_t*)x8, ldx, (const uint8_t*)W8, ldw, M, 2 * I, K, out_scale, st, &e);
+}
 
 // out[M,N] = x[M,K] . W[N,K]^T
 MLB_API int mlb_linear_fwd(void* out, const void* x, const void* W, int M, int N, int K, int ldo, int ldx, int ldw, cudaStream_t st) {
@@ -879,6 +1040,14 @@ MLB_API int mlb_linear_fwd_rope(void* out, const void* x, const void* W, int M, 
                                 const float* cosT, const float* sinT, int T, int rope_cols, cudaStream_t st) {
   RopeEpi r{cosT, sinT, T, rope_cols};
   return gemm_dispatch<false, false, EPI_BF16>(out, ldo, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, st, &r);
+}
+// gu[M, 2I] = x[M,K] . W[2I,K]^T with W = [W_gate; W_up], and sw[M, I] = silu(gu[:, :I]) * gu[:, I:] from the same
+// accumulators (rounded to bf16 first, so sw equals what the separate SwiGLU kernel computes from gu).  Returns -7
+// (nothing launched) when the shape does not take the CTA-pair path (I must be a multiple of 128, M > 128).
+MLB_API int mlb_linear_fwd_swiglu(void* gu, void* sw, const void* x, const void* W, int M, int I, int K, int ldgu, int ldx, int ldw,
+                                  cudaStream_t st) {
+  SwigluEpi e{(bf16*)sw, I};
+  return gemm_dispatch<false, false, EPI_BF16>(gu, ldgu, (const bf16*)x, ldx, (const bf16*)W, ldw, M, 2 * I, K, st, nullptr, &e);
 }
 // dx[M,K] = dout[M,N] . W[N,K]      (GEMM view: D[M,K], reduction N; B(n=k_in, k=n_out) is MN-major)
 MLB_API int mlb_linear_dx(void* dx, const void* dout, const void* W, int M, int N, int K, int lddx, int lddo, int ldw, cudaStream_t st) {
@@ -926,7 +1095,7 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
   g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0; g.sk_group = 1; g.sk_group_m = 0; g.nt_fast = 0;
-  g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0;
+  g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0; g.sw_out = nullptr; g.sw_I = 0; g.out_scale = 1.f;
   GatherArgs ga;
   ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
   ga.b_lo_vec = w_off_elems / 8; ga.b_hi_vec = (w_off_elems + (long)N * K) / 8; ga.b_row_vec = K / 8;

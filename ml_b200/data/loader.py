@@ -74,8 +74,10 @@ class TokenLoader:
 
 
 class BatchPipe:
-    """Two-slot prefetching pipe.  Usage per step: `ids, tgt = pipe.acquire(step)` (device tensors, valid on the
-    current stream) ... compute ... `pipe.release(step)` (queues the refill of that slot with the batch for step+2)."""
+    """Two-slot prefetching pipe.  Usage per step: `ids, tgt = pipe.acquire()` (device tensors, valid on the current
+    stream) ... compute ... `pipe.release()` (queues the refill of that slot with the batch two steps ahead).  Slots
+    are handed out in the order the windows were read, whatever step number the caller is at (a resumed run starts at
+    an arbitrary step); the optional step argument is accepted for readability and ignored."""
 
     def __init__(self, loader: TokenLoader, device, nslots: int = 2):
         self.loader, self.device, self.n = loader, torch.device(device), nslots
@@ -90,6 +92,8 @@ class BatchPipe:
         self.ready = [torch.cuda.Event() for _ in range(nslots)] if cuda else None
         self.consumed = [torch.cuda.Event() for _ in range(nslots)] if cuda else None
         self.slot_pos = [0] * nslots
+        self._head = 0           # slot of the next acquire
+        self._tail = 0           # slot of the next release
         for s in range(nslots):
             self._submit(s)
         for s in range(nslots):
@@ -111,14 +115,20 @@ class BatchPipe:
             self.d_tgt[s].copy_(self.h_tgt[s], non_blocking=True)
             self.ready[s].record(self.copy_stream)
 
-    def acquire(self, step: int):
-        s = step % self.n
+    def next_pos(self) -> int:
+        """File position of the window the next `acquire` hands out (what a checkpoint records)."""
+        return self.slot_pos[self._head]
+
+    def acquire(self, step: int = -1):
+        s = self._head
+        self._head = (s + 1) % self.n
         if self.copy_stream is not None:
             torch.cuda.current_stream().wait_event(self.ready[s])
         return self.d_ids[s], self.d_tgt[s]
 
-    def release(self, step: int):
-        s = step % self.n
+    def release(self, step: int = -1):
+        s = self._tail
+        self._tail = (s + 1) % self.n
         if self.copy_stream is not None:
             self.consumed[s].record(torch.cuda.current_stream())
             # the pinned slot may be rewritten only after its H2D copy has run

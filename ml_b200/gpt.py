@@ -376,7 +376,7 @@ def _train_loop(argv, ddp):
             # copy complete first (a collective: all ranks take part), then rank 0 writes the payload; every rank
             # records its own data position; meta.bin is published once all of that is on disk
             tr.consolidate_state()
-            next_pos = pipe.slot_pos[(step + 1) % pipe.n]
+            next_pos = pipe.next_pos()
             if rank != 0:
                 ck.save_state(a.ckpt_dir, step + 1, rank, next_pos, tr.t)
             if world > 1:

@@ -26,6 +26,7 @@ import os as _os
 
 # head size 64 on the GPU: RoPE in the QKV GEMM's epilogue instead of a separate in-place pass (MLB_NO_ROPE_FUSE=1: off)
 FUSE_ROPE_INTO_QKV = _os.environ.get("MLB_NO_ROPE_FUSE", "0") != "1"
+FUSE_SWIGLU_INTO_GU = _os.environ.get("MLB_NO_SWIGLU_FUSE", "0") != "1"
 
 
 class GPT:
@@ -56,6 +57,12 @@ class GPT:
         self.fp8_act_scale, self.fp8_w_scale = pos("ENTROPY_FP8_ACT_SCALE"), pos("ENTROPY_FP8_W_SCALE")
         if self.fp8_fwd and (sharded or self.lmce_chunk > 0):
             raise ValueError("ENTROPY_FP8_FWD is implemented for the unsharded model with materialised logits only")
+        # On the GPU the 8-bit forward is real: E4M3 copies of the weights (written by AdamW) and of the GEMM inputs
+        # (written by the norm / SwiGLU kernels that produce them) feed tcgen05 kind::f8f6f4 GEMMs.  ENTROPY_FP8_QDQ=1 keeps
+        # the older form on the GPU too: operands rounded to E4M3 but multiplied by the bf16 kernel (the oracle of the
+        # 8-bit path, and what CPU tensors always use).
+        self.fp8_native = (self.fp8_fwd and torch.device(device).type == "cuda" and (dtype in (None, torch.bfloat16)) and
+                           _os.environ.get("ENTROPY_FP8_QDQ", "0") != "1")
         self.device = torch.device(device)
         if dtype is None:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
@@ -77,6 +84,7 @@ class GPT:
             self.m = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
             self.v = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
         self.cos, self.sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, dev)
+        self.params8 = torch.zeros(self.np, dtype=torch.uint8, device=dev) if self.fp8_native else None
         self._alloc_acts(B)
         # hooks: called as hook(name, offset, numel) when a gradient bucket is final
         self.bucket_hook: Optional[Callable[[str, int, int], None]] = None
@@ -112,7 +120,12 @@ class GPT:
         else:
             self.logits = e(BT, V)
         self.losses = f(BT)
-        if self.fp8_fwd:
+        if self.fp8_native:
+            u8 = lambda *s: torch.empty(*s, dtype=torch.uint8, device=self.device)
+            # E4M3 copies of the current GEMM inputs: two norm outputs (the next layer's first norm is produced while
+            # this layer's second one may still be read) and the SwiGLU output
+            self.ln1_8, self.ln2_8, self.sw_8 = u8(BT, C), u8(BT, C), u8(BT, I)
+        elif self.fp8_fwd:
             self.fp8_x = e(BT * max(C, I))                              # E4M3-rounded GEMM input of the moment
             self.fp8_w = e(max(3 * C * C, 2 * I * C, V * C))           # E4M3-rounded weight of the moment
         # scratch
@@ -126,9 +139,10 @@ class GPT:
         self.datty = e(BT, C)
 
     def _fwd_operands(self, x, off, N, K):
-        """(x, W[N, K]) of a forward product; with fp8_fwd both rounded to E4M3 (into scratch that the next call reuses)."""
+        """(x, W[N, K]) of a forward product; with fp8_fwd in its bf16 form both rounded to E4M3 (into scratch that the next
+        call reuses)."""
         W = self.P(off, N, K)
-        if not self.fp8_fwd:
+        if not self.fp8_fwd or self.fp8_native:
             return x, W
         xq = self.fp8_x[:x.numel()].view_as(x)
         wq = self.fp8_w[:N * K].view(N, K)
@@ -166,6 +180,17 @@ class GPT:
     def sync_params(self):
         if self.params.data_ptr() != self.master.data_ptr():
             ops.cast(self.params, self.master)
+        self.refresh_params8()
+
+    def P8(self, off, *shape):
+        return self.params8[off:off + math.prod(shape)].view(*shape)
+
+    def refresh_params8(self):
+        """E4M3 copy of the bf16 parameters (x ENTROPY_FP8_W_SCALE) for the 8-bit forward.  AdamW writes it in the same pass
+        when it runs on this rank's whole buffer; after a parameter broadcast by peers (fused data-parallel step), or
+        after loading weights, it is rebuilt here."""
+        if self.params8 is not None:
+            ops.native_module().cast_bf16_fp8(self.params8, self.params, self.fp8_w_scale)
 
     # ------------------------------------------------------------------ forward
     def _mark(self, name):
@@ -181,6 +206,9 @@ class GPT:
         T, C, I, H, hd = c.T, c.C, c.I, c.H, c.hd
         BT = B * T
         assert B <= self.B
+        if (self.fp8_native and x_in is None and has_head and self.cp is None and self.res is None and
+                not ({"norm", "swiglu"} & self.skip)):       # the reference drops to bf16 under those two ablations too
+            return self._forward_fp8(ids, B, prefix, n_pre)
         sl = lambda t: t[:BT]
         x0 = sl(self.x0)
         if x_in is not None:
@@ -229,9 +257,14 @@ class GPT:
                 ops.add_rmsnorm_fwd(sl(self.resid1[l]), sl(self.ln2[l]), sl(self.rstd2[l]), resid_in, proj,
                                     self.P(o.ln2, C), c.eps)
             if "mlp" not in self.skip:
-                ops.linear_fwd(sl(self.gu[l]), *self._fwd_operands(sl(self.ln2[l]), o.gate, 2 * I, C))
-                if "swiglu" not in self.skip:
-                    ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
+                xin, Wgu = self._fwd_operands(sl(self.ln2[l]), o.gate, 2 * I, C)
+                # on the GPU silu(gate) * up comes out of the gate|up GEMM's epilogue (MLB_NO_SWIGLU_FUSE=1: separate pass)
+                fused = (FUSE_SWIGLU_INTO_GU and xin.is_cuda and "swiglu" not in self.skip and
+                         ops.native_module().linear_fwd_swiglu(sl(self.gu[l]), sl(self.sw[l]), xin, Wgu))
+                if not fused:
+                    ops.linear_fwd(sl(self.gu[l]), xin, Wgu)
+                    if "swiglu" not in self.skip:
+                        ops.swiglu_fwd(sl(self.sw[l]), sl(self.gu[l]))
                 ops.linear_fwd(proj, *self._fwd_operands(sl(self.sw[l]), o.down, C, I))
             if l + 1 == c.L and not has_head:
                 # stage boundary: plain residual add; the next stage starts with its own first norm
@@ -253,6 +286,64 @@ class GPT:
             return None          # the head runs chunk by chunk inside backward; no logits are materialised
         if "head" not in self.skip:
             ops.linear_fwd(self.logits[:BT], *self._fwd_operands(sl(self.lnf_out), Lo.off_lm, c.V, C))
+        self._mark("F_lmhead")
+        return self.logits[:BT]
+
+    def _forward_fp8(self, ids, B, prefix, n_pre):
+        """The forward pass with 8-bit products (ENTROPY_FP8_FWD=1 on the GPU; train/gpt.cu:463-567 with use_fp8): QKV,
+        gate|up, down and the LM head multiply E4M3 activations by E4M3 weights on the tensor cores
+        (tcgen05 kind::f8f6f4, fp32 accumulation, the two dequantisation scales applied to the accumulators); the attention
+        output projection stays in bf16.  The E4M3 activations are written by the kernels that produce the bf16 ones (the
+        norms and SwiGLU), the E4M3 weights by the optimizer.  Everything backward reads is saved in bf16 as usual."""
+        c, Lo = self.cfg, self.layout
+        nat = ops.native_module()
+        T, C, I, H, hd = c.T, c.C, c.I, c.H, c.hd
+        BT = B * T
+        sl = lambda t: t[:BT]
+        sa, deq = self.fp8_act_scale, 1.0 / (self.fp8_act_scale * self.fp8_w_scale)
+        x0 = sl(self.x0)
+        ops.embed_fwd(x0, self.P(Lo.off_wte, c.V, C), ids)
+        if prefix is not None and n_pre > 0:
+            ops.set_prefix(x0, prefix, B, T, n_pre)
+        ln1_8, ln2_8, sw_8 = sl(self.ln1_8), sl(self.ln2_8), sl(self.sw_8)
+        nat.rmsnorm_fwd_fp8(sl(self.ln1[0]), ln1_8, sl(self.rstd1[0]), x0, self.P(Lo.layer(0).ln1, C), c.eps, sa)
+        resid_in = x0
+
+        def lin8(out, x8, x16, off, N, K):
+            if not nat.linear_fwd_fp8(out, x8, self.P8(off, N, K), deq):
+                ops.linear_fwd(out, x16, self.P(off, N, K))      # a shape the 8-bit kernel does not take
+
+        for l in range(c.L):
+            o = Lo.layer(l)
+            qkv = sl(self.qkv[l])
+            want_rope = "rope" not in self.skip
+            roped = (want_rope and hd == 64 and FUSE_ROPE_INTO_QKV and
+                     nat.linear_fwd_fp8_rope(qkv, ln1_8, self.P8(o.qkv, 3 * C, C), deq, self.cos, self.sin, T, 2 * C))
+            if not roped:
+                lin8(qkv, ln1_8, sl(self.ln1[l]), o.qkv, 3 * C, C)
+                if want_rope:
+                    ops.rope_fwd(qkv, self.cos, self.sin, B, T, H, hd)
+            self._mark("F_qkv+rope")
+            if "attn" not in self.skip:
+                ops.attn_fwd(sl(self.atty[l]), self.lse[l][:B], qkv, B, T, H, hd)
+            self._mark("F_attn")
+            proj = sl(self.proj)
+            ops.linear_fwd(proj, sl(self.atty[l]), self.P(o.o, C, C))
+            nat.add_rmsnorm_fwd_fp8(sl(self.resid1[l]), sl(self.ln2[l]), ln2_8, sl(self.rstd2[l]), resid_in, proj,
+                                    self.P(o.ln2, C), c.eps, sa)
+            if "mlp" not in self.skip:
+                lin8(sl(self.gu[l]), ln2_8, sl(self.ln2[l]), o.gate, 2 * I, C)
+                nat.swiglu_fwd_fp8(sl(self.sw[l]), sw_8, sl(self.gu[l]), sa)
+                lin8(proj, sw_8, sl(self.sw[l]), o.down, C, I)
+            if l + 1 < c.L:
+                nw, nout, nrstd = self.P(Lo.layer(l + 1).ln1, C), sl(self.ln1[l + 1]), sl(self.rstd1[l + 1])
+            else:
+                nw, nout, nrstd = self.P(Lo.off_lnf, C), sl(self.lnf_out), sl(self.rstdf)
+            nat.add_rmsnorm_fwd_fp8(sl(self.resid2[l]), nout, ln1_8, nrstd, sl(self.resid1[l]), proj, nw, c.eps, sa)
+            resid_in = sl(self.resid2[l])
+            self._mark("F_mlp+norm")
+        if "head" not in self.skip:
+            lin8(self.logits[:BT], ln1_8, sl(self.lnf_out), Lo.off_lm, c.V, C)
         self._mark("F_lmhead")
         return self.logits[:BT]
 
@@ -404,6 +495,10 @@ class GPT:
         bc1 = 1.0 - b1 ** t
         bc2 = 1.0 - b2 ** t
         s = slice(off, off + n)
+        if self.params8 is not None:      # 8-bit forward: the E4M3 weights come out of the same pass (train/gpt.cu:753-755)
+            ops.native_module().adamw_fp8(self.master[s], self.params[s], self.params8[s], self.grads[s], self.m[s], self.v[s],
+                                          lr, b1, b2, eps, wd, bc1, bc2, grad_scale, self.fp8_w_scale, dev_hyper)
+            return
         ops.adamw(self.master[s], self.params[s], self.grads[s], self.m[s], self.v[s],
                   lr, b1, b2, eps, wd, bc1, bc2, grad_scale, dev_hyper)
 

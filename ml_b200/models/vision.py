@@ -79,8 +79,10 @@ class VisionTower:
         for l in range(vc.vL):
             b = VL.layer_base(l)
             ops.rmsnorm_fwd(self.ln[l], self.rstd[l], x, self.P(b + VL.i_ln, vC), vc.eps)
-            ops.linear_fwd(self.gu[l], self.ln[l], self.P(b + VL.i_gate, 2 * vI, vC))
-            ops.swiglu_fwd(self.sw[l], self.gu[l])
+            Wgu = self.P(b + VL.i_gate, 2 * vI, vC)
+            if not (self.gu[l].is_cuda and ops.native_module().linear_fwd_swiglu(self.gu[l], self.sw[l], self.ln[l], Wgu)):
+                ops.linear_fwd(self.gu[l], self.ln[l], Wgu)
+                ops.swiglu_fwd(self.sw[l], self.gu[l])
             ops.linear_fwd(self.mlp, self.sw[l], self.P(b + VL.i_down, vC, vI))
             ops.residual_add(self.resid[l], x, self.mlp)
             x = self.resid[l]

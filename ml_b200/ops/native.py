@@ -171,6 +171,24 @@ def linear_fwd_rope(out, x, W, cos, sin, T, rope_cols):
     return True
 
 
+def linear_fwd_swiglu(gu, sw, x, W):
+    """gu[M, 2I] = x . W^T (W = [W_gate; W_up]) and sw[M, I] = silu(gate) * up out of the same GEMM's epilogue.  Returns
+    False when the shape does not take that path (nothing was launched): the caller then runs the product and the
+    SwiGLU kernel one after the other."""
+    M, K = x.shape
+    I = sw.shape[1]
+    if W.shape[0] != 2 * I or gu.shape[1] != 2 * I or sw.stride(0) != I:
+        return False
+    fn = lib().mlb_linear_fwd_swiglu
+    fn.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]
+    fn.restype = _i32
+    rc = fn(_b(gu), _b(sw), _b(x), _b(W), M, I, K, gu.stride(0), x.stride(0), W.stride(0), _st())
+    if rc == -7:
+        return False
+    _chk(rc, "linear_fwd_swiglu")
+    return True
+
+
 def linear_dx(dx, dout, W):
     M, N = dout.shape
     K = W.shape[1]
@@ -347,6 +365,96 @@ def cast(out, x, scale=1.0):
         _chk(lib().mlb_cast_b2f(_f(out), _b(x), n, scale, _st()), "cast_b2f")
     else:
         raise TypeError(f"cast {x.dtype} -> {out.dtype} is not a kernel of this library")
+
+
+# ------------------------------------------------------------------ 8-bit forward (E4M3 storage, tcgen05 kind::f8f6f4)
+def _u8(t, name="tensor"):
+    assert t.is_cuda and t.dtype == torch.uint8 and t.is_contiguous(), f"{name}: expected contiguous CUDA uint8 (E4M3 bytes)"
+    return t.data_ptr()
+
+
+def linear_fwd_fp8(out, x8, W8, out_scale):
+    """out[M,N] (bf16) = out_scale * x8 . W8^T with E4M3 operands.  Returns False when the shape does not take the
+    8-bit tensor-core path (nothing was launched)."""
+    M, K = x8.shape
+    N = W8.shape[0]
+    fn = lib().mlb_linear_fwd_fp8
+    fn.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, C.c_float, _vp]
+    fn.restype = _i32
+    rc = fn(_b(out), _u8(x8), _u8(W8), M, N, K, out.stride(0), x8.stride(0), W8.stride(0), out_scale, _st())
+    if rc == -7:
+        return False
+    _chk(rc, "linear_fwd_fp8")
+    return True
+
+
+def linear_fwd_fp8_rope(out, x8, W8, out_scale, cos, sin, T, rope_cols):
+    M, K = x8.shape
+    N = W8.shape[0]
+    fn = lib().mlb_linear_fwd_fp8_rope
+    fn.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, C.c_float, _vp, _vp, _i32, _i32, _vp]
+    fn.restype = _i32
+    rc = fn(_b(out), _u8(x8), _u8(W8), M, N, K, out.stride(0), x8.stride(0), W8.stride(0), out_scale, _f(cos), _f(sin), T, rope_cols, _st())
+    if rc == -7:
+        return False
+    _chk(rc, "linear_fwd_fp8_rope")
+    return True
+
+
+def linear_fwd_fp8_swiglu(gu, sw, x8, W8, out_scale):
+    M, K = x8.shape
+    I = sw.shape[1]
+    if W8.shape[0] != 2 * I or gu.shape[1] != 2 * I or sw.stride(0) != I:
+        return False
+    fn = lib().mlb_linear_fwd_fp8_swiglu
+    fn.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, C.c_float, _vp]
+    fn.restype = _i32
+    rc = fn(_b(gu), _b(sw), _u8(x8), _u8(W8), M, I, K, gu.stride(0), x8.stride(0), W8.stride(0), out_scale, _st())
+    if rc == -7:
+        return False
+    _chk(rc, "linear_fwd_fp8_swiglu")
+    return True
+
+
+def rmsnorm_fwd_fp8(out, out8, rstd, x, w, eps, scale):
+    rows, Cc = x.shape
+    fn = lib().mlb_rmsnorm_fwd_fp8
+    fn.argtypes = [_vp, _vp, _vp, _vp, _vp, C.c_long, _i32, C.c_float, C.c_float, _vp]
+    fn.restype = _i32
+    _chk(fn(_b(out), _u8(out8), _f(rstd), _b(x), _b(w), rows, Cc, eps, scale, _st()), "rmsnorm_fwd_fp8")
+
+
+def add_rmsnorm_fwd_fp8(resid, out, out8, rstd, a, b, w, eps, scale):
+    rows, Cc = a.shape
+    fn = lib().mlb_add_rmsnorm_fwd_fp8
+    fn.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_long, _i32, C.c_float, C.c_float, _vp]
+    fn.restype = _i32
+    _chk(fn(_b(resid), _b(out), _u8(out8), _f(rstd), _b(a), _b(b), _b(w), rows, Cc, eps, scale, _st()), "add_rmsnorm_fwd_fp8")
+
+
+def swiglu_fwd_fp8(out, out8, gu, scale):
+    rows, I2 = gu.shape
+    fn = lib().mlb_swiglu_fwd_fp8
+    fn.argtypes = [_vp, _vp, _vp, C.c_long, _i32, C.c_float, _vp]
+    fn.restype = _i32
+    _chk(fn(_b(out), _u8(out8), _b(gu), rows, I2 // 2, scale, _st()), "swiglu_fwd_fp8")
+
+
+def cast_bf16_fp8(out8, x, scale):
+    fn = lib().mlb_cast_bf16_fp8
+    fn.argtypes = [_vp, _vp, C.c_long, C.c_float, _vp]
+    fn.restype = _i32
+    _chk(fn(_u8(out8), _b(x), x.numel(), scale, _st()), "cast_bf16_fp8")
+
+
+def adamw_fp8(master, params, params8, grads, m, v, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, w_scale, dev_hyper=None):
+    """AdamW that also writes the E4M3 copy of the updated weights (x w_scale) the 8-bit forward reads."""
+    fn = lib().mlb_adamw_fp8
+    fn.argtypes = [_vp] * 6 + [C.c_long] + [C.c_float] * 9 + [_vp, _vp]
+    fn.restype = _i32
+    hp = _f(dev_hyper) if dev_hyper is not None else None
+    _chk(fn(_f(master), _b(params), _u8(params8), _f(grads), _f(m), _f(v), master.numel(), lr, b1, b2, eps, wd, bc1, bc2, grad_scale,
+            w_scale, hp, _st()), "adamw_fp8")
 
 
 def fp8_qdq(out, x, scale=1.0):

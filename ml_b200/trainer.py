@@ -52,6 +52,7 @@ class Trainer:
                        fused_bf16=fused_bf16 or bool(self.run.extra.get("fused_bf16", False)))
         self.accum = self.ddp.accum
         self.t = 1
+        self._probe = None         # (event after the last backward, event after the gradient step) of probe_grad_step
         self.skip_adamw = False    # ablation: leave the optimizer out (single GPU, library-collective mode)
         # the vision tower's gradients are data-parallel too (the reference's multimodal modes are single-GPU only)
         self.vfused = None
@@ -93,7 +94,11 @@ class Trainer:
     def _step_body(self):
         for k in range(self.accum):
             self._micro(k)
+        if self._probe is not None:
+            self._probe[0].record()
         done = self.ddp.finish()
+        if done and self.model.params8 is not None:
+            self.model.refresh_params8()     # parameters came from the bucket kernels (bf16 only): rebuild the E4M3 copy
         h = self.hyper
         if not done and not self.skip_adamw:
             self.ddp.t = self.t
@@ -111,6 +116,8 @@ class Trainer:
         # mean loss of the last micro-batch, reduced on the device (one float to read back)
         BT = self.B * self.cfg.T
         valid = self.B * self.n_text if self.vision is not None else BT
+        if self._probe is not None:
+            self._probe[1].record()
         torch.sum(self.model.losses[:BT], dim=0, keepdim=True, out=self.d_loss)
         self.d_loss.mul_(1.0 / valid)
 
@@ -165,10 +172,15 @@ class Trainer:
         self.launches_per_step = self._launch_count() - n0
 
     # ------------------------------------------------------------------ end-to-end step (host tokens in, loss out)
-    def step_host(self, ids_host: torch.Tensor, tgt_host: torch.Tensor) -> float:
-        """ids_host / tgt_host: int32 [accum, B*T] (or [B*T]) in host memory (pinned for async copies)."""
+    def step_host(self, ids_host: torch.Tensor, tgt_host: torch.Tensor, pixels_host: Optional[torch.Tensor] = None) -> float:
+        """ids_host / tgt_host: int32 [accum, B*T] (or [B*T]) in host memory (pinned for async copies); pixels_host:
+        fp32 [B, 3, H, W] images of a multimodal step.  Returns the mean loss of the step (read back from the device)."""
         self.ids.copy_(ids_host.view(self.accum, -1), non_blocking=True)
         self.tgt.copy_(tgt_host.view(self.accum, -1), non_blocking=True)
+        if pixels_host is not None:
+            if self.pixels is None:
+                self.pixels = torch.empty(pixels_host.shape, dtype=torch.float32, device=self.device)
+            self.pixels.copy_(pixels_host, non_blocking=True)
         self.step()
         self.h_loss.copy_(self.d_loss, non_blocking=True)
         if self.device.type == "cuda":
@@ -186,6 +198,60 @@ class Trainer:
         if err:
             raise RuntimeError(f"kernel error word {err:#x} (code {err >> 24}, detail {err & 0xFFFFFF:#x}); "
                                f"the results since the last check are invalid")
+
+    def probe_grad_step(self, steps: int = 3) -> dict:
+        """What the gradient step (reduction + optimizer, and with several ranks the parameter broadcast) adds after the
+        last backward kernel: `steps` eager steps with an event after backward and one after the gradient step has
+        joined the compute stream.  With kernels launched behind backward this is the exposed communication; the NVLink
+        bytes per rank and the time they would take at 770 GB/s per direction are given beside it."""
+        if self.device.type != "cuda":
+            return {}
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        use_graph, self.use_graph = self.use_graph, False
+        try:
+            for e in ev:
+                self._probe = e
+                self.step()
+        finally:
+            self._probe, self.use_graph = None, use_graph
+        torch.cuda.synchronize(self.device)
+        ms = sorted(a.elapsed_time(b) for a, b in ev)[len(ev) // 2]
+        W, f = self.world, self.ddp.fused
+        out = {"exposed_ms": ms, "mode": "library collectives" if f is None else f.gmode,
+               "overlapped_with_backward": bool(f.overlap) if f is not None else (self.world > 1)}
+        if W > 1:
+            gb = 2 if (f is not None and f.gmode.startswith("bf16")) or (f is None and self.ddp.bf16_reduce) else 4
+            mc = f is not None and f.gmode.endswith("_mc")
+            np_ = self.model.np
+            # reduce-scatter: a rank receives its shard from W-1 peers (one reduced copy through the switch), and sends
+            # each peer's shard of its own gradients (all W shards when the switch pulls them); broadcast: it sends its
+            # bf16 shard to W-1 peers (once with a multicast store) and receives the other W-1 shards
+            rs_in = np_ * gb / W * (1 if mc else W - 1)
+            rs_out = np_ * gb / W * (W if mc else W - 1)
+            bc_out = np_ * 2 / W * (1 if (f is not None and f.params_mc) else W - 1)
+            bc_in = np_ * 2 / W * (W - 1)
+            out.update(nvlink_bytes_in=int(rs_in + bc_in), nvlink_bytes_out=int(rs_out + bc_out),
+                       nvlink_ms_at_770GBs=max(rs_in + bc_in, rs_out + bc_out) / 770e9 * 1e3)
+        return out
+
+    def params_equal_across_ranks(self) -> bool:
+        """Bitwise check that every rank holds the same bf16 parameters (max over ranks == min over ranks)."""
+        if self.world <= 1:
+            return True
+        import torch.distributed as dist
+        ok = True
+        for mdl in (self.model, self.vision):
+            if mdl is None:
+                continue
+            p = mdl.params
+            step = 1 << 26
+            for lo in range(0, p.numel(), step):
+                hi = p[lo:lo + step].float()
+                lo_t = hi.clone()
+                dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.ddp.group)
+                dist.all_reduce(lo_t, op=dist.ReduceOp.MIN, group=self.ddp.group)
+                ok = ok and bool(torch.equal(hi, lo_t))
+        return ok
 
     def consolidate_state(self):
         """Makes the fp32 master weights and AdamW moments complete on every rank.  The fused data-parallel step keeps

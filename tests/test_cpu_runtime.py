@@ -105,6 +105,50 @@ def test_batch_pipe_order_cpu(tmp_path):
     pipe.close()
 
 
+def test_rank_striped_loaders_read_disjoint_windows_fresh_and_after_resume(tmp_path):
+    """Data-parallel ranks stripe the file: rank r serves windows r, r + world, ... with the pipe's prefetch following the
+    same stride; a run resumed at an odd step from the recorded per-rank position continues exactly where it stopped,
+    and the wrap goes back to the rank's own first window."""
+    world, B, T = 3, 1, 10
+    toks = torch.arange(0, 10 * 25 + 1, dtype=torch.int32)          # 25 whole windows: token value = file position
+    p = str(tmp_path / "t.bin")
+    write_token_bin(p, toks)
+    seen, pos_after3 = {}, {}
+    for r in range(world):
+        ld = TokenLoader(p, B, T)
+        ld.set_stride(r, world)
+        pipe = BatchPipe(ld, "cpu")
+        seen[r] = []
+        for step in range(12):
+            ids, tgt = pipe.acquire(step)
+            seen[r].append(int(ids[0]) // (B * T))
+            pipe.release(step)
+            if step == 2:
+                pos_after3[r] = pipe.next_pos()
+        pipe.close()
+    for r in range(world):
+        # 25 windows, a window needs B*T + 1 tokens: rank r has windows r, r+3, ... while they fit, then wraps to window r
+        own = [w for w in range(r, 25, world)]
+        assert seen[r] == (own * 3)[:12], (r, seen[r])
+    first8 = [set(seen[r][:8]) for r in range(world)]
+    assert not (first8[0] & first8[1]) and not (first8[1] & first8[2]) and not (first8[0] & first8[2])
+    # resume after 3 steps: fresh loader, per-rank position from the checkpoint
+    for r in range(world):
+        ld = TokenLoader(p, B, T)
+        ld.set_stride(r, world)
+        ld.pos = pos_after3[r]
+        pipe = BatchPipe(ld, "cpu")
+        got = []
+        for step in range(3, 8):
+            ids, _ = pipe.acquire(step)
+            got.append(int(ids[0]) // (B * T))
+            pipe.release(step)
+        pipe.close()
+        assert got == seen[r][3:8], (r, got, seen[r])
+    with pytest.raises(OSError):
+        TokenLoader(p, 4, 10).set_stride(0, 8)                       # 8 disjoint readers need 8 whole windows
+
+
 def test_checkpoint_layout_roundtrip_and_corruption(tmp_path):
     n = 1000
     master, m, v = torch.randn(n), torch.rand(n), torch.rand(n)

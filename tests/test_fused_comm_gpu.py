@@ -98,13 +98,19 @@ def _free_port():
     return p
 
 
-def _torchrun(body: str, nproc: int, timeout=600, env_extra=None):
+def _torchrun(body: str, nproc: int, timeout=600, env_extra=None, nvls=False):
     path = f"/tmp/mlb_dist_{os.getpid()}.py"
     with open(path, "w") as f:
         f.write("import sys\nsys.path.insert(0, %r)\n" % ROOT + textwrap.dedent(body))
-    # NVLS off in every layer: NCCL, torch's symmetric memory (which otherwise binds allocations to a multicast object
-    # at rendezvous) and the fused kernels (plain peer loads / stores)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", ENTROPY_FUSED_MULTIMEM="0")
+    # Default: NVLS off in every layer - NCCL, torch's symmetric memory (which otherwise binds allocations to a multicast
+    # object at rendezvous) and the fused kernels (plain peer loads / stores).  nvls=True is for tests in which every
+    # rank stays to the end and leaves through a barrier.
+    env = dict(os.environ)
+    if nvls:
+        env.pop("TORCH_SYMM_MEM_DISABLE_MULTICAST", None)
+        env["ENTROPY_FUSED_MULTIMEM"] = "1"
+    else:
+        env.update(NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1", ENTROPY_FUSED_MULTIMEM="0")
     env.update(env_extra or {})
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), path]
@@ -149,6 +155,112 @@ def test_fused_matches_nccl_two_gpus():
     line = [l for l in out.splitlines() if l.startswith("RESULT")][0].split()
     assert float(line[1]) < 8e-3, line        # one bf16 ulp at |w| ~ 1 (norm weights) is 3.9e-3
     assert line[2] == "True" and line[3] == "True" and line[4] == "0", line
+
+
+_MODES_BODY = """
+    import os, torch, torch.distributed as dist
+    from ml_b200 import Config, RunConfig
+    from ml_b200.parallel.bootstrap import init_distributed
+    from ml_b200.trainer import Trainer
+    from ml_b200.data import bench_batch
+    from ml_b200.ops import native
+    rank, world, local, dev = init_distributed()
+    native.lib().mlb_gemm_set_splits(1)   # deterministic weight gradients: the runs may only differ by the reduction
+    cfg = Config(V=512, C=256, L=2, H=4, I=512, T=128)
+    ids, tgt = bench_batch(2, 128, 512, rank)
+    def run(comm, bf16=False, overlap=True, graph=False):
+        os.environ["ENTROPY_FUSED_OVERLAP"] = "1" if overlap else "0"
+        r = RunConfig(); r.comm = comm; r.bf16_reduce = 0; r.extra["fused_bf16"] = bf16
+        tr = Trainer(cfg, 2, dev, r, lr=1e-3, wd=0.1, world=world, rank=rank, use_graph=graph)
+        tr.set_batch(ids.to(dev), tgt.to(dev))
+        for _ in range(5): tr.step()
+        torch.cuda.synchronize()
+        same = tr.params_equal_across_ranks()
+        mode = tr.ddp.fused.gmode if tr.ddp.fused is not None else "nccl"
+        pmc = bool(tr.ddp.fused.params_mc) if tr.ddp.fused is not None else False
+        p = tr.model.params.float().clone()
+        tr.close()
+        return p, same, mode, pmc
+    base, same0, _, _ = run("nccl")
+    for name, kw in CASES:
+        p, same, mode, pmc = run("fused", **kw)
+        if rank == 0:
+            print("RESULT", name, mode, int(pmc), float((p - base).abs().max()), float((p - base).abs().mean()), same, native.get_error(), flush=True)
+    dist.barrier(); torch.cuda.synchronize(); dist.destroy_process_group()
+"""
+
+
+def _check_modes(out, want_mode_suffix, bf16_cases):
+    lines = [l.split() for l in out.splitlines() if l.startswith("RESULT")]
+    assert lines, out[-3000:]
+    for _, name, mode, pmc, dmax, dmean, same, err in lines:
+        assert same == "True" and err == "0", (name, same, err)
+        if name in bf16_cases:
+            # gradients rounded to bf16 before the sum: AdamW turns a rounding-level change of a near-zero gradient
+            # into a step of the other sign (2 * lr * steps at worst); the mean shows that the runs agree
+            assert float(dmax) < 1.2e-2 and float(dmean) < 2e-4, (name, dmax, dmean)
+        else:
+            assert float(dmax) < 8e-3, (name, dmax)      # one bf16 ulp at |w| ~ 1 (norm weights) is 3.9e-3
+    return lines
+
+
+@needs2
+def test_fused_modes_peer_loads_match_nccl():
+    """fp32 and bf16-staged reductions over plain peer loads, overlapped with backward or in one launch after it, eager
+    and replayed from a CUDA graph: same parameters as the library-collective run, identical on every rank."""
+    n = min(torch.cuda.device_count(), 4)
+    cases = [("f32_overlap", {}), ("f32_single_launch", {"overlap": False}), ("bf16_overlap", {"bf16": True}),
+             ("bf16_single_launch", {"bf16": True, "overlap": False}), ("f32_overlap_graph", {"graph": True})]
+    rc, out = _torchrun("CASES = %r\n" % cases + textwrap.dedent(_MODES_BODY), n)
+    assert rc == 0, out[-3000:]
+    lines = _check_modes(out, "", {"bf16_overlap", "bf16_single_launch"})
+    assert all(not l[2].endswith("_mc") for l in lines), lines
+
+
+@needs2
+def test_fused_modes_multimem_match_nccl():
+    """The same through the NVLink multicast address: multimem.ld_reduce of fp32 gradients and of bf16 staging copies,
+    multimem.st of the new parameters.  Skipped when the symmetric buffers get no multicast mapping."""
+    n = min(torch.cuda.device_count(), 4)
+    cases = [("f32_overlap", {}), ("f32_single_launch", {"overlap": False}), ("bf16_overlap", {"bf16": True}),
+             ("f32_overlap_graph", {"graph": True})]
+    rc, out = _torchrun("CASES = %r\n" % cases + textwrap.dedent(_MODES_BODY), n, nvls=True)
+    assert rc == 0, out[-3000:]
+    lines = _check_modes(out, "_mc", {"bf16_overlap"})
+    if not all(l[2].endswith("_mc") for l in lines):
+        pytest.skip(f"no multicast mapping on this machine: modes {[l[2] for l in lines]}")
+    assert all(l[3] == "1" for l in lines), lines
+
+
+@needs2
+def test_fused_checkpoint_resume_equals_uninterrupted_run(tmp_path):
+    """Two ranks, fused gradient step (each rank keeps master / m / v current only for its shard): 6 steps straight
+    against 3 steps + checkpoint + fresh processes that resume for 3 more.  The loss lines of the second half and the
+    rank-disjoint data windows must match."""
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    g = _t.Generator().manual_seed(5)
+    path = str(tmp_path / "tok.bin")
+    write_token_bin(path, _t.randint(0, 512, (2 * 64 * 40 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "512", "ENTROPY_C": "128", "ENTROPY_L": "2", "ENTROPY_H": "2", "ENTROPY_I": "256", "ENTROPY_T": "64",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "1", "ENTROPY_COMM": "fused"}
+    body = """
+        import sys
+        from ml_b200 import gpt
+        sys.exit(gpt.main(ARGS))
+    """
+    def run(args):
+        rc, out = _torchrun("ARGS = %r\n" % (args,) + textwrap.dedent(body), 2, env_extra=env)
+        assert rc == 0, out[-3000:]
+        return [l for l in out.splitlines() if l.startswith("step ") and "loss" in l]
+    full = run(["train_ddp", path, "6"])
+    ck = str(tmp_path / "ck")
+    first = run(["train_ddp", path, "3", "--ckpt-dir", ck, "--save-every", "3"])
+    second = run(["train_ddp", path, "6", "--ckpt-dir", ck, "--resume", "-2"])
+    num = lambda l: float(l.split("loss")[1].split("|")[0])
+    assert len(full) == 6 and len(first) == 3 and len(second) == 3, (full, first, second)
+    for a, b in zip(full[3:], second):
+        assert abs(num(a) - num(b)) < 5e-3, (a, b)
 
 
 @needs2

@@ -50,6 +50,32 @@ def _no_kernel_error():
     assert e == 0, f"kernel error word {e:#x}"
 
 
+# ------------------------------------------------------------------ GEMM with SwiGLU epilogue
+@pytest.mark.parametrize("M,I,K", [(1024, 2048, 768), (392, 256, 128), (4096 + 200, 384, 264), (512, 128, 64)])
+def test_linear_fwd_swiglu_epilogue(M, I, K):
+    """gate|up product with silu(gate) * up formed in the epilogue: both outputs against the fp32 oracle, and the fused
+    activation bit-equal to the separate SwiGLU kernel run on the fused kernel's own [gate | up] output."""
+    torch.manual_seed(M + I)
+    x, W = rnd(M, K), rnd(2 * I, K, scale=K ** -0.5)
+    gu = torch.full((M, 2 * I), float("nan"), device=dev(), dtype=torch.bfloat16)
+    sw = torch.full((M, I), float("nan"), device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_swiglu(gu, sw, x, W)
+    egu = torch.empty(M, 2 * I, device=dev())
+    ref.linear_fwd(egu, x, W)
+    close(gu, egu, name="gate|up")
+    esw = torch.empty(M, I, device=dev())
+    ref.swiglu_fwd(esw, egu)
+    close(sw, esw, name="swiglu", fro=6e-3)        # two roundings (gate / up, then the product) against none
+    sep = torch.empty_like(sw)
+    nat().swiglu_fwd(sep, gu)
+    assert torch.equal(sep, sw)
+    # shapes the epilogue form does not take are declined without a launch
+    assert not nat().linear_fwd_swiglu(torch.empty(64, 2 * I, device=dev(), dtype=torch.bfloat16),
+                                       torch.empty(64, I, device=dev(), dtype=torch.bfloat16), x[:64], W)
+    assert not nat().linear_fwd_swiglu(torch.empty(M, 200, device=dev(), dtype=torch.bfloat16),
+                                       torch.empty(M, 100, device=dev(), dtype=torch.bfloat16), x, W[:200])
+
+
 # ------------------------------------------------------------------ GEMM
 GEMM_SHAPES = [(256, 256, 128), (384, 768, 768), (1024, 2304, 768), (512, 4096, 768), (300, 520, 264), (128, 128, 64),
                (2048, 768, 2048), (256, 1000, 512), (4096 + 136, 776, 392)]
@@ -477,3 +503,111 @@ def test_vision_helpers_and_casts():
     ff = torch.empty(1003, device=dev())
     nat().cast(ff, bb, 0.5)
     close(ff, bb.float() * 0.5, rtol=1e-6, atol=1e-6, name="cast back")
+
+
+# ------------------------------------------------------------------ 8-bit forward (E4M3 storage + tcgen05 kind::f8f6f4)
+def _e4m3(x_f32, scale):
+    """torch's own E4M3 conversion after the kernels' saturation (+-448), as bytes."""
+    return (x_f32 * scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+
+
+def _bytes_close(a8, e8, max_flip_frac=2e-3):
+    """Two E4M3 byte tensors: equal, except that a value computed in a different fp32 operation order may land on the
+    neighbouring code (byte +-1); such flips must be rare."""
+    a, e = a8.view(torch.int8).int(), e8.view(torch.int8).int()
+    d = (a - e).abs()
+    zero_signs = ((a8 & 0x7f) == 0) & ((e8 & 0x7f) == 0)          # +0 and -0 are the same value
+    d = torch.where(zero_signs, torch.zeros_like(d), d)
+    assert int(d.max()) <= 1, f"E4M3 codes differ by {int(d.max())}"
+    assert float((d != 0).float().mean()) <= max_flip_frac, float((d != 0).float().mean())
+
+
+@pytest.mark.parametrize("M,N,K", [(1024, 2304, 768), (512, 768, 2048), (300, 520, 272), (4096, 1024, 256)])
+def test_linear_fwd_fp8_against_dequantised_product(M, N, K):
+    """E4M3 x E4M3 product on the tensor cores against the fp32 product of the same bytes read back as numbers."""
+    torch.manual_seed(N)
+    x, W = rnd(M, K), rnd(N, K, scale=0.05)
+    sa, sw = 4.0, 64.0
+    x8 = torch.empty(M, K, device=dev(), dtype=torch.uint8)
+    W8 = torch.empty(N, K, device=dev(), dtype=torch.uint8)
+    nat().cast_bf16_fp8(x8, x, sa)
+    nat().cast_bf16_fp8(W8, W, sw)
+    assert torch.equal(x8, _e4m3(x.float(), sa)) and torch.equal(W8, _e4m3(W.float(), sw))
+    out = torch.full((M, N), float("nan"), device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_fp8(out, x8, W8, 1.0 / (sa * sw))
+    exp = (x8.view(torch.float8_e4m3fn).float() @ W8.view(torch.float8_e4m3fn).float().t()) / (sa * sw)
+    close(out, exp, name="fp8 linear")
+    # and against the unquantised product: E4M3 keeps 3 mantissa bits, so a few percent in norm
+    full = x.float() @ W.float().t()
+    assert ((out.float() - full).norm() / full.norm()).item() < 0.06
+    # shapes the 8-bit kernel does not take are declined without a launch
+    assert not nat().linear_fwd_fp8(torch.empty(64, N, device=dev(), dtype=torch.bfloat16), x8[:64], W8, 1.0)
+
+
+def test_linear_fwd_fp8_epilogues():
+    """The 8-bit product with the rotary-embedding epilogue and with the SwiGLU epilogue, against the plain 8-bit
+    product followed by the separate kernels."""
+    torch.manual_seed(3)
+    B, T, H, hd, I = 2, 256, 4, 64, 512
+    C = H * hd
+    M = B * T
+    x8 = _e4m3(rnd(M, C).float(), 2.0)
+    Wq8 = _e4m3(rnd(3 * C, C, scale=0.05).float(), 32.0)
+    Wg8 = _e4m3(rnd(2 * I, C, scale=0.05).float(), 32.0)
+    cos, sin = ref.rope_tables(T, hd, 10000.0, dev())
+    plain = torch.empty(M, 3 * C, device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_fp8(plain, x8, Wq8, 1 / 64.0)
+    roped = torch.empty_like(plain)
+    assert nat().linear_fwd_fp8_rope(roped, x8, Wq8, 1 / 64.0, cos, sin, T, 2 * C)
+    nat().rope_fwd(plain, cos, sin, B, T, H, hd)
+    close(roped, plain.float(), name="fp8 qkv + rope", fro=6e-3)      # rotation of fp32 accumulators vs of bf16 outputs
+    gu = torch.empty(M, 2 * I, device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_fp8(gu, x8, Wg8, 1 / 64.0)
+    gu2, sw2 = torch.empty_like(gu), torch.empty(M, I, device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_fp8_swiglu(gu2, sw2, x8, Wg8, 1 / 64.0)
+    assert torch.equal(gu2, gu)
+    sw = torch.empty_like(sw2)
+    nat().swiglu_fwd(sw, gu)
+    assert torch.equal(sw2, sw)
+
+
+@pytest.mark.parametrize("rows,C", [(512, 768), (100, 264), (33, 100)])
+def test_fp8_producers_write_e4m3_copies(rows, C):
+    """Norms / SwiGLU / AdamW with an additional E4M3 output: the bf16 outputs equal the plain kernels', the bytes equal
+    torch's conversion of the fp32 values (up to rare neighbouring-code flips)."""
+    torch.manual_seed(rows)
+    x, b, w = rnd(rows, C), rnd(rows, C), rnd(C, scale=0.2) + 1.0
+    sa = 8.0
+    out, rstd = torch.empty_like(x), torch.empty(rows, device=dev())
+    out2, rstd2, out8 = torch.empty_like(x), torch.empty(rows, device=dev()), torch.empty(rows, C, device=dev(), dtype=torch.uint8)
+    nat().rmsnorm_fwd(out, rstd, x, w, 1e-5)
+    nat().rmsnorm_fwd_fp8(out2, out8, rstd2, x, w, 1e-5, sa)
+    assert torch.equal(out, out2) and torch.equal(rstd, rstd2)
+    y = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+    _bytes_close(out8, _e4m3(y, sa))
+    res, res2 = torch.empty_like(x), torch.empty_like(x)
+    nat().add_rmsnorm_fwd(res, out, rstd, x, b, w, 1e-5)
+    nat().add_rmsnorm_fwd_fp8(res2, out2, out8, rstd2, x, b, w, 1e-5, sa)
+    assert torch.equal(out, out2) and torch.equal(res, res2)
+    s = x.float() + b.float()
+    _bytes_close(out8, _e4m3(s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float(), sa))
+    if C % 8 == 0:
+        I = C
+        gu = rnd(rows, 2 * I)
+        sw, sw2, sw8 = torch.empty(rows, I, device=dev(), dtype=torch.bfloat16), torch.empty(rows, I, device=dev(), dtype=torch.bfloat16), \
+            torch.empty(rows, I, device=dev(), dtype=torch.uint8)
+        nat().swiglu_fwd(sw, gu)
+        nat().swiglu_fwd_fp8(sw2, sw8, gu, sa)
+        assert torch.equal(sw, sw2)
+        g, u = gu[:, :I].float(), gu[:, I:].float()
+        _bytes_close(sw8, _e4m3(g * torch.sigmoid(g) * u, sa), max_flip_frac=2e-2)     # __expf vs torch's sigmoid
+    n = rows * C
+    master, grads = torch.randn(n, device=dev()) * 0.02, torch.randn(n, device=dev()) * 1e-3
+    m, v = torch.zeros(n, device=dev()), torch.zeros(n, device=dev())
+    m2, v2, master2 = m.clone(), v.clone(), master.clone()
+    p, p2, p8 = torch.empty(n, device=dev(), dtype=torch.bfloat16), torch.empty(n, device=dev(), dtype=torch.bfloat16), \
+        torch.empty(n, device=dev(), dtype=torch.uint8)
+    nat().adamw(master, p, grads, m, v, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05)
+    nat().adamw_fp8(master2, p2, p8, grads, m2, v2, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0, 32.0)
+    assert torch.equal(master, master2) and torch.equal(p, p2) and torch.equal(m, m2) and torch.equal(v, v2)
+    assert torch.equal(p8, _e4m3(master2, 32.0))

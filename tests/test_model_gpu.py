@@ -111,6 +111,74 @@ def test_fp8_forward_option_gpu_matches_cpu_oracle():
         assert ((a - b).norm() / (b.norm() + 1e-12)).item() < 0.15, f"grad mismatch (norm) in {name}"
 
 
+def test_fp8_native_forward_against_its_bf16_form_and_trains():
+    """The 8-bit tensor-core forward (E4M3 storage, kind::f8f6f4 GEMMs, fused producers) against the same model with the
+    operands rounded to E4M3 but multiplied by the bf16 kernel (ENTROPY_FP8_QDQ=1): same loss, same logits up to the
+    points where the two differ by design (E4M3 of the fp32 norm output vs of its bf16 rounding), and a short run
+    with the optimizer keeps the E4M3 weights current and brings the loss down."""
+    import os
+    cfg, B = Config(V=512, C=256, L=2, H=4, I=512, T=256), 2
+    ids, tgt = Stream(99).token_pairs(B * cfg.T, cfg.V)
+    os.environ["ENTROPY_FP8_QDQ"] = "1"
+    try:
+        q = GPT(cfg, B, "cuda:0", fp8_fwd=True)
+    finally:
+        del os.environ["ENTROPY_FP8_QDQ"]
+    n = GPT(cfg, B, "cuda:0", fp8_fwd=True)
+    assert n.fp8_native and not q.fp8_native and n.params8 is not None
+    for g in (q, n):
+        g.init_weights(1234)
+    lq = q.forward(ids.cuda()).float().clone()
+    ln = n.forward(ids.cuda()).float().clone()
+    assert ((ln - lq).norm() / lq.norm()).item() < 0.05
+    q.backward(ids.cuda(), tgt.cuda())
+    n.backward(ids.cuda(), tgt.cuda())
+    torch.cuda.synchronize()
+    assert abs(q.mean_loss() - n.mean_loss()) < 2e-2
+    assert ((n.grads - q.grads).norm() / q.grads.norm()).item() < 0.1
+    tr = Trainer(cfg, B, "cuda:0", lr=1e-3, wd=0.0)
+    assert not tr.model.fp8_native
+    from ml_b200.config import RunConfig
+    r = RunConfig()
+    r.fp8_fwd = 1
+    tr8 = Trainer(cfg, B, "cuda:0", r, lr=1e-3, wd=0.0)
+    assert tr8.model.fp8_native
+    tr8.set_batch(ids.cuda(), tgt.cuda())
+    first = None
+    for s in range(40):
+        tr8.step()
+        if s == 0:
+            first = tr8.loss()
+    assert tr8.loss() < 0.6 * first, (first, tr8.loss())
+    exp8 = (tr8.model.master * tr8.model.fp8_w_scale).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert torch.equal(tr8.model.params8, exp8)          # written by AdamW in the same pass as the bf16 copy
+    assert _native().get_error() == 0
+
+
+def test_graph_step_equals_eager_step_from_the_first_step():
+    """The capture's warm-up run IS step 1 (no replay follows it): after 1 and after 4 steps the parameters of a
+    graph-replaying trainer equal those of an eager one bit for bit."""
+    cfg, B = Config(V=512, C=256, L=2, H=4, I=512, T=128), 2
+    ids, tgt = Stream(7).token_pairs(B * cfg.T, cfg.V)
+    _native().lib().mlb_gemm_set_splits(1)      # one work item per weight-gradient tile: no order-dependent fp32 adds
+    try:
+        res = []
+        for graph in (False, True):
+            tr = Trainer(cfg, B, "cuda:0", lr=1e-3, wd=0.1, use_graph=graph)
+            tr.set_batch(ids.cuda(), tgt.cuda())
+            snaps = []
+            for s in range(4):
+                tr.step()
+                if s in (0, 3):
+                    torch.cuda.synchronize()
+                    snaps.append(tr.model.master.clone())
+            res.append(snaps)
+            tr.close()
+    finally:
+        _native().lib().mlb_gemm_set_splits(0)
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+
+
 def test_overfit_gpu():
     cfg = Config(V=256, C=128, L=4, H=4, I=256, T=64)
     tr = Trainer(cfg, 4, "cuda:0", lr=1e-3, wd=0.0)
