@@ -52,6 +52,25 @@ def timeit(fn, iters=20, warm=10, flush=True):
     return ts[len(ts) // 2]
 
 
+def timechain(fn, n=24, iters=8, warm=2):
+    """Back-to-back launches without a synchronisation in between (what a captured training step does): the time of
+    `n` consecutive calls divided by n, median of `iters`; the inputs of one call are what the previous ones left in L2."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / n)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
 def bench_corun(a):
     """How much a small kernel on a second stream costs the tensor-core GEMMs: 24 QKV-shaped products on one stream,
     timed alone and next to a probe kernel (no shared memory, 32 registers) that idles or streams memory meanwhile."""
@@ -123,7 +142,10 @@ def bench_gemm(a):
         for op, ours, lib in (*ops_list,
                               ("dX", lambda: nat.linear_dx(dx, dout, W), lambda: torch.matmul(dout, W, out=dx)),
                               ("dW", lambda: nat.linear_dw(dW, dout, x), lambda: torch.matmul(dout.t(), x, out=dWb))):
-            t, tl = timeit(ours, a.iters, a.warm, not a.hot), timeit(lib, a.iters, a.warm, not a.hot)
+            if a.chain:
+                t, tl = timechain(ours), timechain(lib)
+            else:
+                t, tl = timeit(ours, a.iters, a.warm, not a.hot), timeit(lib, a.iters, a.warm, not a.hot)
             print(f"{nm:<10}{op:<5}{t * 1e3:>10.1f}{fl / t / 1e9:>10.0f}{fl / t / 1e9 / tf_peak:>18.2f}{tl * 1e3:>11.1f}{fl / tl / 1e9:>10.0f}")
         del x, W, out, dout, dx, dW, dWb
     print("kernel error word:", nat.get_error())
@@ -309,6 +331,7 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
+    ap.add_argument("--chain", action="store_true", help="gemm: 24 launches back to back per sample, no synchronisation or flush in between")
     ap.add_argument("--hot", action="store_true", help="gemm: no L2 flush between launches (operands that fit stay in L2, as behind a producer kernel)")
     ap.add_argument("--fwd-balance", type=int, default=1, help="persistent attention kernels: 1 = balanced work schedule from the host, 0 = round robin")
     ap.add_argument("--fwd-mode", type=int, default=3, help="attention forward, head size 64: 1 = thread-per-row kernel, O folded into registers; 2 = O accumulated in TMEM with lazy rescale; 3 = 2 in one pass per key block; 0 = four threads per row")

@@ -840,6 +840,7 @@ int g_tile_order = 0;        // tuning hook: 0 = by operand size, 1 = M first, 2
 int g_sk_groups = 1;         // tuning hook: 0 = stream-K without groups (one linear range per cluster)
 int g_streamk = 1;           // tuning hook: weight-gradient products cut into equal k-block ranges per cluster
 int g_epi_mode = 1;          // tuning hook: pair kernel's epilogue, 0 = TMA store / reduce, 1 = coalesced stores by the warps
+int g_small_tiles = 1;       // tuning hook: 0 = never trade the CTA-pair tile for 128 x 128 tiles on small problems
 template <bool A_MN, bool B_MN, int EPI, int EMODE>
 int launch_tc2(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, const GemmArgs& g, cudaStream_t st) {
   using Gemm2Smem = Gemm2Smem<EMODE>;
@@ -909,8 +910,28 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
     gemm_simt_kernel<EPI><<<grid, 256, 0, st>>>(out, A, B, M, N, K, sam, sak, sbn, sbk, ldo);
     return (int)cudaGetLastError();
   }
-  const int BN = (N > 128) ? 256 : 128;
-  const bool pairs = g_use_pairs && BN == 256 && M > 128;   // 256 x 256 tile shared by a CTA pair
+  // Tile shape.  Large products run on CTA pairs (256 x 256 per SM pair: least operand traffic per FLOP).  When such tiles
+  // are too few to occupy the machine (a skinny output at a small token count, e.g. M = 2048, N = 768: 24 pair tiles for
+  // 74 SM pairs) the 1-CTA kernel with 128 x 128 tiles has the same multiply rate per SM and four times as many tiles.
+  // Estimated cycles: waves x (k-blocks x cycles per k-block + a fixed cost per tile for ramp and epilogue); the 128-wide
+  // tile pays ~25 % more per k-block for its operand traffic.
+  int BN = (N > 128) ? 256 : 128;
+  bool pairs = g_use_pairs && BN == 256 && M > 128;   // 256 x 256 tile shared by a CTA pair
+  if (pairs && !rope && !swi && g_small_tiles) {
+    const long kb = ceil_div_i(K, BK);
+    const long pt = (long)ceil_div_i(M, 256) * ceil_div_i(N, 256), ct = (long)ceil_div_i(M, 128) * ceil_div_i(N, 128);
+    const long pc = pair_clusters(), sm = g_max_ctas > 0 ? g_max_ctas : num_sms();
+    double cost_pair, cost_c128;
+    if (EPI == EPI_F32_ADD) {       // both forms split the reduction to fill the machine
+      cost_pair = (double)pt * kb / pc * 512.0 + 4000.0;
+      cost_c128 = (double)ct * kb / sm * 320.0 + 3000.0;
+      if (ct * kb / 8 < sm) cost_c128 = 1e30;      // too little work per CTA even at the smallest split
+    } else {
+      cost_pair = (double)((pt + pc - 1) / pc) * (kb * 512.0 + 2000.0);
+      cost_c128 = (double)((ct + sm - 1) / sm) * (kb * 320.0 + 2000.0);
+    }
+    if (cost_c128 < 0.8 * cost_pair) { pairs = false; BN = 128; }
+  }
   if (rope && !(pairs && rope->cols % 64 == 0 && N % 64 == 0)) return -7;
   GemmArgs g;
   g.cosT = rope ? rope->cosT : nullptr; g.sinT = rope ? rope->sinT : nullptr;
@@ -1173,6 +1194,7 @@ MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }
 MLB_API void mlb_gemm_use_3d_maps(int on) { g_use_3d = on; }
 MLB_API void mlb_gemm_use_pairs(int on) { g_use_pairs = on; }
 MLB_API void mlb_gemm_epilogue_mode(int m) { g_epi_mode = m; }
+MLB_API void mlb_gemm_small_tiles(int on) { g_small_tiles = on; }
 MLB_API void mlb_gemm_streamk(int on) { g_streamk = on; }
 MLB_API void mlb_gemm_tile_order(int mode) { g_tile_order = mode; }
 MLB_API void mlb_gemm_streamk_groups(int on) { g_sk_groups = on; }

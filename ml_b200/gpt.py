@@ -255,9 +255,27 @@ def _train_loop(argv, ddp):
     ap.add_argument("--eval-batches", type=int, default=8, help="micro-batches per evaluation")
     ap.add_argument("--tensorboard", action="store_true", help="accepted for compatibility: --log-dir always gets event files")
     ap.add_argument("--verbose", action="store_true")
+    # topology / precision options of the prototype's command line (csrc/src/main.cu:30-57)
+    ap.add_argument("--pp-size", type=int, default=1, help="pipeline stages (1F1B over NCCL point-to-point); world must equal pp-size x tp-size")
+    ap.add_argument("--tp-size", type=int, default=1, help="tensor-parallel ranks (column / row parallel linears)")
+    ap.add_argument("--microbatches", type=int, default=0, help="micro-batches per optimizer step of the pipeline (default ENTROPY_MICROBATCHES)")
+    ap.add_argument("--nodes", type=int, default=1)
+    ap.add_argument("--gpus-per-node", type=int, default=0)
+    ap.add_argument("--node-id", "--host-id", type=int, default=0)
+    ap.add_argument("--bf16", action="store_true", help="bf16 compute (what the kernels implement; the default on a GPU)")
+    ap.add_argument("--fp16", action="store_true", help="accepted for compatibility: the kernels are bf16, fp16 is not built")
     a = ap.parse_args(argv)
     if a.max_steps > 0:
         a.steps = a.max_steps
+    if a.fp16:
+        print("note: --fp16 has no effect: the sm_100a kernels compute in bf16 with fp32 master weights", file=sys.stderr)
+    if a.gpus_per_node > 0 and "RANK" not in os.environ and "SLURM_PROCID" not in os.environ:
+        # launched by hand on one of several nodes: global rank = node id x GPUs per node + local rank
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        os.environ["RANK"] = str(a.node_id * a.gpus_per_node + local)
+        os.environ["WORLD_SIZE"] = str(a.nodes * a.gpus_per_node)
+    if a.pp_size > 1 or a.tp_size > 1 or a.microbatches > 0:
+        return _train_loop_model_parallel(a)
     if ddp:
         rank, world, local, dev = init_distributed()
     else:
@@ -391,6 +409,65 @@ def _train_loop(argv, ddp):
     pipe.close()
     tr.close()
     if ddp:
+        shutdown()
+    return 0
+
+
+def _train_loop_model_parallel(a):
+    """`train_ddp --pp-size P` / `--tp-size T`: the model is cut over the ranks instead of replicated.
+    Pipeline: rank = stage, 1F1B over NCCL point-to-point (ml_b200.parallel.pp); every rank reads the same token windows
+    (the first stage uses the ids, the last the targets); the last stage's loss is what is printed.
+    Tensor parallel: every rank holds a slice of each block's heads and MLP columns (ml_b200.parallel.tp.TPDecoder)."""
+    import torch
+    import torch.distributed as dist
+    from . import Config, RunConfig
+    from .data import TokenLoader
+    from .parallel.bootstrap import init_distributed, shutdown
+    rank, world, local, dev = init_distributed()
+    if rank == 0:
+        _banner("train_ddp (model parallel)", dev)
+    cfg = Config.from_env()
+    if a.seq_len > 0:
+        cfg.T = a.seq_len
+    run = RunConfig.from_env()
+    B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
+    if a.pp_size * a.tp_size != world:
+        sys.exit(f"--pp-size {a.pp_size} x --tp-size {a.tp_size} must equal the number of ranks ({world}); "
+                 "data-parallel replicas of a model-parallel group are not built")
+    if a.pp_size > 1 and a.tp_size > 1:
+        sys.exit("pipeline and tensor parallelism cannot be combined in one run here")
+    hyper = dict(lr=a.lr, wd=a.weight_decay)
+    if a.tp_size > 1:
+        from .parallel.tp import TPTrainer
+        M = 1
+        eng = TPTrainer(cfg, B, rank, world, dev, hyper=hyper)
+    else:
+        from .parallel.pp import PipelineStage
+        M = a.microbatches if a.microbatches > 0 else run.microbatches
+        eng = PipelineStage(cfg, B, a.pp_size, rank, dev, microbatches=M, hyper=hyper)
+    loader = TokenLoader(a.bin, B * M, cfg.T)
+    if rank == 0:
+        print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} steps={a.steps}")
+    n = B * cfg.T
+    t_last = time.perf_counter()
+    for step in range(a.steps):
+        ids, tgt = loader.next()
+        ids, tgt = ids.to(dev), tgt.to(dev)
+        eng.hyper["lr"] = lr_at(step, a.steps, a.lr, a.warmup_ratio)
+        if a.tp_size > 1:
+            loss = eng.step(ids, tgt)
+        else:
+            loss = eng.step([ids[k * n:(k + 1) * n] for k in range(M)], [tgt[k * n:(k + 1) * n] for k in range(M)])
+        if (step + 1) % run.log_every == 0 or step + 1 == a.steps:
+            t = torch.tensor([loss if loss is not None else 0.0], device=dev)
+            if world > 1:
+                dist.broadcast(t, src=world - 1)           # the last stage (any tensor-parallel rank) knows the loss
+            now = time.perf_counter()
+            if rank == 0:
+                print(f"step {step + 1:5d} | loss {float(t.item()):.4f} | {(now - t_last) * 1e3:.2f} ms since last log")
+            t_last = now
+    loader.close()
+    if world > 1:
         shutdown()
     return 0
 

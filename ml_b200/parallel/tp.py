@@ -7,6 +7,12 @@ Here the two standard pieces exist and compose into a Megatron-style MLP / atten
 * ColumnParallelLinear: W[N,K] split along N; input replicated, output sharded (QKV, gate|up); backward all-reduces dX;
 * RowParallelLinear:    W[N,K] split along K; input sharded, output all-reduced (O, down); backward needs no collective.
 
+`TPDecoder` is the whole decoder built from these: every block's heads (QKV rows, O columns) and MLP columns are split
+over the ranks, the embedding, the norms and the LM head are replicated (their inputs are, so their gradients agree on
+all ranks without a collective).  `TPTrainer` trains it: fp32 master weights and AdamW moments of this rank's slice in
+flat buffers updated by the AdamW kernel, the module's parameters being views of the flat compute-dtype copy.
+`train_ddp --tp-size N` (ml_b200.gpt) runs it.
+
 Rank math follows the reference's topology: tp_rank = rank % tp, dp = world / (tp * pp) (csrc/src/comm.cu:58-68).
 """
 from __future__ import annotations
@@ -91,3 +97,105 @@ class TPSwiGLU(nn.Module):
     def forward(self, x):
         gu = torch.cat([self.gate(x), self.up(x)], dim=1)
         return self.down(F.swiglu(gu))
+
+
+class TPBlock(nn.Module):
+    """One decoder block with its heads and MLP columns split `tp` ways.  `full` is a ml_b200.models.modules.Block with
+    the complete weights; this rank keeps query / key / value rows and O columns of heads [r*H/tp, (r+1)*H/tp) and
+    gate / up rows and down columns [r*I/tp, (r+1)*I/tp)."""
+
+    def __init__(self, full, cfg, tp_rank: int, tp: int, group=None):
+        super().__init__()
+        C, I, H, hd = cfg.C, cfg.I, cfg.H, cfg.hd
+        assert H % tp == 0 and I % tp == 0, "heads and MLP width must divide by the tensor-parallel size"
+        self.cfg, self.Hl, self.group = cfg, H // tp, group
+        r0, r1 = tp_rank * self.Hl * hd, (tp_rank + 1) * self.Hl * hd
+        W = full.qkv.detach()
+        self.ln1 = nn.Parameter(full.ln1.detach().clone())
+        self.qkv = nn.Parameter(torch.cat([W[r0:r1], W[C + r0:C + r1], W[2 * C + r0:2 * C + r1]]).clone())
+        self.o = nn.Parameter(full.o.detach()[:, r0:r1].clone())
+        self.ln2 = nn.Parameter(full.ln2.detach().clone())
+        i0, i1 = tp_rank * (I // tp), (tp_rank + 1) * (I // tp)
+        G = full.gate_up.detach()
+        self.gate_up = nn.Parameter(torch.cat([G[i0:i1], G[I + i0:I + i1]]).clone())
+        self.down = nn.Parameter(full.down.detach()[:, i0:i1].clone())
+
+    def forward(self, x, cos, sin, B):
+        c = self.cfg
+        h = _AllReduceBackward.apply(F.rmsnorm(x, self.ln1, c.eps), self.group)
+        a = F.rope_causal_attention(F.linear(h, self.qkv), cos, sin, B, c.T, self.Hl, c.hd)
+        x = x + _AllReduceForward.apply(F.linear(a, self.o), self.group)
+        h = _AllReduceBackward.apply(F.rmsnorm(x, self.ln2, c.eps), self.group)
+        return x + _AllReduceForward.apply(F.linear(F.swiglu(F.linear(h, self.gate_up)), self.down), self.group)
+
+
+class TPDecoder(nn.Module):
+    """Tensor-parallel decoder: same function as ml_b200.models.modules.Decoder, weights cut from `full`."""
+
+    def __init__(self, full, tp_rank: int, tp: int, group=None):
+        super().__init__()
+        self.cfg = c = full.cfg
+        self.wte = nn.Parameter(full.wte.detach().clone())
+        self.blocks = nn.ModuleList([TPBlock(b, c, tp_rank, tp, group) for b in full.blocks])
+        self.lnf = nn.Parameter(full.lnf.detach().clone())
+        self.lm = nn.Parameter(full.lm.detach().clone())
+        self.register_buffer("cos", full.cos.clone(), persistent=False)
+        self.register_buffer("sin", full.sin.clone(), persistent=False)
+
+    def forward(self, ids, tgt=None):
+        c = self.cfg
+        B = ids.numel() // c.T
+        x = F.embedding(self.wte, ids.view(-1), c.T)
+        for b in self.blocks:
+            x = b(x, self.cos, self.sin, B)
+        logits = F.linear(F.rmsnorm(x, self.lnf, c.eps), self.lm)
+        if tgt is None:
+            return logits
+        return F.cross_entropy(logits, tgt.view(-1))
+
+
+class TPTrainer:
+    """Training step of a TPDecoder: autograd over the kernels' differentiable forms, then one AdamW kernel over this
+    rank's flat fp32 master / moment buffers (weights initialised like the unsharded model, train/gpt.cu:780-806)."""
+
+    def __init__(self, cfg, B: int, tp_rank: int, tp: int, device, group=None, hyper=None, seed: int = 1234):
+        from ..layout import DecoderLayout
+        from ..models.modules import Decoder
+        from ..utils import rng as _rng
+        from .. import ops
+        self.ops = ops
+        dev = torch.device(device)
+        full = Decoder(cfg, "cpu", torch.float32)
+        full.load_flat(_rng.init_decoder(DecoderLayout(cfg), seed))
+        dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+        self.model = TPDecoder(full, tp_rank, tp, group)
+        ps = list(self.model.parameters())
+        n = sum(p.numel() for p in ps)
+        self.master = torch.cat([p.detach().reshape(-1).float() for p in ps]).to(dev)
+        self.params = self.master if dtype == torch.float32 else self.master.to(dtype)
+        self.grads = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.m, self.v = torch.zeros_like(self.grads), torch.zeros_like(self.grads)
+        self.model.to(dev)
+        off = 0
+        self.slices = []
+        for p in ps:                       # the module's parameters become views of the flat compute-dtype copy
+            p.data = self.params[off:off + p.numel()].view(p.shape)
+            self.slices.append((p, off, p.numel()))
+            off += p.numel()
+        self.hyper = dict(lr=1e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1)
+        if hyper:
+            self.hyper.update(hyper)
+        self.t = 1
+
+    def step(self, ids, tgt) -> float:
+        for p, _, _ in self.slices:
+            p.grad = None
+        loss = self.model(ids, tgt)
+        loss.backward()
+        for p, off, n in self.slices:
+            self.grads[off:off + n].copy_(p.grad.reshape(-1))
+        h = self.hyper
+        self.ops.adamw(self.master, self.params, self.grads, self.m, self.v, h["lr"], h["b1"], h["b2"], h["eps"], h["wd"],
+                       1.0 - h["b1"] ** self.t, 1.0 - h["b2"] ** self.t, 1.0, None)
+        self.t += 1
+        return float(loss.detach())

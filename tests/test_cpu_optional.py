@@ -37,6 +37,65 @@ def test_tensor_parallel_mlp_equals_unsharded():
         assert float(line[1]) < 1e-5 and float(line[2]) < 1e-5 and line[4] == "1"
 
 
+def test_tensor_parallel_decoder_trains_like_the_unsharded_one(tmp_path):
+    """`train_ddp --tp-size 2` on two CPU ranks (heads and MLP columns split, autograd over the kernels' differentiable
+    forms, AdamW kernel on each rank's flat slice) against the flat-buffer trainer on one rank: same losses."""
+    import os
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    g = _t.Generator().manual_seed(5)
+    path = str(tmp_path / "tok.bin")
+    write_token_bin(path, _t.randint(0, 64, (2 * 16 * 12 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "2", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "1", "ENTROPY_DEVICE": "cpu"}
+    import textwrap
+    body = textwrap.dedent("""
+        import os, sys
+        os.environ.update(ENV)
+        from ml_b200 import gpt
+        sys.exit(gpt.main(ARGS))
+    """)
+    def lines(outs):
+        assert all(rc == 0 for rc, _ in outs), outs
+        o = [o for _, o in outs if "step " in o][0]
+        return [float(l.split("loss")[1].split("|")[0]) for l in o.splitlines() if l.startswith("step ") and "loss" in l]
+    tp = lines(run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path, "5", "--tp-size", "2", "--lr", "1e-3"]) + body, 2))
+    one = lines(run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train", path, "5", "--lr", "1e-3"]) + body, 1))
+    assert len(tp) == 5 and len(one) == 5
+    for a, b in zip(tp, one):
+        assert abs(a - b) < 2e-4, (tp, one)
+    assert tp[-1] < tp[0]
+
+
+def test_pipeline_mode_two_stages_equal_one_stage(tmp_path):
+    """`train_ddp --pp-size 2` (1F1B over point-to-point messages, two CPU ranks) against the same schedule with one
+    stage (`--microbatches 4` alone): same losses step by step."""
+    import textwrap
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    g = _t.Generator().manual_seed(6)
+    path = str(tmp_path / "tok.bin")
+    write_token_bin(path, _t.randint(0, 64, (4 * 2 * 16 * 6 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "4", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "1", "ENTROPY_DEVICE": "cpu"}
+    body = textwrap.dedent("""
+        import os, sys
+        os.environ.update(ENV)
+        from ml_b200 import gpt
+        sys.exit(gpt.main(ARGS))
+    """)
+    def lines(outs):
+        assert all(rc == 0 for rc, _ in outs), outs
+        o = [o for _, o in outs if "step " in o][0]
+        return [float(l.split("loss")[1].split("|")[0]) for l in o.splitlines() if l.startswith("step ") and "loss" in l]
+    two = lines(run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path, "4", "--pp-size", "2", "--microbatches", "4", "--lr", "1e-3"]) + body, 2))
+    one = lines(run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path, "4", "--microbatches", "4", "--lr", "1e-3"]) + body, 1))
+    assert len(two) == 4 and len(one) == 4
+    for a, b in zip(two, one):
+        assert abs(a - b) < 2e-4, (two, one)
+    assert two[-1] < two[0]
+
+
 def test_moe_block_routes_and_trains():
     torch.manual_seed(0)
     moe = MoEBlock(C=16, I=24, n_experts=4, top_k=2, std=0.3)
