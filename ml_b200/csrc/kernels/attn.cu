@@ -1835,14 +1835,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_q_tc_kernel(const __g
 
 // ================================================================== SIMT fallback (any head size <= 256, any T)
 // One block per (query row, head, sample); scores kept in shared memory.
+// `last` = index of the last key a query sees: the query's own position (causal) or T - 1 (bidirectional, the vision
+// encoder's attention).
 __global__ void attn_fwd_simt_k(bf16* __restrict__ out, float* __restrict__ lse, const bf16* __restrict__ qkv, int B, int T, int H,
-                                int hd, float scale) {
+                                int hd, float scale, int causal = 1) {
   extern __shared__ float sc[];  // T scores + 32 reduce
   float* red = sc + T;
   const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z, C = H * hd;
+  const int last = causal ? i : T - 1;
   const bf16* q = qkv + ((size_t)(b * T + i)) * 3 * C + h * hd;
   float mx = -INFINITY;
-  for (int j = threadIdx.x; j <= i; j += blockDim.x) {
+  for (int j = threadIdx.x; j <= last; j += blockDim.x) {
     const bf16* k = qkv + ((size_t)(b * T + j)) * 3 * C + C + h * hd;
     float s = 0.f;
     for (int d = 0; d < hd; d++) s += __bfloat162float(q[d]) * __bfloat162float(k[d]);
@@ -1852,12 +1855,12 @@ __global__ void attn_fwd_simt_k(bf16* __restrict__ out, float* __restrict__ lse,
   }
   mx = block_max(mx, red);
   float sum = 0.f;
-  for (int j = threadIdx.x; j <= i; j += blockDim.x) { float p = __expf(sc[j] - mx); sc[j] = p; sum += p; }
+  for (int j = threadIdx.x; j <= last; j += blockDim.x) { float p = __expf(sc[j] - mx); sc[j] = p; sum += p; }
   sum = block_sum(sum, red);
   __syncthreads();
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
-    for (int j = 0; j <= i; j++) acc += sc[j] * __bfloat162float(qkv[((size_t)(b * T + j)) * 3 * C + 2 * C + h * hd + d]);
+    for (int j = 0; j <= last; j++) acc += sc[j] * __bfloat162float(qkv[((size_t)(b * T + j)) * 3 * C + 2 * C + h * hd + d]);
     out[((size_t)(b * T + i)) * C + h * hd + d] = __float2bfloat16(acc / sum);
   }
   if (threadIdx.x == 0) lse[((size_t)b * H + h) * T + i] = mx + __logf(sum);
@@ -1865,13 +1868,14 @@ __global__ void attn_fwd_simt_k(bf16* __restrict__ out, float* __restrict__ lse,
 // dQ for query i.
 __global__ void attn_bwd_q_simt_k(bf16* __restrict__ dqkv, const bf16* __restrict__ dout, const bf16* __restrict__ qkv,
                                   const float* __restrict__ lse, const float* __restrict__ delta, int B, int T, int H, int hd,
-                                  float scale) {
+                                  float scale, int causal = 1) {
   extern __shared__ float sc[];
   const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z, C = H * hd;
+  const int last = causal ? i : T - 1;
   const bf16* q = qkv + ((size_t)(b * T + i)) * 3 * C + h * hd;
   const bf16* dO = dout + ((size_t)(b * T + i)) * C + h * hd;
   const float L = lse[((size_t)b * H + h) * T + i], D = delta[((size_t)b * H + h) * T + i];
-  for (int j = threadIdx.x; j <= i; j += blockDim.x) {
+  for (int j = threadIdx.x; j <= last; j += blockDim.x) {
     const bf16* k = qkv + ((size_t)(b * T + j)) * 3 * C + C + h * hd;
     const bf16* v = k + C;
     float s = 0.f, dp = 0.f;
@@ -1884,21 +1888,22 @@ __global__ void attn_bwd_q_simt_k(bf16* __restrict__ dqkv, const bf16* __restric
   __syncthreads();
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
-    for (int j = 0; j <= i; j++) acc += sc[j] * __bfloat162float(qkv[((size_t)(b * T + j)) * 3 * C + C + h * hd + d]);
+    for (int j = 0; j <= last; j++) acc += sc[j] * __bfloat162float(qkv[((size_t)(b * T + j)) * 3 * C + C + h * hd + d]);
     dqkv[((size_t)(b * T + i)) * 3 * C + h * hd + d] = __float2bfloat16(acc);
   }
 }
 // dK, dV for key j.
 __global__ void attn_bwd_kv_simt_k(bf16* __restrict__ dqkv, const bf16* __restrict__ dout, const bf16* __restrict__ qkv,
                                    const float* __restrict__ lse, const float* __restrict__ delta, int B, int T, int H, int hd,
-                                   float scale) {
+                                   float scale, int causal = 1) {
   extern __shared__ float sc[];  // p[T], ds[T]
   float* sp = sc;
   float* sds = sc + T;
   const int j = blockIdx.x, h = blockIdx.y, b = blockIdx.z, C = H * hd;
+  const int first = causal ? j : 0;      // first query that sees key j
   const bf16* k = qkv + ((size_t)(b * T + j)) * 3 * C + C + h * hd;
   const bf16* v = k + C;
-  for (int i = j + threadIdx.x; i < T; i += blockDim.x) {
+  for (int i = first + threadIdx.x; i < T; i += blockDim.x) {
     const bf16* q = qkv + ((size_t)(b * T + i)) * 3 * C + h * hd;
     const bf16* dO = dout + ((size_t)(b * T + i)) * C + h * hd;
     float s = 0.f, dp = 0.f;
@@ -1914,7 +1919,7 @@ __global__ void attn_bwd_kv_simt_k(bf16* __restrict__ dqkv, const bf16* __restri
   __syncthreads();
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float dk = 0.f, dv = 0.f;
-    for (int i = j; i < T; i++) {
+    for (int i = first; i < T; i++) {
       dk += sds[i] * __bfloat162float(qkv[((size_t)(b * T + i)) * 3 * C + h * hd + d]);
       dv += sp[i] * __bfloat162float(dout[((size_t)(b * T + i)) * C + h * hd + d]);
     }
@@ -2051,6 +2056,24 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
   }
   if (hd > 256) return -4;
   attn_fwd_simt_k<<<dim3(T, H, B), 128, (T + 32) * sizeof(float), st>>>((bf16*)out, lse, (const bf16*)qkv, B, T, H, hd, scale);
+  return (int)cudaGetLastError();
+}
+
+// Bidirectional (no causal mask) attention for short sequences such as a vision encoder's patch tokens: the scalar
+// kernels, any T and head size <= 256.  Same layouts as mlb_attn_fwd / mlb_attn_bwd; delta is scratch of B*H*T floats.
+MLB_API int mlb_attn_bidir_fwd(void* out, float* lse, const void* qkv, int B, int T, int H, int hd, cudaStream_t st) {
+  if (hd > 256 || (size_t)(T + 32) * sizeof(float) > 48 * 1024) return -4;
+  attn_fwd_simt_k<<<dim3(T, H, B), 128, (T + 32) * sizeof(float), st>>>((bf16*)out, lse, (const bf16*)qkv, B, T, H, hd, 1.0f / sqrtf((float)hd), 0);
+  return (int)cudaGetLastError();
+}
+MLB_API int mlb_attn_bidir_bwd(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, int B, int T,
+                               int H, int hd, cudaStream_t st) {
+  if (hd > 256 || (size_t)2 * T * sizeof(float) > 48 * 1024) return -4;
+  const float scale = 1.0f / sqrtf((float)hd);
+  const long heads = (long)B * T * H;
+  attn_delta_scalar_k<<<(unsigned)((heads * 32 + 255) / 256), 256, 0, st>>>(delta, (const bf16*)dout, (const bf16*)out, B, T, H, hd);
+  attn_bwd_q_simt_k<<<dim3(T, H, B), 128, T * sizeof(float), st>>>((bf16*)dqkv, (const bf16*)dout, (const bf16*)qkv, lse, delta, B, T, H, hd, scale, 0);
+  attn_bwd_kv_simt_k<<<dim3(T, H, B), 128, 2 * T * sizeof(float), st>>>((bf16*)dqkv, (const bf16*)dout, (const bf16*)qkv, lse, delta, B, T, H, hd, scale, 0);
   return (int)cudaGetLastError();
 }
 

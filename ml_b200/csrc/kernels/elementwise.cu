@@ -144,6 +144,64 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, flo
   }
 }
 
+// ------------------------------------------------------------------ LayerNorm (the prototype's norm: csrc/kernels/layer_norm_kernel.cu:12-87)
+// y = (x - mean) * rstd * w + b over the last dimension; one warp per row, statistics in fp32, mean / rstd saved for backward.
+__global__ void __launch_bounds__(256) layernorm_fwd_k(bf16* __restrict__ out, float* __restrict__ mean, float* __restrict__ rstd,
+                                                       const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* __restrict__ b,
+                                                       long rows, int C, float eps) {
+  const int lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const bf16* px = x + row * C;
+  float s = 0.f;
+  for (int i = lane; i < C; i += 32) s += __bfloat162float(px[i]);
+  const float mu = warp_sum(s) / (float)C;
+  float ss = 0.f;
+  for (int i = lane; i < C; i += 32) { const float d = __bfloat162float(px[i]) - mu; ss += d * d; }
+  const float r = rsqrtf(warp_sum(ss) / (float)C + eps);
+  if (lane == 0) { mean[row] = mu; rstd[row] = r; }
+  for (int i = lane; i < C; i += 32) {
+    const float y = (__bfloat162float(px[i]) - mu) * r * __bfloat162float(w[i]) + (b ? __bfloat162float(b[i]) : 0.f);
+    out[row * C + i] = __float2bfloat16(y);
+  }
+}
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) with g = dy * w, xhat = (x - mean) * rstd; dw += sum dy * xhat, db += sum dy.
+// One warp per row; a block folds its rows' dw / db contributions in shared memory (C floats each) before the fp32 atomics.
+__global__ void __launch_bounds__(256) layernorm_bwd_k(bf16* __restrict__ dx, float* __restrict__ dw, float* __restrict__ db,
+                                                       const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                       const float* __restrict__ mean, const float* __restrict__ rstd, long rows, int C) {
+  extern __shared__ float sh[];     // dw partial [C], db partial [C]
+  float* sdw = sh;
+  float* sdb = sh + C;
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sh[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row < rows) {
+    const float mu = mean[row], r = rstd[row];
+    const bf16* px = x + row * C;
+    const bf16* pd = dy + row * C;
+    float sg = 0.f, sgx = 0.f;
+    for (int i = lane; i < C; i += 32) {
+      const float g = __bfloat162float(pd[i]) * __bfloat162float(w[i]), xh = (__bfloat162float(px[i]) - mu) * r;
+      sg += g; sgx += g * xh;
+    }
+    sg = warp_sum(sg) / (float)C;
+    sgx = warp_sum(sgx) / (float)C;
+    for (int i = lane; i < C; i += 32) {
+      const float d = __bfloat162float(pd[i]), xh = (__bfloat162float(px[i]) - mu) * r;
+      dx[row * C + i] = __float2bfloat16(r * (d * __bfloat162float(w[i]) - sg - xh * sgx));
+      atomicAdd(&sdw[i], d * xh);
+      if (db) atomicAdd(&sdb[i], d);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    atomicAdd(&dw[i], sdw[i]);
+    if (db) atomicAdd(&db[i], sdb[i]);
+  }
+}
+
 // ------------------------------------------------------------------ RMSNorm backward, ONE launch, deterministic
 // dx = add + rstd*w*dy - x*rstd^3/C * sum_c(dy*w*x);   dw[c] += sum_rows dy*x*rstd.
 // Each block walks a strided set of rows (warp per row) keeping per-column dw partial sums in registers/shared
@@ -868,6 +926,19 @@ MLB_API int mlb_adamw_fp8(float* master, void* params, void* params8, const floa
   if (n == 0) return 0;
   mlb_launch(adamw_k, dim3(gs((n + 3) / 4, 256)), dim3(256), 0, st, master, (bf16*)params, grads, m, v, n, lr, b1, b2, eps, wd, 1.f / bc1, 1.f / bc2,
              grad_scale, dev_hyper, (uint8_t*)params8, w_scale);
+  LAUNCH_RET;
+}
+
+MLB_API int mlb_layernorm_fwd(void* out, float* mean, float* rstd, const void* x, const void* w, const void* b, long rows, int C, float eps,
+                              cudaStream_t st) {
+  layernorm_fwd_k<<<gs(rows, 8), 256, 0, st>>>((bf16*)out, mean, rstd, (const bf16*)x, (const bf16*)w, (const bf16*)b, rows, C, eps);
+  LAUNCH_RET;
+}
+// dw / db (fp32, db may be NULL) are accumulated into; C * 8 bytes of shared memory must fit the default 48 KB.
+MLB_API int mlb_layernorm_bwd(void* dx, float* dw, float* db, const void* dy, const void* x, const void* w, const float* mean,
+                              const float* rstd, long rows, int C, cudaStream_t st) {
+  if ((size_t)C * 8 > 48 * 1024) return -1;
+  layernorm_bwd_k<<<gs(rows, 8), 256, (size_t)C * 8, st>>>((bf16*)dx, dw, db, (const bf16*)dy, (const bf16*)x, (const bf16*)w, mean, rstd, rows, C);
   LAUNCH_RET;
 }
 

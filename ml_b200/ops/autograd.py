@@ -99,6 +99,52 @@ class RopeCausalAttention(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None
 
 
+class BidirAttention(torch.autograd.Function):
+    """qkv[B*T, 3C] -> out[B*T, C]: attention without a mask (every token sees every token), scale 1/sqrt(hd)."""
+
+    @staticmethod
+    def forward(ctx, qkv, B, T, H, hd):
+        q = qkv.contiguous()
+        out = _like(qkv, B * T, H * hd)
+        lse = _like(qkv, B, H, T, dtype=torch.float32)
+        ops.attn_bidir_fwd(out, lse, q, B, T, H, hd)
+        ctx.save_for_backward(q, out, lse)
+        ctx.dims = (B, T, H, hd)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, out, lse = ctx.saved_tensors
+        B, T, H, hd = ctx.dims
+        dqkv = _like(q, *q.shape)
+        ops.attn_bidir_bwd(dqkv, dout.contiguous(), q, out, lse, B, T, H, hd)
+        return dqkv, None, None, None, None
+
+
+class LayerNorm(torch.autograd.Function):
+    """y = (x - mean) * rstd * w + b over the last dimension (b may be None)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, eps):
+        x = x.contiguous()
+        out = _like(x, *x.shape)
+        mean = _like(x, x.shape[0], dtype=torch.float32)
+        rstd = _like(x, x.shape[0], dtype=torch.float32)
+        ops.layernorm_fwd(out, mean, rstd, x, w, b, eps)
+        ctx.save_for_backward(x, w, mean, rstd)
+        ctx.has_b = b is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, mean, rstd = ctx.saved_tensors
+        dx = _like(x, *x.shape)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        db = torch.zeros(w.shape, dtype=torch.float32, device=w.device) if ctx.has_b else None
+        ops.layernorm_bwd(dx, dw, db, dy.contiguous(), x, w, mean, rstd)
+        return dx, dw.to(w.dtype), (db.to(w.dtype) if db is not None else None), None
+
+
 class CrossEntropy(torch.autograd.Function):
     """Mean loss over rows with tgt >= 0; the logits buffer is consumed (overwritten by its gradient)."""
 
@@ -139,4 +185,6 @@ rmsnorm = RMSNorm.apply
 swiglu = SwiGLU.apply
 rope_causal_attention = RopeCausalAttention.apply
 cross_entropy = CrossEntropy.apply
+bidir_attention = BidirAttention.apply
+layer_norm = LayerNorm.apply
 embedding = Embedding.apply

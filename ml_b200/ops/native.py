@@ -253,6 +253,21 @@ def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
     return rc == 1
 
 
+def attn_bidir_fwd(out, lse, qkv, B, T, H, hd):
+    fn = lib().mlb_attn_bidir_fwd
+    fn.argtypes = [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]
+    fn.restype = _i32
+    _chk(fn(_b(out), _f(lse), _b(qkv), B, T, H, hd, _st()), "attn_bidir_fwd")
+
+
+def attn_bidir_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd):
+    delta = scratch("attn_delta", B * H * T, torch.float32, qkv.device)
+    fn = lib().mlb_attn_bidir_bwd
+    fn.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]
+    fn.restype = _i32
+    _chk(fn(_b(dqkv), _b(dout), _b(qkv), _b(out), _f(lse), _f(delta), B, T, H, hd, _st()), "attn_bidir_bwd")
+
+
 # ------------------------------------------------------------------ embedding
 def embed_fwd(out, wte, ids):
     _chk(lib().mlb_embed_fwd(_b(out), _b(wte), _i(ids), ids.numel(), wte.shape[1], _st()), "embed_fwd")
@@ -279,6 +294,22 @@ def rmsnorm_fwd(out, rstd, x, w, eps):
 def add_rmsnorm_fwd(resid, out, rstd, a, b, w, eps):
     rows, Cc = a.shape
     _chk(lib().mlb_add_rmsnorm_fwd(_b(resid), _b(out), _f(rstd), _b(a), _b(b), _b(w), rows, Cc, eps, _st()), "add_rmsnorm_fwd")
+
+
+def layernorm_fwd(out, mean, rstd, x, w, b, eps):
+    rows, Cc = x.shape
+    fn = lib().mlb_layernorm_fwd
+    fn.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, C.c_long, _i32, C.c_float, _vp]
+    fn.restype = _i32
+    _chk(fn(_b(out), _f(mean), _f(rstd), _b(x), _b(w), _b(b) if b is not None else None, rows, Cc, eps, _st()), "layernorm_fwd")
+
+
+def layernorm_bwd(dx, dw, db, dy, x, w, mean, rstd):
+    rows, Cc = x.shape
+    fn = lib().mlb_layernorm_bwd
+    fn.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_long, _i32, _vp]
+    fn.restype = _i32
+    _chk(fn(_b(dx), _f(dw), _f(db) if db is not None else None, _b(dy), _b(x), _b(w), _f(mean), _f(rstd), rows, Cc, _st()), "layernorm_bwd")
 
 
 def rmsnorm_bwd(dx, dw, dy, x, w, rstd, add=None):

@@ -189,6 +189,52 @@ def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
     return False
 
 
+def attn_bidir_fwd(out, lse, qkv, B, T, H, hd):
+    """Bidirectional SDPA (no mask): the vision encoder's attention over patch tokens; layouts as attn_fwd."""
+    v5 = qkv.view(B, T, 3, H, hd)
+    q, k, v = (_f(v5[:, :, i]).permute(0, 2, 1, 3) for i in range(3))
+    s = (q @ k.transpose(-1, -2)) / math.sqrt(hd)
+    l = torch.logsumexp(s, -1)
+    lse.copy_(l)
+    out.view(B, T, H, hd).copy_((torch.exp(s - l[..., None]) @ v).permute(0, 2, 1, 3))
+
+
+def attn_bidir_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd):
+    v5 = qkv.view(B, T, 3, H, hd)
+    q, k, v = (_f(v5[:, :, i]).permute(0, 2, 1, 3) for i in range(3))
+    do = _f(dout).view(B, T, H, hd).permute(0, 2, 1, 3)
+    o = _f(out).view(B, T, H, hd).permute(0, 2, 1, 3)
+    scale = 1.0 / math.sqrt(hd)
+    p = torch.exp((q @ k.transpose(-1, -2)) * scale - lse[..., None])
+    dv = p.transpose(-1, -2) @ do
+    ds = p * (do @ v.transpose(-1, -2) - (do * o).sum(-1, keepdim=True)) * scale
+    d5 = dqkv.view(B, T, 3, H, hd)
+    d5[:, :, 0] = (ds @ k).permute(0, 2, 1, 3).to(dqkv.dtype)
+    d5[:, :, 1] = (ds.transpose(-1, -2) @ q).permute(0, 2, 1, 3).to(dqkv.dtype)
+    d5[:, :, 2] = dv.permute(0, 2, 1, 3).to(dqkv.dtype)
+
+
+def layernorm_fwd(out, mean, rstd, x, w, b, eps):
+    """y = (x - mean) * rstd * w + b over the last dimension (csrc/kernels/layer_norm_kernel.cu:12-87); b may be None."""
+    xf = _f(x)
+    mu = xf.mean(-1)
+    r = torch.rsqrt(xf.var(-1, unbiased=False) + eps)
+    mean.copy_(mu)
+    rstd.copy_(r)
+    y = (xf - mu[:, None]) * r[:, None] * _f(w)
+    out.copy_(y + _f(b) if b is not None else y)
+
+
+def layernorm_bwd(dx, dw, db, dy, x, w, mean, rstd):
+    """dx written; dw (and db when given) accumulated in fp32."""
+    xh = (_f(x) - mean[:, None]) * rstd[:, None]
+    g = _f(dy) * _f(w)
+    dx.copy_(rstd[:, None] * (g - g.mean(-1, keepdim=True) - xh * (g * xh).mean(-1, keepdim=True)))
+    dw.add_((_f(dy) * xh).sum(0))
+    if db is not None:
+        db.add_(_f(dy).sum(0))
+
+
 # ------------------------------------------------------------------ cross entropy
 def ce_fwd_bwd(losses, logits, tgt, dscale, V_valid=None):
     """Fused CE: losses[row] = logsumexp(z) - z[tgt]; logits are overwritten IN PLACE with

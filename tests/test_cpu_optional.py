@@ -180,3 +180,75 @@ def test_sequence_parallel_single_rank_layouts_coincide():
     sp.seq_to_heads(h, x, 2, 3)
     sp.heads_to_seq(back, h, 2, 3)
     assert torch.equal(h, x) and torch.equal(back, x)        # one rank: both layouts coincide
+
+
+def test_layernorm_and_bidirectional_attention_autograd_against_torch():
+    import torch.nn.functional as TF
+    from ml_b200.ops import autograd as F
+    torch.manual_seed(0)
+    x = torch.randn(12, 20, requires_grad=True)
+    w, b = torch.randn(20, requires_grad=True), torch.randn(20, requires_grad=True)
+    y = F.layer_norm(x, w, b, 1e-5)
+    (y * torch.arange(20.0)).sum().backward()
+    x2, w2, b2 = (t.detach().clone().requires_grad_(True) for t in (x, w, b))
+    y2 = TF.layer_norm(x2, (20,), w2, b2, 1e-5)
+    (y2 * torch.arange(20.0)).sum().backward()
+    assert (y - y2).abs().max() < 1e-5
+    for a, e in ((x, x2), (w, w2), (b, b2)):
+        assert (a.grad - e.grad).abs().max() < 1e-4
+    B, T, H, hd = 2, 7, 3, 8
+    qkv = torch.randn(B * T, 3 * H * hd, requires_grad=True)
+    o = F.bidir_attention(qkv, B, T, H, hd)
+    o.square().sum().backward()
+    q2 = qkv.detach().clone().requires_grad_(True)
+    q, k, v = (q2.view(B, T, 3, H, hd)[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    o2 = TF.scaled_dot_product_attention(q, k, v).permute(0, 2, 1, 3).reshape(B * T, H * hd)
+    o2.square().sum().backward()
+    assert (o - o2).abs().max() < 1e-5 and (qkv.grad - q2.grad).abs().max() < 1e-4
+
+
+def test_vit_encoder_matches_a_plain_pytorch_restatement_and_trains():
+    """Patch-embed + bias, norm, positions, CLS token, attention blocks over all tokens, SwiGLU MLPs, final norm,
+    projector: forward and gradients against the same network written with torch.nn.functional, for both norms."""
+    import torch.nn.functional as TF
+    from ml_b200.models.vit import ViTEncoder
+    for norm in ("rms", "layer"):
+        torch.manual_seed(1)
+        m = ViTEncoder(image_size=32, patch=8, C=32, L=2, H=4, I=48, out_dim=24, norm=norm, device="cpu")
+        with torch.no_grad():
+            for n, p in m.named_parameters():
+                if n.endswith("_b"):
+                    p.copy_(torch.randn(p.shape) * 0.05)
+        px = torch.randn(3, 3, 32, 32)
+
+        def nrm(x, w, b):
+            if norm == "layer":
+                return TF.layer_norm(x, (x.shape[-1],), w, b, m.eps)
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + m.eps) * w + b
+
+        def restated(pixels):
+            B = pixels.shape[0]
+            rows = TF.unfold(pixels, kernel_size=8, stride=8).transpose(1, 2)           # [B, NP, 3*8*8]
+            x = nrm(rows @ m.patch_w.t() + m.patch_b, m.pn_w, m.pn_b)
+            x = torch.cat([m.cls.expand(B, 1, -1), x], 1) + m.pos
+            for blk in m.blocks:
+                h = nrm(x, blk.n1_w, blk.n1_b)
+                qkv = (h @ blk.qkv_w.t() + blk.qkv_b).view(B, m.T, 3, 4, 8)
+                q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+                a = TF.scaled_dot_product_attention(q, k, v).permute(0, 2, 1, 3).reshape(B, m.T, 32)
+                x = x + a @ blk.o_w.t() + blk.o_b
+                h = nrm(x, blk.n2_w, blk.n2_b)
+                gu = h @ blk.gu_w.t() + blk.gu_b
+                x = x + (TF.silu(gu[..., :48]) * gu[..., 48:]) @ blk.down_w.t() + blk.down_b
+            return nrm(x, m.fn_w, m.fn_b)[:, 0] @ m.proj.t()
+
+        out = m(px)
+        out.square().sum().backward()
+        got = {n: p.grad.clone() for n, p in m.named_parameters()}
+        m.zero_grad()
+        exp = restated(px)
+        exp.square().sum().backward()
+        assert out.shape == (3, 24) and (out - exp).abs().max() < 1e-4, norm
+        for n, p in m.named_parameters():
+            assert (got[n] - p.grad).abs().max() < 2e-3 * (1 + p.grad.abs().max()), (norm, n)
+        assert m(px, return_all=True).shape == (3, m.T, 24)

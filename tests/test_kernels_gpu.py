@@ -611,3 +611,62 @@ def test_fp8_producers_write_e4m3_copies(rows, C):
     nat().adamw_fp8(master2, p2, p8, grads, m2, v2, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0, 32.0)
     assert torch.equal(master, master2) and torch.equal(p, p2) and torch.equal(m, m2) and torch.equal(v, v2)
     assert torch.equal(p8, _e4m3(master2, 32.0))
+
+
+# ------------------------------------------------------------------ LayerNorm, bidirectional attention (vision encoder)
+@pytest.mark.parametrize("rows,C", [(1000, 768), (37, 100), (8, 2048)])
+def test_layernorm_fwd_bwd(rows, C):
+    torch.manual_seed(rows)
+    x, w, b, dy = rnd(rows, C), rnd(C, scale=0.3) + 1.0, rnd(C, scale=0.2), rnd(rows, C)
+    out, mean, rstd = torch.empty_like(x), torch.empty(rows, device=dev()), torch.empty(rows, device=dev())
+    nat().layernorm_fwd(out, mean, rstd, x, w, b, 1e-5)
+    eo, em, er = torch.empty(rows, C, device=dev()), torch.empty(rows, device=dev()), torch.empty(rows, device=dev())
+    ref.layernorm_fwd(eo, em, er, x, w, b, 1e-5)
+    close(out, eo, name="layernorm out")
+    close(mean, em, rtol=1e-4, atol=1e-5, name="mean")
+    close(rstd, er, rtol=1e-4, atol=1e-5, name="rstd")
+    dx = torch.empty_like(x)
+    dw, db = torch.zeros(C, device=dev()), torch.zeros(C, device=dev())
+    nat().layernorm_bwd(dx, dw, db, dy, x, w, mean, rstd)
+    edx, edw, edb = torch.empty(rows, C, device=dev()), torch.zeros(C, device=dev()), torch.zeros(C, device=dev())
+    ref.layernorm_bwd(edx, edw, edb, dy, x, w, em, er)
+    close(dx, edx, name="layernorm dx", fro=6e-3)
+    close(dw, edw, rtol=1e-3, atol=1e-3, name="layernorm dw")
+    close(db, edb, rtol=1e-3, atol=1e-3, name="layernorm db")
+
+
+@pytest.mark.parametrize("B,T,H,hd", [(2, 197, 4, 64), (3, 50, 2, 32), (1, 17, 3, 24)])
+def test_bidirectional_attention_fwd_bwd(B, T, H, hd):
+    torch.manual_seed(T)
+    C = H * hd
+    qkv, dout = rnd(B * T, 3 * C), rnd(B * T, C)
+    out, lse = torch.empty(B * T, C, device=dev(), dtype=torch.bfloat16), torch.empty(B, H, T, device=dev())
+    nat().attn_bidir_fwd(out, lse, qkv, B, T, H, hd)
+    eo, el = torch.empty(B * T, C, device=dev()), torch.empty(B, H, T, device=dev())
+    ref.attn_bidir_fwd(eo, el, qkv, B, T, H, hd)
+    close(out, eo, name="bidir attn out")
+    close(lse, el, rtol=1e-3, atol=2e-2, name="bidir lse")
+    dqkv = torch.empty_like(qkv)
+    nat().attn_bidir_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd)
+    e = torch.empty(B * T, 3 * C, device=dev())
+    ref.attn_bidir_bwd(e, dout, qkv, eo, el, B, T, H, hd)
+    close(dqkv, e, rtol=3e-2, atol=3e-2, name="bidir dqkv", fro=1.5e-2)
+
+
+def test_vit_encoder_gpu_against_cpu():
+    from ml_b200.models.vit import ViTEncoder
+    torch.manual_seed(2)
+    cpu = ViTEncoder(image_size=64, patch=16, C=128, L=2, H=2, I=256, out_dim=96, device="cpu")
+    gpu = ViTEncoder(image_size=64, patch=16, C=128, L=2, H=2, I=256, out_dim=96, device="cuda:0")
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(cpu.named_parameters(), gpu.named_parameters()):
+            q.copy_(p.to(q.dtype))
+    px = torch.randn(4, 3, 64, 64)
+    oc = cpu(px)
+    og = gpu(px.cuda())
+    oc.square().sum().backward()
+    og.float().square().sum().backward()
+    assert ((og.float().cpu() - oc).norm() / oc.norm()).item() < 3e-2
+    for (n, p), (_, q) in zip(cpu.named_parameters(), gpu.named_parameters()):
+        d = (q.grad.float().cpu() - p.grad).norm() / (p.grad.norm() + 1e-8)
+        assert d.item() < 8e-2, (n, d.item())
