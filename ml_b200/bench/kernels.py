@@ -139,6 +139,19 @@ def bench_gemm(a):
         if nm == "gate|up":
             sw = torch.empty(M, N // 2, device=dev, dtype=torch.bfloat16)
             ops_list.append(("f+sw", lambda: nat.linear_fwd_swiglu(out, sw, x, W), lambda: (torch.matmul(x, W.t(), out=out), nat.swiglu_fwd(sw, out))))
+        if a.fp8:
+            # the reference's gemm_bench has an E4M3 half (train/gemm_bench.cu:53-187): same shapes, 8-bit operands
+            x8 = torch.empty(M, K, device=dev, dtype=torch.uint8)
+            W8 = torch.empty(N, K, device=dev, dtype=torch.uint8)
+            nat.cast_bf16_fp8(x8, x, 1.0)
+            nat.cast_bf16_fp8(W8, W, 16.0)
+            f8 = lambda: nat.linear_fwd_fp8(out, x8, W8, 1.0 / 16.0)
+            if nat.linear_fwd_fp8(out, x8, W8, 1.0 / 16.0):
+                t = timechain(f8) if a.chain else timeit(f8, a.iters, a.warm, not a.hot)
+                print(f"{nm:<10}{'fp8':<5}{t * 1e3:>10.1f}{fl / t / 1e9:>10.0f}{fl / t / 1e9 / (2 * tf_peak):>18.2f}{'':>11}{'':>10}   (fraction of twice the bf16 peak)")
+            tc = timeit(lambda: nat.cast_bf16_fp8(x8, x, 1.0), a.iters, a.warm, not a.hot)
+            print(f"{nm:<10}{'cast':<5}{tc * 1e3:>10.1f}{'':>10}{'':>18}{'':>11}{'':>10}   bf16 -> E4M3 of the {M}x{K} input: {3 * M * K / tc / 1e6:.0f} GB/s")
+            del x8, W8
         for op, ours, lib in (*ops_list,
                               ("dX", lambda: nat.linear_dx(dx, dout, W), lambda: torch.matmul(dout, W, out=dx)),
                               ("dW", lambda: nat.linear_dw(dW, dout, x), lambda: torch.matmul(dout.t(), x, out=dWb))):
@@ -298,6 +311,21 @@ def once(a):
             nat.rmsnorm_bwd(o, dw, x, x, w, r, x)
             nat.ce_fwd_bwd(ls, lg, tg, 1.0 / rows)
             nat.adamw(ma, p, g, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.5, 1.0)
+    elif a.case == "gemm8":
+        # gate|up-shaped products: bf16 with the SwiGLU epilogue, and the 8-bit (E4M3) forms
+        M, I, K = a.M, a.I, a.C
+        x = torch.randn(M, K, device=dev).bfloat16()
+        W = (torch.randn(2 * I, K, device=dev) * 0.02).bfloat16()
+        x8 = torch.empty(M, K, device=dev, dtype=torch.uint8)
+        W8 = torch.empty(2 * I, K, device=dev, dtype=torch.uint8)
+        nat.cast_bf16_fp8(x8, x, 1.0)
+        nat.cast_bf16_fp8(W8, W, 16.0)
+        gu = torch.empty(M, 2 * I, device=dev, dtype=torch.bfloat16)
+        sw = torch.empty(M, I, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            nat.linear_fwd_swiglu(gu, sw, x, W)
+            nat.linear_fwd_fp8(gu, x8, W8, 1.0 / 16.0)
+            nat.linear_fwd_fp8_swiglu(gu, sw, x8, W8, 1.0 / 16.0)
     else:
         nat.lib().mlb_gemm_use_pairs(a.pairs)
         nat.lib().mlb_gemm_epilogue_mode(a.epi)
@@ -320,7 +348,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "corun", "layouts", "mma", "attn", "norm", "once"])
     ap.add_argument("--K", type=int, default=8192)
-    ap.add_argument("--case", default="attn", choices=["attn", "gemm", "norm"])
+    ap.add_argument("--case", default="attn", choices=["attn", "gemm", "gemm8", "norm"])
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--C", type=int, default=768)
     ap.add_argument("--I", type=int, default=2048)
@@ -331,6 +359,7 @@ def main():
     ap.add_argument("--hd", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warm", type=int, default=10)
+    ap.add_argument("--fp8", action="store_true", help="gemm: add the 8-bit (E4M3) forward product and the bf16 -> E4M3 cast per shape")
     ap.add_argument("--chain", action="store_true", help="gemm: 24 launches back to back per sample, no synchronisation or flush in between")
     ap.add_argument("--hot", action="store_true", help="gemm: no L2 flush between launches (operands that fit stay in L2, as behind a producer kernel)")
     ap.add_argument("--fwd-balance", type=int, default=1, help="persistent attention kernels: 1 = balanced work schedule from the host, 0 = round robin")

@@ -268,8 +268,10 @@ __global__ void __launch_bounds__(256) ddp_bucket_kernel(const BucketArgs a) { d
 // All-gather by peer loads: dst[w*chunk_bytes ...] = shard of rank w, for every w; 16-byte vectors, system-scope loads.
 // No barrier is needed here: the producer of the shards (the reduce-scatter + AdamW kernel of the previous step) ends
 // with a barrier across all ranks, and this kernel is ordered after it on the same stream.
-__global__ void __launch_bounds__(512) allgather_pull_kernel(uint4* __restrict__ dst, const uint4* const* __restrict__ src,
-                                                             long chunk_vec, int world) {
+// 31 registers and no shared memory: with 128-thread CTAs and the largest shared-memory split (set at launch) its CTAs fit
+// beside those of the persistent tensor-core kernels, see ddp_bucket_lean_kernel.
+__global__ void __maxnreg__(32) allgather_pull_kernel(uint4* __restrict__ dst, const uint4* const* __restrict__ src,
+                                                      long chunk_vec, int world) {
   const long total = chunk_vec * world;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const int w = (int)(i / chunk_vec);
@@ -381,14 +383,23 @@ MLB_API int mlb_ddp_bucket(const void* grads_ptrs, const void* params_ptrs, cons
 
 // dst (local) <- concatenation of the `world` shards whose device pointers are in src_ptrs (device array); every shard
 // is chunk_bytes long (a multiple of 16).
-MLB_API int mlb_allgather_pull(void* dst, const void* src_ptrs, long chunk_bytes, int world, int ctas, cudaStream_t st) {
-  if ((chunk_bytes & 15) != 0 || world < 1) return -1;
+// `threads` per CTA: 128 for a launch that shares SMs with compute kernels, 512 for one that has the machine.
+MLB_API int mlb_allgather_pull2(void* dst, const void* src_ptrs, long chunk_bytes, int world, int ctas, int threads, cudaStream_t st) {
+  if ((chunk_bytes & 15) != 0 || world < 1 || threads < 32 || threads > 1024) return -1;
+  static bool carve = false;
+  if (!carve) {
+    cudaFuncSetAttribute(allgather_pull_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    carve = true;
+  }
   const long chunk_vec = chunk_bytes / 16;
-  long want = (chunk_vec * world + 511) / 512;
+  long want = (chunk_vec * world + threads - 1) / threads;
   if (want < 1) want = 1;
   if (ctas < 1) ctas = 32;
-  allgather_pull_kernel<<<(int)(want < ctas ? want : ctas), 512, 0, st>>>((uint4*)dst, (const uint4* const*)src_ptrs, chunk_vec, world);
+  allgather_pull_kernel<<<(int)(want < ctas ? want : ctas), threads, 0, st>>>((uint4*)dst, (const uint4* const*)src_ptrs, chunk_vec, world);
   return (int)cudaGetLastError();
+}
+MLB_API int mlb_allgather_pull(void* dst, const void* src_ptrs, long chunk_bytes, int world, int ctas, cudaStream_t st) {
+  return mlb_allgather_pull2(dst, src_ptrs, chunk_bytes, world, ctas, 512, st);
 }
 
 MLB_API int mlb_corun_probe(float* buf, long n_floats, double dur_s, int mode, int ctas, int threads, int max_shared_carveout, cudaStream_t st) {

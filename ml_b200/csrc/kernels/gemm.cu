@@ -78,6 +78,10 @@ struct GemmArgs {
   bf16* sw_out;
   int sw_I;
   float out_scale;   // 8-bit form: accumulators are multiplied by this (1 / (activation scale * weight scale))
+  // optional learned-position add in the bf16 epilogue (pair kernel): out[r, c] += pos[r % pos_period, c], pos is
+  // [pos_period, N] bf16 (the vision tower's patch embedding: positions repeat every n_patch rows)
+  const bf16* pos;
+  int pos_period;
 };
 
 // Work items of one cluster of the pair kernel.  Static mode: items c, c + nclusters, ... of tiles x splits.
@@ -415,7 +419,9 @@ __device__ __forceinline__ void pack64(const uint32_t (&r)[32], const uint32_t (
 // F8: both operands are E4M3 bytes, K-major; a 128-byte shared-memory row then holds 128 elements of K, one stage 128
 // of K (four K = 32 instructions), and the accumulators are multiplied by g.out_scale (the product of the two dequant
 // scales) on their way out.  Everything else - tiles, ring, barriers, epilogue - is shared with the bf16 form.
-template <bool A_MN, bool B_MN, int EPI, int EMODE, bool F8 = false>
+// POS: the learned-position add of GemmArgs::pos is compiled in (its own instantiation, so that the register allocation of
+// the plain kernels is not affected).
+template <bool A_MN, bool B_MN, int EPI, int EMODE, bool F8 = false, bool POS = false>
 __global__ void __cluster_dims__(2, 1, 1) __maxnreg__(160)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
@@ -589,6 +595,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         uint8_t* rowp = buf + lane * 128;
         if (EPI == EPI_BF16) {
           if (F8) scale64(r, r2, g.out_scale);
+          if (POS && g.pos != nullptr && m0 + lane < g.M) {
+            // this lane's row of the position table, columns col0 .. col0 + 63 (clipped to N): eight 16-byte loads
+            const bf16* prow = g.pos + (size_t)((m0 + lane) % g.pos_period) * g.N + col0;
+#pragma unroll
+            for (int v = 0; v < 8; v++) {
+              if (col0 + v * 8 < g.N) {
+                const uint4 pv = __ldg(reinterpret_cast<const uint4*>(prow) + v);
+                const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                  uint32_t* d = (v < 4) ? &r[v * 8 + 2 * e] : &r2[(v - 4) * 8 + 2 * e];
+                  d[0] = __float_as_uint(__uint_as_float(d[0]) + __uint_as_float(pw[e] << 16));
+                  d[1] = __float_as_uint(__uint_as_float(d[1]) + __uint_as_float(pw[e] & 0xffff0000u));
+                }
+              }
+            }
+          }
           if (g.cosT != nullptr && col0 < g.rope_cols) {   // warp-uniform; the slab is one head: r = first half, r2 = second
             const int t = (m0 + lane) % g.rope_T;
             const float4* c4 = reinterpret_cast<const float4*>(g.cosT + (size_t)t * 32);
@@ -841,10 +864,10 @@ int g_sk_groups = 1;         // tuning hook: 0 = stream-K without groups (one li
 int g_streamk = 1;           // tuning hook: weight-gradient products cut into equal k-block ranges per cluster
 int g_epi_mode = 1;          // tuning hook: pair kernel's epilogue, 0 = TMA store / reduce, 1 = coalesced stores by the warps
 int g_small_tiles = 1;       // tuning hook: 0 = never trade the CTA-pair tile for 128 x 128 tiles on small problems
-template <bool A_MN, bool B_MN, int EPI, int EMODE>
+template <bool A_MN, bool B_MN, int EPI, int EMODE, bool POS = false>
 int launch_tc2(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, const GemmArgs& g, cudaStream_t st) {
   using Gemm2Smem = Gemm2Smem<EMODE>;
-  auto kern = gemm_tc2_kernel<A_MN, B_MN, EPI, EMODE>;
+  auto kern = gemm_tc2_kernel<A_MN, B_MN, EPI, EMODE, false, POS>;
   static int max_clusters = -1;
   if (max_clusters < 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Smem::TOTAL);
@@ -890,9 +913,10 @@ int launch_tc_gather(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUten
 // Same for B with N.  EPI_BF16 stores bf16; EPI_F32_ADD accumulates into fp32.
 struct RopeEpi { const float* cosT; const float* sinT; int T, cols; };
 struct SwigluEpi { bf16* out; int I; };
+struct PosEpi { const bf16* pos; int period; };
 template <bool A_MN, bool B_MN, int EPI>
 int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st,
-                  const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr) {
+                  const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr, const PosEpi* pe = nullptr) {
   bool aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && (lda % 8 == 0) && (ldb % 8 == 0) &&
                  ((uintptr_t)out % 16 == 0) && (ldo % 8 == 0) && (N % 8 == 0) && M > 0 && N > 0 && K > 0;
   // MN-major operands are fetched in 64-wide chunks along M/N: the global extent must be a multiple of 8 elements
@@ -904,6 +928,9 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   if (swi && (g_force_simt || !aligned || get_encode() == nullptr || g_epi_mode != 1 || !g_use_pairs || A_MN || B_MN ||
               EPI != EPI_BF16 || N != 2 * swi->I || swi->I % 128 != 0 || M <= 128 || ((uintptr_t)swi->out & 15)))
     return -7;                                                                       // caller runs the separate kernel
+  if (pe && (g_force_simt || !aligned || get_encode() == nullptr || g_epi_mode != 1 || !g_use_pairs || EPI != EPI_BF16 || M <= 128 ||
+             N <= 128 || N % 8 != 0 || ((uintptr_t)pe->pos & 15) || pe->period < 1))
+    return -7;
   if (g_force_simt || !aligned || get_encode() == nullptr) {
     dim3 grid(ceil_div_i(N, 64), ceil_div_i(M, 64));
     long sam = A_MN ? 1 : lda, sak = A_MN ? lda : 1, sbn = B_MN ? 1 : ldb, sbk = B_MN ? ldb : 1;
@@ -917,7 +944,7 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   // tile pays ~25 % more per k-block for its operand traffic.
   int BN = (N > 128) ? 256 : 128;
   bool pairs = g_use_pairs && BN == 256 && M > 128;   // 256 x 256 tile shared by a CTA pair
-  if (pairs && !rope && !swi && g_small_tiles) {
+  if (pairs && !rope && !swi && !pe && g_small_tiles) {
     const long kb = ceil_div_i(K, BK);
     const long pt = (long)ceil_div_i(M, 256) * ceil_div_i(N, 256), ct = (long)ceil_div_i(M, 128) * ceil_div_i(N, 128);
     const long pc = pair_clusters(), sm = g_max_ctas > 0 ? g_max_ctas : num_sms();
@@ -937,6 +964,7 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   g.cosT = rope ? rope->cosT : nullptr; g.sinT = rope ? rope->sinT : nullptr;
   g.rope_T = rope ? rope->T : 1; g.rope_cols = rope ? rope->cols : 0;
   g.sw_out = swi ? swi->out : nullptr; g.sw_I = swi ? swi->I : 0; g.out_scale = 1.f;
+  g.pos = pe ? pe->pos : nullptr; g.pos_period = pe ? pe->period : 1;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, pairs ? 256 : BM);
   g.tiles_n = swi ? swi->I / 128 : ceil_div_i(N, BN);
@@ -977,6 +1005,9 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   if (!tmB) tmB = B_MN ? mlb_tmap_cached(B, K, N, ldb, 64, 64) : mlb_tmap_cached(B, N, K, ldb, b_rows, 64);
   const CUtensorMap* tmD = (EPI == EPI_BF16) ? mlb_tmap_cached(out, M, N, ldo, 32, 64, 2) : mlb_tmap_cached(out, M, N, ldo, 32, 32, 4);
   if (!tmA || !tmB || !tmD) return -2;
+  if constexpr (!A_MN && !B_MN && EPI == EPI_BF16) {
+    if (pairs && pe) return launch_tc2<false, false, EPI_BF16, 1, true>(tmA, tmB, tmD, g, st);
+  }
   if (pairs && g_epi_mode == 0) return launch_tc2<A_MN, B_MN, EPI, 0>(tmA, tmB, tmD, g, st);
   if (pairs) return launch_tc2<A_MN, B_MN, EPI, 1>(tmA, tmB, tmD, g, st);
   if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
@@ -996,6 +1027,7 @@ int gemm_fp8_dispatch(void* out, int ldo, const uint8_t* A, int lda, const uint8
   g.cosT = rope ? rope->cosT : nullptr; g.sinT = rope ? rope->sinT : nullptr;
   g.rope_T = rope ? rope->T : 1; g.rope_cols = rope ? rope->cols : 0;
   g.sw_out = swi ? swi->out : nullptr; g.sw_I = swi ? swi->I : 0; g.out_scale = out_scale;
+  g.pos = nullptr; g.pos_period = 1;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, 256);
   g.tiles_n = swi ? swi->I / 128 : ceil_div_i(N, 256);
@@ -1070,6 +1102,14 @@ MLB_API int mlb_linear_fwd_swiglu(void* gu, void* sw, const void* x, const void*
   SwigluEpi e{(bf16*)sw, I};
   return gemm_dispatch<false, false, EPI_BF16>(gu, ldgu, (const bf16*)x, ldx, (const bf16*)W, ldw, M, 2 * I, K, st, nullptr, &e);
 }
+// out[M,N] = x[M,K] . W[N,K]^T + pos[row % period, :]: the vision tower's patch embedding with the learned positions added
+// on the fp32 accumulators in the epilogue (the reference runs linear_forward + add_posembed_k, train/gpt.cu:861-863).
+// Returns -7 (nothing launched) when the shape does not take the CTA-pair path (M, N > 128).
+MLB_API int mlb_linear_fwd_posembed(void* out, const void* x, const void* W, const void* pos, int period, int M, int N, int K, int ldo,
+                                    int ldx, int ldw, cudaStream_t st) {
+  PosEpi e{(const bf16*)pos, period};
+  return gemm_dispatch<false, false, EPI_BF16>(out, ldo, (const bf16*)x, ldx, (const bf16*)W, ldw, M, N, K, st, nullptr, nullptr, &e);
+}
 // dx[M,K] = dout[M,N] . W[N,K]      (GEMM view: D[M,K], reduction N; B(n=k_in, k=n_out) is MN-major)
 MLB_API int mlb_linear_dx(void* dx, const void* dout, const void* W, int M, int N, int K, int lddx, int lddo, int ldw, cudaStream_t st) {
   return gemm_dispatch<false, true, EPI_BF16>(dx, lddx, (const bf16*)dout, lddo, (const bf16*)W, ldw, M, K, N, st);
@@ -1116,7 +1156,7 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
   g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0; g.sk_group = 1; g.sk_group_m = 0; g.nt_fast = 0;
-  g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0; g.sw_out = nullptr; g.sw_I = 0; g.out_scale = 1.f;
+  g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0; g.sw_out = nullptr; g.sw_I = 0; g.out_scale = 1.f; g.pos = nullptr; g.pos_period = 1;
   GatherArgs ga;
   ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
   ga.b_lo_vec = w_off_elems / 8; ga.b_hi_vec = (w_off_elems + (long)N * K) / 8; ga.b_row_vec = K / 8;

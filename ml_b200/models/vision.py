@@ -73,8 +73,11 @@ class VisionTower:
         if patches.data_ptr() != self.patches.data_ptr():
             self.patches.copy_(patches)
         patches = self.patches
-        ops.linear_fwd(self.patch_out, patches, self.P(VL.o_pw, vC, vc.patch_dim))
-        ops.add_posembed(self.patch_out, self.P(VL.o_pos, vc.n_patch, vC), vc.n_patch)
+        Wp, pos = self.P(VL.o_pw, vC, vc.patch_dim), self.P(VL.o_pos, vc.n_patch, vC)
+        # the learned positions are added on the patch-embedding GEMM's accumulators where the shape allows
+        if not (patches.is_cuda and ops.native_module().linear_fwd_posembed(self.patch_out, patches, Wp, pos, vc.n_patch)):
+            ops.linear_fwd(self.patch_out, patches, Wp)
+            ops.add_posembed(self.patch_out, pos, vc.n_patch)
         x = self.patch_out
         for l in range(vc.vL):
             b = VL.layer_base(l)

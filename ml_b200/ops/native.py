@@ -189,6 +189,23 @@ def linear_fwd_swiglu(gu, sw, x, W):
     return True
 
 
+def linear_fwd_posembed(out, x, W, pos, period):
+    """out = x . W^T + pos[row % period] with the add on the fp32 accumulators in the GEMM epilogue.  Returns False when
+    the shape does not take that path (nothing was launched)."""
+    M, K = x.shape
+    N = W.shape[0]
+    if pos.shape[-1] != N or not pos.is_contiguous():
+        return False
+    fn = lib().mlb_linear_fwd_posembed
+    fn.argtypes = [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]
+    fn.restype = _i32
+    rc = fn(_b(out), _b(x), _b(W), _b(pos), period, M, N, K, out.stride(0), x.stride(0), W.stride(0), _st())
+    if rc == -7:
+        return False
+    _chk(rc, "linear_fwd_posembed")
+    return True
+
+
 def linear_dx(dx, dout, W):
     M, N = dout.shape
     K = W.shape[1]

@@ -76,6 +76,21 @@ def test_linear_fwd_swiglu_epilogue(M, I, K):
                                        torch.empty(M, 100, device=dev(), dtype=torch.bfloat16), x, W[:200])
 
 
+@pytest.mark.parametrize("M,N,K,period", [(392, 768, 768, 196), (1024, 256, 128, 64), (300, 520, 264, 100)])
+def test_linear_fwd_posembed_epilogue(M, N, K, period):
+    """Patch embedding with the learned positions added in the GEMM epilogue (fp32 accumulators + position, one
+    rounding) against the fp32 oracle of product + add."""
+    torch.manual_seed(M)
+    x, W, pos = rnd(M, K), rnd(N, K, scale=K ** -0.5), rnd(period, N, scale=0.5)
+    out = torch.full((M, N), float("nan"), device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_fwd_posembed(out, x, W, pos, period)
+    exp = torch.empty(M, N, device=dev())
+    ref.linear_fwd(exp, x, W)
+    exp += pos.float().repeat((M + period - 1) // period, 1)[:M]
+    close(out, exp, name="patch embed + pos")
+    assert not nat().linear_fwd_posembed(torch.empty(64, N, device=dev(), dtype=torch.bfloat16), x[:64], W, pos, period)
+
+
 # ------------------------------------------------------------------ GEMM
 GEMM_SHAPES = [(256, 256, 128), (384, 768, 768), (1024, 2304, 768), (512, 4096, 768), (300, 520, 264), (128, 128, 64),
                (2048, 768, 2048), (256, 1000, 512), (4096 + 136, 776, 392)]
