@@ -352,7 +352,17 @@ def test_fsdp_fused_world1_matches_unsharded():
 
 
 @needs2
-def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state():
+@pytest.mark.parametrize("name,env", [
+    ("sm_sharing_kernels", {}),
+    ("gather_inside_first_gemm", {"ENTROPY_FSDP_GATHER_GEMM": "1"}),
+    ("whole_sm_ctas_32_64", {"ENTROPY_FSDP_COMM_THREADS": "512", "ENTROPY_FSDP_GATHER_CTAS": "32", "ENTROPY_FSDP_RS_CTAS": "64",
+                             "ENTROPY_FSDP_GATHER_GEMM": "1"}),
+    ("whole_sm_ctas_64_64", {"ENTROPY_FSDP_COMM_THREADS": "512", "ENTROPY_FSDP_GATHER_CTAS": "64", "ENTROPY_FSDP_RS_CTAS": "64",
+                             "ENTROPY_FSDP_GATHER_GEMM": "1"}),
+])
+def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state(name, env):
+    """20 optimizer steps of the sharded engine on its NVLink kernels against the same schedule on library collectives,
+    for the kernels' SM-sharing form, the all-gather inside the first GEMM, and the older whole-SM CTA settings."""
     n = 2
     rc, out = _torchrun("""
         import os
@@ -373,23 +383,25 @@ def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state():
             g = GPT(cfg, 2, dev, sharded=True)
             f = FSDP(g, world, rank, comm=comm, hyper=dict(lr=1e-3, wd=0.1))
             g.init_weights(1234)
-            for _ in range(4): f.step(ids.to(dev), tgt.to(dev))
+            for _ in range(20): f.step(ids.to(dev), tgt.to(dev))
             torch.cuda.synchronize()
             res[comm] = f.full_master()
             res[comm + "_n"] = f.master.numel()
+            res[comm + "_loss"] = g.mean_loss()
         d = float((res["nccl"] - res["fused"]).abs().max())
         dm = float((res["nccl"] - res["fused"]).abs().mean())
-        if rank == 0: print("RESULT", d, res["fused_n"], g.np, native.get_error(), dm, flush=True)
+        if rank == 0: print("RESULT", d, res["fused_n"], g.np, native.get_error(), dm, res["nccl_loss"], res["fused_loss"], flush=True)
         dist.barrier(); torch.cuda.synchronize()
         import os; os._exit(0)
-    """, n)
+    """, n, env_extra=env)
     assert rc == 0, out[-3000:]
     line = [l for l in out.splitlines() if l.startswith("RESULT")][0].split()
+    assert abs(float(line[6]) - float(line[7])) < 5e-2, line      # same loss after 20 steps
     # The two schedules do not run bit-identical arithmetic (gather-fused 1-CTA GEMM vs CTA-pair GEMM, fused mean vs
     # reduce-scatter then scale).  AdamW turns a rounding-level difference in a near-zero gradient into +lr vs -lr, so the
     # bound on single elements is 2 * lr * steps; the mean over all elements shows whether the runs really agree.
-    assert float(line[1]) < 1.0e-2, line
-    assert float(line[5]) < 5e-5, line
+    assert float(line[1]) < 4.5e-2, line          # 2 * lr * 20 steps
+    assert float(line[5]) < 2.5e-4, line
     assert int(line[2]) < 0.6 * int(line[3]) and line[4] == "0", line
 
 

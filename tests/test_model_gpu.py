@@ -161,8 +161,10 @@ def test_fp8_native_forward_against_its_bf16_form_and_trains():
 
 
 def test_graph_step_equals_eager_step_from_the_first_step():
-    """The capture's warm-up run IS step 1 (no replay follows it): after 1 and after 4 steps the parameters of a
-    graph-replaying trainer equal those of an eager one bit for bit."""
+    """The capture's warm-up run IS step 1 (no replay follows it): after the first step the parameters of a
+    graph-replaying trainer equal those of an eager one bit for bit (an optimizer step applied twice would show here),
+    and after four steps they still agree up to what the embedding gradient's atomic adds allow (their order is not
+    fixed, and AdamW turns a last-bit change of a near-zero gradient into a step of the other sign)."""
     cfg, B = Config(V=512, C=256, L=2, H=4, I=512, T=128), 2
     ids, tgt = Stream(7).token_pairs(B * cfg.T, cfg.V)
     _native().lib().mlb_gemm_set_splits(1)      # one work item per weight-gradient tile: no order-dependent fp32 adds
@@ -181,7 +183,9 @@ def test_graph_step_equals_eager_step_from_the_first_step():
             tr.close()
     finally:
         _native().lib().mlb_gemm_set_splits(0)
-    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    assert torch.equal(res[0][0], res[1][0])
+    d = (res[0][1] - res[1][1]).abs()
+    assert d.max().item() < 2 * 1e-3 * 4 and d.mean().item() < 2e-5, (d.max().item(), d.mean().item())
 
 
 def test_overfit_gpu():
