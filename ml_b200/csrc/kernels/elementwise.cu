@@ -802,6 +802,14 @@ __global__ void fp8_qdq_k(bf16* __restrict__ out, const bf16* __restrict__ in, l
   const __nv_fp8_e4m3 q(__bfloat162float(in[i]) * scale);
   out[i] = __float2bfloat16(float(q) * inv_scale);
 }
+// out[0] = scale * sum(x[0..n)): one block, fixed summation order (deterministic); the per-row losses of a step.
+__global__ void __launch_bounds__(1024) sum_scale_k(float* __restrict__ out, const float* __restrict__ x, long n, float scale) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long i = threadIdx.x; i < n; i += blockDim.x) s += x[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[0] = s * scale;
+}
 __global__ void cast_b2f_k(float* __restrict__ out, const bf16* __restrict__ in, long n, float scale) {
   long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __bfloat162float(in[i]) * scale;
@@ -1024,6 +1032,13 @@ MLB_API int mlb_adamw(float* master, void* params, const float* grads, float* m,
                                                 grad_scale, dev_hyper, (uint8_t*)nullptr, 1.f);
   LAUNCH_RET;
 }
+// out[0] = scale * sum of n floats (the mean loss of a step, left on the device for one 4-byte read-back)
+MLB_API int mlb_sum_scale(float* out, const float* x, long n, float scale, cudaStream_t st) {
+  sum_scale_k<<<1, 1024, 0, st>>>(out, x, n, scale);
+  LAUNCH_RET;
+}
+// Zero-fill of a buffer (the gradient buffer at the start of backward: cudaMemsetAsync as in train/gpt.cu:600)
+MLB_API int mlb_zero(void* p, long nbytes, cudaStream_t st) { return (int)cudaMemsetAsync(p, 0, (size_t)nbytes, st); }
 MLB_API int mlb_cast_f2b(void* out, const float* in, long n, float scale, cudaStream_t st) {
   mlb_launch(cast_f2b_k, dim3(gs((n + 3) / 4, 256)), dim3(256), 0, st, (bf16*)out, in, n, scale);
   LAUNCH_RET;

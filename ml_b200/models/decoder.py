@@ -363,7 +363,7 @@ class GPT:
         BT = B * T
         sl = lambda t: t[:BT]
         if zero and self.grads is not None:
-            self.grads.zero_()
+            ops.zero_(self.grads)
         valid = valid_tokens if valid_tokens is not None else BT - B * n_pre
         dln, dresid, dresid1 = sl(self.dln), sl(self.dresid), sl(self.dresid1)
         skip_nb = "norm_bwd" in self.skip

@@ -98,7 +98,7 @@ class VisionTower:
         vc, VL = self.vc, self.layout
         vC, vI, C = vc.vC, vc.vI, self.C
         if zero:
-            self.grads.zero_()
+            ops.zero_(self.grads)
         ops.linear_dw(self.G(VL.o_proj, C, vC), self.dimg, self.fn_out)
         ops.linear_dx(self.dfn, self.dimg, self.P(VL.o_proj, C, vC))
         xlast = self.resid[vc.vL - 1] if vc.vL > 0 else self.patch_out

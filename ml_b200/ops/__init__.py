@@ -11,7 +11,7 @@ _NAMES = [
     "rope_fwd", "rope_bwd", "swiglu_fwd", "swiglu_bwd",
     "linear_fwd", "linear_dx", "linear_dw", "gemm", "attn_fwd", "attn_bwd",
     "attn_bidir_fwd", "attn_bidir_bwd", "layernorm_fwd", "layernorm_bwd",
-    "ce_fwd_bwd", "ce_chunk_stats", "ce_chunk_grad", "adamw", "patchify", "add_posembed", "posembed_grad", "residual_add", "cast", "fp8_qdq",
+    "ce_fwd_bwd", "ce_chunk_stats", "ce_chunk_grad", "adamw", "patchify", "add_posembed", "posembed_grad", "residual_add", "cast", "fp8_qdq", "sum_scale", "zero_",
 ]
 
 _native_mod = None

@@ -509,5 +509,23 @@ def fp8_qdq(out, x, scale=1.0):
     _chk(lib().mlb_fp8_qdq(_b(out), _b(x), x.numel(), scale, _st()), "fp8_qdq")
 
 
+def sum_scale(out, x, scale):
+    """out[0] = scale * sum(x) on the device (x fp32, contiguous)."""
+    fn = lib().mlb_sum_scale
+    fn.argtypes = [_vp, _vp, C.c_long, C.c_float, _vp]
+    fn.restype = _i32
+    _chk(fn(_f(out), _f(x), x.numel(), scale, _st()), "sum_scale")
+
+
+def zero_(x):
+    fn = lib().mlb_zero
+    fn.argtypes = [_vp, C.c_long, _vp]
+    fn.restype = _i32
+    assert x.is_cuda and x.is_contiguous()
+    _chk(fn(x.data_ptr(), x.numel() * x.element_size(), _st()), "zero")
+    global LAUNCHES
+    LAUNCHES -= 1          # a memset node, not a kernel of this library: not part of the launch count
+
+
 def scale_(x, s):
     _chk(lib().mlb_scale_f32(_f(x), x.numel(), s, _st()), "scale_f32")

@@ -331,3 +331,11 @@ def residual_add(out, a, b):
 
 def cast(out, x, scale=1.0):
     out.copy_(_f(x) * scale if scale != 1.0 else x)
+
+
+def sum_scale(out, x, scale):
+    out.copy_((x.double().sum() * scale).to(out.dtype).reshape(1))
+
+
+def zero_(x):
+    x.zero_()

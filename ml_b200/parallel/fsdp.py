@@ -107,6 +107,12 @@ class FSDP:
                 sh[:hi - lo].copy_(host_full[lo:hi].to(self.dev))
         if self.pshard.data_ptr() != self.master.data_ptr():
             ops.cast(self.pshard, self.master)
+        if self.fused is not None and self.world > 1:
+            # The NVLink all-gather PULLS the peers' shards with no collective in front of it: a rank that is done with its
+            # (seconds of host-side) initialisation would otherwise read shards its peers have not written yet and run
+            # its first step on partly empty weights.  Line the ranks up once the shards are in place.
+            torch.cuda.synchronize(self.dev)
+            dist.barrier(group=self.group)
 
     def full_master(self) -> torch.Tensor:
         """Gathers the full fp32 master buffer on every rank (tests, checkpoints of the unsharded layout)."""

@@ -71,10 +71,15 @@ class Trainer:
         self.graph = None
         # optimizer scalars of the current step, read by the AdamW kernels from device memory so that a captured
         # graph follows the step count: {lr, 1/bc1, 1/bc2, grad_scale}
-        self.h_hyper = torch.zeros(4, dtype=torch.float32, pin_memory=cuda)
+        # The host side is a small ring of pinned slots: the copy of step k is asynchronous, and the host may be several
+        # steps ahead of the device (a graph replay is one call), so the slot of step k must not be rewritten before its
+        # copy has run - each slot carries the event of its last copy and is waited for only when the ring wraps.
+        self._hyper_slots = 4
+        self.h_hyper = torch.zeros(self._hyper_slots, 8, dtype=torch.float32, pin_memory=cuda)   # [slot][decoder 4 | vision 4]
+        self._hyper_ev = [None] * self._hyper_slots
+        self._hyper_i = 0
         self.d_hyper = torch.zeros(4, dtype=torch.float32, device=self.device) if cuda else None
         self.ddp.dev_hyper = self.d_hyper
-        self.h_hyper_v = torch.zeros(4, dtype=torch.float32, pin_memory=cuda)
         self.d_hyper_v = torch.zeros(4, dtype=torch.float32, device=self.device) if cuda else None
 
     # ------------------------------------------------------------------ one optimizer step (device-resident inputs)
@@ -118,8 +123,7 @@ class Trainer:
         valid = self.B * self.n_text if self.vision is not None else BT
         if self._probe is not None:
             self._probe[1].record()
-        torch.sum(self.model.losses[:BT], dim=0, keepdim=True, out=self.d_loss)
-        self.d_loss.mul_(1.0 / valid)
+        ops.sum_scale(self.d_loss, self.model.losses[:BT], 1.0 / valid)
 
     def step(self):
         """Runs one optimizer step on the batch currently in self.ids / self.tgt."""
@@ -145,15 +149,23 @@ class Trainer:
         if self.d_hyper is None:
             return
         h = self.hyper
-        self.h_hyper[0] = h["lr"]
-        self.h_hyper[1] = 1.0 / (1.0 - h["b1"] ** self.t)
-        self.h_hyper[2] = 1.0 / (1.0 - h["b2"] ** self.t)
-        self.h_hyper[3] = self.ddp.adamw_grad_scale
-        self.d_hyper.copy_(self.h_hyper, non_blocking=True)
+        i = self._hyper_i
+        self._hyper_i = (i + 1) % self._hyper_slots
+        if self._hyper_ev[i] is not None:
+            self._hyper_ev[i].synchronize()       # the copy that last read this slot has run
+        slot = self.h_hyper[i]
+        slot[0] = h["lr"]
+        slot[1] = 1.0 / (1.0 - h["b1"] ** self.t)
+        slot[2] = 1.0 / (1.0 - h["b2"] ** self.t)
+        slot[3] = self.ddp.adamw_grad_scale
+        self.d_hyper.copy_(slot[:4], non_blocking=True)
         if self.vision is not None:
-            self.h_hyper_v.copy_(self.h_hyper)
-            self.h_hyper_v[3] = 1.0 / (self.world * self.accum)
-            self.d_hyper_v.copy_(self.h_hyper_v, non_blocking=True)
+            slot[4:8] = slot[:4]
+            slot[7] = 1.0 / (self.world * self.accum)
+            self.d_hyper_v.copy_(slot[4:8], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._hyper_ev[i] = ev
 
     def _capture(self):
         """Runs the current step eagerly on a side stream (that warms the allocator and the tensor-map caches, and it IS

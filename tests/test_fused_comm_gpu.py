@@ -381,7 +381,7 @@ def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state(name, env):
         res = {}
         for comm in ("nccl", "fused"):
             g = GPT(cfg, 2, dev, sharded=True)
-            f = FSDP(g, world, rank, comm=comm, hyper=dict(lr=1e-3, wd=0.1))
+            f = FSDP(g, world, rank, comm=comm, hyper=dict(lr=2e-4, wd=0.1))
             g.init_weights(1234)
             for _ in range(20): f.step(ids.to(dev), tgt.to(dev))
             torch.cuda.synchronize()
@@ -400,8 +400,10 @@ def test_fsdp_fused_two_gpus_matches_nccl_and_shards_state(name, env):
     # The two schedules do not run bit-identical arithmetic (gather-fused 1-CTA GEMM vs CTA-pair GEMM, fused mean vs
     # reduce-scatter then scale).  AdamW turns a rounding-level difference in a near-zero gradient into +lr vs -lr, so the
     # bound on single elements is 2 * lr * steps; the mean over all elements shows whether the runs really agree.
-    assert float(line[1]) < 4.5e-2, line          # 2 * lr * 20 steps
-    assert float(line[5]) < 2.5e-4, line
+    # (a learning rate of 2e-4 keeps the two trajectories from drifting apart chaotically over 20 steps of fitting one
+    # batch, which 1e-3 does: 0.1 - 0.3 in the loss; a unit that silently skipped its update would still show)
+    assert float(line[1]) < 9e-3, line            # 2 * lr * 20 steps
+    assert float(line[5]) < 2e-4, line
     assert int(line[2]) < 0.6 * int(line[3]) and line[4] == "0", line
 
 
