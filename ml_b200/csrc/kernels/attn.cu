@@ -442,8 +442,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
 
 // ================================================================== forward, head size 64: one thread per query row
 // A persistent CTA works on PAIRS of 128-query tiles of one (sample, head): tile 0 is owned by warps 0-3, tile 1 by
-// warps 4-7 (thread = one query row: no cross-thread reductions, no shared-memory exchange), warp 8 issues every MMA,
-// warp 9 every TMA load.  Per key block j and tile t:   S_t = Q_t K_j^T (TMEM) -> p = exp2(s*c - m) in 32-column chunks
+// warps 4-7 (thread = one query row: no cross-thread reductions, no shared-memory exchange), warp 8 issues tile 0's
+// MMAs, warp 10 tile 1's, warp 9 every TMA load.  Per key block j and tile t:   S_t = Q_t K_j^T (TMEM) -> p = exp2(s*c - m) in 32-column chunks
 // straight out of TMEM -> P_t written as packed bf16 into its own TMEM columns (the A operand of the next MMA never
 // touches shared memory, and the next block's scores can be issued before P_t V_j) -> O_t += P_t V_j.
 // Where O lives and what m is depends on the variant (template MODE):
@@ -455,12 +455,31 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_tc_kernel(const __gri
 //      threshold is passed (the default: one TMEM read of the scores per block instead of two).
 // The two tiles share K_j / V_j (one load per 256 queries) and run out of phase: while one tile's threads compute
 // exponentials the tensor core works for the other tile.  Both tiles walk the same key blocks; the block past tile
-// 0's diagonal is fully masked for it (its threads write P = 0 without computing anything).
+// 0's diagonal is fully masked for it (its threads compute nothing; modes 2 and 3 skip its P V).
 // A CTA's items come from a balanced schedule built on the host (attn_schedule), the finished O rows leave through a
 // swizzled staging tile and one TMA store per warp.
-// mbarriers per tile: bar_s S complete (commit) | bar_p P stored (4 warps) | bar_o P V complete (commit) |
-// bar_of O_blk folded (4 warps, mode 1 only).  K has 3 slots, V 4: block g+3 is fetched as soon as both tiles have
-// consumed S(g), which (in-order tensor pipe) also means P V of block g-1 has finished.
+// mbarriers per tile: bar_s S complete (commit) | bar_sc S read out of TMEM (4 warps; in mode 3 half way through the
+// block, so that the next block's Q K^T is issued under the rest of the exponentials) | bar_p P stored (4 warps) |
+// bar_o P V complete (commit) | bar_of O_blk folded (4 warps, mode 1 only).  K has 3 slots, V 4, Q 2 buffers: each is a
+// ring with a "full" barrier (TMA bytes) and a "released" barrier on which the 8 softmax warps arrive when they have
+// seen the MMAs that read the slot complete (Q K^T for K and Q, P V for V).
+// What the cycle stamps showed about the issuing threads: every tcgen05.mma and every tcgen05.commit costs its thread
+// ~75 cycles whatever the product's size, so 12 MMAs and 2 commits per key block and tile are ~1000 cycles of one
+// thread; with a single thread for both tiles that chain (3200 cycles per key block, never waiting) was the kernel's
+// pace.
+// The one-pass variant writes P as the upper halves of the fp32 exponentials (one byte-permute per pair instead of a
+// rounding conversion; equal speed when measured, kept for its single instruction).  Cutting off 16 mantissa bits loses
+// 2^-8 / mantissa of the value, 0.28 % on average over mantissas; the exponentials are therefore taken of
+// z + log2(1.0028), which centres the error of P, and the row sum (of the same, unrounded values) is divided by 1.0028
+// once per row.  Error of O against an fp32 reference: 2.1e-3 relative Frobenius (a bf16 rounding of the reference
+// itself: 1.6e-3), mean signed error below 1e-5.
+constexpr float P_BIAS_LOG2 = 0.0040339f;     // log2(1.0028)
+constexpr float P_BIAS_INV = 0.99720782f;     // 1 / 1.0028
+__device__ __forceinline__ uint32_t pack_hi16(float lo, float hi) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+  return r;
+}
 struct Fwd2Smem {
   static constexpr int Q = 0;                          // 2 buffers x 2 tiles
   static constexpr int KN = 3;                         // K slots; V has one more
@@ -471,7 +490,7 @@ struct Fwd2Smem {
   static constexpr int SCHED = BAR + 256;                 // this CTA's first 64 work items
   static constexpr int TOTAL = SCHED + 256 + 1024;
 };
-constexpr int FWD2_THREADS = 10 * 32;   // 8 softmax warps, MMA warp, loader warp
+constexpr int FWD2_THREADS = 11 * 32;   // 8 softmax warps, MMA warp of tile 0, loader warp, MMA warp of tile 1
 
 struct Fwd2Step {   // one key block of one item in this CTA's flattened sequence
   int w, li, p, b, h, nkb, j;
@@ -495,9 +514,10 @@ struct Fwd2Step {   // one key block of one item in this CTA's flattened sequenc
 };
 
 // MODE 1: O folded into registers every block | 2: O in TMEM, lazy rescale, two passes | 3: the same in one pass.
-// (Measured without gain on top of mode 3 and taken out again: the next chunk's TMEM load in flight during the current
-// chunk's arithmetic; 4, 6 or 8 of every 16 exponential pairs as a cubic on the FMA pipe instead of the special-function
-// unit - equal, 5 % and 10 % slower.)
+// (Measured without gain on top of mode 3 and taken out again: 4, 6 or 8 of every 16 exponential pairs as a cubic on the
+// FMA pipe instead of the special-function unit - equal, 3 % and 5 % slower although the pure exponential chunks got
+// shorter; fp16 exponentials two at a time; tile 1 started half a block behind tile 0; the MMA and loader threads
+// sleeping between barrier probes.)
 template <int MODE>
 __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tm_out,
                                                                            const AttnArgs a) {
@@ -512,8 +532,12 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
   constexpr int KN = S::KN, VN = S::KN + 1;
   uint64_t *bar_q = bars /*[2]*/, *bar_s = bars + 2 /*[2]*/, *bar_p = bars + 4 /*[2]*/, *bar_o = bars + 6 /*[2]*/, *bar_of = bars + 8 /*[2]*/,
            *bar_k = bars + 10 /*[KN]*/, *bar_v = bars + 10 + KN /*[VN]*/;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 10 + KN + VN);
-  volatile int* s_abort = (volatile int*)(bars + 11 + KN + VN);
+  // slot released: both tiles' MMAs that read it have completed (one arrival per softmax warp, which saw them complete)
+  uint64_t *bar_kf = bars + 10 + KN + VN /*[KN]*/, *bar_vf = bar_kf + KN /*[VN]*/, *bar_qf = bar_vf + VN /*[2]*/;
+  uint64_t* bar_sc = bar_qf + 2 /*[2]*/;     // S_t read out by its four softmax warps
+  uint32_t* tmem_slot = (uint32_t*)(bar_sc + 2);
+  volatile int* s_abort = (volatile int*)(bar_sc + 3);
+  static_assert((10 + 2 * (KN + VN) + 2 + 2 + 2) * 8 <= 256, "barrier area");
   {
     __shared__ int s_skip;
     if (threadIdx.x == 0) s_skip = *(volatile int*)&g_mlb_error;
@@ -540,8 +564,9 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
       tc::mbar_init(&bar_q[i], 1); tc::mbar_init(&bar_s[i], 1); tc::mbar_init(&bar_o[i], 1);
       tc::mbar_init(&bar_p[i], 4); tc::mbar_init(&bar_of[i], 4);
     }
-    for (int i = 0; i < KN; i++) tc::mbar_init(&bar_k[i], 1);
-    for (int i = 0; i < VN; i++) tc::mbar_init(&bar_v[i], 1);
+    for (int i = 0; i < KN; i++) { tc::mbar_init(&bar_k[i], 1); tc::mbar_init(&bar_kf[i], 8); }
+    for (int i = 0; i < VN; i++) { tc::mbar_init(&bar_v[i], 1); tc::mbar_init(&bar_vf[i], 8); }
+    for (int i = 0; i < 2; i++) { tc::mbar_init(&bar_qf[i], 8); tc::mbar_init(&bar_sc[i], 4); }
     *s_abort = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tm);
@@ -553,6 +578,7 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;     // S0 @0, S1 @128, P0 @256, P1 @320 (bf16 pairs), O0 @384, O1 @448
   auto wait = [&](uint64_t* bar, uint32_t phase, int where) -> bool {
+    if (tc::mbar_try(bar, phase)) return true;      // the common case costs one probe
     if (*s_abort) return false;
     if (!tc::mbar_wait(bar, phase, where)) { *s_abort = 1; return false; }
     return true;
@@ -567,11 +593,16 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
         for (int t = 0; t < 2; t++)
           tc::tma_load_2d(smem + S::Q + (qb * 2 + t) * TILE_BYTES, &tm, &bar_q[qb], s.h * HD, s.b * a.T + (2 * s.p + t) * 128);
       };
-      auto load_kv = [&](const Fwd2Step& s, int g) {
-        tc::mbar_expect_tx(&bar_k[g % KN], TILE_BYTES);
-        tc::tma_load_2d(smem + S::K + (g % KN) * TILE_BYTES, &tm, &bar_k[g % KN], C + s.h * HD, s.b * a.T + s.j * 128);
-        tc::mbar_expect_tx(&bar_v[g % VN], TILE_BYTES);
-        tc::tma_load_2d(smem + S::V + (g % VN) * TILE_BYTES, &tm, &bar_v[g % VN], 2 * C + s.h * HD, s.b * a.T + s.j * 128);
+      // Block n goes into K slot n % KN and V slot n % VN once the previous tenant's readers are done.  Every slot is a
+      // ring of its own (full barrier / released barrier), so no wait here can be overtaken by two phases however far
+      // one tile runs ahead of the other.
+      auto load_kv = [&](const Fwd2Step& s, int n) {
+        if (n >= KN) wait(&bar_kf[n % KN], (n / KN + 1) & 1, 70);
+        tc::mbar_expect_tx(&bar_k[n % KN], TILE_BYTES);
+        tc::tma_load_2d(smem + S::K + (n % KN) * TILE_BYTES, &tm, &bar_k[n % KN], C + s.h * HD, s.b * a.T + s.j * 128);
+        if (n >= VN) wait(&bar_vf[n % VN], (n / VN + 1) & 1, 71);
+        tc::mbar_expect_tx(&bar_v[n % VN], TILE_BYTES);
+        tc::tma_load_2d(smem + S::V + (n % VN) * TILE_BYTES, &tm, &bar_v[n % VN], 2 * C + s.h * HD, s.b * a.T + s.j * 128);
       };
       Fwd2Step c0, c3;      // steps g and g + KN
       c0.set_item(item_at(0), 0, total, npair, nq, BH, a.H);
@@ -587,45 +618,49 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
         }
       }
       for (int g = 0; c0.valid; g++) {
-        // both tiles have consumed S(g): K slot g % KN is free; they folded O_blk(g-1) before storing P(g): V slot
-        // (g-1) % VN is free.  Block g + KN goes into both.
-        wait(&bar_p[0], g & 1, 70);
-        wait(&bar_p[1], g & 1, 71);
         if (c3.valid) load_kv(c3, g + KN);
         if (c0.j == c0.nkb - 1) {
-          // this item's last scores have been consumed: its Q buffer takes the item after next
+          // once this item's MMAs are done its Q buffer takes the item after next
           Fwd2Step nx;
           nx.set_item(item_at(c0.li + 2), c0.li + 2, total, npair, nq, BH, a.H);
-          if (nx.valid) load_q(nx);
+          if (nx.valid) {
+            wait(&bar_qf[c0.li & 1], (c0.li >> 1) & 1, 72);
+            load_q(nx);
+          }
         }
         c0.advance(item_at, total, npair, nq, BH, a.H);
         c3.advance(item_at, total, npair, nq, BH, a.H);
       }
     }
-  } else if (warp == 8) {
-    // ---------------------------------------------------------------- MMA warp: waits, tcgen05.mma, commits, nothing else
-    // (the MMAs here are short, 50-65 cycles each: every instruction this thread spends between two of them shows)
+  } else if (warp == 8 || warp == 10) {
+    // ---------------------------------------------------------------- MMA warps: one issuing thread per tile (warp 8: tile
+    // 0, warp 10: tile 1).  A single thread for both tiles was the kernel's pace: its serial chain of waits, descriptor
+    // arithmetic and issues took ~3200 cycles per key block, all of it busy.  Slot and phase counters are kept
+    // incrementally (no division on this thread).
     if (lane == 0) {
+      const int t = warp == 8 ? 0 : 1;
       constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_o = tc::idesc_bf16(128, HD, 0, 1);     // A = P (TMEM, K-major), B = V (MN-major)
-      const uint64_t dq0 = desc_base_k(tc::smem_u32(smem + S::Q)), dk0 = desc_base_k(tc::smem_u32(smem + S::K));
-      const uint64_t dv0 = desc_base_mn(tc::smem_u32(smem + S::V));
       constexpr uint64_t TILE_D = TILE_BYTES >> 4;     // one tile further, in descriptor address units
+      const uint64_t dq0 = desc_base_k(tc::smem_u32(smem + S::Q)) + (uint64_t)t * TILE_D, dk0 = desc_base_k(tc::smem_u32(smem + S::K));
+      const uint64_t dv0 = desc_base_mn(tc::smem_u32(smem + S::V));
+      const uint32_t d_s = tmem + t * 128, d_p = tmem + 256 + t * 64, d_o = tmem + 384 + t * HD;
       int li = 0, j = 0, w = item_at(0), w_next = item_at(1);   // the next item's index is fetched an item ahead
       auto item_nkb = [&](int w_) { return min(2 * (npair - 1 - w_ / BH) + 2, nq); };
       bool valid = w >= 0;
       int nkb = valid ? item_nkb(w) : 0;
+      int qt_t = valid ? 2 * (npair - 1 - w / BH) + t : 0;      // this tile's diagonal block in the current item
       if (valid) {
         const bool ok0 = wait(&bar_q[0], 0, 60) && wait(&bar_k[0], 0, 61);
-        for (int t = 0; t < 2; t++) {
-          if (ok0) {
-            tc::tc_fence_after();
+        if (ok0) {
+          tc::tc_fence_after();
 #pragma unroll
-            for (int ks = 0; ks < 4; ks++) tc::mma_bf16_ss(tmem + t * 128, dq0 + t * TILE_D + ks * 2, dk0 + ks * 2, idesc_s, ks > 0);
-          }
-          tc::mma_commit(&bar_s[t]);
+          for (int ks = 0; ks < 4; ks++) tc::mma_bf16_ss(d_s, dq0 + ks * 2, dk0 + ks * 2, idesc_s, ks > 0);
         }
+        tc::mma_commit(&bar_s[t]);
       }
+      int k1 = 1 % KN, k1p = 0;     // slot and phase parity of key block g + 1
+      int vs = 0, vp = 0;           // of value block g
       for (int g = 0; valid; g++) {
         // next step: same item, or the first block of this CTA's next item
         int nli = li, nj = j + 1, nw = w;
@@ -633,36 +668,38 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
         const bool has_next = nw >= 0;
         bool next_ok = has_next;
         if (has_next) {
-          next_ok = wait(&bar_k[(g + 1) % KN], ((g + 1) / KN) & 1, 62);
+          next_ok = wait(&bar_k[k1], k1p, 62);
           if (next_ok && nj == 0) next_ok = wait(&bar_q[nli & 1], (nli >> 1) & 1, 63);
         }
-        const bool v_ok = wait(&bar_v[g % VN], (g / VN) & 1, 64);
-        const uint64_t dqn = dq0 + (uint64_t)((nli & 1) * 2) * TILE_D, dkn = dk0 + (uint64_t)((g + 1) % KN) * TILE_D;
-        const uint64_t dvg = dv0 + (uint64_t)(g % VN) * TILE_D;
-        for (int t = 0; t < 2; t++) {
-          bool go = wait(&bar_p[t], g & 1, 65);        // P_t(g) is in TMEM and S_t(g) has been read out
-          if (has_next) {                              // the next scores first: the tile's threads wait for nothing else
-            if (go && next_ok) {
-              tc::tc_fence_after();
-#pragma unroll
-              for (int ks = 0; ks < 4; ks++) tc::mma_bf16_ss(tmem + t * 128, dqn + t * TILE_D + ks * 2, dkn + ks * 2, idesc_s, ks > 0);
-            }
-            tc::mma_commit(&bar_s[t]);
-          }
-          if constexpr (!LAZY) {
-            if (go && g > 0) go = wait(&bar_of[t], (g - 1) & 1, 66);   // O_blk_t(g-1) has been folded
-          }
-          if (go && v_ok) {
+        const uint64_t dqn = dq0 + (uint64_t)((nli & 1) * 2) * TILE_D, dkn = dk0 + (uint64_t)k1 * TILE_D;
+        const uint64_t dvg = dv0 + (uint64_t)vs * TILE_D;
+        if (has_next) {                              // the next scores as soon as S_t(g) has been read out
+          const bool sc_ok = wait(&bar_sc[t], g & 1, 73);
+          if (sc_ok && next_ok) {
             tc::tc_fence_after();
-            // LAZY: O accumulates in TMEM over the item's key blocks (the softmax warps rescale it in place when needed)
-            const bool acc0 = LAZY && j > 0;
 #pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(tmem + 384 + t * HD, tmem + 256 + t * 64 + ks * 8, dvg + ks * 128, idesc_o, ks > 0 || acc0);
+            for (int ks = 0; ks < 4; ks++) tc::mma_bf16_ss(d_s, dqn + ks * 2, dkn + ks * 2, idesc_s, ks > 0);
           }
-          tc::mma_commit(&bar_o[t]);
+          tc::mma_commit(&bar_s[t]);
         }
-        if (nj == 0 && has_next) { nkb = item_nkb(nw); w_next = item_at(nli + 1); }
+        const bool v_ok = wait(&bar_v[vs], vp, 64);
+        bool go = wait(&bar_p[t], g & 1, 65);        // P_t(g) is in TMEM
+        if constexpr (!LAZY) {
+          if (go && g > 0) go = wait(&bar_of[t], (g - 1) & 1, 66);   // O_blk_t(g-1) has been folded
+        }
+        // LAZY: a block past the tile's diagonal (tile 0's last one) adds nothing to the accumulated O and is not multiplied
+        if (go && v_ok && !(LAZY && j > qt_t)) {
+          tc::tc_fence_after();
+          // LAZY: O accumulates in TMEM over the item's key blocks (the softmax warps rescale it in place when needed)
+          const bool acc0 = LAZY && j > 0;
+#pragma unroll
+          for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(d_o, d_p + ks * 8, dvg + ks * 128, idesc_o, ks > 0 || acc0);
+        }
+        tc::mma_commit(&bar_o[t]);
+        if (nj == 0 && has_next) { nkb = item_nkb(nw); qt_t = 2 * (npair - 1 - nw / BH) + t; w_next = item_at(nli + 1); }
         li = nli; j = nj; w = nw; valid = has_next;
+        if (++k1 == KN) { k1 = 0; k1p ^= 1; }
+        if (++vs == VN) { vs = 0; vp ^= 1; }
       }
     }
   } else {
@@ -714,6 +751,14 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
           tc::tmem_st16(t_o + c * 32 + 16, w1);
         }
       };
+      // The slots' release barriers are arrived on from here (one lane per warp, 8 warps) rather than by tcgen05.commit:
+      // every tcgen05 instruction costs its issuing thread ~75 cycles, and that thread's chain sets the block time.
+      auto s_seen = [&](int j) {          // Q K^T of block g has completed: its K slot, and after an item's last block Q
+        if (lane == 0) {
+          tc::mbar_arrive(&bar_kf[g % KN]);
+          if (j == it.nkb - 1) tc::mbar_arrive(&bar_qf[it.li & 1]);
+        }
+      };
       for (int j = 0; j < it.nkb; j++, g++) {
         if constexpr (MODE == 3) {
           // One pass per key block: exponentials against the reference maximum of an earlier block while the row
@@ -723,6 +768,7 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
           if (tl && g < 16) tl[g * 8 + 0] = clock64();
           wait(&bar_s[t], g & 1, 67);
           tc::tc_fence_after();
+          s_seen(j);
           if (tl && g < 16) tl[g * 8 + 1] = clock64();
           const bool diag = (j == qt);
           const int kc0 = j * 128;
@@ -731,39 +777,39 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
             if (!p_free) {
               wait(&bar_o[t], (g - 1) & 1, 68);
               tc::tc_fence_after();
+              if (lane == 0) tc::mbar_arrive(&bar_vf[(g - 1) % VN]);     // P V of block g-1 is done with its V slot
               p_free = true;
             }
           };
-          if (j > qt) {                  // past the diagonal: every key of this block is masked for every row of the tile
+          auto release_s = [&]() {       // this warp's rows of S(g) have been read out of TMEM (or are not needed)
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&bar_sc[t]);
+          };
+          if (j > qt) {                  // past the diagonal: every key of this block is masked for every row of the tile;
+            release_s();                 // the MMA thread skips its P V
             free_p();
-            uint32_t z[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) z[i] = 0u;
-#pragma unroll
-            for (int c = 0; c < 4; c++) tc::tmem_st16(t_p + c * 16, z);
           } else {
             bool exact = (j == 0);
-            auto for_chunks = [&](auto&& fn) {   // fn(c, r): chunk c of this row's 128 scores in r[32]
+            auto mask = [&](int c, uint32_t (&r)[32]) {
+              if (diag) {
 #pragma unroll
-              for (int c = 0; c < 4; c++) {
-                uint32_t r[32];
-                tc::tmem_ld32(t_s + c * 32, r);
-                tc::tmem_ld_wait();
-                fn(c, r);
+                for (int i = 0; i < 32; i++)
+                  if (kc0 + c * 32 + i > qrow) r[i] = 0xff800000u;     // exp2(-inf) = 0
               }
             };
             for (int attempt = 0; attempt < 2; attempt++) {
               if (exact) {
                 float mx = -INFINITY;
-                for_chunks([&](int c, uint32_t (&r)[32]) {
-                  if (diag) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                      if (kc0 + c * 32 + i > qrow) r[i] = 0xff800000u;
-                  }
+                for (int c = 0; c < 4; c++) {
+                  uint32_t r[32];
+                  tc::tmem_ld32(t_s + c * 32, r);
+                  tc::tmem_ld_wait();
+                  mask(c, r);
 #pragma unroll
                   for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                });
+                }
                 const float m_new = fmaxf(m, mx * sl2);   // finite: key 0 is visible to every query
                 if (j > 0) {
                   const float alpha = ex2_approx(m - m_new);
@@ -773,33 +819,61 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
                 }
                 m = m_new;
               }
-              const uint64_t nm2 = pk2(-m, -m);
+              const uint64_t nm2 = pk2(P_BIAS_LOG2 - m, P_BIAS_LOG2 - m);
               uint64_t rs2 = pk2(0.f, 0.f);
               float mx = -INFINITY;
-              for_chunks([&](int c, uint32_t (&r)[32]) {
-                uint32_t pw[16];
-                if (diag) {
-#pragma unroll
-                  for (int i = 0; i < 32; i++)
-                    if (kc0 + c * 32 + i > qrow) r[i] = 0xff800000u;     // exp2(-inf) = 0
-                }
+              // exponentials of one 32-column chunk held in registers; track: the row maximum is followed next to them
+              auto exps = [&](uint32_t (&r)[32], uint32_t (&pw)[16], auto track) {
 #pragma unroll
                 for (int x = 0; x < 16; x++) {
                   float z0, z1;
-                  mx = max3(mx, __uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
+                  if constexpr (decltype(track)::value) mx = max3(mx, __uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1]));
                   upk2(fma2(pk2(__uint_as_float(r[2 * x]), __uint_as_float(r[2 * x + 1])), sl2x2, nm2), z0, z1);
                   const float p0 = ex2_approx(z0), p1 = ex2_approx(z1);
                   rs2 = add2(rs2, pk2(p0, p1));
-                  pw[x] = pack_bf16(p0, p1);
+                  pw[x] = pack_hi16(p0, p1);
                 }
-                if (c == 0) free_p();
-                tc::tmem_st16(t_p + c * 16, pw);
-                if (tl && g < 16) tl[g * 8 + 2 + c] = clock64();     // mode 3: stamps 2..5 = chunks done
-              });
-              if (!exact && __any_sync(0xffffffffu, mx * sl2 - m > 8.f)) {
-                exact = true;           // this attempt's P is overwritten and its row sum dropped
-                continue;
+              };
+              // The scores leave TMEM ahead of the arithmetic: chunks 2 and 3 are in registers when chunks 0 and 1 are
+              // done, and S is handed back to the MMA thread there - the next block's Q K^T runs under the second half
+              // of this block's exponentials instead of after them.
+              uint32_t ra[32], rb[32], pw0[16], pw1[16];
+              tc::tmem_ld32(t_s, ra);
+              tc::tmem_ld_wait();
+              mask(0, ra);
+              tc::tmem_ld32(t_s + 32, rb);
+              exps(ra, pw0, std::true_type{});
+              if (tl && g < 16) tl[g * 8 + 2] = clock64();     // mode 3: stamps 2..5 = chunks done
+              tc::tmem_ld_wait();
+              mask(1, rb);
+              tc::tmem_ld32(t_s + 64, ra);
+              free_p();
+              tc::tmem_st16(t_p, pw0);
+              exps(rb, pw1, std::true_type{});
+              tc::tmem_st16(t_p + 16, pw1);
+              if (tl && g < 16) tl[g * 8 + 3] = clock64();
+              tc::tmem_ld32(t_s + 96, rb);
+              tc::tmem_ld_wait();
+              mask(2, ra);
+              mask(3, rb);
+              if (!exact) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  mx = max3(mx, __uint_as_float(ra[i]), __uint_as_float(ra[i + 1]));
+                  mx = max3(mx, __uint_as_float(rb[i]), __uint_as_float(rb[i + 1]));
+                }
+                if (__any_sync(0xffffffffu, mx * sl2 - m > 8.f)) {
+                  exact = true;           // S has not been handed back: this attempt's P is overwritten, its row sum dropped
+                  continue;
+                }
               }
+              release_s();
+              exps(ra, pw0, std::false_type{});
+              tc::tmem_st16(t_p + 32, pw0);
+              if (tl && g < 16) tl[g * 8 + 4] = clock64();
+              exps(rb, pw1, std::false_type{});
+              tc::tmem_st16(t_p + 48, pw1);
+              if (tl && g < 16) tl[g * 8 + 5] = clock64();
               float rs_lo, rs_hi;
               upk2(rs2, rs_lo, rs_hi);
               l += rs_lo + rs_hi;
@@ -816,6 +890,7 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
         if (tl && g < 16) tl[g * 8 + 0] = clock64();
         wait(&bar_s[t], g & 1, 67);
         tc::tc_fence_after();
+        s_seen(j);
         if (tl && g < 16) tl[g * 8 + 1] = clock64();
         float alpha = 1.f;
         bool resc = false;
@@ -861,6 +936,7 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
         if (j > 0) {   // the previous block's P V has had the whole row-maximum pass to complete; P's columns are free after it
           wait(&bar_o[t], (g - 1) & 1, 68);
           tc::tc_fence_after();
+          if (lane == 0) tc::mbar_arrive(&bar_vf[(g - 1) % VN]);
           if (tl && g < 16) tl[g * 8 + 5] = clock64();
           if constexpr (LAZY) {
             if (resc) rescale(alpha);
@@ -907,13 +983,15 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
         tc::tmem_st_wait();
         tc::tc_fence_before();
         __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&bar_p[t]);
+        if (lane == 0) { tc::mbar_arrive(&bar_sc[t]); tc::mbar_arrive(&bar_p[t]); }
         if (tl && g < 16) tl[g * 8 + 4] = clock64();
         alpha_prev = alpha;
       }
       wait(&bar_o[t], (g - 1) & 1, 69);
       tc::tc_fence_after();
+      if (lane == 0) tc::mbar_arrive(&bar_vf[(g - 1) % VN]);
       fold(alpha_prev);
+      if constexpr (MODE == 3) l *= P_BIAS_INV;
       const float inv = 1.f / l;
       const bool store = !*s_abort && qrow < a.T;
       bf16* dst = a.out + ((size_t)(it.b * a.T + qrow)) * C + it.h * HD;
@@ -927,7 +1005,7 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
           if (lane == 0) tc::tma_wait_group_read<0>();      // the previous item's rows have been read out of the staging tile
           __syncwarp();
         }
-#pragma unroll
+  #pragma unroll
         for (int c = 0; c < 2; c++) {
           uint32_t r[32];
           tc::tmem_ld32(t_o + c * 32, r);
@@ -943,7 +1021,7 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
             else if (store) *reinterpret_cast<uint4*>(dst + c * 32 + v8 * 8) = pk;
           }
         }
-        if (a.out_tma) {
+          if (a.out_tma) {
           tc::fence_async_smem();
           __syncwarp();
           if (lane == 0 && !*s_abort && qt * 128 < a.T) {   // (an odd number of query tiles leaves the last pair's second tile empty)

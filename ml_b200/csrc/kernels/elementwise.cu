@@ -21,6 +21,12 @@ __device__ __forceinline__ void load8(const bf16* p, float (&f)[8]) {
 #pragma unroll
   for (int i = 0; i < 4; i++) { float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
 }
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {     // 8 bf16 held packed in four registers
+  f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+  f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+  f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+  f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
 __device__ __forceinline__ void store8(bf16* p, const float (&f)[8]) {
   uint4 u;
   u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
@@ -237,17 +243,24 @@ __global__ void __launch_bounds__(256, (VPL <= 3) ? 2 : 1) rmsnorm_bwd_k(bf16* _
     }
     for (long row = (long)blockIdx.x * nwarp + warp; row < rows; row += (long)gridDim.x * nwarp) {
       const float r = rstd[row];
-      float xv[NC][8], dv[NC][8];
+      // The row's x, dy and residual-stream gradient stay in registers PACKED (four registers per eight values) between
+      // the two passes, and every load of the row is issued before the row's reduction: `add` does not depend on it, and
+      // fetching it only afterwards cost a second DRAM round trip per row.
+      uint4 xr[NC], dr[NC], ar[NC];
       float dot = 0.f;
 #pragma unroll
       for (int v = 0; v < NV; v++) {
         const long off = row * C + (v * 32 + lane) * 8;
         const int cv = CACHE ? v : 0, cw = CACHE_W ? v : 0;
-        load8(x + off, xv[cv]);
-        load8(dy + off, dv[cv]);
+        xr[cv] = *reinterpret_cast<const uint4*>(x + off);
+        dr[cv] = *reinterpret_cast<const uint4*>(dy + off);
+        if (CACHE) ar[cv] = add ? *reinterpret_cast<const uint4*>(add + off) : make_uint4(0, 0, 0, 0);
         if (!CACHE_W) load8(w + (v * 32 + lane) * 8, ww[0]);
+        float xf[8], df[8];
+        unpack8(xr[cv], xf);
+        unpack8(dr[cv], df);
 #pragma unroll
-        for (int j = 0; j < 8; j++) dot += dv[cv][j] * ww[cw][j] * xv[cv][j];
+        for (int j = 0; j < 8; j++) dot += df[j] * ww[cw][j] * xf[j];
       }
       dot = warp_sum(dot);
       const float k = r * r * r * invC * dot;
@@ -255,18 +268,20 @@ __global__ void __launch_bounds__(256, (VPL <= 3) ? 2 : 1) rmsnorm_bwd_k(bf16* _
       for (int v = 0; v < NV; v++) {
         const long off = row * C + (v * 32 + lane) * 8;
         const int cv = CACHE ? v : 0, cw = CACHE_W ? v : 0;
-        if (!CACHE) { load8(x + off, xv[0]); load8(dy + off, dv[0]); }
-        if (!CACHE_W) load8(w + (v * 32 + lane) * 8, ww[0]);
-        float o[8];
-        if (add) load8(add + off, o);
-        else {
-#pragma unroll
-          for (int j = 0; j < 8; j++) o[j] = 0.f;
+        if (!CACHE) {
+          xr[0] = *reinterpret_cast<const uint4*>(x + off);
+          dr[0] = *reinterpret_cast<const uint4*>(dy + off);
+          ar[0] = add ? *reinterpret_cast<const uint4*>(add + off) : make_uint4(0, 0, 0, 0);
         }
+        if (!CACHE_W) load8(w + (v * 32 + lane) * 8, ww[0]);
+        float xf[8], df[8], o[8];
+        unpack8(xr[cv], xf);
+        unpack8(dr[cv], df);
+        unpack8(ar[cv], o);
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-          o[j] += dv[cv][j] * ww[cw][j] * r - xv[cv][j] * k;
-          acc[v][j] += dv[cv][j] * xv[cv][j] * r;
+          o[j] += df[j] * ww[cw][j] * r - xf[j] * k;
+          acc[v][j] += df[j] * xf[j] * r;
         }
         store8(dx + off, o);
       }
