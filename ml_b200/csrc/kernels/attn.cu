@@ -1325,9 +1325,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kv_tc_kernel(const __
 //     partial buffer, written with plain stores right after block j+1's operands are handed over, and a second
 //     kernel adds the partials of a query row in fp32 in key-tile order (deterministic), applies the scale and RoPE's
 //     backward rotation and writes bf16 dQ.
-// Warps: 8 element-wise (TMEM lane group x 64-query half), 4 drain (dQ partial tiles, dK / dV epilogue), 1 MMA issuer, 1 loader.
+// Warps: 8 element-wise (TMEM lane group x 64-query half), 4 drain (dQ partial tiles, dK / dV epilogue), 2 MMA issuers (scores / gradients), 1 loader.
 // mbarriers: bar_s scores complete (commit) | bar_free S^T/dP^T read out (8 warps) | bar_p P^T/dS^T stored (8 warps) |
-// bar_d dV/dK/dQ MMAs complete (commit) | bar_dqf dQ read out (4 warps) | bar_epi dK/dV of a key tile read out (4 warps).
+// bar_dv dV MMAs complete (commit: P^T may be overwritten) | bar_d[2] dV/dK/dQ MMAs complete (commit, alternating so
+// that a waiter two blocks behind cannot mistake a phase) | bar_dqf dQ read out (4 warps) | bar_epi dK/dV of a key tile read out (4 warps).
 struct BwdFusedSmem {
   static constexpr int K = 0;
   static constexpr int V = K + TILE_BYTES;
@@ -1343,9 +1344,10 @@ struct BwdFusedSmem {
 
 constexpr int BWDF_E_WARPS = 8;       // element-wise warps: TMEM lane group (w & 3) x 64-query column half (w >> 2)
 constexpr int BWDF_D_WARPS = 4;       // drain warps: dQ partial tiles and the dK / dV epilogue, one TMEM lane group each
-// Warp w runs on scheduler w % 4.  Warps 12 and 13 stay idle so that the MMA warp (14) and the loader warp (15) land on
-// schedulers 2 and 3: every scheduler then carries two element-wise warps, one drain warp and one light warp.
-constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS + 2;   // issues every MMA
+// Warp w runs on scheduler w % 4.  Warp 12 stays idle so that the two MMA warps (13, 14) and the loader warp (15) land on
+// schedulers 1, 2 and 3: every scheduler then carries two element-wise warps, one drain warp and at most one light warp.
+constexpr int BWDF_SCORE_WARP = BWDF_E_WARPS + BWDF_D_WARPS + 1;  // issues S^T / dP^T (scheduler 1)
+constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS + 2;   // issues dV / dK / dQ (scheduler 2)
 constexpr int BWDF_LOAD_WARP = BWDF_CTRL_WARP + 1;                // issues every TMA load
 constexpr int BWDF_THREADS = (BWDF_LOAD_WARP + 1) * 32;
 
@@ -1359,8 +1361,8 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + S::BAR);
-  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[3]*/, *bar_s = bars + 4, *bar_free = bars + 5, *bar_p = bars + 6, *bar_d = bars + 7,
-           *bar_dqf = bars + 8, *bar_epi = bars + 9;
+  uint64_t *bar_kv = bars, *bar_q = bars + 1 /*[3]*/, *bar_s = bars + 4, *bar_free = bars + 5, *bar_p = bars + 6, *bar_dv = bars + 7,
+           *bar_dqf = bars + 8, *bar_epi = bars + 9, *bar_d = bars + 12 /*[2]: block blk completes bar_d[blk & 1]*/;
   uint32_t* tmem_slot = (uint32_t*)(bars + 10);
   volatile int* s_abort = (volatile int*)(bars + 11);
   float* s_stat = (float*)(smem + S::STAT);   // [8 warps][-lse*log2e x64 | -delta x64]
@@ -1399,7 +1401,7 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
   if (tid == 0) {
     tc::mbar_init(bar_kv, 1);
     for (int i = 0; i < 3; i++) tc::mbar_init(&bar_q[i], 1);
-    tc::mbar_init(bar_s, 1); tc::mbar_init(bar_d, 1);
+    tc::mbar_init(bar_s, 1); tc::mbar_init(bar_dv, 1); tc::mbar_init(&bar_d[0], 1); tc::mbar_init(&bar_d[1], 1);
     tc::mbar_init(bar_free, BWDF_E_WARPS); tc::mbar_init(bar_p, BWDF_E_WARPS);
     tc::mbar_init(bar_dqf, BWDF_D_WARPS); tc::mbar_init(bar_epi, BWDF_D_WARPS);
     *s_abort = 0;
@@ -1416,8 +1418,9 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
   // S^T 128 | dP^T 128 | P^T (bf16 pairs) 64 | dV 64 | dK 64 | dQ 64
   const uint32_t t_st = tmem, t_dpt = tmem + 128, t_pt = tmem + 256, t_dv = tmem + 320, t_dk = tmem + 384, t_dq = tmem + 448;
   auto wait = [&](uint64_t* bar, uint32_t phase, int where) -> bool {
+    if (tc::mbar_try(bar, phase)) return true;
     if (*s_abort) return false;
-    if (!tc::mbar_wait_sleep(bar, phase, where)) { *s_abort = 1; return false; }
+    if (!tc::mbar_wait(bar, phase, where)) { *s_abort = 1; return false; }
     return true;
   };
   long long* tl = (a.timeline && blockIdx.x == 0 && lane == 0) ? a.timeline : nullptr;
@@ -1449,13 +1452,13 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
         for (int it = 0; it < n_it; it++, blk++) {
           // the tiles of block it+2 go where block it-1's were: its dV / dK MMAs must have finished reading them
           // (every completion of bar_d is observed, so this thread's parity never falls a whole period behind)
-          if (blk > 0) wait(bar_d, (blk - 1) & 1, 43);
+          if (blk > 0) wait(&bar_d[(blk - 1) & 1], ((blk - 1) >> 1) & 1, 43);
           if (it + 2 < n_it) load_q_do(cur, kt + it + 2, blk + 2);
         }
         const Item nx = item_at(li + 1);
         if (nx.valid) {
           // every MMA of this key tile is complete: K, V and all Q / dO buffers are free for the next item
-          wait(bar_d, (blk - 1) & 1, 44);
+          wait(&bar_d[(blk - 1) & 1], ((blk - 1) >> 1) & 1, 44);
           load_kv(nx);
           load_q_do(nx, nx.kt, blk);
           if (nq - nx.kt > 1) load_q_do(nx, nx.kt + 1, blk + 1);
@@ -1463,10 +1466,12 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
         cur = nx;
       }
     }
-  } else if (warp == BWDF_CTRL_WARP) {
-    // ---------------------------------------------------------------- MMA warp: waits, tcgen05.mma, commits, nothing else
-    // (these MMAs take 50-65 cycles each: every instruction this thread spends between two of them shows, so the
-    // descriptors are formed by adding small constants to per-buffer bases)
+  } else if (warp == BWDF_CTRL_WARP || warp == BWDF_SCORE_WARP) {
+    // ---------------------------------------------------------------- two MMA warps: waits, tcgen05.mma, commits, nothing else
+    // Every tcgen05.mma / commit costs its issuing thread ~75 cycles whatever the product's size: 32 MMAs and two commits
+    // per query block from ONE thread were 2700 of the block's 3500 cycles, never waiting.  The 8 score MMAs have
+    // their own issuing thread, so they go out while the 24 gradient MMAs of the previous block are still being issued.
+    // (Descriptors are formed by adding small constants to per-buffer bases.)
     if (lane == 0) {
       constexpr uint32_t idesc_s = tc::idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_d = tc::idesc_bf16(128, HD, 0, 1);    // A K-major (P^T in TMEM / dS^T), B MN-major (dO / Q)
@@ -1487,44 +1492,62 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
         for (int ks = 0; ks < HD / 16; ks++) tc::mma_bf16_ss(t_dpt, dVk + ks * 2, dDOk + o + ks * 2, idesc_s, ks > 0);
       };
       int blk = 0, buf = 0, q_use = 0;     // buffer blk % 3 and how many times it has been filled before (blk / 3)
-      for (int item = 0;; item++) {
-        const Item cur = item_at(item);
-        if (!cur.valid) break;
-        const int n_it = nq - cur.kt;
-        if (wait(bar_kv, item & 1, 40)) issue_scores(buf, q_use & 1);
-        tc::mma_commit(bar_s);
-        for (int it = 0; it < n_it; it++, blk++) {
-          int nbuf = buf + 1, nq_use = q_use;
-          if (nbuf == 3) { nbuf = 0; nq_use++; }
-          // S^T / dP^T of this block are in registers: the score MMAs of the next block may overwrite them
-          wait(bar_free, blk & 1, 42);
-          if (it + 1 < n_it) {
-            tc::tc_fence_after();
-            issue_scores(nbuf, nq_use & 1);
-            tc::mma_commit(bar_s);
+      if (warp == BWDF_SCORE_WARP) {
+        // the score products: S^T / dP^T of block j+1 as soon as block j's have been read out of TMEM
+        for (int item = 0;; item++) {
+          const Item cur = item_at(item);
+          if (!cur.valid) break;
+          const int n_it = nq - cur.kt;
+          if (wait(bar_kv, item & 1, 40)) issue_scores(buf, q_use & 1);
+          tc::mma_commit(bar_s);
+          for (int it = 0; it < n_it; it++, blk++) {
+            int nbuf = buf + 1, nq_use = q_use;
+            if (nbuf == 3) { nbuf = 0; nq_use++; }
+            // S^T / dP^T of this block are in registers: the score MMAs of the next block may overwrite them
+            wait(bar_free, blk & 1, 42);
+            if (it + 1 < n_it) {
+              tc::tc_fence_after();
+              issue_scores(nbuf, nq_use & 1);
+              tc::mma_commit(bar_s);
+            }
+            buf = nbuf; q_use = nq_use;
           }
-          bool go = wait(bar_p, blk & 1, 45);     // P^T in TMEM, dS^T in shared memory
-          if (tl) tl[blk * 8 + 5] = clock64();
-          if (it == 0 && item > 0) go = wait(bar_epi, (item - 1) & 1, 46) && go;   // previous tile's dK / dV have been read out
-          if (go) {
-            tc::tc_fence_after();
-            const uint64_t o = (uint64_t)buf * TILE_D;
-            const uint64_t od = (uint64_t)(blk & 1) * 2 * TILE_D;     // dS^T buffer of this block
-            const uint32_t acc = it > 0;
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(t_dv, t_pt + ks * 8, dDOmn + o + ks * 128, idesc_d, acc | (ks > 0));
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, dSTk + od + (ks >> 2) * TILE_D + (ks & 3) * 2, dQmn + o + ks * 128, idesc_d, acc | (ks > 0));
-            if (blk > 0) go = wait(bar_dqf, (blk - 1) & 1, 47);   // the previous dQ tile has left TMEM
+        }
+      } else {
+        // the gradient products of block j once P^T / dS^T are stored
+        for (int item = 0;; item++) {
+          const Item cur = item_at(item);
+          if (!cur.valid) break;
+          const int n_it = nq - cur.kt;
+          for (int it = 0; it < n_it; it++, blk++) {
+            bool go = wait(bar_p, blk & 1, 45);     // P^T in TMEM, dS^T in shared memory
+            if (tl) tl[blk * 8 + 5] = clock64();
+            if (it == 0) go = wait(bar_kv, item & 1, 40) && go;       // (seen by the score thread long ago; this thread reads K too)
+            go = wait(&bar_q[buf], q_use & 1, 41) && go;
+            if (it == 0 && item > 0) go = wait(bar_epi, (item - 1) & 1, 46) && go;   // previous tile's dK / dV have been read out
+            const bool dv_go = go;
             if (go) {
               tc::tc_fence_after();
+              const uint64_t o = (uint64_t)buf * TILE_D;
+              const uint64_t od = (uint64_t)(blk & 1) * 2 * TILE_D;     // dS^T buffer of this block
+              const uint32_t acc = it > 0;
 #pragma unroll
-              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, dSTmn + od + ks * 128, dKmn + ks * 128, idesc_q, ks > 0);
+              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ts(t_dv, t_pt + ks * 8, dDOmn + o + ks * 128, idesc_d, acc | (ks > 0));
+              tc::mma_commit(bar_dv);       // P^T's columns are free for the next block while dK and dQ are still going
+#pragma unroll
+              for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dk, dSTk + od + (ks >> 2) * TILE_D + (ks & 3) * 2, dQmn + o + ks * 128, idesc_d, acc | (ks > 0));
+              if (blk > 0) go = wait(bar_dqf, (blk - 1) & 1, 47);   // the previous dQ tile has left TMEM
+              if (go) {
+                tc::tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) tc::mma_bf16_ss(t_dq, dSTmn + od + ks * 128, dKmn + ks * 128, idesc_q, ks > 0);
+              }
             }
+            if (!dv_go) tc::mma_commit(bar_dv);     // (aborting: keep the barrier's phases in step)
+            tc::mma_commit(&bar_d[blk & 1]);
+            if (tl) tl[blk * 8 + 6] = clock64();
+            if (++buf == 3) { buf = 0; q_use++; }
           }
-          tc::mma_commit(bar_d);
-          if (tl) tl[blk * 8 + 6] = clock64();
-          buf = nbuf; q_use = nq_use;
         }
       }
     }
@@ -1570,6 +1593,8 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
         wait(bar_s, blk & 1, 48);          // S^T, dP^T of this block are complete
         tc::tc_fence_after();
         if (tl && warp == 0) tl[blk * 8 + 1] = clock64();
+        // dS^T of this block goes into the shared-memory tile that block blk-2's dK / dQ MMAs read
+        if (blk >= 2) wait(&bar_d[blk & 1], ((blk >> 1) + 1) & 1, 51);
         uint32_t pw[2][16];
         const bool diag = (it == 0);
 #pragma unroll
@@ -1610,15 +1635,15 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
               pw[hf][v8 * 4 + x] = pack_bf16(p0, p1);
               dw[x] = pack_bf16(d0, d1);
             }
-            // dS^T goes straight into the buffer that block blk-2 used (its MMAs completed before block blk-1's P^T
-            // was stored): only the two TMEM stores of P^T are left to do once the previous block's MMAs are out of the way
+            // dS^T goes straight into the buffer that block blk-2 used: only the two TMEM stores of P^T are left to do
+            // once the previous block's dV MMAs are out of the way
             *reinterpret_cast<uint4*>(smem + S::DST + (blk & 1) * 2 * TILE_BYTES + sw_off(row, qc)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
           }
         }
         tc::fence_async_smem();
         if (tl && warp == 0) tl[blk * 8 + 2] = clock64();
         // P^T's TMEM columns belong to the previous block's dV MMAs until they complete
-        if (blk > 0) { wait(bar_d, (blk - 1) & 1, 49); tc::tc_fence_after(); }
+        if (blk > 0) { wait(bar_dv, (blk - 1) & 1, 49); tc::tc_fence_after(); }
         if (tl && warp == 0) tl[blk * 8 + 3] = clock64();
         tc::tmem_st16(t_pt + lane_addr + ch * 32, pw[0]);
         tc::tmem_st16(t_pt + lane_addr + ch * 32 + 16, pw[1]);
@@ -1649,7 +1674,7 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
       const int n_it = nq - kt;
       for (int it = 0; it < n_it; it++, blk++) {
         const int i = kt + it;
-        wait(bar_d, blk & 1, 50);          // dV, dK, dQ MMAs of this block are complete
+        wait(&bar_d[blk & 1], (blk >> 1) & 1, 50);          // dV, dK, dQ MMAs of this block are complete
         tc::tc_fence_after();
         uint32_t r0[32], r1[32];
         tc::tmem_ld32(t_dq + lane_addr, r0);

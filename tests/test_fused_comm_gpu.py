@@ -33,14 +33,21 @@ def test_fused_engine_world1_matches_separate_adamw():
             tr = Trainer(cfg, 2, "cuda:0", r, lr=1e-3, wd=0.1)
             assert (tr.ddp.fused is not None) == (comm == "fused")
             tr.set_batch(ids.cuda(), tgt.cuda())
-            for _ in range(5):
+            for _ in range(2):
                 tr.step()
             torch.cuda.synchronize()
-            res.append((tr.model.master.clone(), tr.model.params.clone(), tr.loss()))
+            early = tr.model.master.clone()
+            for _ in range(3):
+                tr.step()
+            torch.cuda.synchronize()
+            res.append((tr.model.master.clone(), tr.model.params.clone(), tr.loss(), early))
     finally:
         native.lib().mlb_gemm_set_splits(0)
-    # same gradients, same update formula
-    assert (res[0][0] - res[1][0]).abs().max() < 2e-4
+    # Same gradients, same update formula: after two steps the masters agree to rounding (the two kernels contract
+    # their multiply-adds differently).  Later a last-bit difference that flips a bf16 parameter changes the next
+    # gradients, and Adam's normalised step turns that into up to ~lr per step for near-zero gradients: bounded, not equal.
+    assert (res[0][3] - res[1][3]).abs().max() < 1e-6
+    assert (res[0][0] - res[1][0]).abs().max() < 1e-3
     assert abs(res[0][2] - res[1][2]) < 2e-2
     assert torch.equal(res[1][1], res[1][0].to(torch.bfloat16))     # bf16 copy written by the fused kernel
 
