@@ -6,7 +6,7 @@ train/gemm_bench.cu, train/attn_bench.cu, train/norm_bench2.cu).
     python -m ml_b200.bench.kernels mma                         cycles per tcgen05.mma by N and A-operand source
     python -m ml_b200.bench.kernels attn  [--B 16 --T 1024]     flash attention fwd / bwd vs torch SDPA
     python -m ml_b200.bench.kernels norm                        RMSNorm fwd / add+norm / bwd, CE, AdamW, SwiGLU bandwidth
-    python -m ml_b200.bench.kernels once  --case attn|gemm      a few un-timed launches (what an `ncu` capture wraps)
+    python -m ml_b200.bench.kernels once  --case attn|gemm|vision      a few un-timed launches (what an `ncu` capture wraps)
     python -m ml_b200.bench.kernels corun                       tensor-core GEMMs next to a small kernel on a second stream
 
 Timing: CUDA events on the launching stream, `--warm` warm-up launches, L2 flushed (256 MB write) before every timed
@@ -314,6 +314,20 @@ def once(a):
             nat.rmsnorm_bwd(o, dw, x, x, w, r, x)
             nat.ce_fwd_bwd(ls, lg, tg, 1.0 / rows)
             nat.adamw(ma, p, g, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.5, 0.5, 1.0)
+    elif a.case == "vision":
+        # the multimodal bench's vision tower (196 patches of 16 x 16 x 3, width 768, 4 MLP blocks, MLP width 2048) on
+        # a.B images: fp32 pixels -> patch rows -> patch embedding with the position add in its epilogue -> blocks ->
+        # projector, and the whole backward
+        from ml_b200 import VisionConfig
+        from ml_b200.models.vision import VisionTower
+        vc = VisionConfig(vC=768, vL=4, vI=2048, n_patch=196)
+        vt = VisionTower(vc, a.C, a.B, dev)
+        vt.init_weights(777)
+        px = torch.randn(a.B, 3, vc.image_hw, vc.image_hw, device=dev)
+        for _ in range(3):
+            vt.forward_pixels(px)
+            vt.dimg.copy_(vt.img)
+            vt.backward()
     elif a.case == "gemm8":
         # gate|up-shaped products: bf16 with the SwiGLU epilogue, and the 8-bit (E4M3) forms
         M, I, K = a.M, a.I, a.C
@@ -351,7 +365,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemm", "corun", "layouts", "mma", "attn", "norm", "once"])
     ap.add_argument("--K", type=int, default=8192)
-    ap.add_argument("--case", default="attn", choices=["attn", "gemm", "gemm8", "norm"])
+    ap.add_argument("--case", default="attn", choices=["attn", "gemm", "gemm8", "norm", "vision"])
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--C", type=int, default=768)
     ap.add_argument("--I", type=int, default=2048)

@@ -491,13 +491,14 @@ def test_embedding_and_prefix():
 
 def test_vision_helpers_and_casts():
     torch.manual_seed(14)
-    B, P, g = 2, 16, 3
-    px = torch.randn(B, 3, g * P, g * P, device=dev())
-    out = torch.empty(B * g * g, 3 * P * P, device=dev(), dtype=torch.bfloat16)
-    e = torch.empty(B * g * g, 3 * P * P, device=dev())
-    nat().patchify(out, px, P)
-    ref.patchify(e, px, P)
-    assert torch.equal(out, e.to(torch.bfloat16))
+    B, g = 2, 3
+    for P in (16, 8, 4):        # eight pixels per thread where the patch edge allows it, else one
+        px = torch.randn(B, 3, g * P, g * P, device=dev())
+        out = torch.empty(B * g * g, 3 * P * P, device=dev(), dtype=torch.bfloat16)
+        e = torch.empty(B * g * g, 3 * P * P, device=dev())
+        nat().patchify(out, px, P)
+        ref.patchify(e, px, P)
+        assert torch.equal(out, e.to(torch.bfloat16)), P
     NP, vC, n_patch = B * 9, 96, 9
     x, pos = rnd(NP, vC), rnd(n_patch, vC)
     a, ee = x.clone(), x.clone()
