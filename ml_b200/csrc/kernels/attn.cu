@@ -58,6 +58,7 @@ struct AttnArgs {
   long long* timeline; // optional: SM cycle stamps of CTA (0,0,0) of the fused backward, eight per (query block) step
   const int* sched;    // forward over tile pairs: per CTA the work items in order, -1 terminated; nullptr = round robin
   int sched_stride;    // entries per CTA in `sched`
+  int dynamic;         // persistent kernels: draw the work items from the device counter instead
   int out_tma;         // forward over tile pairs: O leaves through a staging tile and TMA stores (needs T % 128 == 0)
 };
 
@@ -480,6 +481,53 @@ __device__ __forceinline__ uint32_t pack_hi16(float lo, float hi) {
   asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
   return r;
 }
+// ------------------------------------------------------------------ work items from a device counter
+// Alternative to the host-built table: the CTAs of a launch draw item numbers 0, 1, 2, ... (heaviest first) from a
+// counter in device memory.  One thread per CTA (the loader) draws - always ahead of where the CTA is working, since it
+// needs the next items for its prefetches - and publishes what it drew in a shared-memory ring (value, then sequence
+// number); every other role of the CTA reads its li-th item from the ring and waits, bounded, if it is not there yet.
+// A CTA that finds the counter exhausted publishes -1 from then on.  The last CTA to leave resets the counters, so
+// there is nothing to zero between launches (or graph replays); one launch per kernel kind may be in flight on a device.
+// A shape met for the first time needs no table then (none can be built during graph capture).  Off by default: a CTA
+// has to claim its next item while it still works on the current one (the prefetches need it), which costs the balance
+// more than the table's fixed assignment does - 4 us per forward and 10 us per backward call alone, 0.3 ms per step
+// next to the gradient kernels that run behind backward on 4 GPUs.
+__device__ int g_attn_ctr[4];      // [2 * kind]: next item, [2 * kind + 1]: CTAs that have left
+struct ItemRing {
+  volatile int* val;   // [64]
+  volatile int* seq;   // [64]: li + 1 once item li has been published; seq[64]: index of the first -1 item (INT_MAX until known)
+  int published;       // publisher only
+  __device__ __forceinline__ int draw(int li, int kind, int total) {          // publisher thread
+    while (published <= li) {
+      if (published >= seq[64]) { published = li + 1; break; }              // exhausted: nothing more to draw or publish
+      int w = atomicAdd(&g_attn_ctr[2 * kind], 1);
+      if (w >= total) { seq[64] = published; __threadfence_block(); published = li + 1; break; }
+      val[published & 63] = w;
+      __threadfence_block();
+      seq[published & 63] = published + 1;
+      published++;
+    }
+    return li >= seq[64] ? -1 : val[li & 63];
+  }
+  __device__ __forceinline__ int read(int li, volatile int* abort_flag) const {     // everyone else
+    for (long spin = 0; spin < (1L << 26); spin++) {
+      if (seq[li & 63] == li + 1) return val[li & 63];
+      if (li >= seq[64]) return -1;
+      if (*abort_flag) return -1;
+    }
+    mlb_set_error(MLB_ERR_MBAR_TIMEOUT, 0x7f);
+    *abort_flag = 1;
+    return -1;
+  }
+};
+__device__ __forceinline__ void attn_ctr_leave(int kind) {        // one thread per CTA, after the CTA's last draw
+  __threadfence();
+  if (atomicAdd(&g_attn_ctr[2 * kind + 1], 1) == (int)gridDim.x - 1) {
+    g_attn_ctr[2 * kind] = 0;
+    g_attn_ctr[2 * kind + 1] = 0;
+    __threadfence();
+  }
+}
 struct Fwd2Smem {
   static constexpr int Q = 0;                          // 2 buffers x 2 tiles
   static constexpr int KN = 3;                         // K slots; V has one more
@@ -488,7 +536,7 @@ struct Fwd2Smem {
   static constexpr int OST = V + (KN + 1) * TILE_BYTES;   // O staging: 8 warps x [32 rows x 128 B] bf16, swizzled
   static constexpr int BAR = OST + 2 * TILE_BYTES;
   static constexpr int SCHED = BAR + 256;                 // this CTA's first 64 work items
-  static constexpr int TOTAL = SCHED + 256 + 1024;
+  static constexpr int TOTAL = SCHED + 768 + 1024;             // SCHED: 64 items, or a ring of 64 (value, sequence number) + end marker
 };
 constexpr int FWD2_THREADS = 11 * 32;   // 8 softmax warps, MMA warp of tile 0, loader warp, MMA warp of tile 1
 
@@ -518,7 +566,7 @@ struct Fwd2Step {   // one key block of one item in this CTA's flattened sequenc
 // FMA pipe instead of the special-function unit - equal, 3 % and 5 % slower although the pure exponential chunks got
 // shorter; fp16 exponentials two at a time; tile 1 started half a block behind tile 0; the MMA and loader threads
 // sleeping between barrier probes.)
-template <int MODE>
+template <int MODE, bool DYN = false>
 __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tm_out,
                                                                            const AttnArgs a) {
   mlb_pdl_sync();
@@ -553,7 +601,12 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
   const int* srow = a.sched ? a.sched + (size_t)blockIdx.x * a.sched_stride : nullptr;
   int* s_sched = (int*)(smem + S::SCHED);     // the row's first 64 entries: a global load at an item boundary stalls
   if (srow && tid < 64) s_sched[tid] = tid < a.sched_stride ? __ldg(srow + tid) : -1;   // its warp for a DRAM latency
+  constexpr bool dyn = DYN;
+  ItemRing ring{(volatile int*)s_sched, (volatile int*)s_sched + 64, 0};
+  if (dyn && tid <= 64) s_sched[64 + tid] = tid < 64 ? 0 : 0x7fffffff;
+  const bool publisher = warp == 9 && lane == 0;
   auto item_at = [&](int li) -> int {
+    if (dyn) return publisher ? ring.draw(li, 0, total) : ring.read(li, s_abort);
     if (srow) return li < 64 ? s_sched[li] : __ldg(srow + li);
     const int x = blockIdx.x + li * stride;
     return x < total ? x : -1;
@@ -1048,6 +1101,7 @@ __global__ void __maxnreg__(160) attn_fwd_rows_tc_kernel(const __grid_constant__
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 8) tc::tmem_dealloc(tmem, TMEM_COLS);
+  if (dyn && tid == 0) attn_ctr_leave(0);
 }
 
 // ================================================================== backward: delta = rowsum(dO * O)
@@ -1339,7 +1393,7 @@ struct BwdFusedSmem {
   static constexpr int STAT = DQS + TILE_BYTES;          // 8 warps x (-lse*log2e [64], -delta [64])
   static constexpr int BAR = STAT + 4096;
   static constexpr int SCHED = BAR + 256;                // this CTA's first 64 work items
-  static constexpr int TOTAL = SCHED + 256 + 1024;
+  static constexpr int TOTAL = SCHED + 768 + 1024;             // SCHED: 64 items, or a ring of 64 (value, sequence number) + end marker
 };
 
 constexpr int BWDF_E_WARPS = 8;       // element-wise warps: TMEM lane group (w & 3) x 64-query column half (w >> 2)
@@ -1351,6 +1405,7 @@ constexpr int BWDF_CTRL_WARP = BWDF_E_WARPS + BWDF_D_WARPS + 2;   // issues dV /
 constexpr int BWDF_LOAD_WARP = BWDF_CTRL_WARP + 1;                // issues every TMA load
 constexpr int BWDF_THREADS = (BWDF_LOAD_WARP + 1) * 32;
 
+template <bool DYN>
 __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant__ CUtensorMap tm_qkv,
                                                                             const __grid_constant__ CUtensorMap tm_do,
                                                                             const __grid_constant__ CUtensorMap tm_dq, const AttnArgs a) {
@@ -1383,9 +1438,14 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
   int* s_sched = (int*)(smem + S::SCHED);
   if (srow && tid < 64) s_sched[tid] = tid < a.sched_stride ? __ldg(srow + tid) : -1;
   struct Item { int kt, b, h, row0; bool valid; };
+  constexpr bool dyn = DYN;
+  ItemRing ring{(volatile int*)s_sched, (volatile int*)s_sched + 64, 0};
+  if (dyn && tid <= 64) s_sched[64 + tid] = tid < 64 ? 0 : 0x7fffffff;
+  const bool publisher = warp == BWDF_LOAD_WARP && lane == 0;
   auto item_at = [&](int li) -> Item {
     int w;
-    if (srow) w = li < 64 ? s_sched[li] : __ldg(srow + li);
+    if (dyn) w = publisher ? ring.draw(li, 1, total) : ring.read(li, s_abort);
+    else if (srow) w = li < 64 ? s_sched[li] : __ldg(srow + li);
     else { w = blockIdx.x + li * gridDim.x; if (w >= total) w = -1; }
     Item r;
     r.valid = w >= 0;
@@ -1721,6 +1781,7 @@ __global__ void __maxnreg__(120) attn_bwd_fused_tc_kernel(const __grid_constant_
   tc::tc_fence_before();
   __syncthreads();
   if (warp == BWDF_CTRL_WARP) tc::tmem_dealloc(tmem, TMEM_COLS);
+  if (dyn && tid == 0) attn_ctr_leave(1);
 }
 
 // dQ partial tiles -> bf16 Q slice of dqkv[rows, 3C]: sum over the key tiles kt <= i of query tile i (fp32, fixed
@@ -2032,6 +2093,7 @@ __global__ void attn_bwd_kv_simt_k(bf16* __restrict__ dqkv, const bf16* __restri
 }
 
 int g_attn_force_simt = 0;
+int g_attn_dynamic = 0;
 int g_fwd_rows = 3;   // head size 64: 1 / 2 / 3 = thread-per-row forward over tile pairs (variants at the launch), 0 = four-threads-per-row forward
 
 template <typename K>
@@ -2049,6 +2111,8 @@ bool tc_ok(const void* qkv, const void* other, int H, int hd) {
 static long long* g_timeline = nullptr;
 MLB_API void mlb_attn_force_simt(int on) { g_attn_force_simt = on; }
 MLB_API void mlb_attn_fwd_mode(int rows) { g_fwd_rows = rows; }
+// 1: the persistent attention kernels draw their work items from a device counter (see ItemRing); 0: host-built table
+MLB_API void mlb_attn_dynamic(int on) { g_attn_dynamic = on; }
 // Diagnostic: device buffer of at least 8 * (query blocks per CTA) int64 that CTA (0,0,0) of the fused backward fills
 // with SM cycle stamps, eight per block: element-wise warp 0 before / after the score wait, after its exponentials,
 // after the previous block's MMAs completed, after P^T / dS^T are stored; control thread when it saw P^T and when the
@@ -2130,7 +2194,8 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
       // more than 2^8; 3: as 2 with the row maximum tracked inside the exponential pass (one pass per key block)
       const long pairs = (long)(((T + 127) / 128 + 1) / 2) * H * B;
       const dim3 grid2((unsigned)(pairs < sms ? pairs : sms));
-      a.sched = pairs > sms ? attn_schedule(0, B, H, T, (int)grid2.x, &a.sched_stride, st) : nullptr;
+      a.dynamic = (g_attn_dynamic && g_fwd_rows != 1 && g_fwd_rows != 2) ? 1 : 0;      // (the default variant only)
+      a.sched = (pairs > sms && !a.dynamic) ? attn_schedule(0, B, H, T, (int)grid2.x, &a.sched_stride, st) : nullptr;
       const CUtensorMap* to = (T % 128 == 0 && g_fwd_rows >= 2) ? mlb_tmap_cached(out, (uint64_t)B * T, C, C, 32, 64, 2) : nullptr;
       a.out_tma = to != nullptr;
       if (!to) to = tm;      // unused by the kernel then
@@ -2140,10 +2205,16 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
     (void)once;                                                                                                                \
     mlb_launch(attn_fwd_rows_tc_kernel<MODE>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, *to, a);              \
   }
-      switch (g_fwd_rows) {
-        case 1: MLB_FWD2(1) break;
-        case 2: MLB_FWD2(2) break;
-        default: MLB_FWD2(3) break;
+      if (a.dynamic && g_fwd_rows != 1 && g_fwd_rows != 2) {
+        static int once = set_smem(attn_fwd_rows_tc_kernel<3, true>, Fwd2Smem::TOTAL);
+        (void)once;
+        mlb_launch(attn_fwd_rows_tc_kernel<3, true>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, *to, a);
+      } else {
+        switch (g_fwd_rows) {
+          case 1: MLB_FWD2(1) break;
+          case 2: MLB_FWD2(2) break;
+          default: MLB_FWD2(3) break;
+        }
       }
 #undef MLB_FWD2
     } else if (hd == 64) {
@@ -2214,8 +2285,9 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
       const long nqh = (T + 127) / 128;
       const CUtensorMap* tpart = mlb_tmap_cached(dq_part, (uint64_t)B * (nqh * (nqh + 1) / 2) * 128, C, C, 32, 64, 2);
       if (!tpart) return -2;
-      static int o0 = set_smem(attn_bwd_fused_tc_kernel, BwdFusedSmem::TOTAL);
-      (void)o0;
+      static int o0 = set_smem(attn_bwd_fused_tc_kernel<false>, BwdFusedSmem::TOTAL);
+      static int o1 = set_smem(attn_bwd_fused_tc_kernel<true>, BwdFusedSmem::TOTAL);
+      (void)o0; (void)o1;
       // persistent CTAs, one per SM, over the (key tile, sample, head) items
       int sms = 0, devid = 0;
       cudaGetDevice(&devid);
@@ -2223,8 +2295,10 @@ MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const vo
       if (sms <= 0) sms = 148;
       const long n_items = nqh * H * B;
       dim3 grid_f((unsigned)(n_items < sms ? n_items : sms));
-      a.sched = n_items > sms ? attn_schedule(1, B, H, T, (int)grid_f.x, &a.sched_stride, st) : nullptr;
-      mlb_launch(attn_bwd_fused_tc_kernel, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
+      a.dynamic = g_attn_dynamic;
+      a.sched = (n_items > sms && !a.dynamic) ? attn_schedule(1, B, H, T, (int)grid_f.x, &a.sched_stride, st) : nullptr;
+      if (a.dynamic) mlb_launch(attn_bwd_fused_tc_kernel<true>, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
+      else mlb_launch(attn_bwd_fused_tc_kernel<false>, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
       const long groups = (long)B * T * H * (hd / 32);
       mlb_launch(attn_dq_finish_k, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, st, (bf16*)dqkv, (const bf16*)dq_part, (long)B * T, T, H, hd, scale, cosT, sinT);
       cudaError_t e = cudaGetLastError();

@@ -237,6 +237,31 @@ def bwd_mode(request):
     nat().FUSED_ATTN_BWD = old
 
 
+@pytest.mark.parametrize("B,T,H", [(2, 384, 2), (3, 1024, 4), (1, 128, 1), (16, 512, 12)])
+def test_attn_dynamic_work_counter_equals_static_schedule(B, T, H):
+    """Work items drawn from the device counter instead of the host-built table: the same bits out of forward and
+    backward (who computes an item does not enter its arithmetic), twice in a row (the last CTA resets the counter)."""
+    torch.manual_seed(B * T + H)
+    hd, C = 64, H * 64
+    qkv, dout = rnd(B * T, 3 * C), rnd(B * T, C)
+    outs = []
+    for dyn in (False, True, True):
+        nat().attn_dynamic(dyn)
+        try:
+            out = torch.full((B * T, C), float("nan"), device=dev(), dtype=torch.bfloat16)
+            lse = torch.empty(B, H, T, device=dev())
+            dqkv = torch.full((B * T, 3 * C), float("nan"), device=dev(), dtype=torch.bfloat16)
+            nat().attn_fwd(out, lse, qkv, B, T, H, hd)
+            nat().attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd)
+            torch.cuda.synchronize()
+        finally:
+            nat().attn_dynamic(False)
+        outs.append((out, lse, dqkv))
+    for o in outs[1:]:
+        assert torch.equal(o[0], outs[0][0]) and torch.equal(o[1], outs[0][1]) and torch.equal(o[2], outs[0][2])
+
+
+
 @pytest.mark.parametrize("B,T,H,hd", [c for c in ATTN_CASES if c[3] == 64] + [(3, 640, 2, 64), (1, 1100, 1, 64), (4, 1024, 12, 64)])
 @pytest.mark.parametrize("rows", [1, 2, 3, 0], ids=["thread_per_row", "thread_per_row_lazy_rescale", "thread_per_row_one_pass", "four_threads_per_row"])
 @pytest.mark.parametrize("qscale", [1.0, 3.0], ids=["unit_scale", "peaked_scores"])
