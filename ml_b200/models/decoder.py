@@ -32,13 +32,14 @@ FUSE_SWIGLU_INTO_GU = _os.environ.get("MLB_NO_SWIGLU_FUSE", "0") != "1"
 class GPT:
     def __init__(self, cfg: Config, B: int, device="cpu", dtype: Optional[torch.dtype] = None,
                  opt_state: bool = True, alloc_grads: bool = True, alloc=None, sharded: bool = False,
-                 lmce_chunk: Optional[int] = None, fp8_fwd: Optional[bool] = None):
+                 lmce_chunk: Optional[int] = None, fp8_fwd: Optional[bool] = None, canaries: Optional[bool] = None):
         """alloc(numel, dtype) -> flat tensor: optional allocator for the parameter and gradient buffers (the
         data-parallel engines pass a symmetric-memory allocator so peers can address them).
         sharded=True: no flat master / params / grads / m / v are allocated here; a sharding engine
         (ml_b200.parallel.fsdp) owns the storage and serves parameter / gradient views through `self.res`.
         lmce_chunk > 0 (default: ENTROPY_LMCE_CHUNK): the LM head and its cross-entropy run over vocabulary chunks of
-        that many columns inside backward, and the [B*T, V] logits buffer is never allocated (train/gpt.cu:221-239,396-445)."""
+        that many columns inside backward, and the [B*T, V] logits buffer is never allocated (train/gpt.cu:221-239,396-445).
+        canaries=True (default: MLB_CANARY=1): activation buffers sit between guard bands; see check_canaries()."""
         cfg.validate()
         self.cfg = cfg
         self.B = B
@@ -85,11 +86,25 @@ class GPT:
             self.v = torch.zeros(self.np, dtype=torch.float32, device=dev) if opt_state else None
         self.cos, self.sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, dev)
         self.params8 = torch.zeros(self.np, dtype=torch.uint8, device=dev) if self.fp8_native else None
+        self.canaries = bool(canaries) if canaries is not None else _os.environ.get("MLB_CANARY", "0") == "1"
+        self._guard = None
         self._alloc_acts(B)
         # hooks: called as hook(name, offset, numel) when a gradient bucket is final
         self.bucket_hook: Optional[Callable[[str, int, int], None]] = None
         self.prof = None
         self.skip = set()
+
+    def check_canaries(self):
+        """With canaries=True: raises if any kernel of the steps so far wrote into the guard band in front of or behind
+        an activation buffer (synchronises the device)."""
+        if self._guard is None:
+            raise RuntimeError("this model was built without canaries (canaries=True or MLB_CANARY=1)")
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        self._guard.name_buffers(self)
+        bad = self._guard.check()
+        if bad:
+            raise RuntimeError("guard bands overwritten: " + ", ".join(bad))
 
     # ------------------------------------------------------------------ buffers
     def _alloc_acts(self, B):
@@ -97,6 +112,12 @@ class GPT:
         BT, C, I, V, Lh = B * c.T, c.C, c.I, c.V, c.L
         e = lambda *s: torch.empty(*s, dtype=self.dtype, device=self.device)
         f = lambda *s: torch.empty(*s, dtype=torch.float32, device=self.device)
+        if self.canaries:
+            # every buffer between two bands of a fixed byte pattern (ml_b200.utils.canary): check_canaries() after a step
+            from ..utils.canary import GuardedAlloc
+            self._guard = GuardedAlloc(self.device)
+            e = lambda *s: self._guard.empty(*s, dtype=self.dtype)
+            f = lambda *s: self._guard.empty(*s, dtype=torch.float32)
         self.x0 = e(BT, C)
         self.ln1 = [e(BT, C) for _ in range(Lh)]
         self.qkv = [e(BT, 3 * C) for _ in range(Lh)]

@@ -2,6 +2,7 @@
 with asserted thresholds, and gradient-accumulation semantics."""
 import math
 
+import pytest
 import torch
 import torch.nn.functional as F
 
@@ -301,3 +302,21 @@ def test_module_tree_grouped_query_attention_and_qkv_bias():
     assert abs(loss.item() - ref.item()) < 1e-5
     for n, p in m.named_parameters():
         assert torch.allclose(p.grad, P[n].grad, atol=2e-5, rtol=1e-4), n
+
+
+def test_guard_bands_around_activation_buffers():
+    """canaries=True: a full step leaves every band intact; a write just past the end of a buffer is reported by name."""
+    cfg = Config(V=96, C=32, L=2, H=2, I=64, T=16)
+    g = GPT(cfg, 2, "cpu", canaries=True)
+    g.init_weights(5)
+    ids, tgt = Stream(9).token_pairs(2 * 16, 96)
+    g.forward(ids)
+    g.backward(ids, tgt)
+    g.check_canaries()
+    flat = g.gu[1].view(-1)
+    torch.as_strided(flat, (flat.numel() + 1,), (1,))[-1] = 3.0       # one element beyond the buffer
+    with pytest.raises(RuntimeError, match=r"gu\[1\]:back"):
+        g.check_canaries()
+    plain = GPT(cfg, 2, "cpu")
+    with pytest.raises(RuntimeError, match="without canaries"):
+        plain.check_canaries()

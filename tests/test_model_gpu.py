@@ -260,3 +260,26 @@ def test_mm_overfit_gpu():
         if s == 0:
             first = tr.loss()
     assert abs(first - 5.565) < 0.06 and tr.loss() < 0.01, (first, tr.loss())   # reference: 5.56500 -> 0.00115
+
+
+@pytest.mark.parametrize("cfg,B,kw", [
+    (Config(V=512, C=256, L=2, H=4, I=512, T=256), 2, {}),                    # tcgen05 everywhere
+    (Config(V=384, C=256, L=1, H=2, I=384, T=128), 2, {}),                    # hd=128 attention kernels
+    (Config(V=500, C=192, L=2, H=3, I=264, T=200), 3, {}),                    # ragged tiles: T, I and V off the tile sizes
+    (Config(V=512, C=256, L=2, H=4, I=512, T=256), 2, {"lmce_chunk": 200}),   # chunked LM head
+    (Config(V=512, C=256, L=2, H=4, I=512, T=256), 2, {"fp8_fwd": True}),     # 8-bit forward and its producers
+])
+def test_no_kernel_writes_outside_its_buffers(cfg, B, kw):
+    """Every activation / scratch buffer between guard bands: two full steps (forward, backward, AdamW) leave all bands
+    intact - no kernel stores outside its output, whatever the tile remainder."""
+    ids, tgt = Stream(7).token_pairs(B * cfg.T, cfg.V)
+    g = GPT(cfg, B, "cuda:0", canaries=True, **kw)
+    g.init_weights(1234)
+    di, dt = ids.cuda(), tgt.cuda()
+    for t in (1, 2):
+        g.forward(di)
+        g.backward(di, dt)
+        g.adamw(1e-3, t=t)
+    g.check_canaries()
+    assert _native().get_error() == 0
+    assert g.mean_loss() == g.mean_loss()      # not NaN
