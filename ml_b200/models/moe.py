@@ -3,7 +3,8 @@
 The reference's prototype has router / gating / expert kernels that nothing calls and a forward that hard-codes expert 0
 (csrc/kernels/moe_kernels.cu:18-194, csrc/src/model.cu:829-861).  This block is functional: softmax router, top-k
 selection with renormalised gates, tokens grouped per expert, each expert a SwiGLU MLP on the fused ops (tcgen05 GEMMs on
-GPU), results combined by gate weight.  Single-process (no expert-parallel all-to-all).
+GPU), results combined by gate weight.  Single-process; `ml_b200.parallel.ep.EPMoEBlock` is the expert-parallel form
+(experts split over ranks, tokens exchanged by all-to-all).
 """
 from __future__ import annotations
 

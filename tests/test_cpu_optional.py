@@ -252,3 +252,46 @@ def test_vit_encoder_matches_a_plain_pytorch_restatement_and_trains():
         for n, p in m.named_parameters():
             assert (got[n] - p.grad).abs().max() < 2e-3 * (1 + p.grad.abs().max()), (norm, n)
         assert m(px, return_all=True).shape == (3, m.T, 24)
+
+
+def test_expert_parallel_moe_two_ranks_equals_single_process_block():
+    """Experts split over two gloo ranks, tokens exchanged by all-to-all: every rank's output, its auxiliary loss, the
+    expert-weight gradients (on their owners) and the summed router gradient equal the single-process block's."""
+    from tests.test_cpu_ddp import run_ranks
+    outs = run_ranks("""
+        import torch, torch.distributed as dist
+        from ml_b200.parallel.bootstrap import init_distributed, shutdown
+        from ml_b200.models.moe import MoEBlock
+        from ml_b200.parallel.ep import EPMoEBlock
+        rank, world, local, dev = init_distributed("cpu")
+        torch.manual_seed(3)
+        full = MoEBlock(32, 48, n_experts=4, top_k=2)
+        xs = [torch.randn(20 + 5 * r, 32) for r in range(world)]          # a different token count per rank
+        ep = EPMoEBlock(full, rank, world)
+        x = xs[rank].clone().requires_grad_(True)
+        out, aux = ep(x)
+        (out.square().sum() + aux).backward()
+        # single-process oracle: every rank's tokens through all experts, losses summed
+        for p in full.parameters():
+            p.grad = None
+        ref_outs = []
+        for r in range(world):
+            xr = xs[r].clone().requires_grad_(True)
+            o, a = full(xr)
+            (o.square().sum() + a).backward()
+            ref_outs.append((o.detach(), a.detach(), xr.grad))
+        assert torch.allclose(out, ref_outs[rank][0], atol=1e-5), (out - ref_outs[rank][0]).abs().max()
+        assert torch.allclose(aux, ref_outs[rank][1], atol=1e-6)
+        assert torch.allclose(x.grad, ref_outs[rank][2], atol=1e-5)
+        El = full.E // world
+        for i in range(El):
+            assert torch.allclose(ep.gate_up[i].grad, full.gate_up[rank * El + i].grad, atol=1e-5)
+            assert torch.allclose(ep.down[i].grad, full.down[rank * El + i].grad, atol=1e-5)
+        g = ep.router.grad.clone()
+        dist.all_reduce(g)
+        assert torch.allclose(g, full.router.grad, atol=1e-5)
+        print("EP_OK", rank, flush=True)
+        shutdown()
+    """, world=2)
+    for rc, o in outs:
+        assert rc == 0 and "EP_OK" in o, o[-2000:]

@@ -100,3 +100,38 @@ def test_tensor_parallel_mode_two_gpus_equals_unsharded(token_file, tmp_path):
     assert len(tp) == 5 and len(one) == 5, (tp, one)
     for a, b in zip(tp, one):
         assert abs(a - b) < 5e-2, (tp, one)
+
+
+@needs2
+def test_expert_parallel_moe_two_gpus_equals_single_process_block():
+    """`parallel/ep.py` on NCCL: experts split over two GPUs, dispatch / combine by all-to-all, expert MLPs on the
+    tcgen05 GEMMs (bf16), against the single-process block on the same tokens."""
+    rc, out = _torchrun("""
+        import torch, torch.distributed as dist
+        from ml_b200.parallel.bootstrap import init_distributed
+        from ml_b200.models.moe import MoEBlock
+        from ml_b200.parallel.ep import EPMoEBlock
+        from ml_b200.ops import native
+        rank, world, local, dev = init_distributed()
+        torch.manual_seed(3)
+        full = MoEBlock(256, 512, n_experts=4, top_k=2, device=dev, dtype=torch.bfloat16)
+        g = torch.Generator(device="cpu").manual_seed(11)
+        xs = [torch.randn(384 + 128 * r, 256, generator=g).to(dev).bfloat16() for r in range(world)]
+        ep = EPMoEBlock(full, rank, world)
+        x = xs[rank].clone().requires_grad_(True)
+        out, aux = ep(x)
+        (out.float().square().sum() + aux).backward()
+        xr = xs[rank].clone().requires_grad_(True)
+        o, a = full(xr)
+        (o.float().square().sum() + a).backward()
+        torch.cuda.synchronize()
+        rel = float((out.float() - o.float()).norm() / o.float().norm())
+        relg = float((x.grad.float() - xr.grad.float()).norm() / xr.grad.float().norm())
+        print("EP", rank, rel, relg, abs(float(aux) - float(a)), native.get_error(), flush=True)
+        dist.barrier(); dist.destroy_process_group()
+    """, 2)
+    assert rc == 0, out[-3000:]
+    lines = [l.split() for l in out.splitlines() if l.startswith("EP ")]
+    assert len(lines) == 2, out[-2000:]
+    for l in lines:
+        assert float(l[2]) < 1e-2 and float(l[3]) < 2e-2 and float(l[4]) < 1e-3 and l[5] == "0", l
