@@ -199,8 +199,7 @@ class RunConfig:
         "ENTROPY_CE_THREADS": "the cross-entropy kernel's block size is fixed",
         "ENTROPY_MLP_DUAL": "weight-gradient and input-gradient GEMMs already run as separate persistent kernels",
         "ENTROPY_BETA0_GRADS": "weight gradients are add-reduced by stream-K pieces, which needs the zero-fill",
-        "ENTROPY_AUTOTUNE": "the GEMMs are hand-written kernels with static shape heuristics (no library plans to time)",
-        "ENTROPY_AUTOTUNE_K": "see ENTROPY_AUTOTUNE",
+        "ENTROPY_AUTOTUNE_K": "the plan cache times every form of this library's GEMM (at most 48 per shape), there is no top-k to cut",
         "ENTROPY_LT_WS_MB": "no library workspace is used",
         "ENTROPY_SKIP_GEMM_BWD": "read and never used by the reference either (train/gpt.cu:583)",
         "ENTROPY_LMCE_FUSED_DX": "the chunked head feeds the tensor-core GEMMs; the direct dX kernel is not rebuilt",

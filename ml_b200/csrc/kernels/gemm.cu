@@ -16,6 +16,7 @@
 
 #include <cstdio>
 #include <map>
+#include <array>
 #include <mutex>
 #include <tuple>
 #include <vector>
@@ -915,8 +916,8 @@ struct RopeEpi { const float* cosT; const float* sinT; int T, cols; };
 struct SwigluEpi { bf16* out; int I; };
 struct PosEpi { const bf16* pos; int period; };
 template <bool A_MN, bool B_MN, int EPI>
-int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st,
-                  const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr, const PosEpi* pe = nullptr) {
+int gemm_dispatch_impl(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st,
+                       const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr, const PosEpi* pe = nullptr) {
   bool aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && (lda % 8 == 0) && (ldb % 8 == 0) &&
                  ((uintptr_t)out % 16 == 0) && (ldo % 8 == 0) && (N % 8 == 0) && M > 0 && N > 0 && K > 0;
   // MN-major operands are fetched in 64-wide chunks along M/N: the global extent must be a multiple of 8 elements
@@ -1012,6 +1013,85 @@ int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int
   if (pairs) return launch_tc2<A_MN, B_MN, EPI, 1>(tmA, tmB, tmD, g, st);
   if (BN == 256) return launch_tc<256, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
   return launch_tc<128, A_MN, B_MN, EPI>(tmA, tmB, tmD, g, st);
+}
+
+// ------------------------------------------------------------------ plan cache + autotune (ENTROPY_AUTOTUNE, train/gemm.cuh)
+// The reference times the library's top-k algorithms per GEMM shape and caches the winner.  Here the candidates are
+// this file's own forms: tile (CTA-pair tiles forced / chosen by the cost model / 1-CTA kernel), order of the tiles
+// in flight (M first / N first), epilogue (TMA store or reduce / coalesced stores by the warps) and, for the fp32
+// add-reduce products, stream-K on / off and its grouping.  With autotuning on, the first call of a shape outside
+// graph capture runs every candidate a few times on the call's own operands (add-reduce products into a scratch
+// output), keeps the fastest in a per-process cache, and every call of that shape then runs with its plan.
+struct GemmPlan { int tile, order, epi, streamk, skg; float us; };
+int g_autotune = 0;
+static std::map<std::array<int, 7>, GemmPlan> g_plans;
+static std::mutex g_plans_mu;
+struct PlanScope {      // applies a plan to the tuning globals for one dispatch
+  int pairs, small, order, epi, sk, skg;
+  explicit PlanScope(const GemmPlan& p) : pairs(g_use_pairs), small(g_small_tiles), order(g_tile_order), epi(g_epi_mode), sk(g_streamk), skg(g_sk_groups) {
+    g_use_pairs = p.tile != 2; g_small_tiles = p.tile == 1; g_tile_order = p.order; g_epi_mode = p.epi; g_streamk = p.streamk; g_sk_groups = p.skg;
+  }
+  ~PlanScope() { g_use_pairs = pairs; g_small_tiles = small; g_tile_order = order; g_epi_mode = epi; g_streamk = sk; g_sk_groups = skg; }
+};
+template <bool A_MN, bool B_MN, int EPI>
+int gemm_dispatch(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st,
+                  const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr, const PosEpi* pe = nullptr) {
+  if (!g_autotune || g_force_simt) return gemm_dispatch_impl<A_MN, B_MN, EPI>(out, ldo, A, lda, B, ldb, M, N, K, st, rope, swi, pe);
+  const std::array<int, 7> key = {(A_MN ? 4 : 0) | (B_MN ? 2 : 0) | (EPI == EPI_F32_ADD ? 1 : 0), M, N, K,
+                                  (rope ? 1 : 0) | (swi ? 2 : 0) | (pe ? 4 : 0), ldo, lda * 131 + ldb};
+  GemmPlan plan{};
+  bool have = false;
+  {
+    std::lock_guard<std::mutex> lk(g_plans_mu);
+    auto it = g_plans.find(key);
+    if (it != g_plans.end()) { plan = it->second; have = true; }
+  }
+  if (!have) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return gemm_dispatch_impl<A_MN, B_MN, EPI>(out, ldo, A, lda, B, ldb, M, N, K, st, rope, swi, pe);   // no timing inside a capture
+    }
+    void* tune_out = out;
+    void* scratch = nullptr;
+    if (EPI == EPI_F32_ADD) {      // the candidates must not add to the caller's accumulator
+      if (cudaMalloc(&scratch, (size_t)M * ldo * sizeof(float)) != cudaSuccess) { cudaGetLastError(); scratch = nullptr; }
+      tune_out = scratch;
+    }
+    plan = GemmPlan{1, 0, 1, 1, 1, 0.f};       // the static heuristics
+    if (tune_out != nullptr) {
+      cudaEvent_t e0, e1;
+      cudaEventCreate(&e0);
+      cudaEventCreate(&e1);
+      float best = 1e30f;
+      const bool fixed_epi = rope || swi || pe;      // these epilogues exist in one form only
+      for (int tile = 0; tile < (fixed_epi ? 1 : 3); tile++)
+        for (int order = 1; order <= 2; order++)
+          for (int epi = fixed_epi ? 1 : 0; epi < 2; epi++)
+            for (int sk = (EPI == EPI_F32_ADD) ? 0 : 1; sk < 2; sk++)
+              for (int skg = (EPI == EPI_F32_ADD && sk) ? 0 : 1; skg < 2; skg++) {
+                GemmPlan c{fixed_epi ? 1 : tile, order, epi, sk, skg, 0.f};
+                PlanScope scope(c);
+                if (gemm_dispatch_impl<A_MN, B_MN, EPI>(tune_out, ldo, A, lda, B, ldb, M, N, K, st, rope, swi, pe) != 0) { cudaGetLastError(); continue; }
+                cudaEventRecord(e0, st);
+                int rc = 0;
+                for (int i = 0; i < 3 && rc == 0; i++) rc = gemm_dispatch_impl<A_MN, B_MN, EPI>(tune_out, ldo, A, lda, B, ldb, M, N, K, st, rope, swi, pe);
+                cudaEventRecord(e1, st);
+                if (cudaEventSynchronize(e1) != cudaSuccess || rc != 0) { cudaGetLastError(); continue; }
+                float ms = 0.f;
+                cudaEventElapsedTime(&ms, e0, e1);
+                c.us = ms * 1000.f / 3.f;
+                if (c.us < best) { best = c.us; plan = c; }
+              }
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+    }
+    if (scratch) cudaFree(scratch);
+    std::lock_guard<std::mutex> lk(g_plans_mu);
+    g_plans[key] = plan;
+  }
+  PlanScope scope(plan);
+  return gemm_dispatch_impl<A_MN, B_MN, EPI>(out, ldo, A, lda, B, ldb, M, N, K, st, rope, swi, pe);
 }
 
 // 8-bit forward product on the CTA-pair kernel: out[M,N] (bf16) = out_scale * x8[M,K] . W8[N,K]^T, operands E4M3 bytes.
@@ -1233,6 +1313,20 @@ MLB_API void mlb_gemm_set_max_ctas(int n) { g_max_ctas = n; }
 MLB_API void mlb_gemm_set_splits(int n) { g_force_splits = n; }
 MLB_API void mlb_gemm_use_3d_maps(int on) { g_use_3d = on; }
 MLB_API void mlb_gemm_use_pairs(int on) { g_use_pairs = on; }
+// 1: time this file's GEMM forms per shape on first use and keep the fastest (see GemmPlan); 0: static heuristics
+MLB_API void mlb_gemm_autotune(int on) { g_autotune = on; }
+MLB_API int mlb_gemm_plan_count() { std::lock_guard<std::mutex> lk(g_plans_mu); return (int)g_plans.size(); }
+// plan i of the cache in iteration order: {form bits, M, N, K, tile, order, epilogue, stream-K, groups, microseconds}
+MLB_API int mlb_gemm_plan_get(int i, int* out10) {
+  std::lock_guard<std::mutex> lk(g_plans_mu);
+  if (i < 0 || i >= (int)g_plans.size()) return -1;
+  auto it = g_plans.begin();
+  std::advance(it, i);
+  out10[0] = it->first[0]; out10[1] = it->first[1]; out10[2] = it->first[2]; out10[3] = it->first[3];
+  out10[4] = it->second.tile; out10[5] = it->second.order; out10[6] = it->second.epi; out10[7] = it->second.streamk;
+  out10[8] = it->second.skg; out10[9] = (int)it->second.us;
+  return 0;
+}
 MLB_API void mlb_gemm_epilogue_mode(int m) { g_epi_mode = m; }
 MLB_API void mlb_gemm_small_tiles(int on) { g_small_tiles = on; }
 MLB_API void mlb_gemm_streamk(int on) { g_streamk = on; }

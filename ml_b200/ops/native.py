@@ -87,6 +87,32 @@ def lib():
     return L
 
 
+def gemm_autotune(on: bool):
+    """Per-shape plan cache of the GEMMs (the reference's ENTROPY_AUTOTUNE, train/gemm.cuh): on = the first call of a shape
+    outside graph capture times this library's own forms (tile, tile order, epilogue, stream-K) and later calls use the
+    fastest; off = static heuristics."""
+    L = lib()
+    L.mlb_gemm_autotune.argtypes = [_i32]
+    L.mlb_gemm_autotune.restype = None
+    L.mlb_gemm_autotune(1 if on else 0)
+
+
+def gemm_plans():
+    """The plan cache as a list of dicts (form: bit 2 = A MN-major, bit 1 = B MN-major, bit 0 = fp32 add-reduce)."""
+    L = lib()
+    L.mlb_gemm_plan_count.restype = _i32
+    L.mlb_gemm_plan_count.argtypes = []
+    L.mlb_gemm_plan_get.restype = _i32
+    L.mlb_gemm_plan_get.argtypes = [_i32, C.POINTER(C.c_int)]
+    out = []
+    buf = (C.c_int * 10)()
+    for i in range(L.mlb_gemm_plan_count()):
+        if L.mlb_gemm_plan_get(i, buf) == 0:
+            out.append(dict(form=buf[0], M=buf[1], N=buf[2], K=buf[3], tile=("pair", "model", "1cta")[buf[4]],
+                            order=buf[5], epilogue=("tma", "warps")[buf[6]], streamk=buf[7], groups=buf[8], us=buf[9]))
+    return out
+
+
 def attn_dynamic(on: bool):
     """The persistent attention kernels draw their work items from a counter in device memory (on) instead of following
     the table built on the host (off, the default; ENTROPY_ATTN_DYNAMIC=1 turns it on at load).  Measured: alone the

@@ -51,6 +51,9 @@ class Trainer:
                        opt_hyper=self.hyper, rank=rank,
                        fused_bf16=fused_bf16 or bool(self.run.extra.get("fused_bf16", False)))
         self.accum = self.ddp.accum
+        if self.device.type == "cuda" and "ENTROPY_AUTOTUNE" in self.run.extra.get("explicit", ()):
+            from .ops import native as _native
+            _native.gemm_autotune(bool(self.run.autotune))       # plans are timed in the eager step before graph capture
         self.t = 1
         self._probe = None         # (event after the last backward, event after the gradient step) of probe_grad_step
         self.skip_adamw = False    # ablation: leave the optimizer out (single GPU, library-collective mode)

@@ -711,3 +711,33 @@ def test_vit_encoder_gpu_against_cpu():
     for (n, p), (_, q) in zip(cpu.named_parameters(), gpu.named_parameters()):
         d = (q.grad.float().cpu() - p.grad).norm() / (p.grad.norm() + 1e-8)
         assert d.item() < 8e-2, (n, d.item())
+
+
+def test_gemm_autotune_plan_cache():
+    """Autotune on: the first call of a shape times this library's forms and caches a plan, later calls reuse it; every
+    form computes the same product (bf16 outputs within rounding of each other, the add-reduce form really adds once)."""
+    torch.manual_seed(5)
+    M, N, K = 1024, 768, 512
+    x, W, dy = rnd(M, K), rnd(N, K, scale=K ** -0.5), rnd(M, N)
+    base, dW0 = torch.empty(M, N, device=dev(), dtype=torch.bfloat16), torch.ones(N, K, device=dev())
+    nat().linear_fwd(base, x, W)
+    nat().linear_dw(dW0, dy, x)
+    n0 = len(nat().gemm_plans())
+    nat().gemm_autotune(True)
+    try:
+        out, dW = torch.empty_like(base), torch.ones(N, K, device=dev())
+        nat().linear_fwd(out, x, W)
+        nat().linear_dw(dW, dy, x)              # tuned into a scratch output: the accumulator gets the product exactly once
+        plans = nat().gemm_plans()
+        assert len(plans) == n0 + 2
+        nat().linear_fwd(out, x, W)
+        assert len(nat().gemm_plans()) == n0 + 2
+    finally:
+        nat().gemm_autotune(False)
+    e = torch.empty(M, N, device=dev())
+    ref.linear_fwd(e, x, W)
+    close(out, e, name="tuned forward")
+    edw = torch.ones(N, K, device=dev())
+    ref.linear_dw(edw, dy, x)
+    close(dW, edw, rtol=2e-2, atol=2e-2, name="tuned dW")
+    close(dW0, edw, rtol=2e-2, atol=2e-2, name="untuned dW")
