@@ -107,7 +107,8 @@ class RunConfig:
     train_graph: int = 0
     skip_adamw: int = 0
     nccl_id: str = ""
-    attn: str = "flash"            # reference names: cudnn|mat|flash|packed ; here flash == tcgen05 kernel
+    attn: str = "cudnn"            # reference names: cudnn (its default) | mat | packed | flash (its scalar flash kernel); here every
+                                   # name but an explicit "flash" runs the tcgen05 kernels, "flash" the scalar flash kernels
     rms_atomic: int = 1
     ce_online: int = 1
     ce_threads: int = 256
@@ -158,7 +159,7 @@ class RunConfig:
             train_graph=env_int("ENTROPY_TRAIN_GRAPH", 0, e),
             skip_adamw=env_int("ENTROPY_SKIP_ADAMW", 0, e),
             nccl_id=env_str("ENTROPY_NCCL_ID", "", e),
-            attn=env_str("ENTROPY_ATTN", "flash", e),
+            attn=env_str("ENTROPY_ATTN", "cudnn", e),
             rms_atomic=env_int("ENTROPY_RMS_ATOMIC", 1, e),
             ce_online=env_int("ENTROPY_CE_ONLINE", 1, e),
             ce_threads=env_int("ENTROPY_CE_THREADS", 256, e),
@@ -193,7 +194,7 @@ class RunConfig:
 
     # Knobs of the reference that are read here but change nothing in this design, with the reason.
     NO_EFFECT = {
-        "ENTROPY_ATTN": "one tcgen05 flash-attention kernel replaces the cudnn / mat / packed / flash back ends",
+        "ENTROPY_ATTN": "the tcgen05 flash-attention kernels replace the cudnn / mat / packed back ends (only 'flash' selects another one: the scalar flash kernels)",
         "ENTROPY_RMS_ATOMIC": "RMSNorm backward is one deterministic kernel (no atomic / atomic-free pair)",
         "ENTROPY_CE_ONLINE": "cross-entropy is always the fused online-softmax kernel",
         "ENTROPY_CE_THREADS": "the cross-entropy kernel's block size is fixed",
@@ -208,7 +209,8 @@ class RunConfig:
 
     def ineffective_knobs(self):
         """[(name, reason)] for every knob that was set explicitly and has no effect here."""
-        return sorted((k, v) for k, v in self.NO_EFFECT.items() if k in self.extra.get("explicit", ()))
+        return sorted((k, v) for k, v in self.NO_EFFECT.items() if k in self.extra.get("explicit", ())
+                      and not (k == "ENTROPY_ATTN" and self.attn == "flash"))
 
     def warn_ineffective(self, log=None):
         """One line naming the knobs that are set but do nothing in this design (printed once by the CLI modes)."""

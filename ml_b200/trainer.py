@@ -51,6 +51,9 @@ class Trainer:
                        opt_hyper=self.hyper, rank=rank,
                        fused_bf16=fused_bf16 or bool(self.run.extra.get("fused_bf16", False)))
         self.accum = self.ddp.accum
+        if self.device.type == "cuda" and "ENTROPY_ATTN" in self.run.extra.get("explicit", ()):
+            from .ops import native as _native
+            _native.lib().mlb_attn_force_simt(1 if self.run.attn == "flash" else 0)     # the reference's scalar flash back end
         if self.device.type == "cuda" and "ENTROPY_AUTOTUNE" in self.run.extra.get("explicit", ()):
             from .ops import native as _native
             _native.gemm_autotune(bool(self.run.autotune))       # plans are timed in the eager step before graph capture

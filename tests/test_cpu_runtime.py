@@ -221,6 +221,9 @@ def test_plan_and_lmce_and_knobs(capsys):
     assert lmce_check.main(env={"ENTROPY_CHECK_BT": "5", "ENTROPY_CHECK_V": "33", "ENTROPY_CHECK_CHUNK": "4"}) == 0
     r = RunConfig.from_env({"ENTROPY_ACCUM": "16", "ENTROPY_BF16_REDUCE": "0", "ENTROPY_ATTN": "mat", "ENTROPY_PEAK_TFLOPS": "989"})
     assert (r.accum, r.bf16_reduce, r.attn, r.peak_tflops) == (16, 0, "mat", 989.0)
+    # "mat" has no counterpart here and is reported; "flash" selects the scalar flash kernels and is not
+    assert [k for k, _ in r.ineffective_knobs()] == ["ENTROPY_ATTN"]
+    assert RunConfig.from_env({"ENTROPY_ATTN": "flash"}).ineffective_knobs() == []
     c = Config.from_env({"ENTROPY_V": "50304", "ENTROPY_T": "2048"})
     assert (c.V, c.T, c.C) == (50304, 2048, 768)
 
