@@ -2263,11 +2263,23 @@ MLB_API long mlb_attn_bwd_scratch_bytes(int B, int T, int H, int hd) {
 // single-kernel backward runs; without it the two-kernel backward (dK/dV kernel + dQ kernel) runs.  If cosT/sinT are given, RoPE's
 // backward rotation is applied to dQ and dK before they are stored (tensor-core path only; returns 1 if it was applied,
 // 0 if the caller still has to rotate, <0 or a CUDA error code > 1 on failure).
+// have_delta != 0: `delta` already holds rowsum(dO * O) per (sample, head, query) - written by the epilogue of the GEMM
+// that produced dO (mlb_linear_dx_delta) - and the pass over dO and O is skipped.
+static int attn_bwd_impl(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, void* dq_part,
+                         int B, int T, int H, int hd, const float* cosT, const float* sinT, int have_delta, cudaStream_t st);
 MLB_API int mlb_attn_bwd(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, void* dq_part,
                          int B, int T, int H, int hd, const float* cosT, const float* sinT, cudaStream_t st) {
+  return attn_bwd_impl(dqkv, dout, qkv, out, lse, delta, dq_part, B, T, H, hd, cosT, sinT, 0, st);
+}
+MLB_API int mlb_attn_bwd_have_delta(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta,
+                                    void* dq_part, int B, int T, int H, int hd, const float* cosT, const float* sinT, cudaStream_t st) {
+  return attn_bwd_impl(dqkv, dout, qkv, out, lse, delta, dq_part, B, T, H, hd, cosT, sinT, 1, st);
+}
+static int attn_bwd_impl(void* dqkv, const void* dout, const void* qkv, const void* out, const float* lse, float* delta, void* dq_part,
+                         int B, int T, int H, int hd, const float* cosT, const float* sinT, int have_delta, cudaStream_t st) {
   const int C = H * hd;
   const float scale = 1.0f / sqrtf((float)hd);
-  {
+  if (!have_delta) {
     const long heads = (long)B * T * H;
     const int gsz = hd / 8;
     const bool vec = (hd % 8 == 0) && heads * gsz < (1L << 31) && gsz <= 32 && (gsz & (gsz - 1)) == 0 && ((uintptr_t)dout % 16 == 0) && ((uintptr_t)out % 16 == 0);

@@ -83,6 +83,12 @@ struct GemmArgs {
   // [pos_period, N] bf16 (the vision tower's patch embedding: positions repeat every n_patch rows)
   const bf16* pos;
   int pos_period;
+  // optional row-dot in the bf16 epilogue (pair kernel, the attention output projection's input gradient D = dO[M, H*64]):
+  // dl_out[(b*H + h)*T + t] = sum over the 64 columns of head h of D[row, .] * dl_o[row, .] with row = b*T + t, taken on the
+  // fp32 accumulators - the "delta" term of the attention backward, which otherwise costs a pass over dO and O
+  const bf16* dl_o;
+  float* dl_out;
+  int dl_T, dl_H;
 };
 
 // Work items of one cluster of the pair kernel.  Static mode: items c, c + nclusters, ... of tiles x splits.
@@ -422,7 +428,7 @@ __device__ __forceinline__ void pack64(const uint32_t (&r)[32], const uint32_t (
 // scales) on their way out.  Everything else - tiles, ring, barriers, epilogue - is shared with the bf16 form.
 // POS: the learned-position add of GemmArgs::pos is compiled in (its own instantiation, so that the register allocation of
 // the plain kernels is not affected).
-template <bool A_MN, bool B_MN, int EPI, int EMODE, bool F8 = false, bool POS = false>
+template <bool A_MN, bool B_MN, int EPI, int EMODE, bool F8 = false, bool POS = false, bool DELTA = false>
 __global__ void __cluster_dims__(2, 1, 1) __maxnreg__(160)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmD, const GemmArgs g) {
@@ -612,6 +618,24 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
               }
             }
+          }
+          if (DELTA && g.dl_o != nullptr && m0 + lane < g.M) {
+            // the slab is one head of this lane's row: dot of its 64 fp32 values with the forward pass's attention output
+            const bf16* orow = g.dl_o + (size_t)(m0 + lane) * g.N + col0;
+            float acc_d = 0.f;
+#pragma unroll
+            for (int v = 0; v < 8; v++) {
+              const uint4 ov = __ldg(reinterpret_cast<const uint4*>(orow) + v);
+              const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+              const uint32_t* d = (v < 4) ? &r[v * 8] : &r2[(v - 4) * 8];
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                acc_d = fmaf(__uint_as_float(d[2 * e]), __uint_as_float(ow[e] << 16), acc_d);
+                acc_d = fmaf(__uint_as_float(d[2 * e + 1]), __uint_as_float(ow[e] & 0xffff0000u), acc_d);
+              }
+            }
+            const int row = m0 + lane, bb = row / g.dl_T;
+            g.dl_out[((size_t)bb * g.dl_H + (col0 >> 6)) * g.dl_T + (row - bb * g.dl_T)] = acc_d;
           }
           if (g.cosT != nullptr && col0 < g.rope_cols) {   // warp-uniform; the slab is one head: r = first half, r2 = second
             const int t = (m0 + lane) % g.rope_T;
@@ -865,10 +889,10 @@ int g_sk_groups = 1;         // tuning hook: 0 = stream-K without groups (one li
 int g_streamk = 1;           // tuning hook: weight-gradient products cut into equal k-block ranges per cluster
 int g_epi_mode = 1;          // tuning hook: pair kernel's epilogue, 0 = TMA store / reduce, 1 = coalesced stores by the warps
 int g_small_tiles = 1;       // tuning hook: 0 = never trade the CTA-pair tile for 128 x 128 tiles on small problems
-template <bool A_MN, bool B_MN, int EPI, int EMODE, bool POS = false>
+template <bool A_MN, bool B_MN, int EPI, int EMODE, bool POS = false, bool DELTA = false>
 int launch_tc2(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmD, const GemmArgs& g, cudaStream_t st) {
   using Gemm2Smem = Gemm2Smem<EMODE>;
-  auto kern = gemm_tc2_kernel<A_MN, B_MN, EPI, EMODE, false, POS>;
+  auto kern = gemm_tc2_kernel<A_MN, B_MN, EPI, EMODE, false, POS, DELTA>;
   static int max_clusters = -1;
   if (max_clusters < 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Smem::TOTAL);
@@ -915,9 +939,11 @@ int launch_tc_gather(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUten
 struct RopeEpi { const float* cosT; const float* sinT; int T, cols; };
 struct SwigluEpi { bf16* out; int I; };
 struct PosEpi { const bf16* pos; int period; };
+struct DeltaEpi { const bf16* o; float* out; int T, H; };
 template <bool A_MN, bool B_MN, int EPI>
 int gemm_dispatch_impl(void* out, int ldo, const bf16* A, int lda, const bf16* B, int ldb, int M, int N, int K, cudaStream_t st,
-                       const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr, const PosEpi* pe = nullptr) {
+                       const RopeEpi* rope = nullptr, const SwigluEpi* swi = nullptr, const PosEpi* pe = nullptr,
+                       const DeltaEpi* dl = nullptr) {
   bool aligned = ((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && (lda % 8 == 0) && (ldb % 8 == 0) &&
                  ((uintptr_t)out % 16 == 0) && (ldo % 8 == 0) && (N % 8 == 0) && M > 0 && N > 0 && K > 0;
   // MN-major operands are fetched in 64-wide chunks along M/N: the global extent must be a multiple of 8 elements
@@ -932,6 +958,9 @@ int gemm_dispatch_impl(void* out, int ldo, const bf16* A, int lda, const bf16* B
   if (pe && (g_force_simt || !aligned || get_encode() == nullptr || g_epi_mode != 1 || !g_use_pairs || EPI != EPI_BF16 || M <= 128 ||
              N <= 128 || N % 8 != 0 || ((uintptr_t)pe->pos & 15) || pe->period < 1))
     return -7;
+  if (dl && (g_force_simt || !aligned || get_encode() == nullptr || g_epi_mode != 1 || !g_use_pairs || A_MN || !B_MN || EPI != EPI_BF16 ||
+             M <= 128 || N <= 128 || N != dl->H * 64 || M % dl->T != 0 || ((uintptr_t)dl->o & 15)))
+    return -7;                                                                       // caller runs the separate kernels
   if (g_force_simt || !aligned || get_encode() == nullptr) {
     dim3 grid(ceil_div_i(N, 64), ceil_div_i(M, 64));
     long sam = A_MN ? 1 : lda, sak = A_MN ? lda : 1, sbn = B_MN ? 1 : ldb, sbk = B_MN ? ldb : 1;
@@ -945,7 +974,7 @@ int gemm_dispatch_impl(void* out, int ldo, const bf16* A, int lda, const bf16* B
   // tile pays ~25 % more per k-block for its operand traffic.
   int BN = (N > 128) ? 256 : 128;
   bool pairs = g_use_pairs && BN == 256 && M > 128;   // 256 x 256 tile shared by a CTA pair
-  if (pairs && !rope && !swi && !pe && g_small_tiles) {
+  if (pairs && !rope && !swi && !pe && !dl && g_small_tiles) {
     const long kb = ceil_div_i(K, BK);
     const long pt = (long)ceil_div_i(M, 256) * ceil_div_i(N, 256), ct = (long)ceil_div_i(M, 128) * ceil_div_i(N, 128);
     const long pc = pair_clusters(), sm = g_max_ctas > 0 ? g_max_ctas : num_sms();
@@ -966,6 +995,7 @@ int gemm_dispatch_impl(void* out, int ldo, const bf16* A, int lda, const bf16* B
   g.rope_T = rope ? rope->T : 1; g.rope_cols = rope ? rope->cols : 0;
   g.sw_out = swi ? swi->out : nullptr; g.sw_I = swi ? swi->I : 0; g.out_scale = 1.f;
   g.pos = pe ? pe->pos : nullptr; g.pos_period = pe ? pe->period : 1;
+  g.dl_o = dl ? dl->o : nullptr; g.dl_out = dl ? dl->out : nullptr; g.dl_T = dl ? dl->T : 1; g.dl_H = dl ? dl->H : 1;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, pairs ? 256 : BM);
   g.tiles_n = swi ? swi->I / 128 : ceil_div_i(N, BN);
@@ -1008,6 +1038,9 @@ int gemm_dispatch_impl(void* out, int ldo, const bf16* A, int lda, const bf16* B
   if (!tmA || !tmB || !tmD) return -2;
   if constexpr (!A_MN && !B_MN && EPI == EPI_BF16) {
     if (pairs && pe) return launch_tc2<false, false, EPI_BF16, 1, true>(tmA, tmB, tmD, g, st);
+  }
+  if constexpr (!A_MN && B_MN && EPI == EPI_BF16) {
+    if (dl) return pairs ? launch_tc2<false, true, EPI_BF16, 1, false, true>(tmA, tmB, tmD, g, st) : -7;
   }
   if (pairs && g_epi_mode == 0) return launch_tc2<A_MN, B_MN, EPI, 0>(tmA, tmB, tmD, g, st);
   if (pairs) return launch_tc2<A_MN, B_MN, EPI, 1>(tmA, tmB, tmD, g, st);
@@ -1107,7 +1140,7 @@ int gemm_fp8_dispatch(void* out, int ldo, const uint8_t* A, int lda, const uint8
   g.cosT = rope ? rope->cosT : nullptr; g.sinT = rope ? rope->sinT : nullptr;
   g.rope_T = rope ? rope->T : 1; g.rope_cols = rope ? rope->cols : 0;
   g.sw_out = swi ? swi->out : nullptr; g.sw_I = swi ? swi->I : 0; g.out_scale = out_scale;
-  g.pos = nullptr; g.pos_period = 1;
+  g.pos = nullptr; g.pos_period = 1; g.dl_o = nullptr; g.dl_out = nullptr; g.dl_T = 1; g.dl_H = 1;
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, 256);
   g.tiles_n = swi ? swi->I / 128 : ceil_div_i(N, 256);
@@ -1194,6 +1227,15 @@ MLB_API int mlb_linear_fwd_posembed(void* out, const void* x, const void* W, con
 MLB_API int mlb_linear_dx(void* dx, const void* dout, const void* W, int M, int N, int K, int lddx, int lddo, int ldw, cudaStream_t st) {
   return gemm_dispatch<false, true, EPI_BF16>(dx, lddx, (const bf16*)dout, lddo, (const bf16*)W, ldw, M, K, N, st);
 }
+// dx = dout . W as mlb_linear_dx, for the attention output projection: also delta[b, h, t] = sum_c dx[row, h*64 + c] * o[row, h*64 + c]
+// (row = b*T + t, o = the forward pass's attention output [M, H*64]) from the epilogue.  -7: the shape does not take this
+// path, nothing was launched.
+MLB_API int mlb_linear_dx_delta(void* dx, const void* dout, const void* W, const void* o, float* delta, int T, int H, int M, int N, int K,
+                                int lddx, int lddo, int ldw, cudaStream_t st) {
+  if (K != H * 64 || lddx != K) return -7;
+  DeltaEpi e{(const bf16*)o, delta, T, H};
+  return gemm_dispatch_impl<false, true, EPI_BF16>(dx, lddx, (const bf16*)dout, lddo, (const bf16*)W, ldw, M, K, N, st, nullptr, nullptr, nullptr, &e);
+}
 // dW[N,K] += dout[M,N]^T . x[M,K]   (GEMM view: D[N,K], reduction M; both operands MN-major)
 MLB_API int mlb_linear_dw(void* dW, const void* dout, const void* x, int M, int N, int K, int lddw, int lddo, int ldx, cudaStream_t st) {
   return gemm_dispatch<true, true, EPI_F32_ADD>(dW, lddw, (const bf16*)dout, lddo, (const bf16*)x, ldx, N, K, M, st);
@@ -1236,7 +1278,7 @@ MLB_API int mlb_linear_fwd_gather(void* out, const void* x, int M, int N, int K,
   g.out = out; g.M = M; g.N = N; g.K = K; g.ldo = ldo;
   g.tiles_m = ceil_div_i(M, BM); g.tiles_n = ceil_div_i(N, BN); g.kb_total = ceil_div_i(K, BK);
   g.splits = 1; g.kb_per_split = g.kb_total; g.a3d = g.b3d = 0; g.streamk = 0; g.sk_group = 1; g.sk_group_m = 0; g.nt_fast = 0;
-  g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0; g.sw_out = nullptr; g.sw_I = 0; g.out_scale = 1.f; g.pos = nullptr; g.pos_period = 1;
+  g.cosT = g.sinT = nullptr; g.rope_T = 1; g.rope_cols = 0; g.sw_out = nullptr; g.sw_I = 0; g.out_scale = 1.f; g.pos = nullptr; g.pos_period = 1; g.dl_o = nullptr; g.dl_out = nullptr; g.dl_T = 1; g.dl_H = 1;
   GatherArgs ga;
   ga.src = (const uint4* const*)src_ptrs; ga.dst = (uint4*)unit_dst; ga.shard_vec = shard_elems / 8;
   ga.b_lo_vec = w_off_elems / 8; ga.b_hi_vec = (w_off_elems + (long)N * K) / 8; ga.b_row_vec = K / 8;

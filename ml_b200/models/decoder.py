@@ -27,6 +27,7 @@ import os as _os
 # head size 64 on the GPU: RoPE in the QKV GEMM's epilogue instead of a separate in-place pass (MLB_NO_ROPE_FUSE=1: off)
 FUSE_ROPE_INTO_QKV = _os.environ.get("MLB_NO_ROPE_FUSE", "0") != "1"
 FUSE_SWIGLU_INTO_GU = _os.environ.get("MLB_NO_SWIGLU_FUSE", "0") != "1"
+FUSE_DELTA_INTO_DX = _os.environ.get("MLB_NO_DELTA_FUSE", "0") != "1"
 
 
 class GPT:
@@ -423,14 +424,18 @@ class GPT:
                                 sl(self.rstd2[l]), dresid)
             self._mark("B_norm")
             ops.linear_dw(self.G(o.o, C, C), dresid1, sl(self.atty[l]))
-            ops.linear_dx(datty, dresid1, self.P(o.o, C, C))
+            # head size 64: the attention backward's delta = rowsum(dO * O) comes out of the epilogue of the product that makes dO
+            have_delta = (FUSE_DELTA_INTO_DX and hd == 64 and self.cp is None and dresid1.is_cuda and
+                          ops.native_module().linear_dx_delta(datty, dresid1, self.P(o.o, C, C), sl(self.atty[l]), B, T, H))
+            if not have_delta:
+                ops.linear_dx(datty, dresid1, self.P(o.o, C, C))
             want_rope = "rope" not in self.skip
             if self.cp is not None:
                 self.cp.attn_bwd(self, l, dqkv, datty, B)
                 fused = False
             else:
                 fused = ops.attn_bwd(dqkv, datty, sl(self.qkv[l]), sl(self.atty[l]), self.lse[l][:B], B, T, H, hd,
-                                     rope=(self.cos, self.sin) if want_rope else None)
+                                     rope=(self.cos, self.sin) if want_rope else None, have_delta=bool(have_delta))
             if want_rope and not fused:
                 ops.rope_bwd(dqkv, self.cos, self.sin, B, T, H, hd)
             self._mark("B_attn")

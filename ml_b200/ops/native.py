@@ -288,8 +288,28 @@ FUSED_ATTN_BWD = True   # head size 64: single fused backward kernel (False = se
 FUSED_ATTN_BWD_MAX_SCRATCH = 4 << 30   # bytes of dQ partials (grows with B*T*T) the fused backward may use
 
 
-def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
+def linear_dx_delta(dx, dout, W, o, B, T, H):
+    """dx[M, C] = dout[M, N] . W[N, C] for the attention output projection (C = H * 64) with the attention backward's
+    delta[b, h, t] = sum_c dx[row, h*64 + c] * o[row, h*64 + c] written by the same kernel's epilogue into the scratch that
+    attn_bwd(..., have_delta=True) reads.  Returns False when the shape does not take that path (nothing was launched)."""
+    M, N = dout.shape
+    Cc = W.shape[1]
+    if Cc != H * 64 or M != B * T or dx.stride(0) != Cc or o.stride(0) != Cc:
+        return False
+    delta = scratch("attn_delta", B * H * T, torch.float32, dout.device)
+    fn = lib().mlb_linear_dx_delta
+    fn.argtypes = [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]
+    fn.restype = _i32
+    rc = fn(_b(dx), _b(dout), _b(W), _b(o), _f(delta), T, H, M, N, Cc, dx.stride(0), dout.stride(0), W.stride(0), _st())
+    if rc == -7:
+        return False
+    _chk(rc, "linear_dx_delta")
+    return True
+
+
+def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None, have_delta=False):
     """rope=(cos, sin): ask the kernel to apply RoPE's backward rotation to dQ/dK in its epilogue.
+    have_delta: linear_dx_delta has just written this call's delta term, the pass over dO and O is left out.
     Returns True if it did (tensor-core path), False if the caller still has to call rope_bwd."""
     delta = scratch("attn_delta", B * H * T, torch.float32, qkv.device)
     acc = None
@@ -302,9 +322,14 @@ def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
             acc = scratch(("attn_dq_part", nbytes), nbytes // 2, torch.bfloat16, qkv.device).data_ptr()
     cp = _f(rope[0]) if rope is not None else None
     sp = _f(rope[1]) if rope is not None else None
-    rc = lib().mlb_attn_bwd(_b(dqkv), _b(dout), _b(qkv), _b(out), _f(lse), _f(delta), acc, B, T, H, hd, cp, sp, _st())
+    fn = lib().mlb_attn_bwd
+    if have_delta:
+        fn = lib().mlb_attn_bwd_have_delta
+        fn.argtypes = lib().mlb_attn_bwd.argtypes
+        fn.restype = _i32
+    rc = fn(_b(dqkv), _b(dout), _b(qkv), _b(out), _f(lse), _f(delta), acc, B, T, H, hd, cp, sp, _st())
     global LAUNCHES
-    LAUNCHES += 3
+    LAUNCHES += 2 if have_delta else 3
     if rc < 0 or rc > 1:
         raise RuntimeError(f"attn_bwd failed: code {rc}")
     return rc == 1

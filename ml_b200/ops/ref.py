@@ -166,7 +166,7 @@ def attn_fwd(out, lse, qkv, B, T, H, hd):
     out.view(B, T, H, hd).copy_(o.permute(0, 2, 1, 3))
 
 
-def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None):
+def attn_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd, rope=None, have_delta=False):
     """Returns False: RoPE's backward rotation is never fused here (the caller applies rope_bwd)."""
     v5 = qkv.view(B, T, 3, H, hd)
     q, k, v = (_f(v5[:, :, i]).permute(0, 2, 1, 3) for i in range(3))

@@ -741,3 +741,30 @@ def test_gemm_autotune_plan_cache():
     ref.linear_dw(edw, dy, x)
     close(dW, edw, rtol=2e-2, atol=2e-2, name="tuned dW")
     close(dW0, edw, rtol=2e-2, atol=2e-2, name="untuned dW")
+
+
+@pytest.mark.parametrize("B,T,H,N", [(2, 256, 4, 256), (3, 200, 3, 192), (16, 1024, 12, 768)])
+def test_linear_dx_delta_epilogue(B, T, H, N):
+    """Input gradient of the attention output projection with delta = rowsum(dO * O) per head from its epilogue: the
+    product against the fp32 oracle, delta against the fp32 row dots, and the attention backward fed with that delta
+    against the one that runs its own pass over dO and O."""
+    torch.manual_seed(B * T + H)
+    C, hd, M = H * 64, 64, B * T
+    dy, W = rnd(M, N), rnd(N, C, scale=N ** -0.5)
+    qkv = rnd(M, 3 * C)
+    out = torch.empty(M, C, device=dev(), dtype=torch.bfloat16)
+    lse = torch.empty(B, H, T, device=dev())
+    nat().attn_fwd(out, lse, qkv, B, T, H, hd)
+    dx = torch.full((M, C), float("nan"), device=dev(), dtype=torch.bfloat16)
+    assert nat().linear_dx_delta(dx, dy, W, out, B, T, H)
+    e = torch.empty(M, C, device=dev())
+    ref.linear_dx(e, dy, W)
+    close(dx, e, name="dx")
+    delta = nat().scratch("attn_delta", B * H * T, torch.float32, torch.device(dev()))[:B * H * T].view(B, H, T).clone()
+    ed = (e.view(B, T, H, 64) * out.float().view(B, T, H, 64)).sum(-1).permute(0, 2, 1)
+    close(delta, ed, rtol=1e-2, atol=1e-2, name="delta", fro=5e-3)
+    a = torch.empty(M, 3 * C, device=dev(), dtype=torch.bfloat16)
+    b = torch.empty_like(a)
+    nat().attn_bwd(a, dx, qkv, out, lse, B, T, H, hd, have_delta=True)
+    nat().attn_bwd(b, dx, qkv, out, lse, B, T, H, hd)
+    close(a, b.float(), name="attention backward with the epilogue's delta", fro=6e-3)
