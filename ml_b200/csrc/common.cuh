@@ -43,16 +43,23 @@ __device__ __forceinline__ void mlb_pdl_sync() {
 #ifdef __CUDACC__
 #include <cstdlib>
 #include <utility>
-inline bool mlb_pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("MLB_PDL");     // off unless MLB_PDL=1: measured slower inside a captured step (20.6 vs 19.8 ms)
-    on = (e != nullptr && e[0] == '1') ? 1 : 0;
+// MLB_PDL: 0 (default) no kernel starts early; 1 every kernel launched through mlb_launch / mlb_launch_tmem may (measured
+// slower inside a captured step, 20.6 vs 19.8 ms: a kernel that allocates tensor memory or most of an SM's shared memory
+// cannot become resident next to its predecessor anyway, and one that does delays it); 2 only the kernels launched
+// through mlb_launch - the element-wise ones, whose CTAs fit beside a tensor-core kernel's (also measured slower in the
+// captured step: 18.1-18.5 against 17.75 ms, the early-resident CTAs take issue slots and registers from the kernel
+// they wait for).
+inline int mlb_pdl_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("MLB_PDL");
+    mode = (e != nullptr && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
   }
-  return on != 0;
+  return mode;
 }
+inline bool mlb_pdl_enabled() { return mlb_pdl_mode() == 1; }
 template <typename... KArgs, typename... Args>
-inline cudaError_t mlb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+inline cudaError_t mlb_launch_attr(bool early, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -62,8 +69,17 @@ inline cudaError_t mlb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = mlb_pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = early ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t mlb_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  return mlb_launch_attr(mlb_pdl_mode() != 0, kern, grid, block, smem, st, std::forward<Args>(args)...);
+}
+// for kernels that allocate tensor memory (GEMMs, attention): they start early only in mode 1
+template <typename... KArgs, typename... Args>
+inline cudaError_t mlb_launch_tmem(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  return mlb_launch_attr(mlb_pdl_mode() == 1, kern, grid, block, smem, st, std::forward<Args>(args)...);
 }
 #endif
 

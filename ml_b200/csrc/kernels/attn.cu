@@ -2203,12 +2203,12 @@ MLB_API int mlb_attn_fwd(void* out, float* lse, const void* qkv, int B, int T, i
   {                                                                                                                            \
     static int once = set_smem(attn_fwd_rows_tc_kernel<MODE>, Fwd2Smem::TOTAL);                                          \
     (void)once;                                                                                                                \
-    mlb_launch(attn_fwd_rows_tc_kernel<MODE>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, *to, a);              \
+    mlb_launch_tmem(attn_fwd_rows_tc_kernel<MODE>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, *to, a);              \
   }
       if (a.dynamic && g_fwd_rows != 1 && g_fwd_rows != 2) {
         static int once = set_smem(attn_fwd_rows_tc_kernel<3, true>, Fwd2Smem::TOTAL);
         (void)once;
-        mlb_launch(attn_fwd_rows_tc_kernel<3, true>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, *to, a);
+        mlb_launch_tmem(attn_fwd_rows_tc_kernel<3, true>, grid2, dim3(FWD2_THREADS), Fwd2Smem::TOTAL, st, *tm, *to, a);
       } else {
         switch (g_fwd_rows) {
           case 1: MLB_FWD2(1) break;
@@ -2309,8 +2309,8 @@ static int attn_bwd_impl(void* dqkv, const void* dout, const void* qkv, const vo
       dim3 grid_f((unsigned)(n_items < sms ? n_items : sms));
       a.dynamic = g_attn_dynamic;
       a.sched = (n_items > sms && !a.dynamic) ? attn_schedule(1, B, H, T, (int)grid_f.x, &a.sched_stride, st) : nullptr;
-      if (a.dynamic) mlb_launch(attn_bwd_fused_tc_kernel<true>, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
-      else mlb_launch(attn_bwd_fused_tc_kernel<false>, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
+      if (a.dynamic) mlb_launch_tmem(attn_bwd_fused_tc_kernel<true>, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
+      else mlb_launch_tmem(attn_bwd_fused_tc_kernel<false>, grid_f, dim3(BWDF_THREADS), BwdFusedSmem::TOTAL, st, *tq, *td, *tpart, a);
       const long groups = (long)B * T * H * (hd / 32);
       mlb_launch(attn_dq_finish_k, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, st, (bf16*)dqkv, (const bf16*)dq_part, (long)B * T, T, H, hd, scale, cosT, sinT);
       cudaError_t e = cudaGetLastError();

@@ -877,7 +877,7 @@ int launch_tc(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap*
   int cap = g_max_ctas > 0 ? g_max_ctas : num_sms();
   int grid = total < cap ? total : cap;
   GatherArgs none{};
-  return (int)mlb_launch(kern, dim3(grid), dim3(GEMM_THREADS), GemmSmem<BN>::TOTAL, st, *tmA, *tmB, *tmD, g, none);
+  return (int)mlb_launch_tmem(kern, dim3(grid), dim3(GEMM_THREADS), GemmSmem<BN>::TOTAL, st, *tmA, *tmB, *tmD, g, none);
 }
 
 // CTA-pair kernel: one cluster of two CTAs per SM pair; the grid is sized from the number of clusters that can be
@@ -910,7 +910,7 @@ int launch_tc2(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap
   int cap = max_clusters;
   if (g_max_ctas > 0 && g_max_ctas / 2 < cap) cap = g_max_ctas / 2 > 0 ? g_max_ctas / 2 : 1;
   int clusters = total < cap ? total : cap;
-  return (int)mlb_launch(kern, dim3(2 * clusters), dim3(GEMM2_THREADS), Gemm2Smem::TOTAL, st, *tmA, *tmB, *tmD, g);
+  return (int)mlb_launch_tmem(kern, dim3(2 * clusters), dim3(GEMM2_THREADS), Gemm2Smem::TOTAL, st, *tmA, *tmB, *tmD, g);
 }
 int pair_clusters() { return (g_max_ctas > 0 ? g_max_ctas : num_sms()) / 2; }
 
@@ -1170,7 +1170,7 @@ int gemm_fp8_dispatch(void* out, int ldo, const uint8_t* A, int lda, const uint8
   int cap = max_clusters;
   if (g_max_ctas > 0 && g_max_ctas / 2 < cap) cap = g_max_ctas / 2 > 0 ? g_max_ctas / 2 : 1;
   int clusters = total < cap ? total : cap;
-  return (int)mlb_launch(kern, dim3(2 * clusters), dim3(GEMM2_THREADS), Smem::TOTAL, st, *tmA, *tmB, *tmD, g);
+  return (int)mlb_launch_tmem(kern, dim3(2 * clusters), dim3(GEMM2_THREADS), Smem::TOTAL, st, *tmA, *tmB, *tmD, g);
 }
 
 }  // namespace
