@@ -1,4 +1,4 @@
-"""Sequence (context) parallelism, all-to-all flavour: every rank of a group holds a contiguous 1/cp slice of each
+"""Sequence (context) parallelism.  All-to-all flavour (`SequenceParallel`, the default): every rank of a group holds a contiguous 1/cp slice of each
 sequence for everything that is token-local (embedding, norms, linears, SwiGLU, LM head, loss) and switches to a
 head-sharded layout - all tokens, H/cp heads - around attention, so the attention kernels run unchanged on full
 sequences and the causal work is balanced over the ranks by construction.
@@ -8,6 +8,9 @@ sequences and the causal work is balanced over the ranks by construction.
 
 The reference has no sequence sharding of any kind (its long-sequence story is flash attention's O(T) memory and the
 chunked LM head: train/gpt.cu:196-239); this is added capability, not a rebuild of reference code.
+
+The ring flavour (`RingSequenceParallel`, `make_model(..., ring=True)`) keeps the layout and sends the key / value chunks
+around instead; see its docstring.
 
 Use `make_model(cfg, B, device, group)`: it returns a `GPT` whose cfg.T is the LOCAL length, whose RoPE tables are this
 rank's rows of the full tables, and whose attention calls go through the `SequenceParallel` object attached as
@@ -91,8 +94,117 @@ class SequenceParallel:
         self.heads_to_seq(dqkv, dqh, B, 3)
 
 
-def make_model(cfg: Config, B: int, device="cpu", group=None, dtype: Optional[torch.dtype] = None, **gpt_kwargs):
-    """A `GPT` over this rank's slice of the sequences (cfg.T is the full length; the model's own cfg.T becomes T/cp)."""
+class RingSequenceParallel:
+    """Ring flavour: the layout never changes - every rank keeps its T/cp tokens and all heads - and the key / value
+    chunks travel around the ring instead (point-to-point sends to the next rank, cp - 1 hops).  At hop k rank r holds
+    the chunk of rank s = r - k: for s < r its queries attend to all of it (the unmasked attention kernels), for
+    s == r causally (the training kernels), for s > r not at all (those keys lie in the future), and the partial outputs
+    are merged by their log-sum-exp.  Backward runs the flash backward per chunk pair with the MERGED statistics (the
+    row's final log-sum-exp and the final output in the delta term), adds the query gradients locally and lets the
+    key / value gradients travel with their chunk until they are home.  Needs no divisibility of the head count and
+    moves 2/3 of an all-to-all's bytes per hop, but the causal work is uneven (rank r works on r + 1 chunk pairs);
+    a zig-zag token order that would even it out is not implemented."""
+
+    def __init__(self, cfg_full: Config, B: int, device, dtype, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if cfg_full.T % self.world:
+            raise ValueError(f"sequence parallelism over {self.world} ranks needs T={cfg_full.T} divisible by it")
+        self.T, self.Tl, self.H, self.hd = cfg_full.T, cfg_full.T // self.world, cfg_full.H, cfg_full.hd
+        self.Hc = cfg_full.H          # (all heads stay local; kept for symmetry with SequenceParallel)
+        self.B = B
+        C, n, L = cfg_full.C, B * self.Tl, cfg_full.L
+        e = lambda *s: torch.empty(*s, dtype=dtype, device=device)
+        f = lambda *s: torch.empty(*s, dtype=torch.float32, device=device)
+        self.lse_tot = [f(B, self.H, self.Tl) for _ in range(L)]
+        self.kv = [e(n, 2 * C), e(n, 2 * C)]              # the travelling chunk: current and incoming
+        self.dkv = [f(n, 2 * C), f(n, 2 * C)]            # its gradient, travelling with it (fp32: summed over the hops)
+        self.pair, self.dpair = e(n, 3 * C), e(n, 3 * C)   # [Q of this rank | K, V of the visiting chunk] and its gradient
+        self.o_part, self.lse_part = e(n, C), f(B, self.H, self.Tl)
+        self.o_acc, self.dq_acc = f(n, C), f(n, C)
+
+    def _rotate(self, send, recv):
+        """send -> next rank, recv <- previous rank (lists of tensors, matched pairwise)."""
+        nxt, prv = (self.rank + 1) % self.world, (self.rank - 1) % self.world
+        if self.group is not None:
+            nxt, prv = dist.get_global_rank(self.group, nxt), dist.get_global_rank(self.group, prv)
+        ops_ = []
+        for s_, r_ in zip(send, recv):
+            ops_.append(dist.P2POp(dist.isend, s_, nxt, self.group))
+            ops_.append(dist.P2POp(dist.irecv, r_, prv, self.group))
+        for w in dist.batch_isend_irecv(ops_):
+            w.wait()
+
+    def _weights(self, lse_old, lse_new, B):
+        """exp(lse_old - lse_new) as a [B*Tl, H, 1] factor for rows of a [B*Tl, H*hd] tensor."""
+        return torch.exp(lse_old - lse_new).permute(0, 2, 1).reshape(B * self.Tl, self.H, 1)
+
+    def attn_fwd(self, model, l: int, atty: torch.Tensor, qkv: torch.Tensor, B: int):
+        n, C, W, r = B * self.Tl, self.H * self.hd, self.world, self.rank
+        cur = 0
+        self.kv[cur][:n].copy_(qkv[:, C:])
+        lse_tot = self.lse_tot[l][:B]
+        first = True
+        for k in range(W):
+            s = (r - k) % W
+            if s <= r:
+                o, lse = self.o_part[:n], self.lse_part[:B]
+                if s == r:
+                    ops.attn_fwd(o, lse, qkv, B, self.Tl, self.H, self.hd)
+                else:
+                    pair = self.pair[:n]
+                    pair[:, :C].copy_(qkv[:, :C])
+                    pair[:, C:].copy_(self.kv[cur][:n])
+                    ops.attn_bidir_fwd(o, lse, pair, B, self.Tl, self.H, self.hd)
+                if first:
+                    self.o_acc[:n].copy_(o)
+                    lse_tot.copy_(lse)
+                    first = False
+                else:
+                    new = torch.logaddexp(lse_tot, lse)
+                    acc = self.o_acc[:n].view(n, self.H, self.hd)
+                    acc.mul_(self._weights(lse_tot, new, B)).add_(o.float().view(n, self.H, self.hd) * self._weights(lse, new, B))
+                    lse_tot.copy_(new)
+            if k < W - 1:
+                self._rotate([self.kv[cur][:n]], [self.kv[1 - cur][:n]])
+                cur = 1 - cur
+        atty.copy_(self.o_acc[:n])
+
+    def attn_bwd(self, model, l: int, dqkv: torch.Tensor, datty: torch.Tensor, B: int):
+        """dqkv (RoPE's backward rotation NOT applied: the caller rotates with its local tables)."""
+        n, C, W, r = B * self.Tl, self.H * self.hd, self.world, self.rank
+        qkv, atty, lse_tot = model.qkv[l][:n], model.atty[l][:n], self.lse_tot[l][:B]
+        cur = 0
+        self.kv[cur][:n].copy_(qkv[:, C:])
+        self.dkv[cur][:n].zero_()
+        self.dq_acc[:n].zero_()
+        d = self.dpair[:n]
+        for k in range(W):
+            s = (r - k) % W
+            if s <= r:
+                if s == r:
+                    ops.attn_bwd(d, datty, qkv, atty, lse_tot, B, self.Tl, self.H, self.hd, rope=None)
+                else:
+                    pair = self.pair[:n]
+                    pair[:, :C].copy_(qkv[:, :C])
+                    pair[:, C:].copy_(self.kv[cur][:n])
+                    ops.attn_bidir_bwd(d, datty, pair, atty, lse_tot, B, self.Tl, self.H, self.hd)
+                self.dq_acc[:n].add_(d[:, :C])
+                self.dkv[cur][:n].add_(d[:, C:])
+            # the chunk and its gradient move on; after the last hop the gradient is back at its owner
+            if k < W - 1:
+                self._rotate([self.kv[cur][:n], self.dkv[cur][:n]], [self.kv[1 - cur][:n], self.dkv[1 - cur][:n]])
+            else:
+                self._rotate([self.dkv[cur][:n]], [self.dkv[1 - cur][:n]])
+            cur = 1 - cur
+        dqkv[:, :C].copy_(self.dq_acc[:n])
+        dqkv[:, C:].copy_(self.dkv[cur][:n])
+
+
+def make_model(cfg: Config, B: int, device="cpu", group=None, dtype: Optional[torch.dtype] = None, ring: bool = False, **gpt_kwargs):
+    """A `GPT` over this rank's slice of the sequences (cfg.T is the full length; the model's own cfg.T becomes T/cp).
+    ring=True: key / value chunks travel around a ring (RingSequenceParallel) instead of the all-to-all layout switch."""
     from ..models import GPT
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -103,7 +215,7 @@ def make_model(cfg: Config, B: int, device="cpu", group=None, dtype: Optional[to
     cos, sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, m.device)
     Tl = local.T
     m.cos, m.sin = cos[rank * Tl:(rank + 1) * Tl].contiguous(), sin[rank * Tl:(rank + 1) * Tl].contiguous()
-    m.cp = SequenceParallel(cfg, B, m.device, m.dtype, group)
+    m.cp = (RingSequenceParallel if ring else SequenceParallel)(cfg, B, m.device, m.dtype, group)
     return m
 
 

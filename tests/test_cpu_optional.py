@@ -2,6 +2,7 @@
 block, logger."""
 import io
 
+import pytest
 import torch
 
 from ml_b200.models.moe import MoEBlock
@@ -295,3 +296,45 @@ def test_expert_parallel_moe_two_ranks_equals_single_process_block():
     """, world=2)
     for rc, o in outs:
         assert rc == 0 and "EP_OK" in o, o[-2000:]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_ring_sequence_parallel_model_equals_full_sequence_model(world):
+    """Ring flavour: key / value chunks travel rank to rank, partial outputs merged by their log-sum-exp, key / value
+    gradients travel home with their chunk: loss and every gradient equal the single-process model on the full
+    sequences (2 ranks, and 3 ranks with a head count the all-to-all flavour could not split)."""
+    from tests.test_cpu_ddp import run_ranks
+    outs = run_ranks("""
+        import torch, torch.distributed as dist
+        from ml_b200 import Config
+        from ml_b200.models import GPT
+        from ml_b200.parallel.bootstrap import init_distributed, shutdown
+        from ml_b200.parallel import cp
+        from ml_b200.utils.rng import Stream
+        torch.set_num_threads(2)
+        rank, world, local, dev = init_distributed("cpu")
+        cfg = Config(V=97, C=48, L=2, H=4, I=80, T=48)
+        B = 2
+        ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+        tgt[::5] = -1
+        valid = int((tgt >= 0).sum())
+        full = GPT(cfg, B)
+        full.init_weights(1234)
+        full.forward(ids)
+        full.backward(ids, tgt, valid_tokens=valid)
+        m = cp.make_model(cfg, B, "cpu", ring=True)
+        assert m.cfg.T == cfg.T // world and isinstance(m.cp, cp.RingSequenceParallel)
+        m.init_weights(1234)
+        li, lt = cp.local_tokens(ids, B, cfg.T, rank, world), cp.local_tokens(tgt, B, cfg.T, rank, world)
+        m.forward(li)
+        m.backward(li, lt, valid_tokens=valid)
+        cp.reduce_grads(m)
+        loss = cp.global_mean_loss(m, valid)
+        print("RING", abs(loss - full.mean_loss(valid_tokens=valid)), float((m.grads - full.grads).abs().max()),
+              float(full.grads.abs().max()), flush=True)
+        shutdown()
+    """, world=world)
+    assert all(rc == 0 for rc, _ in outs), outs
+    for _, o in outs:
+        line = [l for l in o.splitlines() if l.startswith("RING")][0].split()
+        assert float(line[1]) < 1e-5 and float(line[2]) < 2e-5 and float(line[3]) > 1e-3

@@ -56,6 +56,49 @@ def test_sequence_parallel_two_gpus_equals_full_sequence_model():
     assert float(line[1]) < 2e-2 and float(line[2]) < 3e-2 and line[3] == "0", line
 
 
+@needs2
+def test_ring_sequence_parallel_two_gpus_equals_full_sequence_model():
+    """The ring flavour on NCCL point-to-point: each rank keeps half of every sequence and all heads, the key / value chunk
+    of the other rank visits it (unmasked attention kernels for the earlier chunk, the tcgen05 causal kernels for its
+    own), against the one-GPU model on the full sequences."""
+    rc, out = _torchrun("""
+        import torch, torch.distributed as dist
+        from ml_b200 import Config
+        from ml_b200.models import GPT
+        from ml_b200.parallel.bootstrap import init_distributed
+        from ml_b200.parallel import cp
+        from ml_b200.utils.rng import Stream
+        from ml_b200.ops import native
+        rank, world, local, dev = init_distributed()
+        native.lib().mlb_gemm_set_splits(1)
+        cfg = Config(V=512, C=256, L=2, H=4, I=512, T=256)
+        B = 2
+        ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+        tgt[::5] = -1
+        valid = int((tgt >= 0).sum())
+        ids, tgt = ids.to(dev), tgt.to(dev)
+        full = GPT(cfg, B, dev)
+        full.init_weights(1234)
+        full.forward(ids)
+        full.backward(ids, tgt, valid_tokens=valid)
+        m = cp.make_model(cfg, B, dev, ring=True)
+        m.init_weights(1234)
+        li, lt = cp.local_tokens(ids, B, cfg.T, rank, world), cp.local_tokens(tgt, B, cfg.T, rank, world)
+        m.forward(li)
+        m.backward(li, lt, valid_tokens=valid)
+        cp.reduce_grads(m)
+        torch.cuda.synchronize()
+        loss = cp.global_mean_loss(m, valid)
+        rel = float((m.grads - full.grads).norm() / full.grads.norm())
+        if rank == 0:
+            print("RING", abs(loss - full.mean_loss(valid_tokens=valid)), rel, native.get_error(), flush=True)
+        dist.barrier(); dist.destroy_process_group()
+    """, 2)
+    assert rc == 0, out[-3000:]
+    line = [l for l in out.splitlines() if l.startswith("RING")][0].split()
+    assert float(line[1]) < 2e-2 and float(line[2]) < 3e-2 and line[3] == "0", line
+
+
 def _mode_losses(args, nproc, env_extra, tmp_path):
     body = textwrap.dedent("""
         import sys
