@@ -507,7 +507,12 @@ __global__ void swiglu_bwd_scalar_k(bf16* dgu, const bf16* dout, const bf16* gu,
 // ------------------------------------------------------------------ fused cross-entropy (one block per row, in place)
 // pass 1: online max / sum-exp over the row; pass 2 (row is L2-resident): logits <- (softmax - onehot) * dscale.
 // Rows with tgt < 0: loss 0, gradient row zeroed.
-__global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, bf16* __restrict__ logits,
+__device__ __forceinline__ float exp2f_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__global__ void __launch_bounds__(512, 4) ce_fwd_bwd_k(float* __restrict__ losses, bf16* __restrict__ logits,
                                                     const int* __restrict__ tgt, int V, long ld, float dscale) {
   mlb_pdl_sync();
   __shared__ float red[32];
@@ -525,16 +530,25 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, 
     return;
   }
   float m = -INFINITY, s = 0.f;
+  constexpr float L2E = 1.4426950408889634f;
   if (vec) {
-    for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) {
-      float x[8];
-      load8(z + i, x);
-      float mx = x[0];
+    // two 16-byte loads in flight per thread and step (one row per block: the bytes in flight are what keeps HBM busy);
+    // exponentials as exp2 of one fused multiply-add
+    const int step = blockDim.x * 8;
+    for (int i = threadIdx.x * 8; i < V; i += 2 * step) {
+      const bool two = i + step < V;
+      const uint4 ra = *reinterpret_cast<const uint4*>(z + i);
+      const uint4 rb = two ? *reinterpret_cast<const uint4*>(z + i + step) : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);   // -inf
+      float xa[8], xb[8];
+      unpack8(ra, xa);
+      unpack8(rb, xb);
+      float mx = fmaxf(xa[0], xb[0]);
 #pragma unroll
-      for (int j = 1; j < 8; j++) mx = fmaxf(mx, x[j]);
-      if (mx > m) { s *= __expf(m - mx); m = mx; }
+      for (int j = 1; j < 8; j++) mx = fmaxf(mx, fmaxf(xa[j], xb[j]));
+      if (mx > m) { s *= exp2f_fast((m - mx) * L2E); m = mx; }
+      const float nm = -m * L2E;
 #pragma unroll
-      for (int j = 0; j < 8; j++) s += __expf(x[j] - m);
+      for (int j = 0; j < 8; j++) s += exp2f_fast(fmaf(xa[j], L2E, nm)) + exp2f_fast(fmaf(xb[j], L2E, nm));
     }
   } else {
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -551,12 +565,24 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_k(float* __restrict__ losses, 
   if (threadIdx.x == 0) losses[row] = __logf(S) + M - zt;
   const float inv = dscale / S;
   if (vec) {
-    for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) {
-      float x[8];
-      load8(z + i, x);
+    const int step = blockDim.x * 8;
+    const float nM = -M * L2E;
+    for (int i = threadIdx.x * 8; i < V; i += 2 * step) {
+      const bool two = i + step < V;
+      const uint4 ra = *reinterpret_cast<const uint4*>(z + i);
+      uint4 rb = make_uint4(0, 0, 0, 0);
+      if (two) rb = *reinterpret_cast<const uint4*>(z + i + step);
+      float xa[8], xb[8];
+      unpack8(ra, xa);
+      unpack8(rb, xb);
 #pragma unroll
-      for (int j = 0; j < 8; j++) x[j] = __expf(x[j] - M) * inv - ((i + j == t) ? dscale : 0.f);
-      store8(z + i, x);
+      for (int j = 0; j < 8; j++) xa[j] = exp2f_fast(fmaf(xa[j], L2E, nM)) * inv - ((i + j == t) ? dscale : 0.f);
+      store8(z + i, xa);
+      if (two) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) xb[j] = exp2f_fast(fmaf(xb[j], L2E, nM)) * inv - ((i + step + j == t) ? dscale : 0.f);
+        store8(z + i + step, xb);
+      }
     }
   } else {
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
