@@ -87,7 +87,9 @@ __global__ void gather_prefix_k(bf16* __restrict__ dprefix, const bf16* __restri
 
 // ------------------------------------------------------------------ RMSNorm forward (one warp per row)
 // ADD: resid = a + b is stored (bf16) and the norm is taken over the un-rounded fp32 sum.
-template <bool ADD, bool F8 = false>
+// NV > 0: C = NV * 256; the whole row (and the weight vector's slice) is fetched with all loads in flight at once and
+// stays in registers between the sum of squares and the scaling - one read of the inputs instead of two.
+template <bool ADD, bool F8 = false, int NV = 0>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, float* __restrict__ rstd, bf16* __restrict__ resid,
                                                      const bf16* __restrict__ a, const bf16* __restrict__ b,
                                                      const bf16* __restrict__ w, long rows, int C, float eps,
@@ -99,6 +101,44 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(bf16* __restrict__ out, flo
   const bf16* pa = a + row * C;
   const bf16* pb = ADD ? b + row * C : nullptr;
   float ss = 0.f;
+  if constexpr (NV > 0) {
+    uint4 ra[NV], rb[NV], rw[NV];
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int i = (v * 32 + lane) * 8;
+      ra[v] = *reinterpret_cast<const uint4*>(pa + i);
+      if (ADD) rb[v] = *reinterpret_cast<const uint4*>(pb + i);
+      rw[v] = __ldg(reinterpret_cast<const uint4*>(w + i));
+    }
+    float x[NV][8];
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      unpack8(ra[v], x[v]);
+      if (ADD) {
+        float y[8];
+        unpack8(rb[v], y);
+#pragma unroll
+        for (int j = 0; j < 8; j++) x[v][j] += y[j];
+        store8(resid + row * C + (v * 32 + lane) * 8, x[v]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) ss += x[v][j] * x[v][j];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / (float)C + eps);
+    if (lane == 0) rstd[row] = r;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int i = (v * 32 + lane) * 8;
+      float ww[8];
+      unpack8(rw[v], ww);
+#pragma unroll
+      for (int j = 0; j < 8; j++) x[v][j] = x[v][j] * r * ww[j];
+      store8(out + row * C + i, x[v]);
+      if (F8) store8_e4m3(out8 + row * C + i, x[v], s8);
+    }
+    return;
+  }
   if ((C & 7) == 0) {
     for (int i = lane * 8; i < C; i += 256) {
       float x[8];
@@ -949,15 +989,31 @@ MLB_API int mlb_gather_prefix_grad(void* dprefix, const void* dresid, int B, int
   mlb_launch(gather_prefix_k, dim3(gs(n, 256)), dim3(256), 0, st, (bf16*)dprefix, (const bf16*)dresid, B, T, n_pre, C);
   LAUNCH_RET;
 }
+// Rows of 256, 512, 768 or 1024 aligned columns take the register-resident form of the kernel.
+template <bool ADD, bool F8>
+static void rmsnorm_fwd_launch(void* out, void* out8, float* rstd, void* resid, const void* a, const void* b, const void* w, long rows, int C,
+                               float eps, float scale, cudaStream_t st) {
+  const bool al = (C % 256 == 0) && C <= 1024 && ((uintptr_t)a % 16 == 0) && (!ADD || ((uintptr_t)b % 16 == 0 && (uintptr_t)resid % 16 == 0)) &&
+                  ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0) && (!F8 || (uintptr_t)out8 % 8 == 0);
+#define RF(NV)                                                                                                                   \
+  mlb_launch(rmsnorm_fwd_k<ADD, F8, NV>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b, \
+             (const bf16*)w, rows, C, eps, (uint8_t*)out8, scale)
+  switch (al ? C / 256 : 0) {
+    case 1: RF(1); break;
+    case 2: RF(2); break;
+    case 3: RF(3); break;
+    case 4: RF(4); break;
+    default: RF(0); break;
+  }
+#undef RF
+}
 MLB_API int mlb_rmsnorm_fwd(void* out, float* rstd, const void* x, const void* w, long rows, int C, float eps, cudaStream_t st) {
-  mlb_launch(rmsnorm_fwd_k<false>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w, rows, C, eps,
-             (uint8_t*)nullptr, 1.f);
+  rmsnorm_fwd_launch<false, false>(out, nullptr, rstd, nullptr, x, nullptr, w, rows, C, eps, 1.f, st);
   LAUNCH_RET;
 }
 MLB_API int mlb_add_rmsnorm_fwd(void* resid, void* out, float* rstd, const void* a, const void* b, const void* w, long rows, int C,
                                 float eps, cudaStream_t st) {
-  mlb_launch(rmsnorm_fwd_k<true>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b, (const bf16*)w,
-                                                   rows, C, eps, (uint8_t*)nullptr, 1.f);
+  rmsnorm_fwd_launch<true, false>(out, nullptr, rstd, resid, a, b, w, rows, C, eps, 1.f, st);
   LAUNCH_RET;
 }
 
@@ -966,14 +1022,12 @@ MLB_API int mlb_add_rmsnorm_fwd(void* resid, void* out, float* rstd, const void*
 // scalar path of the same kernel.
 MLB_API int mlb_rmsnorm_fwd_fp8(void* out, void* out8, float* rstd, const void* x, const void* w, long rows, int C, float eps, float scale,
                                 cudaStream_t st) {
-  mlb_launch(rmsnorm_fwd_k<false, true>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, nullptr, (const bf16*)x, nullptr, (const bf16*)w,
-             rows, C, eps, (uint8_t*)out8, scale);
+  rmsnorm_fwd_launch<false, true>(out, out8, rstd, nullptr, x, nullptr, w, rows, C, eps, scale, st);
   LAUNCH_RET;
 }
 MLB_API int mlb_add_rmsnorm_fwd_fp8(void* resid, void* out, void* out8, float* rstd, const void* a, const void* b, const void* w, long rows,
                                     int C, float eps, float scale, cudaStream_t st) {
-  mlb_launch(rmsnorm_fwd_k<true, true>, dim3(gs(rows, 8)), dim3(256), 0, st, (bf16*)out, rstd, (bf16*)resid, (const bf16*)a, (const bf16*)b,
-             (const bf16*)w, rows, C, eps, (uint8_t*)out8, scale);
+  rmsnorm_fwd_launch<true, true>(out, out8, rstd, resid, a, b, w, rows, C, eps, scale, st);
   LAUNCH_RET;
 }
 MLB_API int mlb_swiglu_fwd_fp8(void* out, void* out8, const void* gu, long rows, int I, float scale, cudaStream_t st) {
