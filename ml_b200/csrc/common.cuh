@@ -28,6 +28,13 @@ enum : int {
   MLB_API void mlb_clear_error_##tag() {                                       \
     int v = 0;                                                                 \
     cudaMemcpyToSymbol(g_mlb_error, &v, sizeof(int));                          \
+  }                                                                            \
+  /* the word copied to (pinned) host memory behind the work already in `st`: no synchronisation of its own */ \
+  MLB_API int mlb_read_error_async_##tag(int* host_dst, cudaStream_t st) {     \
+    void* p = nullptr;                                                         \
+    cudaError_t e = cudaGetSymbolAddress(&p, g_mlb_error);                     \
+    if (e != cudaSuccess) return (int)e;                                       \
+    return (int)cudaMemcpyAsync(host_dst, p, sizeof(int), cudaMemcpyDeviceToHost, st); \
   }
 static __device__ int g_mlb_error = 0;
 

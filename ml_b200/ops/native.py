@@ -154,6 +154,18 @@ def get_error() -> int:
     return 0
 
 
+def read_errors_async(host_words: torch.Tensor):
+    """The four error words copied into `host_words` (pinned int32[4]) behind the current stream's work, without a
+    synchronisation of their own: a caller that synchronises the stream anyway (to read a loss) checks them for free."""
+    L = lib()
+    base = host_words.data_ptr()
+    for i, tag in enumerate(("gemm", "attn", "elementwise", "comm")):
+        fn = getattr(L, "mlb_read_error_async_" + tag)
+        fn.argtypes = [_vp, _vp]
+        fn.restype = _i32
+        _chk(fn(base + 4 * i, _st()), "read_error_async")
+
+
 def clear_error():
     L = lib()
     for tag in ("gemm", "attn", "elementwise", "comm"):

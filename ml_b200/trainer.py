@@ -58,6 +58,7 @@ class Trainer:
             from .ops import native as _native
             _native.gemm_autotune(bool(self.run.autotune))       # plans are timed in the eager step before graph capture
         self.t = 1
+        self.h_err = None          # pinned copy of the kernels' error words, filled behind every step_host
         self._probe = None         # (event after the last backward, event after the gradient step) of probe_grad_step
         self.skip_adamw = False    # ablation: leave the optimizer out (single GPU, library-collective mode)
         # the vision tower's gradients are data-parallel too (the reference's multimodal modes are single-GPU only)
@@ -202,8 +203,14 @@ class Trainer:
         self.step()
         self.h_loss.copy_(self.d_loss, non_blocking=True)
         if self.device.type == "cuda":
+            # the kernels' error words ride behind the loss: one synchronisation for both
+            from .ops import native
+            if self.h_err is None:
+                self.h_err = torch.zeros(4, dtype=torch.int32).pin_memory()
+            native.read_errors_async(self.h_err)
             torch.cuda.current_stream().synchronize()
-            self._check_kernels()
+            if bool(self.h_err.any()):
+                self._check_kernels()
         return float(self.h_loss[0])
 
     def _check_kernels(self):
