@@ -102,15 +102,20 @@ class RingSequenceParallel:
     are merged by their log-sum-exp.  Backward runs the flash backward per chunk pair with the MERGED statistics (the
     row's final log-sum-exp and the final output in the delta term), adds the query gradients locally and lets the
     key / value gradients travel with their chunk until they are home.  Needs no divisibility of the head count and
-    moves 2/3 of an all-to-all's bytes per hop, but the causal work is uneven (rank r works on r + 1 chunk pairs);
-    a zig-zag token order that would even it out is not implemented."""
+    moves 2/3 of an all-to-all's bytes per hop.  In the plain order the causal work is uneven (rank r works on r + 1
+    chunk pairs); zigzag=True (see __init__) evens it out."""
 
-    def __init__(self, cfg_full: Config, B: int, device, dtype, group=None):
+    def __init__(self, cfg_full: Config, B: int, device, dtype, group=None, zigzag: bool = False):
+        """zigzag=True: every sequence is cut into 2 * cp chunks and rank r keeps chunks r and 2*cp - 1 - r (an early and a
+        late one), which evens out the causal work: besides its own causal attention every rank then runs exactly two
+        half-size unmasked products per hop, whichever rank it is."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        if cfg_full.T % self.world:
-            raise ValueError(f"sequence parallelism over {self.world} ranks needs T={cfg_full.T} divisible by it")
+        if cfg_full.T % (self.world * (2 if zigzag else 1)):
+            raise ValueError(f"sequence parallelism over {self.world} ranks needs T={cfg_full.T} divisible by "
+                             f"{self.world * (2 if zigzag else 1)}")
+        self.zigzag = bool(zigzag) and self.world > 1
         self.T, self.Tl, self.H, self.hd = cfg_full.T, cfg_full.T // self.world, cfg_full.H, cfg_full.hd
         self.Hc = cfg_full.H          # (all heads stay local; kept for symmetry with SequenceParallel)
         self.B = B
@@ -123,6 +128,7 @@ class RingSequenceParallel:
         self.pair, self.dpair = e(n, 3 * C), e(n, 3 * C)   # [Q of this rank | K, V of the visiting chunk] and its gradient
         self.o_part, self.lse_part = e(n, C), f(B, self.H, self.Tl)
         self.o_acc, self.dq_acc = f(n, C), f(n, C)
+        self.half_o = e(n, C)                             # zig-zag backward: a half of the final output, contiguous
 
     def _rotate(self, send, recv):
         """send -> next rank, recv <- previous rank (lists of tensors, matched pairwise)."""
@@ -140,7 +146,78 @@ class RingSequenceParallel:
         """exp(lse_old - lse_new) as a [B*Tl, H, 1] factor for rows of a [B*Tl, H*hd] tensor."""
         return torch.exp(lse_old - lse_new).permute(0, 2, 1).reshape(B * self.Tl, self.H, 1)
 
+    # ------------------------------------------------------------------ zig-zag order: work in half chunks
+    def _half(self, x, i, B):
+        """Rows of local half i (0: the early chunk, 1: the late chunk) of x [B*Tl, cols] as a view [B, h, cols]."""
+        return x.view(B, 2, self.Tl // 2, -1)[:, i]
+
+    def _zz_pairs(self, s):
+        """(query half, key half) pairs that rank r's queries owe the visiting chunk pair of rank s != r: both of its
+        query halves against the early keys (s < r), or its late queries against both key halves (s > r)."""
+        return [(0, 0), (1, 0)] if s < self.rank else [(1, 0), (1, 1)]
+
+    def _zz_fwd(self, model, l, atty, qkv, B):
+        n, C, W, r, h = B * self.Tl, self.H * self.hd, self.world, self.rank, self.Tl // 2
+        nh = B * h
+        cur = 0
+        self.kv[cur][:n].copy_(qkv[:, C:])
+        lse_tot = self.lse_tot[l][:B]
+        # own chunks: the local order is the global order, so this is plain causal attention on the local sequence
+        ops.attn_fwd(self.o_part[:n], lse_tot, qkv, B, self.Tl, self.H, self.hd)
+        self.o_acc[:n].copy_(self.o_part[:n])
+        acc = self.o_acc[:n]
+        for k in range(1, W):
+            self._rotate([self.kv[cur][:n]], [self.kv[1 - cur][:n]])
+            cur = 1 - cur
+            s = (r - k) % W
+            for qi, ki in self._zz_pairs(s):
+                pair, o, lse = self.pair[:nh], self.o_part[:nh], self.lse_part.view(-1)[:B * self.H * h].view(B, self.H, h)
+                pair.view(B, h, 3 * C)[:, :, :C].copy_(self._half(qkv, qi, B)[:, :, :C])
+                pair.view(B, h, 3 * C)[:, :, C:].copy_(self._half(self.kv[cur][:n], ki, B))
+                ops.attn_bidir_fwd(o, lse, pair, B, h, self.H, self.hd)
+                old = lse_tot.view(B, self.H, 2, h)[:, :, qi]
+                new = torch.logaddexp(old, lse)
+                w_old = torch.exp(old - new).permute(0, 2, 1).unsqueeze(-1)           # [B, h, H, 1]
+                w_new = torch.exp(lse - new).permute(0, 2, 1).unsqueeze(-1)
+                a = self._half(acc, qi, B).view(B, h, self.H, self.hd)
+                a.mul_(w_old).add_(o.float().view(B, h, self.H, self.hd) * w_new)
+                old.copy_(new)
+        atty.copy_(acc)
+
+    def _zz_bwd(self, model, l, dqkv, datty, B):
+        n, C, W, r, h = B * self.Tl, self.H * self.hd, self.world, self.rank, self.Tl // 2
+        nh = B * h
+        qkv, atty, lse_tot = model.qkv[l][:n], model.atty[l][:n], self.lse_tot[l][:B]
+        cur = 0
+        self.kv[cur][:n].copy_(qkv[:, C:])
+        d = self.dpair[:n]
+        ops.attn_bwd(d, datty, qkv, atty, lse_tot, B, self.Tl, self.H, self.hd, rope=None)
+        self.dq_acc[:n].copy_(d[:, :C])
+        self.dkv[cur][:n].copy_(d[:, C:])
+        do_h, o_h = self.o_part[:nh], self.half_o[:nh]
+        lse_h = self.lse_part.view(-1)[:B * self.H * h].view(B, self.H, h)
+        for k in range(1, W):
+            self._rotate([self.kv[cur][:n], self.dkv[cur][:n]], [self.kv[1 - cur][:n], self.dkv[1 - cur][:n]])
+            cur = 1 - cur
+            s = (r - k) % W
+            for qi, ki in self._zz_pairs(s):
+                pair, dp = self.pair[:nh], self.dpair[:nh]
+                pair.view(B, h, 3 * C)[:, :, :C].copy_(self._half(qkv, qi, B)[:, :, :C])
+                pair.view(B, h, 3 * C)[:, :, C:].copy_(self._half(self.kv[cur][:n], ki, B))
+                do_h.view(B, h, C).copy_(self._half(datty, qi, B))
+                o_h.view(B, h, C).copy_(self._half(atty, qi, B))
+                lse_h.copy_(lse_tot.view(B, self.H, 2, h)[:, :, qi])
+                ops.attn_bidir_bwd(dp, do_h, pair, o_h, lse_h, B, h, self.H, self.hd)
+                self._half(self.dq_acc[:n], qi, B).add_(dp.view(B, h, 3 * C)[:, :, :C])
+                self._half(self.dkv[cur][:n], ki, B).add_(dp.view(B, h, 3 * C)[:, :, C:])
+        self._rotate([self.dkv[cur][:n]], [self.dkv[1 - cur][:n]])       # one more hop: the gradients are home
+        cur = 1 - cur
+        dqkv[:, :C].copy_(self.dq_acc[:n])
+        dqkv[:, C:].copy_(self.dkv[cur][:n])
+
     def attn_fwd(self, model, l: int, atty: torch.Tensor, qkv: torch.Tensor, B: int):
+        if self.zigzag:
+            return self._zz_fwd(model, l, atty, qkv, B)
         n, C, W, r = B * self.Tl, self.H * self.hd, self.world, self.rank
         cur = 0
         self.kv[cur][:n].copy_(qkv[:, C:])
@@ -173,6 +250,8 @@ class RingSequenceParallel:
 
     def attn_bwd(self, model, l: int, dqkv: torch.Tensor, datty: torch.Tensor, B: int):
         """dqkv (RoPE's backward rotation NOT applied: the caller rotates with its local tables)."""
+        if self.zigzag:
+            return self._zz_bwd(model, l, dqkv, datty, B)
         n, C, W, r = B * self.Tl, self.H * self.hd, self.world, self.rank
         qkv, atty, lse_tot = model.qkv[l][:n], model.atty[l][:n], self.lse_tot[l][:B]
         cur = 0
@@ -202,7 +281,14 @@ class RingSequenceParallel:
         dqkv[:, C:].copy_(self.dkv[cur][:n])
 
 
-def make_model(cfg: Config, B: int, device="cpu", group=None, dtype: Optional[torch.dtype] = None, ring: bool = False, **gpt_kwargs):
+def _zigzag_rows(T: int, rank: int, world: int):
+    """Positions [0, T) that rank `rank` holds in the zig-zag order: chunk rank, then chunk 2*world - 1 - rank."""
+    h = T // (2 * world)
+    return list(range(rank * h, (rank + 1) * h)) + list(range((2 * world - 1 - rank) * h, (2 * world - rank) * h))
+
+
+def make_model(cfg: Config, B: int, device="cpu", group=None, dtype: Optional[torch.dtype] = None, ring: bool = False,
+               zigzag: bool = False, **gpt_kwargs):
     """A `GPT` over this rank's slice of the sequences (cfg.T is the full length; the model's own cfg.T becomes T/cp).
     ring=True: key / value chunks travel around a ring (RingSequenceParallel) instead of the all-to-all layout switch."""
     from ..models import GPT
@@ -214,13 +300,21 @@ def make_model(cfg: Config, B: int, device="cpu", group=None, dtype: Optional[to
     m = GPT(local, B, device, dtype, **gpt_kwargs)
     cos, sin = ops.rope_tables(cfg.T, cfg.hd, cfg.rope_theta, m.device)
     Tl = local.T
+    if ring and zigzag and world > 1:
+        rows = torch.tensor(_zigzag_rows(cfg.T, rank, world), device=cos.device)
+        m.cos, m.sin = cos[rows].contiguous(), sin[rows].contiguous()
+        m.cp = RingSequenceParallel(cfg, B, m.device, m.dtype, group, zigzag=True)
+        return m
     m.cos, m.sin = cos[rank * Tl:(rank + 1) * Tl].contiguous(), sin[rank * Tl:(rank + 1) * Tl].contiguous()
     m.cp = (RingSequenceParallel if ring else SequenceParallel)(cfg, B, m.device, m.dtype, group)
     return m
 
 
-def local_tokens(ids: torch.Tensor, B: int, T: int, rank: int, world: int) -> torch.Tensor:
-    """This rank's slice [B, T/world] of ids [B*T], flattened."""
+def local_tokens(ids: torch.Tensor, B: int, T: int, rank: int, world: int, zigzag: bool = False) -> torch.Tensor:
+    """This rank's slice [B, T/world] of ids [B*T], flattened (zigzag: its early and its late chunk, in that order)."""
+    if zigzag and world > 1:
+        rows = torch.tensor(_zigzag_rows(T, rank, world), device=ids.device)
+        return ids.view(B, T)[:, rows].contiguous().view(-1)
     Tl = T // world
     return ids.view(B, T)[:, rank * Tl:(rank + 1) * Tl].contiguous().view(-1)
 

@@ -298,11 +298,12 @@ def test_expert_parallel_moe_two_ranks_equals_single_process_block():
         assert rc == 0 and "EP_OK" in o, o[-2000:]
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_ring_sequence_parallel_model_equals_full_sequence_model(world):
+@pytest.mark.parametrize("world,zigzag", [(2, False), (3, False), (2, True), (3, True)])
+def test_ring_sequence_parallel_model_equals_full_sequence_model(world, zigzag):
     """Ring flavour: key / value chunks travel rank to rank, partial outputs merged by their log-sum-exp, key / value
     gradients travel home with their chunk: loss and every gradient equal the single-process model on the full
-    sequences (2 ranks, and 3 ranks with a head count the all-to-all flavour could not split)."""
+    sequences (2 ranks, and 3 ranks with a head count the all-to-all flavour could not split); also in the zig-zag token
+    order, where every rank holds an early and a late chunk."""
     from tests.test_cpu_ddp import run_ranks
     outs = run_ranks("""
         import torch, torch.distributed as dist
@@ -322,10 +323,11 @@ def test_ring_sequence_parallel_model_equals_full_sequence_model(world):
         full.init_weights(1234)
         full.forward(ids)
         full.backward(ids, tgt, valid_tokens=valid)
-        m = cp.make_model(cfg, B, "cpu", ring=True)
-        assert m.cfg.T == cfg.T // world and isinstance(m.cp, cp.RingSequenceParallel)
+        zz = ZIGZAG
+        m = cp.make_model(cfg, B, "cpu", ring=True, zigzag=zz)
+        assert m.cfg.T == cfg.T // world and isinstance(m.cp, cp.RingSequenceParallel) and m.cp.zigzag == zz
         m.init_weights(1234)
-        li, lt = cp.local_tokens(ids, B, cfg.T, rank, world), cp.local_tokens(tgt, B, cfg.T, rank, world)
+        li, lt = cp.local_tokens(ids, B, cfg.T, rank, world, zigzag=zz), cp.local_tokens(tgt, B, cfg.T, rank, world, zigzag=zz)
         m.forward(li)
         m.backward(li, lt, valid_tokens=valid)
         cp.reduce_grads(m)
@@ -333,7 +335,7 @@ def test_ring_sequence_parallel_model_equals_full_sequence_model(world):
         print("RING", abs(loss - full.mean_loss(valid_tokens=valid)), float((m.grads - full.grads).abs().max()),
               float(full.grads.abs().max()), flush=True)
         shutdown()
-    """, world=world)
+    """.replace("ZIGZAG", str(bool(zigzag))), world=world)
     assert all(rc == 0 for rc, _ in outs), outs
     for _, o in outs:
         line = [l for l in o.splitlines() if l.startswith("RING")][0].split()

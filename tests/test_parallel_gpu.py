@@ -57,10 +57,11 @@ def test_sequence_parallel_two_gpus_equals_full_sequence_model():
 
 
 @needs2
-def test_ring_sequence_parallel_two_gpus_equals_full_sequence_model():
+@pytest.mark.parametrize("zigzag", [False, True])
+def test_ring_sequence_parallel_two_gpus_equals_full_sequence_model(zigzag):
     """The ring flavour on NCCL point-to-point: each rank keeps half of every sequence and all heads, the key / value chunk
     of the other rank visits it (unmasked attention kernels for the earlier chunk, the tcgen05 causal kernels for its
-    own), against the one-GPU model on the full sequences."""
+    own), against the one-GPU model on the full sequences; also in the zig-zag order (an early and a late chunk per rank)."""
     rc, out = _torchrun("""
         import torch, torch.distributed as dist
         from ml_b200 import Config
@@ -81,9 +82,9 @@ def test_ring_sequence_parallel_two_gpus_equals_full_sequence_model():
         full.init_weights(1234)
         full.forward(ids)
         full.backward(ids, tgt, valid_tokens=valid)
-        m = cp.make_model(cfg, B, dev, ring=True)
+        m = cp.make_model(cfg, B, dev, ring=True, zigzag=ZIGZAG)
         m.init_weights(1234)
-        li, lt = cp.local_tokens(ids, B, cfg.T, rank, world), cp.local_tokens(tgt, B, cfg.T, rank, world)
+        li, lt = cp.local_tokens(ids, B, cfg.T, rank, world, zigzag=ZIGZAG), cp.local_tokens(tgt, B, cfg.T, rank, world, zigzag=ZIGZAG)
         m.forward(li)
         m.backward(li, lt, valid_tokens=valid)
         cp.reduce_grads(m)
@@ -93,7 +94,7 @@ def test_ring_sequence_parallel_two_gpus_equals_full_sequence_model():
         if rank == 0:
             print("RING", abs(loss - full.mean_loss(valid_tokens=valid)), rel, native.get_error(), flush=True)
         dist.barrier(); dist.destroy_process_group()
-    """, 2)
+    """.replace("ZIGZAG", str(bool(zigzag))), 2)
     assert rc == 0, out[-3000:]
     line = [l for l in out.splitlines() if l.startswith("RING")][0].split()
     assert float(line[1]) < 2e-2 and float(line[2]) < 3e-2 and line[3] == "0", line
