@@ -258,6 +258,9 @@ def _train_loop(argv, ddp):
     # topology / precision options of the prototype's command line (csrc/src/main.cu:30-57)
     ap.add_argument("--pp-size", type=int, default=1, help="pipeline stages (1F1B over NCCL point-to-point); world must equal pp-size x tp-size")
     ap.add_argument("--tp-size", type=int, default=1, help="tensor-parallel ranks (column / row parallel linears)")
+    ap.add_argument("--cp-size", type=int, default=1, help="sequence-parallel ranks: every rank keeps 1/N of each sequence (must equal the number of ranks)")
+    ap.add_argument("--cp-mode", default="alltoall", choices=["alltoall", "ring", "zigzag"],
+                    help="sequence parallelism by an all-to-all layout switch around attention, by key/value chunks travelling a ring, or the ring in zig-zag token order")
     ap.add_argument("--microbatches", type=int, default=0, help="micro-batches per optimizer step of the pipeline (default ENTROPY_MICROBATCHES)")
     ap.add_argument("--nodes", type=int, default=1)
     ap.add_argument("--gpus-per-node", type=int, default=0)
@@ -274,7 +277,7 @@ def _train_loop(argv, ddp):
         local = int(os.environ.get("LOCAL_RANK", "0"))
         os.environ["RANK"] = str(a.node_id * a.gpus_per_node + local)
         os.environ["WORLD_SIZE"] = str(a.nodes * a.gpus_per_node)
-    if a.pp_size > 1 or a.tp_size > 1 or a.microbatches > 0:
+    if a.pp_size > 1 or a.tp_size > 1 or a.cp_size > 1 or a.microbatches > 0:
         return _train_loop_model_parallel(a)
     if ddp:
         rank, world, local, dev = init_distributed()
@@ -414,7 +417,8 @@ def _train_loop(argv, ddp):
 
 
 def _train_loop_model_parallel(a):
-    """`train_ddp --pp-size P` / `--tp-size T`: the model is cut over the ranks instead of replicated.
+    """`train_ddp --pp-size P` / `--tp-size T` / `--cp-size S`: the model (or every sequence) is cut over the ranks instead of replicated.
+    Sequence parallel: every rank keeps 1/S of each sequence (ml_b200.parallel.cp.CPTrainer, --cp-mode alltoall | ring | zigzag).
     Pipeline: rank = stage, 1F1B over NCCL point-to-point (ml_b200.parallel.pp); every rank reads the same token windows
     (the first stage uses the ids, the last the targets); the last stage's loss is what is printed.
     Tensor parallel: every rank holds a slice of each block's heads and MLP columns (ml_b200.parallel.tp.TPDecoder)."""
@@ -431,13 +435,17 @@ def _train_loop_model_parallel(a):
         cfg.T = a.seq_len
     run = RunConfig.from_env()
     B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
-    if a.pp_size * a.tp_size != world:
-        sys.exit(f"--pp-size {a.pp_size} x --tp-size {a.tp_size} must equal the number of ranks ({world}); "
+    if a.pp_size * a.tp_size * a.cp_size != world:
+        sys.exit(f"--pp-size {a.pp_size} x --tp-size {a.tp_size} x --cp-size {a.cp_size} must equal the number of ranks ({world}); "
                  "data-parallel replicas of a model-parallel group are not built")
-    if a.pp_size > 1 and a.tp_size > 1:
-        sys.exit("pipeline and tensor parallelism cannot be combined in one run here")
+    if (a.pp_size > 1) + (a.tp_size > 1) + (a.cp_size > 1) > 1:
+        sys.exit("pipeline, tensor and sequence parallelism cannot be combined in one run here")
     hyper = dict(lr=a.lr, wd=a.weight_decay)
-    if a.tp_size > 1:
+    if a.cp_size > 1:
+        from .parallel.cp import CPTrainer
+        M = 1
+        eng = CPTrainer(cfg, B, dev, mode=a.cp_mode, hyper=hyper)
+    elif a.tp_size > 1:
         from .parallel.tp import TPTrainer
         M = 1
         eng = TPTrainer(cfg, B, rank, world, dev, hyper=hyper)
@@ -447,15 +455,15 @@ def _train_loop_model_parallel(a):
         eng = PipelineStage(cfg, B, a.pp_size, rank, dev, microbatches=M, hyper=hyper)
     loader = TokenLoader(a.bin, B * M, cfg.T)
     if rank == 0:
-        print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} steps={a.steps}")
+        print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} cp={a.cp_size} ({a.cp_mode}) steps={a.steps}")
     n = B * cfg.T
     t_last = time.perf_counter()
     for step in range(a.steps):
         ids, tgt = loader.next()
         ids, tgt = ids.to(dev), tgt.to(dev)
         eng.hyper["lr"] = lr_at(step, a.steps, a.lr, a.warmup_ratio)
-        if a.tp_size > 1:
-            loss = eng.step(ids, tgt)
+        if a.tp_size > 1 or a.cp_size > 1:
+            loss = eng.step(ids.view(-1), tgt.view(-1))
         else:
             loss = eng.step([ids[k * n:(k + 1) * n] for k in range(M)], [tgt[k * n:(k + 1) * n] for k in range(M)])
         if (step + 1) % run.log_every == 0 or step + 1 == a.steps:

@@ -331,3 +331,36 @@ def global_mean_loss(model, valid_tokens: int, group=None) -> float:
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(s, group=group)
     return float(s.item()) / valid_tokens
+
+
+class CPTrainer:
+    """Training step of a sequence-parallel model (`train_ddp --cp-size N --cp-mode alltoall|ring|zigzag`): every rank
+    gets the full token windows, keeps its slice of every sequence, and all ranks apply the same AdamW update to the
+    summed gradients (fp32 master weights and moments replicated, as in plain data parallelism)."""
+
+    def __init__(self, cfg: Config, B: int, device, group=None, mode: str = "alltoall", hyper=None, seed: int = 1234):
+        assert mode in ("alltoall", "ring", "zigzag")
+        self.cfg, self.B, self.group, self.mode = cfg, B, group, mode
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.model = make_model(cfg, B, device, group, ring=mode != "alltoall", zigzag=mode == "zigzag")
+        self.model.init_weights(seed)
+        self.hyper = dict(lr=1e-4, b1=0.9, b2=0.95, eps=1e-8, wd=0.1)
+        if hyper:
+            self.hyper.update(hyper)
+        self.t = 1
+
+    def step(self, ids: torch.Tensor, tgt: torch.Tensor) -> float:
+        """ids / tgt: the full windows [B*T] on this rank's device (the same on every rank).  Returns the mean loss."""
+        m, zz = self.model, self.mode == "zigzag"
+        valid = int((tgt >= 0).sum())
+        li = local_tokens(ids, self.B, self.cfg.T, self.rank, self.world, zigzag=zz)
+        lt = local_tokens(tgt, self.B, self.cfg.T, self.rank, self.world, zigzag=zz)
+        m.forward(li)
+        m.backward(li, lt, valid_tokens=valid)
+        reduce_grads(m, self.group)
+        h = self.hyper
+        m.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], t=self.t)
+        self.t += 1
+        return global_mean_loss(m, valid, self.group)
+

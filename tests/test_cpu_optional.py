@@ -97,6 +97,34 @@ def test_pipeline_mode_two_stages_equal_one_stage(tmp_path):
     assert two[-1] < two[0]
 
 
+@pytest.mark.parametrize("mode", ["alltoall", "zigzag"])
+def test_sequence_parallel_mode_equals_single_process_training(tmp_path, mode):
+    """`train_ddp --cp-size 2 --cp-mode ...` on two CPU ranks against `train` in one process: same losses step by step."""
+    import textwrap
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    g = _t.Generator().manual_seed(6)
+    path = str(tmp_path / "tok.bin")
+    write_token_bin(path, _t.randint(0, 64, (2 * 16 * 8 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "2", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "1", "ENTROPY_DEVICE": "cpu"}
+    body = textwrap.dedent("""
+        import os, sys
+        os.environ.update(ENV)
+        from ml_b200 import gpt
+        sys.exit(gpt.main(ARGS))
+    """)
+    def lines(outs):
+        assert all(rc == 0 for rc, _ in outs), outs
+        o = [o for _, o in outs if "step " in o][0]
+        return [float(l.split("loss")[1].split("|")[0]) for l in o.splitlines() if l.startswith("step ") and "loss" in l]
+    two = lines(run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path, "4", "--cp-size", "2", "--cp-mode", mode, "--lr", "1e-3"]) + body, 2))
+    one = lines(run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train", path, "4", "--lr", "1e-3"]) + body, 1))
+    assert len(two) == 4 and len(one) == 4, (two, one)
+    for a, b in zip(two, one):
+        assert abs(a - b) < 2e-4, (two, one)
+
+
 def test_moe_block_routes_and_trains():
     torch.manual_seed(0)
     moe = MoEBlock(C=16, I=24, n_experts=4, top_k=2, std=0.3)
