@@ -179,3 +179,14 @@ def test_expert_parallel_moe_two_gpus_equals_single_process_block():
     assert len(lines) == 2, out[-2000:]
     for l in lines:
         assert float(l[2]) < 1e-2 and float(l[3]) < 2e-2 and float(l[4]) < 1e-3 and l[5] == "0", l
+
+
+@needs2
+def test_sequence_parallel_mode_two_gpus_equals_unsharded(token_file, tmp_path):
+    """`train_ddp --cp-size 2 --cp-mode zigzag`: every sequence split over two GPUs (ring of key / value chunks in zig-zag
+    order) against the flat-buffer trainer on one GPU."""
+    cp2 = _mode_losses(["train_ddp", token_file, "5", "--cp-size", "2", "--cp-mode", "zigzag", "--lr", "1e-3"], 2, ENV, tmp_path)
+    one = _mode_losses(["train", token_file, "5", "--lr", "1e-3"], 1, ENV, tmp_path)
+    assert len(cp2) == 5 and len(one) == 5, (cp2, one)
+    for a, b in zip(cp2, one):
+        assert abs(a - b) < 5e-2, (cp2, one)
