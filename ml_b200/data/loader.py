@@ -15,6 +15,7 @@ import ctypes as C
 import torch
 
 from ..utils.hostlib import lib
+from ..utils import streams
 
 _ERR = {1: "cannot open file", 2: "bad magic / short header (not an llm.c .bin)", 3: "fewer than B*T+1 tokens"}
 
@@ -88,7 +89,7 @@ class BatchPipe:
         self.d_ids = [torch.empty(n, dtype=torch.int32, device=self.device) for _ in range(nslots)]
         self.d_tgt = [torch.empty(n, dtype=torch.int32, device=self.device) for _ in range(nslots)]
         self.pipe = lib().mlb_pipe_create(loader.h, nslots)
-        self.copy_stream = torch.cuda.Stream(self.device) if cuda else None
+        self.copy_stream = streams.side_stream(self.device) if cuda else None
         self.ready = [torch.cuda.Event() for _ in range(nslots)] if cuda else None
         self.consumed = [torch.cuda.Event() for _ in range(nslots)] if cuda else None
         self.slot_pos = [0] * nslots
@@ -108,12 +109,12 @@ class BatchPipe:
             self.d_ids[s].copy_(self.h_ids[s])
             self.d_tgt[s].copy_(self.h_tgt[s])
             return
-        with torch.cuda.stream(self.copy_stream):
+        with streams.on(self.copy_stream):
             if not first:
                 self.copy_stream.wait_event(self.consumed[s])
             self.d_ids[s].copy_(self.h_ids[s], non_blocking=True)
             self.d_tgt[s].copy_(self.h_tgt[s], non_blocking=True)
-            self.ready[s].record(self.copy_stream)
+            self.ready[s].record()
 
     def next_pos(self) -> int:
         """File position of the window the next `acquire` hands out (what a checkpoint records)."""

@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
+from ..utils import streams
 
 
 class DDP:
@@ -42,7 +43,7 @@ class DDP:
         self.dev_hyper = None      # CUDA fp32[4] {lr, 1/bc1, 1/bc2, grad_scale}: set by a graph-replaying trainer
         self.reduce_now = True
         self.scale = 1.0 / (self.world * self.accum)
-        self.comm_stream = torch.cuda.Stream(model.device) if self.cuda else None
+        self.comm_stream = streams.side_stream(model.device) if self.cuda else None
         self.staging = torch.empty(model.np, dtype=torch.bfloat16, device=model.device) if self.bf16_reduce and comm == "nccl" else None
         self.works = []
         self._comm_used = False   # the side stream joined this step (it may only be waited on if it did: a CUDA-graph
@@ -77,7 +78,7 @@ class DDP:
         ev = torch.cuda.Event()
         ev.record()
         self._comm_used = True
-        with torch.cuda.stream(self.comm_stream):
+        with streams.on(self.comm_stream):
             self.comm_stream.wait_event(ev)
             if self.bf16_reduce:
                 st = self.staging[off:off + n]
@@ -105,7 +106,7 @@ class DDP:
         ev = torch.cuda.Event()
         ev.record()
         self._comm_used = True
-        with torch.cuda.stream(self.comm_stream):
+        with streams.on(self.comm_stream):
             self.comm_stream.wait_event(ev)
             self._adamw(off, n)
 
@@ -118,7 +119,7 @@ class DDP:
             return True
         if self.cuda:
             if self._comm_used:
-                torch.cuda.current_stream().wait_stream(self.comm_stream)
+                streams.join(self.comm_stream)
                 self._comm_used = False
         else:
             for w, off, n in self.works:

@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
+from ..utils import streams
 
 
 class Unit:
@@ -71,7 +72,7 @@ class FSDP:
         self.dslot = [self._alloc_symm(maxpad, f32) for _ in range(2)]
         self.slot_unit = [-1, -1]       # which unit each gather slot holds
         self.dslot_unit = [-1, -1]
-        self.comm_stream = torch.cuda.Stream(self.dev) if self.cuda else None
+        self.comm_stream = streams.side_stream(self.dev) if self.cuda else None
         self.gather_ev = [None, None]
         self.rs_ev = [None, None]
         self.fused = None
@@ -159,7 +160,7 @@ class FSDP:
             if self.cuda:
                 ev = torch.cuda.Event()
                 ev.record()
-                with torch.cuda.stream(self.comm_stream):
+                with streams.on(self.comm_stream):
                     self.comm_stream.wait_event(ev)
                     self.gslot[slot][:u.chunk].copy_(src)
                     self.gather_ev[slot] = torch.cuda.Event()
@@ -172,7 +173,7 @@ class FSDP:
             return
         ev = torch.cuda.Event()
         ev.record()          # everything that used this slot before has been enqueued on the compute stream
-        with torch.cuda.stream(self.comm_stream):
+        with streams.on(self.comm_stream):
             self.comm_stream.wait_event(ev)
             if self.fused is not None:
                 if self.fused.gather_in_gemm and self._fwd_pass and u.name.startswith("layer"):
@@ -254,7 +255,7 @@ class FSDP:
             return
         ev = torch.cuda.Event()
         ev.record()
-        with torch.cuda.stream(self.comm_stream):
+        with streams.on(self.comm_stream):
             self.comm_stream.wait_event(ev)
             if self.fused is not None:
                 self.fused.reduce_scatter_adamw(ui, d, scale, bc1, bc2)
@@ -272,7 +273,7 @@ class FSDP:
         """End of an optimizer step: join the communication stream and invalidate the gather slots (their contents are
         parameters of the previous step)."""
         if self.cuda:
-            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            streams.join(self.comm_stream)
         self.slot_unit = [-1, -1]
         self.lazy = [-1, -1]
         self.dslot_unit = [-1, -1]

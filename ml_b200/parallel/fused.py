@@ -30,6 +30,7 @@ import torch
 
 from ..ops import native
 from .symm import PeerTable, empty as symm_empty, multimem_wanted
+from ..utils import streams
 
 MAX_BUCKETS = 64
 GMODES = {"f32": 0, "f32_mc": 1, "bf16": 2, "bf16_mc": 3}
@@ -122,7 +123,7 @@ class FusedGradEngine:
             self.params_mc = None
         self.done = torch.zeros(2 * MAX_BUCKETS, dtype=torch.int32, device=dev)
         self.epoch = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=dev)
-        self.stream = torch.cuda.Stream(dev, priority=-1)
+        self.stream = streams.side_stream(dev, priority=-1)
         self.used = False
         self.launched = []                  # (off, n) of the launches of the current / last step: who owns what
         self._step_ranges = []
@@ -140,7 +141,7 @@ class FusedGradEngine:
         ev = torch.cuda.Event()
         ev.record()
         self.used = True
-        with torch.cuda.stream(self.stream):
+        with streams.on(self.stream):
             self.stream.wait_event(ev)
             self._launch(off, n, scale, hyper, t, dev_hyper, lean=not last)
 
@@ -169,7 +170,7 @@ class FusedGradEngine:
             self._launch(self.whole[0], self.whole[1], scale, hyper, t, dev_hyper, lean=False)
         self.pending = []
         if self.used:
-            torch.cuda.current_stream().wait_stream(self.stream)
+            streams.join(self.stream)
             self.used = False
         if self._step_ranges:
             self.launched, self._step_ranges = self._step_ranges, []

@@ -18,6 +18,7 @@ from typing import Optional, Tuple
 import torch
 
 from .hostlib import lib
+from . import streams
 
 
 def step_dir(root: str, step: int) -> str:
@@ -43,10 +44,10 @@ class CheckpointWriter:
         if rc:
             raise OSError(rc, f"mkdir {d}")
         off, n = shard if shard is not None else (0, master.numel())
-        side = torch.cuda.Stream(master.device) if master.is_cuda else None
+        side = streams.side_stream(master.device) if master.is_cuda else None
         if side is not None:
             side.wait_stream(torch.cuda.current_stream())
-        ctx = torch.cuda.stream(side) if side is not None else _null()
+        ctx = streams.on(side) if side is not None else _null()
         with ctx:
             hw = self._snap(master[off:off + n])
             ho = torch.empty(2 * n, dtype=torch.float32, pin_memory=master.is_cuda)

@@ -312,6 +312,78 @@ def test_rank_leaves_between_steps_ends_with_error_not_hang():
     assert "SURVIVOR 2" in out, out[-3000:]
 
 
+@needs2
+def test_one_stream_run_matches_the_multi_stream_run_two_gpus():
+    """Stream-dependency check of the overlapping engines.  With MLB_ONE_STREAM=1 the gradient reductions, the per-slice
+    side-stream AdamW, the fused reduce + AdamW launches and the sharded engine's gathers / reduce-scatters are enqueued
+    in program order on the launching stream, so that run cannot miss a cross-stream wait; the normal multi-stream run
+    has to agree with it: parameters equal after the first step, within AdamW's rounding-flip bound after five."""
+    rc, out = _torchrun("""
+        import os
+        os.environ["MLB_NO_ROPE_FUSE"] = "1"
+        import torch, torch.distributed as dist
+        from ml_b200 import Config, RunConfig
+        from ml_b200.models import GPT
+        from ml_b200.parallel.bootstrap import init_distributed
+        from ml_b200.parallel.fsdp import FSDP
+        from ml_b200.trainer import Trainer
+        from ml_b200.data import bench_batch
+        from ml_b200.ops import native
+        from ml_b200.utils import streams
+        rank, world, local, dev = init_distributed()
+        native.lib().mlb_gemm_set_splits(1)   # deterministic weight gradients: the runs may only differ by stream order
+        cfg = Config(V=512, C=256, L=3, H=4, I=512, T=128)
+        ids, tgt = bench_batch(2, 128, 512, rank)
+        def ddp(one, comm, bf16=0, opt=0, overlap="0"):
+            os.environ["MLB_ONE_STREAM"] = "1" if one else "0"
+            os.environ["ENTROPY_FUSED_OVERLAP"] = overlap
+            r = RunConfig(); r.comm = comm; r.bf16_reduce = bf16; r.ddp_overlap_opt = opt
+            tr = Trainer(cfg, 2, dev, r, lr=1e-3, wd=0.1, world=world, rank=rank)
+            side = tr.ddp.fused.stream if tr.ddp.fused is not None else tr.ddp.comm_stream
+            assert isinstance(side, streams.InlineStream) == one
+            tr.set_batch(ids.to(dev), tgt.to(dev))
+            tr.step(); torch.cuda.synchronize()
+            first, grads = tr.model.params.float().clone(), tr.model.grads.clone()
+            for _ in range(4): tr.step()
+            torch.cuda.synchronize()
+            last = tr.model.params.float().clone()
+            tr.close()
+            return first, last, grads
+        def fsdp(one):
+            os.environ["MLB_ONE_STREAM"] = "1" if one else "0"
+            g = GPT(cfg, 2, dev, sharded=True)
+            f = FSDP(g, world, rank, comm="nccl", hyper=dict(lr=1e-3, wd=0.1))
+            assert isinstance(f.comm_stream, streams.InlineStream) == one
+            g.init_weights(1234)
+            f.step(ids.to(dev), tgt.to(dev)); torch.cuda.synchronize()
+            first = f.full_master()
+            for _ in range(4): f.step(ids.to(dev), tgt.to(dev))
+            torch.cuda.synchronize()
+            return first, f.full_master(), None
+        cases = [("ddp_nccl_f32", lambda one: ddp(one, "nccl")),
+                 ("ddp_nccl_bf16_side_adamw", lambda one: ddp(one, "nccl", bf16=1, opt=1)),
+                 ("ddp_fused_overlapped", lambda one: ddp(one, "fused", overlap="1")),
+                 ("fsdp_nccl", fsdp)]
+        for name, fn in cases:
+            a, b = fn(True), fn(False)
+            d0 = float((a[0] - b[0]).abs().max()); d1 = (a[1] - b[1]).abs()
+            # what the gradient buffer holds after the first step (the reduced mean with library collectives): a
+            # reduction that had not finished when its consumer ran shows here at full size
+            dg = float((a[2] - b[2]).abs().max() / a[2].abs().max()) if a[2] is not None else 0.0
+            if rank == 0:
+                print("RESULT", name, d0, float(d1.max()), float(d1.mean()), native.get_error(), dg, flush=True)
+        dist.barrier(); torch.cuda.synchronize()
+        os._exit(0)
+    """, 2)
+    assert rc == 0, out[-3000:]
+    lines = [l.split() for l in out.splitlines() if l.startswith("RESULT")]
+    assert [l[1] for l in lines] == ["ddp_nccl_f32", "ddp_nccl_bf16_side_adamw", "ddp_fused_overlapped", "fsdp_nccl"], out[-3000:]
+    for l in lines:
+        assert float(l[2]) == 0.0, l              # first step: the same parameters
+        assert float(l[3]) < 1.2e-2 and float(l[4]) < 1e-4 and l[5] == "0", l     # 2 * lr * 5 steps plus one bf16 ulp
+        assert float(l[6]) < 1e-5, l              # only the embedding gradient's atomic adds may reorder
+
+
 def test_fsdp_fused_world1_matches_unsharded():
     """FSDP engine on one GPU with the NVLink-native kernels (pull all-gather, reduce-scatter + sharded AdamW)."""
     from ml_b200 import Config

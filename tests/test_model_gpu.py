@@ -283,3 +283,56 @@ def test_no_kernel_writes_outside_its_buffers(cfg, B, kw):
     g.check_canaries()
     assert _native().get_error() == 0
     assert g.mean_loss() == g.mean_loss()      # not NaN
+
+
+def test_one_stream_run_matches_the_multi_stream_run(tmp_path, monkeypatch):
+    """Stream-dependency check: MLB_ONE_STREAM=1 enqueues everything the side streams would carry (the token pipe's
+    host-to-device copies, the checkpoint snapshot) in program order on the launching stream, so it cannot miss a
+    cross-stream wait.  The normal run must reproduce it: the same windows reach the model, the parameters after the
+    first step are equal bit for bit, and the snapshot taken between two steps holds exactly the parameters of the step
+    it was asked for."""
+    from ml_b200.data import TokenLoader, BatchPipe, write_token_bin
+    from ml_b200.utils import ckpt, streams
+    cfg, B, steps = Config(V=512, C=256, L=2, H=4, I=512, T=128), 2, 4
+    g = torch.Generator().manual_seed(3)
+    path = str(tmp_path / "tok.bin")
+    write_token_bin(path, torch.randint(0, cfg.V, ((steps + 3) * B * cfg.T + 1,), generator=g, dtype=torch.int32))
+    _native().lib().mlb_gemm_set_splits(1)
+    res = {}
+    try:
+        for mode in ("1", "0"):
+            monkeypatch.setenv("MLB_ONE_STREAM", mode)
+            assert streams.one_stream() == (mode == "1")
+            tr = Trainer(cfg, B, "cuda:0", lr=1e-3, wd=0.1)
+            pipe = BatchPipe(TokenLoader(path, B, cfg.T), "cuda:0")
+            assert isinstance(pipe.copy_stream, streams.InlineStream) == (mode == "1")
+            w = ckpt.CheckpointWriter()
+            seen, snaps = [], []
+            for s in range(steps):
+                ids, tgt = pipe.acquire(s)
+                tr.ids.copy_(ids.view(tr.accum, -1))
+                tr.tgt.copy_(tgt.view(tr.accum, -1))
+                seen.append(ids.clone())
+                tr.step()
+                pipe.release(s)
+                if s == 1:
+                    at_save = tr.model.master.clone()
+                    w.save(str(tmp_path / f"ck{mode}"), s + 1, 0.0, 0, tr.model.master, tr.model.m, tr.model.v)
+                if s in (0, steps - 1):
+                    torch.cuda.synchronize()
+                    snaps.append(tr.model.master.clone())
+            w.wait()
+            back = [torch.empty_like(tr.model.master) for _ in range(3)]
+            ckpt.load(str(tmp_path / f"ck{mode}"), 2, *back)
+            assert torch.equal(back[0], at_save)
+            res[mode] = (torch.stack(seen).cpu(), snaps)
+            w.close()
+            pipe.close()
+            tr.close()
+    finally:
+        _native().lib().mlb_gemm_set_splits(0)
+    assert torch.equal(res["0"][0], res["1"][0])
+    assert torch.equal(res["0"][1][0], res["1"][1][0])
+    d = (res["0"][1][1] - res["1"][1][1]).abs()
+    assert d.max().item() < 2 * 1e-3 * steps and d.mean().item() < 2e-5, (d.max().item(), d.mean().item())
+    assert _native().get_error() == 0
