@@ -32,6 +32,11 @@ struct Loader {
   // Data-parallel striping: this reader serves windows `first`, `first + every`, `first + 2*every`, ... of the file (a
   // window is B*T tokens), so `every` ranks with first = 0..every-1 read disjoint windows, prefetch included.
   int64_t first = 0, every = 1;
+  // Vocabulary check (0 = off): the first window holding a token >= vocab is remembered; the reader of that window
+  // asks with mlb_loader_bad() before the tokens reach the device (the kernels index tables by token id).
+  int vocab = 0;
+  std::atomic<int64_t> bad_pos{-1};
+  std::atomic<int> bad_tok{0};
 };
 
 struct Job { int slot; int32_t* ids; int32_t* tgt; };
@@ -52,7 +57,12 @@ void fill(Loader* ld, int32_t* ids, int32_t* tgt) {
   const int64_t n = (int64_t)ld->B * ld->T;
   if (ld->pos + n + 1 > ld->ntok) ld->pos = ld->first * n;   // wrap to this reader's first window
   const uint16_t* w = ld->tok + ld->pos;
-  for (int64_t i = 0; i < n; i++) { ids[i] = w[i]; tgt[i] = w[i + 1]; }
+  uint16_t mx = w[0];
+  for (int64_t i = 0; i < n; i++) { ids[i] = w[i]; tgt[i] = w[i + 1]; mx = w[i + 1] > mx ? w[i + 1] : mx; }
+  if (ld->vocab > 0 && (int)mx >= ld->vocab && ld->bad_pos.load() < 0) {
+    ld->bad_tok.store(mx);
+    ld->bad_pos.store(ld->pos);
+  }
   ld->pos += n * ld->every;
 }
 
@@ -116,6 +126,16 @@ int mlb_loader_set_stride(void* h, int64_t first, int64_t every) {
   return 0;
 }
 void mlb_loader_next(void* h, int32_t* ids, int32_t* tgt) { fill((Loader*)h, ids, tgt); }
+// Tokens >= vocab are reported from now on (vocab 0 switches the check off).
+void mlb_loader_set_vocab(void* h, int vocab) { ((Loader*)h)->vocab = vocab; }
+// 1 if a window with a token >= vocab has been served: *pos = its file position, *tok = its largest token.
+int mlb_loader_bad(void* h, int64_t* pos, int* tok) {
+  Loader* ld = (Loader*)h;
+  const int64_t p = ld->bad_pos.load();
+  if (p < 0) return 0;
+  *pos = p; *tok = ld->bad_tok.load();
+  return 1;
+}
 void mlb_loader_close(void* h) {
   Loader* ld = (Loader*)h;
   if (!ld) return;

@@ -43,11 +43,20 @@ __device__ __forceinline__ void store8_e4m3(uint8_t* p, const float (&f)[8], flo
 }
 
 // ------------------------------------------------------------------ embedding
-__global__ void embed_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ wte, const int* __restrict__ ids, int C) {
+// A token id outside [0, V) (a token file made with a larger vocabulary, a damaged file) would index past the table:
+// such a row gets zeros / no gradient, and the error word says so (MLB_ERR_BOUNDS, detail 0xE1 forward, 0xE2 backward,
+// 0xCE for a cross-entropy target), so the step that read it fails on the host instead of corrupting memory.
+__global__ void embed_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ wte, const int* __restrict__ ids, int C, int V) {
   mlb_pdl_sync();
   const long row = blockIdx.x;
-  const bf16* src = wte + (long)ids[row] * C;
+  const int id = ids[row];
   bf16* dst = out + row * C;
+  if ((unsigned)id >= (unsigned)V) {
+    if (threadIdx.x == 0) mlb_set_error(MLB_ERR_BOUNDS, 0xE1);
+    for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = __float2bfloat16(0.f);
+    return;
+  }
+  const bf16* src = wte + (long)id * C;
   if ((C & 7) == 0) {
     for (int i = threadIdx.x * 8; i < C; i += blockDim.x * 8)
       *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
@@ -56,11 +65,16 @@ __global__ void embed_fwd_k(bf16* __restrict__ out, const bf16* __restrict__ wte
   }
 }
 __global__ void embed_bwd_k(float* __restrict__ dwte, const bf16* __restrict__ dout, const int* __restrict__ ids, int C,
-                            int T, int n_pre) {
+                            int V, int T, int n_pre) {
   mlb_pdl_sync();
   const long row = blockIdx.x;
   if ((int)(row % T) < n_pre) return;
-  float* dst = dwte + (long)ids[row] * C;
+  const int id = ids[row];
+  if ((unsigned)id >= (unsigned)V) {
+    if (threadIdx.x == 0) mlb_set_error(MLB_ERR_BOUNDS, 0xE2);
+    return;
+  }
+  float* dst = dwte + (long)id * C;
   const bf16* src = dout + row * C;
   for (int i = threadIdx.x; i < C; i += blockDim.x) atomicAdd(dst + i, __bfloat162float(src[i]));
 }
@@ -560,7 +574,8 @@ __global__ void __launch_bounds__(512, 4) ce_fwd_bwd_k(float* __restrict__ losse
   bf16* z = logits + row * ld;
   const int t = tgt[row];
   const bool vec = ((V & 7) == 0) && ((ld & 7) == 0);
-  if (t < 0) {
+  if (t >= V && threadIdx.x == 0) mlb_set_error(MLB_ERR_BOUNDS, 0xCE);      // treated like an ignored row
+  if (t < 0 || t >= V) {
     if (threadIdx.x == 0) losses[row] = 0.f;
     if (vec) {
       for (int i = threadIdx.x * 8; i < V; i += blockDim.x * 8) *reinterpret_cast<uint4*>(z + i) = make_uint4(0, 0, 0, 0);
@@ -700,7 +715,8 @@ __global__ void __launch_bounds__(512) ce_fwd_bwd_smem_k(float* __restrict__ los
   bf16* z = logits + row * ld;
   const int t = tgt[row];
   const int nv = V >> 3;
-  if (t < 0) {
+  if (t >= V && threadIdx.x == 0) mlb_set_error(MLB_ERR_BOUNDS, 0xCE);
+  if (t < 0 || t >= V) {
     if (threadIdx.x == 0) losses[row] = 0.f;
     for (int i = threadIdx.x; i < nv; i += blockDim.x) reinterpret_cast<uint4*>(z)[i] = make_uint4(0, 0, 0, 0);
     return;
@@ -969,12 +985,12 @@ inline int gs(long n, int per_block) { return (int)((n + per_block - 1) / per_bl
 static int g_ce_smem = 0;     // tuning hook: 0 = always the two-pass cross-entropy kernel
 MLB_API void mlb_ce_mode(int smem_row) { g_ce_smem = smem_row; }
 
-MLB_API int mlb_embed_fwd(void* out, const void* wte, const int* ids, long BT, int C, cudaStream_t st) {
-  mlb_launch(embed_fwd_k, dim3((unsigned)BT), dim3(96), 0, st, (bf16*)out, (const bf16*)wte, ids, C);
+MLB_API int mlb_embed_fwd(void* out, const void* wte, const int* ids, long BT, int C, int V, cudaStream_t st) {
+  mlb_launch(embed_fwd_k, dim3((unsigned)BT), dim3(96), 0, st, (bf16*)out, (const bf16*)wte, ids, C, V);
   LAUNCH_RET;
 }
-MLB_API int mlb_embed_bwd(float* dwte, const void* dout, const int* ids, long BT, int C, int T, int n_pre, cudaStream_t st) {
-  mlb_launch(embed_bwd_k, dim3((unsigned)BT), dim3(256), 0, st, dwte, (const bf16*)dout, ids, C, T, n_pre);
+MLB_API int mlb_embed_bwd(float* dwte, const void* dout, const int* ids, long BT, int C, int V, int T, int n_pre, cudaStream_t st) {
+  mlb_launch(embed_bwd_k, dim3((unsigned)BT), dim3(256), 0, st, dwte, (const bf16*)dout, ids, C, V, T, n_pre);
   LAUNCH_RET;
 }
 MLB_API int mlb_set_prefix(void* x, const void* prefix, int B, int T, int n_pre, int C, cudaStream_t st) {

@@ -28,13 +28,25 @@ def write_token_bin(path: str, tokens: torch.Tensor):
 
 
 class TokenLoader:
-    def __init__(self, path: str, B: int, T: int):
+    def __init__(self, path: str, B: int, T: int, vocab: int = 0):
+        """vocab > 0: a window holding a token id >= vocab raises ValueError when it is handed out (`next_into`, or
+        `BatchPipe.acquire`'s upload), before the ids reach a kernel that would use them as table indices."""
         err = C.c_int(0)
         self.h = lib().mlb_loader_open(path.encode(), B, T, C.byref(err))
         if not self.h:
             raise OSError(f"{path}: {_ERR.get(err.value, 'error %d' % err.value)}")
-        self.B, self.T, self.path = B, T, path
+        self.B, self.T, self.path, self.vocab = B, T, path, int(vocab)
         self.ntok = lib().mlb_loader_ntok(self.h)
+        if self.vocab > 0:
+            lib().mlb_loader_set_vocab(self.h, self.vocab)
+
+    def check_vocab(self):
+        if self.vocab <= 0:
+            return
+        pos, tok = C.c_int64(0), C.c_int(0)
+        if lib().mlb_loader_bad(self.h, C.byref(pos), C.byref(tok)):
+            raise ValueError(f"{self.path}: token id {tok.value} in the window at position {pos.value} is outside the "
+                             f"model's vocabulary of {self.vocab}")
 
     def set_stride(self, first: int, every: int):
         """Data-parallel striping: this loader serves windows first, first + every, ... (rank, world); the ranks' windows
@@ -55,6 +67,7 @@ class TokenLoader:
         assert ids.dtype == torch.int32 and tgt.dtype == torch.int32 and ids.numel() == n and tgt.numel() == n
         assert not ids.is_cuda and ids.is_contiguous() and tgt.is_contiguous()
         lib().mlb_loader_next(self.h, ids.data_ptr(), tgt.data_ptr())
+        self.check_vocab()
 
     def next(self):
         ids = torch.empty(self.B * self.T, dtype=torch.int32)
@@ -105,6 +118,7 @@ class BatchPipe:
 
     def _upload(self, s, first=False):
         self.slot_pos[s] = lib().mlb_pipe_wait(self.pipe, s)
+        self.loader.check_vocab()
         if self.copy_stream is None:
             self.d_ids[s].copy_(self.h_ids[s])
             self.d_tgt[s].copy_(self.h_tgt[s])

@@ -47,8 +47,8 @@ def lib():
         "mlb_attn_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_attn_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
         "mlb_attn_bwd_scratch_bytes": [_i32, _i32, _i32, _i32],
-        "mlb_embed_fwd": [_vp, _vp, _vp, _i64, _i32, _vp],
-        "mlb_embed_bwd": [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _vp],
+        "mlb_embed_fwd": [_vp, _vp, _vp, _i64, _i32, _i32, _vp],
+        "mlb_embed_bwd": [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp],
         "mlb_set_prefix": [_vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_gather_prefix_grad": [_vp, _vp, _i32, _i32, _i32, _i32, _vp],
         "mlb_rmsnorm_fwd": [_vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp],
@@ -364,11 +364,11 @@ def attn_bidir_bwd(dqkv, dout, qkv, out, lse, B, T, H, hd):
 
 # ------------------------------------------------------------------ embedding
 def embed_fwd(out, wte, ids):
-    _chk(lib().mlb_embed_fwd(_b(out), _b(wte), _i(ids), ids.numel(), wte.shape[1], _st()), "embed_fwd")
+    _chk(lib().mlb_embed_fwd(_b(out), _b(wte), _i(ids), ids.numel(), wte.shape[1], wte.shape[0], _st()), "embed_fwd")
 
 
 def embed_bwd(dwte, dout, ids, T, n_pre):
-    _chk(lib().mlb_embed_bwd(_f(dwte), _b(dout), _i(ids), ids.numel(), dwte.shape[1], T, n_pre, _st()), "embed_bwd")
+    _chk(lib().mlb_embed_bwd(_f(dwte), _b(dout), _i(ids), ids.numel(), dwte.shape[1], dwte.shape[0], T, n_pre, _st()), "embed_bwd")
 
 
 def set_prefix(x, prefix, B, T, n_pre):

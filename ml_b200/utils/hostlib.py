@@ -24,6 +24,8 @@ def lib():
         "mlb_loader_set_pos": (None, [vp, i64]),
         "mlb_loader_set_stride": (i32, [vp, i64, i64]),
         "mlb_loader_next": (None, [vp, vp, vp]),
+        "mlb_loader_set_vocab": (None, [vp, i32]),
+        "mlb_loader_bad": (i32, [vp, vp, vp]),
         "mlb_loader_close": (None, [vp]),
         "mlb_pipe_create": (vp, [vp, i32]),
         "mlb_pipe_submit": (None, [vp, i32, vp, vp]),

@@ -105,6 +105,33 @@ def test_batch_pipe_order_cpu(tmp_path):
     pipe.close()
 
 
+def test_loader_reports_a_token_outside_the_vocabulary(tmp_path):
+    """With vocab= the loader refuses a window that holds a token id >= vocab (the kernels use ids as table indices):
+    directly, and through the prefetching pipe, which meets the window one slot ahead of its reader."""
+    toks = torch.arange(0, 101, dtype=torch.int32) % 50
+    toks[57] = 77
+    p = str(tmp_path / "t.bin")
+    write_token_bin(p, toks)
+    ld = TokenLoader(p, 1, 10, vocab=50)
+    for _ in range(5):
+        ld.next()                               # windows at 0 .. 40: tokens 0 .. 50 of the file, all below 50
+    with pytest.raises(ValueError, match="token id 77 in the window at position 50"):
+        ld.next()
+    ld.close()
+    ld = TokenLoader(p, 1, 10, vocab=50)
+    pipe = BatchPipe(ld, "cpu")                 # two windows prefetched
+    with pytest.raises(ValueError, match="outside the model's vocabulary of 50"):
+        for step in range(6):
+            pipe.acquire(step)
+            pipe.release(step)
+    assert step == 3                            # releasing window 3 fetched window 5, the one with the bad token
+    pipe.close()
+    ld = TokenLoader(p, 1, 10, vocab=78)        # a vocabulary that covers it: nothing to report
+    for _ in range(9):
+        ld.next()
+    ld.close()
+
+
 def test_rank_striped_loaders_read_disjoint_windows_fresh_and_after_resume(tmp_path):
     """Data-parallel ranks stripe the file: rank r serves windows r, r + world, ... with the pipe's prefetch following the
     same stride; a run resumed at an odd step from the recorded per-rank position continues exactly where it stopped,

@@ -402,6 +402,56 @@ def test_swiglu(rows, I):
     close(dgu, edgu, name="swiglu bwd")
 
 
+@pytest.mark.parametrize("smem_row", [1, 0], ids=["row_in_smem", "two_pass"])
+def test_token_ids_outside_the_vocabulary_are_reported_not_followed(smem_row):
+    """A token id or a target >= V (a token file made with a larger vocabulary) must not become an address: the kernels
+    check the index first, give such a row zeros / no gradient / loss 0, and record MLB_ERR_BOUNDS with the kernel's tag
+    in the error word; every other row is computed as usual."""
+    torch.manual_seed(17)
+    B, T, C, V = 2, 16, 96, 56
+    bounds = lambda tag: (3 << 24) | tag
+    wte = rnd(V, C)
+    ids = torch.randint(0, V, (B * T,), device=dev(), dtype=torch.int32)
+    bad = torch.tensor([5, 20], device=dev())
+    ids[5], ids[20] = V + 5, -3
+    good = torch.ones(B * T, dtype=torch.bool, device=dev())
+    good[bad] = False
+    assert nat().get_error() == 0
+    out = torch.full((B * T, C), 7.0, device=dev(), dtype=torch.bfloat16)
+    nat().embed_fwd(out, wte, ids)
+    torch.cuda.synchronize()
+    assert nat().get_error() == bounds(0xE1)
+    nat().clear_error()
+    assert torch.equal(out[good], wte[ids[good].long()]) and (out[bad] == 0).all()
+    d = rnd(B * T, C)
+    dw, edw = torch.zeros(V, C, device=dev()), torch.zeros(V, C, device=dev())
+    nat().embed_bwd(dw, d, ids, T, 0)
+    torch.cuda.synchronize()
+    assert nat().get_error() == bounds(0xE2)
+    nat().clear_error()
+    edw.index_add_(0, ids[good].long(), d[good].float())
+    close(dw, edw, rtol=1e-4, atol=1e-4, name="embed bwd, bad rows dropped")
+    rows = 12
+    logits = rnd(rows, V, scale=3.0)
+    tgt = torch.randint(0, V, (rows,), device=dev(), dtype=torch.int32)
+    tgt[3] = V + 7
+    a, la = logits.clone(), torch.full((rows,), 9.0, device=dev())
+    nat().lib().mlb_ce_mode(smem_row)
+    try:
+        nat().ce_fwd_bwd(la, a, tgt, 0.25)
+        torch.cuda.synchronize()
+    finally:
+        nat().lib().mlb_ce_mode(0)
+    assert nat().get_error() == bounds(0xCE)
+    nat().clear_error()
+    ok = tgt < V
+    e, le = logits.float().clone(), torch.empty(rows, device=dev())
+    ref.ce_fwd_bwd(le, e, torch.where(ok, tgt, torch.full_like(tgt, -1)), 0.25)
+    close(la, le, rtol=1e-3, atol=1e-3, name="ce loss with one bad target")
+    close(a, e, rtol=2e-2, atol=1e-4, name="dlogits with one bad target")
+    assert la[3] == 0 and (a[3] == 0).all()
+
+
 @pytest.mark.parametrize("rows,V", [(64, 50304), (16, 512), (9, 1001)])
 @pytest.mark.parametrize("smem_row", [1, 0], ids=["row_in_smem", "two_pass"])
 def test_cross_entropy(rows, V, smem_row):
