@@ -237,9 +237,14 @@ def _train_loop(argv, ddp):
     from .utils import ckpt as ck
     from .utils.metrics import MetricsLogger
     ap = argparse.ArgumentParser(prog="gpt train")
-    ap.add_argument("bin")
+    ap.add_argument("bin", nargs="?", default="", help="llm.c token file (or --data)")
     ap.add_argument("steps", nargs="?", type=int, default=100)
+    ap.add_argument("--data", default="", help="token file, same as the positional argument")
     ap.add_argument("--ckpt-dir", "--checkpoint", default="")
+    ap.add_argument("--output", default="", help="checkpoint directory when --ckpt-dir / --checkpoint is not given")
+    ap.add_argument("--log-every", type=int, default=0, help="print / log every N steps (default ENTROPY_LOG_EVERY or 10)")
+    ap.add_argument("--wandb-project", default="entropy")
+    ap.add_argument("--wandb-run-name", default="entropy-run")
     ap.add_argument("--save-every", type=int, default=0)
     ap.add_argument("--resume", type=int, default=-1, help="step to resume from (-2 = latest)")
     ap.add_argument("--log-dir", default="")
@@ -270,6 +275,15 @@ def _train_loop(argv, ddp):
     a = ap.parse_args(argv)
     if a.max_steps > 0:
         a.steps = a.max_steps
+    if a.data and a.bin.isdigit() and a.steps == 100:
+        a.steps = int(a.bin)               # `train --data tokens.bin 500`: the lone positional is the step count
+        a.bin = ""
+    a.bin = a.data or a.bin
+    if not a.bin:
+        ap.error("a token file is required (positional or --data)")
+    a.ckpt_dir = a.ckpt_dir or a.output
+    if a.log_every > 0:
+        os.environ["ENTROPY_LOG_EVERY"] = str(a.log_every)
     if a.fp16:
         print("note: --fp16 has no effect: the sm_100a kernels compute in bf16 with fp32 master weights", file=sys.stderr)
     if a.gpus_per_node > 0 and "RANK" not in os.environ and "SLURM_PROCID" not in os.environ:
@@ -342,7 +356,7 @@ def _train_loop(argv, ddp):
         return ev
 
     writer = ck.CheckpointWriter() if (a.ckpt_dir and rank == 0) else None
-    logger = MetricsLogger(a.log_dir, rank, wandb=a.wandb) if a.log_dir else None
+    logger = MetricsLogger(a.log_dir, rank, wandb=a.wandb, wandb_project=a.wandb_project, wandb_run_name=a.wandb_run_name) if a.log_dir else None
     stop = {"flag": False}
     for sig in (signal.SIGINT, signal.SIGTERM):
         try:

@@ -17,9 +17,11 @@ from .hostlib import lib
 
 
 class MetricsLogger:
-    def __init__(self, log_dir: str, rank: int = 0, tensorboard: bool = True, wandb: bool = False):
+    def __init__(self, log_dir: str, rank: int = 0, tensorboard: bool = True, wandb: bool = False,
+                 wandb_project: str = "entropy", wandb_run_name: str = "entropy-run"):
         self.enabled = rank == 0
         self.dir, self.wandb, self.h = log_dir, wandb, None
+        self.wandb_project, self.wandb_run_name = wandb_project, wandb_run_name
         if self.enabled:
             os.makedirs(log_dir, exist_ok=True)
             self.h = lib().mlb_metrics_open(log_dir.encode(), 1 if tensorboard else 0)
@@ -46,7 +48,7 @@ class MetricsLogger:
             lib().mlb_metrics_close(self.h)
             self.h = None
             if self.wandb and shutil.which("wandb"):
-                subprocess.run(["wandb", "sync", self.dir], check=False)
+                subprocess.run(["wandb", "sync", "--project", self.wandb_project, "--id", self.wandb_run_name, self.dir], check=False)
 
 
 def read_tfevents(path: str):

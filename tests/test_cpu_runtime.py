@@ -279,6 +279,31 @@ def test_cli_train_checkpoint_resume(tmp_path):
     assert la == lc, (la, lc)
 
 
+def test_cli_prototype_flags_and_vocabulary_check(tmp_path):
+    """--data / --output / --log-every (names of the prototype's command line, csrc/src/main.cu:30-57) do what the
+    positional file, --ckpt-dir and ENTROPY_LOG_EVERY do; a token file whose ids exceed the model's vocabulary ends the
+    run with a message instead of reaching the kernels."""
+    import subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    toks = (torch.arange(0, 20000, dtype=torch.int64) * 7919 % 251).to(torch.int32)
+    p = str(tmp_path / "d.bin")
+    write_token_bin(p, toks)
+    env = dict(os.environ, ENTROPY_DEVICE="cpu", ENTROPY_V="256", ENTROPY_C="32", ENTROPY_L="1", ENTROPY_H="2", ENTROPY_I="64",
+               ENTROPY_T="16", ENTROPY_B="2", PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    a = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "train", "--data", p, "6", "--output", str(tmp_path / "out"),
+                        "--save-every", "3", "--log-every", "2", "--wandb-project", "x", "--wandb-run-name", "y"],
+                       env=env, capture_output=True, text=True, timeout=300)
+    assert a.returncode == 0, a.stdout + a.stderr
+    steps = [int(l.split()[1]) for l in a.stdout.splitlines() if l.startswith("step ")]
+    assert steps == [2, 4, 6], a.stdout
+    assert ck.latest_step(str(tmp_path / "out")) == 6
+    b = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "train", p, "4"], env=dict(env, ENTROPY_V="128"),
+                       capture_output=True, text=True, timeout=300)
+    assert b.returncode != 0 and "outside the model's vocabulary of 128" in b.stderr, b.stdout + b.stderr
+    c = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "train"], env=env, capture_output=True, text=True, timeout=300)
+    assert c.returncode != 0 and "token file is required" in c.stderr
+
+
 def test_cli_train_eval_flags_and_chunked_head(tmp_path):
     """--eval-every / --eval-bin print a forward-only held-out loss, log it under eval/loss, and leave the training
     trajectory untouched; --max-steps / --batch-size / --seq-len override the positional / environment values; the same
