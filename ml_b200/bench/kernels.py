@@ -366,15 +366,19 @@ def main():
     ap.add_argument("what", choices=["gemm", "corun", "layouts", "mma", "attn", "norm", "once"])
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--case", default="attn", choices=["attn", "gemm", "gemm8", "norm", "vision"])
-    ap.add_argument("--M", type=int, default=16384)
+    # the reference's micro-benchmark knobs set the defaults: ENTROPY_BENCH_BT = rows of the GEMM shapes
+    # (train/gemm_bench.cu:166), ENTROPY_BENCH_B / ENTROPY_BENCH_STEPS = attention batch and timed launches
+    # (train/attn_bench.cu:61-62)
+    env_int = lambda k, d: int(os.environ[k]) if os.environ.get(k, "").isdigit() and int(os.environ[k]) > 0 else d
+    ap.add_argument("--M", type=int, default=env_int("ENTROPY_BENCH_BT", 16384))
     ap.add_argument("--C", type=int, default=768)
     ap.add_argument("--I", type=int, default=2048)
     ap.add_argument("--V", type=int, default=50304)
-    ap.add_argument("--B", type=int, default=16)
+    ap.add_argument("--B", type=int, default=env_int("ENTROPY_BENCH_B", 16))
     ap.add_argument("--T", type=int, default=1024)
     ap.add_argument("--H", type=int, default=12)
     ap.add_argument("--hd", type=int, default=64)
-    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=env_int("ENTROPY_BENCH_STEPS", 20))
     ap.add_argument("--warm", type=int, default=10)
     ap.add_argument("--fp8", action="store_true", help="gemm: add the 8-bit (E4M3) forward product and the bf16 -> E4M3 cast per shape")
     ap.add_argument("--chain", action="store_true", help="gemm: 24 launches back to back per sample, no synchronisation or flush in between")

@@ -134,7 +134,11 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--compile", action="store_true", help="wrap the module in torch.compile (the reference script's option)")
-    ap.add_argument("--f32-master", action="store_true", help="fp32 parameters under bf16 autocast instead of pure-bf16 parameters")
+    ap.add_argument("--f32-master", action="store_true", default=os.environ.get("ENTROPY_F32_MASTER", "0") == "1",
+                    help="fp32 parameters under bf16 autocast instead of pure-bf16 parameters (also ENTROPY_F32_MASTER=1, the "
+                         "fair-comparison switch of reference/bench_jax.py:30)")
+    ap.add_argument("--data", default="", help="llm.c token file: every step trains on the next window instead of one fixed "
+                                               "random batch (reference/bench_jax.py:45-60)")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     a = ap.parse_args(argv)
     cfg = Config.from_env()
@@ -151,10 +155,20 @@ def main(argv=None) -> int:
     g = torch.Generator(device=dev).manual_seed(7)
     ids = torch.randint(0, cfg.V, (a.B, cfg.T), device=dev, generator=g)
     tgt = torch.randint(0, cfg.V, (a.B, cfg.T), device=dev, generator=g)
+    loader = None
+    if a.data:
+        from ..data import TokenLoader
+        loader = TokenLoader(a.data, a.B, cfg.T, vocab=cfg.V)
+        h_ids = torch.empty(a.B * cfg.T, dtype=torch.int32, pin_memory=cuda)
+        h_tgt = torch.empty_like(h_ids, pin_memory=cuda)
     name = torch.cuda.get_device_properties(dev).name if cuda else "cpu"
     print(f"torch {torch.__version__} on {name}  params={nparam / 1e6:.1f}M  compile={a.compile}  f32_master={a.f32_master}")
 
     def step():
+        if loader is not None:
+            loader.next_into(h_ids, h_tgt)
+            ids.copy_(h_ids.view(a.B, cfg.T), non_blocking=True)
+            tgt.copy_(h_tgt.view(a.B, cfg.T), non_blocking=True)
         opt.zero_grad(set_to_none=True)
         if cuda and a.f32_master:
             with torch.autocast("cuda", dtype=torch.bfloat16):

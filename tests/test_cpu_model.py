@@ -220,10 +220,18 @@ def test_torch_baseline_module_is_a_whole_model_oracle(capsys):
     os.environ.update(ENTROPY_V="64", ENTROPY_C="32", ENTROPY_L="1", ENTROPY_H="2", ENTROPY_I="64", ENTROPY_T="16")
     try:
         assert main(["--B", "2", "--steps", "2", "--warmup", "1", "--device", "cpu"]) == 0
+        # the same loop over an llm.c token file (a new window every step), fp32 parameters asked for by the environment
+        import tempfile
+        from ml_b200.data import write_token_bin
+        with tempfile.TemporaryDirectory() as d:
+            write_token_bin(d + "/t.bin", torch.arange(0, 400, dtype=torch.int32) % 64)
+            os.environ["ENTROPY_F32_MASTER"] = "1"
+            assert main(["--B", "2", "--steps", "2", "--warmup", "1", "--device", "cpu", "--data", d + "/t.bin"]) == 0
     finally:
         os.environ.clear()
         os.environ.update(old)
-    assert "tok/s" in capsys.readouterr().out
+    out = capsys.readouterr().out
+    assert out.count("tok/s") == 2 and "f32_master=True" in out
 
 
 def test_fp8_forward_option_rounds_forward_operands_only():
