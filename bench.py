@@ -29,7 +29,6 @@ import statistics
 import subprocess
 import sys
 import sysconfig
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -280,7 +279,7 @@ def run_ours(args):
     import torch.distributed as dist
     from ml_b200 import Config, RunConfig, VisionConfig
     from ml_b200.layout import flops_per_step
-    from ml_b200.parallel.bootstrap import init_distributed, shutdown
+    from ml_b200.parallel.bootstrap import init_distributed, leave
     from ml_b200.trainer import Trainer
     from ml_b200.data import bench_batch, mm_batch, random_pixels
     from ml_b200.ops import native
@@ -432,17 +431,7 @@ def run_ours(args):
     sys.stdout.flush()
     # ---- teardown: a communicator cannot be destroyed while a CUDA graph that recorded its collectives is alive, so the
     # graph goes first; the destroy runs under a watchdog so that a teardown that blocks cannot hold the benchmark
-    if tr is not None:
-        tr.close()
-    if world > 1:
-        barrier()
-        th = threading.Thread(target=shutdown, daemon=True)
-        th.start()
-        th.join(timeout=20.0)
-        if th.is_alive():
-            sys.stderr.write("process-group teardown did not return within 20 s; leaving without it\n")
-            sys.stderr.flush()
-            os._exit(0)
+    leave([tr])
     return 0
 
 

@@ -168,9 +168,9 @@ def mode_mm_bench(argv):
     if rank == 0:
         print(f"mm step: {dt * 1e3:.2f} ms | text tok/s {world * B * T_text / dt:.0f} | image tok/s {world * B * n_patch / dt:.0f} | loss {ls:.4f}")
     if world > 1:
+        from .parallel.bootstrap import leave
         sys.stdout.flush()
-        torch.cuda.synchronize()
-        os._exit(0)
+        leave([tr])
     return 0
 
 
@@ -602,8 +602,8 @@ def mode_bench_fsdp(argv):
                   f"the numbers above are not valid")
     sys.stdout.flush()
     if world > 1:
-        torch.cuda.synchronize()
-        os._exit(0)
+        from .parallel.bootstrap import leave
+        leave()
     return 0
 
 

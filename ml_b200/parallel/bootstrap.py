@@ -44,3 +44,31 @@ def init_distributed(device: Optional[str] = None, timeout_s: float = 600.0, bac
 def shutdown():
     if dist.is_initialized():
         dist.destroy_process_group()
+
+
+def leave(closeables=(), limit_s: float = 20.0) -> bool:
+    """Orderly end of a multi-process benchmark or training mode.  A communicator cannot be destroyed while a CUDA graph
+    that recorded its collectives is alive, so everything with a `close()` (a Trainer drops its captured graph there)
+    goes first; then the device is drained, the ranks meet at a barrier, and the process group is destroyed under a
+    watchdog.  Returns True after a clean teardown.  If the destroy has not returned after `limit_s` seconds the process
+    says so on stderr and exits with status 0 at once: the results are printed by then, and a benchmark should not be
+    held (or turned into a failure) by its teardown."""
+    import sys
+    import threading
+    for c in closeables:
+        if c is not None:
+            c.close()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if not dist.is_initialized():
+        return True
+    dist.barrier()
+    th = threading.Thread(target=shutdown, daemon=True)
+    th.start()
+    th.join(timeout=limit_s)
+    if th.is_alive():
+        sys.stdout.flush()
+        sys.stderr.write(f"process-group teardown did not return within {limit_s:.0f} s; leaving without it\n")
+        sys.stderr.flush()
+        os._exit(0)
+    return True
