@@ -154,6 +154,21 @@ def get_error() -> int:
     return 0
 
 
+_ERR_CODES = {1: "an mbarrier wait inside a kernel's pipeline ran out", 2: "a wait on a peer's or the host's flag ran out",
+              3: "an index was out of range"}
+_ERR_BOUNDS = {0xE1: "token id outside the vocabulary (embedding forward)", 0xE2: "token id outside the vocabulary (embedding backward)",
+               0xCE: "target outside the vocabulary (cross-entropy)"}
+
+
+def describe_error(err: int) -> str:
+    """The error word in words: (code << 24) | detail, see csrc/common.cuh."""
+    code, detail = err >> 24, err & 0xFFFFFF
+    text = _ERR_CODES.get(code, f"code {code}")
+    if code == 3 and detail in _ERR_BOUNDS:
+        return f"{text}: {_ERR_BOUNDS[detail]}"
+    return f"{text}, detail {detail:#x}"
+
+
 def read_errors_async(host_words: torch.Tensor):
     """The four error words copied into `host_words` (pinned int32[4]) behind the current stream's work, without a
     synchronisation of their own: a caller that synchronises the stream anyway (to read a loss) checks them for free."""

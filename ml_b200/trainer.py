@@ -221,7 +221,7 @@ class Trainer:
         from .ops import native
         err = native.get_error()
         if err:
-            raise RuntimeError(f"kernel error word {err:#x} (code {err >> 24}, detail {err & 0xFFFFFF:#x}); "
+            raise RuntimeError(f"kernel error word {err:#x} ({native.describe_error(err)}); "
                                f"the results since the last check are invalid")
 
     def probe_grad_step(self, steps: int = 3) -> dict:

@@ -336,3 +336,21 @@ def test_one_stream_run_matches_the_multi_stream_run(tmp_path, monkeypatch):
     d = (res["0"][1][1] - res["1"][1][1]).abs()
     assert d.max().item() < 2 * 1e-3 * steps and d.mean().item() < 2e-5, (d.max().item(), d.mean().item())
     assert _native().get_error() == 0
+
+
+def test_step_host_refuses_a_token_id_beyond_the_vocabulary():
+    """The public step call reads the kernels' error words with the loss: a batch with a token id >= V raises with the
+    reason in words (the embedding skipped that row instead of indexing past its table), and the next clean batch
+    trains as usual."""
+    cfg, B = Config(V=256, C=128, L=2, H=4, I=256, T=64), 2
+    tr = Trainer(cfg, B, "cuda:0")
+    ids, tgt = Stream(3).token_pairs(B * cfg.T, cfg.V)
+    bad = ids.clone()
+    bad[7] = cfg.V + 100
+    with pytest.raises(RuntimeError, match="token id outside the vocabulary"):
+        tr.step_host(bad.pin_memory(), tgt.pin_memory())
+    _native().clear_error()
+    loss = tr.step_host(ids.pin_memory(), tgt.pin_memory())
+    assert 4.0 < loss < 7.0, loss
+    assert _native().get_error() == 0
+    tr.close()
