@@ -11,6 +11,7 @@ thread only enqueues copies.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -163,6 +164,44 @@ class BatchPipe:
             pass
 
 
+def is_llmc_bin(path: str) -> bool:
+    """True if the file starts with the llm.c header word."""
+    import struct
+    with open(path, "rb") as f:
+        head = f.read(4)
+    return len(head) == 4 and struct.unpack("<i", head)[0] == 20240520
+
+
+def read_raw_tokens(path: str):
+    """Token ids of a file in one of the prototype loader's formats (csrc/src/data_loader.cu:13-180): raw little-endian
+    uint32 without header (`.bin` / `.tokens`), or whitespace-separated decimal ids (anything else).  numpy uint32."""
+    import numpy as np
+    if path.endswith(".bin") or path.endswith(".tokens"):
+        return np.fromfile(path, dtype="<u4")
+    with open(path) as f:
+        return np.array([int(t) for t in f.read().split()], dtype=np.uint32)
+
+
+def open_token_file(path: str, B: int, T: int, vocab: int = 0, scratch_dir: str = "") -> "TokenLoader":
+    """A `TokenLoader` over `path`, whatever its format: an llm.c file is opened as it is; a raw uint32 or text token
+    file is first rewritten in the llm.c format (16-bit ids, so every id must be below 65536) under `scratch_dir`
+    (default: the system's temporary directory), one private copy per process."""
+    if is_llmc_bin(path):
+        return TokenLoader(path, B, T, vocab=vocab)
+    import tempfile
+    arr = read_raw_tokens(path)
+    if arr.size and int(arr.max()) >= 65536:
+        raise ValueError(f"{path}: token id {int(arr.max())} does not fit the 16-bit ids of the llm.c format the loader streams")
+    d = scratch_dir or tempfile.gettempdir()
+    os.makedirs(d, exist_ok=True)
+    out = os.path.join(d, f"{os.path.basename(path)}.{os.getpid()}.llmc.bin")
+    write_token_bin(out, torch.from_numpy(arr.astype("int32")))
+    ld = TokenLoader(out, B, T, vocab=vocab)
+    os.unlink(out)            # the mapping keeps the data; nothing is left behind
+    ld.path = path
+    return ld
+
+
 class RawTokenLoader:
     """The prototype loader's formats (csrc/src/data_loader.cu:13-180): a `.bin` / `.tokens` file of raw little-endian
     uint32 tokens without header, or a whitespace-separated text file of token ids.  `next()` returns input ids,
@@ -170,12 +209,7 @@ class RawTokenLoader:
     whole samples (the reference shuffles single tokens, which destroys the sequences)."""
 
     def __init__(self, path: str, B: int, T: int, shuffle: bool = False, seed: int = 0):
-        import numpy as np
-        if path.endswith(".bin") or path.endswith(".tokens"):
-            arr = np.fromfile(path, dtype="<u4")
-        else:
-            with open(path) as f:
-                arr = np.array([int(t) for t in f.read().split()], dtype=np.uint32)
+        arr = read_raw_tokens(path)
         n = arr.size // T
         if n < B:
             raise OSError(f"{path}: {arr.size} tokens are fewer than one batch of {B}x{T}")

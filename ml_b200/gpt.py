@@ -231,7 +231,7 @@ def _train_loop(argv, ddp):
     import torch.distributed as dist
     from . import Config, RunConfig
     from .trainer import Trainer
-    from .data import TokenLoader, BatchPipe
+    from .data import TokenLoader, BatchPipe, open_token_file
     from .layout import flops_per_step
     from .parallel.bootstrap import init_distributed, shutdown
     from .utils import ckpt as ck
@@ -306,7 +306,7 @@ def _train_loop(argv, ddp):
     B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
     tr = Trainer(cfg, B, dev, run, lr=a.lr, wd=a.weight_decay, world=world, rank=rank,
                  use_graph=bool(run.train_graph) and a.warmup_ratio <= 0)
-    loader = TokenLoader(a.bin, B * tr.accum, cfg.T, vocab=cfg.V)
+    loader = open_token_file(a.bin, B * tr.accum, cfg.T, vocab=cfg.V)
     if rank == 0:
         run.warn_ineffective()
         print(f"loader: {a.bin}  {loader.ntok} tokens")
@@ -333,7 +333,7 @@ def _train_loop(argv, ddp):
     eval_loader = None
     if a.eval_every > 0:
         # held-out file if given, else the tail of the training file read from its last windows backwards in file order
-        eval_loader = TokenLoader(a.eval_bin or a.bin, B, cfg.T, vocab=cfg.V)
+        eval_loader = open_token_file(a.eval_bin or a.bin, B, cfg.T, vocab=cfg.V)
         if rank == 0 and a.verbose:
             print(f"eval: {a.eval_bin or a.bin}  {eval_loader.ntok} tokens, {a.eval_batches} batches every {a.eval_every} steps")
 
@@ -439,7 +439,7 @@ def _train_loop_model_parallel(a):
     import torch
     import torch.distributed as dist
     from . import Config, RunConfig
-    from .data import TokenLoader
+    from .data import TokenLoader, open_token_file
     from .parallel.bootstrap import init_distributed, shutdown
     rank, world, local, dev = init_distributed()
     if rank == 0:
@@ -467,7 +467,7 @@ def _train_loop_model_parallel(a):
         from .parallel.pp import PipelineStage
         M = a.microbatches if a.microbatches > 0 else run.microbatches
         eng = PipelineStage(cfg, B, a.pp_size, rank, dev, microbatches=M, hyper=hyper)
-    loader = TokenLoader(a.bin, B * M, cfg.T, vocab=cfg.V)
+    loader = open_token_file(a.bin, B * M, cfg.T, vocab=cfg.V)
     if rank == 0:
         print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} cp={a.cp_size} ({a.cp_mode}) steps={a.steps}")
     n = B * cfg.T

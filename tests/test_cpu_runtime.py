@@ -304,6 +304,40 @@ def test_cli_prototype_flags_and_vocabulary_check(tmp_path):
     assert c.returncode != 0 and "token file is required" in c.stderr
 
 
+def test_train_reads_the_prototype_loaders_token_files(tmp_path):
+    """A raw little-endian uint32 file (`.tokens`) and a text file of ids (the prototype loader's formats,
+    csrc/src/data_loader.cu:13-180) train to the same losses as the llm.c file with the same tokens; ids that do not
+    fit 16 bits are refused with a message."""
+    import subprocess, sys
+    import numpy as np
+    from ml_b200.data import open_token_file
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    toks = (torch.arange(0, 3000, dtype=torch.int64) * 7919 % 251).to(torch.int32)
+    llmc, raw, txt = str(tmp_path / "d.bin"), str(tmp_path / "d.tokens"), str(tmp_path / "d.txt")
+    write_token_bin(llmc, toks)
+    toks.numpy().astype("<u4").tofile(raw)
+    with open(txt, "w") as f:
+        f.write(" ".join(str(int(t)) for t in toks))
+    env = dict(os.environ, ENTROPY_DEVICE="cpu", ENTROPY_V="256", ENTROPY_C="32", ENTROPY_L="1", ENTROPY_H="2", ENTROPY_I="64",
+               ENTROPY_T="16", ENTROPY_B="2", ENTROPY_LOG_EVERY="2", PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    out = {}
+    for name, path in (("llmc", llmc), ("raw", raw), ("txt", txt)):
+        r = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "train", "--data", path, "4"], env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        out[name] = [l.split("|")[1] for l in r.stdout.splitlines() if l.startswith("step ")]
+    assert len(out["llmc"]) == 2 and out["llmc"] == out["raw"] == out["txt"], out
+    ld = open_token_file(raw, 2, 16, scratch_dir=str(tmp_path / "scratch"))
+    assert ld.ntok == 3000 and ld.path == raw
+    ids, tgt = ld.next()
+    assert ids.tolist() == toks[:32].tolist() and tgt.tolist() == toks[1:33].tolist()
+    ld.close()
+    assert os.listdir(tmp_path / "scratch") == []         # the rewritten copy lives only as the loader's mapping
+    big = str(tmp_path / "big.tokens")
+    np.array([1, 2, 70000, 4] * 20, dtype="<u4").tofile(big)
+    with pytest.raises(ValueError, match="70000 does not fit"):
+        open_token_file(big, 1, 8)
+
+
 def test_cli_train_eval_flags_and_chunked_head(tmp_path):
     """--eval-every / --eval-bin print a forward-only held-out loss, log it under eval/loss, and leave the training
     trajectory untouched; --max-steps / --batch-size / --seq-len override the positional / environment values; the same
