@@ -33,6 +33,18 @@ _FLAGS_FOR_HASH = " ".join(f for f in NVCC_FLAGS if f != str(CSRC))
 # One library serves single- and multi-GPU runs: every TMA load in these sources is a plain per-CTA load.
 
 
+def external_lib(name: str):
+    """MLB_LIB_DIR=<dir>: use the libraries some other build put there (the CMake project at the repository root, a
+    packager's build) as they are - no staleness check, no rebuild.  Returns the path, or None when the variable is unset."""
+    d = os.environ.get("MLB_LIB_DIR", "")
+    if not d:
+        return None
+    path = Path(d) / name
+    if not path.exists():
+        raise FileNotFoundError(f"MLB_LIB_DIR={d} has no {name}")
+    return path
+
+
 def _nvcc():
     for c in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if c and os.path.exists(c):

@@ -20,12 +20,13 @@ _i32, _i64, _f32, _vp = C.c_int, C.c_long, C.c_float, C.c_void_p
 
 @lru_cache(maxsize=1)
 def lib():
-    if not _build.is_fresh(_build.CUDA_LIB, _build.cuda_hash()):
+    ext = _build.external_lib("libmlb_cuda.so")
+    if ext is None and not _build.is_fresh(_build.CUDA_LIB, _build.cuda_hash()):
         if _build.CUDA_LIB.exists() and _build._nvcc() is None:
             pass  # no compiler on this machine: use the library that travelled with the tree
         else:
             _build.build_cuda()
-    L = C.CDLL(str(_build.CUDA_LIB))
+    L = C.CDLL(str(ext or _build.CUDA_LIB))
     sig = {
         "mlb_linear_fwd": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],
         "mlb_linear_dx": [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp],

@@ -9,9 +9,10 @@ from .. import build as _build
 
 @lru_cache(maxsize=1)
 def lib():
-    if not _build.is_fresh(_build.HOST_LIB, _build.host_hash()):
+    ext = _build.external_lib("libmlb_host.so")
+    if ext is None and not _build.is_fresh(_build.HOST_LIB, _build.host_hash()):
         _build.build_host()
-    L = C.CDLL(str(_build.HOST_LIB))
+    L = C.CDLL(str(ext or _build.HOST_LIB))
     u64, i64, i32, vp, cp, f32, f64 = C.c_uint64, C.c_int64, C.c_int32, C.c_void_p, C.c_char_p, C.c_float, C.c_double
     sig = {
         "mlb_rng_normal": (u64, [u64, vp, i64, f32]),

@@ -338,6 +338,23 @@ def test_train_reads_the_prototype_loaders_token_files(tmp_path):
         open_token_file(big, 1, 8)
 
 
+def test_external_library_directory(tmp_path, monkeypatch):
+    """MLB_LIB_DIR points the loaders at libraries built elsewhere (the CMake project at the repository root): unset it
+    changes nothing, a directory without the library is an error rather than a silent fall-back to the in-tree one."""
+    from ml_b200 import build
+    monkeypatch.delenv("MLB_LIB_DIR", raising=False)
+    assert build.external_lib("libmlb_host.so") is None
+    monkeypatch.setenv("MLB_LIB_DIR", str(tmp_path))
+    with pytest.raises(FileNotFoundError, match="has no libmlb_host.so"):
+        build.external_lib("libmlb_host.so")
+    build.build_host()
+    monkeypatch.setenv("MLB_LIB_DIR", str(build.LIB))
+    assert build.external_lib("libmlb_host.so") == build.HOST_LIB
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cm = open(os.path.join(root, "CMakeLists.txt")).read()
+    assert "100a" in cm and "ml_b200/csrc" in cm and "no_alloc.h" in cm
+
+
 def test_cli_train_eval_flags_and_chunked_head(tmp_path):
     """--eval-every / --eval-bin print a forward-only held-out loss, log it under eval/loss, and leave the training
     trajectory untouched; --max-steps / --batch-size / --seq-len override the positional / environment values; the same
