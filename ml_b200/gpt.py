@@ -252,6 +252,8 @@ def _train_loop(argv, ddp):
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
     ap.add_argument("--warmup-ratio", type=float, default=0.0)
+    ap.add_argument("--max-grad-norm", type=float, default=0.0,
+                    help="clip the gradient of the whole model to this L2 norm (0 = off; with several ranks needs ENTROPY_COMM=nccl)")
     ap.add_argument("--max-steps", type=int, default=0, help="same as the positional step count")
     ap.add_argument("--batch-size", type=int, default=0, help="per-GPU micro-batch (default ENTROPY_B or 16)")
     ap.add_argument("--seq-len", type=int, default=0, help="sequence length (default ENTROPY_T)")
@@ -305,7 +307,7 @@ def _train_loop(argv, ddp):
     run = RunConfig.from_env()
     B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
     tr = Trainer(cfg, B, dev, run, lr=a.lr, wd=a.weight_decay, world=world, rank=rank,
-                 use_graph=bool(run.train_graph) and a.warmup_ratio <= 0)
+                 use_graph=bool(run.train_graph) and a.warmup_ratio <= 0, max_grad_norm=a.max_grad_norm)
     loader = open_token_file(a.bin, B * tr.accum, cfg.T, vocab=cfg.V)
     if rank == 0:
         run.warn_ineffective()
@@ -399,7 +401,10 @@ def _train_loop(argv, ddp):
                 print(f"step {step + 1:5d} | loss {loss:.4f} | {dt * 1e3:.2f} ms | {win * world / dt:.0f} tok/s | "
                       f"{fl / dt / 1e12:.1f} TFLOP/s | MFU {100 * fl / dt / peak:.1f}%")
                 if logger:
-                    logger.log(step + 1, loss, tr.hyper["lr"], tokens_seen, dt * 1e3, {"mfu": fl / dt / peak, "tflops": fl / dt / 1e12})
+                    extra = {"mfu": fl / dt / peak, "tflops": fl / dt / 1e12}
+                    if tr.grad_norm is not None:
+                        extra["grad_norm"] = float(tr.grad_norm)
+                    logger.log(step + 1, loss, tr.hyper["lr"], tokens_seen, dt * 1e3, extra)
         if eval_loader is not None and ((step + 1) % a.eval_every == 0 or step + 1 == a.steps):
             ev = evaluate()
             if rank == 0:

@@ -42,6 +42,8 @@ class DDP:
         self.t = 1
         self.dev_hyper = None      # CUDA fp32[4] {lr, 1/bc1, 1/bc2, grad_scale}: set by a graph-replaying trainer
         self.reduce_now = True
+        self.clip_coef = 1.0       # host-side gradient-clipping factor of the current step (the CPU path; on CUDA the
+                                   # trainer writes the clipped scale into dev_hyper instead)
         self.scale = 1.0 / (self.world * self.accum)
         self.comm_stream = streams.side_stream(model.device) if self.cuda else None
         self.staging = torch.empty(model.np, dtype=torch.bfloat16, device=model.device) if self.bf16_reduce and comm == "nccl" else None
@@ -100,7 +102,7 @@ class DDP:
 
     def _adamw(self, off, n):
         h = self.hyper
-        self.model.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, self.adamw_grad_scale, off, n, self.dev_hyper)
+        self.model.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, self.adamw_grad_scale * self.clip_coef, off, n, self.dev_hyper)
 
     def _side_adamw(self, off, n):
         ev = torch.cuda.Event()

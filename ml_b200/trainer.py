@@ -22,7 +22,10 @@ from . import ops
 class Trainer:
     def __init__(self, cfg: Config, B: int, device="cuda", run: Optional[RunConfig] = None, lr=1e-4, wd=0.1,
                  b1=0.9, b2=0.95, eps=1e-8, world=1, rank=0, group=None, seed=1234, use_graph=False,
-                 vision: Optional[VisionConfig] = None, n_text: Optional[int] = None):
+                 vision: Optional[VisionConfig] = None, n_text: Optional[int] = None, max_grad_norm: float = 0.0):
+        """max_grad_norm > 0: the gradient of the whole model (decoder and vision tower together, mean over ranks and
+        micro-batches) is scaled down to that L2 norm when it is longer, by folding the factor into the scale the AdamW
+        kernels apply anyway - no extra pass writes the gradients.  The norm of the last step stays in `grad_norm`."""
         self.cfg, self.B, self.run = cfg, B, run or RunConfig()
         self.device = torch.device(device)
         self.world, self.rank = world, rank
@@ -51,6 +54,16 @@ class Trainer:
                        opt_hyper=self.hyper, rank=rank,
                        fused_bf16=fused_bf16 or bool(self.run.extra.get("fused_bf16", False)))
         self.accum = self.ddp.accum
+        self.max_grad_norm = float(max_grad_norm)
+        self.grad_norm = None      # 0-d tensor: L2 norm of the mean gradient of the last step, before clipping
+        if self.max_grad_norm > 0:
+            # one buffer for the life of the trainer: a captured graph writes it in place at every replay
+            self.grad_norm = torch.zeros((), dtype=torch.float32, device=self.device)
+            if world > 1 and self.ddp.fused is not None:
+                raise ValueError("gradient clipping needs the whole reduced gradient before the optimizer runs; the fused "
+                                 "data-parallel step updates shard by shard while it reduces: use ENTROPY_COMM=nccl")
+            if self.ddp.overlap_opt:
+                raise ValueError("gradient clipping and the per-slice optimizer behind backward exclude each other")
         if self.device.type == "cuda" and "ENTROPY_ATTN" in self.run.extra.get("explicit", ()):
             from .ops import native as _native
             _native.lib().mlb_attn_force_simt(1 if self.run.attn == "flash" else 0)     # the reference's scalar flash back end
@@ -108,7 +121,12 @@ class Trainer:
             self._micro(k)
         if self._probe is not None:
             self._probe[0].record()
+        clip = self.max_grad_norm > 0
+        if clip and self.ddp.fused is not None:
+            self._clip()             # one rank: the gradients are final, and finish() launches the kernel that applies them
         done = self.ddp.finish()
+        if clip and self.ddp.fused is None:
+            self._clip()             # library collectives: finish() has joined the reductions
         if done and self.model.params8 is not None:
             self.model.refresh_params8()     # parameters came from the bucket kernels (bf16 only): rebuild the E4M3 copy
         h = self.hyper
@@ -120,11 +138,11 @@ class Trainer:
                 self.vfused.bucket(0, self.vision.np, 1.0 / (self.world * self.accum), h, self.t, self.d_hyper_v)
                 self.vfused.finish()
             else:
-                if self.world > 1:
+                if self.world > 1 and not clip:
                     import torch.distributed as dist
                     dist.all_reduce(self.vision.grads, group=self.ddp.group)
-                self.vision.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, 1.0 / (self.world * self.accum),
-                                  self.d_hyper_v)
+                self.vision.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t,
+                                  self.ddp.clip_coef / (self.world * self.accum), self.d_hyper_v)
         # mean loss of the last micro-batch, reduced on the device (one float to read back)
         BT = self.B * self.cfg.T
         valid = self.B * self.n_text if self.vision is not None else BT
@@ -132,8 +150,29 @@ class Trainer:
             self._probe[1].record()
         ops.sum_scale(self.d_loss, self.model.losses[:BT], 1.0 / valid)
 
+    def _clip(self):
+        """Global-norm clipping folded into the optimizer's gradient scale: coef = min(1, max_norm / |mean gradient|).
+        On CUDA the two scales the AdamW kernels read from device memory are overwritten by device arithmetic (no
+        synchronisation, capturable); on the CPU the factor goes through the host."""
+        m, v = self.model, self.vision
+        base, sv = self.ddp.adamw_grad_scale, 1.0 / (self.world * self.accum)
+        sq = torch.linalg.vector_norm(m.grads).square() * (base * base)
+        if v is not None:
+            if self.world > 1 and self.vfused is None:
+                import torch.distributed as dist
+                dist.all_reduce(v.grads, group=self.ddp.group)      # (moved up from the vision optimizer step)
+            sq = sq + torch.linalg.vector_norm(v.grads).square() * (sv * sv)
+        self.grad_norm.copy_(sq.sqrt())
+        coef = torch.clamp(self.max_grad_norm / (self.grad_norm + 1e-6), max=1.0)
+        if self.d_hyper is not None:
+            self.d_hyper[3:4].copy_((coef * base).reshape(1))
+            self.d_hyper_v[3:4].copy_((coef * sv).reshape(1))
+        else:
+            self.ddp.clip_coef = float(coef)
+
     def step(self):
         """Runs one optimizer step on the batch currently in self.ids / self.tgt."""
+        self.ddp.clip_coef = 1.0
         self.ddp.t = self.t
         self._push_hyper()
         if self.use_graph:

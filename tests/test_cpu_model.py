@@ -328,3 +328,49 @@ def test_guard_bands_around_activation_buffers():
     plain = GPT(cfg, 2, "cpu")
     with pytest.raises(RuntimeError, match="without canaries"):
         plain.check_canaries()
+
+
+def test_gradient_clipping_is_folded_into_the_optimizer_scale():
+    """Trainer(max_grad_norm=): the step equals a hand-made one that measures the gradient's L2 norm and hands
+    min(1, max / norm) to AdamW as its gradient scale; the gradients themselves are not rewritten; with accumulation the
+    norm is that of the mean gradient; the combinations that cannot see the whole gradient are refused."""
+    from ml_b200.trainer import Trainer
+    cfg, B = Config(V=64, C=32, L=2, H=2, I=64, T=16), 2
+    ids, tgt = Stream(5).token_pairs(B * cfg.T, cfg.V)
+    g = GPT(cfg, B)
+    g.init_weights(1234)
+    tr = Trainer(cfg, B, "cpu", lr=1e-2, wd=0.0, max_grad_norm=0.05)
+    plain = Trainer(cfg, B, "cpu", lr=1e-2, wd=0.0)
+    tr.set_batch(ids, tgt)
+    plain.set_batch(ids, tgt)
+    coefs = []
+    for t in range(1, 4):
+        g.forward(ids)
+        g.backward(ids, tgt)
+        nrm = float(g.grads.norm())
+        coefs.append(min(1.0, 0.05 / (nrm + 1e-6)))
+        g.adamw(1e-2, wd=0.0, t=t, grad_scale=coefs[-1])
+        tr.step()
+        plain.step()
+        assert abs(float(tr.grad_norm) - nrm) < 1e-5 * nrm
+        assert torch.equal(tr.model.grads, g.grads)
+    assert max(coefs) < 0.5                                   # the clip was active in every step
+    assert (tr.model.master - g.master).abs().max() < 1e-6
+    assert (tr.model.master - plain.model.master).abs().max() > 1e-4      # and it matters (Adam's moments saw scaled gradients)
+    assert plain.grad_norm is None
+    # accumulation: two micro-batches, the norm is that of their mean
+    from ml_b200 import RunConfig
+    r = RunConfig()
+    r.accum = 2
+    ta = Trainer(cfg, B, "cpu", r, lr=1e-2, wd=0.0, max_grad_norm=0.05)
+    ta.set_batch(torch.stack([ids, ids]), torch.stack([tgt, tgt]))
+    ta.step()
+    g2 = GPT(cfg, B)
+    g2.init_weights(1234)
+    g2.forward(ids)
+    g2.backward(ids, tgt)
+    assert abs(float(ta.grad_norm) - float(g2.grads.norm())) < 1e-5     # the mean of two equal micro-batches
+    r2 = RunConfig()
+    r2.overlap_opt = 1
+    with pytest.raises(ValueError, match="exclude each other"):
+        Trainer(cfg, B, "cpu", r2, max_grad_norm=1.0)

@@ -291,12 +291,16 @@ def test_cli_prototype_flags_and_vocabulary_check(tmp_path):
     env = dict(os.environ, ENTROPY_DEVICE="cpu", ENTROPY_V="256", ENTROPY_C="32", ENTROPY_L="1", ENTROPY_H="2", ENTROPY_I="64",
                ENTROPY_T="16", ENTROPY_B="2", PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
     a = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "train", "--data", p, "6", "--output", str(tmp_path / "out"),
-                        "--save-every", "3", "--log-every", "2", "--wandb-project", "x", "--wandb-run-name", "y"],
+                        "--save-every", "3", "--log-every", "2", "--wandb-project", "x", "--wandb-run-name", "y",
+                        "--max-grad-norm", "0.5", "--log-dir", str(tmp_path / "log")],
                        env=env, capture_output=True, text=True, timeout=300)
     assert a.returncode == 0, a.stdout + a.stderr
     steps = [int(l.split()[1]) for l in a.stdout.splitlines() if l.startswith("step ")]
     assert steps == [2, 4, 6], a.stdout
     assert ck.latest_step(str(tmp_path / "out")) == 6
+    import json
+    rows = [json.loads(l) for l in open(tmp_path / "log" / "metrics.jsonl")]
+    assert len(rows) == 3 and all(r["grad_norm"] > 0 for r in rows), rows
     b = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "train", p, "4"], env=dict(env, ENTROPY_V="128"),
                        capture_output=True, text=True, timeout=300)
     assert b.returncode != 0 and "outside the model's vocabulary of 128" in b.stderr, b.stdout + b.stderr

@@ -354,3 +354,40 @@ def test_step_host_refuses_a_token_id_beyond_the_vocabulary():
     assert 4.0 < loss < 7.0, loss
     assert _native().get_error() == 0
     tr.close()
+
+
+@pytest.mark.parametrize("comm", ["fused", "nccl"])
+def test_gradient_clipping_on_the_device(comm):
+    """max_grad_norm on CUDA: the norm and the clipped scale are computed by device arithmetic and land in the scalars
+    the AdamW kernels read (the fused reduce + AdamW kernel of one rank, or the separate optimizer kernel), eager and
+    under graph replay; AdamW's first moment shows that the kernels applied the clipped scale."""
+    from ml_b200 import RunConfig
+    cfg, B, mx = Config(V=512, C=256, L=2, H=4, I=512, T=128), 2, 0.05
+    ids, tgt = Stream(7).token_pairs(B * cfg.T, cfg.V)
+    _native().lib().mlb_gemm_set_splits(1)
+    res = {}
+    try:
+        for name, graph, clip in (("eager", False, mx), ("graph", True, mx), ("plain", False, 0.0)):
+            r = RunConfig()
+            r.comm = comm
+            tr = Trainer(cfg, B, "cuda:0", r, lr=1e-3, wd=0.1, use_graph=graph, max_grad_norm=clip)
+            assert (tr.ddp.fused is not None) == (comm == "fused")
+            tr.set_batch(ids.cuda(), tgt.cuda())
+            for s in range(3):
+                tr.step()
+                torch.cuda.synchronize()
+                if clip:
+                    nrm = float(tr.model.grads.norm())
+                    assert abs(float(tr.grad_norm) - nrm) < 1e-3 * nrm, (float(tr.grad_norm), nrm)
+                    assert nrm > 2 * mx                                    # the clip is active
+                    assert abs(float(tr.d_hyper[3]) - mx / (float(tr.grad_norm) + 1e-6)) < 1e-6
+            res[name] = (tr.model.master.clone(), float(tr.model.m.norm()))
+            tr.close()
+    finally:
+        _native().lib().mlb_gemm_set_splits(0)
+    d = (res["eager"][0] - res["graph"][0]).abs()
+    assert d.max().item() < 8e-3 and d.mean().item() < 2e-5, (d.max().item(), d.mean().item())
+    # AdamW's step is almost invariant to a common gradient scale; its first moment is not: the kernels saw gradients
+    # about mx / |g| = 1/60 as long
+    assert res["eager"][1] < 0.1 * res["plain"][1] and res["graph"][1] < 0.1 * res["plain"][1], [v[1] for v in res.values()]
+    assert _native().get_error() == 0
