@@ -475,9 +475,28 @@ def _train_loop_model_parallel(a):
     loader = open_token_file(a.bin, B * M, cfg.T, vocab=cfg.V)
     if rank == 0:
         print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} cp={a.cp_size} ({a.cp_mode}) steps={a.steps}")
+    # Checkpoints: every rank holds its own part of the model (a pipeline stage, a tensor-parallel slice; a replica under
+    # sequence parallelism), so every rank writes its flat fp32 master / moment buffers as weights_rank_<r>.bin /
+    # optim_rank_<r>.bin; meta.bin is published by rank 0 once all of them are on disk.
+    from .utils import ckpt as ck
+    holder = eng if hasattr(eng, "master") else eng.model
+    nst = holder.master.numel()
+    start_step, tokens_seen, last_loss = 0, 0, 0.0
+    if a.ckpt_dir and a.resume != -1:
+        st = ck.latest_step(a.ckpt_dir) if a.resume == -2 else a.resume
+        info = ck.load(a.ckpt_dir, st, holder.master, holder.m, holder.v, rank=rank, shard=(0, nst)) if st is not None else None
+        if info is not None:
+            (eng if hasattr(eng, "master") else eng.model).sync_params()
+            start_step, tokens_seen, eng.t = info["step"], info["tokens_seen"], info["opt_t"]
+            loader.pos = info["loader_pos"]
+            if rank == 0:
+                print(f"resumed from step {start_step} (loss {info['loss']:.4f}, {tokens_seen} tokens seen)")
+        elif rank == 0:
+            print("no checkpoint to resume from; starting fresh")
+    writer = ck.CheckpointWriter() if a.ckpt_dir and a.save_every > 0 else None
     n = B * cfg.T
     t_last = time.perf_counter()
-    for step in range(a.steps):
+    for step in range(start_step, a.steps):
         ids, tgt = loader.next()
         ids, tgt = ids.to(dev), tgt.to(dev)
         eng.hyper["lr"] = lr_at(step, a.steps, a.lr, a.warmup_ratio)
@@ -490,9 +509,22 @@ def _train_loop_model_parallel(a):
             if world > 1:
                 dist.broadcast(t, src=world - 1)           # the last stage (any tensor-parallel rank) knows the loss
             now = time.perf_counter()
+            last_loss = float(t.item())
             if rank == 0:
-                print(f"step {step + 1:5d} | loss {float(t.item()):.4f} | {(now - t_last) * 1e3:.2f} ms since last log")
+                print(f"step {step + 1:5d} | loss {last_loss:.4f} | {(now - t_last) * 1e3:.2f} ms since last log")
             t_last = now
+        tokens_seen += B * M * cfg.T
+        if writer is not None and (step + 1) % a.save_every == 0:
+            writer.save(a.ckpt_dir, step + 1, last_loss, tokens_seen, holder.master, holder.m, holder.v, rank=rank, shard=(0, nst),
+                        loader_pos=loader.pos, opt_t=eng.t, write_meta=False, wait=True)
+            if world > 1:
+                dist.barrier()
+            if rank == 0:
+                ck.write_meta(a.ckpt_dir, step + 1, last_loss, tokens_seen)
+            if world > 1:
+                dist.barrier()
+    if writer is not None:
+        writer.close()
     loader.close()
     if world > 1:
         shutdown()

@@ -187,6 +187,11 @@ class TPTrainer:
             self.hyper.update(hyper)
         self.t = 1
 
+    def sync_params(self):
+        """Compute-dtype parameters from the fp32 master weights (after a checkpoint was loaded into them)."""
+        if self.params is not self.master:
+            self.params.copy_(self.master)
+
     def step(self, ids, tgt) -> float:
         for p, _, _ in self.slices:
             p.grad = None

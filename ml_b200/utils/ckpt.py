@@ -97,6 +97,13 @@ class _null:
         return False
 
 
+def write_meta(root: str, step: int, loss: float, tokens_seen: int):
+    """Publishes step_<N>/meta.bin: the mark that the step's payload (every rank's files) is complete."""
+    rc = lib().mlb_ckpt_write_meta(step_dir(root, step).encode(), int(step), float(loss), int(tokens_seen))
+    if rc:
+        raise OSError(rc, "write meta.bin")
+
+
 def read_meta(root: str, step: int):
     """Returns (step, loss, tokens_seen) or None when there is no such checkpoint (caller starts fresh).
     Raises on a corrupt / truncated meta.bin."""

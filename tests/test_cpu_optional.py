@@ -368,3 +368,41 @@ def test_ring_sequence_parallel_model_equals_full_sequence_model(world, zigzag):
     for _, o in outs:
         line = [l for l in o.splitlines() if l.startswith("RING")][0].split()
         assert float(line[1]) < 1e-5 and float(line[2]) < 2e-5 and float(line[3]) > 1e-3
+
+
+@pytest.mark.parametrize("flags", [["--pp-size", "2", "--microbatches", "4"], ["--tp-size", "2"]], ids=["pipeline", "tensor"])
+def test_model_parallel_modes_checkpoint_and_resume(tmp_path, flags):
+    """`train_ddp --pp-size 2` / `--tp-size 2` with --ckpt-dir: every rank writes its own part of the model, and two
+    steps + resume + two steps print the losses of four uninterrupted steps."""
+    import os
+    import textwrap
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    from ml_b200.utils import ckpt
+    g = _t.Generator().manual_seed(6)
+    path, ck = str(tmp_path / "tok.bin"), str(tmp_path / "ck")
+    write_token_bin(path, _t.randint(0, 64, (4 * 2 * 16 * 6 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "4", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "1", "ENTROPY_DEVICE": "cpu"}
+    body = textwrap.dedent("""
+        import os, sys
+        os.environ.update(ENV)
+        from ml_b200 import gpt
+        sys.exit(gpt.main(ARGS))
+    """)
+    def run(args):
+        outs = run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path] + args + flags + ["--lr", "1e-3"]) + body, 2)
+        assert all(rc == 0 for rc, _ in outs), outs
+        o = [o for _, o in outs if "step " in o][0]
+        return {int(l.split()[1]): float(l.split("loss")[1].split("|")[0]) for l in o.splitlines() if l.startswith("step ")}, o
+    whole, _ = run(["4"])
+    first, _ = run(["2", "--ckpt-dir", ck, "--save-every", "2"])
+    assert ckpt.latest_step(ck) == 2
+    files = sorted(os.listdir(ckpt.step_dir(ck, 2)))
+    assert files == ["meta.bin", "optim_rank_0.bin", "optim_rank_1.bin", "state_rank_0.bin", "state_rank_1.bin",
+                     "weights_rank_0.bin", "weights_rank_1.bin"], files
+    rest, out = run(["4", "--ckpt-dir", ck, "--resume", "-2"])
+    assert "resumed from step 2" in out and sorted(rest) == [3, 4]
+    assert first == {k: whole[k] for k in (1, 2)}
+    for k in (3, 4):
+        assert abs(rest[k] - whole[k]) < 1e-6, (rest, whole)
