@@ -371,10 +371,14 @@ def _train_loop(argv, ddp):
     peak = run.peak_tflops * 1e12 * world
     t_last, s_last = time.perf_counter(), start_step
     loss = float("nan")
+    stop_all = False
     for step in range(start_step, a.steps):
-        if stop["flag"]:
+        # One process stops at once.  Several ranks must leave at the same step (a rank that left alone would strand the
+        # others in their next collective), so they agree at the logging steps, where the loss is all-reduced anyway:
+        # the flag of any rank stops all of them.
+        if stop_all or (stop["flag"] and world == 1):
             if rank == 0:
-                print("signal received: stopping after this step")
+                print("signal received: stopping")
             break
         ids, tgt = pipe.acquire(step)
         tr.ids.copy_(ids.view(tr.accum, -1))
@@ -391,9 +395,10 @@ def _train_loop(argv, ddp):
         if (step + 1) % run.log_every == 0 or step + 1 == a.steps:
             loss = tr.loss()
             if world > 1:
-                t = torch.tensor([loss], device=dev)
+                t = torch.tensor([loss, 1.0 if stop["flag"] else 0.0], device=dev)
                 dist.all_reduce(t)
-                loss = float(t.item()) / world
+                loss = float(t[0].item()) / world
+                stop_all = float(t[1].item()) > 0
             now = time.perf_counter()
             dt = (now - t_last) / max(1, step + 1 - s_last)
             t_last, s_last = now, step + 1
@@ -496,6 +501,12 @@ def _train_loop_model_parallel(a):
     writer = ck.CheckpointWriter() if a.ckpt_dir and a.save_every > 0 else None
     n = B * cfg.T
     t_last = time.perf_counter()
+    stop = {"flag": False}
+    for sig in (signal.SIGINT, signal.SIGTERM):
+        try:
+            signal.signal(sig, lambda *_: stop.__setitem__("flag", True))
+        except ValueError:
+            pass
     for step in range(start_step, a.steps):
         ids, tgt = loader.next()
         ids, tgt = ids.to(dev), tgt.to(dev)
@@ -506,8 +517,10 @@ def _train_loop_model_parallel(a):
             loss = eng.step([ids[k * n:(k + 1) * n] for k in range(M)], [tgt[k * n:(k + 1) * n] for k in range(M)])
         if (step + 1) % run.log_every == 0 or step + 1 == a.steps:
             t = torch.tensor([loss if loss is not None else 0.0], device=dev)
+            f = torch.tensor([1.0 if stop["flag"] else 0.0], device=dev)
             if world > 1:
                 dist.broadcast(t, src=world - 1)           # the last stage (any tensor-parallel rank) knows the loss
+                dist.all_reduce(f)                         # a signal on any rank stops all of them, at the same step
             now = time.perf_counter()
             last_loss = float(t.item())
             if rank == 0:
@@ -523,6 +536,10 @@ def _train_loop_model_parallel(a):
                 ck.write_meta(a.ckpt_dir, step + 1, last_loss, tokens_seen)
             if world > 1:
                 dist.barrier()
+        if ((step + 1) % run.log_every == 0 or step + 1 == a.steps) and float(f.item()) > 0:
+            if rank == 0:
+                print("signal received: stopping")
+            break
     if writer is not None:
         writer.close()
     loader.close()

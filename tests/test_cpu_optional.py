@@ -406,3 +406,31 @@ def test_model_parallel_modes_checkpoint_and_resume(tmp_path, flags):
     assert first == {k: whole[k] for k in (1, 2)}
     for k in (3, 4):
         assert abs(rest[k] - whole[k]) < 1e-6, (rest, whole)
+
+
+@pytest.mark.parametrize("flags", [[], ["--pp-size", "2", "--microbatches", "2"]], ids=["data_parallel", "pipeline"])
+def test_a_signal_on_one_rank_stops_all_ranks_at_the_same_step(tmp_path, flags):
+    """SIGTERM reaches only rank 1 (a supervisor normally signals every rank; this is the hard case): the ranks agree on
+    the stop at a logging step and both leave with status 0 - none is stranded in a collective."""
+    import textwrap
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    g = _t.Generator().manual_seed(6)
+    path = str(tmp_path / "tok.bin")
+    write_token_bin(path, _t.randint(0, 64, (40 * 2 * 16 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "2", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "5", "ENTROPY_DEVICE": "cpu"}
+    body = textwrap.dedent("""
+        import os, sys, signal, threading
+        os.environ.update(ENV)
+        from ml_b200 import gpt
+        if os.environ["RANK"] == "1":
+            threading.Timer(6.0, lambda: os.kill(os.getpid(), signal.SIGTERM)).start()
+        sys.exit(gpt.main(ARGS))
+    """)
+    outs = run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path, "100000"] + flags + ["--lr", "1e-3"]) + body, 2, timeout=240)
+    assert all(rc == 0 for rc, _ in outs), outs
+    o = [o for _, o in outs if "step " in o][0]
+    assert "signal received: stopping" in o and "<timeout>" not in o
+    last = max(int(l.split()[1]) for l in o.splitlines() if l.startswith("step "))
+    assert 5 <= last < 100000 and last % 5 == 0
