@@ -62,6 +62,11 @@ class VisionTower:
             ops.cast(self.params, self.master)
 
     # ------------------------------------------------------------------
+    def sync_params(self):
+        """Compute-dtype parameters from the fp32 master weights (after loading a checkpoint into them)."""
+        if self.params.data_ptr() != self.master.data_ptr():
+            ops.cast(self.params, self.master)
+
     def forward_pixels(self, pixels):
         """pixels: fp32 [B, 3, Himg, Wimg]."""
         ops.patchify(self.patches, pixels, self.vc.patch)

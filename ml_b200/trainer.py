@@ -71,6 +71,7 @@ class Trainer:
             from .ops import native as _native
             _native.gemm_autotune(bool(self.run.autotune))       # plans are timed in the eager step before graph capture
         self.t = 1
+        self._writer = None        # checkpoint writer of save_checkpoint (rank 0)
         self.h_err = None          # pinned copy of the kernels' error words, filled behind every step_host
         self._probe = None         # (event after the last backward, event after the gradient step) of probe_grad_step
         self.skip_adamw = False    # ablation: leave the optimizer out (single GPU, library-collective mode)
@@ -327,6 +328,48 @@ class Trainer:
             if eng is not None:
                 eng.consolidate()
 
+    # ------------------------------------------------------------------ checkpoints (the calls the CLI's train loop makes)
+    def save_checkpoint(self, root: str, step: int, loss: float = 0.0, tokens_seen: int = 0, loader_pos: int = 0,
+                        wait: bool = True):
+        """Writes `root/step_<step>/` (layout of utils/ckpt.py): fp32 master weights and AdamW moments of the decoder and,
+        if there is one, of the vision tower, the optimizer's step count, and per rank the data position `loader_pos`.
+        A collective when there are several ranks - every rank must call it: the fused data-parallel step keeps the
+        fp32 state current only for the shard a rank owns, so it is completed first; rank 0 writes the payload and
+        publishes `meta.bin` last.  wait=False returns while the files are still being written (the next save, or
+        `close()`, waits for them)."""
+        from .utils import ckpt as ck
+        self.consolidate_state()
+        if self.rank != 0:
+            ck.save_state(root, step, self.rank, loader_pos, self.t)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier(group=self.ddp.group)
+        if self.rank == 0:
+            if self._writer is None:
+                self._writer = ck.CheckpointWriter()
+            self._writer.save(root, step, float(loss) if loss == loss else 0.0, int(tokens_seen), self.model.master, self.model.m,
+                              self.model.v, loader_pos=loader_pos, opt_t=self.t, vision=self.vision, wait=wait)
+
+    def load_checkpoint(self, root: str, step: int = -2):
+        """Restores the state written by `save_checkpoint` on every rank (step -2: the latest complete one) and rebuilds
+        the bf16 parameters.  Returns dict(step, loss, tokens_seen, loader_pos, opt_t) with this rank's own data
+        position, or None when there is nothing to load."""
+        from .utils import ckpt as ck
+        st = ck.latest_step(root) if step == -2 else step
+        if st is None:
+            return None
+        info = ck.load(root, st, self.model.master, self.model.m, self.model.v, vision=self.vision)
+        if info is None:
+            return None
+        self.model.sync_params()
+        if self.vision is not None:
+            self.vision.sync_params()
+        self.t = info["opt_t"]
+        own = ck.load_state(root, st, self.rank)
+        if own is not None:
+            info["loader_pos"] = own["loader_pos"]
+        return info
+
     def close(self):
         """Drops the captured graph (a communicator cannot be torn down while a graph that recorded its collectives is
         alive) and waits for the device."""
@@ -335,6 +378,9 @@ class Trainer:
             self.graph = None
         if self.device.type == "cuda":
             torch.cuda.synchronize(self.device)
+        if self._writer is not None:
+            self._writer.close()
+            self._writer = None
 
     def set_batch(self, ids: torch.Tensor, tgt: torch.Tensor):
         self.ids.copy_(ids.view(self.accum, -1))

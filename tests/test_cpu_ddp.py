@@ -186,3 +186,35 @@ def test_gloo_pipeline_1f1b_equals_single_process():
         assert float(line[2]) < 5e-5, line
     last = [l for l in outs[1][1].splitlines() if l.startswith("PPDIFF")][0].split()
     assert last[3] != "None"
+
+
+def test_trainer_checkpoint_methods_two_ranks(tmp_path):
+    """Trainer.save_checkpoint / load_checkpoint as collectives: rank 0 writes the payload, every rank its own data
+    position; fresh trainers on both ranks resume to the uninterrupted run's parameters."""
+    outs = run_ranks(f"""
+        import torch, torch.distributed as dist
+        from ml_b200 import Config, RunConfig
+        from ml_b200.parallel.bootstrap import init_distributed, shutdown
+        from ml_b200.trainer import Trainer
+        from ml_b200.data import bench_batch
+        rank, world, local, dev = init_distributed("cpu")
+        cfg = Config(V=64, C=32, L=2, H=2, I=64, T=16)
+        ids, tgt = bench_batch(2, 16, 64, rank)
+        def make():
+            tr = Trainer(cfg, 2, dev, RunConfig(), lr=1e-2, wd=0.1, world=world, rank=rank)
+            tr.set_batch(ids, tgt)
+            return tr
+        a = make()
+        for _ in range(2): a.step()
+        a.save_checkpoint({str(tmp_path)!r}, 2, loss=a.loss(), tokens_seen=64, loader_pos=100 + rank)
+        for _ in range(2): a.step()
+        dist.barrier()
+        b = make()
+        info = b.load_checkpoint({str(tmp_path)!r})
+        for _ in range(2): b.step()
+        print("CK", rank, info["step"], info["loader_pos"], b.t, bool(torch.equal(a.model.master, b.model.master)), flush=True)
+        a.close(); b.close(); shutdown()
+    """)
+    assert all(rc == 0 for rc, _ in outs), outs
+    got = sorted(l.split()[1:] for _, o in outs for l in o.splitlines() if l.startswith("CK"))
+    assert got == [["0", "2", "100", "5", "True"], ["1", "2", "101", "5", "True"]], got

@@ -374,3 +374,38 @@ def test_gradient_clipping_is_folded_into_the_optimizer_scale():
     r2.overlap_opt = 1
     with pytest.raises(ValueError, match="exclude each other"):
         Trainer(cfg, B, "cpu", r2, max_grad_norm=1.0)
+
+
+def test_trainer_checkpoint_roundtrip_including_the_vision_tower(tmp_path):
+    """Trainer.save_checkpoint / load_checkpoint: three steps, save, three more; a fresh trainer that loads the
+    checkpoint and runs the same three steps ends bit-identical (decoder, vision tower, moments, step count)."""
+    from ml_b200 import VisionConfig
+    from ml_b200.data import mm_batch
+    from ml_b200.trainer import Trainer
+    cfg = Config(V=64, C=32, L=2, H=2, I=64, T=24)
+    vc = VisionConfig(vC=24, vL=1, vI=48, n_patch=8)
+    B = 2
+    patches, ids, tgt = mm_batch(B, vc.n_patch, cfg.T - vc.n_patch, cfg.V, vc.patch_dim, seed=5)
+
+    def make():
+        tr = Trainer(cfg, B, "cpu", lr=1e-2, wd=0.1, vision=vc, n_text=cfg.T - vc.n_patch)
+        tr.vision.patches.copy_(patches)
+        tr.set_batch(ids, tgt)
+        return tr
+    a = make()
+    for _ in range(3):
+        a.step()
+    a.save_checkpoint(str(tmp_path), 3, loss=a.loss(), tokens_seen=123, loader_pos=77)
+    for _ in range(3):
+        a.step()
+    b = make()
+    assert b.load_checkpoint(str(tmp_path / "nothing_here")) is None
+    info = b.load_checkpoint(str(tmp_path))
+    assert (info["step"], info["tokens_seen"], info["loader_pos"], info["opt_t"]) == (3, 123, 77, 4) and b.t == 4
+    for _ in range(3):
+        b.step()
+    for x, y in ((a.model.master, b.model.master), (a.model.m, b.model.m), (a.vision.master, b.vision.master), (a.vision.v, b.vision.v)):
+        assert torch.equal(x, y)
+    assert a.loss() == b.loss()
+    a.close()
+    b.close()
