@@ -421,11 +421,19 @@ def test_a_signal_on_one_rank_stops_all_ranks_at_the_same_step(tmp_path, flags):
     env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "2", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
            "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "5", "ENTROPY_DEVICE": "cpu"}
     body = textwrap.dedent("""
-        import os, sys, signal, threading
+        import os, sys, signal, threading, time
         os.environ.update(ENV)
         from ml_b200 import gpt
         if os.environ["RANK"] == "1":
-            threading.Timer(6.0, lambda: os.kill(os.getpid(), signal.SIGTERM)).start()
+            # from 6 s on, every 2 s: a signal that arrives before the training loop has installed its handler is
+            # swallowed by this one instead of ending the process
+            signal.signal(signal.SIGTERM, lambda *_: None)
+            def nag():
+                time.sleep(6.0)
+                while True:
+                    os.kill(os.getpid(), signal.SIGTERM)
+                    time.sleep(2.0)
+            threading.Thread(target=nag, daemon=True).start()
         sys.exit(gpt.main(ARGS))
     """)
     outs = run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path, "100000"] + flags + ["--lr", "1e-3"]) + body, 2, timeout=240)
