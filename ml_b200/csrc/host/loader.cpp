@@ -104,7 +104,7 @@ void* mlb_loader_open(const char* path, int B, int T, int* err) {
   if (h[0] != 20240520) { munmap(m, st.st_size); close(fd); *err = 2; return nullptr; }
   int64_t ntok = h[2];
   int64_t have = ((int64_t)st.st_size - 256) / 2;
-  if (ntok > have) ntok = have;  // truncated file: serve what is there
+  if (ntok <= 0 || ntok > have) ntok = have;  // truncated file, or a count that does not fit the header's int32: serve what is there
   if (ntok < (int64_t)B * T + 1) { munmap(m, st.st_size); close(fd); *err = 3; return nullptr; }
   madvise(m, st.st_size, MADV_SEQUENTIAL);
   Loader* ld = new Loader;

@@ -89,6 +89,22 @@ def test_loader_windows_wrap_and_errors(tmp_path):
     assert TokenLoader(str(tr), B, T).ntok == 100
 
 
+def test_loader_trusts_the_file_size_when_the_header_count_is_unusable(tmp_path):
+    """The header's token count is an int32: a file written with a count of 0 (or one that overflowed) is served by its
+    size instead of being refused."""
+    import numpy as np
+    p = str(tmp_path / "t.bin")
+    write_token_bin(p, torch.arange(0, 100, dtype=torch.int32))
+    raw = bytearray(open(p, "rb").read())
+    raw[8:12] = np.int32(-5).tobytes()
+    open(p, "wb").write(raw)
+    ld = TokenLoader(p, 1, 10)
+    assert ld.ntok == 100
+    ids, tgt = ld.next()
+    assert ids.tolist() == list(range(10)) and tgt.tolist() == list(range(1, 11))
+    ld.close()
+
+
 def test_batch_pipe_order_cpu(tmp_path):
     toks = torch.arange(0, 500, dtype=torch.int32)
     p = str(tmp_path / "t.bin")
