@@ -22,10 +22,21 @@
 
 namespace {
 
-struct Loader {
+// One mapped token file.  `base` = tokens in the shards before it: a position handed to the caller is base + offset.
+struct Shard {
   int fd = -1;
   const uint8_t* map = nullptr;
   size_t map_bytes = 0;
+  const uint16_t* tok = nullptr;
+  int64_t ntok = 0, base = 0;
+};
+
+struct Loader {
+  // A data set is one file or several shards read one after the other (a window never spans two shards; the tail of a
+  // shard that does not hold a whole window is skipped, as at the end of a single file).  tok / ntok / pos describe the
+  // shard being read.
+  std::vector<Shard> shards;
+  int cur = 0;
   const uint16_t* tok = nullptr;
   int64_t ntok = 0, pos = 0;
   int B = 0, T = 0;
@@ -55,13 +66,19 @@ struct Pipe {
 
 void fill(Loader* ld, int32_t* ids, int32_t* tgt) {
   const int64_t n = (int64_t)ld->B * ld->T;
-  if (ld->pos + n + 1 > ld->ntok) ld->pos = ld->first * n;   // wrap to this reader's first window
+  if (ld->pos + n + 1 > ld->ntok) {
+    // on to the next shard (the only one, again, for a single file), at this reader's first window
+    ld->cur = (ld->cur + 1) % (int)ld->shards.size();
+    ld->tok = ld->shards[ld->cur].tok;
+    ld->ntok = ld->shards[ld->cur].ntok;
+    ld->pos = ld->first * n;
+  }
   const uint16_t* w = ld->tok + ld->pos;
   uint16_t mx = w[0];
   for (int64_t i = 0; i < n; i++) { ids[i] = w[i]; tgt[i] = w[i + 1]; mx = w[i + 1] > mx ? w[i + 1] : mx; }
   if (ld->vocab > 0 && (int)mx >= ld->vocab && ld->bad_pos.load() < 0) {
     ld->bad_tok.store(mx);
-    ld->bad_pos.store(ld->pos);
+    ld->bad_pos.store(ld->shards[ld->cur].base + ld->pos);
   }
   ld->pos += n * ld->every;
 }
@@ -91,38 +108,75 @@ void worker(Pipe* p) {
 
 extern "C" {
 
-// Returns a handle or nullptr; *err: 1 = cannot open, 2 = bad magic / short header, 3 = too few tokens.
-void* mlb_loader_open(const char* path, int B, int T, int* err) {
-  *err = 0;
+// Maps one token file; 0 or the error code of mlb_loader_open.  `need` = tokens a shard must hold at least.
+static int map_shard(const char* path, int64_t need, Shard* out) {
   int fd = open(path, O_RDONLY);
-  if (fd < 0) { *err = 1; return nullptr; }
+  if (fd < 0) return 1;
   struct stat st;
-  if (fstat(fd, &st) != 0 || (size_t)st.st_size < 256) { close(fd); *err = 2; return nullptr; }
+  if (fstat(fd, &st) != 0 || (size_t)st.st_size < 256) { close(fd); return 2; }
   void* m = mmap(nullptr, st.st_size, PROT_READ, MAP_PRIVATE, fd, 0);
-  if (m == MAP_FAILED) { close(fd); *err = 1; return nullptr; }
+  if (m == MAP_FAILED) { close(fd); return 1; }
   const int32_t* h = (const int32_t*)m;
-  if (h[0] != 20240520) { munmap(m, st.st_size); close(fd); *err = 2; return nullptr; }
+  if (h[0] != 20240520) { munmap(m, st.st_size); close(fd); return 2; }
   int64_t ntok = h[2];
   int64_t have = ((int64_t)st.st_size - 256) / 2;
   if (ntok <= 0 || ntok > have) ntok = have;  // truncated file, or a count that does not fit the header's int32: serve what is there
-  if (ntok < (int64_t)B * T + 1) { munmap(m, st.st_size); close(fd); *err = 3; return nullptr; }
+  if (ntok < need) { munmap(m, st.st_size); close(fd); return 3; }
   madvise(m, st.st_size, MADV_SEQUENTIAL);
+  out->fd = fd; out->map = (const uint8_t*)m; out->map_bytes = st.st_size;
+  out->tok = (const uint16_t*)((const uint8_t*)m + 256);
+  out->ntok = ntok;
+  return 0;
+}
+
+// Returns a handle or nullptr; *err: 1 = cannot open, 2 = bad magic / short header, 3 = too few tokens.
+void* mlb_loader_open(const char* path, int B, int T, int* err) {
+  Shard sh;
+  *err = map_shard(path, (int64_t)B * T + 1, &sh);
+  if (*err) return nullptr;
   Loader* ld = new Loader;
-  ld->fd = fd; ld->map = (const uint8_t*)m; ld->map_bytes = st.st_size;
-  ld->tok = (const uint16_t*)((const uint8_t*)m + 256);
-  ld->ntok = ntok; ld->B = B; ld->T = T;
+  ld->shards.push_back(sh);
+  ld->tok = sh.tok; ld->ntok = sh.ntok; ld->B = B; ld->T = T;
   return ld;
 }
-int64_t mlb_loader_ntok(void* h) { return ((Loader*)h)->ntok; }
-int64_t mlb_loader_pos(void* h) { return ((Loader*)h)->pos; }
-void mlb_loader_set_pos(void* h, int64_t pos) { ((Loader*)h)->pos = pos; }
+// Appends another shard of the same data set (read after the ones before it); same error codes, 0 = ok.  Call before
+// the first window is read.
+int mlb_loader_add(void* h, const char* path) {
+  Loader* ld = (Loader*)h;
+  Shard sh;
+  int err = map_shard(path, (int64_t)ld->B * ld->T + 1, &sh);
+  if (err) return err;
+  sh.base = ld->shards.back().base + ld->shards.back().ntok;
+  ld->shards.push_back(sh);
+  return 0;
+}
+int64_t mlb_loader_ntok(void* h) {
+  Loader* ld = (Loader*)h;
+  return ld->shards.back().base + ld->shards.back().ntok;
+}
+int64_t mlb_loader_pos(void* h) {
+  Loader* ld = (Loader*)h;
+  return ld->shards[ld->cur].base + ld->pos;
+}
+void mlb_loader_set_pos(void* h, int64_t pos) {
+  Loader* ld = (Loader*)h;
+  int c = 0;
+  while (c + 1 < (int)ld->shards.size() && pos >= ld->shards[c + 1].base) c++;
+  ld->cur = c;
+  ld->tok = ld->shards[c].tok;
+  ld->ntok = ld->shards[c].ntok;
+  ld->pos = pos - ld->shards[c].base;
+}
 // Reader `first` of `every` (data-parallel rank / world).  Returns 1 if the file is too short for that many disjoint
 // readers (fewer than `every` whole windows), else 0; the position moves to the reader's first window.
 int mlb_loader_set_stride(void* h, int64_t first, int64_t every) {
   Loader* ld = (Loader*)h;
   const int64_t n = (int64_t)ld->B * ld->T;
-  if (every < 1 || first < 0 || first >= every || every * n + 1 > ld->ntok) return 1;
-  ld->first = first; ld->every = every; ld->pos = first * n;
+  if (every < 1 || first < 0 || first >= every) return 1;
+  for (const Shard& sh : ld->shards)
+    if (every * n + 1 > sh.ntok) return 1;      // every shard must hold a window for every reader
+  ld->first = first; ld->every = every;
+  ld->cur = 0; ld->tok = ld->shards[0].tok; ld->ntok = ld->shards[0].ntok; ld->pos = first * n;
   return 0;
 }
 void mlb_loader_next(void* h, int32_t* ids, int32_t* tgt) { fill((Loader*)h, ids, tgt); }
@@ -139,8 +193,10 @@ int mlb_loader_bad(void* h, int64_t* pos, int* tok) {
 void mlb_loader_close(void* h) {
   Loader* ld = (Loader*)h;
   if (!ld) return;
-  munmap((void*)ld->map, ld->map_bytes);
-  close(ld->fd);
+  for (const Shard& sh : ld->shards) {
+    munmap((void*)sh.map, sh.map_bytes);
+    close(sh.fd);
+  }
   delete ld;
 }
 

@@ -28,14 +28,41 @@ def write_token_bin(path: str, tokens: torch.Tensor):
         raise OSError(f"write_token_bin({path}) failed: {rc}")
 
 
+def expand_shards(path: str):
+    """One data set, one or several llm.c files read one after the other: a plain path, a comma-separated list, or a
+    glob pattern (`fineweb_train_*.bin`), expanded in sorted order."""
+    import glob
+    out = []
+    for part in path.split(","):
+        part = part.strip()
+        if any(ch in part for ch in "*?["):
+            found = sorted(glob.glob(part))
+            if not found:
+                raise OSError(f"{part}: no file matches")
+            out.extend(found)
+        elif part:
+            out.append(part)
+    if not out:
+        raise OSError("no token file given")
+    return out
+
+
 class TokenLoader:
     def __init__(self, path: str, B: int, T: int, vocab: int = 0):
-        """vocab > 0: a window holding a token id >= vocab raises ValueError when it is handed out (`next_into`, or
+        """path: an llm.c token file, or several shards of one data set (see `expand_shards`); positions (`pos`, what a
+        checkpoint records) count tokens from the start of the first shard.  vocab > 0: a window holding a token id >= vocab raises ValueError when it is handed out (`next_into`, or
         `BatchPipe.acquire`'s upload), before the ids reach a kernel that would use them as table indices."""
         err = C.c_int(0)
-        self.h = lib().mlb_loader_open(path.encode(), B, T, C.byref(err))
+        self.paths = expand_shards(path)
+        self.h = lib().mlb_loader_open(self.paths[0].encode(), B, T, C.byref(err))
         if not self.h:
-            raise OSError(f"{path}: {_ERR.get(err.value, 'error %d' % err.value)}")
+            raise OSError(f"{self.paths[0]}: {_ERR.get(err.value, 'error %d' % err.value)}")
+        for extra in self.paths[1:]:
+            rc = lib().mlb_loader_add(self.h, extra.encode())
+            if rc:
+                lib().mlb_loader_close(self.h)
+                self.h = None
+                raise OSError(f"{extra}: {_ERR.get(rc, 'error %d' % rc)}")
         self.B, self.T, self.path, self.vocab = B, T, path, int(vocab)
         self.ntok = lib().mlb_loader_ntok(self.h)
         if self.vocab > 0:
@@ -186,7 +213,7 @@ def open_token_file(path: str, B: int, T: int, vocab: int = 0, scratch_dir: str 
     """A `TokenLoader` over `path`, whatever its format: an llm.c file is opened as it is; a raw uint32 or text token
     file is first rewritten in the llm.c format (16-bit ids, so every id must be below 65536) under `scratch_dir`
     (default: the system's temporary directory), one private copy per process."""
-    if is_llmc_bin(path):
+    if any(ch in path for ch in ",*?[") or is_llmc_bin(path):
         return TokenLoader(path, B, T, vocab=vocab)
     import tempfile
     arr = read_raw_tokens(path)

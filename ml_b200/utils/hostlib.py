@@ -20,6 +20,7 @@ def lib():
         "mlb_rng_token_pairs": (u64, [u64, vp, vp, i64, i32]),
         "mlb_rng_uniform": (u64, [u64, vp, i64]),
         "mlb_loader_open": (vp, [cp, i32, i32, C.POINTER(C.c_int)]),
+        "mlb_loader_add": (i32, [vp, cp]),
         "mlb_loader_ntok": (i64, [vp]),
         "mlb_loader_pos": (i64, [vp]),
         "mlb_loader_set_pos": (None, [vp, i64]),

@@ -105,6 +105,36 @@ def test_loader_trusts_the_file_size_when_the_header_count_is_unusable(tmp_path)
     ld.close()
 
 
+def test_loader_reads_several_shards_in_order(tmp_path):
+    """A data set of several llm.c shards (comma list or glob): windows come shard after shard, a window never spans
+    two of them, positions count from the start of the first shard and can be restored, the wrap goes back to the first
+    shard, striped readers start every shard at their own window."""
+    for i, n in enumerate((35, 25, 31)):
+        write_token_bin(str(tmp_path / f"s{i}.bin"), torch.arange(0, n, dtype=torch.int32) + 100 * i)
+    ld = TokenLoader(str(tmp_path / "s*.bin"), 1, 10)
+    assert ld.ntok == 91 and len(ld.paths) == 3
+    first, pos = [], []
+    for _ in range(9):
+        pos.append(ld.pos)
+        ids, tgt = ld.next()
+        assert (tgt - ids).eq(1).all()
+        first.append(int(ids[0]))
+    # shard 0: windows at 0, 10, 20 (30 would need token 40); shard 1: 100, 110; shard 2: 200, 210, 220; then shard 0 again
+    assert first == [0, 10, 20, 100, 110, 200, 210, 220, 0]
+    assert pos[:4] == [0, 10, 20, 30] and pos[4] == 35 + 10 and pos[5] == 35 + 20 and pos[6] == 60 + 10
+    ld.pos = 35 + 10                                   # as a resumed run would: second window of the second shard
+    assert int(ld.next()[0][0]) == 110 and int(ld.next()[0][0]) == 200
+    ld.close()
+    two = TokenLoader(f"{tmp_path / 's0.bin'},{tmp_path / 's2.bin'}", 1, 10)
+    two.set_stride(1, 2)                               # reader 1 of 2: windows 1, 3, ... of every shard
+    assert [int(two.next()[0][0]) for _ in range(4)] == [10, 210, 10, 210]
+    two.close()
+    with pytest.raises(OSError, match="fewer than"):
+        TokenLoader(str(tmp_path / "s*.bin"), 1, 10).set_stride(0, 3)      # shard 1 has no window for a third reader
+    with pytest.raises(OSError, match="no file matches"):
+        TokenLoader(str(tmp_path / "nothing*.bin"), 1, 10)
+
+
 def test_batch_pipe_order_cpu(tmp_path):
     toks = torch.arange(0, 500, dtype=torch.int32)
     p = str(tmp_path / "t.bin")
