@@ -1,5 +1,5 @@
-"""Sequence (context) parallelism.  All-to-all flavour (`SequenceParallel`, the default): every rank of a group holds a contiguous 1/cp slice of each
-sequence for everything that is token-local (embedding, norms, linears, SwiGLU, LM head, loss) and switches to a
+"""Sequence (context) parallelism.  All-to-all flavour (`SequenceParallel`, the default): every rank of a group holds a
+contiguous 1/cp slice of each sequence for everything that is token-local (embedding, norms, linears, SwiGLU, LM head, loss) and switches to a
 head-sharded layout - all tokens, H/cp heads - around attention, so the attention kernels run unchanged on full
 sequences and the causal work is balanced over the ranks by construction.
 
