@@ -499,8 +499,10 @@ def _train_loop_model_parallel(a):
         elif rank == 0:
             print("no checkpoint to resume from; starting fresh")
     writer = ck.CheckpointWriter() if a.ckpt_dir and a.save_every > 0 else None
+    from .utils.metrics import MetricsLogger
+    logger = MetricsLogger(a.log_dir, rank, wandb=a.wandb, wandb_project=a.wandb_project, wandb_run_name=a.wandb_run_name) if a.log_dir else None
     n = B * cfg.T
-    t_last = time.perf_counter()
+    t_last, s_last = time.perf_counter(), start_step
     stop = {"flag": False}
     for sig in (signal.SIGINT, signal.SIGTERM):
         try:
@@ -525,7 +527,9 @@ def _train_loop_model_parallel(a):
             last_loss = float(t.item())
             if rank == 0:
                 print(f"step {step + 1:5d} | loss {last_loss:.4f} | {(now - t_last) * 1e3:.2f} ms since last log")
-            t_last = now
+            if logger:
+                logger.log(step + 1, last_loss, eng.hyper["lr"], tokens_seen + B * M * cfg.T, (now - t_last) * 1e3 / max(1, step + 1 - s_last))
+            t_last, s_last = now, step + 1
         tokens_seen += B * M * cfg.T
         if writer is not None and (step + 1) % a.save_every == 0:
             writer.save(a.ckpt_dir, step + 1, last_loss, tokens_seen, holder.master, holder.m, holder.v, rank=rank, shard=(0, nst),
@@ -542,6 +546,8 @@ def _train_loop_model_parallel(a):
             break
     if writer is not None:
         writer.close()
+    if logger:
+        logger.close()
     loader.close()
     if world > 1:
         shutdown()

@@ -396,8 +396,11 @@ def test_model_parallel_modes_checkpoint_and_resume(tmp_path, flags):
         o = [o for _, o in outs if "step " in o][0]
         return {int(l.split()[1]): float(l.split("loss")[1].split("|")[0]) for l in o.splitlines() if l.startswith("step ")}, o
     whole, _ = run(["4"])
-    first, _ = run(["2", "--ckpt-dir", ck, "--save-every", "2"])
+    first, _ = run(["2", "--ckpt-dir", ck, "--save-every", "2", "--log-dir", str(tmp_path / "log")])
     assert ckpt.latest_step(ck) == 2
+    import json
+    rows = [json.loads(l) for l in open(tmp_path / "log" / "metrics.jsonl")]
+    assert [r["step"] for r in rows] == [1, 2] and abs(rows[1]["loss"] - first[2]) < 1e-3 and rows[1]["tokens_seen"] > rows[0]["tokens_seen"] > 0
     files = sorted(os.listdir(ckpt.step_dir(ck, 2)))
     assert files == ["meta.bin", "optim_rank_0.bin", "optim_rank_1.bin", "state_rank_0.bin", "state_rank_1.bin",
                      "weights_rank_0.bin", "weights_rank_1.bin"], files
