@@ -16,7 +16,7 @@ import signal
 import sys
 import time
 
-MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|bench_fsdp|plan|lmce_check"
+MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|bench_fsdp|generate|plan|lmce_check"
 
 
 def _banner(mode, dev):
@@ -667,6 +667,41 @@ def mode_bench_fsdp(argv):
     return 0
 
 
+def mode_generate(argv):
+    """`generate --ckpt-dir DIR [--step N] --prompt "12 7 99" [--n 32] [--temperature 0] [--top-k 0] [--seed 0]`: loads
+    the fp32 master weights of a checkpoint written by `train` (model shape from the ENTROPY_* variables, as there) and
+    prints the prompt's continuation as token ids (this package has no tokenizer).  Not a mode of the reference."""
+    import argparse
+    import torch
+    from . import Config
+    from .models import GPT
+    from .utils import ckpt as ck
+    ap = argparse.ArgumentParser(prog="gpt generate")
+    ap.add_argument("--ckpt-dir", "--checkpoint", required=True)
+    ap.add_argument("--step", type=int, default=-2, help="checkpoint step (-2 = latest)")
+    ap.add_argument("--prompt", required=True, help="token ids separated by spaces or commas")
+    ap.add_argument("--n", type=int, default=32)
+    ap.add_argument("--temperature", type=float, default=0.0)
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--seed", type=int, default=0)
+    a = ap.parse_args(argv)
+    dev = _device()
+    cfg = Config.from_env()
+    prompt = torch.tensor([[int(t) for t in a.prompt.replace(",", " ").split()]], dtype=torch.long)
+    if prompt.numel() == 0 or int(prompt.max()) >= cfg.V or int(prompt.min()) < 0:
+        sys.exit(f"the prompt needs at least one token id, all in [0, {cfg.V})")
+    g = GPT(cfg, 1, dev)
+    st = ck.latest_step(a.ckpt_dir) if a.step == -2 else a.step
+    info = ck.load(a.ckpt_dir, st, g.master, torch.empty_like(g.master), torch.empty_like(g.master)) if st is not None else None
+    if info is None:
+        sys.exit(f"no checkpoint in {a.ckpt_dir}")
+    g.sync_params()
+    out = g.generate(prompt, a.n, a.temperature, a.top_k, a.seed)
+    print(f"checkpoint step {info['step']} (loss {info['loss']:.4f})")
+    print(" ".join(str(int(t)) for t in out[0]))
+    return 0
+
+
 def main(argv=None):
     argv = list(sys.argv[1:] if argv is None else argv)
     mode = argv[0] if argv else "overfit"
@@ -679,7 +714,7 @@ def main(argv=None):
         print(plan_from_env())
         return 0
     table = {"overfit": mode_overfit, "mm_overfit": mode_mm_overfit, "mm_bench": mode_mm_bench, "bench": mode_bench,
-             "bench_ddp": mode_bench_ddp, "bench_fsdp": mode_bench_fsdp, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
+             "bench_ddp": mode_bench_ddp, "bench_fsdp": mode_bench_fsdp, "generate": mode_generate, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
     if mode not in table:
         print(f"usage: python -m ml_b200.gpt [{MODES}] [args]", file=sys.stderr)
         return 2

@@ -471,6 +471,38 @@ class GPT:
             ops.ce_fwd_bwd(self.losses[:BT], self.logits[:BT], tgt, 1.0)
         return self.mean_loss(B=B, valid_tokens=valid)
 
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, n_new: int, temperature: float = 0.0, top_k: int = 0, seed: int = 0) -> torch.Tensor:
+        """Continues `prompt` [b, P] (token ids, b <= B, P >= 1) by `n_new` tokens with the training forward pass: every
+        new token is one forward over the whole window (there is no key / value cache - this is a way to look at what a
+        checkpoint has learnt, not a serving path), the window slides once it is full.  temperature 0 = greedy; else
+        softmax sampling at that temperature, over the `top_k` most likely tokens if top_k > 0, from a generator seeded
+        with `seed`.  The reference has no sampling mode; needs materialised logits (no chunked LM head)."""
+        if self.logits is None:
+            raise ValueError("generate() reads the [B*T, V] logits: build the model without lmce_chunk")
+        c = self.cfg
+        b, P = prompt.shape
+        assert 1 <= b <= self.B and P >= 1
+        out = prompt.to(self.device).long()
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        ids = torch.zeros(b, c.T, dtype=torch.int32, device=self.device)
+        for _ in range(n_new):
+            ctx = out[:, -c.T:]
+            n = ctx.shape[1]
+            ids.zero_()
+            ids[:, :n] = ctx.to(torch.int32)       # positions past n hold padding: causal attention keeps it out of row n - 1
+            logits = self.forward(ids.view(-1), B=b).view(b, c.T, c.V)[:, n - 1].float()
+            if temperature <= 0:
+                nxt = logits.argmax(-1)
+            else:
+                logits = logits / temperature
+                if top_k > 0:
+                    kth = logits.topk(min(top_k, c.V), dim=-1).values[:, -1:]
+                    logits = logits.masked_fill(logits < kth, float("-inf"))
+                nxt = torch.multinomial(torch.softmax(logits, -1).cpu(), 1, generator=gen).view(-1).to(self.device)
+            out = torch.cat([out, nxt.view(b, 1)], dim=1)
+        return out
+
     def _lmhead_chunk_stats(self, tgt, BT):
         """Pass 1 of the chunked LM head: per-row running maximum, sum of exponentials and target logit over the
         vocabulary chunks (the logits tile is overwritten chunk after chunk)."""

@@ -409,3 +409,38 @@ def test_trainer_checkpoint_roundtrip_including_the_vision_tower(tmp_path):
     assert a.loss() == b.loss()
     a.close()
     b.close()
+
+
+def test_generate_continues_a_prompt_like_the_module_restatement():
+    """GPT.generate (greedy): the same tokens as an argmax loop over the nn.Module restatement with the same weights,
+    also past the point where the window is full and slides; a model that has memorised a periodic sequence continues
+    it; sampling is reproducible for a seed and stays inside top-k."""
+    from ml_b200.bench.torch_baseline import TorchDecoder
+    from ml_b200.trainer import Trainer
+    cfg, B = Config(V=32, C=32, L=2, H=2, I=64, T=16), 2
+    tr = Trainer(cfg, B, "cpu", lr=1e-2, wd=0.0)
+    period = torch.tensor([3, 7, 1, 9, 4], dtype=torch.int32)
+    seq = period.repeat(8)[:B * cfg.T + 1]
+    ids = torch.stack([seq[0:16], seq[5:21]]).reshape(-1)
+    tgt = torch.stack([seq[1:17], seq[6:22]]).reshape(-1)
+    tr.set_batch(ids, tgt)
+    for _ in range(150):
+        tr.step()
+    g = tr.model
+    prompt = torch.stack([seq[0:6], seq[5:11]]).long()
+    out = g.generate(prompt, 14)                      # 6 + 14 = 20 > T: the window slides for the last tokens
+    assert out.shape == (2, 20) and torch.equal(out[:, :6], prompt)
+    m = TorchDecoder(cfg).load_flat(g.master)
+    ref = prompt.clone()
+    for _ in range(14):
+        ctx = ref[:, -cfg.T:]
+        pad = torch.zeros(2, cfg.T, dtype=torch.long)
+        pad[:, :ctx.shape[1]] = ctx
+        ref = torch.cat([ref, m(pad)[:, ctx.shape[1] - 1].argmax(-1, keepdim=True)], dim=1)
+    assert torch.equal(out, ref)
+    assert torch.equal(out[0, :16], seq[0:16].long())          # the memorised continuation
+    a = g.generate(prompt, 5, temperature=1.0, top_k=3, seed=11)
+    b = g.generate(prompt, 5, temperature=1.0, top_k=3, seed=11)
+    assert torch.equal(a, b) and a.shape == (2, 11)
+    one = g.generate(prompt[:1], 3)
+    assert torch.equal(one, out[:1, :9])

@@ -318,6 +318,13 @@ def test_cli_train_checkpoint_resume(tmp_path):
     b = subprocess.run(base + ["15", "--ckpt-dir", str(tmp_path / "ck"), "--resume", "-2"], env=env, capture_output=True, text=True, timeout=300)
     assert b.returncode == 0, b.stdout + b.stderr
     assert "resumed from step 10" in b.stdout and "step    15 | loss" in b.stdout
+    # the generate mode reads the same checkpoint: prompt + n new ids, greedy runs repeat
+    gen = [subprocess.run([sys.executable, "-m", "ml_b200.gpt", "generate", "--ckpt-dir", str(tmp_path / "ck"), "--prompt", "5, 17 200", "--n", "6"],
+                          env=env, capture_output=True, text=True, timeout=300) for _ in range(2)]
+    assert gen[0].returncode == 0, gen[0].stdout + gen[0].stderr
+    toks = gen[0].stdout.strip().splitlines()[-1].split()
+    assert "checkpoint step 10" in gen[0].stdout and toks[:3] == ["5", "17", "200"] and len(toks) == 9
+    assert all(0 <= int(t) < 256 for t in toks) and gen[0].stdout == gen[1].stdout
     # an uninterrupted 15-step run ends at the same loss as 10 steps + resume + 5 steps
     c = subprocess.run(base + ["15"], env=env, capture_output=True, text=True, timeout=300)
     la = [l for l in b.stdout.splitlines() if l.startswith("step    15")][0].split("|")[1]
