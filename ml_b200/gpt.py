@@ -16,7 +16,7 @@ import signal
 import sys
 import time
 
-MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|bench_fsdp|generate|plan|lmce_check"
+MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|bench_fsdp|eval|generate|plan|lmce_check"
 
 
 def _banner(mode, dev):
@@ -667,6 +667,47 @@ def mode_bench_fsdp(argv):
     return 0
 
 
+def mode_eval(argv):
+    """`eval --ckpt-dir DIR [--step N] --data FILE [--batches 8] [--batch-size B]`: forward-only mean loss (and its
+    exponential, the perplexity) of a checkpoint over the first `--batches` windows of a token file - the number
+    `train --eval-bin FILE --eval-every N` prints for that step.  Not a mode of the reference."""
+    import argparse
+    import math
+    import torch
+    from . import Config, RunConfig
+    from .data import open_token_file
+    from .models import GPT
+    from .utils import ckpt as ck
+    ap = argparse.ArgumentParser(prog="gpt eval")
+    ap.add_argument("--ckpt-dir", "--checkpoint", required=True)
+    ap.add_argument("--step", type=int, default=-2, help="checkpoint step (-2 = latest)")
+    ap.add_argument("--data", required=True)
+    ap.add_argument("--batches", type=int, default=8)
+    ap.add_argument("--batch-size", type=int, default=0)
+    a = ap.parse_args(argv)
+    dev = _device()
+    cfg, run = Config.from_env(), RunConfig.from_env()
+    B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
+    g = GPT(cfg, B, dev, lmce_chunk=(run.lmce_chunk or None))
+    st = ck.latest_step(a.ckpt_dir) if a.step == -2 else a.step
+    info = ck.load(a.ckpt_dir, st, g.master, torch.empty_like(g.master), torch.empty_like(g.master)) if st is not None else None
+    if info is None:
+        sys.exit(f"no checkpoint in {a.ckpt_dir}")
+    g.sync_params()
+    loader = open_token_file(a.data, B, cfg.T, vocab=cfg.V)
+    ewin = B * cfg.T
+    span = max(1, loader.ntok - ewin - 1)
+    tot = 0.0
+    for k in range(a.batches):
+        loader.pos = (k * ewin) % span
+        ids, tgt = loader.next()
+        tot += g.eval_loss(ids.to(dev).view(-1), tgt.to(dev).view(-1), B=B)
+    ev = tot / max(1, a.batches)
+    print(f"checkpoint step {info['step']} | eval loss {ev:.4f} | perplexity {math.exp(min(ev, 80.0)):.2f} | {a.batches} x {B} x {cfg.T} tokens of {a.data}")
+    loader.close()
+    return 0
+
+
 def mode_generate(argv):
     """`generate --ckpt-dir DIR [--step N] --prompt "12 7 99" [--n 32] [--temperature 0] [--top-k 0] [--seed 0]`: loads
     the fp32 master weights of a checkpoint written by `train` (model shape from the ENTROPY_* variables, as there) and
@@ -714,7 +755,7 @@ def main(argv=None):
         print(plan_from_env())
         return 0
     table = {"overfit": mode_overfit, "mm_overfit": mode_mm_overfit, "mm_bench": mode_mm_bench, "bench": mode_bench,
-             "bench_ddp": mode_bench_ddp, "bench_fsdp": mode_bench_fsdp, "generate": mode_generate, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
+             "bench_ddp": mode_bench_ddp, "bench_fsdp": mode_bench_fsdp, "generate": mode_generate, "eval": mode_eval, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
     if mode not in table:
         print(f"usage: python -m ml_b200.gpt [{MODES}] [args]", file=sys.stderr)
         return 2

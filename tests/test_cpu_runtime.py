@@ -446,6 +446,14 @@ def test_cli_train_eval_flags_and_chunked_head(tmp_path):
     num = lambda line: float(re.search(r"loss ([0-9.]+)", line).group(1))
     for a_, b_ in zip(tr(ch.stdout) + [l for l in ch.stdout.splitlines() if "eval loss" in l], tr(ev.stdout) + evals):
         assert num(a_) == pytest.approx(num(b_), abs=2e-4), (a_, b_)
+    # the eval mode on the checkpoint of step 10 prints what the training run printed for that step
+    sv = subprocess.run(base + ["--eval-bin", q, "--eval-every", "5", "--eval-batches", "3", "--ckpt-dir", str(tmp_path / "ck"), "--save-every", "10"],
+                        env=env, capture_output=True, text=True, timeout=300)
+    assert sv.returncode == 0, sv.stdout + sv.stderr
+    e2 = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "eval", "--ckpt-dir", str(tmp_path / "ck"), "--data", q, "--batches", "3", "--batch-size", "2"],
+                        env=dict(env, ENTROPY_T="16"), capture_output=True, text=True, timeout=300)
+    assert e2.returncode == 0, e2.stdout + e2.stderr
+    assert "checkpoint step 10" in e2.stdout and num(e2.stdout.split("eval")[1]) == pytest.approx(v10, abs=2e-4), e2.stdout
 
 
 def test_raw_token_loader_formats(tmp_path):
