@@ -16,7 +16,7 @@ import signal
 import sys
 import time
 
-MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|bench_fsdp|eval|generate|plan|lmce_check"
+MODES = "overfit|mm_overfit|mm_bench|bench|train|bench_ddp|train_ddp|bench_fsdp|eval|generate|export|plan|lmce_check"
 
 
 def _banner(mode, dev):
@@ -252,6 +252,8 @@ def _train_loop(argv, ddp):
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
     ap.add_argument("--warmup-ratio", type=float, default=0.0)
+    ap.add_argument("--init-from", default="", help="start from the weights of a Hugging Face Llama directory of the same shape "
+                                                    "(written by the export mode, or any matching checkpoint) instead of the random init")
     ap.add_argument("--max-grad-norm", type=float, default=0.0,
                     help="clip the gradient of the whole model to this L2 norm (0 = off; with several ranks needs ENTROPY_COMM=nccl)")
     ap.add_argument("--max-steps", type=int, default=0, help="same as the positional step count")
@@ -308,6 +310,12 @@ def _train_loop(argv, ddp):
     B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
     tr = Trainer(cfg, B, dev, run, lr=a.lr, wd=a.weight_decay, world=world, rank=rank,
                  use_graph=bool(run.train_graph) and a.warmup_ratio <= 0, max_grad_norm=a.max_grad_norm)
+    if a.init_from:
+        from .utils import export
+        tr.model.master.copy_(export.load_hf(cfg, a.init_from).to(tr.model.master.device))
+        tr.model.sync_params()
+        if rank == 0:
+            print(f"initial weights from {a.init_from}")
     loader = open_token_file(a.bin, B * tr.accum, cfg.T, vocab=cfg.V)
     if rank == 0:
         run.warn_ineffective()
@@ -708,6 +716,32 @@ def mode_eval(argv):
     return 0
 
 
+def mode_export(argv):
+    """`export --ckpt-dir DIR [--step N] --out DIR2 [--dtype float32|bfloat16]`: a checkpoint's decoder weights as a
+    directory `transformers.LlamaForCausalLM.from_pretrained` reads (ml_b200.utils.export).  Not a mode of the reference."""
+    import argparse
+    import torch
+    from . import Config
+    from .layout import DecoderLayout
+    from .utils import ckpt as ck, export
+    ap = argparse.ArgumentParser(prog="gpt export")
+    ap.add_argument("--ckpt-dir", "--checkpoint", required=True)
+    ap.add_argument("--step", type=int, default=-2)
+    ap.add_argument("--out", required=True)
+    ap.add_argument("--dtype", default="float32", choices=["float32", "bfloat16"])
+    a = ap.parse_args(argv)
+    cfg = Config.from_env()
+    n = DecoderLayout(cfg).num_params
+    master = torch.empty(n, dtype=torch.float32)
+    st = ck.latest_step(a.ckpt_dir) if a.step == -2 else a.step
+    info = ck.load(a.ckpt_dir, st, master, torch.empty_like(master), torch.empty_like(master)) if st is not None else None
+    if info is None:
+        sys.exit(f"no checkpoint in {a.ckpt_dir}")
+    path = export.export_hf(cfg, master, a.out, getattr(torch, a.dtype))
+    print(f"checkpoint step {info['step']} -> {path} ({n / 1e6:.1f}M parameters, {a.dtype})")
+    return 0
+
+
 def mode_generate(argv):
     """`generate --ckpt-dir DIR [--step N] --prompt "12 7 99" [--n 32] [--temperature 0] [--top-k 0] [--seed 0]`: loads
     the fp32 master weights of a checkpoint written by `train` (model shape from the ENTROPY_* variables, as there) and
@@ -755,7 +789,7 @@ def main(argv=None):
         print(plan_from_env())
         return 0
     table = {"overfit": mode_overfit, "mm_overfit": mode_mm_overfit, "mm_bench": mode_mm_bench, "bench": mode_bench,
-             "bench_ddp": mode_bench_ddp, "bench_fsdp": mode_bench_fsdp, "generate": mode_generate, "eval": mode_eval, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
+             "bench_ddp": mode_bench_ddp, "bench_fsdp": mode_bench_fsdp, "generate": mode_generate, "eval": mode_eval, "export": mode_export, "train": lambda a: _train_loop(a, False), "train_ddp": lambda a: _train_loop(a, True)}
     if mode not in table:
         print(f"usage: python -m ml_b200.gpt [{MODES}] [args]", file=sys.stderr)
         return 2

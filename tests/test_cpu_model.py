@@ -1,6 +1,7 @@
 """CPU (no GPU) end-to-end checks of the explicit forward/backward engine against PyTorch autograd, the overfit modes
 with asserted thresholds, and gradient-accumulation semantics."""
 import math
+import os
 
 import pytest
 import torch
@@ -444,3 +445,27 @@ def test_generate_continues_a_prompt_like_the_module_restatement():
     assert torch.equal(a, b) and a.shape == (2, 11)
     one = g.generate(prompt[:1], 3)
     assert torch.equal(one, out[:1, :9])
+
+
+def test_export_to_the_hugging_face_llama_layout(tmp_path):
+    """The flat parameter buffer written in the Hugging Face Llama naming loads into transformers' LlamaForCausalLM,
+    whose logits then equal this engine's (same RoPE convention, norm epsilon, fused QKV split, gate / up order); the
+    way back reproduces the buffer bit for bit."""
+    transformers = pytest.importorskip("transformers")
+    from ml_b200.utils import export
+    cfg, B = Config(V=97, C=48, L=2, H=4, I=80, T=16), 2
+    g = GPT(cfg, B)
+    g.init_weights(1234)
+    ids, _ = Stream(5).token_pairs(B * cfg.T, cfg.V)
+    ours = g.forward(ids).view(B, cfg.T, cfg.V).clone()
+    path = export.export_hf(cfg, g.master, str(tmp_path / "hf"))
+    assert os.path.basename(path) in ("model.safetensors", "pytorch_model.bin")
+    hf = transformers.LlamaForCausalLM.from_pretrained(str(tmp_path / "hf"), torch_dtype=torch.float32, attn_implementation="eager")
+    hf.eval()
+    with torch.no_grad():
+        theirs = hf(input_ids=ids.view(B, cfg.T).long()).logits
+    assert (ours - theirs).abs().max() < 2e-4, float((ours - theirs).abs().max())
+    assert torch.equal(export.load_hf(cfg, str(tmp_path / "hf")), g.master)
+    assert torch.equal(export.from_hf_state_dict(cfg, hf.state_dict()), g.master)
+    with pytest.raises(ValueError, match="where the configuration needs"):
+        export.from_hf_state_dict(Config(V=97, C=48, L=2, H=4, I=96, T=16), hf.state_dict())

@@ -325,6 +325,16 @@ def test_cli_train_checkpoint_resume(tmp_path):
     toks = gen[0].stdout.strip().splitlines()[-1].split()
     assert "checkpoint step 10" in gen[0].stdout and toks[:3] == ["5", "17", "200"] and len(toks) == 9
     assert all(0 <= int(t) < 256 for t in toks) and gen[0].stdout == gen[1].stdout
+    # export the checkpoint in the Hugging Face layout and start a new run from it: its first logged loss is a trained
+    # model's, not the random init's
+    ex = subprocess.run([sys.executable, "-m", "ml_b200.gpt", "export", "--ckpt-dir", str(tmp_path / "ck"), "--out", str(tmp_path / "hf")],
+                        env=env, capture_output=True, text=True, timeout=300)
+    assert ex.returncode == 0 and "checkpoint step 10" in ex.stdout, ex.stdout + ex.stderr
+    assert os.path.exists(tmp_path / "hf" / "config.json")
+    warm = subprocess.run(base + ["5", "--init-from", str(tmp_path / "hf")], env=env, capture_output=True, text=True, timeout=300)
+    assert warm.returncode == 0 and "initial weights from" in warm.stdout, warm.stdout + warm.stderr
+    first = lambda out: float([l for l in out.splitlines() if l.startswith("step     5")][0].split("loss")[1].split("|")[0])
+    assert first(warm.stdout) < first(a.stdout) - 0.02, (warm.stdout, a.stdout)
     # an uninterrupted 15-step run ends at the same loss as 10 steps + resume + 5 steps
     c = subprocess.run(base + ["15"], env=env, capture_output=True, text=True, timeout=300)
     la = [l for l in b.stdout.splitlines() if l.startswith("step    15")][0].split("|")[1]
