@@ -231,7 +231,7 @@ def _train_loop(argv, ddp):
     import torch.distributed as dist
     from . import Config, RunConfig
     from .trainer import Trainer
-    from .data import TokenLoader, BatchPipe, open_token_file
+    from .data import BatchPipe, open_token_file
     from .layout import flops_per_step
     from .parallel.bootstrap import init_distributed, shutdown
     from .utils import ckpt as ck
@@ -457,7 +457,7 @@ def _train_loop_model_parallel(a):
     import torch
     import torch.distributed as dist
     from . import Config, RunConfig
-    from .data import TokenLoader, open_token_file
+    from .data import open_token_file
     from .parallel.bootstrap import init_distributed, shutdown
     rank, world, local, dev = init_distributed()
     if rank == 0:

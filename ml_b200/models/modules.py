@@ -11,7 +11,6 @@ module has no flat-buffer counterpart (`from_flat` / `load_flat` are for the def
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn as nn

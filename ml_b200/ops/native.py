@@ -7,7 +7,6 @@ back to PyTorch: if the library cannot be loaded the import fails.
 from __future__ import annotations
 
 import ctypes as C
-import math
 import os
 from functools import lru_cache
 

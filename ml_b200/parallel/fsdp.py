@@ -20,7 +20,7 @@ launched in front of the first consuming GEMM (`mlb_allgather_pull`), so no NCCL
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Tuple
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist
