@@ -270,6 +270,8 @@ def _train_loop(argv, ddp):
     ap.add_argument("--cp-size", type=int, default=1, help="sequence-parallel ranks: every rank keeps 1/N of each sequence (must equal the number of ranks)")
     ap.add_argument("--cp-mode", default="alltoall", choices=["alltoall", "ring", "zigzag"],
                     help="sequence parallelism by an all-to-all layout switch around attention, by key/value chunks travelling a ring, or the ring in zig-zag token order")
+    ap.add_argument("--fsdp", action="store_true", help="train_ddp: parameters, gradients and optimizer state sharded over the ranks "
+                                                        "(ZeRO-3 style, ml_b200.parallel.fsdp); every rank writes its shards to the checkpoint")
     ap.add_argument("--microbatches", type=int, default=0, help="micro-batches per optimizer step of the pipeline (default ENTROPY_MICROBATCHES)")
     ap.add_argument("--nodes", type=int, default=1)
     ap.add_argument("--gpus-per-node", type=int, default=0)
@@ -295,7 +297,7 @@ def _train_loop(argv, ddp):
         local = int(os.environ.get("LOCAL_RANK", "0"))
         os.environ["RANK"] = str(a.node_id * a.gpus_per_node + local)
         os.environ["WORLD_SIZE"] = str(a.nodes * a.gpus_per_node)
-    if a.pp_size > 1 or a.tp_size > 1 or a.cp_size > 1 or a.microbatches > 0:
+    if a.pp_size > 1 or a.tp_size > 1 or a.cp_size > 1 or a.microbatches > 0 or a.fsdp:
         return _train_loop_model_parallel(a)
     if ddp:
         rank, world, local, dev = init_distributed()
@@ -467,13 +469,19 @@ def _train_loop_model_parallel(a):
         cfg.T = a.seq_len
     run = RunConfig.from_env()
     B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
-    if a.pp_size * a.tp_size * a.cp_size != world:
+    if a.fsdp and (a.pp_size > 1 or a.tp_size > 1 or a.cp_size > 1):
+        sys.exit("--fsdp shards a data-parallel model; it is not combined with pipeline, tensor or sequence parallelism here")
+    if not a.fsdp and a.pp_size * a.tp_size * a.cp_size != world:
         sys.exit(f"--pp-size {a.pp_size} x --tp-size {a.tp_size} x --cp-size {a.cp_size} must equal the number of ranks ({world}); "
                  "data-parallel replicas of a model-parallel group are not built")
     if (a.pp_size > 1) + (a.tp_size > 1) + (a.cp_size > 1) > 1:
         sys.exit("pipeline, tensor and sequence parallelism cannot be combined in one run here")
     hyper = dict(lr=a.lr, wd=a.weight_decay)
-    if a.cp_size > 1:
+    if a.fsdp:
+        from .parallel.fsdp import FSDPTrainer
+        M = 1
+        eng = FSDPTrainer(cfg, B, dev, world, rank, comm=run.comm, hyper=hyper)
+    elif a.cp_size > 1:
         from .parallel.cp import CPTrainer
         M = 1
         eng = CPTrainer(cfg, B, dev, mode=a.cp_mode, hyper=hyper)
@@ -486,8 +494,11 @@ def _train_loop_model_parallel(a):
         M = a.microbatches if a.microbatches > 0 else run.microbatches
         eng = PipelineStage(cfg, B, a.pp_size, rank, dev, microbatches=M, hyper=hyper)
     loader = open_token_file(a.bin, B * M, cfg.T, vocab=cfg.V)
+    if a.fsdp and world > 1:
+        loader.set_stride(rank, world)         # data parallel: every rank its own windows
     if rank == 0:
-        print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} cp={a.cp_size} ({a.cp_mode}) steps={a.steps}")
+        print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} cp={a.cp_size} ({a.cp_mode}) "
+              f"fsdp={int(a.fsdp)} steps={a.steps}")
     # Checkpoints: every rank holds its own part of the model (a pipeline stage, a tensor-parallel slice; a replica under
     # sequence parallelism), so every rank writes its flat fp32 master / moment buffers as weights_rank_<r>.bin /
     # optim_rank_<r>.bin; meta.bin is published by rank 0 once all of them are on disk.
@@ -521,11 +532,13 @@ def _train_loop_model_parallel(a):
         ids, tgt = loader.next()
         ids, tgt = ids.to(dev), tgt.to(dev)
         eng.hyper["lr"] = lr_at(step, a.steps, a.lr, a.warmup_ratio)
-        if a.tp_size > 1 or a.cp_size > 1:
+        if a.tp_size > 1 or a.cp_size > 1 or a.fsdp:
             loss = eng.step(ids.view(-1), tgt.view(-1))
         else:
             loss = eng.step([ids[k * n:(k + 1) * n] for k in range(M)], [tgt[k * n:(k + 1) * n] for k in range(M)])
         if (step + 1) % run.log_every == 0 or step + 1 == a.steps:
+            if a.fsdp:
+                loss = eng.loss()                          # mean over the ranks (a collective)
             t = torch.tensor([loss if loss is not None else 0.0], device=dev)
             f = torch.tensor([1.0 if stop["flag"] else 0.0], device=dev)
             if world > 1:
@@ -538,7 +551,7 @@ def _train_loop_model_parallel(a):
             if logger:
                 logger.log(step + 1, last_loss, eng.hyper["lr"], tokens_seen + B * M * cfg.T, (now - t_last) * 1e3 / max(1, step + 1 - s_last))
             t_last, s_last = now, step + 1
-        tokens_seen += B * M * cfg.T
+        tokens_seen += B * M * cfg.T * (world if a.fsdp else 1)
         if writer is not None and (step + 1) % a.save_every == 0:
             writer.save(a.ckpt_dir, step + 1, last_loss, tokens_seen, holder.master, holder.m, holder.v, rank=rank, shard=(0, nst),
                         loader_pos=loader.pos, opt_t=eng.t, write_meta=False, wait=True)

@@ -288,3 +288,45 @@ class FSDP:
         m.backward(ids, tgt, zero=False)
         self.finish_step()
         return m
+
+
+class FSDPTrainer:
+    """Sharded training behind the interface of the model-parallel trainers (`train_ddp --fsdp`): `step(ids, tgt)` on this
+    rank's own batch (the ranks are data parallel), `loss()` = the mean over the ranks of the last step's losses,
+    `master / m / v` = this rank's 1/world shards (what a per-rank checkpoint holds), `sync_params()` after loading
+    them.  Initial weights are those of the unsharded model for the same seed."""
+
+    def __init__(self, cfg, B: int, device, world: int, rank: int, group=None, comm: str = "nccl", hyper=None, seed: int = 1234):
+        from ..models import GPT
+        self.model = GPT(cfg, B, device, sharded=True)
+        self.f = FSDP(self.model, world, rank, group=group, comm=comm, hyper=hyper)
+        self.model.init_weights(seed)
+        self.world, self.group = world, group
+        self.hyper = self.f.hyper
+
+    master = property(lambda self: self.f.master)
+    m = property(lambda self: self.f.m)
+    v = property(lambda self: self.f.v)
+
+    @property
+    def t(self):
+        return self.f.t
+
+    @t.setter
+    def t(self, value):
+        self.f.t = int(value)
+
+    def sync_params(self):
+        if self.f.pshard.data_ptr() != self.f.master.data_ptr():
+            ops.cast(self.f.pshard, self.f.master)
+
+    def step(self, ids, tgt):
+        self.f.step(ids, tgt)
+        return None                     # the loss is read only when asked for: loss()
+
+    def loss(self) -> float:
+        v = torch.tensor([self.model.mean_loss()], dtype=torch.float32, device=self.model.device)
+        if self.world > 1:
+            dist.all_reduce(v, group=self.group)
+        return float(v.item()) / self.world
+

@@ -445,3 +445,44 @@ def test_a_signal_on_one_rank_stops_all_ranks_at_the_same_step(tmp_path, flags):
     assert "signal received: stopping" in o and "<timeout>" not in o
     last = max(int(l.split()[1]) for l in o.splitlines() if l.startswith("step "))
     assert 5 <= last < 100000 and last % 5 == 0
+
+
+def test_sharded_training_mode_equals_data_parallel_and_resumes(tmp_path):
+    """`train_ddp --fsdp` on two CPU ranks: the losses of plain data-parallel training (same windows per rank, same
+    AdamW), per-rank shard files in the checkpoint, and two steps + resume + two steps equal four uninterrupted ones."""
+    import os
+    import textwrap
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    from ml_b200.utils import ckpt
+    g = _t.Generator().manual_seed(6)
+    path, ck = str(tmp_path / "tok.bin"), str(tmp_path / "ck")
+    write_token_bin(path, _t.randint(0, 64, (2 * 2 * 16 * 8 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "2", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "1", "ENTROPY_DEVICE": "cpu"}
+    body = textwrap.dedent("""
+        import os, sys
+        os.environ.update(ENV)
+        from ml_b200 import gpt
+        sys.exit(gpt.main(ARGS))
+    """)
+    def run(args):
+        outs = run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path] + args + ["--lr", "1e-3"]) + body, 2)
+        assert all(rc == 0 for rc, _ in outs), outs
+        o = [o for _, o in outs if "step " in o][0]
+        return {int(l.split()[1]): float(l.split("loss")[1].split("|")[0]) for l in o.splitlines() if l.startswith("step ")}, o
+    dp, _ = run(["4"])
+    whole, out = run(["4", "--fsdp"])
+    assert "fsdp=1" in out and sorted(whole) == [1, 2, 3, 4]
+    for k in whole:
+        assert abs(whole[k] - dp[k]) < 2e-4, (whole, dp)
+    first, _ = run(["2", "--fsdp", "--ckpt-dir", ck, "--save-every", "2"])
+    shard_bytes = [os.path.getsize(os.path.join(ckpt.step_dir(ck, 2), f"weights_rank_{r}.bin")) for r in (0, 1)]
+    from ml_b200 import Config
+    from ml_b200.layout import DecoderLayout
+    full = DecoderLayout(Config(V=64, C=32, L=2, H=4, I=48, T=16)).num_params * 4
+    assert shard_bytes[0] == shard_bytes[1] and 0.5 * full <= shard_bytes[0] < 0.6 * full      # half of the model each (+ padding)
+    rest, out = run(["4", "--fsdp", "--ckpt-dir", ck, "--resume", "-2"])
+    assert "resumed from step 2" in out and sorted(rest) == [3, 4]
+    for k in (3, 4):
+        assert abs(rest[k] - whole[k]) < 1e-6, (rest, whole)
