@@ -471,9 +471,23 @@ def _train_loop_model_parallel(a):
     B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
     if a.fsdp and (a.pp_size > 1 or a.tp_size > 1 or a.cp_size > 1):
         sys.exit("--fsdp shards a data-parallel model; it is not combined with pipeline, tensor or sequence parallelism here")
-    if not a.fsdp and a.pp_size * a.tp_size * a.cp_size != world:
-        sys.exit(f"--pp-size {a.pp_size} x --tp-size {a.tp_size} x --cp-size {a.cp_size} must equal the number of ranks ({world}); "
-                 "data-parallel replicas of a model-parallel group are not built")
+    mp = 1 if a.fsdp else a.pp_size * a.tp_size * a.cp_size
+    if world % mp:
+        sys.exit(f"--pp-size {a.pp_size} x --tp-size {a.tp_size} x --cp-size {a.cp_size} must divide the number of ranks ({world})")
+    # ranks [d * mp, (d + 1) * mp) form model-parallel group d; the groups are data-parallel replicas of each other
+    # (rank math of the prototype's topology: csrc/src/comm.cu:11-186)
+    dp = 1 if a.fsdp else world // mp
+    d, j = (rank // mp, rank % mp) if not a.fsdp else (0, rank)
+    mp_group = dp_group = None
+    if dp > 1:
+        for dd in range(dp):
+            gq = dist.new_group(list(range(dd * mp, (dd + 1) * mp)))
+            if dd == d:
+                mp_group = gq
+        for jj in range(mp):
+            gq = dist.new_group(list(range(jj, world, mp)))
+            if jj == j:
+                dp_group = gq
     if (a.pp_size > 1) + (a.tp_size > 1) + (a.cp_size > 1) > 1:
         sys.exit("pipeline, tensor and sequence parallelism cannot be combined in one run here")
     hyper = dict(lr=a.lr, wd=a.weight_decay)
@@ -484,21 +498,25 @@ def _train_loop_model_parallel(a):
     elif a.cp_size > 1:
         from .parallel.cp import CPTrainer
         M = 1
-        eng = CPTrainer(cfg, B, dev, mode=a.cp_mode, hyper=hyper)
+        eng = CPTrainer(cfg, B, dev, group=mp_group, mode=a.cp_mode, hyper=hyper)
     elif a.tp_size > 1:
         from .parallel.tp import TPTrainer
         M = 1
-        eng = TPTrainer(cfg, B, rank, world, dev, hyper=hyper)
+        eng = TPTrainer(cfg, B, j, a.tp_size, dev, group=mp_group, hyper=hyper)
     else:
         from .parallel.pp import PipelineStage
         M = a.microbatches if a.microbatches > 0 else run.microbatches
-        eng = PipelineStage(cfg, B, a.pp_size, rank, dev, microbatches=M, hyper=hyper)
+        eng = PipelineStage(cfg, B, a.pp_size, j, dev, microbatches=M, hyper=hyper, prev_rank=d * mp + j - 1, next_rank=d * mp + j + 1)
+    if dp > 1:
+        eng.dp, eng.dp_group = dp, dp_group
     loader = open_token_file(a.bin, B * M, cfg.T, vocab=cfg.V)
     if a.fsdp and world > 1:
         loader.set_stride(rank, world)         # data parallel: every rank its own windows
+    elif dp > 1:
+        loader.set_stride(d, dp)               # every replica its own windows, the same ones on all ranks of a replica
     if rank == 0:
         print(f"training: B={B} T={cfg.T} micro-batches={M} pp={a.pp_size} tp={a.tp_size} cp={a.cp_size} ({a.cp_mode}) "
-              f"fsdp={int(a.fsdp)} steps={a.steps}")
+              f"fsdp={int(a.fsdp)} replicas={dp} steps={a.steps}")
     # Checkpoints: every rank holds its own part of the model (a pipeline stage, a tensor-parallel slice; a replica under
     # sequence parallelism), so every rank writes its flat fp32 master / moment buffers as weights_rank_<r>.bin /
     # optim_rank_<r>.bin; meta.bin is published by rank 0 once all of them are on disk.
@@ -539,11 +557,13 @@ def _train_loop_model_parallel(a):
         if (step + 1) % run.log_every == 0 or step + 1 == a.steps:
             if a.fsdp:
                 loss = eng.loss()                          # mean over the ranks (a collective)
-            t = torch.tensor([loss if loss is not None else 0.0], device=dev)
+            # mean over the ranks that know a loss (a pipeline's last stage; every rank otherwise), hence over the replicas
+            t = torch.tensor([loss if loss is not None else 0.0, 0.0 if loss is None else 1.0], device=dev)
             f = torch.tensor([1.0 if stop["flag"] else 0.0], device=dev)
             if world > 1:
-                dist.broadcast(t, src=world - 1)           # the last stage (any tensor-parallel rank) knows the loss
+                dist.all_reduce(t)
                 dist.all_reduce(f)                         # a signal on any rank stops all of them, at the same step
+            t = t[:1] / t[1].clamp(min=1.0)
             now = time.perf_counter()
             last_loss = float(t.item())
             if rank == 0:
@@ -551,7 +571,7 @@ def _train_loop_model_parallel(a):
             if logger:
                 logger.log(step + 1, last_loss, eng.hyper["lr"], tokens_seen + B * M * cfg.T, (now - t_last) * 1e3 / max(1, step + 1 - s_last))
             t_last, s_last = now, step + 1
-        tokens_seen += B * M * cfg.T * (world if a.fsdp else 1)
+        tokens_seen += B * M * cfg.T * (world if a.fsdp else dp)
         if writer is not None and (step + 1) % a.save_every == 0:
             writer.save(a.ckpt_dir, step + 1, last_loss, tokens_seen, holder.master, holder.m, holder.v, rank=rank, shard=(0, nst),
                         loader_pos=loader.pos, opt_t=eng.t, write_meta=False, wait=True)

@@ -338,6 +338,10 @@ class CPTrainer:
     gets the full token windows, keeps its slice of every sequence, and all ranks apply the same AdamW update to the
     summed gradients (fp32 master weights and moments replicated, as in plain data parallelism)."""
 
+    # data-parallel replicas of the sequence-parallel group: gradients are also summed over `dp_group` (the same
+    # sequence slice of every replica); set by the caller after construction
+    dp, dp_group = 1, None
+
     def __init__(self, cfg: Config, B: int, device, group=None, mode: str = "alltoall", hyper=None, seed: int = 1234):
         assert mode in ("alltoall", "ring", "zigzag")
         self.cfg, self.B, self.group, self.mode = cfg, B, group, mode
@@ -359,8 +363,10 @@ class CPTrainer:
         m.forward(li)
         m.backward(li, lt, valid_tokens=valid)
         reduce_grads(m, self.group)
+        if self.dp > 1:
+            dist.all_reduce(m.grads, group=self.dp_group)
         h = self.hyper
-        m.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], t=self.t)
+        m.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], t=self.t, grad_scale=1.0 / self.dp)
         self.t += 1
         return global_mean_loss(m, valid, self.group)
 

@@ -35,6 +35,10 @@ def stage_layers(L: int, pp: int, s: int):
 
 
 class PipelineStage:
+    # data-parallel replicas of the pipeline: the stage's gradients are summed over `dp_group` (the same stage of every
+    # replica) before its optimizer step; set by the caller after construction
+    dp, dp_group = 1, None
+
     def __init__(self, cfg: Config, B: int, pp: int, stage: int, device="cpu", microbatches: int = 4, group=None,
                  prev_rank: Optional[int] = None, next_rank: Optional[int] = None, seed: int = 1234, hyper=None):
         self.full_cfg, self.pp, self.stage, self.M, self.group = cfg, pp, stage, microbatches, group
@@ -172,6 +176,8 @@ class PipelineStage:
             if not self.first:
                 self._p2p([dist.P2POp(dist.isend, d_in.contiguous(), self.prev_rank, self.group)])
         h = self.hyper
-        m.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, 1.0 / M)
+        if self.dp > 1:
+            dist.all_reduce(m.grads, group=self.dp_group)
+        m.adamw(h["lr"], h["b1"], h["b2"], h["eps"], h["wd"], self.t, 1.0 / (M * self.dp))
         self.t += 1
         return sum(self.losses) / len(self.losses) if self.losses else None

@@ -187,6 +187,10 @@ class TPTrainer:
             self.hyper.update(hyper)
         self.t = 1
 
+    # data-parallel replicas of the tensor-parallel group: this rank's gradient slice is summed over `dp_group` (the
+    # same slice of every replica) before the optimizer step; set by the caller after construction
+    dp, dp_group = 1, None
+
     def sync_params(self):
         """Compute-dtype parameters from the fp32 master weights (after a checkpoint was loaded into them)."""
         if self.params is not self.master:
@@ -200,7 +204,9 @@ class TPTrainer:
         for p, off, n in self.slices:
             self.grads[off:off + n].copy_(p.grad.reshape(-1))
         h = self.hyper
+        if self.dp > 1:
+            torch.distributed.all_reduce(self.grads, group=self.dp_group)
         self.ops.adamw(self.master, self.params, self.grads, self.m, self.v, h["lr"], h["b1"], h["b2"], h["eps"], h["wd"],
-                       1.0 - h["b1"] ** self.t, 1.0 - h["b2"] ** self.t, 1.0, None)
+                       1.0 - h["b1"] ** self.t, 1.0 - h["b2"] ** self.t, 1.0 / self.dp, None)
         self.t += 1
         return float(loss.detach())

@@ -486,3 +486,38 @@ def test_sharded_training_mode_equals_data_parallel_and_resumes(tmp_path):
     assert "resumed from step 2" in out and sorted(rest) == [3, 4]
     for k in (3, 4):
         assert abs(rest[k] - whole[k]) < 1e-6, (rest, whole)
+
+
+def test_data_parallel_replicas_of_model_parallel_groups(tmp_path):
+    """Four CPU ranks.  `--tp-size 2`: two tensor-parallel groups that are data-parallel replicas of each other give the
+    losses of plain data-parallel training on two ranks (same windows per replica, mean gradient).  `--pp-size 2`: two
+    pipelines of two stages give the losses of two single-stage replicas."""
+    import textwrap
+    import torch as _t
+    from ml_b200.data import write_token_bin
+    g = _t.Generator().manual_seed(6)
+    path = str(tmp_path / "tok.bin")
+    write_token_bin(path, _t.randint(0, 64, (2 * 2 * 2 * 16 * 6 + 1,), generator=g, dtype=_t.int32))
+    env = {"ENTROPY_V": "64", "ENTROPY_C": "32", "ENTROPY_L": "2", "ENTROPY_H": "4", "ENTROPY_I": "48", "ENTROPY_T": "16",
+           "ENTROPY_B": "2", "ENTROPY_LOG_EVERY": "1", "ENTROPY_DEVICE": "cpu"}
+    body = textwrap.dedent("""
+        import os, sys
+        os.environ.update(ENV)
+        from ml_b200 import gpt
+        sys.exit(gpt.main(ARGS))
+    """)
+    def run(args, world):
+        outs = run_ranks("ENV = %r\nARGS = %r\n" % (env, ["train_ddp", path, "3"] + args + ["--lr", "1e-3"]) + body, world)
+        assert all(rc == 0 for rc, _ in outs), outs
+        o = [o for _, o in outs if "step " in o][0]
+        return [float(l.split("loss")[1].split("|")[0]) for l in o.splitlines() if l.startswith("step ")], o
+    dp2, _ = run([], 2)
+    tp2dp2, out = run(["--tp-size", "2"], 4)
+    assert "replicas=2" in out and len(tp2dp2) == 3
+    for a, b in zip(tp2dp2, dp2):
+        assert abs(a - b) < 2e-4, (tp2dp2, dp2)
+    one_stage, out1 = run(["--microbatches", "2"], 2)
+    pp2dp2, out2 = run(["--pp-size", "2", "--microbatches", "2"], 4)
+    assert "replicas=2" in out1 and "replicas=2" in out2
+    for a, b in zip(pp2dp2, one_stage):
+        assert abs(a - b) < 2e-4, (pp2dp2, one_stage)
