@@ -490,7 +490,8 @@ def test_sharded_training_mode_equals_data_parallel_and_resumes(tmp_path):
 
 def test_data_parallel_replicas_of_model_parallel_groups(tmp_path):
     """Four CPU ranks.  `--tp-size 2`: two tensor-parallel groups that are data-parallel replicas of each other give the
-    losses of plain data-parallel training on two ranks (same windows per replica, mean gradient).  `--pp-size 2`: two
+    losses of plain data-parallel training on two ranks (same windows per replica, mean gradient); so do two
+    sequence-parallel groups (all-to-all and zig-zag ring, whose messages then go through sub-groups).  `--pp-size 2`: two
     pipelines of two stages give the losses of two single-stage replicas."""
     import textwrap
     import torch as _t
@@ -516,6 +517,11 @@ def test_data_parallel_replicas_of_model_parallel_groups(tmp_path):
     assert "replicas=2" in out and len(tp2dp2) == 3
     for a, b in zip(tp2dp2, dp2):
         assert abs(a - b) < 2e-4, (tp2dp2, dp2)
+    for mode in ("alltoall", "zigzag"):                # sequence-parallel groups inside a larger world
+        cp2dp2, out = run(["--cp-size", "2", "--cp-mode", mode], 4)
+        assert "replicas=2" in out
+        for a, b in zip(cp2dp2, dp2):
+            assert abs(a - b) < 2e-4, (mode, cp2dp2, dp2)
     one_stage, out1 = run(["--microbatches", "2"], 2)
     pp2dp2, out2 = run(["--pp-size", "2", "--microbatches", "2"], 4)
     assert "replicas=2" in out1 and "replicas=2" in out2
