@@ -255,7 +255,7 @@ def _train_loop(argv, ddp):
     ap.add_argument("--init-from", default="", help="start from the weights of a Hugging Face Llama directory of the same shape "
                                                     "(written by the export mode, or any matching checkpoint) instead of the random init")
     ap.add_argument("--max-grad-norm", type=float, default=0.0,
-                    help="clip the gradient of the whole model to this L2 norm (0 = off; with several ranks needs ENTROPY_COMM=nccl)")
+                    help="clip the gradient of the whole model to this L2 norm (0 = off; with several ranks the gradients are reduced by library collectives)")
     ap.add_argument("--max-steps", type=int, default=0, help="same as the positional step count")
     ap.add_argument("--batch-size", type=int, default=0, help="per-GPU micro-batch (default ENTROPY_B or 16)")
     ap.add_argument("--seq-len", type=int, default=0, help="sequence length (default ENTROPY_T)")

@@ -31,6 +31,12 @@ class Trainer:
         self.world, self.rank = world, rank
         cuda = self.device.type == "cuda"
         comm = self.run.comm if cuda else "nccl"
+        if max_grad_norm > 0 and world > 1 and comm == "fused":
+            # clipping needs the norm of the whole reduced gradient before any parameter is updated; the fused step
+            # updates shard by shard while it reduces, so this run reduces with library collectives instead
+            comm = "nccl"
+            if rank == 0:
+                print("note: max_grad_norm with several ranks: gradients are reduced by library collectives (as with ENTROPY_COMM=nccl)")
         alloc = None
         if comm == "fused" and world > 1:
             from .parallel import symm

@@ -218,3 +218,40 @@ def test_trainer_checkpoint_methods_two_ranks(tmp_path):
     assert all(rc == 0 for rc, _ in outs), outs
     got = sorted(l.split()[1:] for _, o in outs for l in o.splitlines() if l.startswith("CK"))
     assert got == [["0", "2", "100", "5", "True"], ["1", "2", "101", "5", "True"]], got
+
+
+def test_gradient_clipping_two_ranks_uses_the_norm_of_the_mean_gradient():
+    """max_grad_norm with two ranks: both ranks see the same norm - that of the gradient averaged over the ranks, i.e. of
+    one model on the concatenated batch - and stay bit-identical."""
+    import torch
+    from ml_b200 import Config
+    from ml_b200.models import GPT
+    from ml_b200.data import bench_batch
+    outs = run_ranks("""
+        import torch, torch.distributed as dist
+        from ml_b200 import Config, RunConfig
+        from ml_b200.parallel.bootstrap import init_distributed, shutdown
+        from ml_b200.trainer import Trainer
+        from ml_b200.data import bench_batch
+        rank, world, local, dev = init_distributed("cpu")
+        cfg = Config(V=64, C=32, L=2, H=2, I=64, T=16)
+        tr = Trainer(cfg, 2, dev, RunConfig(), lr=1e-2, wd=0.0, world=world, rank=rank, max_grad_norm=0.05)
+        ids, tgt = bench_batch(2, 16, 64, rank)
+        tr.set_batch(ids, tgt)
+        tr.step()
+        first = float(tr.grad_norm)
+        for _ in range(2): tr.step()
+        print("CLIP", rank, repr(first), tr.params_equal_across_ranks(), flush=True)
+        shutdown()
+    """)
+    assert all(rc == 0 for rc, _ in outs), outs
+    got = [l.split() for _, o in outs for l in o.splitlines() if l.startswith("CLIP")]
+    assert len(got) == 2 and got[0][2] == got[1][2] and got[0][3] == got[1][3] == "True", got
+    cfg = Config(V=64, C=32, L=2, H=2, I=64, T=16)
+    g = GPT(cfg, 4)
+    g.init_weights(1234)
+    parts = [bench_batch(2, 16, 64, r) for r in (0, 1)]
+    ids, tgt = torch.cat([p[0] for p in parts]), torch.cat([p[1] for p in parts])
+    g.forward(ids)
+    g.backward(ids, tgt)
+    assert abs(float(got[0][2]) - float(g.grads.norm())) < 1e-5 * float(g.grads.norm())
