@@ -469,6 +469,9 @@ def _train_loop_model_parallel(a):
         cfg.T = a.seq_len
     run = RunConfig.from_env()
     B = a.batch_size if a.batch_size > 0 else (run.B if "ENTROPY_B" in os.environ else 16)
+    if a.max_grad_norm > 0 or a.init_from or a.eval_every > 0:
+        sys.exit("--max-grad-norm, --init-from and --eval-every belong to the data-parallel loop; they are not built for "
+                 "--pp-size / --tp-size / --cp-size / --fsdp / --microbatches runs")
     if a.fsdp and (a.pp_size > 1 or a.tp_size > 1 or a.cp_size > 1):
         sys.exit("--fsdp shards a data-parallel model; it is not combined with pipeline, tensor or sequence parallelism here")
     mp = 1 if a.fsdp else a.pp_size * a.tp_size * a.cp_size
